@@ -1,0 +1,192 @@
+/*
+ * C ABI of the B200 (sm_100a) implementation of portDNN's convolution hot path.
+ *
+ * portDNN itself exposes no C ABI: its boundary is the set of C++ launch templates in
+ * include/portdnn/<op>/launch.h, which forward to SNN_EXPORT'ed template instantiations
+ * inside libportdnn.so (e.g. internal::launch_direct, include/portdnn/internal/conv2d/direct.h:34-39).
+ * Every entry point below replaces one such exported launcher; the C++ headers under
+ * include/portdnn/ rebuild the reference's templates on top of these functions.
+ *
+ * Conventions
+ *  - All pointers are device pointers unless stated; the caller owns every buffer.
+ *  - All work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = legacy default
+ *    stream) and the call returns without synchronising.
+ *  - Return value: a PdnnStatus with the numeric values of sycldnn::StatusCode
+ *    (include/portdnn/status.h:31-44). Nothing throws. There is no CPU fallback: without a
+ *    CUDA device every compute entry point returns PDNN_ALLOCATION_PROBLEM.
+ *  - dtype selects the element type of every tensor of the call: fp32 tensors are multiplied
+ *    with a 3xTF32 split on the tensor cores (or fp32 FMA in the direct kernels); fp16/bf16
+ *    tensors accumulate in fp32.
+ */
+#ifndef PORTDNN_B200_H_
+#define PORTDNN_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* sycldnn::StatusCode, include/portdnn/status.h:31-44 */
+typedef enum PdnnStatus {
+  PDNN_OK = 0,
+  PDNN_INVALID_ALGORITHM = 1,
+  PDNN_INDEX_EXCEEDED = 2,
+  PDNN_INSUFFICIENT_WORKSPACE = 3,
+  PDNN_ALLOCATION_PROBLEM = 4,
+  PDNN_INVALID_PARAMETER = 5
+} PdnnStatus;
+
+typedef enum PdnnDataType { PDNN_F32 = 0, PDNN_F16 = 1, PDNN_BF16 = 2 } PdnnDataType;
+
+/* sycldnn::conv2d::conv_type::{Forward,InputBackprop,FilterBackprop}, include/portdnn/conv2d/conv_type.h:32-48 */
+typedef enum PdnnPass { PDNN_FORWARD = 0, PDNN_INPUT_BACKPROP = 1, PDNN_FILTER_BACKPROP = 2 } PdnnPass;
+
+/* sycldnn::conv2d::Algorithm, include/portdnn/conv2d/algorithm.h:30-45.  Direct runs the
+ * general SIMT kernel; Tiled, Im2col and Matmul run the tcgen05 implicit-GEMM kernel (which
+ * needs no im2col buffer); Winograd and WinogradLarge run the fused F(2x2,3x3) kernel where it
+ * applies and the implicit-GEMM kernel otherwise.  A shape the tensor-core kernels cannot take
+ * (channel or feature count not a multiple of 8 elements of 16 bits / 4 of 32 bits) is routed
+ * to the direct kernel whatever the algorithm. */
+typedef enum PdnnAlgorithm {
+  PDNN_ALGO_NOT_SUPPORTED = 0,
+  PDNN_ALGO_DIRECT = 1,
+  PDNN_ALGO_TILED = 2,
+  PDNN_ALGO_IM2COL = 3,
+  PDNN_ALGO_WINOGRAD = 4,
+  PDNN_ALGO_WINOGRAD_LARGE = 5,
+  PDNN_ALGO_MATMUL = 6
+} PdnnAlgorithm;
+
+/* sycldnn::pooling::{Max,MaxWithNan,Average}, include/portdnn/pooling/operators.h */
+typedef enum PdnnPoolOp { PDNN_POOL_MAX = 0, PDNN_POOL_MAX_WITH_NAN = 1, PDNN_POOL_AVERAGE = 2 } PdnnPoolOp;
+
+/* sycldnn::pointwise::{Relu,Tanh}, include/portdnn/pointwise/operators.h.  PDNN_ACT_RELU6 has no
+ * counterpart in the reference (min(max(x,0),6)); it exists for the MobileNet-v2 workload. */
+typedef enum PdnnActivation { PDNN_ACT_NONE = -1, PDNN_ACT_RELU = 0, PDNN_ACT_TANH = 1, PDNN_ACT_RELU6 = 2 } PdnnActivation;
+
+/* Field-for-field mirror of sycldnn::conv2d::Conv2DParams (include/portdnn/conv2d/params.h:32-112).
+ * input_format: 0 NHWC, 1 NCHW (include/portdnn/data_format.h:31-43); filter_format: 0 HWCF, 1 FCHW,
+ * 2 FHWC (include/portdnn/filter_format.h:32-53); group_format: 0 STRIDED, 1 INTERLEAVED. */
+typedef struct PdnnConv2DParams {
+  int channels, features, batch, in_rows, in_cols;
+  int window_rows, window_cols, stride_rows, stride_cols;
+  int out_rows, out_cols, pad_rows, pad_cols;
+  int dilation_rows, dilation_cols, groups;
+  int input_format, filter_format, group_format;
+} PdnnConv2DParams;
+
+/* Mirror of sycldnn::depthwise_conv2d::DepthwiseConv2DParams (include/portdnn/depthwise_conv2d/params.h:33-94). */
+typedef struct PdnnDepthwiseConv2DParams {
+  int channels, channel_multiplier, batch, in_rows, in_cols;
+  int window_rows, window_cols, stride_rows, stride_cols;
+  int out_rows, out_cols, pad_rows, pad_cols;
+} PdnnDepthwiseConv2DParams;
+
+/* Mirror of sycldnn::pooling::PoolingParams (include/portdnn/pooling/params.h:30-73). */
+typedef struct PdnnPoolingParams {
+  int in_rows, in_cols, out_rows, out_cols;
+  int window_rows, window_cols, stride_rows, stride_cols;
+  int batch, channels, pad_rows, pad_cols;
+  int input_format;
+} PdnnPoolingParams;
+
+/* Optional fused epilogue of the forward convolution: out = act(alpha*conv + bias[k]) + beta*out_prev.
+ * The reference has no fused form: it issues binaryop Add (tools/layer.h:100-125), a pointwise
+ * launch (tools/layer.h:207-228) and the compat alpha/beta blend (include/portdnn/compat/scaling.hpp:202-281)
+ * as separate kernels; the fused result matches that chain. bias may be NULL. */
+typedef struct PdnnConvEpilogue {
+  const void* bias;  /* [features], same dtype as the tensors; NULL = none */
+  int activation;    /* PdnnActivation */
+  float alpha;       /* scales the convolution result; 1 = plain */
+  float beta;        /* scales the previous contents of out; 0 = overwrite */
+} PdnnConvEpilogue;
+
+/* Replaces conv2d::launch -> sublaunch -> launch_{direct,tiled,im2col,winograd,matmul}
+ * (include/portdnn/conv2d/launch.h:59-118, include/portdnn/internal/conv2d/launch.h:169-207).
+ * Argument slots as in the reference: Forward (x, w, y); InputBackprop (dy, w, dx);
+ * FilterBackprop (x, dy, dW).  workspace_elems counts ELEMENTS of dtype, as
+ * query_workspace_size does (include/portdnn/conv2d/workspace_size.h:42-47). When the chosen
+ * kernel needs scratch and workspace is NULL or too small the library takes it from the
+ * stream-ordered allocator (cudaMallocAsync) for the duration of the call, the way the
+ * reference's im2col driver self-allocates (include/portdnn/internal/conv2d/im2col.h:224-246). */
+int pdnn_conv2d(int pass, int dtype, const void* input, const void* filter, void* output,
+                const PdnnConv2DParams* params, int algorithm, void* workspace, size_t workspace_elems,
+                void* stream);
+
+/* As pdnn_conv2d for PDNN_FORWARD, with the fused epilogue described at PdnnConvEpilogue. */
+int pdnn_conv2d_fused(int dtype, const void* input, const void* filter, void* output,
+                      const PdnnConv2DParams* params, int algorithm, const PdnnConvEpilogue* epilogue,
+                      void* workspace, size_t workspace_elems, void* stream);
+
+/* Replaces conv2d::query_workspace_size (include/portdnn/conv2d/workspace_size.h:158-163). Sizes in elements. */
+int pdnn_conv2d_workspace_size(int pass, int dtype, const PdnnConv2DParams* params, int algorithm,
+                               size_t* required_elems, size_t* recommended_elems);
+
+/* Parameter checks of conv2d::validate_params + sublaunch (include/portdnn/internal/conv2d/launch.h:42-97,169-197)
+ * without launching anything; host only. */
+int pdnn_conv2d_validate(int pass, const PdnnConv2DParams* params, int algorithm);
+
+/* Replaces depthwise_conv2d::launch (include/portdnn/depthwise_conv2d/launch.h:54-91,
+ * src/depthwise_conv2d/launch.cc:41-121).  Filter is [R][S][C][mult]; slots as for pdnn_conv2d.
+ * The filter-backprop pass reduces over batch and image in two stages and needs
+ * pdnn_depthwise_workspace_bytes() of scratch; with workspace NULL it is taken from the
+ * stream-ordered allocator. */
+int pdnn_depthwise_conv2d(int pass, int dtype, const void* input, const void* filter, void* output,
+                          const PdnnDepthwiseConv2DParams* params, void* workspace, size_t workspace_bytes,
+                          void* stream);
+size_t pdnn_depthwise_workspace_bytes(int pass, int dtype, const PdnnDepthwiseConv2DParams* params);
+
+/* Replaces pooling::launch, two-pointer form (include/portdnn/pooling/launch.h:112-180,
+ * src/pooling/launch_pooling.cc:89-165): forward for every op (input -> output) and the
+ * average gradient (direction 1: input = dy, output = dx).  NHWC only. */
+int pdnn_pooling(int op, int direction, int dtype, const void* input, void* output,
+                 const PdnnPoolingParams* params, void* stream);
+
+/* Replaces pooling::launch, four-pointer form for the max gradient
+ * (include/portdnn/pooling/launch.h:182-257): (x, y, dy) -> dx. */
+int pdnn_pooling_max_grad(int op, int dtype, const void* input_data, const void* output_data,
+                          const void* input_backprop, void* output_backprop,
+                          const PdnnPoolingParams* params, void* stream);
+
+/* Replaces pointwise::launch forward / gradient (include/portdnn/pointwise/launch.h:61-179).
+ * The gradient's first tensor is the forward OUTPUT, as the reference kernel treats it
+ * (src/pointwise/kernels.h:205-233). */
+int pdnn_pointwise(int op, int dtype, const void* input, void* output, size_t n_items, void* stream);
+int pdnn_pointwise_grad(int op, int dtype, const void* output_forward, const void* input_backprop,
+                        void* output_backprop, size_t n_items, void* stream);
+
+/* Replaces binaryop::launch<Add> in its bias form, lhs_dims={rows,C}, rhs_dims={1,C}
+ * (include/portdnn/binaryop/launch.h:58-97, test/bias/bias_fixture.h:78-85), optionally followed
+ * by an activation in the same pass (PDNN_ACT_NONE for the plain reference behaviour). */
+int pdnn_bias_add(int dtype, const void* input, const void* bias, void* output, size_t rows, int channels,
+                  int activation, void* stream);
+
+/* out = alpha*a + beta*b elementwise (b may be NULL when beta == 0): the compat layer's
+ * alpha/beta blend, include/portdnn/compat/scaling.hpp:202-281, as one pass. */
+int pdnn_scale_blend(int dtype, const void* a, float alpha, const void* b, float beta, void* out, size_t n_items,
+                     void* stream);
+
+/* Replaces matmul::launch / Backend::matmul / Backend::batch_matmul
+ * (include/portdnn/matmul/launch.h:37-90, include/portdnn/backend/backend_interface.h:78-118):
+ * out[b] = beta*out[b] + op(lhs[b]) * op(rhs[b]), row-major, strided batches. */
+int pdnn_matmul(int dtype, int transpose_lhs, int transpose_rhs, const void* lhs, const void* rhs, void* output,
+                int batches, int m, int k, int n, float beta, void* stream);
+
+/* Reads (and optionally clears) the 4-word record the tensor-core kernels fill when one of
+ * their bounded waits gives up instead of spinning: word 0 is 0 when nothing went wrong, else
+ * 1 (wait timed out), word 1 the CTA, word 2 the wait site, word 3 the phase parity.
+ * Synchronises the device.  The reference has no counterpart (its kernels never wait on one
+ * another). */
+int pdnn_device_error_record(unsigned words[4], int clear);
+
+/* Text of the last failure recorded by this thread ("" if none); host only. */
+const char* pdnn_last_error(void);
+
+/* Number of kernels this library has launched in the calling process; host only. */
+unsigned long long pdnn_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PORTDNN_B200_H_ */

@@ -1,0 +1,210 @@
+// extern "C" entry points declared in include/portdnn_b200.h.
+#include "common.cuh"
+#include "tc_gemm.cuh"
+
+#include <mutex>
+
+namespace pdnn {
+
+std::atomic<unsigned long long> g_launches{0};
+
+char* last_error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+int device_sm_count() {
+  static int sms = -2;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    int dev = 0;
+    cudaDeviceProp prop;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
+      cudaGetLastError();
+      sms = -1;
+      return;
+    }
+    sms = prop.major >= 10 ? prop.multiProcessorCount : -1;  // the kernels are sm_100a only
+  });
+  return sms;
+}
+
+namespace {
+
+// conv2d::validate_params + the checks of sublaunch (include/portdnn/internal/conv2d/launch.h:42-97,169-197).
+int validate_conv(int pass, const PdnnConv2DParams* p, int algorithm) {
+  if (p == nullptr) return fail(PDNN_INVALID_PARAMETER, "conv2d: null params");
+  if (pass < 0 || pass > 2) return fail(PDNN_INVALID_PARAMETER, "conv2d: bad pass %d", pass);
+#define PDNN_REQUIRE(cond, msg) \
+  if (!(cond)) return fail(PDNN_INVALID_PARAMETER, "conv2d: %s", msg)
+  PDNN_REQUIRE(p->batch > 0, "The number of batches must be positive.");
+  PDNN_REQUIRE(p->channels > 0, "The number of channels must be positive.");
+  PDNN_REQUIRE(p->features > 0, "The number of features must be positive.");
+  PDNN_REQUIRE(p->in_rows > 0, "The number of input rows must be positive.");
+  PDNN_REQUIRE(p->in_cols > 0, "The number of input columns must be positive.");
+  PDNN_REQUIRE(p->out_rows > 0, "The number of output rows must be positive.");
+  PDNN_REQUIRE(p->out_cols > 0, "The number of output columns must be positive.");
+  PDNN_REQUIRE(p->window_rows > 0, "The number of window rows must be positive.");
+  PDNN_REQUIRE(p->window_cols > 0, "The number of window columns must be positive.");
+  PDNN_REQUIRE(p->stride_rows > 0, "The stride in the row direction must be positive.");
+  PDNN_REQUIRE(p->stride_cols > 0, "The stride in the column direction must be positive.");
+  PDNN_REQUIRE(p->pad_rows >= 0, "The padding in the row direction must be non-negative.");
+  PDNN_REQUIRE(p->pad_cols >= 0, "The padding in the column direction must be non-negative.");
+  PDNN_REQUIRE(p->groups > 0, "The number of groups must be positive.");
+  PDNN_REQUIRE(p->channels % p->groups == 0, "Channels must be divisible by groups.");
+  PDNN_REQUIRE(p->features % p->groups == 0, "Features must be divisible by groups.");
+  PDNN_REQUIRE(p->dilation_rows == 1 && p->dilation_cols == 1, "Only dilation 1 is supported.");
+  PDNN_REQUIRE(p->input_format != 0 || p->filter_format == 0 || p->filter_format == 2, "Unsupported layout combination.");
+  PDNN_REQUIRE(p->input_format != 1 || p->filter_format == 1, "Unsupported layout combination.");
+  PDNN_REQUIRE(p->input_format == 0 || p->input_format == 1, "Unknown input format.");
+  PDNN_REQUIRE(p->groups != 1 || p->group_format == 0, "Interleaved is unsupported when group size is one.");
+  PDNN_REQUIRE(p->group_format != 1 || p->filter_format == 0, "Unsupported group and filter format combination.");
+  PDNN_REQUIRE(p->groups == 1 || pass == PDNN_FORWARD, "Grouped convolution is only supported for the forward pass.");
+#undef PDNN_REQUIRE
+  if (algorithm <= PDNN_ALGO_NOT_SUPPORTED || algorithm > PDNN_ALGO_MATMUL)
+    return fail(PDNN_INVALID_ALGORITHM, "conv2d: algorithm %d is not runnable", algorithm);
+  if (p->input_format == 1 && algorithm != PDNN_ALGO_DIRECT)
+    return fail(PDNN_INVALID_ALGORITHM, "conv2d: NCHW is only supported by the direct algorithm");
+  if (p->groups > 1 && algorithm != PDNN_ALGO_IM2COL)
+    return fail(PDNN_INVALID_ALGORITHM, "conv2d: grouped convolution is only supported by the im2col algorithm");
+  // Per-algorithm applicability, as the reference's launchers report it.
+  if (algorithm == PDNN_ALGO_MATMUL &&
+      !(p->window_rows == 1 && p->window_cols == 1 && p->stride_rows == 1 && p->stride_cols == 1 && p->pad_rows == 0 &&
+        p->pad_cols == 0))
+    return fail(PDNN_INVALID_ALGORITHM, "conv2d: the matmul algorithm needs a 1x1 window, stride 1 and no padding");
+  return PDNN_OK;
+}
+
+int run_conv(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams* p, int algorithm,
+             const PdnnConvEpilogue* epi, void* ws, size_t ws_elems, void* stream) {
+  int st = validate_conv(pass, p, algorithm);
+  if (st != PDNN_OK) return st;
+  if (dtype < PDNN_F32 || dtype > PDNN_BF16) return fail(PDNN_INVALID_PARAMETER, "conv2d: unknown dtype %d", dtype);
+  if (in == nullptr || fil == nullptr || out == nullptr) return fail(PDNN_INVALID_PARAMETER, "conv2d: null tensor");
+  if (device_sm_count() <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "conv2d: no sm_100 CUDA device");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (algorithm != PDNN_ALGO_DIRECT && tc_conv_supported(pass, dtype, in, fil, out, *p))
+    return tc_conv2d(pass, dtype, in, fil, out, *p, epi, ws, ws_elems, s);
+  return launch_direct_conv(pass, dtype, in, fil, out, *p, epi, s);
+}
+
+}  // namespace
+}  // namespace pdnn
+
+using namespace pdnn;
+
+extern "C" {
+
+int pdnn_conv2d(int pass, int dtype, const void* input, const void* filter, void* output,
+                const PdnnConv2DParams* params, int algorithm, void* workspace, size_t workspace_elems, void* stream) {
+  return run_conv(pass, dtype, input, filter, output, params, algorithm, nullptr, workspace, workspace_elems, stream);
+}
+
+int pdnn_conv2d_fused(int dtype, const void* input, const void* filter, void* output, const PdnnConv2DParams* params,
+                      int algorithm, const PdnnConvEpilogue* epilogue, void* workspace, size_t workspace_elems,
+                      void* stream) {
+  if (epilogue != nullptr && (epilogue->activation < PDNN_ACT_NONE || epilogue->activation > PDNN_ACT_RELU6))
+    return fail(PDNN_INVALID_PARAMETER, "conv2d: unknown activation %d", epilogue->activation);
+  return run_conv(PDNN_FORWARD, dtype, input, filter, output, params, algorithm, epilogue, workspace, workspace_elems,
+                  stream);
+}
+
+int pdnn_conv2d_validate(int pass, const PdnnConv2DParams* params, int algorithm) {
+  return validate_conv(pass, params, algorithm);
+}
+
+int pdnn_conv2d_workspace_size(int pass, int dtype, const PdnnConv2DParams* params, int algorithm,
+                               size_t* required_elems, size_t* recommended_elems) {
+  if (required_elems) *required_elems = 0;
+  if (recommended_elems) *recommended_elems = 0;
+  int st = validate_conv(pass, params, algorithm);
+  if (st != PDNN_OK) return st;
+  if (algorithm == PDNN_ALGO_DIRECT) return PDNN_OK;
+  // The implicit-GEMM kernels read the tensors in place; only the filter backprop's split
+  // reduction wants scratch, and it can do without (it then allocates for the call).
+  const size_t elems = tc_conv_workspace_elems(pass, dtype, *params);
+  if (recommended_elems) *recommended_elems = elems;
+  return PDNN_OK;
+}
+
+int pdnn_depthwise_conv2d(int pass, int dtype, const void* input, const void* filter, void* output,
+                          const PdnnDepthwiseConv2DParams* params, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  if (params == nullptr || input == nullptr || filter == nullptr || output == nullptr)
+    return fail(PDNN_INVALID_PARAMETER, "depthwise: null argument");
+  return launch_depthwise(pass, dtype, input, filter, output, *params, workspace, workspace_bytes,
+                          static_cast<cudaStream_t>(stream));
+}
+
+size_t pdnn_depthwise_workspace_bytes(int pass, int dtype, const PdnnDepthwiseConv2DParams* params) {
+  if (params == nullptr) return 0;
+  return depthwise_workspace_bytes(pass, dtype, *params);
+}
+
+int pdnn_pooling(int op, int direction, int dtype, const void* input, void* output, const PdnnPoolingParams* params,
+                 void* stream) {
+  if (params == nullptr || input == nullptr || output == nullptr) return fail(PDNN_INVALID_PARAMETER, "pooling: null argument");
+  return launch_pooling(op, direction, dtype, input, output, *params, static_cast<cudaStream_t>(stream));
+}
+
+int pdnn_pooling_max_grad(int op, int dtype, const void* input_data, const void* output_data,
+                          const void* input_backprop, void* output_backprop, const PdnnPoolingParams* params,
+                          void* stream) {
+  if (params == nullptr || input_data == nullptr || output_data == nullptr || input_backprop == nullptr ||
+      output_backprop == nullptr)
+    return fail(PDNN_INVALID_PARAMETER, "pooling: null argument");
+  return launch_pooling_max_grad(op, dtype, input_data, output_data, input_backprop, output_backprop, *params,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int pdnn_pointwise(int op, int dtype, const void* input, void* output, size_t n_items, void* stream) {
+  if (n_items != 0 && (input == nullptr || output == nullptr)) return fail(PDNN_INVALID_PARAMETER, "pointwise: null tensor");
+  return launch_pointwise(op, dtype, input, output, n_items, static_cast<cudaStream_t>(stream));
+}
+
+int pdnn_pointwise_grad(int op, int dtype, const void* output_forward, const void* input_backprop,
+                        void* output_backprop, size_t n_items, void* stream) {
+  if (n_items != 0 && (output_forward == nullptr || input_backprop == nullptr || output_backprop == nullptr))
+    return fail(PDNN_INVALID_PARAMETER, "pointwise: null tensor");
+  return launch_pointwise_grad(op, dtype, output_forward, input_backprop, output_backprop, n_items,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int pdnn_bias_add(int dtype, const void* input, const void* bias, void* output, size_t rows, int channels,
+                  int activation, void* stream) {
+  if (rows != 0 && (input == nullptr || bias == nullptr || output == nullptr))
+    return fail(PDNN_INVALID_PARAMETER, "bias: null tensor");
+  return launch_bias_add(dtype, input, bias, output, rows, channels, activation, static_cast<cudaStream_t>(stream));
+}
+
+int pdnn_scale_blend(int dtype, const void* a, float alpha, const void* b, float beta, void* out, size_t n_items,
+                     void* stream) {
+  if (n_items != 0 && (a == nullptr || out == nullptr || (beta != 0.f && b == nullptr)))
+    return fail(PDNN_INVALID_PARAMETER, "blend: null tensor");
+  return launch_scale_blend(dtype, a, alpha, b, beta, out, n_items, static_cast<cudaStream_t>(stream));
+}
+
+int pdnn_matmul(int dtype, int transpose_lhs, int transpose_rhs, const void* lhs, const void* rhs, void* output,
+                int batches, int m, int k, int n, float beta, void* stream) {
+  if (batches <= 0 || m <= 0 || k <= 0 || n <= 0) return fail(PDNN_INVALID_PARAMETER, "matmul: sizes must be positive");
+  if (lhs == nullptr || rhs == nullptr || output == nullptr) return fail(PDNN_INVALID_PARAMETER, "matmul: null tensor");
+  if (dtype < PDNN_F32 || dtype > PDNN_BF16) return fail(PDNN_INVALID_PARAMETER, "matmul: unknown dtype %d", dtype);
+  if (device_sm_count() <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "matmul: no sm_100 CUDA device");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int tl = transpose_lhs != 0, tr = transpose_rhs != 0;
+  if (tc_matmul_supported(dtype, tl, tr, lhs, rhs, output, batches, m, k, n))
+    return tc_matmul(dtype, tl, tr, lhs, rhs, output, batches, m, k, n, beta, s);
+  return simt_matmul(dtype, tl, tr, lhs, rhs, output, batches, m, k, n, beta, s);
+}
+
+int pdnn_device_error_record(unsigned words[4], int clear) {
+  if (words == nullptr) return fail(PDNN_INVALID_PARAMETER, "null output");
+  if (device_sm_count() <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no sm_100 CUDA device");
+  return tc_read_error_record(words, clear);
+}
+
+const char* pdnn_last_error(void) { return last_error_buffer(); }
+
+unsigned long long pdnn_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"

@@ -1,0 +1,711 @@
+// HBM-bound operators for NHWC tensors: pooling, depthwise convolution, pointwise
+// activations, bias add and the alpha/beta blend.  One thread owns a 16-byte packet of
+// channels (8 halves or 4 floats) of one pixel, so that a warp reads and writes whole
+// 512-byte lines along the channel axis; shapes whose channel count is not a multiple of
+// the packet fall back to one element per thread.  Arithmetic is done in fp32 and rounded
+// once on store.
+//
+// Semantics follow portDNN: src/pooling/kernels.h, src/pooling/operators_impl.h,
+// src/depthwise_conv2d/kernels.h, src/pointwise/kernels.h, src/binaryop/kernels.h.
+#include "common.cuh"
+
+#include <cfloat>
+
+namespace pdnn {
+
+namespace {
+
+constexpr int kBlock = 256;
+
+template <typename T>
+__device__ __forceinline__ float lowest_of();
+template <>
+__device__ __forceinline__ float lowest_of<float>() { return -FLT_MAX; }
+template <>
+__device__ __forceinline__ float lowest_of<__half>() { return -65504.f; }
+template <>
+__device__ __forceinline__ float lowest_of<__nv_bfloat16>() { return -3.3895313892515355e38f; }
+
+// V elements starting at p: one 16-byte load when V > 1.
+template <typename T, int V>
+__device__ __forceinline__ void load_vec(const T* p, float (&v)[V]) {
+  if constexpr (V == 1) {
+    v[0] = to_f32(__ldg(p));
+  } else {
+    Vec16<T> pk = load16(p);
+#pragma unroll
+    for (int i = 0; i < V; ++i) v[i] = to_f32(pk.get(i));
+  }
+}
+template <typename T, int V>
+__device__ __forceinline__ void store_vec(T* p, const float (&v)[V]) {
+  if constexpr (V == 1) {
+    p[0] = from_f32<T>(v[0]);
+  } else {
+    Vec16<T> pk;
+#pragma unroll
+    for (int i = 0; i < V; ++i) pk.set(i, from_f32<T>(v[i]));
+    store16(p, pk);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Pooling forward.  Window clamped to the image; Average divides by the valid count
+// (src/pooling/kernels.h:61-101).  Max keeps v only if v > max starting from lowest(), so a
+// NaN never wins; MaxWithNan takes a NaN and then keeps it (src/pooling/operators_impl.h:27-65).
+// ------------------------------------------------------------------------------------------
+template <typename T, int OP, int V, typename Index>
+__global__ void __launch_bounds__(kBlock) pool_forward_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                              PdnnPoolingParams p, Index n_items) {
+  const Index cvecs = (Index)(p.channels / V);
+  for (Index idx = (Index)blockIdx.x * kBlock + threadIdx.x; idx < n_items; idx += (Index)gridDim.x * kBlock) {
+    const Index cv = idx % cvecs;
+    Index t = idx / cvecs;
+    const int ow = (int)(t % (Index)p.out_cols);
+    t /= (Index)p.out_cols;
+    const int oh = (int)(t % (Index)p.out_rows);
+    const int n = (int)(t / (Index)p.out_rows);
+    int r0 = oh * p.stride_rows - p.pad_rows, c0 = ow * p.stride_cols - p.pad_cols;
+    const int r1 = min(r0 + p.window_rows, p.in_rows), c1 = min(c0 + p.window_cols, p.in_cols);
+    r0 = max(r0, 0);
+    c0 = max(c0, 0);
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = (OP == PDNN_POOL_AVERAGE) ? 0.f : lowest_of<T>();
+    const T* xn = x + (size_t)n * p.in_rows * p.in_cols * p.channels + (size_t)cv * V;
+    for (int r = r0; r < r1; ++r) {
+      for (int c = c0; c < c1; ++c) {
+        float v[V];
+        load_vec<T, V>(xn + ((size_t)r * p.in_cols + c) * p.channels, v);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          if (OP == PDNN_POOL_MAX) {
+            if (v[i] > acc[i]) acc[i] = v[i];
+          } else if (OP == PDNN_POOL_MAX_WITH_NAN) {
+            if (isnan(v[i]) || v[i] > acc[i]) acc[i] = v[i];
+          } else {
+            acc[i] += v[i];
+          }
+        }
+      }
+    }
+    if (OP == PDNN_POOL_AVERAGE) {
+      const float tally = (float)((r1 - r0) * (c1 - c0));
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = acc[i] / tally;
+    }
+    store_vec<T, V>(y + (size_t)idx * V, acc);
+  }
+}
+
+template <int OP>
+__device__ __forceinline__ bool pool_equal(float a, float b) {
+  // src/pooling/operators_impl.h:89-108
+  if (OP == PDNN_POOL_MAX_WITH_NAN) return a == b || (isnan(a) && isnan(b));
+  return a == b;
+}
+
+// ------------------------------------------------------------------------------------------
+// Max-pool gradient (src/pooling/kernels.h:142-243): dx[i] collects dy[o] from every output o
+// whose clamped window holds i, if x[i] == y[o] and no earlier element of that window
+// (row-major) equals y[o].  The scan for an earlier maximum only runs for lanes that matched.
+// ------------------------------------------------------------------------------------------
+template <typename T, int OP, int V, typename Index>
+__global__ void __launch_bounds__(kBlock)
+    pool_max_grad_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy,
+                         T* __restrict__ dx, PdnnPoolingParams p, Index n_items) {
+  const Index cvecs = (Index)(p.channels / V);
+  for (Index idx = (Index)blockIdx.x * kBlock + threadIdx.x; idx < n_items; idx += (Index)gridDim.x * kBlock) {
+    const Index cv = idx % cvecs;
+    Index t = idx / cvecs;
+    const int w = (int)(t % (Index)p.in_cols);
+    t /= (Index)p.in_cols;
+    const int h = (int)(t % (Index)p.in_rows);
+    const int n = (int)(t / (Index)p.in_rows);
+    float xv[V], grad[V];
+    load_vec<T, V>(x + (size_t)idx * V, xv);
+#pragma unroll
+    for (int i = 0; i < V; ++i) grad[i] = 0.f;
+    const int hp = h + p.pad_rows, wp = w + p.pad_cols;
+    const int oh_lo = hp < p.window_rows ? 0 : (hp - p.window_rows) / p.stride_rows + 1;
+    const int oh_hi = min(hp / p.stride_rows + 1, p.out_rows);
+    const int ow_lo = wp < p.window_cols ? 0 : (wp - p.window_cols) / p.stride_cols + 1;
+    const int ow_hi = min(wp / p.stride_cols + 1, p.out_cols);
+    const T* xn = x + (size_t)n * p.in_rows * p.in_cols * p.channels + (size_t)cv * V;
+    const size_t out_n = (size_t)n * p.out_rows * p.out_cols * p.channels + (size_t)cv * V;
+    for (int oh = oh_lo; oh < oh_hi; ++oh) {
+      int r0 = oh * p.stride_rows - p.pad_rows;
+      const int r1 = min(r0 + p.window_rows, p.in_rows);
+      r0 = max(r0, 0);
+      for (int ow = ow_lo; ow < ow_hi; ++ow) {
+        int c0 = ow * p.stride_cols - p.pad_cols;
+        const int c1 = min(c0 + p.window_cols, p.in_cols);
+        c0 = max(c0, 0);
+        const size_t o = out_n + ((size_t)oh * p.out_cols + ow) * p.channels;
+        float yv[V];
+        load_vec<T, V>(y + o, yv);
+        bool hit[V];
+        bool any = false;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          hit[i] = pool_equal<OP>(xv[i], yv[i]);
+          any |= hit[i];
+        }
+        if (!any) continue;
+        bool scanning = true;
+        for (int r = r0; r < r1 && scanning; ++r) {
+          for (int c = c0; c < c1; ++c) {
+            if (r == h && c == w) {
+              scanning = false;
+              break;
+            }
+            float ev[V];
+            load_vec<T, V>(xn + ((size_t)r * p.in_cols + c) * p.channels, ev);
+#pragma unroll
+            for (int i = 0; i < V; ++i)
+              if (pool_equal<OP>(ev[i], yv[i])) hit[i] = false;
+          }
+        }
+        float dv[V];
+        load_vec<T, V>(dy + o, dv);
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+          if (hit[i]) grad[i] += dv[i];
+      }
+    }
+    store_vec<T, V>(dx + (size_t)idx * V, grad);
+  }
+}
+
+// Average-pool gradient (src/pooling/kernels.h:312-366): dx[i] = sum_o dy[o] / valid(o).
+template <typename T, int V, typename Index>
+__global__ void __launch_bounds__(kBlock)
+    pool_avg_grad_kernel(const T* __restrict__ dy, T* __restrict__ dx, PdnnPoolingParams p, Index n_items) {
+  const Index cvecs = (Index)(p.channels / V);
+  for (Index idx = (Index)blockIdx.x * kBlock + threadIdx.x; idx < n_items; idx += (Index)gridDim.x * kBlock) {
+    const Index cv = idx % cvecs;
+    Index t = idx / cvecs;
+    const int w = (int)(t % (Index)p.in_cols);
+    t /= (Index)p.in_cols;
+    const int h = (int)(t % (Index)p.in_rows);
+    const int n = (int)(t / (Index)p.in_rows);
+    float grad[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) grad[i] = 0.f;
+    const int hp = h + p.pad_rows, wp = w + p.pad_cols;
+    const int oh_lo = hp < p.window_rows ? 0 : (hp - p.window_rows) / p.stride_rows + 1;
+    const int oh_hi = min(hp / p.stride_rows + 1, p.out_rows);
+    const int ow_lo = wp < p.window_cols ? 0 : (wp - p.window_cols) / p.stride_cols + 1;
+    const int ow_hi = min(wp / p.stride_cols + 1, p.out_cols);
+    const size_t out_n = (size_t)n * p.out_rows * p.out_cols * p.channels + (size_t)cv * V;
+    for (int oh = oh_lo; oh < oh_hi; ++oh) {
+      int r0 = oh * p.stride_rows - p.pad_rows;
+      const int r1 = min(r0 + p.window_rows, p.in_rows);
+      r0 = max(r0, 0);
+      for (int ow = ow_lo; ow < ow_hi; ++ow) {
+        int c0 = ow * p.stride_cols - p.pad_cols;
+        const int c1 = min(c0 + p.window_cols, p.in_cols);
+        c0 = max(c0, 0);
+        const float cnt = (float)((r1 - r0) * (c1 - c0));
+        float dv[V];
+        load_vec<T, V>(dy + out_n + ((size_t)oh * p.out_cols + ow) * p.channels, dv);
+#pragma unroll
+        for (int i = 0; i < V; ++i) grad[i] += dv[i] / cnt;
+      }
+    }
+    store_vec<T, V>(dx + (size_t)idx * V, grad);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Depthwise convolution.  Filter [R][S][C][mult], output channel c*mult+m
+// (src/depthwise_conv2d/kernels.h:58-125).  The packet form needs mult == 1.
+// ------------------------------------------------------------------------------------------
+template <typename T, int V, typename Index>
+__global__ void __launch_bounds__(kBlock)
+    depthwise_forward_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                             PdnnDepthwiseConv2DParams p, Index n_items) {
+  const int F = p.channels * p.channel_multiplier;
+  const Index fvecs = (Index)(F / V);
+  for (Index idx = (Index)blockIdx.x * kBlock + threadIdx.x; idx < n_items; idx += (Index)gridDim.x * kBlock) {
+    const int f = (int)(idx % fvecs) * V;
+    Index t = idx / fvecs;
+    const int ow = (int)(t % (Index)p.out_cols);
+    t /= (Index)p.out_cols;
+    const int oh = (int)(t % (Index)p.out_rows);
+    const int n = (int)(t / (Index)p.out_rows);
+    const int c = (V == 1) ? f / p.channel_multiplier : f;
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 0.f;
+    const T* xn = x + (size_t)n * p.in_rows * p.in_cols * p.channels + c;
+    const int ih0 = oh * p.stride_rows - p.pad_rows, iw0 = ow * p.stride_cols - p.pad_cols;
+    for (int r = 0; r < p.window_rows; ++r) {
+      const int ih = ih0 + r;
+      if (ih < 0 || ih >= p.in_rows) continue;
+      for (int s = 0; s < p.window_cols; ++s) {
+        const int iw = iw0 + s;
+        if (iw < 0 || iw >= p.in_cols) continue;
+        float xv[V], wv[V];
+        load_vec<T, V>(xn + ((size_t)ih * p.in_cols + iw) * p.channels, xv);
+        load_vec<T, V>(w + ((size_t)r * p.window_cols + s) * F + f, wv);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fmaf(xv[i], wv[i], acc[i]);
+      }
+    }
+    store_vec<T, V>(y + (size_t)idx * V, acc);
+  }
+}
+
+// Input backprop (src/depthwise_conv2d/kernels.h:154-225): dx[n,h,w,c] = sum over taps (r,s)
+// with (h+pad-r) divisible by the stride, and over the multiplier, of dy * w.
+template <typename T, int V, typename Index>
+__global__ void __launch_bounds__(kBlock)
+    depthwise_input_backprop_kernel(const T* __restrict__ dy, const T* __restrict__ w, T* __restrict__ dx,
+                                    PdnnDepthwiseConv2DParams p, Index n_items) {
+  const int M = p.channel_multiplier, F = p.channels * M;
+  const Index cvecs = (Index)(p.channels / V);
+  for (Index idx = (Index)blockIdx.x * kBlock + threadIdx.x; idx < n_items; idx += (Index)gridDim.x * kBlock) {
+    const int c = (int)(idx % cvecs) * V;
+    Index t = idx / cvecs;
+    const int wi = (int)(t % (Index)p.in_cols);
+    t /= (Index)p.in_cols;
+    const int h = (int)(t % (Index)p.in_rows);
+    const int n = (int)(t / (Index)p.in_rows);
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 0.f;
+    const T* dyn = dy + (size_t)n * p.out_rows * p.out_cols * F + (size_t)c * M;
+    for (int r = 0; r < p.window_rows; ++r) {
+      const int th = h + p.pad_rows - r;
+      if (th < 0 || th % p.stride_rows) continue;
+      const int oh = th / p.stride_rows;
+      if (oh >= p.out_rows) continue;
+      for (int s = 0; s < p.window_cols; ++s) {
+        const int tw = wi + p.pad_cols - s;
+        if (tw < 0 || tw % p.stride_cols) continue;
+        const int ow = tw / p.stride_cols;
+        if (ow >= p.out_cols) continue;
+        const T* dp = dyn + ((size_t)oh * p.out_cols + ow) * F;
+        const T* wp = w + ((size_t)r * p.window_cols + s) * F + (size_t)c * M;
+        if constexpr (V == 1) {
+          for (int m = 0; m < M; ++m) acc[0] = fmaf(to_f32(__ldg(dp + m)), to_f32(__ldg(wp + m)), acc[0]);
+        } else {
+          float dv[V], wv[V];
+          load_vec<T, V>(dp, dv);
+          load_vec<T, V>(wp, wv);
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc[i] = fmaf(dv[i], wv[i], acc[i]);
+        }
+      }
+    }
+    store_vec<T, V>(dx + (size_t)idx * V, acc);
+  }
+}
+
+// Filter backprop, stage 1 (src/depthwise_conv2d/kernels.h:259-360 computes the same sum with
+// a work-group reduction): dW[r,s,f] = sum_{n,oh,ow} x[n,oh*st-pad+r,ow*st-pad+s,c] * dy[n,oh,ow,f].
+// blockIdx.x = slice of the N*Ho*Wo pixels, blockIdx.y = tap, blockIdx.z = tile of 32*V features.
+// threadIdx.x walks feature packets (coalesced), threadIdx.y walks pixels; the 8 pixel lanes are
+// summed through shared memory and the block writes partial[slice][tap][f] in fp32.
+constexpr int kFbpLanesF = 32, kFbpLanesP = 8;
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kFbpLanesF* kFbpLanesP)
+    depthwise_filter_backprop_partial_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                                             float* __restrict__ partial, PdnnDepthwiseConv2DParams p,
+                                             long long pixels_per_slice) {
+  __shared__ float red[kFbpLanesP][kFbpLanesF][V];
+  const int M = p.channel_multiplier, F = p.channels * M;
+  const int tap = blockIdx.y, r = tap / p.window_cols, s = tap % p.window_cols;
+  const int f = (blockIdx.z * kFbpLanesF + threadIdx.x) * V;
+  const long long pixels = (long long)p.batch * p.out_rows * p.out_cols;
+  const long long begin = (long long)blockIdx.x * pixels_per_slice;
+  const long long end = begin + pixels_per_slice < pixels ? begin + pixels_per_slice : pixels;
+  float acc[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc[i] = 0.f;
+  if (f < F) {
+    const int c = (V == 1) ? f / M : f;
+    for (long long pix = begin + threadIdx.y; pix < end; pix += kFbpLanesP) {
+      const int ow = (int)(pix % p.out_cols);
+      const long long t = pix / p.out_cols;
+      const int oh = (int)(t % p.out_rows);
+      const int n = (int)(t / p.out_rows);
+      const int ih = oh * p.stride_rows - p.pad_rows + r, iw = ow * p.stride_cols - p.pad_cols + s;
+      if (ih < 0 || ih >= p.in_rows || iw < 0 || iw >= p.in_cols) continue;
+      float xv[V], dv[V];
+      load_vec<T, V>(x + (((size_t)n * p.in_rows + ih) * p.in_cols + iw) * p.channels + c, xv);
+      load_vec<T, V>(dy + (size_t)pix * F + f, dv);
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = fmaf(xv[i], dv[i], acc[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < V; ++i) red[threadIdx.y][threadIdx.x][i] = acc[i];
+  __syncthreads();
+  if (threadIdx.y == 0 && f < F) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      float sum = 0.f;
+#pragma unroll
+      for (int l = 0; l < kFbpLanesP; ++l) sum += red[l][threadIdx.x][i];
+      partial[((size_t)blockIdx.x * gridDim.y + tap) * F + f + i] = sum;
+    }
+  }
+}
+
+// Stage 2: dW[i] = sum over slices of partial[slice][i], in slice order (deterministic).
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+    reduce_slices_kernel(const float* __restrict__ partial, T* __restrict__ out, int slices, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) {
+    float sum = 0.f;
+    for (int sl = 0; sl < slices; ++sl) sum += partial[(size_t)sl * n + i];
+    out[i] = from_f32<T>(sum);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Pointwise, bias, blend
+// ------------------------------------------------------------------------------------------
+template <typename T, int V, int MODE>  // MODE 0: forward, 1: gradient
+__global__ void __launch_bounds__(kBlock)
+    pointwise_kernel(int op, const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, size_t n_packets) {
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n_packets; i += (size_t)gridDim.x * kBlock) {
+    float av[V], res[V];
+    load_vec<T, V>(a + i * V, av);
+    if (MODE == 0) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) res[j] = apply_activation(av[j], op);
+    } else {
+      float bv[V];
+      load_vec<T, V>(b + i * V, bv);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        // src/pointwise/kernels.h:53-78: a is the forward output, b the incoming gradient.
+        if (op == PDNN_ACT_RELU) res[j] = av[j] > 0.f ? bv[j] : 0.f;
+        else if (op == PDNN_ACT_TANH) res[j] = (1.f - av[j] * av[j]) * bv[j];
+        else res[j] = (av[j] > 0.f && av[j] < 6.f) ? bv[j] : 0.f;
+      }
+    }
+    store_vec<T, V>(out + i * V, res);
+  }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kBlock) bias_add_kernel(const T* __restrict__ in, const T* __restrict__ bias,
+                                                          T* __restrict__ out, size_t n_packets, int cvecs, int act) {
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n_packets; i += (size_t)gridDim.x * kBlock) {
+    float v[V], b[V];
+    load_vec<T, V>(in + i * V, v);
+    load_vec<T, V>(bias + (i % cvecs) * V, b);
+#pragma unroll
+    for (int j = 0; j < V; ++j) v[j] = apply_activation(to_f32(from_f32<T>(v[j] + b[j])), act);  // sum rounded to T first, as two passes would
+    store_vec<T, V>(out + i * V, v);
+  }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kBlock) scale_blend_kernel(const T* __restrict__ a, float alpha, const T* __restrict__ b,
+                                                             float beta, T* __restrict__ out, size_t n_packets) {
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n_packets; i += (size_t)gridDim.x * kBlock) {
+    float av[V], res[V];
+    load_vec<T, V>(a + i * V, av);
+    if (b != nullptr) {
+      float bv[V];
+      load_vec<T, V>(b + i * V, bv);
+      // Rounded separately, like the reference's Mul, Mul, Add passes
+      // (include/portdnn/compat/scaling.hpp:202-259).
+#pragma unroll
+      for (int j = 0; j < V; ++j)
+        res[j] = __fadd_rn(to_f32(from_f32<T>(__fmul_rn(alpha, av[j]))), to_f32(from_f32<T>(__fmul_rn(beta, bv[j]))));
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) res[j] = __fmul_rn(alpha, av[j]);
+    }
+    store_vec<T, V>(out + i * V, res);
+  }
+}
+
+// ---- dispatch helpers -------------------------------------------------------------------------
+template <typename F>
+int dispatch_dtype(int dtype, F&& f) {
+  switch (dtype) {
+    case PDNN_F32: return f(float{});
+    case PDNN_F16: return f(__half{});
+    case PDNN_BF16: return f(__nv_bfloat16{});
+  }
+  return fail(PDNN_INVALID_PARAMETER, "unknown dtype %d", dtype);
+}
+
+bool pool_params_ok(const PdnnPoolingParams& p) {
+  // pooling::validate_params, include/portdnn/pooling/launch.h:56-88
+  return p.batch > 0 && p.channels > 0 && p.in_rows > 0 && p.in_cols > 0 && p.out_rows > 0 && p.out_cols > 0 &&
+         p.window_rows > 0 && p.window_cols > 0 && p.stride_rows > 0 && p.stride_cols > 0 && p.pad_rows >= 0 &&
+         p.pad_cols >= 0;
+}
+
+}  // namespace
+
+int launch_pooling(int op, int direction, int dtype, const void* in, void* out, const PdnnPoolingParams& p,
+                   cudaStream_t s) {
+  if (!pool_params_ok(p)) return fail(PDNN_INVALID_PARAMETER, "pooling: non-positive size or negative padding");
+  if (p.input_format != 0) return fail(PDNN_INVALID_PARAMETER, "pooling: only NHWC is implemented");
+  if (op < 0 || op > 2 || direction < 0 || direction > 1) return fail(PDNN_INVALID_PARAMETER, "pooling: bad op/direction");
+  if (direction == 1 && op != PDNN_POOL_AVERAGE)
+    return fail(PDNN_INVALID_PARAMETER, "pooling: the max gradient takes four tensors (pdnn_pooling_max_grad)");
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  return dispatch_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    constexpr int VN = Vec16<T>::N;
+    const bool vec = (p.channels % VN == 0) && aligned16(in) && aligned16(out);
+    const size_t pixels = direction == 0 ? (size_t)p.batch * p.out_rows * p.out_cols
+                                         : (size_t)p.batch * p.in_rows * p.in_cols;
+    const size_t items = pixels * (p.channels / (vec ? VN : 1));
+    const unsigned grid = grid_for(items, kBlock, sms);
+    const bool wide = items >= 0xFFFFFFFFull - (size_t)grid * kBlock;
+    auto go = [&](auto vtag, auto itag) {
+      constexpr int V = decltype(vtag)::value;
+      using Index = decltype(itag);
+      const T* x = static_cast<const T*>(in);
+      T* y = static_cast<T*>(out);
+      if (direction == 1) {
+        pool_avg_grad_kernel<T, V, Index><<<grid, kBlock, 0, s>>>(x, y, p, (Index)items);
+      } else if (op == PDNN_POOL_MAX) {
+        pool_forward_kernel<T, PDNN_POOL_MAX, V, Index><<<grid, kBlock, 0, s>>>(x, y, p, (Index)items);
+      } else if (op == PDNN_POOL_MAX_WITH_NAN) {
+        pool_forward_kernel<T, PDNN_POOL_MAX_WITH_NAN, V, Index><<<grid, kBlock, 0, s>>>(x, y, p, (Index)items);
+      } else {
+        pool_forward_kernel<T, PDNN_POOL_AVERAGE, V, Index><<<grid, kBlock, 0, s>>>(x, y, p, (Index)items);
+      }
+    };
+    if (vec) {
+      if (wide) go(std::integral_constant<int, VN>{}, (unsigned long long)0);
+      else go(std::integral_constant<int, VN>{}, (unsigned)0);
+    } else {
+      if (wide) go(std::integral_constant<int, 1>{}, (unsigned long long)0);
+      else go(std::integral_constant<int, 1>{}, (unsigned)0);
+    }
+    return check_launch("pooling");
+  });
+}
+
+int launch_pooling_max_grad(int op, int dtype, const void* x, const void* y, const void* dy, void* dx,
+                            const PdnnPoolingParams& p, cudaStream_t s) {
+  if (!pool_params_ok(p)) return fail(PDNN_INVALID_PARAMETER, "pooling: non-positive size or negative padding");
+  if (p.input_format != 0) return fail(PDNN_INVALID_PARAMETER, "pooling: only NHWC is implemented");
+  if (op != PDNN_POOL_MAX && op != PDNN_POOL_MAX_WITH_NAN) return fail(PDNN_INVALID_PARAMETER, "max gradient: bad op");
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  return dispatch_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    constexpr int VN = Vec16<T>::N;
+    const bool vec = (p.channels % VN == 0) && aligned16(x) && aligned16(y) && aligned16(dy) && aligned16(dx);
+    const size_t items = (size_t)p.batch * p.in_rows * p.in_cols * (p.channels / (vec ? VN : 1));
+    const unsigned grid = grid_for(items, kBlock, sms);
+    const bool wide = items >= 0xFFFFFFFFull - (size_t)grid * kBlock;
+    auto go = [&](auto vtag, auto itag) {
+      constexpr int V = decltype(vtag)::value;
+      using Index = decltype(itag);
+      if (op == PDNN_POOL_MAX)
+        pool_max_grad_kernel<T, PDNN_POOL_MAX, V, Index><<<grid, kBlock, 0, s>>>(
+            static_cast<const T*>(x), static_cast<const T*>(y), static_cast<const T*>(dy), static_cast<T*>(dx), p,
+            (Index)items);
+      else
+        pool_max_grad_kernel<T, PDNN_POOL_MAX_WITH_NAN, V, Index><<<grid, kBlock, 0, s>>>(
+            static_cast<const T*>(x), static_cast<const T*>(y), static_cast<const T*>(dy), static_cast<T*>(dx), p,
+            (Index)items);
+    };
+    if (vec) {
+      if (wide) go(std::integral_constant<int, VN>{}, (unsigned long long)0);
+      else go(std::integral_constant<int, VN>{}, (unsigned)0);
+    } else {
+      if (wide) go(std::integral_constant<int, 1>{}, (unsigned long long)0);
+      else go(std::integral_constant<int, 1>{}, (unsigned)0);
+    }
+    return check_launch("pooling max gradient");
+  });
+}
+
+namespace {
+bool depthwise_params_ok(const PdnnDepthwiseConv2DParams& p) {
+  return p.batch > 0 && p.channels > 0 && p.channel_multiplier > 0 && p.in_rows > 0 && p.in_cols > 0 &&
+         p.out_rows > 0 && p.out_cols > 0 && p.window_rows > 0 && p.window_cols > 0 && p.stride_rows > 0 &&
+         p.stride_cols > 0 && p.pad_rows >= 0 && p.pad_cols >= 0;
+}
+
+// Number of pixel slices of the filter-backprop reduction: enough blocks to fill the device,
+// at least 256 pixels per slice.
+int fbp_slices(const PdnnDepthwiseConv2DParams& p, int V, int sms) {
+  const long long pixels = (long long)p.batch * p.out_rows * p.out_cols;
+  const int F = p.channels * p.channel_multiplier;
+  const int ftiles = (F + kFbpLanesF * V - 1) / (kFbpLanesF * V);
+  const long long other = (long long)p.window_rows * p.window_cols * ftiles;
+  long long want = ((long long)sms * 8 + other - 1) / other;
+  const long long cap = (pixels + 255) / 256;
+  if (want > cap) want = cap;
+  if (want < 1) want = 1;
+  if (want > 1024) want = 1024;
+  return (int)want;
+}
+}  // namespace
+
+size_t depthwise_workspace_bytes(int pass, int dtype, const PdnnDepthwiseConv2DParams& p) {
+  if (pass != PDNN_FILTER_BACKPROP || !depthwise_params_ok(p)) return 0;
+  int sms = device_sm_count();
+  if (sms <= 0) sms = 148;
+  const int VN = 16 / (int)dtype_size(dtype);
+  // sized for the scalar form, which never uses fewer slices than the packet form
+  const int slices = fbp_slices(p, 1, sms) > fbp_slices(p, VN, sms) ? fbp_slices(p, 1, sms) : fbp_slices(p, VN, sms);
+  return (size_t)slices * p.window_rows * p.window_cols * p.channels * p.channel_multiplier * sizeof(float);
+}
+
+int launch_depthwise(int pass, int dtype, const void* in, const void* fil, void* out,
+                     const PdnnDepthwiseConv2DParams& p, void* ws, size_t ws_bytes, cudaStream_t s) {
+  if (!depthwise_params_ok(p)) return fail(PDNN_INVALID_PARAMETER, "depthwise: non-positive size or negative padding");
+  if (pass < 0 || pass > 2) return fail(PDNN_INVALID_PARAMETER, "depthwise: bad pass");
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    constexpr int VN = Vec16<T>::N;
+    const int F = p.channels * p.channel_multiplier;
+    // the reference vectorises only for multiplier 1 too (src/depthwise_conv2d/launch.cc:41-121)
+    const bool vec = p.channel_multiplier == 1 && (p.channels % VN == 0) && aligned16(in) && aligned16(fil) && aligned16(out);
+    if (pass == PDNN_FILTER_BACKPROP) {
+      const int V = vec ? VN : 1;
+      const int slices = fbp_slices(p, V, sms);
+      const size_t n_out = (size_t)p.window_rows * p.window_cols * F;
+      const size_t need = (size_t)slices * n_out * sizeof(float);
+      float* partial = static_cast<float*>(ws);
+      bool own = false;
+      if (partial == nullptr || ws_bytes < need) {
+        if (cudaMallocAsync(reinterpret_cast<void**>(&partial), need, s) != cudaSuccess) {
+          cudaGetLastError();
+          return fail(PDNN_ALLOCATION_PROBLEM, "depthwise filter backprop: cannot allocate %zu bytes of scratch", need);
+        }
+        own = true;
+      }
+      const long long pixels = (long long)p.batch * p.out_rows * p.out_cols;
+      const long long per_slice = (pixels + slices - 1) / slices;
+      dim3 block(kFbpLanesF, kFbpLanesP);
+      dim3 grid(slices, p.window_rows * p.window_cols, (F + kFbpLanesF * V - 1) / (kFbpLanesF * V));
+      if (vec)
+        depthwise_filter_backprop_partial_kernel<T, VN><<<grid, block, 0, s>>>(
+            static_cast<const T*>(in), static_cast<const T*>(fil), partial, p, per_slice);
+      else
+        depthwise_filter_backprop_partial_kernel<T, 1><<<grid, block, 0, s>>>(
+            static_cast<const T*>(in), static_cast<const T*>(fil), partial, p, per_slice);
+      int st = check_launch("depthwise filter backprop (partial sums)");
+      if (st == PDNN_OK) {
+        reduce_slices_kernel<T><<<grid_for(n_out, kBlock, sms), kBlock, 0, s>>>(partial, static_cast<T*>(out), slices, n_out);
+        st = check_launch("depthwise filter backprop (slice reduction)");
+      }
+      if (own) cudaFreeAsync(partial, s);
+      return st;
+    }
+    const size_t pixels = pass == PDNN_FORWARD ? (size_t)p.batch * p.out_rows * p.out_cols
+                                               : (size_t)p.batch * p.in_rows * p.in_cols;
+    const size_t items = pixels * ((pass == PDNN_FORWARD ? F : p.channels) / (vec ? VN : 1));
+    const unsigned grid = grid_for(items, kBlock, sms);
+    const bool wide = items >= 0xFFFFFFFFull - (size_t)grid * kBlock;
+    auto go = [&](auto vtag, auto itag) {
+      constexpr int V = decltype(vtag)::value;
+      using Index = decltype(itag);
+      if (pass == PDNN_FORWARD)
+        depthwise_forward_kernel<T, V, Index><<<grid, kBlock, 0, s>>>(
+            static_cast<const T*>(in), static_cast<const T*>(fil), static_cast<T*>(out), p, (Index)items);
+      else
+        depthwise_input_backprop_kernel<T, V, Index><<<grid, kBlock, 0, s>>>(
+            static_cast<const T*>(in), static_cast<const T*>(fil), static_cast<T*>(out), p, (Index)items);
+    };
+    if (vec) {
+      if (wide) go(std::integral_constant<int, VN>{}, (unsigned long long)0);
+      else go(std::integral_constant<int, VN>{}, (unsigned)0);
+    } else {
+      if (wide) go(std::integral_constant<int, 1>{}, (unsigned long long)0);
+      else go(std::integral_constant<int, 1>{}, (unsigned)0);
+    }
+    return check_launch("depthwise conv2d");
+  });
+}
+
+int launch_pointwise(int op, int dtype, const void* in, void* out, size_t n, cudaStream_t s) {
+  if (op < 0 || op > 2) return fail(PDNN_INVALID_PARAMETER, "pointwise: bad op");
+  if (n == 0) return PDNN_OK;
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  return dispatch_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    constexpr int VN = Vec16<T>::N;
+    // the reference picks the widest vector that divides n (src/pointwise/launch_pointwise_forward.cc:32-70)
+    if (n % VN == 0 && aligned16(in) && aligned16(out))
+      pointwise_kernel<T, VN, 0><<<grid_for(n / VN, kBlock, sms), kBlock, 0, s>>>(
+          op, static_cast<const T*>(in), nullptr, static_cast<T*>(out), n / VN);
+    else
+      pointwise_kernel<T, 1, 0><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(op, static_cast<const T*>(in), nullptr,
+                                                                            static_cast<T*>(out), n);
+    return check_launch("pointwise");
+  });
+}
+
+int launch_pointwise_grad(int op, int dtype, const void* fwd, const void* err, void* out, size_t n, cudaStream_t s) {
+  if (op < 0 || op > 2) return fail(PDNN_INVALID_PARAMETER, "pointwise: bad op");
+  if (n == 0) return PDNN_OK;
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  return dispatch_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    constexpr int VN = Vec16<T>::N;
+    if (n % VN == 0 && aligned16(fwd) && aligned16(err) && aligned16(out))
+      pointwise_kernel<T, VN, 1><<<grid_for(n / VN, kBlock, sms), kBlock, 0, s>>>(
+          op, static_cast<const T*>(fwd), static_cast<const T*>(err), static_cast<T*>(out), n / VN);
+    else
+      pointwise_kernel<T, 1, 1><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
+          op, static_cast<const T*>(fwd), static_cast<const T*>(err), static_cast<T*>(out), n);
+    return check_launch("pointwise gradient");
+  });
+}
+
+int launch_bias_add(int dtype, const void* in, const void* bias, void* out, size_t rows, int channels, int act,
+                    cudaStream_t s) {
+  if (channels <= 0) return fail(PDNN_INVALID_PARAMETER, "bias: channels must be positive");
+  if (rows == 0) return PDNN_OK;
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  return dispatch_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    constexpr int VN = Vec16<T>::N;
+    const size_t n = rows * (size_t)channels;
+    if (channels % VN == 0 && aligned16(in) && aligned16(bias) && aligned16(out))
+      bias_add_kernel<T, VN><<<grid_for(n / VN, kBlock, sms), kBlock, 0, s>>>(
+          static_cast<const T*>(in), static_cast<const T*>(bias), static_cast<T*>(out), n / VN, channels / VN, act);
+    else
+      bias_add_kernel<T, 1><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
+          static_cast<const T*>(in), static_cast<const T*>(bias), static_cast<T*>(out), n, channels, act);
+    return check_launch("bias add");
+  });
+}
+
+int launch_scale_blend(int dtype, const void* a, float alpha, const void* b, float beta, void* out, size_t n,
+                       cudaStream_t s) {
+  if (n == 0) return PDNN_OK;
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  if (beta == 0.f) b = nullptr;
+  return dispatch_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    constexpr int VN = Vec16<T>::N;
+    if (n % VN == 0 && aligned16(a) && aligned16(out) && (b == nullptr || aligned16(b)))
+      scale_blend_kernel<T, VN><<<grid_for(n / VN, kBlock, sms), kBlock, 0, s>>>(
+          static_cast<const T*>(a), alpha, static_cast<const T*>(b), beta, static_cast<T*>(out), n / VN);
+    else
+      scale_blend_kernel<T, 1><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
+          static_cast<const T*>(a), alpha, static_cast<const T*>(b), beta, static_cast<T*>(out), n);
+    return check_launch("scale blend");
+  });
+}
+
+}  // namespace pdnn

@@ -1,0 +1,1093 @@
+// Implicit-GEMM engine on the Blackwell tensor cores: one persistent, warp-specialised kernel
+// serves conv2d forward / input backprop / filter backprop and the (batched) matmul.
+//
+//   D[128 x BN] (fp32, in TMEM) = sum over reduction steps of A_step[128 x 64] * B_step[64 x BN]
+//
+// Each step's operands are fetched by TMA straight from the NHWC activation tensor and the filter
+// (no im2col buffer): a 128-row A tile is a box of output pixels (tw x th x tn) shifted by the
+// filter tap, with TMA's out-of-bounds zero fill standing in for the padding.  Stride-2
+// convolutions read through one tensor map per input parity, so every load is a dense box.
+// Operands land in shared memory in the 128-byte swizzled layout that tcgen05.mma consumes; the
+// accumulators live in tensor memory (two buffers, so the epilogue of one tile overlaps the
+// main loop of the next) and are written to global memory by four epilogue warps with bias,
+// activation and alpha/beta applied on the way.
+//
+// fp32 tensors are multiplied as three TF32 products (hi*hi + hi*lo + lo*hi): four extra warps
+// split each landed stage into its high and low parts in shared memory before the MMA warp
+// consumes it.
+//
+// Warp roles (192 threads; 320 with the split): warp 0 TMA producer, warp 1 MMA issuer and TMEM
+// owner, warps 2-5 epilogue, warps 6-9 hi/lo split.
+#include "tc_gemm.cuh"
+#include "umma.cuh"
+
+#include <algorithm>
+#include <cstring>
+#include <mutex>
+
+namespace pdnn {
+
+using namespace umma;
+
+namespace {
+
+constexpr int kMaxTaps = 64;
+constexpr int kTileM = 128;
+constexpr int kABytes = kTileM * 128;  // one A stage: 128 rows of 128 bytes
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 227 * 1024;
+
+__device__ unsigned g_error_record[4];
+
+struct TapEntry {
+  short dw, dh, a_map, b_tap;
+};
+
+enum BMode { B_MN_3 = 0, B_K_3 = 1, B_K_FHWC = 2, B_MN_FHWC = 3, B_MN_4 = 4, B_K_4 = 5 };
+
+struct alignas(64) GemmArgs {
+  CUtensorMap a_map[4];
+  CUtensorMap b_map;
+  TapEntry taps[kMaxTaps];
+  int a_mn;          // 0: A rows are output pixels (K-major); 1: A rows are reduction steps (MN-major)
+  int b_mode;        // BMode
+  int epr;           // elements per 128-byte row: 64 (16-bit) or 32 (fp32)
+  int n_tiles, bn;   // column tiles and their width
+  int tiles_w, tiles_h, tiles_n;  // row-tile grid
+  int tw, th, tn;    // a_mn == 0: pixel box of a row tile; a_mn == 1: pixel box of a reduction slab
+  int etw, eth, etn; // pixel box of a row tile as the epilogue sees it
+  int num_taps;
+  int cblocks;       // a_mn == 0: reduction blocks per tap
+  int slabs_w, slabs_h, slabs_n, splits, slabs_per_split, split_is_batch;  // a_mn == 1
+  int b_batch_mul;
+  int stages, tmem_cols;
+  unsigned idesc;
+  unsigned a_lbo, a_sbo, a_kadv, b_lbo, b_sbo, b_kadv;  // bytes
+  int a_boxes, b_boxes;
+  unsigned a_box_bytes, b_box_bytes;
+  // epilogue
+  void* out;
+  const void* bias;
+  int out_dtype, act;
+  float alpha, beta;
+  int ext_w, ext_h, ext_n, ext_cols;
+  long long stride_w, stride_h, stride_n, split_stride, tap_stride;  // elements
+  int vec_ok;  // rows are 16-byte aligned: packed stores allowed
+};
+
+struct TileCoord {
+  int w0, h0, n0, nf0, tap, split;
+  long long out_off;
+  int ks_begin, ks_end;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmArgs& a, int tile) {
+  TileCoord t;
+  const int nt = tile % a.n_tiles;
+  int r = tile / a.n_tiles;
+  t.nf0 = nt * a.bn;
+  if (!a.a_mn) {
+    const int mw = r % a.tiles_w;
+    r /= a.tiles_w;
+    const int mh = r % a.tiles_h;
+    const int mn = r / a.tiles_h;
+    t.w0 = mw * a.tw;
+    t.h0 = mh * a.th;
+    t.n0 = mn * a.tn;
+    t.tap = 0;
+    t.split = 0;
+    t.out_off = 0;
+    t.ks_begin = 0;
+    t.ks_end = a.num_taps * a.cblocks;
+  } else {
+    const int mt = r % a.tiles_w;
+    r /= a.tiles_w;
+    t.tap = r % a.num_taps;
+    t.split = r / a.num_taps;
+    t.w0 = mt * kTileM;
+    t.h0 = 0;
+    t.n0 = 0;
+    t.out_off = (long long)t.split * a.split_stride + (long long)t.tap * a.tap_stride;
+    const int total = a.slabs_w * a.slabs_h * a.slabs_n;
+    t.ks_begin = a.split_is_batch ? 0 : t.split * a.slabs_per_split;
+    t.ks_end = min(t.ks_begin + a.slabs_per_split, total);
+  }
+  return t;
+}
+
+template <typename OutT, int N>
+__device__ __forceinline__ void store_chunk(const GemmArgs& a, const uint32_t (&acc)[N], bool zero, OutT* row_ptr,
+                                            const OutT* bias, int col0, bool row_valid) {
+  // row_ptr points at column 0 of this row; col0 is the first column of the chunk.
+  constexpr int P = 16 / sizeof(OutT);  // elements per 16-byte packet
+#pragma unroll
+  for (int g = 0; g < N / P; ++g) {
+    const int c = col0 + g * P;
+    if (!row_valid || c >= a.ext_cols) continue;
+    float v[P];
+#pragma unroll
+    for (int i = 0; i < P; ++i) v[i] = zero ? 0.f : a.alpha * __uint_as_float(acc[g * P + i]);
+    const bool full = a.vec_ok && (c + P <= a.ext_cols);
+    if (bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < P; ++i)
+        if (c + i < a.ext_cols) v[i] += to_f32(__ldg(bias + c + i));
+    }
+    if (a.act != PDNN_ACT_NONE) {
+#pragma unroll
+      for (int i = 0; i < P; ++i) v[i] = apply_activation(v[i], a.act);
+    }
+    if (full) {
+      if (a.beta != 0.f) {
+        Vec16<OutT> old;
+        old.raw = *reinterpret_cast<const uint4*>(row_ptr + c);
+#pragma unroll
+        for (int i = 0; i < P; ++i) v[i] += a.beta * to_f32(old.get(i));
+      }
+      Vec16<OutT> pk;
+#pragma unroll
+      for (int i = 0; i < P; ++i) pk.set(i, from_f32<OutT>(v[i]));
+      *reinterpret_cast<uint4*>(row_ptr + c) = pk.raw;
+    } else {
+#pragma unroll
+      for (int i = 0; i < P; ++i) {
+        if (c + i < a.ext_cols) {
+          float r = v[i];
+          if (a.beta != 0.f) r += a.beta * to_f32(row_ptr[c + i]);
+          row_ptr[c + i] = from_f32<OutT>(r);
+        }
+      }
+    }
+  }
+}
+
+template <typename OutT>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc, int row,
+                                              bool zero) {
+  const int lw = row % a.etw, lh = (row / a.etw) % a.eth, ln = row / (a.etw * a.eth);
+  const int w = t.w0 + lw, h = t.h0 + lh, n = t.n0 + ln;
+  const bool row_valid = (w < a.ext_w) && (h < a.ext_h) && (n < a.ext_n);
+  OutT* row_ptr = static_cast<OutT*>(a.out) + t.out_off + (long long)n * a.stride_n + (long long)h * a.stride_h +
+                  (long long)w * a.stride_w;
+  const OutT* bias = static_cast<const OutT*>(a.bias);
+  int c0 = 0;
+  for (; c0 + 32 <= a.bn; c0 += 32) {
+    uint32_t acc[32];
+    if (!zero) {
+      tmem_ld_32x32(tmem_acc + (uint32_t)c0, acc);
+      tmem_wait_ld();
+    }
+    store_chunk<OutT, 32>(a, acc, zero, row_ptr, bias, t.nf0 + c0, row_valid);
+  }
+  if (c0 < a.bn) {  // bn is a multiple of 16
+    uint32_t acc[16];
+    if (!zero) {
+      tmem_ld_32x16(tmem_acc + (uint32_t)c0, acc);
+      tmem_wait_ld();
+    }
+    store_chunk<OutT, 16>(a, acc, zero, row_ptr, bias, t.nf0 + c0, row_valid);
+  }
+}
+
+template <bool SPLIT>
+__global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const __grid_constant__ GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  const GemmArgs& a = args;
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+  uint8_t* smem = smem_raw + (base - raw_addr);
+
+  const uint32_t b_bytes = (uint32_t)a.bn * 128u;
+  const uint32_t part_bytes = kABytes + b_bytes;              // one A tile + one B tile
+  const uint32_t stage_bytes = SPLIT ? 2u * part_bytes : part_bytes;
+  const int S = a.stages;
+  // barrier block after the stages
+  uint8_t* bar_mem = smem + (size_t)S * stage_bytes;
+  const uint32_t bar_base = base + (uint32_t)S * stage_bytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(kMaxStages + s); };
+  auto ready_bar = [&](int s) { return bar_base + 8u * (uint32_t)(2 * kMaxStages + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * kMaxStages + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * kMaxStages + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 8 * (3 * kMaxStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * (3 * kMaxStages + 4) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(ready_bar(s), 4);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), (uint32_t)a.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t acc_stride = (uint32_t)a.tmem_cols / 2u;
+
+  const int total_tiles = a.a_mn ? a.n_tiles * a.tiles_w * a.num_taps * a.splits
+                                 : a.n_tiles * a.tiles_w * a.tiles_h * a.tiles_n;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer ------------------------------------------
+    if (lane == 0) {
+      for (int i = 0; i < 4; ++i) prefetch_tensormap(&a.a_map[i]);
+      prefetch_tensormap(&a.b_map);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const TileCoord t = decode_tile(a, tile);
+        const TapEntry e_fixed = a.taps[t.tap];
+        for (int ks = t.ks_begin; ks < t.ks_end; ++ks, ++it) {
+          const int s = (int)(it % (uint32_t)S);
+          const uint32_t ph = (it / (uint32_t)S) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g_error_record, 0x100u + (unsigned)s)) {
+            ok = false;
+            break;
+          }
+          const uint32_t fb = full_bar(s);
+          mbar_arrive_expect_tx(fb, kABytes + b_bytes);
+          const uint32_t sa = base + (uint32_t)s * stage_bytes;
+          const uint32_t sb = sa + kABytes;
+          if (!a.a_mn) {
+            const int tap = ks / a.cblocks, cb = ks % a.cblocks;
+            const TapEntry e = a.taps[tap];
+            const int kc = cb * a.epr;
+            tma_load_4d(sa, &a.a_map[e.a_map], fb, kc, t.w0 + e.dw, t.h0 + e.dh, t.n0);
+            const int btap = e.b_tap + t.n0 * a.b_batch_mul;
+            switch (a.b_mode) {
+              case B_MN_3:
+                for (int j = 0; j < a.b_boxes; ++j)
+                  tma_load_4d(sb + (uint32_t)j * a.b_box_bytes, &a.b_map, fb, t.nf0 + j * a.epr, kc, btap, 0);
+                break;
+              case B_K_3: tma_load_4d(sb, &a.b_map, fb, kc, t.nf0, btap, 0); break;
+              case B_K_FHWC: tma_load_4d(sb, &a.b_map, fb, kc, btap, t.nf0, 0); break;
+              default:  // B_MN_FHWC
+                for (int j = 0; j < a.b_boxes; ++j)
+                  tma_load_4d(sb + (uint32_t)j * a.b_box_bytes, &a.b_map, fb, t.nf0 + j * a.epr, btap, kc, 0);
+                break;
+            }
+          } else {
+            const int kw = (ks % a.slabs_w) * a.tw;
+            const int kh = ((ks / a.slabs_w) % a.slabs_h) * a.th;
+            const int kn = (ks / (a.slabs_w * a.slabs_h)) * a.tn + (a.split_is_batch ? t.split : 0);
+            for (int j = 0; j < a.a_boxes; ++j)
+              tma_load_4d(sa + (uint32_t)j * a.a_box_bytes, &a.a_map[e_fixed.a_map], fb, t.w0 + j * a.epr,
+                          kw + e_fixed.dw, kh + e_fixed.dh, kn);
+            if (a.b_mode == B_MN_4) {
+              for (int j = 0; j < a.b_boxes; ++j)
+                tma_load_4d(sb + (uint32_t)j * a.b_box_bytes, &a.b_map, fb, t.nf0 + j * a.epr, kw, kh, kn);
+            } else {  // B_K_4
+              tma_load_4d(sb, &a.b_map, fb, kw, t.nf0, 0, kn);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ---------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+        const TileCoord t = decode_tile(a, tile);
+        const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
+        if (!mbar_wait(acc_empty_bar((int)buf), aph ^ 1u, abort_flag, g_error_record, 0x200u + buf)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * acc_stride;
+        for (int ks = t.ks_begin; ks < t.ks_end; ++ks, ++it) {
+          const int s = (int)(it % (uint32_t)S);
+          const uint32_t ph = (it / (uint32_t)S) & 1u;
+          if (!mbar_wait(SPLIT ? ready_bar(s) : full_bar(s), ph, abort_flag, g_error_record, 0x300u + (unsigned)s)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = base + (uint32_t)s * stage_bytes;
+          const uint32_t sb = sa + kABytes;
+          const uint64_t a_hi = make_smem_desc(sa, a.a_lbo, a.a_sbo);
+          const uint64_t b_hi = make_smem_desc(sb, a.b_lbo, a.b_sbo);
+          const bool first_step = (ks == t.ks_begin);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t ka = (uint64_t)((a.a_kadv * (uint32_t)k) >> 4), kb = (uint64_t)((a.b_kadv * (uint32_t)k) >> 4);
+            const uint32_t acc = (first_step && k == 0) ? 0u : 1u;
+            if (SPLIT) {
+              const uint64_t a_lo = make_smem_desc(sa + part_bytes, a.a_lbo, a.a_sbo);
+              const uint64_t b_lo = make_smem_desc(sb + part_bytes, a.b_lbo, a.b_sbo);
+              mma_tf32(d_tmem, a_lo + ka, b_hi + kb, a.idesc, acc);
+              mma_tf32(d_tmem, a_hi + ka, b_lo + kb, a.idesc, 1u);
+              mma_tf32(d_tmem, a_hi + ka, b_hi + kb, a.idesc, 1u);
+            } else {
+              mma_f16(d_tmem, a_hi + ka, b_hi + kb, a.idesc, acc);
+            }
+          }
+          mma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+        }
+        if (!ok) break;
+        if (t.ks_end > t.ks_begin) mma_commit(acc_full_bar((int)buf));
+        else mbar_arrive(acc_full_bar((int)buf));  // nothing to accumulate: the epilogue writes zeros
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------- epilogue ------------------------------------------------
+    const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
+    const int row = q * 32 + lane;
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
+      const TileCoord t = decode_tile(a, tile);
+      const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
+      if (!mbar_wait(acc_full_bar((int)buf), aph, abort_flag, g_error_record, 0x400u + buf)) break;
+      tc_fence_after_sync();
+      const uint32_t tmem_acc = tmem_base + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
+      const bool zero = !(t.ks_end > t.ks_begin);
+      if (a.out_dtype == PDNN_F16) epilogue_tile<__half>(a, t, tmem_acc, row, zero);
+      else if (a.out_dtype == PDNN_BF16) epilogue_tile<__nv_bfloat16>(a, t, tmem_acc, row, zero);
+      else epilogue_tile<float>(a, t, tmem_acc, row, zero);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar((int)buf));
+    }
+  } else if (SPLIT) {
+    // ------------------------------- hi/lo split (fp32 as 3xTF32) ----------------------------
+    // hi keeps the 19 leading bits (what the tensor core reads of an fp32 word); lo = x - hi is
+    // exact in fp32.  Element positions do not change, so the swizzle is irrelevant here.
+    const int tid = threadIdx.x - 6 * 32;  // 0..127
+    const int chunks = (int)(part_bytes >> 4);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const TileCoord t = decode_tile(a, tile);
+      for (int ks = t.ks_begin; ks < t.ks_end; ++ks, ++it) {
+        const int s = (int)(it % (uint32_t)S);
+        const uint32_t ph = (it / (uint32_t)S) & 1u;
+        if (!mbar_wait(full_bar(s), ph, abort_flag, g_error_record, 0x500u + (unsigned)s)) {
+          ok = false;
+          break;
+        }
+        uint4* hi = reinterpret_cast<uint4*>(smem + (size_t)s * stage_bytes);
+        uint4* lo = reinterpret_cast<uint4*>(smem + (size_t)s * stage_bytes + part_bytes);
+        for (int c = tid; c < chunks; c += 128) {
+          uint4 v = hi[c], h, l;
+          h.x = v.x & 0xFFFFE000u;
+          h.y = v.y & 0xFFFFE000u;
+          h.z = v.z & 0xFFFFE000u;
+          h.w = v.w & 0xFFFFE000u;
+          l.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(h.x));
+          l.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(h.y));
+          l.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(h.z));
+          l.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(h.w));
+          hi[c] = h;
+          lo[c] = l;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready_bar(s));
+      }
+    }
+  }
+
+  // ------------------------------- teardown ---------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // Loads already issued may still be landing in shared memory: give them time before the
+    // CTA's shared memory is released.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)a.tmem_cols);
+}
+
+// ================================================================================================
+// Host side: tensor maps and launch plans
+// ================================================================================================
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+// 4-D tiled map with the 128-byte swizzle and zero fill outside the tensor.  dims[0] is the
+// contiguous dimension; strides_bytes[i] is the stride of dims[i+1].
+bool make_map(CUtensorMap* map, int dtype, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
+              const uint32_t box[4]) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) {
+    fail(PDNN_ALLOCATION_PROBLEM, "cuTensorMapEncodeTiled is unavailable");
+    return false;
+  }
+  CUtensorMapDataType dt = dtype == PDNN_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                          : dtype == PDNN_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                              : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  cuuint64_t d[4], st[3];
+  cuuint32_t b[4], es[4] = {1, 1, 1, 1};
+  for (int i = 0; i < 4; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+  }
+  for (int i = 0; i < 3; ++i) st[i] = strides_bytes[i];
+  CUresult r = fn(map, dt, 4, const_cast<void*>(base), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fail(PDNN_INVALID_PARAMETER,
+         "cuTensorMapEncodeTiled failed (%d): dims %llu %llu %llu %llu strides %llu %llu %llu box %u %u %u %u", (int)r,
+         (unsigned long long)d[0], (unsigned long long)d[1], (unsigned long long)d[2], (unsigned long long)d[3],
+         (unsigned long long)st[0], (unsigned long long)st[1], (unsigned long long)st[2], b[0], b[1], b[2], b[3]);
+    return false;
+  }
+  return true;
+}
+
+int floor_div(int a, int b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); }
+int pos_mod(int a, int b) { return a - floor_div(a, b) * b; }
+int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Splits `total` (a power of two) rows into a box tw x th x tn of powers of two that wastes the
+// fewest rows when tiled over [W, H, N]; ties go to the widest box.
+void choose_box(int total, int W, int H, int N, int* tw, int* th, int* tn) {
+  double best = -1;
+  for (int w = total; w >= 1; w >>= 1)
+    for (int h = total / w; h >= 1; h >>= 1) {
+      const int n = total / (w * h);
+      if (w > 256 || h > 256 || n > 256) continue;
+      const double covered = (double)ceil_div(W, w) * w * (double)ceil_div(H, h) * h * (double)ceil_div(N, n) * n;
+      const double eff = ((double)W * H * N) / covered;
+      if (eff > best + 1e-9) {
+        best = eff;
+        *tw = w;
+        *th = h;
+        *tn = n;
+      }
+    }
+}
+
+int pick_bn(long long row_tiles, int cols, int unit, int max_bn, int sms) {
+  // cost ~ waves * (bn + fixed overhead); unit: granularity the B loader needs
+  int best_bn = unit;
+  double best = 1e30;
+  for (int bn = unit; bn <= max_bn; bn += unit) {
+    if (bn != 16 && bn != 32 && bn != 48 && bn % 64 != 0) continue;
+    const long long tiles = row_tiles * ceil_div(cols, bn);
+    const double waves = (double)((tiles + sms - 1) / sms);
+    const double cost = waves * (bn + 40.0);
+    if (cost < best - 1e-9) {
+      best = cost;
+      best_bn = bn;
+    }
+    if (bn >= ((cols + unit - 1) / unit) * unit) break;
+  }
+  return best_bn;
+}
+
+int next_pow2(int v) {
+  int p = 32;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+void set_operand_layout(GemmArgs& g, int dtype, int b_mn) {
+  const bool f32 = dtype == PDNN_F32;
+  g.epr = f32 ? 32 : 64;
+  const unsigned kstep_bytes_k = 32;                     // one UMMA K step inside a 128-byte row
+  const unsigned kstep_bytes_mn = (f32 ? 8u : 16u) * 128u;  // UMMA K rows of 128 bytes
+  const unsigned rows = (unsigned)g.epr;                 // reduction rows per stage for MN-major operands
+  if (g.a_mn) {
+    g.a_lbo = rows * 128u;
+    g.a_sbo = 1024u;
+    g.a_kadv = kstep_bytes_mn;
+    g.a_boxes = kTileM / g.epr;
+    g.a_box_bytes = rows * 128u;
+  } else {
+    g.a_lbo = 16u;
+    g.a_sbo = 1024u;
+    g.a_kadv = kstep_bytes_k;
+    g.a_boxes = 1;
+    g.a_box_bytes = kABytes;
+  }
+  if (b_mn) {
+    g.b_lbo = rows * 128u;
+    g.b_sbo = 1024u;
+    g.b_kadv = kstep_bytes_mn;
+    g.b_boxes = g.bn / g.epr;
+    g.b_box_bytes = rows * 128u;
+  } else {
+    g.b_lbo = 16u;
+    g.b_sbo = 1024u;
+    g.b_kadv = kstep_bytes_k;
+    g.b_boxes = 1;
+    g.b_box_bytes = (unsigned)g.bn * 128u;
+  }
+  g.idesc = make_idesc(dtype == PDNN_F32 ? 2 : (dtype == PDNN_BF16 ? 1 : 0), g.a_mn, b_mn, g.bn);
+  g.tmem_cols = next_pow2(2 * g.bn);
+  const unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (f32 ? 2u : 1u);
+  int stages = (int)((kSmemBudget - 2048) / stage);
+  g.stages = std::max(2, std::min(kMaxStages, stages));
+}
+
+int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
+  const bool split = dtype == PDNN_F32;
+  const long long total = g.a_mn ? (long long)g.n_tiles * g.tiles_w * g.num_taps * g.splits
+                                 : (long long)g.n_tiles * g.tiles_w * g.tiles_h * g.tiles_n;
+  if (total <= 0) return PDNN_OK;
+  if (total > 0x7FFFFFFFll) return fail(PDNN_INDEX_EXCEEDED, "tensor-core gemm: too many tiles");
+  const unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
+  // At least 120 KB so that two CTAs never share an SM (and with it the tensor memory).
+  const size_t smem = std::max<size_t>(1024 + (size_t)g.stages * stage + 512, 120 * 1024);
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(umma_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(umma_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+  });
+  if (attr_err != cudaSuccess) return fail(PDNN_ALLOCATION_PROBLEM, "cannot opt in to %d bytes of shared memory", kSmemBudget);
+  const int sms = device_sm_count();
+  const unsigned grid = (unsigned)std::min<long long>(total, sms);
+  if (split) umma_gemm_kernel<true><<<grid, 320, smem, s>>>(g);
+  else umma_gemm_kernel<false><<<grid, 192, smem, s>>>(g);
+  return check_launch("tensor-core gemm");
+}
+
+void set_epilogue(GemmArgs& g, const PdnnConvEpilogue* epi) {
+  g.bias = nullptr;
+  g.act = PDNN_ACT_NONE;
+  g.alpha = 1.f;
+  g.beta = 0.f;
+  if (epi != nullptr) {
+    g.bias = epi->bias;
+    g.act = epi->activation;
+    g.alpha = epi->alpha;
+    g.beta = epi->beta;
+  }
+}
+
+bool conv_common_ok(int dtype, const PdnnConv2DParams& p) {
+  const int align = dtype == PDNN_F32 ? 4 : 8;
+  if (p.input_format != 0 || p.groups != 1) return false;
+  if (p.filter_format != 0 && p.filter_format != 2) return false;
+  if (p.channels % align || p.features % align) return false;
+  if (p.stride_rows < 1 || p.stride_rows > 2 || p.stride_cols < 1 || p.stride_cols > 2) return false;
+  if (p.window_rows * p.window_cols > kMaxTaps) return false;
+  if (p.in_cols > 32767 || p.in_rows > 32767) return false;
+  return true;
+}
+
+// One tensor map per input parity of x ([C, W', H', N] view of the pixels with h % sr == ph,
+// w % sc == pw).  Returns false if a parity class is empty.
+bool make_parity_maps(GemmArgs& g, int dtype, const void* x, const PdnnConv2DParams& p, const uint32_t box[4]) {
+  const size_t es = dtype_size(dtype);
+  for (int ph = 0; ph < p.stride_rows; ++ph)
+    for (int pw = 0; pw < p.stride_cols; ++pw) {
+      const int Hq = ceil_div(p.in_rows - ph, p.stride_rows), Wq = ceil_div(p.in_cols - pw, p.stride_cols);
+      if (Hq <= 0 || Wq <= 0) return false;
+      const uint64_t dims[4] = {(uint64_t)p.channels, (uint64_t)Wq, (uint64_t)Hq, (uint64_t)p.batch};
+      const uint64_t st[3] = {(uint64_t)p.stride_cols * p.channels * es,
+                              (uint64_t)p.stride_rows * p.in_cols * p.channels * es,
+                              (uint64_t)p.in_rows * p.in_cols * p.channels * es};
+      const char* base = static_cast<const char*>(x) + ((size_t)ph * p.in_cols + pw) * p.channels * es;
+      if (!make_map(&g.a_map[ph * p.stride_cols + pw], dtype, base, dims, st, box)) return false;
+    }
+  for (int i = p.stride_rows * p.stride_cols; i < 4; ++i) g.a_map[i] = g.a_map[0];
+  return true;
+}
+
+int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnConv2DParams& p,
+                 const PdnnConvEpilogue* epi, cudaStream_t s) {
+  GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  const size_t es = dtype_size(dtype);
+  const int sms = device_sm_count();
+  g.a_mn = 0;
+  const bool hwcf = p.filter_format == 0;
+  const int epr = dtype == PDNN_F32 ? 32 : 64;
+  choose_box(kTileM, p.out_cols, p.out_rows, p.batch, &g.tw, &g.th, &g.tn);
+  g.etw = g.tw;
+  g.eth = g.th;
+  g.etn = g.tn;
+  g.tiles_w = ceil_div(p.out_cols, g.tw);
+  g.tiles_h = ceil_div(p.out_rows, g.th);
+  g.tiles_n = ceil_div(p.batch, g.tn);
+  const long long row_tiles = (long long)g.tiles_w * g.tiles_h * g.tiles_n;
+  g.bn = pick_bn(row_tiles, p.features, hwcf ? epr : 16, dtype == PDNN_F32 ? 128 : 256, sms);
+  g.n_tiles = ceil_div(p.features, g.bn);
+  set_operand_layout(g, dtype, hwcf ? 1 : 0);
+  const uint32_t abox[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)g.th, (uint32_t)g.tn};
+  if (!make_parity_maps(g, dtype, x, p, abox)) return PDNN_INVALID_PARAMETER;
+  // taps
+  int nt = 0;
+  for (int r = 0; r < p.window_rows; ++r)
+    for (int c = 0; c < p.window_cols; ++c) {
+      const int hh = r - p.pad_rows, ww = c - p.pad_cols;
+      TapEntry e;
+      e.dh = (short)floor_div(hh, p.stride_rows);
+      e.dw = (short)floor_div(ww, p.stride_cols);
+      e.a_map = (short)(pos_mod(hh, p.stride_rows) * p.stride_cols + pos_mod(ww, p.stride_cols));
+      e.b_tap = (short)(r * p.window_cols + c);
+      g.taps[nt++] = e;
+    }
+  g.num_taps = nt;
+  g.cblocks = ceil_div(p.channels, epr);
+  const uint64_t taps = (uint64_t)p.window_rows * p.window_cols;
+  if (hwcf) {
+    g.b_mode = B_MN_3;
+    const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)p.channels, taps, 1};
+    const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.channels * p.features * es,
+                            taps * p.channels * p.features * es};
+    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
+    if (!make_map(&g.b_map, dtype, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+  } else {
+    g.b_mode = B_K_FHWC;
+    const uint64_t dims[4] = {(uint64_t)p.channels, taps, (uint64_t)p.features, 1};
+    const uint64_t st[3] = {(uint64_t)p.channels * es, taps * p.channels * es, taps * p.channels * p.features * es};
+    const uint32_t box[4] = {(uint32_t)epr, 1, (uint32_t)g.bn, 1};
+    if (!make_map(&g.b_map, dtype, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+  }
+  set_epilogue(g, epi);
+  g.out = y;
+  g.out_dtype = dtype;
+  g.ext_w = p.out_cols;
+  g.ext_h = p.out_rows;
+  g.ext_n = p.batch;
+  g.ext_cols = p.features;
+  g.stride_w = p.features;
+  g.stride_h = (long long)p.out_cols * p.features;
+  g.stride_n = (long long)p.out_rows * p.out_cols * p.features;
+  g.vec_ok = 1;
+  return launch_gemm(g, dtype, s);
+}
+
+int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, const PdnnConv2DParams& p,
+                        cudaStream_t s) {
+  const size_t es = dtype_size(dtype);
+  const int sms = device_sm_count();
+  const bool hwcf = p.filter_format == 0;
+  const int epr = dtype == PDNN_F32 ? 32 : 64;
+  // dx is produced one output parity class at a time: positions h = sr*i + qh, w = sc*j + qw only
+  // receive taps with r = (qh + pad) mod sr, s = (qw + pad) mod sc, and within a class the
+  // relation between i and the dy row is a plain shift.
+  for (int qh = 0; qh < p.stride_rows; ++qh)
+    for (int qw = 0; qw < p.stride_cols; ++qw) {
+      const int Hq = ceil_div(p.in_rows - qh, p.stride_rows), Wq = ceil_div(p.in_cols - qw, p.stride_cols);
+      if (Hq <= 0 || Wq <= 0) continue;
+      GemmArgs g;
+      std::memset(&g, 0, sizeof(g));
+      g.a_mn = 0;
+      choose_box(kTileM, Wq, Hq, p.batch, &g.tw, &g.th, &g.tn);
+      g.etw = g.tw;
+      g.eth = g.th;
+      g.etn = g.tn;
+      g.tiles_w = ceil_div(Wq, g.tw);
+      g.tiles_h = ceil_div(Hq, g.th);
+      g.tiles_n = ceil_div(p.batch, g.tn);
+      const long long row_tiles = (long long)g.tiles_w * g.tiles_h * g.tiles_n;
+      g.bn = pick_bn(row_tiles, p.channels, hwcf ? 16 : epr, dtype == PDNN_F32 ? 128 : 256, sms);
+      g.n_tiles = ceil_div(p.channels, g.bn);
+      set_operand_layout(g, dtype, hwcf ? 0 : 1);
+      {
+        const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)p.out_cols, (uint64_t)p.out_rows, (uint64_t)p.batch};
+        const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.out_cols * p.features * es,
+                                (uint64_t)p.out_rows * p.out_cols * p.features * es};
+        const uint32_t box[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)g.th, (uint32_t)g.tn};
+        if (!make_map(&g.a_map[0], dtype, dy, dims, st, box)) return PDNN_INVALID_PARAMETER;
+        for (int i = 1; i < 4; ++i) g.a_map[i] = g.a_map[0];
+      }
+      int nt = 0;
+      for (int r = 0; r < p.window_rows; ++r) {
+        const int th = qh + p.pad_rows - r;
+        if (pos_mod(th, p.stride_rows) != 0) continue;
+        for (int c = 0; c < p.window_cols; ++c) {
+          const int tw = qw + p.pad_cols - c;
+          if (pos_mod(tw, p.stride_cols) != 0) continue;
+          TapEntry e;
+          e.dh = (short)floor_div(th, p.stride_rows);
+          e.dw = (short)floor_div(tw, p.stride_cols);
+          e.a_map = 0;
+          e.b_tap = (short)(r * p.window_cols + c);
+          g.taps[nt++] = e;
+        }
+      }
+      g.num_taps = nt;
+      g.cblocks = ceil_div(p.features, epr);
+      const uint64_t taps = (uint64_t)p.window_rows * p.window_cols;
+      if (hwcf) {
+        g.b_mode = B_K_3;
+        const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)p.channels, taps, 1};
+        const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.channels * p.features * es,
+                                taps * p.channels * p.features * es};
+        const uint32_t box[4] = {(uint32_t)epr, (uint32_t)g.bn, 1, 1};
+        if (!make_map(&g.b_map, dtype, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+      } else {
+        g.b_mode = B_MN_FHWC;
+        const uint64_t dims[4] = {(uint64_t)p.channels, taps, (uint64_t)p.features, 1};
+        const uint64_t st[3] = {(uint64_t)p.channels * es, taps * p.channels * es, taps * p.channels * p.features * es};
+        const uint32_t box[4] = {(uint32_t)epr, 1, (uint32_t)epr, 1};
+        if (!make_map(&g.b_map, dtype, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+      }
+      set_epilogue(g, nullptr);
+      g.out = static_cast<char*>(dx) + ((size_t)qh * p.in_cols + qw) * p.channels * es;
+      g.out_dtype = dtype;
+      g.ext_w = Wq;
+      g.ext_h = Hq;
+      g.ext_n = p.batch;
+      g.ext_cols = p.channels;
+      g.stride_w = (long long)p.stride_cols * p.channels;
+      g.stride_h = (long long)p.stride_rows * p.in_cols * p.channels;
+      g.stride_n = (long long)p.in_rows * p.in_cols * p.channels;
+      g.vec_ok = 1;
+      const int st_ = launch_gemm(g, dtype, s);
+      if (st_ != PDNN_OK) return st_;
+    }
+  return PDNN_OK;
+}
+
+struct FbpPlan {
+  int tw, th, tn, slabs_w, slabs_h, slabs_n, splits, slabs_per_split, m_tiles, n_tiles, bn;
+};
+
+FbpPlan plan_filter_backprop(int dtype, const PdnnConv2DParams& p, int sms) {
+  FbpPlan f;
+  const int epr = dtype == PDNN_F32 ? 32 : 64;
+  choose_box(epr, p.out_cols, p.out_rows, p.batch, &f.tw, &f.th, &f.tn);
+  f.slabs_w = ceil_div(p.out_cols, f.tw);
+  f.slabs_h = ceil_div(p.out_rows, f.th);
+  f.slabs_n = ceil_div(p.batch, f.tn);
+  f.m_tiles = ceil_div(p.channels, kTileM);
+  const int max_bn = dtype == PDNN_F32 ? 128 : 256;
+  f.bn = std::min(max_bn, ceil_div(p.features, epr) * epr);
+  f.n_tiles = ceil_div(p.features, f.bn);
+  const long long out_tiles = (long long)f.m_tiles * f.n_tiles * p.window_rows * p.window_cols;
+  const long long total_slabs = (long long)f.slabs_w * f.slabs_h * f.slabs_n;
+  long long want = std::max<long long>(1, (2ll * sms) / out_tiles);
+  want = std::min<long long>(want, std::max<long long>(1, total_slabs / 8));  // at least 8 slabs per split
+  want = std::min<long long>(want, 64);
+  f.slabs_per_split = (int)((total_slabs + want - 1) / want);
+  f.splits = (int)((total_slabs + f.slabs_per_split - 1) / f.slabs_per_split);
+  return f;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_splits_kernel(const float* __restrict__ partial, T* __restrict__ out,
+                                                            int splits, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
+    float sum = 0.f;
+    for (int sp = 0; sp < splits; ++sp) sum += partial[(size_t)sp * n + i];
+    out[i] = from_f32<T>(sum);
+  }
+}
+
+int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, const PdnnConv2DParams& p, void* ws,
+                         size_t ws_elems, cudaStream_t s) {
+  const size_t es = dtype_size(dtype);
+  const int sms = device_sm_count();
+  const int epr = dtype == PDNN_F32 ? 32 : 64;
+  const FbpPlan f = plan_filter_backprop(dtype, p, sms);
+  GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.a_mn = 1;
+  g.tw = f.tw;
+  g.th = f.th;
+  g.tn = f.tn;
+  g.etw = kTileM;
+  g.eth = 1;
+  g.etn = 1;
+  g.tiles_w = f.m_tiles;
+  g.tiles_h = g.tiles_n = 1;
+  g.bn = f.bn;
+  g.n_tiles = f.n_tiles;
+  g.slabs_w = f.slabs_w;
+  g.slabs_h = f.slabs_h;
+  g.slabs_n = f.slabs_n;
+  g.splits = f.splits;
+  g.slabs_per_split = f.slabs_per_split;
+  g.split_is_batch = 0;
+  set_operand_layout(g, dtype, 1);
+  const uint32_t box[4] = {(uint32_t)epr, (uint32_t)f.tw, (uint32_t)f.th, (uint32_t)f.tn};
+  if (!make_parity_maps(g, dtype, x, p, box)) return PDNN_INVALID_PARAMETER;
+  {
+    g.b_mode = B_MN_4;
+    const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)p.out_cols, (uint64_t)p.out_rows, (uint64_t)p.batch};
+    const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.out_cols * p.features * es,
+                            (uint64_t)p.out_rows * p.out_cols * p.features * es};
+    if (!make_map(&g.b_map, dtype, dy, dims, st, box)) return PDNN_INVALID_PARAMETER;
+  }
+  int nt = 0;
+  for (int r = 0; r < p.window_rows; ++r)
+    for (int c = 0; c < p.window_cols; ++c) {
+      const int hh = r - p.pad_rows, ww = c - p.pad_cols;
+      TapEntry e;
+      e.dh = (short)floor_div(hh, p.stride_rows);
+      e.dw = (short)floor_div(ww, p.stride_cols);
+      e.a_map = (short)(pos_mod(hh, p.stride_rows) * p.stride_cols + pos_mod(ww, p.stride_cols));
+      e.b_tap = 0;
+      g.taps[nt++] = e;
+    }
+  g.num_taps = nt;
+  set_epilogue(g, nullptr);
+  const size_t n_out = (size_t)nt * p.channels * p.features;
+  float* partial = nullptr;
+  bool own = false;
+  if (f.splits > 1) {
+    const size_t need_bytes = (size_t)f.splits * n_out * sizeof(float);
+    if (ws != nullptr && ws_elems * es >= need_bytes && aligned16(ws)) {
+      partial = static_cast<float*>(ws);
+    } else {
+      if (cudaMallocAsync(reinterpret_cast<void**>(&partial), need_bytes, s) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(PDNN_ALLOCATION_PROBLEM, "filter backprop: cannot allocate %zu bytes of scratch", need_bytes);
+      }
+      own = true;
+    }
+    g.out = partial;
+    g.out_dtype = PDNN_F32;
+  } else {
+    g.out = dw;
+    g.out_dtype = dtype;
+  }
+  g.ext_w = p.channels;
+  g.ext_h = g.ext_n = 1;
+  g.ext_cols = p.features;
+  g.stride_w = p.features;
+  g.stride_h = g.stride_n = 0;
+  g.split_stride = (long long)n_out;
+  g.tap_stride = (long long)p.channels * p.features;
+  g.vec_ok = 1;
+  int st = launch_gemm(g, dtype, s);
+  if (st == PDNN_OK && f.splits > 1) {
+    const unsigned grid = grid_for(n_out, 256, sms);
+    if (dtype == PDNN_F32) reduce_splits_kernel<float><<<grid, 256, 0, s>>>(partial, static_cast<float*>(dw), f.splits, n_out);
+    else if (dtype == PDNN_F16) reduce_splits_kernel<__half><<<grid, 256, 0, s>>>(partial, static_cast<__half*>(dw), f.splits, n_out);
+    else reduce_splits_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(partial, static_cast<__nv_bfloat16*>(dw), f.splits, n_out);
+    st = check_launch("filter backprop split reduction");
+  }
+  if (own) cudaFreeAsync(partial, s);
+  return st;
+}
+
+// ---- SIMT matmul ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) simt_matmul_kernel(const T* __restrict__ lhs, const T* __restrict__ rhs,
+                                                          T* __restrict__ out, int tl, int tr, int batches, int m, int k,
+                                                          int n, float beta) {
+  const size_t total = (size_t)batches * m * n;
+  for (size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
+    const int j = (int)(idx % n);
+    const int i = (int)((idx / n) % m);
+    const int b = (int)(idx / ((size_t)m * n));
+    const T* A = lhs + (size_t)b * m * k;
+    const T* B = rhs + (size_t)b * k * n;
+    float acc = 0.f;
+    for (int l = 0; l < k; ++l) {
+      const float av = to_f32(tl ? A[(size_t)l * m + i] : A[(size_t)i * k + l]);
+      const float bv = to_f32(tr ? B[(size_t)j * k + l] : B[(size_t)l * n + j]);
+      acc = fmaf(av, bv, acc);
+    }
+    if (beta != 0.f) acc += beta * to_f32(out[idx]);
+    out[idx] = from_f32<T>(acc);
+  }
+}
+
+}  // namespace
+
+// ================================================================================================
+// Public (library-internal) interface
+// ================================================================================================
+
+bool tc_conv_supported(int pass, int dtype, const void* in, const void* fil, const void* out,
+                       const PdnnConv2DParams& p) {
+  if (!conv_common_ok(dtype, p)) return false;
+  if (!aligned16(in) || !aligned16(fil) || !aligned16(out)) return false;
+  if (encode_fn() == nullptr) return false;
+  for (int ph = 0; ph < p.stride_rows; ++ph)
+    for (int pw = 0; pw < p.stride_cols; ++pw)
+      if (p.in_rows - ph <= 0 || p.in_cols - pw <= 0) return false;
+  if (pass == PDNN_FILTER_BACKPROP && p.filter_format != 0) return false;
+  return true;
+}
+
+size_t tc_conv_workspace_elems(int pass, int dtype, const PdnnConv2DParams& p) {
+  if (pass != PDNN_FILTER_BACKPROP || !conv_common_ok(dtype, p) || p.filter_format != 0) return 0;
+  int sms = device_sm_count();
+  if (sms <= 0) sms = 148;
+  const FbpPlan f = plan_filter_backprop(dtype, p, sms);
+  if (f.splits <= 1) return 0;
+  const size_t bytes = (size_t)f.splits * p.window_rows * p.window_cols * p.channels * p.features * sizeof(float);
+  return (bytes + dtype_size(dtype) - 1) / dtype_size(dtype);
+}
+
+int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
+              const PdnnConvEpilogue* epi, void* ws, size_t ws_elems, cudaStream_t s) {
+  switch (pass) {
+    case PDNN_FORWARD: return conv_forward(dtype, in, fil, out, p, epi, s);
+    case PDNN_INPUT_BACKPROP: return conv_input_backprop(dtype, in, fil, out, p, s);
+    case PDNN_FILTER_BACKPROP: return conv_filter_backprop(dtype, in, fil, out, p, ws, ws_elems, s);
+  }
+  return fail(PDNN_INVALID_PARAMETER, "bad pass %d", pass);
+}
+
+bool tc_matmul_supported(int dtype, int tl, int tr, const void* lhs, const void* rhs, const void* out, int batches,
+                         int m, int k, int n) {
+  const int align = dtype == PDNN_F32 ? 4 : 8;
+  if (!aligned16(lhs) || !aligned16(rhs) || !aligned16(out)) return false;
+  if (encode_fn() == nullptr) return false;
+  if ((tl ? m : k) % align) return false;  // lhs row pitch
+  if ((tr ? k : n) % align) return false;  // rhs row pitch
+  if (n % align) return false;             // output row pitch
+  // batch strides must be multiples of 16 bytes too
+  if (batches > 1 && (((size_t)m * k) % align || ((size_t)k * n) % align || ((size_t)m * n) % align)) return false;
+  return m > 0 && k > 0 && n > 0 && batches > 0;
+}
+
+int tc_matmul(int dtype, int tl, int tr, const void* lhs, const void* rhs, void* out, int batches, int m, int k, int n,
+              float beta, cudaStream_t s) {
+  const size_t es = dtype_size(dtype);
+  const int sms = device_sm_count();
+  const int epr = dtype == PDNN_F32 ? 32 : 64;
+  GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.a_mn = tl ? 1 : 0;
+  const int m_tiles = ceil_div(m, kTileM);
+  const int b_mn = tr ? 0 : 1;
+  g.bn = pick_bn((long long)m_tiles * batches, n, b_mn ? epr : 16, dtype == PDNN_F32 ? 128 : 256, sms);
+  g.n_tiles = ceil_div(n, g.bn);
+  set_operand_layout(g, dtype, b_mn);
+  g.taps[0] = TapEntry{0, 0, 0, 0};
+  g.num_taps = 1;
+  g.etw = kTileM;
+  g.eth = g.etn = 1;
+  if (!tl) {
+    g.tw = kTileM;
+    g.th = g.tn = 1;
+    g.tiles_w = m_tiles;
+    g.tiles_h = 1;
+    g.tiles_n = batches;
+    g.cblocks = ceil_div(k, epr);
+    g.b_batch_mul = 1;
+    const uint64_t dims[4] = {(uint64_t)k, (uint64_t)m, 1, (uint64_t)batches};
+    const uint64_t st[3] = {(uint64_t)k * es, (uint64_t)m * k * es, (uint64_t)m * k * es};
+    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)kTileM, 1, 1};
+    if (!make_map(&g.a_map[0], dtype, lhs, dims, st, box)) return PDNN_INVALID_PARAMETER;
+    if (b_mn) {
+      g.b_mode = B_MN_3;
+      const uint64_t bd[4] = {(uint64_t)n, (uint64_t)k, (uint64_t)batches, 1};
+      const uint64_t bs[3] = {(uint64_t)n * es, (uint64_t)k * n * es, (uint64_t)batches * k * n * es};
+      const uint32_t bb[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
+      if (!make_map(&g.b_map, dtype, rhs, bd, bs, bb)) return PDNN_INVALID_PARAMETER;
+    } else {
+      g.b_mode = B_K_3;
+      const uint64_t bd[4] = {(uint64_t)k, (uint64_t)n, (uint64_t)batches, 1};
+      const uint64_t bs[3] = {(uint64_t)k * es, (uint64_t)k * n * es, (uint64_t)batches * k * n * es};
+      const uint32_t bb[4] = {(uint32_t)epr, (uint32_t)g.bn, 1, 1};
+      if (!make_map(&g.b_map, dtype, rhs, bd, bs, bb)) return PDNN_INVALID_PARAMETER;
+    }
+    g.ext_w = m;
+    g.ext_h = 1;
+    g.ext_n = batches;
+    g.stride_w = n;
+    g.stride_h = 0;
+    g.stride_n = (long long)m * n;
+  } else {
+    g.tw = epr;
+    g.th = g.tn = 1;
+    g.tiles_w = m_tiles;
+    g.tiles_h = g.tiles_n = 1;
+    g.slabs_w = ceil_div(k, epr);
+    g.slabs_h = g.slabs_n = 1;
+    g.splits = batches;
+    g.slabs_per_split = g.slabs_w;
+    g.split_is_batch = 1;
+    const uint64_t dims[4] = {(uint64_t)m, (uint64_t)k, 1, (uint64_t)batches};
+    const uint64_t st[3] = {(uint64_t)m * es, (uint64_t)m * k * es, (uint64_t)m * k * es};
+    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
+    if (!make_map(&g.a_map[0], dtype, lhs, dims, st, box)) return PDNN_INVALID_PARAMETER;
+    if (b_mn) {
+      g.b_mode = B_MN_4;
+      const uint64_t bd[4] = {(uint64_t)n, (uint64_t)k, 1, (uint64_t)batches};
+      const uint64_t bs[3] = {(uint64_t)n * es, (uint64_t)k * n * es, (uint64_t)k * n * es};
+      const uint32_t bb[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
+      if (!make_map(&g.b_map, dtype, rhs, bd, bs, bb)) return PDNN_INVALID_PARAMETER;
+    } else {
+      g.b_mode = B_K_4;
+      const uint64_t bd[4] = {(uint64_t)k, (uint64_t)n, 1, (uint64_t)batches};
+      const uint64_t bs[3] = {(uint64_t)k * es, (uint64_t)k * n * es, (uint64_t)k * n * es};
+      const uint32_t bb[4] = {(uint32_t)epr, (uint32_t)g.bn, 1, 1};
+      if (!make_map(&g.b_map, dtype, rhs, bd, bs, bb)) return PDNN_INVALID_PARAMETER;
+    }
+    g.ext_w = m;
+    g.ext_h = g.ext_n = 1;
+    g.stride_w = n;
+    g.split_stride = (long long)m * n;
+    g.tap_stride = 0;
+  }
+  for (int i = 1; i < 4; ++i) g.a_map[i] = g.a_map[0];
+  set_epilogue(g, nullptr);
+  g.beta = beta;
+  g.out = out;
+  g.out_dtype = dtype;
+  g.ext_cols = n;
+  g.vec_ok = 1;
+  return launch_gemm(g, dtype, s);
+}
+
+int simt_matmul(int dtype, int tl, int tr, const void* lhs, const void* rhs, void* out, int batches, int m, int k, int n,
+                float beta, cudaStream_t s) {
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  const size_t total = (size_t)batches * m * n;
+  const unsigned grid = grid_for(total, 256, sms);
+  if (dtype == PDNN_F32)
+    simt_matmul_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(lhs), static_cast<const float*>(rhs),
+                                                    static_cast<float*>(out), tl, tr, batches, m, k, n, beta);
+  else if (dtype == PDNN_F16)
+    simt_matmul_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(lhs), static_cast<const __half*>(rhs),
+                                                     static_cast<__half*>(out), tl, tr, batches, m, k, n, beta);
+  else if (dtype == PDNN_BF16)
+    simt_matmul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(lhs),
+                                                            static_cast<const __nv_bfloat16*>(rhs),
+                                                            static_cast<__nv_bfloat16*>(out), tl, tr, batches, m, k, n, beta);
+  else
+    return fail(PDNN_INVALID_PARAMETER, "unknown dtype %d", dtype);
+  return check_launch("simt matmul");
+}
+
+int tc_read_error_record(unsigned out[4], int clear) {
+  if (cudaMemcpyFromSymbol(out, g_error_record, sizeof(unsigned) * 4) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(PDNN_ALLOCATION_PROBLEM, "cannot read the device error record");
+  }
+  if (clear) {
+    const unsigned zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_error_record, zero, sizeof(zero));
+  }
+  return PDNN_OK;
+}
+
+}  // namespace pdnn

@@ -1,0 +1,169 @@
+"""The tcgen05 implicit-GEMM engine (conv2d forward / input backprop / filter backprop and the
+matmul backend) against the CPU oracle on seeded inputs, through the C ABI.
+
+Parity bars (relative error = max |diff| / max |ref| on identical, already-rounded inputs):
+fp32 via 3xTF32 <= 1e-4, fp16 / bf16 <= 2e-2.
+"""
+import numpy as np
+import pytest
+import torch
+
+import portdnn_b200 as pd
+from conftest import rel_err
+from gpu_util import TOL, assert_no_device_error, rounded, to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+
+
+def _conv_case(orc, dtype, n, h, w, c, k, win, st, same=True, pad=None, seed=0):
+    rng = np.random.default_rng(seed)
+    p = pd.conv_params(n, h, w, c, k, win, st, same, pad)
+    po = orc.conv_params(n, h, w, c, k, win, st, same, pad)
+    x = rounded(rng.uniform(-1, 1, n * h * w * c).astype(np.float32), dtype)
+    wt = rounded((rng.uniform(-1, 1, win * win * c * k) * np.sqrt(1.0 / (win * win * c))).astype(np.float32), dtype)
+    dy = rounded(rng.standard_normal(n * p.out_rows * p.out_cols * k).astype(np.float32), dtype)
+    return p, po, x, wt, dy
+
+
+FWD_SHAPES = [
+    # n, h, w, c, k, window, stride, same, pad
+    (1, 56, 56, 256, 256, 3, 1, True, None),   # the single VGG-style layer
+    (2, 56, 56, 64, 64, 3, 1, True, None),     # ResNet stage-1 3x3
+    (2, 56, 56, 64, 256, 1, 1, True, None),    # 1x1 expand
+    (2, 56, 56, 128, 128, 3, 2, True, None),   # stride-2 3x3 (pad_low 0, pad_high 1)
+    (2, 56, 56, 256, 512, 1, 2, True, None),   # stride-2 projection
+    (3, 14, 14, 256, 256, 3, 1, True, None),
+    (5, 7, 7, 512, 512, 3, 1, True, None),
+    (2, 32, 32, 8, 64, 7, 2, None, 3),         # stem-like 7x7/2 with explicit pad 3
+    (2, 15, 13, 24, 40, 3, 1, True, None),     # ragged rows, column tail
+    (3, 9, 9, 16, 16, 5, 2, False, None),      # VALID
+    (2, 10, 12, 72, 96, 1, 1, True, None),     # MobileNet-like widths
+]
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("shape", FWD_SHAPES)
+def test_forward_against_oracle(orc, dtype, shape):
+    n, h, w, c, k, win, st, same, pad = shape
+    p, po, x, wt, _ = _conv_case(orc, dtype, n, h, w, c, k, win, st, bool(same), pad)
+    y = to_host(pd.conv2d(pd.FORWARD, to_dev(x, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_TILED))
+    assert_no_device_error()
+    assert rel_err(y, orc.conv2d(orc.FORWARD, x, wt, po)) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_forward_fhwc_filter(orc, dtype):
+    n, h, w, c, k, win, st = 2, 20, 20, 64, 48, 3, 1
+    p, po, x, wt, _ = _conv_case(orc, dtype, n, h, w, c, k, win, st)
+    p.filter_format = 2
+    w_fhwc = np.ascontiguousarray(wt.reshape(win, win, c, k).transpose(3, 0, 1, 2))
+    y = to_host(pd.conv2d(pd.FORWARD, to_dev(x, dtype), to_dev(w_fhwc, dtype), p, algorithm=pd.ALGO_IM2COL))
+    assert_no_device_error()
+    assert rel_err(y, orc.conv2d(orc.FORWARD, x, wt, po)) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_forward_fused_epilogue(orc, dtype):
+    n, h, w, c, k, win, st = 2, 28, 28, 128, 128, 3, 1
+    p, po, x, wt, _ = _conv_case(orc, dtype, n, h, w, c, k, win, st)
+    rng = np.random.default_rng(5)
+    bias = rounded(rng.standard_normal(k).astype(np.float32), dtype)
+    prev = rounded(rng.standard_normal(n * h * w * k).astype(np.float32), dtype)
+    conv = orc.conv2d(orc.FORWARD, x, wt, po)
+    ref = np.maximum(0.5 * conv + np.tile(bias, n * h * w), 0) + 0.25 * prev
+    out = to_dev(prev, dtype)
+    pd.conv2d(pd.FORWARD, to_dev(x, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_TILED, out=out,
+              bias=to_dev(bias, dtype), activation=pd.ACT_RELU, alpha=0.5, beta=0.25)
+    assert_no_device_error()
+    assert rel_err(to_host(out), ref) <= TOL[dtype]
+
+
+BWD_SHAPES = [
+    (2, 28, 28, 128, 128, 3, 1, True, None),
+    (2, 28, 28, 64, 256, 1, 1, True, None),
+    (2, 28, 28, 128, 128, 3, 2, True, None),
+    (2, 28, 28, 256, 512, 1, 2, True, None),
+    (3, 7, 7, 512, 512, 3, 1, True, None),
+    (2, 15, 13, 24, 40, 3, 1, True, None),
+    (2, 17, 17, 16, 32, 5, 2, False, None),
+]
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("shape", BWD_SHAPES)
+def test_input_backprop_against_oracle(orc, dtype, shape):
+    n, h, w, c, k, win, st, same, pad = shape
+    p, po, _, wt, dy = _conv_case(orc, dtype, n, h, w, c, k, win, st, bool(same), pad)
+    dx = to_host(pd.conv2d(pd.INPUT_BACKPROP, to_dev(dy, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_TILED))
+    assert_no_device_error()
+    assert rel_err(dx, orc.conv2d(orc.INPUT_BACKPROP, dy, wt, po)) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("shape", BWD_SHAPES)
+def test_filter_backprop_against_oracle(orc, dtype, shape):
+    n, h, w, c, k, win, st, same, pad = shape
+    p, po, x, _, dy = _conv_case(orc, dtype, n, h, w, c, k, win, st, bool(same), pad)
+    dw = to_host(pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, dtype), to_dev(dy, dtype), p, algorithm=pd.ALGO_TILED))
+    assert_no_device_error()
+    assert rel_err(dw, orc.conv2d(orc.FILTER_BACKPROP, x, dy, po)) <= TOL[dtype]
+
+
+def test_filter_backprop_with_caller_workspace(orc):
+    n, h, w, c, k, win, st = 8, 28, 28, 64, 64, 3, 1
+    p, po, x, _, dy = _conv_case(orc, "f16", n, h, w, c, k, win, st)
+    _, rec = pd.conv2d_workspace_size(pd.FILTER_BACKPROP, pd.F16, p, pd.ALGO_TILED)
+    assert rec > 0
+    ws = torch.empty(rec, dtype=torch.float16, device="cuda")
+    dw = to_host(pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, "f16"), to_dev(dy, "f16"), p, algorithm=pd.ALGO_TILED,
+                           workspace=ws))
+    assert_no_device_error()
+    assert rel_err(dw, orc.conv2d(orc.FILTER_BACKPROP, x, dy, po)) <= TOL["f16"]
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("tl", [False, True])
+@pytest.mark.parametrize("tr", [False, True])
+@pytest.mark.parametrize("dims", [(1, 256, 192, 128, 0.0), (2, 200, 136, 72, 0.0), (3, 128, 64, 64, 1.0)])
+def test_matmul_against_oracle(orc, dtype, tl, tr, dims):
+    batches, m, k, n, beta = dims
+    rng = np.random.default_rng(21)
+    a = rounded(rng.uniform(-1, 1, batches * m * k).astype(np.float32), dtype)
+    b = rounded(rng.uniform(-1, 1, batches * k * n).astype(np.float32), dtype)
+    c0 = rounded(rng.uniform(-1, 1, batches * m * n).astype(np.float32), dtype)
+    out = to_dev(c0, dtype)
+    pd.matmul(to_dev(a, dtype), to_dev(b, dtype), batches, m, k, n, tl, tr, beta=beta, out=out)
+    assert_no_device_error()
+    ref = orc.matmul(tl, tr, a, b, batches, m, k, n, beta=beta, out=c0)
+    assert rel_err(to_host(out), ref) <= TOL[dtype]
+
+
+def test_matmul_odd_sizes_take_the_simt_kernel(orc):
+    batches, m, k, n = 2, 13, 7, 5
+    rng = np.random.default_rng(22)
+    a = rng.standard_normal(batches * m * k).astype(np.float32)
+    b = rng.standard_normal(batches * k * n).astype(np.float32)
+    got = to_host(pd.matmul(to_dev(a, "f32"), to_dev(b, "f32"), batches, m, k, n))
+    assert rel_err(got, orc.matmul(False, False, a, b, batches, m, k, n)) <= 1e-5
+
+
+@pytest.mark.parametrize("shape", [(64, 56, 56, 64, 64, 3, 1), (64, 56, 56, 256, 128, 1, 2), (32, 28, 28, 128, 128, 3, 2)])
+def test_full_size_layers_tensor_core_vs_direct_kernel(shape):
+    """At sizes the CPU oracle cannot finish quickly: the tensor-core engine against the direct
+    CUDA kernel (itself checked against the oracle and the reference vectors), all three passes,
+    plus linearity of the forward pass."""
+    n, h, w, c, k, win, st = shape
+    g = torch.Generator(device="cuda").manual_seed(3)
+    p = pd.conv_params(n, h, w, c, k, win, st)
+    x = (torch.rand(n * h * w * c, device="cuda", generator=g) * 2 - 1).half()
+    wt = ((torch.rand(win * win * c * k, device="cuda", generator=g) * 2 - 1) * (1.0 / (win * win * c)) ** 0.5).half()
+    dy = torch.randn(n * p.out_rows * p.out_cols * k, device="cuda", generator=g).half()
+    for pass_, a, b in ((pd.FORWARD, x, wt), (pd.INPUT_BACKPROP, dy, wt), (pd.FILTER_BACKPROP, x, dy)):
+        fast = pd.conv2d(pass_, a, b, p, algorithm=pd.ALGO_TILED).float()
+        slow = pd.conv2d(pass_, a, b, p, algorithm=pd.ALGO_DIRECT).float()
+        assert_no_device_error()
+        err = (fast - slow).abs().max().item() / slow.abs().max().item()
+        assert err <= 2e-2, (pass_, err)
+    y1 = pd.conv2d(pd.FORWARD, x, wt, p).float()
+    y2 = pd.conv2d(pd.FORWARD, (x.float() * 0.5).half(), wt, p).float()
+    assert ((y1 * 0.5 - y2).abs().max() / y1.abs().max()).item() <= 2e-3
