@@ -48,6 +48,7 @@ enum BMode { B_MN_3 = 0, B_K_3 = 1, B_K_FHWC = 2, B_MN_FHWC = 3, B_MN_4 = 4, B_K
 struct alignas(64) GemmArgs {
   CUtensorMap a_map[4];
   CUtensorMap b_map;
+  CUtensorMap out_map;  // used when tma_store != 0
   TapEntry taps[kMaxTaps];
   int a_mn;          // 0: A rows are output pixels (K-major); 1: A rows are reduction steps (MN-major)
   int b_mode;        // BMode
@@ -63,6 +64,7 @@ struct alignas(64) GemmArgs {
   int stages, tmem_cols;
   unsigned idesc;
   unsigned a_lbo, a_sbo, a_kadv, b_lbo, b_sbo, b_kadv;  // bytes
+  unsigned a_layout, b_layout;  // descriptor swizzle codes
   int a_boxes, b_boxes;
   unsigned a_box_bytes, b_box_bytes;
   // epilogue
@@ -73,6 +75,8 @@ struct alignas(64) GemmArgs {
   int ext_w, ext_h, ext_n, ext_cols;
   long long stride_w, stride_h, stride_n, split_stride, tap_stride;  // elements
   int vec_ok;  // rows are 16-byte aligned: packed stores allowed
+  int tma_store;  // 1: the epilogue stages 128-byte column blocks in shared memory and stores them by TMA
+  int cpb;        // output columns per 128-byte block: 64 (16-bit) or 32 (fp32)
 };
 
 struct TileCoord {
@@ -189,6 +193,79 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& a, const TileCoord
   }
 }
 
+// Epilogue through shared memory: each of the 128 epilogue threads owns one accumulator row.
+// Per 128-byte column block (64 16-bit or 32 fp32 outputs) the row is converted and written to
+// a staging tile in the 128-byte swizzled layout (16-byte chunk j of row r lands at chunk
+// j ^ (r % 8), which spreads a warp's stores over all banks), then one thread issues a TMA store
+// of the whole 128-row block; the tensor map clips rows and columns that fall outside the
+// tensor.  Two staging tiles alternate so that the store of one block overlaps the conversion
+// of the next.  Thread 64 (lane 0 of the first epilogue warp) issues and tracks the stores; the
+// hand-offs use mbarriers (free: the issuer says the tile may be overwritten; written: all 128
+// rows are in place) so that every wait is bounded.  Returns false if a wait gave up.
+struct EpilogueSync {
+  uint32_t free_bar[2], written_bar[2];
+  volatile int* abort_flag;
+};
+
+template <typename OutT>
+__device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc, int row,
+                                                  bool zero, uint8_t* staging, uint32_t staging_addr,
+                                                  const EpilogueSync& sync, uint32_t& store_count) {
+  constexpr int CPB = 128 / sizeof(OutT);  // columns per block
+  constexpr int P = 16 / sizeof(OutT);     // columns per 16-byte chunk
+  const OutT* bias = static_cast<const OutT*>(a.bias);
+  const bool issuer = threadIdx.x == 64;
+  const int c2 = a.a_mn ? t.tap : t.h0, c3 = a.a_mn ? t.split : t.n0;
+  for (int c0 = 0; c0 < a.bn; c0 += CPB, ++store_count) {
+    const uint32_t sbuf = store_count & 1u, par = (store_count >> 1) & 1u;
+    if (issuer) {
+      bulk_wait_group_read<1>();  // the store that last used this tile has finished reading it
+      mbar_arrive(sync.free_bar[sbuf]);
+    }
+    if (!mbar_wait(sync.free_bar[sbuf], par, sync.abort_flag, g_error_record, 0x600u + sbuf)) return false;
+    uint8_t* tile = staging + sbuf * kABytes + (size_t)row * 128;
+#pragma unroll
+    for (int half = 0; half < CPB / 32; ++half) {
+      uint32_t acc[32];
+      if (!zero) {
+        tmem_ld_32x32(tmem_acc + (uint32_t)(c0 + half * 32), acc);
+        tmem_wait_ld();
+      }
+      const int colbase = t.nf0 + c0 + half * 32;
+#pragma unroll
+      for (int g = 0; g < 32 / P; ++g) {
+        float v[P];
+#pragma unroll
+        for (int i = 0; i < P; ++i) v[i] = zero ? 0.f : a.alpha * __uint_as_float(acc[g * P + i]);
+        if (bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < P; ++i) {
+            const int c = colbase + g * P + i;
+            if (c < a.ext_cols) v[i] += to_f32(__ldg(bias + c));
+          }
+        }
+        if (a.act != PDNN_ACT_NONE) {
+#pragma unroll
+          for (int i = 0; i < P; ++i) v[i] = apply_activation(v[i], a.act);
+        }
+        Vec16<OutT> pk;
+#pragma unroll
+        for (int i = 0; i < P; ++i) pk.set(i, from_f32<OutT>(v[i]));
+        const int chunk = half * (32 / P) + g;  // 0..7 within the 128-byte row
+        *reinterpret_cast<uint4*>(tile + ((chunk ^ (row & 7)) << 4)) = pk.raw;
+      }
+    }
+    fence_proxy_async_smem();
+    mbar_arrive(sync.written_bar[sbuf]);
+    if (issuer) {
+      if (!mbar_wait(sync.written_bar[sbuf], par, sync.abort_flag, g_error_record, 0x610u + sbuf)) return false;
+      tma_store_4d(&a.out_map, staging_addr + sbuf * kABytes, t.nf0 + c0, t.w0, c2, c3);
+      bulk_commit_group();
+    }
+  }
+  return true;
+}
+
 template <bool SPLIT>
 __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const __grid_constant__ GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -201,16 +278,20 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
   const uint32_t part_bytes = kABytes + b_bytes;              // one A tile + one B tile
   const uint32_t stage_bytes = SPLIT ? 2u * part_bytes : part_bytes;
   const int S = a.stages;
-  // barrier block after the stages
-  uint8_t* bar_mem = smem + (size_t)S * stage_bytes;
-  const uint32_t bar_base = base + (uint32_t)S * stage_bytes;
+  // two 16 KB staging tiles for the TMA-store epilogue, then the barrier block
+  const uint32_t staging_base = base + (uint32_t)S * stage_bytes;
+  const uint32_t staging_bytes = a.tma_store ? 2u * (uint32_t)kABytes : 0u;
+  uint8_t* bar_mem = smem + (size_t)S * stage_bytes + staging_bytes;
+  const uint32_t bar_base = staging_base + staging_bytes;
   auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(kMaxStages + s); };
   auto ready_bar = [&](int s) { return bar_base + 8u * (uint32_t)(2 * kMaxStages + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * kMaxStages + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * kMaxStages + 2 + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 8 * (3 * kMaxStages + 4));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * (3 * kMaxStages + 4) + 8);
+  auto epi_free_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * kMaxStages + 4 + b); };
+  auto epi_written_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * kMaxStages + 6 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 8 * (3 * kMaxStages + 8));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * (3 * kMaxStages + 8) + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -223,6 +304,8 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full_bar(b), 1);
       mbar_init(acc_empty_bar(b), 4);
+      mbar_init(epi_free_bar(b), 1);
+      mbar_init(epi_written_bar(b), 128);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -317,16 +400,16 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
           tc_fence_after_sync();
           const uint32_t sa = base + (uint32_t)s * stage_bytes;
           const uint32_t sb = sa + kABytes;
-          const uint64_t a_hi = make_smem_desc(sa, a.a_lbo, a.a_sbo);
-          const uint64_t b_hi = make_smem_desc(sb, a.b_lbo, a.b_sbo);
+          const uint64_t a_hi = make_smem_desc(sa, a.a_lbo, a.a_sbo, a.a_layout);
+          const uint64_t b_hi = make_smem_desc(sb, a.b_lbo, a.b_sbo, a.b_layout);
           const bool first_step = (ks == t.ks_begin);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint64_t ka = (uint64_t)((a.a_kadv * (uint32_t)k) >> 4), kb = (uint64_t)((a.b_kadv * (uint32_t)k) >> 4);
             const uint32_t acc = (first_step && k == 0) ? 0u : 1u;
             if (SPLIT) {
-              const uint64_t a_lo = make_smem_desc(sa + part_bytes, a.a_lbo, a.a_sbo);
-              const uint64_t b_lo = make_smem_desc(sb + part_bytes, a.b_lbo, a.b_sbo);
+              const uint64_t a_lo = make_smem_desc(sa + part_bytes, a.a_lbo, a.a_sbo, a.a_layout);
+              const uint64_t b_lo = make_smem_desc(sb + part_bytes, a.b_lbo, a.b_sbo, a.b_layout);
               mma_tf32(d_tmem, a_lo + ka, b_hi + kb, a.idesc, acc);
               mma_tf32(d_tmem, a_hi + ka, b_lo + kb, a.idesc, 1u);
               mma_tf32(d_tmem, a_hi + ka, b_hi + kb, a.idesc, 1u);
@@ -345,7 +428,8 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
     // ------------------------------- epilogue ------------------------------------------------
     const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
     const int row = q * 32 + lane;
-    uint32_t tcount = 0;
+    uint32_t tcount = 0, store_count = 0;
+    const EpilogueSync esync{{epi_free_bar(0), epi_free_bar(1)}, {epi_written_bar(0), epi_written_bar(1)}, abort_flag};
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
       const TileCoord t = decode_tile(a, tile);
       const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
@@ -353,13 +437,24 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
       tc_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
       const bool zero = !(t.ks_end > t.ks_begin);
-      if (a.out_dtype == PDNN_F16) epilogue_tile<__half>(a, t, tmem_acc, row, zero);
-      else if (a.out_dtype == PDNN_BF16) epilogue_tile<__nv_bfloat16>(a, t, tmem_acc, row, zero);
-      else epilogue_tile<float>(a, t, tmem_acc, row, zero);
+      if (a.tma_store) {
+        uint8_t* staging = smem + (size_t)S * stage_bytes;
+        bool ok;
+        if (a.out_dtype == PDNN_F16) ok = epilogue_tile_tma<__half>(a, t, tmem_acc, row, zero, staging, staging_base, esync, store_count);
+        else if (a.out_dtype == PDNN_BF16) ok = epilogue_tile_tma<__nv_bfloat16>(a, t, tmem_acc, row, zero, staging, staging_base, esync, store_count);
+        else ok = epilogue_tile_tma<float>(a, t, tmem_acc, row, zero, staging, staging_base, esync, store_count);
+        if (!ok) break;
+      } else {
+        if (a.out_dtype == PDNN_F16) epilogue_tile<__half>(a, t, tmem_acc, row, zero);
+        else if (a.out_dtype == PDNN_BF16) epilogue_tile<__nv_bfloat16>(a, t, tmem_acc, row, zero);
+        else epilogue_tile<float>(a, t, tmem_acc, row, zero);
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar((int)buf));
     }
+    // the staging tiles must not be released while a store is still reading them
+    if (a.tma_store && threadIdx.x == 64) bulk_wait_group<0>();
   } else if (SPLIT) {
     // ------------------------------- hi/lo split (fp32 as 3xTF32) ----------------------------
     // hi keeps the 19 leading bits (what the tensor core reads of an fp32 word); lo = x - hi is
@@ -436,10 +531,12 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 4-D tiled map with the 128-byte swizzle and zero fill outside the tensor.  dims[0] is the
-// contiguous dimension; strides_bytes[i] is the stride of dims[i+1].
-bool make_map(CUtensorMap* map, int dtype, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
-              const uint32_t box[4]) {
+// 4-D tiled map with a 128-byte swizzle and zero fill outside the tensor.  dims[0] is the
+// contiguous dimension; strides_bytes[i] is the stride of dims[i+1].  A 32-bit operand that the
+// MMA reads MN-major must be swizzled in 32-byte units (the only MN-major layout tcgen05 accepts
+// for tf32); everything else uses the ordinary 16-byte-unit pattern.
+bool make_map(CUtensorMap* map, int dtype, bool mn_major, const void* base, const uint64_t dims[4],
+              const uint64_t strides_bytes[3], const uint32_t box[4]) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) {
     fail(PDNN_ALLOCATION_PROBLEM, "cuTensorMapEncodeTiled is unavailable");
@@ -455,8 +552,10 @@ bool make_map(CUtensorMap* map, int dtype, const void* base, const uint64_t dims
     b[i] = box[i];
   }
   for (int i = 0; i < 3; ++i) st[i] = strides_bytes[i];
-  CUresult r = fn(map, dt, 4, const_cast<void*>(base), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUtensorMapSwizzle sw =
+      (dtype == PDNN_F32 && mn_major) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+  CUresult r = fn(map, dt, 4, const_cast<void*>(base), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     fail(PDNN_INVALID_PARAMETER,
          "cuTensorMapEncodeTiled failed (%d): dims %llu %llu %llu %llu strides %llu %llu %llu box %u %u %u %u", (int)r,
@@ -496,6 +595,7 @@ int pick_bn(long long row_tiles, int cols, int unit, int max_bn, int sms) {
   double best = 1e30;
   for (int bn = unit; bn <= max_bn; bn += unit) {
     if (bn != 16 && bn != 32 && bn != 48 && bn % 64 != 0) continue;
+    if (cols >= 64 && bn % 64 != 0) continue;  // whole 128-byte output blocks for the TMA-store epilogue
     const long long tiles = row_tiles * ceil_div(cols, bn);
     const double waves = (double)((tiles + sms - 1) / sms);
     const double cost = waves * (bn + 40.0);
@@ -520,9 +620,13 @@ void set_operand_layout(GemmArgs& g, int dtype, int b_mn) {
   const unsigned kstep_bytes_k = 32;                     // one UMMA K step inside a 128-byte row
   const unsigned kstep_bytes_mn = (f32 ? 8u : 16u) * 128u;  // UMMA K rows of 128 bytes
   const unsigned rows = (unsigned)g.epr;                 // reduction rows per stage for MN-major operands
+  // MN-major fp32: 32-byte swizzle units, pattern repeats every 4 rows of 128 bytes.
+  const unsigned mn_sbo = f32 ? 512u : 1024u, mn_layout = f32 ? 1u : 2u;
+  g.a_layout = g.a_mn ? mn_layout : 2u;
+  g.b_layout = b_mn ? mn_layout : 2u;
   if (g.a_mn) {
     g.a_lbo = rows * 128u;
-    g.a_sbo = 1024u;
+    g.a_sbo = mn_sbo;
     g.a_kadv = kstep_bytes_mn;
     g.a_boxes = kTileM / g.epr;
     g.a_box_bytes = rows * 128u;
@@ -535,7 +639,7 @@ void set_operand_layout(GemmArgs& g, int dtype, int b_mn) {
   }
   if (b_mn) {
     g.b_lbo = rows * 128u;
-    g.b_sbo = 1024u;
+    g.b_sbo = mn_sbo;
     g.b_kadv = kstep_bytes_mn;
     g.b_boxes = g.bn / g.epr;
     g.b_box_bytes = rows * 128u;
@@ -548,9 +652,23 @@ void set_operand_layout(GemmArgs& g, int dtype, int b_mn) {
   }
   g.idesc = make_idesc(dtype == PDNN_F32 ? 2 : (dtype == PDNN_BF16 ? 1 : 0), g.a_mn, b_mn, g.bn);
   g.tmem_cols = next_pow2(2 * g.bn);
-  const unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (f32 ? 2u : 1u);
-  int stages = (int)((kSmemBudget - 2048) / stage);
-  g.stages = std::max(2, std::min(kMaxStages, stages));
+}
+
+// Chooses the store path of the epilogue and sizes the pipeline; call once the output fields of
+// `g` are set.  out_dims / out_strides describe the output as a 4-D tensor whose dimension 0 is
+// the column (feature) axis and whose other dimensions are the ones the row-tile box spans.
+bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], const uint64_t out_strides[3]) {
+  g.cpb = 128 / (int)dtype_size(g.out_dtype);
+  g.tma_store = 0;
+  if (g.beta == 0.f && g.bn % g.cpb == 0 && aligned16(g.out)) {
+    const uint32_t box[4] = {(uint32_t)g.cpb, (uint32_t)g.etw, (uint32_t)g.eth, (uint32_t)g.etn};
+    if (!make_map(&g.out_map, g.out_dtype, false, g.out, out_dims, out_strides, box)) return false;
+    g.tma_store = 1;
+  }
+  const unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (compute_dtype == PDNN_F32 ? 2u : 1u);
+  const int budget = kSmemBudget - 2048 - (g.tma_store ? 2 * kABytes : 0);
+  g.stages = std::max(2, std::min(kMaxStages, (int)(budget / stage)));
+  return true;
 }
 
 int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
@@ -561,7 +679,8 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   if (total > 0x7FFFFFFFll) return fail(PDNN_INDEX_EXCEEDED, "tensor-core gemm: too many tiles");
   const unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
   // At least 120 KB so that two CTAs never share an SM (and with it the tensor memory).
-  const size_t smem = std::max<size_t>(1024 + (size_t)g.stages * stage + 512, 120 * 1024);
+  const size_t smem =
+      std::max<size_t>(1024 + (size_t)g.stages * stage + (g.tma_store ? 2 * kABytes : 0) + 512, 120 * 1024);
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -603,7 +722,8 @@ bool conv_common_ok(int dtype, const PdnnConv2DParams& p) {
 
 // One tensor map per input parity of x ([C, W', H', N] view of the pixels with h % sr == ph,
 // w % sc == pw).  Returns false if a parity class is empty.
-bool make_parity_maps(GemmArgs& g, int dtype, const void* x, const PdnnConv2DParams& p, const uint32_t box[4]) {
+bool make_parity_maps(GemmArgs& g, int dtype, bool mn_major, const void* x, const PdnnConv2DParams& p,
+                      const uint32_t box[4]) {
   const size_t es = dtype_size(dtype);
   for (int ph = 0; ph < p.stride_rows; ++ph)
     for (int pw = 0; pw < p.stride_cols; ++pw) {
@@ -614,10 +734,186 @@ bool make_parity_maps(GemmArgs& g, int dtype, const void* x, const PdnnConv2DPar
                               (uint64_t)p.stride_rows * p.in_cols * p.channels * es,
                               (uint64_t)p.in_rows * p.in_cols * p.channels * es};
       const char* base = static_cast<const char*>(x) + ((size_t)ph * p.in_cols + pw) * p.channels * es;
-      if (!make_map(&g.a_map[ph * p.stride_cols + pw], dtype, base, dims, st, box)) return false;
+      if (!make_map(&g.a_map[ph * p.stride_cols + pw], dtype, mn_major, base, dims, st, box)) return false;
     }
   for (int i = p.stride_rows * p.stride_cols; i < 4; ++i) g.a_map[i] = g.a_map[0];
   return true;
+}
+
+// Output side of a forward convolution: y is [N, Ho, Wo, K].
+int finish_forward(GemmArgs& g, int dtype, void* y, const PdnnConv2DParams& p, const PdnnConvEpilogue* epi,
+                   cudaStream_t s) {
+  const size_t es = dtype_size(dtype);
+  set_epilogue(g, epi);
+  g.out = y;
+  g.out_dtype = dtype;
+  g.ext_w = p.out_cols;
+  g.ext_h = p.out_rows;
+  g.ext_n = p.batch;
+  g.ext_cols = p.features;
+  g.stride_w = p.features;
+  g.stride_h = (long long)p.out_cols * p.features;
+  g.stride_n = (long long)p.out_rows * p.out_cols * p.features;
+  g.vec_ok = 1;
+  const uint64_t od[4] = {(uint64_t)p.features, (uint64_t)p.out_cols, (uint64_t)p.out_rows, (uint64_t)p.batch};
+  const uint64_t os[3] = {(uint64_t)p.features * es, (uint64_t)p.out_cols * p.features * es,
+                          (uint64_t)p.out_rows * p.out_cols * p.features * es};
+  if (!setup_store(g, dtype, od, os)) return PDNN_INVALID_PARAMETER;
+  return launch_gemm(g, dtype, s);
+}
+
+// ---- forward convolution for very few input channels (network stems) ---------------------------
+// With C < 8 (16-bit) or C < 4 (fp32) a pixel is narrower than the 16-byte unit TMA needs, and a
+// 64-element reduction step per tap would be mostly padding.  Instead the input is first copied
+// into a zero-padded tensor with CP = 8 (4) channels per pixel and explicit spatial padding; one
+// 128-byte row then holds 8 consecutive pixels, i.e. a whole filter row (S <= 8) of one output
+// pixel, and the tensor map walks output pixels with a stride of stride_cols pixels, so rows
+// overlap.  The reduction runs over filter rows: R steps of 64 (32) elements.  The filter is
+// repacked the same way ([R][8][CP][K], zeros in the padding).
+template <typename T>
+__global__ void __launch_bounds__(256) pack_small_c_input_kernel(const T* __restrict__ x, uint4* __restrict__ xp, int N,
+                                                                int H, int W, int C, int Hp, int Wp, int pad_top,
+                                                                int pad_left) {
+  constexpr int CP = 16 / sizeof(T);
+  const size_t total = (size_t)N * Hp * Wp;
+  for (size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
+    const int wp = (int)(idx % Wp);
+    const size_t t = idx / Wp;
+    const int hp = (int)(t % Hp);
+    const int n = (int)(t / Hp);
+    const int h = hp - pad_top, w = wp - pad_left;
+    Vec16<T> pk;
+    pk.raw = make_uint4(0u, 0u, 0u, 0u);
+    if (h >= 0 && h < H && w >= 0 && w < W) {
+      const T* src = x + (((size_t)n * H + h) * W + w) * C;
+      for (int c = 0; c < C && c < CP; ++c) pk.set(c, src[c]);
+    }
+    xp[idx] = pk.raw;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) pack_small_c_filter_kernel(const T* __restrict__ w, T* __restrict__ wp, int R,
+                                                                 int S, int C, int K) {
+  constexpr int CP = 16 / sizeof(T);
+  const size_t total = (size_t)R * 8 * CP * K;
+  for (size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
+    const int k = (int)(idx % K);
+    size_t t = idx / K;
+    const int c = (int)(t % CP);
+    t /= CP;
+    const int sidx = (int)(t % 8);
+    const int r = (int)(t / 8);
+    wp[idx] = (sidx < S && c < C) ? w[(((size_t)r * S + sidx) * C + c) * K + k] : from_f32<T>(0.f);
+  }
+}
+
+bool small_c_applicable(int dtype, const PdnnConv2DParams& p) {
+  const int cp = 16 / (int)dtype_size(dtype);
+  return p.input_format == 0 && p.filter_format == 0 && p.groups == 1 && p.channels < cp && p.window_cols <= 8 &&
+         p.window_rows <= kMaxTaps && p.stride_rows <= 4 && p.stride_cols <= 4 && p.features % cp == 0;
+}
+
+struct SmallCPlan {
+  int Hp, Wp;
+  size_t xp_bytes, wp_bytes;
+};
+
+SmallCPlan plan_small_c(int dtype, const PdnnConv2DParams& p) {
+  SmallCPlan sp;
+  const size_t es = dtype_size(dtype);
+  sp.Hp = (p.out_rows - 1) * p.stride_rows + p.window_rows;
+  sp.Wp = (p.out_cols - 1) * p.stride_cols + 8;
+  sp.xp_bytes = (((size_t)p.batch * sp.Hp * sp.Wp * 16) + 255) / 256 * 256;
+  sp.wp_bytes = (((size_t)p.window_rows * 8 * (16 / es) * p.features * es) + 255) / 256 * 256;
+  return sp;
+}
+
+// Returns PDNN_OK, an error, or -1 if the tensor maps could not be encoded (the caller then uses
+// the direct kernel).
+int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const PdnnConv2DParams& p,
+                         const PdnnConvEpilogue* epi, void* ws, size_t ws_elems, cudaStream_t s) {
+  const size_t es = dtype_size(dtype);
+  const int sms = device_sm_count();
+  const int epr = dtype == PDNN_F32 ? 32 : 64;
+  const SmallCPlan sp = plan_small_c(dtype, p);
+  const size_t need = sp.xp_bytes + sp.wp_bytes;
+  char* scratch = static_cast<char*>(ws);
+  bool own = false;
+  if (scratch == nullptr || ws_elems * es < need || ((uintptr_t)scratch & 255u)) {
+    if (cudaMallocAsync(reinterpret_cast<void**>(&scratch), need, s) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(PDNN_ALLOCATION_PROBLEM, "conv2d: cannot allocate %zu bytes of scratch for the packed input", need);
+    }
+    own = true;
+  }
+  char* xp = scratch;
+  char* wpk = scratch + sp.xp_bytes;
+  auto release = [&] {
+    if (own) cudaFreeAsync(scratch, s);
+  };
+
+  GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.a_mn = 0;
+  choose_box(kTileM, p.out_cols, p.out_rows, p.batch, &g.tw, &g.th, &g.tn);
+  g.etw = g.tw;
+  g.eth = g.th;
+  g.etn = g.tn;
+  g.tiles_w = ceil_div(p.out_cols, g.tw);
+  g.tiles_h = ceil_div(p.out_rows, g.th);
+  g.tiles_n = ceil_div(p.batch, g.tn);
+  g.bn = pick_bn((long long)g.tiles_w * g.tiles_h * g.tiles_n, p.features, epr, dtype == PDNN_F32 ? 128 : 256, sms);
+  g.n_tiles = ceil_div(p.features, g.bn);
+  set_operand_layout(g, dtype, 1);
+  const size_t row_pitch = (size_t)sp.Wp * 16;
+  for (int q = 0; q < p.stride_rows; ++q) {
+    const int Hq = ceil_div(sp.Hp - q, p.stride_rows);
+    const uint64_t dims[4] = {(uint64_t)epr, (uint64_t)p.out_cols, (uint64_t)std::max(Hq, 1), (uint64_t)p.batch};
+    const uint64_t st[3] = {(uint64_t)p.stride_cols * 16, (uint64_t)p.stride_rows * row_pitch, (uint64_t)sp.Hp * row_pitch};
+    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)g.th, (uint32_t)g.tn};
+    if (!make_map(&g.a_map[q], dtype, false, xp + (size_t)q * row_pitch, dims, st, box)) {
+      release();
+      return -1;
+    }
+  }
+  for (int q = p.stride_rows; q < 4; ++q) g.a_map[q] = g.a_map[0];
+  for (int r = 0; r < p.window_rows; ++r)
+    g.taps[r] = TapEntry{0, (short)(r / p.stride_rows), (short)(r % p.stride_rows), (short)r};
+  g.num_taps = p.window_rows;
+  g.cblocks = 1;
+  {
+    g.b_mode = B_MN_3;
+    const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)epr, (uint64_t)p.window_rows, 1};
+    const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)epr * p.features * es,
+                            (uint64_t)p.window_rows * epr * p.features * es};
+    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
+    if (!make_map(&g.b_map, dtype, true, wpk, dims, st, box)) {
+      release();
+      return -1;
+    }
+  }
+  const size_t n_pix = (size_t)p.batch * sp.Hp * sp.Wp;
+  const size_t n_fil = (size_t)p.window_rows * epr * p.features;
+  if (dtype == PDNN_F32) {
+    pack_small_c_input_kernel<float><<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
+        static_cast<const float*>(x), reinterpret_cast<uint4*>(xp), p.batch, p.in_rows, p.in_cols, p.channels, sp.Hp,
+        sp.Wp, p.pad_rows, p.pad_cols);
+    pack_small_c_filter_kernel<float><<<grid_for(n_fil, 256, sms), 256, 0, s>>>(
+        static_cast<const float*>(w), reinterpret_cast<float*>(wpk), p.window_rows, p.window_cols, p.channels, p.features);
+  } else {
+    // fp16 and bf16 are both moved as 16-bit words
+    pack_small_c_input_kernel<__half><<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
+        static_cast<const __half*>(x), reinterpret_cast<uint4*>(xp), p.batch, p.in_rows, p.in_cols, p.channels, sp.Hp,
+        sp.Wp, p.pad_rows, p.pad_cols);
+    pack_small_c_filter_kernel<__half><<<grid_for(n_fil, 256, sms), 256, 0, s>>>(
+        static_cast<const __half*>(w), reinterpret_cast<__half*>(wpk), p.window_rows, p.window_cols, p.channels, p.features);
+  }
+  int st = check_launch("conv2d small-channel packing");
+  count_launch();
+  if (st == PDNN_OK) st = finish_forward(g, dtype, y, p, epi, s);
+  release();
+  return st;
 }
 
 int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnConv2DParams& p,
@@ -641,7 +937,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   g.n_tiles = ceil_div(p.features, g.bn);
   set_operand_layout(g, dtype, hwcf ? 1 : 0);
   const uint32_t abox[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)g.th, (uint32_t)g.tn};
-  if (!make_parity_maps(g, dtype, x, p, abox)) return PDNN_INVALID_PARAMETER;
+  if (!make_parity_maps(g, dtype, false, x, p, abox)) return PDNN_INVALID_PARAMETER;
   // taps
   int nt = 0;
   for (int r = 0; r < p.window_rows; ++r)
@@ -663,26 +959,15 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.channels * p.features * es,
                             taps * p.channels * p.features * es};
     const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
-    if (!make_map(&g.b_map, dtype, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+    if (!make_map(&g.b_map, dtype, true, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
   } else {
     g.b_mode = B_K_FHWC;
     const uint64_t dims[4] = {(uint64_t)p.channels, taps, (uint64_t)p.features, 1};
     const uint64_t st[3] = {(uint64_t)p.channels * es, taps * p.channels * es, taps * p.channels * p.features * es};
     const uint32_t box[4] = {(uint32_t)epr, 1, (uint32_t)g.bn, 1};
-    if (!make_map(&g.b_map, dtype, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+    if (!make_map(&g.b_map, dtype, false, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
   }
-  set_epilogue(g, epi);
-  g.out = y;
-  g.out_dtype = dtype;
-  g.ext_w = p.out_cols;
-  g.ext_h = p.out_rows;
-  g.ext_n = p.batch;
-  g.ext_cols = p.features;
-  g.stride_w = p.features;
-  g.stride_h = (long long)p.out_cols * p.features;
-  g.stride_n = (long long)p.out_rows * p.out_cols * p.features;
-  g.vec_ok = 1;
-  return launch_gemm(g, dtype, s);
+  return finish_forward(g, dtype, y, p, epi, s);
 }
 
 int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, const PdnnConv2DParams& p,
@@ -717,7 +1002,7 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
         const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.out_cols * p.features * es,
                                 (uint64_t)p.out_rows * p.out_cols * p.features * es};
         const uint32_t box[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)g.th, (uint32_t)g.tn};
-        if (!make_map(&g.a_map[0], dtype, dy, dims, st, box)) return PDNN_INVALID_PARAMETER;
+        if (!make_map(&g.a_map[0], dtype, false, dy, dims, st, box)) return PDNN_INVALID_PARAMETER;
         for (int i = 1; i < 4; ++i) g.a_map[i] = g.a_map[0];
       }
       int nt = 0;
@@ -744,13 +1029,13 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
         const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.channels * p.features * es,
                                 taps * p.channels * p.features * es};
         const uint32_t box[4] = {(uint32_t)epr, (uint32_t)g.bn, 1, 1};
-        if (!make_map(&g.b_map, dtype, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+        if (!make_map(&g.b_map, dtype, false, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
       } else {
         g.b_mode = B_MN_FHWC;
         const uint64_t dims[4] = {(uint64_t)p.channels, taps, (uint64_t)p.features, 1};
         const uint64_t st[3] = {(uint64_t)p.channels * es, taps * p.channels * es, taps * p.channels * p.features * es};
         const uint32_t box[4] = {(uint32_t)epr, 1, (uint32_t)epr, 1};
-        if (!make_map(&g.b_map, dtype, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+        if (!make_map(&g.b_map, dtype, true, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
       }
       set_epilogue(g, nullptr);
       g.out = static_cast<char*>(dx) + ((size_t)qh * p.in_cols + qw) * p.channels * es;
@@ -763,6 +1048,13 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
       g.stride_h = (long long)p.stride_rows * p.in_cols * p.channels;
       g.stride_n = (long long)p.in_rows * p.in_cols * p.channels;
       g.vec_ok = 1;
+      {
+        const uint64_t od[4] = {(uint64_t)p.channels, (uint64_t)Wq, (uint64_t)Hq, (uint64_t)p.batch};
+        const uint64_t os[3] = {(uint64_t)p.stride_cols * p.channels * es,
+                                (uint64_t)p.stride_rows * p.in_cols * p.channels * es,
+                                (uint64_t)p.in_rows * p.in_cols * p.channels * es};
+        if (!setup_store(g, dtype, od, os)) return PDNN_INVALID_PARAMETER;
+      }
       const int st_ = launch_gemm(g, dtype, s);
       if (st_ != PDNN_OK) return st_;
     }
@@ -831,13 +1123,13 @@ int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, con
   g.split_is_batch = 0;
   set_operand_layout(g, dtype, 1);
   const uint32_t box[4] = {(uint32_t)epr, (uint32_t)f.tw, (uint32_t)f.th, (uint32_t)f.tn};
-  if (!make_parity_maps(g, dtype, x, p, box)) return PDNN_INVALID_PARAMETER;
+  if (!make_parity_maps(g, dtype, true, x, p, box)) return PDNN_INVALID_PARAMETER;
   {
     g.b_mode = B_MN_4;
     const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)p.out_cols, (uint64_t)p.out_rows, (uint64_t)p.batch};
     const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.out_cols * p.features * es,
                             (uint64_t)p.out_rows * p.out_cols * p.features * es};
-    if (!make_map(&g.b_map, dtype, dy, dims, st, box)) return PDNN_INVALID_PARAMETER;
+    if (!make_map(&g.b_map, dtype, true, dy, dims, st, box)) return PDNN_INVALID_PARAMETER;
   }
   int nt = 0;
   for (int r = 0; r < p.window_rows; ++r)
@@ -880,6 +1172,15 @@ int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, con
   g.split_stride = (long long)n_out;
   g.tap_stride = (long long)p.channels * p.features;
   g.vec_ok = 1;
+  {
+    const uint64_t eo = dtype_size(g.out_dtype);
+    const uint64_t od[4] = {(uint64_t)p.features, (uint64_t)p.channels, (uint64_t)nt, (uint64_t)f.splits};
+    const uint64_t os[3] = {(uint64_t)p.features * eo, (uint64_t)p.channels * p.features * eo, (uint64_t)n_out * eo};
+    if (!setup_store(g, dtype, od, os)) {
+      if (own) cudaFreeAsync(partial, s);
+      return PDNN_INVALID_PARAMETER;
+    }
+  }
   int st = launch_gemm(g, dtype, s);
   if (st == PDNN_OK && f.splits > 1) {
     const unsigned grid = grid_for(n_out, 256, sms);
@@ -923,9 +1224,10 @@ __global__ void __launch_bounds__(256) simt_matmul_kernel(const T* __restrict__ 
 
 bool tc_conv_supported(int pass, int dtype, const void* in, const void* fil, const void* out,
                        const PdnnConv2DParams& p) {
+  if (encode_fn() == nullptr) return false;
+  if (pass == PDNN_FORWARD && small_c_applicable(dtype, p)) return aligned16(out);
   if (!conv_common_ok(dtype, p)) return false;
   if (!aligned16(in) || !aligned16(fil) || !aligned16(out)) return false;
-  if (encode_fn() == nullptr) return false;
   for (int ph = 0; ph < p.stride_rows; ++ph)
     for (int pw = 0; pw < p.stride_cols; ++pw)
       if (p.in_rows - ph <= 0 || p.in_cols - pw <= 0) return false;
@@ -934,6 +1236,10 @@ bool tc_conv_supported(int pass, int dtype, const void* in, const void* fil, con
 }
 
 size_t tc_conv_workspace_elems(int pass, int dtype, const PdnnConv2DParams& p) {
+  if (pass == PDNN_FORWARD && small_c_applicable(dtype, p)) {
+    const SmallCPlan sp = plan_small_c(dtype, p);
+    return (sp.xp_bytes + sp.wp_bytes) / dtype_size(dtype);
+  }
   if (pass != PDNN_FILTER_BACKPROP || !conv_common_ok(dtype, p) || p.filter_format != 0) return 0;
   int sms = device_sm_count();
   if (sms <= 0) sms = 148;
@@ -946,7 +1252,12 @@ size_t tc_conv_workspace_elems(int pass, int dtype, const PdnnConv2DParams& p) {
 int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
               const PdnnConvEpilogue* epi, void* ws, size_t ws_elems, cudaStream_t s) {
   switch (pass) {
-    case PDNN_FORWARD: return conv_forward(dtype, in, fil, out, p, epi, s);
+    case PDNN_FORWARD:
+      if (small_c_applicable(dtype, p)) {
+        const int st = conv_forward_small_c(dtype, in, fil, out, p, epi, ws, ws_elems, s);
+        return st == -1 ? launch_direct_conv(pass, dtype, in, fil, out, p, epi, s) : st;
+      }
+      return conv_forward(dtype, in, fil, out, p, epi, s);
     case PDNN_INPUT_BACKPROP: return conv_input_backprop(dtype, in, fil, out, p, s);
     case PDNN_FILTER_BACKPROP: return conv_filter_backprop(dtype, in, fil, out, p, ws, ws_elems, s);
   }
@@ -994,19 +1305,19 @@ int tc_matmul(int dtype, int tl, int tr, const void* lhs, const void* rhs, void*
     const uint64_t dims[4] = {(uint64_t)k, (uint64_t)m, 1, (uint64_t)batches};
     const uint64_t st[3] = {(uint64_t)k * es, (uint64_t)m * k * es, (uint64_t)m * k * es};
     const uint32_t box[4] = {(uint32_t)epr, (uint32_t)kTileM, 1, 1};
-    if (!make_map(&g.a_map[0], dtype, lhs, dims, st, box)) return PDNN_INVALID_PARAMETER;
+    if (!make_map(&g.a_map[0], dtype, false, lhs, dims, st, box)) return PDNN_INVALID_PARAMETER;
     if (b_mn) {
       g.b_mode = B_MN_3;
       const uint64_t bd[4] = {(uint64_t)n, (uint64_t)k, (uint64_t)batches, 1};
       const uint64_t bs[3] = {(uint64_t)n * es, (uint64_t)k * n * es, (uint64_t)batches * k * n * es};
       const uint32_t bb[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
-      if (!make_map(&g.b_map, dtype, rhs, bd, bs, bb)) return PDNN_INVALID_PARAMETER;
+      if (!make_map(&g.b_map, dtype, true, rhs, bd, bs, bb)) return PDNN_INVALID_PARAMETER;
     } else {
       g.b_mode = B_K_3;
       const uint64_t bd[4] = {(uint64_t)k, (uint64_t)n, (uint64_t)batches, 1};
       const uint64_t bs[3] = {(uint64_t)k * es, (uint64_t)k * n * es, (uint64_t)batches * k * n * es};
       const uint32_t bb[4] = {(uint32_t)epr, (uint32_t)g.bn, 1, 1};
-      if (!make_map(&g.b_map, dtype, rhs, bd, bs, bb)) return PDNN_INVALID_PARAMETER;
+      if (!make_map(&g.b_map, dtype, false, rhs, bd, bs, bb)) return PDNN_INVALID_PARAMETER;
     }
     g.ext_w = m;
     g.ext_h = 1;
@@ -1027,19 +1338,19 @@ int tc_matmul(int dtype, int tl, int tr, const void* lhs, const void* rhs, void*
     const uint64_t dims[4] = {(uint64_t)m, (uint64_t)k, 1, (uint64_t)batches};
     const uint64_t st[3] = {(uint64_t)m * es, (uint64_t)m * k * es, (uint64_t)m * k * es};
     const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
-    if (!make_map(&g.a_map[0], dtype, lhs, dims, st, box)) return PDNN_INVALID_PARAMETER;
+    if (!make_map(&g.a_map[0], dtype, true, lhs, dims, st, box)) return PDNN_INVALID_PARAMETER;
     if (b_mn) {
       g.b_mode = B_MN_4;
       const uint64_t bd[4] = {(uint64_t)n, (uint64_t)k, 1, (uint64_t)batches};
       const uint64_t bs[3] = {(uint64_t)n * es, (uint64_t)k * n * es, (uint64_t)k * n * es};
       const uint32_t bb[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
-      if (!make_map(&g.b_map, dtype, rhs, bd, bs, bb)) return PDNN_INVALID_PARAMETER;
+      if (!make_map(&g.b_map, dtype, true, rhs, bd, bs, bb)) return PDNN_INVALID_PARAMETER;
     } else {
       g.b_mode = B_K_4;
       const uint64_t bd[4] = {(uint64_t)k, (uint64_t)n, 1, (uint64_t)batches};
       const uint64_t bs[3] = {(uint64_t)k * es, (uint64_t)k * n * es, (uint64_t)k * n * es};
       const uint32_t bb[4] = {(uint32_t)epr, (uint32_t)g.bn, 1, 1};
-      if (!make_map(&g.b_map, dtype, rhs, bd, bs, bb)) return PDNN_INVALID_PARAMETER;
+      if (!make_map(&g.b_map, dtype, false, rhs, bd, bs, bb)) return PDNN_INVALID_PARAMETER;
     }
     g.ext_w = m;
     g.ext_h = g.ext_n = 1;
@@ -1054,6 +1365,11 @@ int tc_matmul(int dtype, int tl, int tr, const void* lhs, const void* rhs, void*
   g.out_dtype = dtype;
   g.ext_cols = n;
   g.vec_ok = 1;
+  {
+    const uint64_t od[4] = {(uint64_t)n, (uint64_t)m, 1, (uint64_t)batches};
+    const uint64_t os[3] = {(uint64_t)n * es, (uint64_t)m * n * es, (uint64_t)m * n * es};
+    if (!setup_store(g, dtype, od, os)) return PDNN_INVALID_PARAMETER;
+  }
   return launch_gemm(g, dtype, s);
 }
 

@@ -87,6 +87,27 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap
       ::"r"(smem_dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+// Tile store shared -> global through a tensor map; rows/columns outside the tensor are clipped.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t smem_src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+               "r"(smem_src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk groups still have to READ their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until at most N of this thread's bulk groups are still in flight at all.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// Barrier among `count` threads (a multiple of 32) that all name the same id (1..15).
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -170,17 +191,19 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 
 // ---- descriptors ---------------------------------------------------------------------------------
 // Shared-memory matrix descriptor, 128-byte swizzle.  Addresses and offsets are in bytes here and
-// stored in units of 16 bytes; bits [46,48) = 1 marks the sm_100 format, bits [61,64) = 2 selects
-// SWIZZLE_128B.  For a K-major operand `sbo` is the distance between groups of 8 rows (1024 for
-// dense 128-byte rows) and `lbo` is unused; for an MN-major operand `lbo` is the distance between
-// 64-element (128-byte) column blocks and `sbo` the distance between groups of 8 k-rows.
-__host__ __device__ inline uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+// stored in units of 16 bytes; bits [46,48) = 1 marks the sm_100 format, bits [61,64) hold the
+// swizzle code: 2 = 128-byte rows swizzled in 16-byte units, 1 = 128-byte rows swizzled in
+// 32-byte units (the MN-major layout of 32-bit operands).  For a K-major operand `sbo` is the
+// distance between groups of 8 rows (1024 for dense 128-byte rows) and `lbo` is unused; for an
+// MN-major operand `lbo` is the distance between 128-byte column blocks and `sbo` the distance
+// between groups of 8 k-rows (4 k-rows for code 1).
+__host__ __device__ inline uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout = 2) {
   uint64_t d = 0;
   d |= (uint64_t)((addr >> 4) & 0x3FFFu);
   d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
   d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)(layout & 7u) << 61;
   return d;
 }
 
