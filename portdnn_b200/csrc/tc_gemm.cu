@@ -43,7 +43,7 @@ struct TapEntry {
   short dw, dh, a_map, b_tap;
 };
 
-enum BMode { B_MN_3 = 0, B_K_3 = 1, B_K_FHWC = 2, B_MN_FHWC = 3, B_MN_4 = 4, B_K_4 = 5 };
+enum BMode { B_MN_3 = 0, B_K_3 = 1, B_K_FHWC = 2, B_MN_FHWC = 3, B_MN_4 = 4, B_K_4 = 5, B_MN_3X = 6 };
 
 struct alignas(64) GemmArgs {
   CUtensorMap a_map[4];
@@ -77,6 +77,7 @@ struct alignas(64) GemmArgs {
   int vec_ok;  // rows are 16-byte aligned: packed stores allowed
   int tma_store;  // 1: the epilogue stages 128-byte column blocks in shared memory and stores them by TMA
   int cpb;        // output columns per 128-byte block: 64 (16-bit) or 32 (fp32)
+  int epi_fast;   // 1: 16-bit output, alpha 1, bias/ReLU done on packed pairs (see epilogue_tile_tma_fast)
 };
 
 struct TileCoord {
@@ -266,7 +267,103 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs& a, const TileC
   return true;
 }
 
-template <bool SPLIT>
+// Packed-pair arithmetic for the 16-bit fast epilogue.
+template <typename OutT>
+struct Pair;
+template <>
+struct Pair<__half> {
+  using type = __half2;
+  static __device__ __forceinline__ type pack(float a, float b) { return __floats2half2_rn(a, b); }
+  static __device__ __forceinline__ type splat(float v) { return __float2half2_rn(v); }
+};
+template <>
+struct Pair<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  static __device__ __forceinline__ type pack(float a, float b) { return __floats2bfloat162_rn(a, b); }
+  static __device__ __forceinline__ type splat(float v) { return __float2bfloat162_rn(v); }
+};
+
+// The common case of the TMA-store epilogue, kept short because the four epilogue warps are
+// issue-bound: 16-bit output, alpha == 1, optional bias, activation none / ReLU / ReLU6.  The
+// accumulators are rounded to the output type first and bias and activation are applied to
+// packed pairs in that type - the arithmetic of separate convolution, bias-add and activation
+// passes.  Same staging and hand-off protocol as epilogue_tile_tma.
+template <typename P2>
+__device__ __forceinline__ uint32_t pair_bits(P2 v) {
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <typename P2>
+__device__ __forceinline__ P2 bits_pair(uint32_t v) {
+  return *reinterpret_cast<P2*>(&v);
+}
+
+// Converts 32 accumulator columns of one row (four 16-byte chunks, numbered from chunk_base) and
+// writes them into the row's 128 bytes of the staging tile.
+template <typename OutT>
+__device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bool zero, const OutT* bias, int col0,
+                                                   int ext_cols, int act, uint8_t* row_ptr, int row, int chunk_base) {
+  using P2 = typename Pair<OutT>::type;
+  const P2 zero2 = Pair<OutT>::splat(0.f), six2 = Pair<OutT>::splat(6.f);
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint4 bv = make_uint4(0u, 0u, 0u, 0u);
+    if (bias != nullptr && col0 + g * 8 + 8 <= ext_cols) bv = __ldg(reinterpret_cast<const uint4*>(bias + col0 + g * 8));
+    const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      P2 v = zero ? zero2
+                  : Pair<OutT>::pack(__uint_as_float(acc[g * 8 + 2 * i]), __uint_as_float(acc[g * 8 + 2 * i + 1]));
+      if (bias != nullptr) v = __hadd2(v, bits_pair<P2>(bw[i]));
+      if (act != PDNN_ACT_NONE) v = __hmax2(v, zero2);
+      if (act == PDNN_ACT_RELU6) v = __hmin2(v, six2);
+      o[i] = pair_bits(v);
+    }
+    *reinterpret_cast<uint4*>(row_ptr + (((chunk_base + g) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <typename OutT>
+__device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc,
+                                                       int row, bool zero, uint8_t* staging, uint32_t staging_addr,
+                                                       const EpilogueSync& sync, uint32_t& store_count) {
+  const OutT* bias = static_cast<const OutT*>(a.bias);
+  const bool issuer = threadIdx.x == 64;
+  const int c2 = a.a_mn ? t.tap : t.h0, c3 = a.a_mn ? t.split : t.n0;
+  const int act = a.act, ext_cols = a.ext_cols;
+  for (int c0 = 0; c0 < a.bn; c0 += 64, ++store_count) {
+    const uint32_t sbuf = store_count & 1u, par = (store_count >> 1) & 1u;
+    uint32_t acc0[32];
+    if (!zero) tmem_ld_32x32(tmem_acc + (uint32_t)c0, acc0);  // issued before waiting for the staging tile
+    if (issuer) {
+      bulk_wait_group_read<1>();
+      mbar_arrive(sync.free_bar[sbuf]);
+    }
+    if (!mbar_wait(sync.free_bar[sbuf], par, sync.abort_flag, g_error_record, 0x600u + sbuf)) return false;
+    if (!zero) tmem_wait_ld();
+    uint8_t* row_ptr = staging + sbuf * kABytes + (size_t)row * 128;
+    {
+      uint32_t acc1[32];
+      if (!zero) tmem_ld_32x32(tmem_acc + (uint32_t)(c0 + 32), acc1);  // overlaps the conversion of the first half
+      fast_convert_store<OutT>(acc0, zero, bias, t.nf0 + c0, ext_cols, act, row_ptr, row, 0);
+      if (!zero) tmem_wait_ld();
+      fast_convert_store<OutT>(acc1, zero, bias, t.nf0 + c0 + 32, ext_cols, act, row_ptr, row, 4);
+    }
+    fence_proxy_async_smem();
+    mbar_arrive(sync.written_bar[sbuf]);
+    if (issuer) {
+      if (!mbar_wait(sync.written_bar[sbuf], par, sync.abort_flag, g_error_record, 0x610u + sbuf)) return false;
+      tma_store_4d(&a.out_map, staging_addr + sbuf * kABytes, t.nf0 + c0, t.w0, c2, c3);
+      bulk_commit_group();
+    }
+  }
+  return true;
+}
+
+// EPI selects the epilogue compiled into the instantiation: 0 = direct stores from registers,
+// 1 = staged TMA store with fp32 arithmetic, 2 = staged TMA store with packed 16-bit arithmetic.
+// One epilogue per instantiation keeps each kernel's register allocation tight.
+template <bool SPLIT, int EPI, typename OutT>
 __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const __grid_constant__ GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const GemmArgs& a = args;
@@ -325,56 +422,91 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
 
   if (warp == 0) {
     // ------------------------------- TMA producer ------------------------------------------
+    // One thread; the loop body is kept to a wait, an expect_tx and the copies, with all
+    // coordinates advanced incrementally: a lone thread issues an instruction every few cycles
+    // at best, so every division or table lookup per step would show up as pipeline bubbles.
     if (lane == 0) {
       for (int i = 0; i < 4; ++i) prefetch_tensormap(&a.a_map[i]);
       prefetch_tensormap(&a.b_map);
-      uint32_t it = 0;
+      const int epr = a.epr, b_mode = a.b_mode, b_boxes = a.b_boxes, a_boxes = a.a_boxes, cblocks = a.cblocks;
+      const uint32_t a_box_bytes = a.a_box_bytes, b_box_bytes = a.b_box_bytes, tx_bytes = kABytes + b_bytes;
+      const CUtensorMap* bmap = &a.b_map;
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
+      auto next_stage = [&] {
+        if (++s == S) {
+          s = 0;
+          ph ^= 1u;
+        }
+      };
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const TileCoord t = decode_tile(a, tile);
-        const TapEntry e_fixed = a.taps[t.tap];
-        for (int ks = t.ks_begin; ks < t.ks_end; ++ks, ++it) {
-          const int s = (int)(it % (uint32_t)S);
-          const uint32_t ph = (it / (uint32_t)S) & 1u;
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g_error_record, 0x100u + (unsigned)s)) {
-            ok = false;
-            break;
-          }
-          const uint32_t fb = full_bar(s);
-          mbar_arrive_expect_tx(fb, kABytes + b_bytes);
-          const uint32_t sa = base + (uint32_t)s * stage_bytes;
-          const uint32_t sb = sa + kABytes;
-          if (!a.a_mn) {
-            const int tap = ks / a.cblocks, cb = ks % a.cblocks;
+        if (!a.a_mn) {
+          for (int tap = 0; tap < a.num_taps && ok; ++tap) {
             const TapEntry e = a.taps[tap];
-            const int kc = cb * a.epr;
-            tma_load_4d(sa, &a.a_map[e.a_map], fb, kc, t.w0 + e.dw, t.h0 + e.dh, t.n0);
+            const CUtensorMap* amap = &a.a_map[e.a_map];
+            const int aw = t.w0 + e.dw, ah = t.h0 + e.dh;
             const int btap = e.b_tap + t.n0 * a.b_batch_mul;
-            switch (a.b_mode) {
-              case B_MN_3:
-                for (int j = 0; j < a.b_boxes; ++j)
-                  tma_load_4d(sb + (uint32_t)j * a.b_box_bytes, &a.b_map, fb, t.nf0 + j * a.epr, kc, btap, 0);
+            for (int cb = 0, kc = 0; cb < cblocks; ++cb, kc += epr) {
+              if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g_error_record, 0x100u + (unsigned)s)) {
+                ok = false;
                 break;
-              case B_K_3: tma_load_4d(sb, &a.b_map, fb, kc, t.nf0, btap, 0); break;
-              case B_K_FHWC: tma_load_4d(sb, &a.b_map, fb, kc, btap, t.nf0, 0); break;
-              default:  // B_MN_FHWC
-                for (int j = 0; j < a.b_boxes; ++j)
-                  tma_load_4d(sb + (uint32_t)j * a.b_box_bytes, &a.b_map, fb, t.nf0 + j * a.epr, btap, kc, 0);
-                break;
+              }
+              const uint32_t fb = full_bar(s);
+              mbar_arrive_expect_tx(fb, tx_bytes);
+              const uint32_t sa = base + (uint32_t)s * stage_bytes;
+              const uint32_t sb = sa + kABytes;
+              tma_load_4d(sa, amap, fb, kc, aw, ah, t.n0);
+              switch (b_mode) {
+                case B_MN_3X: tma_load_4d(sb, bmap, fb, 0, kc, t.nf0 / epr, btap); break;
+                case B_MN_3:
+                  for (int j = 0; j < b_boxes; ++j)
+                    tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, t.nf0 + j * epr, kc, btap, 0);
+                  break;
+                case B_K_3: tma_load_4d(sb, bmap, fb, kc, t.nf0, btap, 0); break;
+                case B_K_FHWC: tma_load_4d(sb, bmap, fb, kc, btap, t.nf0, 0); break;
+                default:  // B_MN_FHWC
+                  for (int j = 0; j < b_boxes; ++j)
+                    tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, t.nf0 + j * epr, btap, kc, 0);
+                  break;
+              }
+              next_stage();
             }
-          } else {
-            const int kw = (ks % a.slabs_w) * a.tw;
-            const int kh = ((ks / a.slabs_w) % a.slabs_h) * a.th;
-            const int kn = (ks / (a.slabs_w * a.slabs_h)) * a.tn + (a.split_is_batch ? t.split : 0);
-            for (int j = 0; j < a.a_boxes; ++j)
-              tma_load_4d(sa + (uint32_t)j * a.a_box_bytes, &a.a_map[e_fixed.a_map], fb, t.w0 + j * a.epr,
-                          kw + e_fixed.dw, kh + e_fixed.dh, kn);
-            if (a.b_mode == B_MN_4) {
-              for (int j = 0; j < a.b_boxes; ++j)
-                tma_load_4d(sb + (uint32_t)j * a.b_box_bytes, &a.b_map, fb, t.nf0 + j * a.epr, kw, kh, kn);
+          }
+        } else {
+          const TapEntry e = a.taps[t.tap];
+          const CUtensorMap* amap = &a.a_map[e.a_map];
+          const int batch = a.split_is_batch ? t.split : 0;
+          // slab coordinates of ks_begin, then advanced like an odometer
+          int iw = t.ks_begin % a.slabs_w, ih = (t.ks_begin / a.slabs_w) % a.slabs_h,
+              in = t.ks_begin / (a.slabs_w * a.slabs_h);
+          for (int ks = t.ks_begin; ks < t.ks_end; ++ks) {
+            if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g_error_record, 0x100u + (unsigned)s)) {
+              ok = false;
+              break;
+            }
+            const uint32_t fb = full_bar(s);
+            mbar_arrive_expect_tx(fb, tx_bytes);
+            const uint32_t sa = base + (uint32_t)s * stage_bytes;
+            const uint32_t sb = sa + kABytes;
+            const int kw = iw * a.tw, kh = ih * a.th, kn = in * a.tn + batch;
+            for (int j = 0; j < a_boxes; ++j)
+              tma_load_4d(sa + (uint32_t)j * a_box_bytes, amap, fb, t.w0 + j * epr, kw + e.dw, kh + e.dh, kn);
+            if (b_mode == B_MN_4) {
+              for (int j = 0; j < b_boxes; ++j)
+                tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, t.nf0 + j * epr, kw, kh, kn);
             } else {  // B_K_4
-              tma_load_4d(sb, &a.b_map, fb, kw, t.nf0, 0, kn);
+              tma_load_4d(sb, bmap, fb, kw, t.nf0, 0, kn);
             }
+            if (++iw == a.slabs_w) {
+              iw = 0;
+              if (++ih == a.slabs_h) {
+                ih = 0;
+                ++in;
+              }
+            }
+            next_stage();
           }
         }
       }
@@ -382,7 +514,13 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ---------------------------------------------
     if (lane == 0) {
-      uint32_t it = 0, tcount = 0;
+      // Descriptor words that do not change: everything but the 14-bit start address.
+      const uint64_t a_desc0 = make_smem_desc(0, a.a_lbo, a.a_sbo, a.a_layout);
+      const uint64_t b_desc0 = make_smem_desc(0, a.b_lbo, a.b_sbo, a.b_layout);
+      const uint32_t a_kadv = a.a_kadv >> 4, b_kadv = a.b_kadv >> 4, idesc = a.idesc;
+      const uint32_t lo_off = part_bytes >> 4;
+      int s = 0;
+      uint32_t ph = 0, tcount = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
         const TileCoord t = decode_tile(a, tile);
@@ -390,34 +528,36 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
         if (!mbar_wait(acc_empty_bar((int)buf), aph ^ 1u, abort_flag, g_error_record, 0x200u + buf)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * acc_stride;
-        for (int ks = t.ks_begin; ks < t.ks_end; ++ks, ++it) {
-          const int s = (int)(it % (uint32_t)S);
-          const uint32_t ph = (it / (uint32_t)S) & 1u;
+        uint32_t accumulate = 0u;
+        for (int ks = t.ks_begin; ks < t.ks_end; ++ks) {
           if (!mbar_wait(SPLIT ? ready_bar(s) : full_bar(s), ph, abort_flag, g_error_record, 0x300u + (unsigned)s)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
           const uint32_t sa = base + (uint32_t)s * stage_bytes;
-          const uint32_t sb = sa + kABytes;
-          const uint64_t a_hi = make_smem_desc(sa, a.a_lbo, a.a_sbo, a.a_layout);
-          const uint64_t b_hi = make_smem_desc(sb, a.b_lbo, a.b_sbo, a.b_layout);
-          const bool first_step = (ks == t.ks_begin);
+          // start addresses stay below 2^18, so adding to the low word never carries into the
+          // neighbouring descriptor field
+          uint64_t da = a_desc0 + (uint64_t)(sa >> 4);
+          uint64_t db = b_desc0 + (uint64_t)((sa + kABytes) >> 4);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint64_t ka = (uint64_t)((a.a_kadv * (uint32_t)k) >> 4), kb = (uint64_t)((a.b_kadv * (uint32_t)k) >> 4);
-            const uint32_t acc = (first_step && k == 0) ? 0u : 1u;
             if (SPLIT) {
-              const uint64_t a_lo = make_smem_desc(sa + part_bytes, a.a_lbo, a.a_sbo, a.a_layout);
-              const uint64_t b_lo = make_smem_desc(sb + part_bytes, a.b_lbo, a.b_sbo, a.b_layout);
-              mma_tf32(d_tmem, a_lo + ka, b_hi + kb, a.idesc, acc);
-              mma_tf32(d_tmem, a_hi + ka, b_lo + kb, a.idesc, 1u);
-              mma_tf32(d_tmem, a_hi + ka, b_hi + kb, a.idesc, 1u);
+              mma_tf32(d_tmem, da + lo_off, db, idesc, accumulate);
+              mma_tf32(d_tmem, da, db + lo_off, idesc, 1u);
+              mma_tf32(d_tmem, da, db, idesc, 1u);
             } else {
-              mma_f16(d_tmem, a_hi + ka, b_hi + kb, a.idesc, acc);
+              mma_f16(d_tmem, da, db, idesc, accumulate);
             }
+            accumulate = 1u;
+            da += a_kadv;
+            db += b_kadv;
           }
           mma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+          if (++s == S) {
+            s = 0;
+            ph ^= 1u;
+          }
         }
         if (!ok) break;
         if (t.ks_end > t.ks_begin) mma_commit(acc_full_bar((int)buf));
@@ -437,37 +577,34 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
       tc_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
       const bool zero = !(t.ks_end > t.ks_begin);
-      if (a.tma_store) {
-        uint8_t* staging = smem + (size_t)S * stage_bytes;
-        bool ok;
-        if (a.out_dtype == PDNN_F16) ok = epilogue_tile_tma<__half>(a, t, tmem_acc, row, zero, staging, staging_base, esync, store_count);
-        else if (a.out_dtype == PDNN_BF16) ok = epilogue_tile_tma<__nv_bfloat16>(a, t, tmem_acc, row, zero, staging, staging_base, esync, store_count);
-        else ok = epilogue_tile_tma<float>(a, t, tmem_acc, row, zero, staging, staging_base, esync, store_count);
-        if (!ok) break;
+      uint8_t* staging = smem + (size_t)S * stage_bytes;
+      bool ok = true;
+      if constexpr (EPI == 2) {
+        ok = epilogue_tile_tma_fast<OutT>(a, t, tmem_acc, row, zero, staging, staging_base, esync, store_count);
+      } else if constexpr (EPI == 1) {
+        ok = epilogue_tile_tma<OutT>(a, t, tmem_acc, row, zero, staging, staging_base, esync, store_count);
       } else {
-        if (a.out_dtype == PDNN_F16) epilogue_tile<__half>(a, t, tmem_acc, row, zero);
-        else if (a.out_dtype == PDNN_BF16) epilogue_tile<__nv_bfloat16>(a, t, tmem_acc, row, zero);
-        else epilogue_tile<float>(a, t, tmem_acc, row, zero);
+        epilogue_tile<OutT>(a, t, tmem_acc, row, zero);
       }
+      if (!ok) break;
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar((int)buf));
     }
     // the staging tiles must not be released while a store is still reading them
-    if (a.tma_store && threadIdx.x == 64) bulk_wait_group<0>();
+    if (EPI != 0 && threadIdx.x == 64) bulk_wait_group<0>();
   } else if (SPLIT) {
     // ------------------------------- hi/lo split (fp32 as 3xTF32) ----------------------------
     // hi keeps the 19 leading bits (what the tensor core reads of an fp32 word); lo = x - hi is
     // exact in fp32.  Element positions do not change, so the swizzle is irrelevant here.
     const int tid = threadIdx.x - 6 * 32;  // 0..127
     const int chunks = (int)(part_bytes >> 4);
-    uint32_t it = 0;
+    int s = 0;
+    uint32_t ph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const TileCoord t = decode_tile(a, tile);
-      for (int ks = t.ks_begin; ks < t.ks_end; ++ks, ++it) {
-        const int s = (int)(it % (uint32_t)S);
-        const uint32_t ph = (it / (uint32_t)S) & 1u;
+      for (int ks = t.ks_begin; ks < t.ks_end; ++ks) {
         if (!mbar_wait(full_bar(s), ph, abort_flag, g_error_record, 0x500u + (unsigned)s)) {
           ok = false;
           break;
@@ -490,6 +627,10 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(ready_bar(s));
+        if (++s == S) {
+          s = 0;
+          ph ^= 1u;
+        }
       }
     }
   }
@@ -664,11 +805,37 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
     const uint32_t box[4] = {(uint32_t)g.cpb, (uint32_t)g.etw, (uint32_t)g.eth, (uint32_t)g.etn};
     if (!make_map(&g.out_map, g.out_dtype, false, g.out, out_dims, out_strides, box)) return false;
     g.tma_store = 1;
+    g.epi_fast = (g.out_dtype != PDNN_F32 && g.alpha == 1.f && g.ext_cols % 8 == 0 &&
+                  (g.act == PDNN_ACT_NONE || g.act == PDNN_ACT_RELU || g.act == PDNN_ACT_RELU6) &&
+                  (g.bias == nullptr || aligned16(g.bias)))
+                     ? 1
+                     : 0;
   }
   const unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (compute_dtype == PDNN_F32 ? 2u : 1u);
   const int budget = kSmemBudget - 2048 - (g.tma_store ? 2 * kABytes : 0);
   g.stages = std::max(2, std::min(kMaxStages, (int)(budget / stage)));
   return true;
+}
+
+using GemmKernel = void (*)(const GemmArgs);
+
+// Kernel instantiation for (split, epilogue kind, output dtype); nullptr for combinations that
+// are never launched (the split kernel only produces fp32; packed arithmetic is 16-bit only).
+GemmKernel select_kernel(bool split, int epi, int out_dtype) {
+  if (split) {
+    if (out_dtype != PDNN_F32) return nullptr;
+    return epi == 1 ? umma_gemm_kernel<true, 1, float> : epi == 0 ? umma_gemm_kernel<true, 0, float> : nullptr;
+  }
+  switch (out_dtype) {
+    case PDNN_F16:
+      return epi == 2 ? umma_gemm_kernel<false, 2, __half>
+                      : epi == 1 ? umma_gemm_kernel<false, 1, __half> : umma_gemm_kernel<false, 0, __half>;
+    case PDNN_BF16:
+      return epi == 2 ? umma_gemm_kernel<false, 2, __nv_bfloat16>
+                      : epi == 1 ? umma_gemm_kernel<false, 1, __nv_bfloat16> : umma_gemm_kernel<false, 0, __nv_bfloat16>;
+    default:
+      return epi == 1 ? umma_gemm_kernel<false, 1, float> : epi == 0 ? umma_gemm_kernel<false, 0, float> : nullptr;
+  }
 }
 
 int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
@@ -684,15 +851,21 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(umma_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(umma_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    for (int sp = 0; sp < 2; ++sp)
+      for (int epi = 0; epi < 3; ++epi)
+        for (int dt = 0; dt < 3; ++dt) {
+          GemmKernel k = select_kernel(sp != 0, epi, dt);
+          if (k != nullptr && attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+        }
   });
   if (attr_err != cudaSuccess) return fail(PDNN_ALLOCATION_PROBLEM, "cannot opt in to %d bytes of shared memory", kSmemBudget);
+  const int epi = g.epi_fast ? 2 : (g.tma_store ? 1 : 0);
+  GemmKernel kernel = select_kernel(split, epi, g.out_dtype);
+  if (kernel == nullptr) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: no kernel for this output type");
   const int sms = device_sm_count();
   const unsigned grid = (unsigned)std::min<long long>(total, sms);
-  if (split) umma_gemm_kernel<true><<<grid, 320, smem, s>>>(g);
-  else umma_gemm_kernel<false><<<grid, 192, smem, s>>>(g);
+  kernel<<<grid, split ? 320 : 192, smem, s>>>(g);
   return check_launch("tensor-core gemm");
 }
 
@@ -953,7 +1126,16 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   g.num_taps = nt;
   g.cblocks = ceil_div(p.channels, epr);
   const uint64_t taps = (uint64_t)p.window_rows * p.window_cols;
-  if (hwcf) {
+  if (hwcf && p.features % epr == 0) {
+    // All 128-byte column blocks of the tile in one copy: the block index is a tensor dimension
+    // of its own (stride 128 bytes), placed after the reduction rows so that the blocks land
+    // one after another in shared memory.
+    g.b_mode = B_MN_3X;
+    const uint64_t dims[4] = {(uint64_t)epr, (uint64_t)p.channels, (uint64_t)(p.features / epr), taps};
+    const uint64_t st[3] = {(uint64_t)p.features * es, 128, (uint64_t)p.channels * p.features * es};
+    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, (uint32_t)(g.bn / epr), 1};
+    if (!make_map(&g.b_map, dtype, true, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+  } else if (hwcf) {
     g.b_mode = B_MN_3;
     const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)p.channels, taps, 1};
     const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.channels * p.features * es,
