@@ -22,6 +22,7 @@
 #include "umma.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -77,6 +78,8 @@ struct alignas(64) GemmArgs {
   int vec_ok;  // rows are 16-byte aligned: packed stores allowed
   int tma_store;  // 1: the epilogue stages 128-byte column blocks in shared memory and stores them by TMA
   int cpb;        // output columns per 128-byte block: 64 (16-bit) or 32 (fp32)
+  int nsw;        // staging slices per epilogue warp (2 or 4)
+  int occ2;       // host-side: sized so that two CTAs share an SM
   int epi_fast;   // 1: 16-bit output, alpha 1, bias/ReLU done on packed pairs (see epilogue_tile_tma_fast)
 };
 
@@ -194,37 +197,51 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& a, const TileCoord
   }
 }
 
-// Epilogue through shared memory: each of the 128 epilogue threads owns one accumulator row.
-// Per 128-byte column block (64 16-bit or 32 fp32 outputs) the row is converted and written to
-// a staging tile in the 128-byte swizzled layout (16-byte chunk j of row r lands at chunk
-// j ^ (r % 8), which spreads a warp's stores over all banks), then one thread issues a TMA store
-// of the whole 128-row block; the tensor map clips rows and columns that fall outside the
-// tensor.  Two staging tiles alternate so that the store of one block overlaps the conversion
-// of the next.  Thread 64 (lane 0 of the first epilogue warp) issues and tracks the stores; the
-// hand-offs use mbarriers (free: the issuer says the tile may be overwritten; written: all 128
-// rows are in place) so that every wait is bounded.  Returns false if a wait gave up.
-struct EpilogueSync {
-  uint32_t free_bar[2], written_bar[2];
-  volatile int* abort_flag;
+// Epilogue through shared memory.  Each of the 128 epilogue threads owns one accumulator row and
+// each epilogue warp works on its own: per 128-byte column block (64 16-bit or 32 fp32 outputs)
+// the warp converts its 32 rows, writes them to a 4 KB staging slice in the 128-byte swizzled
+// layout (16-byte chunk j of row r lands at chunk j ^ (r % 8), which spreads the warp's stores
+// over all banks) and its lane 0 issues a TMA store of that 32-row block.  32 consecutive rows of
+// a row tile are themselves a box of pixels because every tile extent is a power of two.  The
+// tensor map clips rows and columns outside the tensor.  A warp cycles through `nsw` slices and
+// only waits for the store that last read the slice it is about to overwrite, so several stores
+// per warp are in flight and no warp waits for another.
+struct WarpStore {
+  uint8_t* buf;       // this warp's slices
+  uint32_t buf_addr;  // the same, as a shared-space address
+  int nsw;            // number of slices (2 or 4)
+  int qw, qh, qn;     // position of the warp's rows inside the row tile
 };
 
+__device__ __forceinline__ void wait_slice_free(const WarpStore& ws, int lane) {
+  if (lane == 0) {
+    if (ws.nsw == 4) bulk_wait_group_read<3>();
+    else bulk_wait_group_read<1>();
+  }
+  __syncwarp();
+}
+
+__device__ __forceinline__ void issue_slice_store(const GemmArgs& a, const TileCoord& t, const WarpStore& ws,
+                                                  uint32_t slot, int col, int lane) {
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    const int c2 = (a.a_mn ? t.tap : t.h0) + ws.qh, c3 = (a.a_mn ? t.split : t.n0) + ws.qn;
+    tma_store_4d(&a.out_map, ws.buf_addr + slot * 4096u, col, t.w0 + ws.qw, c2, c3);
+    bulk_commit_group();
+  }
+}
+
 template <typename OutT>
-__device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc, int row,
-                                                  bool zero, uint8_t* staging, uint32_t staging_addr,
-                                                  const EpilogueSync& sync, uint32_t& store_count) {
+__device__ __forceinline__ void epilogue_tile_tma(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc, int lane,
+                                                  bool zero, const WarpStore& ws, uint32_t& store_count) {
   constexpr int CPB = 128 / sizeof(OutT);  // columns per block
   constexpr int P = 16 / sizeof(OutT);     // columns per 16-byte chunk
   const OutT* bias = static_cast<const OutT*>(a.bias);
-  const bool issuer = threadIdx.x == 64;
-  const int c2 = a.a_mn ? t.tap : t.h0, c3 = a.a_mn ? t.split : t.n0;
   for (int c0 = 0; c0 < a.bn; c0 += CPB, ++store_count) {
-    const uint32_t sbuf = store_count & 1u, par = (store_count >> 1) & 1u;
-    if (issuer) {
-      bulk_wait_group_read<1>();  // the store that last used this tile has finished reading it
-      mbar_arrive(sync.free_bar[sbuf]);
-    }
-    if (!mbar_wait(sync.free_bar[sbuf], par, sync.abort_flag, g_error_record, 0x600u + sbuf)) return false;
-    uint8_t* tile = staging + sbuf * kABytes + (size_t)row * 128;
+    const uint32_t slot = store_count & (uint32_t)(ws.nsw - 1);
+    wait_slice_free(ws, lane);
+    uint8_t* row_ptr = ws.buf + slot * 4096u + (size_t)lane * 128;
 #pragma unroll
     for (int half = 0; half < CPB / 32; ++half) {
       uint32_t acc[32];
@@ -253,18 +270,11 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs& a, const TileC
 #pragma unroll
         for (int i = 0; i < P; ++i) pk.set(i, from_f32<OutT>(v[i]));
         const int chunk = half * (32 / P) + g;  // 0..7 within the 128-byte row
-        *reinterpret_cast<uint4*>(tile + ((chunk ^ (row & 7)) << 4)) = pk.raw;
+        *reinterpret_cast<uint4*>(row_ptr + ((chunk ^ (lane & 7)) << 4)) = pk.raw;
       }
     }
-    fence_proxy_async_smem();
-    mbar_arrive(sync.written_bar[sbuf]);
-    if (issuer) {
-      if (!mbar_wait(sync.written_bar[sbuf], par, sync.abort_flag, g_error_record, 0x610u + sbuf)) return false;
-      tma_store_4d(&a.out_map, staging_addr + sbuf * kABytes, t.nf0 + c0, t.w0, c2, c3);
-      bulk_commit_group();
-    }
+    issue_slice_store(a, t, ws, slot, t.nf0 + c0, lane);
   }
-  return true;
 }
 
 // Packed-pair arithmetic for the 16-bit fast epilogue.
@@ -283,11 +293,6 @@ struct Pair<__nv_bfloat16> {
   static __device__ __forceinline__ type splat(float v) { return __float2bfloat162_rn(v); }
 };
 
-// The common case of the TMA-store epilogue, kept short because the four epilogue warps are
-// issue-bound: 16-bit output, alpha == 1, optional bias, activation none / ReLU / ReLU6.  The
-// accumulators are rounded to the output type first and bias and activation are applied to
-// packed pairs in that type - the arithmetic of separate convolution, bias-add and activation
-// passes.  Same staging and hand-off protocol as epilogue_tile_tma.
 template <typename P2>
 __device__ __forceinline__ uint32_t pair_bits(P2 v) {
   return *reinterpret_cast<uint32_t*>(&v);
@@ -298,7 +303,7 @@ __device__ __forceinline__ P2 bits_pair(uint32_t v) {
 }
 
 // Converts 32 accumulator columns of one row (four 16-byte chunks, numbered from chunk_base) and
-// writes them into the row's 128 bytes of the staging tile.
+// writes them into the row's 128 bytes of the staging slice.
 template <typename OutT>
 __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bool zero, const OutT* bias, int col0,
                                                    int ext_cols, int act, uint8_t* row_ptr, int row, int chunk_base) {
@@ -323,41 +328,31 @@ __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bo
   }
 }
 
+// The common case of the staged epilogue, kept short because a lone warp per scheduler is
+// latency-bound: 16-bit output, alpha == 1, optional bias, activation none / ReLU / ReLU6.  The
+// accumulators are rounded to the output type first and bias and activation are applied to
+// packed pairs in that type - the arithmetic of separate convolution, bias-add and activation
+// passes.
 template <typename OutT>
-__device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc,
-                                                       int row, bool zero, uint8_t* staging, uint32_t staging_addr,
-                                                       const EpilogueSync& sync, uint32_t& store_count) {
+__device__ __forceinline__ void epilogue_tile_tma_fast(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc,
+                                                       int lane, bool zero, const WarpStore& ws,
+                                                       uint32_t& store_count) {
   const OutT* bias = static_cast<const OutT*>(a.bias);
-  const bool issuer = threadIdx.x == 64;
-  const int c2 = a.a_mn ? t.tap : t.h0, c3 = a.a_mn ? t.split : t.n0;
   const int act = a.act, ext_cols = a.ext_cols;
   for (int c0 = 0; c0 < a.bn; c0 += 64, ++store_count) {
-    const uint32_t sbuf = store_count & 1u, par = (store_count >> 1) & 1u;
-    uint32_t acc0[32];
-    if (!zero) tmem_ld_32x32(tmem_acc + (uint32_t)c0, acc0);  // issued before waiting for the staging tile
-    if (issuer) {
-      bulk_wait_group_read<1>();
-      mbar_arrive(sync.free_bar[sbuf]);
+    const uint32_t slot = store_count & (uint32_t)(ws.nsw - 1);
+    uint32_t acc0[32], acc1[32];
+    if (!zero) {  // issued before waiting for the staging slice
+      tmem_ld_32x32(tmem_acc + (uint32_t)c0, acc0);
+      tmem_ld_32x32(tmem_acc + (uint32_t)(c0 + 32), acc1);
     }
-    if (!mbar_wait(sync.free_bar[sbuf], par, sync.abort_flag, g_error_record, 0x600u + sbuf)) return false;
+    wait_slice_free(ws, lane);
     if (!zero) tmem_wait_ld();
-    uint8_t* row_ptr = staging + sbuf * kABytes + (size_t)row * 128;
-    {
-      uint32_t acc1[32];
-      if (!zero) tmem_ld_32x32(tmem_acc + (uint32_t)(c0 + 32), acc1);  // overlaps the conversion of the first half
-      fast_convert_store<OutT>(acc0, zero, bias, t.nf0 + c0, ext_cols, act, row_ptr, row, 0);
-      if (!zero) tmem_wait_ld();
-      fast_convert_store<OutT>(acc1, zero, bias, t.nf0 + c0 + 32, ext_cols, act, row_ptr, row, 4);
-    }
-    fence_proxy_async_smem();
-    mbar_arrive(sync.written_bar[sbuf]);
-    if (issuer) {
-      if (!mbar_wait(sync.written_bar[sbuf], par, sync.abort_flag, g_error_record, 0x610u + sbuf)) return false;
-      tma_store_4d(&a.out_map, staging_addr + sbuf * kABytes, t.nf0 + c0, t.w0, c2, c3);
-      bulk_commit_group();
-    }
+    uint8_t* row_ptr = ws.buf + slot * 4096u + (size_t)lane * 128;
+    fast_convert_store<OutT>(acc0, zero, bias, t.nf0 + c0, ext_cols, act, row_ptr, lane, 0);
+    fast_convert_store<OutT>(acc1, zero, bias, t.nf0 + c0 + 32, ext_cols, act, row_ptr, lane, 4);
+    issue_slice_store(a, t, ws, slot, t.nf0 + c0, lane);
   }
-  return true;
 }
 
 // EPI selects the epilogue compiled into the instantiation: 0 = direct stores from registers,
@@ -377,7 +372,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
   const int S = a.stages;
   // two 16 KB staging tiles for the TMA-store epilogue, then the barrier block
   const uint32_t staging_base = base + (uint32_t)S * stage_bytes;
-  const uint32_t staging_bytes = a.tma_store ? 2u * (uint32_t)kABytes : 0u;
+  const uint32_t staging_bytes = a.tma_store ? (uint32_t)a.nsw * 4u * 4096u : 0u;  // 4 warps x nsw slices
   uint8_t* bar_mem = smem + (size_t)S * stage_bytes + staging_bytes;
   const uint32_t bar_base = staging_base + staging_bytes;
   auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
@@ -385,8 +380,6 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
   auto ready_bar = [&](int s) { return bar_base + 8u * (uint32_t)(2 * kMaxStages + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * kMaxStages + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * kMaxStages + 2 + b); };
-  auto epi_free_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * kMaxStages + 4 + b); };
-  auto epi_written_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * kMaxStages + 6 + b); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 8 * (3 * kMaxStages + 8));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * (3 * kMaxStages + 8) + 8);
 
@@ -401,8 +394,6 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full_bar(b), 1);
       mbar_init(acc_empty_bar(b), 4);
-      mbar_init(epi_free_bar(b), 1);
-      mbar_init(epi_written_bar(b), 128);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -569,7 +560,14 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
     const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
     const int row = q * 32 + lane;
     uint32_t tcount = 0, store_count = 0;
-    const EpilogueSync esync{{epi_free_bar(0), epi_free_bar(1)}, {epi_written_bar(0), epi_written_bar(1)}, abort_flag};
+    const int wslot = warp - 2;  // 0..3: which staging slices this warp owns
+    WarpStore ws;
+    ws.nsw = a.nsw;
+    ws.buf = smem + (size_t)S * stage_bytes + (size_t)wslot * (size_t)a.nsw * 4096u;
+    ws.buf_addr = staging_base + (uint32_t)wslot * (uint32_t)a.nsw * 4096u;
+    ws.qw = (q * 32) % a.etw;
+    ws.qh = ((q * 32) / a.etw) % a.eth;
+    ws.qn = (q * 32) / (a.etw * a.eth);
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
       const TileCoord t = decode_tile(a, tile);
       const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
@@ -577,22 +575,19 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
       tc_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
       const bool zero = !(t.ks_end > t.ks_begin);
-      uint8_t* staging = smem + (size_t)S * stage_bytes;
-      bool ok = true;
       if constexpr (EPI == 2) {
-        ok = epilogue_tile_tma_fast<OutT>(a, t, tmem_acc, row, zero, staging, staging_base, esync, store_count);
+        epilogue_tile_tma_fast<OutT>(a, t, tmem_acc, lane, zero, ws, store_count);
       } else if constexpr (EPI == 1) {
-        ok = epilogue_tile_tma<OutT>(a, t, tmem_acc, row, zero, staging, staging_base, esync, store_count);
+        epilogue_tile_tma<OutT>(a, t, tmem_acc, lane, zero, ws, store_count);
       } else {
         epilogue_tile<OutT>(a, t, tmem_acc, row, zero);
       }
-      if (!ok) break;
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar((int)buf));
     }
     // the staging tiles must not be released while a store is still reading them
-    if (EPI != 0 && threadIdx.x == 64) bulk_wait_group<0>();
+    if (EPI != 0 && lane == 0) bulk_wait_group<0>();
   } else if (SPLIT) {
     // ------------------------------- hi/lo split (fp32 as 3xTF32) ----------------------------
     // hi keeps the 19 leading bits (what the tensor core reads of an fp32 word); lo = x - hi is
@@ -730,7 +725,24 @@ void choose_box(int total, int W, int H, int N, int* tw, int* th, int* tn) {
     }
 }
 
-int pick_bn(long long row_tiles, int cols, int unit, int max_bn, int sms) {
+// Tiles with a short reduction are bound by the latency of their epilogue chain (TMEM read,
+// convert, stage, store), not by any throughput limit; two CTAs per SM overlap two such chains.
+// That needs at most 256 TMEM columns (bn <= 128) and half the shared memory per CTA.
+// PDNN_TC_OCC2=0/1 overrides the heuristic (for experiments).
+bool want_occ2(int ksteps, int cols) {
+  static const int forced = [] {
+    const char* e = getenv("PDNN_TC_OCC2");
+    return e == nullptr ? -1 : atoi(e);
+  }();
+  if (forced >= 0) return forced != 0;
+  return ksteps <= 4 || cols <= 128;
+}
+
+int pick_bn(long long row_tiles, int cols, int unit, int max_bn, int sms, int ksteps = 1 << 30) {
+  if (want_occ2(ksteps, cols)) {
+    max_bn = std::min(max_bn, 128);
+    sms *= 2;
+  }
   // cost ~ waves * (bn + fixed overhead); unit: granularity the B loader needs
   int best_bn = unit;
   double best = 1e30;
@@ -802,7 +814,9 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   g.cpb = 128 / (int)dtype_size(g.out_dtype);
   g.tma_store = 0;
   if (g.beta == 0.f && g.bn % g.cpb == 0 && aligned16(g.out)) {
-    const uint32_t box[4] = {(uint32_t)g.cpb, (uint32_t)g.etw, (uint32_t)g.eth, (uint32_t)g.etn};
+    // one store covers the 32 rows of one epilogue warp: a sub-box of the row tile
+    const int sw = std::min(g.etw, 32), sh = std::min(g.eth, 32 / sw), sn = 32 / (sw * sh);
+    const uint32_t box[4] = {(uint32_t)g.cpb, (uint32_t)sw, (uint32_t)sh, (uint32_t)sn};
     if (!make_map(&g.out_map, g.out_dtype, false, g.out, out_dims, out_strides, box)) return false;
     g.tma_store = 1;
     g.epi_fast = (g.out_dtype != PDNN_F32 && g.alpha == 1.f && g.ext_cols % 8 == 0 &&
@@ -812,7 +826,26 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
                      : 0;
   }
   const unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (compute_dtype == PDNN_F32 ? 2u : 1u);
-  const int budget = kSmemBudget - 2048 - (g.tma_store ? 2 * kABytes : 0);
+  // Tiles with few reduction steps are bound by their output: give them deeper store staging
+  // and a shallower load pipeline; long reductions get the opposite.
+  const int ksteps = g.a_mn ? g.slabs_per_split : g.num_taps * g.cblocks;
+  g.nsw = 2;
+  g.occ2 = 0;
+  if (!g.a_mn && compute_dtype != PDNN_F32 && g.tma_store && g.bn <= 128 && want_occ2(ksteps, g.ext_cols)) {
+    // two CTAs per SM: 113 KB each, 2 x 128 TMEM columns each
+    const int budget2 = 113 * 1024 - 2048 - 2 * 4 * 4096;
+    const int st2 = (int)(budget2 / stage);
+    if (st2 >= 2) {
+      g.occ2 = 1;
+      g.stages = std::min(kMaxStages, st2);
+      return true;
+    }
+  }
+  if (g.tma_store && ksteps <= 8) {
+    const int stages_deep = (int)((kSmemBudget - 2048 - 4 * 4 * 4096) / stage);
+    if (stages_deep >= std::min(ksteps + 1, 3)) g.nsw = 4;
+  }
+  const int budget = kSmemBudget - 2048 - (g.tma_store ? g.nsw * 4 * 4096 : 0);
   g.stages = std::max(2, std::min(kMaxStages, (int)(budget / stage)));
   return true;
 }
@@ -845,9 +878,11 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   if (total <= 0) return PDNN_OK;
   if (total > 0x7FFFFFFFll) return fail(PDNN_INDEX_EXCEEDED, "tensor-core gemm: too many tiles");
   const unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
-  // At least 120 KB so that two CTAs never share an SM (and with it the tensor memory).
-  const size_t smem =
-      std::max<size_t>(1024 + (size_t)g.stages * stage + (g.tma_store ? 2 * kABytes : 0) + 512, 120 * 1024);
+  // Unless the plan is sized for two CTAs per SM (each then allocates at most 256 of the 512
+  // TMEM columns), ask for at least 120 KB so that CTAs never share an SM: a CTA that cannot get
+  // its TMEM columns would wait for them without a limit.
+  size_t smem = 1024 + (size_t)g.stages * stage + (g.tma_store ? g.nsw * 4 * 4096 : 0) + 512;
+  if (!(g.occ2 && g.tmem_cols <= 256)) smem = std::max<size_t>(smem, 120 * 1024);
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -864,7 +899,7 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   GemmKernel kernel = select_kernel(split, epi, g.out_dtype);
   if (kernel == nullptr) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: no kernel for this output type");
   const int sms = device_sm_count();
-  const unsigned grid = (unsigned)std::min<long long>(total, sms);
+  const unsigned grid = (unsigned)std::min<long long>(total, (long long)sms * (g.occ2 ? 2 : 1));
   kernel<<<grid, split ? 320 : 192, smem, s>>>(g);
   return check_launch("tensor-core gemm");
 }
@@ -1106,7 +1141,8 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   g.tiles_h = ceil_div(p.out_rows, g.th);
   g.tiles_n = ceil_div(p.batch, g.tn);
   const long long row_tiles = (long long)g.tiles_w * g.tiles_h * g.tiles_n;
-  g.bn = pick_bn(row_tiles, p.features, hwcf ? epr : 16, dtype == PDNN_F32 ? 128 : 256, sms);
+  g.bn = pick_bn(row_tiles, p.features, hwcf ? epr : 16, dtype == PDNN_F32 ? 128 : 256, sms,
+                 p.window_rows * p.window_cols * ceil_div(p.channels, epr));
   g.n_tiles = ceil_div(p.features, g.bn);
   set_operand_layout(g, dtype, hwcf ? 1 : 0);
   const uint32_t abox[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)g.th, (uint32_t)g.tn};
@@ -1469,7 +1505,7 @@ int tc_matmul(int dtype, int tl, int tr, const void* lhs, const void* rhs, void*
   g.a_mn = tl ? 1 : 0;
   const int m_tiles = ceil_div(m, kTileM);
   const int b_mn = tr ? 0 : 1;
-  g.bn = pick_bn((long long)m_tiles * batches, n, b_mn ? epr : 16, dtype == PDNN_F32 ? 128 : 256, sms);
+  g.bn = pick_bn((long long)m_tiles * batches, n, b_mn ? epr : 16, dtype == PDNN_F32 ? 128 : 256, sms, ceil_div(k, epr));
   g.n_tiles = ceil_div(n, g.bn);
   set_operand_layout(g, dtype, b_mn);
   g.taps[0] = TapEntry{0, 0, 0, 0};
