@@ -137,6 +137,23 @@ int pdnn_depthwise_conv2d(int pass, int dtype, const void* input, const void* fi
                           void* stream);
 size_t pdnn_depthwise_workspace_bytes(int pass, int dtype, const PdnnDepthwiseConv2DParams* params);
 
+/* No counterpart in the reference.  The filter-backprop pass of pdnn_depthwise_conv2d for hosts
+ * that may not allocate device memory once they are running - an inference server with a fixed
+ * memory plan, a framework that owns the whole device heap, a latency-critical loop where an
+ * allocator call is not allowed.  Same arguments, same result: (x, dy) -> dW for the filter
+ * [R][S][C][mult].  The partial sums live in one fixed 8 MiB array inside the library
+ * (pdnn_noalloc_scratch_bytes()); the call performs no cudaMalloc, cudaFree or other allocating
+ * call.  It returns PDNN_INSUFFICIENT_WORKSPACE when R*S*C*mult*4 bytes exceed that array.
+ *  - The first call on each device looks the array's device address up (a one-time, host-side
+ *    query made with that device current); make that first call before any stream capture.
+ *  - All calls on a device share the array, and it keeps whatever the last call left there.
+ *    Every call overwrites the part it reads, so stale contents never reach a result, but two
+ *    calls that overlap on the GPU (different streams, no ordering between them) race on it:
+ *    keep calls to this entry point ordered. */
+int pdnn_depthwise_filter_backprop_noalloc(int dtype, const void* input, const void* output_grad, void* filter_grad,
+                                           const PdnnDepthwiseConv2DParams* params, void* stream);
+size_t pdnn_noalloc_scratch_bytes(void);
+
 /* Replaces pooling::launch, two-pointer form (include/portdnn/pooling/launch.h:112-180,
  * src/pooling/launch_pooling.cc:89-165): forward for every op (input -> output) and the
  * average gradient (direction 1: input = dy, output = dx).  NHWC only. */

@@ -77,6 +77,7 @@ def lib():
         L.pdnn_last_error.restype = ctypes.c_char_p
         L.pdnn_launch_count.restype = ctypes.c_ulonglong
         L.pdnn_depthwise_workspace_bytes.restype = ctypes.c_size_t
+        L.pdnn_noalloc_scratch_bytes.restype = ctypes.c_size_t
         _LIB = L
     return _LIB
 
@@ -214,6 +215,20 @@ def depthwise_conv2d(pass_, inp, fil, params, out=None, workspace=None):
     _check(lib().pdnn_depthwise_conv2d(pass_, _dtype_code(inp), _ptr(inp), _ptr(fil), _ptr(out), ctypes.byref(p),
                                        _ptr(workspace), ctypes.c_size_t(ws_bytes), _stream()))
     return out
+
+
+def depthwise_filter_backprop_noalloc(inp, output_grad, params, out):
+    """pdnn_depthwise_filter_backprop_noalloc: (x, dy) -> dW into the caller's ``out`` without any
+    device allocation inside the library (the partial sums use the library's fixed scratch array).
+    No counterpart in the reference."""
+    _require_cuda(inp, output_grad, out)
+    _check(lib().pdnn_depthwise_filter_backprop_noalloc(_dtype_code(inp), _ptr(inp), _ptr(output_grad), _ptr(out),
+                                                        ctypes.byref(params), _stream()))
+    return out
+
+
+def noalloc_scratch_bytes():
+    return int(lib().pdnn_noalloc_scratch_bytes())
 
 
 def depthwise_workspace_bytes(pass_, dtype, params):

@@ -136,6 +136,16 @@ int pdnn_depthwise_conv2d(int pass, int dtype, const void* input, const void* fi
                           static_cast<cudaStream_t>(stream));
 }
 
+int pdnn_depthwise_filter_backprop_noalloc(int dtype, const void* input, const void* output_grad, void* filter_grad,
+                                           const PdnnDepthwiseConv2DParams* params, void* stream) {
+  if (params == nullptr || input == nullptr || output_grad == nullptr || filter_grad == nullptr)
+    return fail(PDNN_INVALID_PARAMETER, "depthwise: null argument");
+  return launch_depthwise_filter_backprop_static(dtype, input, output_grad, filter_grad, *params,
+                                                 static_cast<cudaStream_t>(stream));
+}
+
+size_t pdnn_noalloc_scratch_bytes(void) { return static_scratch_bytes(); }
+
 size_t pdnn_depthwise_workspace_bytes(int pass, int dtype, const PdnnDepthwiseConv2DParams* params) {
   if (params == nullptr) return 0;
   return depthwise_workspace_bytes(pass, dtype, *params);

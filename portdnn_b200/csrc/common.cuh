@@ -106,6 +106,9 @@ int launch_pooling_max_grad(int op, int dtype, const void* x, const void* y, con
 int launch_depthwise(int pass, int dtype, const void* in, const void* fil, void* out,
                      const PdnnDepthwiseConv2DParams& p, void* ws, size_t ws_bytes, cudaStream_t s);
 size_t depthwise_workspace_bytes(int pass, int dtype, const PdnnDepthwiseConv2DParams& p);
+int launch_depthwise_filter_backprop_static(int dtype, const void* in, const void* dy, void* dw,
+                                            const PdnnDepthwiseConv2DParams& p, cudaStream_t s);
+size_t static_scratch_bytes();
 int launch_pointwise(int op, int dtype, const void* in, void* out, size_t n, cudaStream_t s);
 int launch_pointwise_grad(int op, int dtype, const void* fwd, const void* err, void* out, size_t n, cudaStream_t s);
 int launch_bias_add(int dtype, const void* in, const void* bias, void* out, size_t rows, int channels, int act,

@@ -10,6 +10,7 @@
 #include "common.cuh"
 
 #include <cfloat>
+#include <mutex>
 
 namespace pdnn {
 
@@ -705,6 +706,92 @@ int launch_scale_blend(int dtype, const void* a, float alpha, const void* b, flo
       scale_blend_kernel<T, 1><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
           static_cast<const T*>(a), alpha, static_cast<const T*>(b), beta, static_cast<T*>(out), n);
     return check_launch("scale blend");
+  });
+}
+
+// ------------------------------------------------------------------------------------------
+// Depthwise filter backprop for callers that must not allocate
+// ------------------------------------------------------------------------------------------
+// Some hosts of this library run where a device allocation is off the table: inside a framework
+// that hands every byte of device memory to its own arena up front, in a real-time serving loop
+// that forbids allocator calls after start-up, or under a memory budget that is fixed before the
+// first request.  launch_depthwise() needs scratch for the per-slice partial sums of its filter
+// backprop and takes it from the caller or from cudaMallocAsync; this variant instead keeps the
+// partial sums in the fixed array below, which every device that loads the library holds from
+// load until the process exits.
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB of fp32 partial sums
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mutex;
+float* g_static_scratch_ptr[kMaxDevices] = {};
+
+// The array's name is only a host-side handle: the address the kernels need has to be asked for,
+// once per device and with that device current.
+int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return fail(PDNN_ALLOCATION_PROBLEM, "static scratch: no usable current device");
+  }
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return fail(PDNN_ALLOCATION_PROBLEM, "static scratch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    }
+    g_static_scratch_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_scratch_ptr[dev];
+  return PDNN_OK;
+}
+}  // namespace
+
+size_t static_scratch_bytes() { return kStaticScratchBytes; }
+
+int launch_depthwise_filter_backprop_static(int dtype, const void* in, const void* dy, void* dw,
+                                            const PdnnDepthwiseConv2DParams& p, cudaStream_t s) {
+  if (!depthwise_params_ok(p)) return fail(PDNN_INVALID_PARAMETER, "depthwise: non-positive size or negative padding");
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  const int F = p.channels * p.channel_multiplier;
+  const size_t n_out = (size_t)p.window_rows * p.window_cols * F;
+  if (n_out * sizeof(float) > kStaticScratchBytes)
+    return fail(PDNN_INSUFFICIENT_WORKSPACE,
+                "depthwise filter backprop without allocation: the filter gradient has %zu elements, the fixed "
+                "scratch holds at most %zu",
+                n_out, kStaticScratchBytes / sizeof(float));
+  float* partial = nullptr;
+  const int st0 = static_scratch_for_current_device(&partial);
+  if (st0 != PDNN_OK) return st0;
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    constexpr int VN = Vec16<T>::N;
+    const bool vec = p.channel_multiplier == 1 && (p.channels % VN == 0) && aligned16(in) && aligned16(dy) && aligned16(dw);
+    const int V = vec ? VN : 1;
+    // as many pixel slices as the general path would use, but no more than the array holds
+    int slices = fbp_slices(p, V, sms);
+    const size_t fit = kStaticScratchBytes / (n_out * sizeof(float));
+    if ((size_t)slices > fit) slices = (int)fit;
+    const long long pixels = (long long)p.batch * p.out_rows * p.out_cols;
+    const long long per_slice = (pixels + slices - 1) / slices;
+    dim3 block(kFbpLanesF, kFbpLanesP);
+    dim3 grid(slices, p.window_rows * p.window_cols, (F + kFbpLanesF * V - 1) / (kFbpLanesF * V));
+    // Stage 1 writes every partial[slice][tap][f] it later reads, so the array's old contents
+    // never leak into a result and nothing has to be cleared first.
+    if (vec)
+      depthwise_filter_backprop_partial_kernel<T, VN><<<grid, block, 0, s>>>(
+          static_cast<const T*>(in), static_cast<const T*>(dy), partial, p, per_slice);
+    else
+      depthwise_filter_backprop_partial_kernel<T, 1><<<grid, block, 0, s>>>(
+          static_cast<const T*>(in), static_cast<const T*>(dy), partial, p, per_slice);
+    int st = check_launch("depthwise filter backprop, fixed scratch (partial sums)");
+    if (st != PDNN_OK) return st;
+    reduce_slices_kernel<T><<<grid_for(n_out, kBlock, sms), kBlock, 0, s>>>(partial, static_cast<T*>(dw), slices, n_out);
+    return check_launch("depthwise filter backprop, fixed scratch (slice reduction)");
   });
 }
 
