@@ -1,0 +1,2 @@
+// See data_format.h: all layout and padding tags live there.
+#include "portdnn/data_format.h"

@@ -1,0 +1,64 @@
+"""Batch sharding across GPUs and the one collective of the path.
+
+The reference is single-device (one sycl::queue per backend, include/portdnn/backend/
+snn_usm_backend.h:79-80).  Here the convolution path is sharded by batch, one process per GPU:
+forward and input backprop need no exchange at all (every rank holds all filters); filter
+backprop reduces over the batch, so each rank's filter gradients are summed with ONE all-reduce
+over a contiguous fp32 buffer.  torch.distributed (NCCL on GPUs, gloo in the CPU tests) is the
+plumbing; nothing here touches peer memory directly.
+"""
+import numpy as np
+
+
+def shard_batch(global_batch, world_size, rank):
+    """Images [start, start+count) of the global batch that `rank` owns: contiguous, sizes differ
+    by at most one, earlier ranks take the remainder."""
+    if world_size <= 0 or not 0 <= rank < world_size:
+        raise ValueError("bad rank/world size")
+    base, rem = divmod(global_batch, world_size)
+    count = base + (1 if rank < rem else 0)
+    start = rank * base + min(rank, rem)
+    return start, count
+
+
+def filter_gradient_layout(filter_sizes, pad_to=None):
+    """Offsets of each layer's filter gradient inside the one contiguous buffer, each rounded
+    up to 64 elements (256 bytes of fp32) so that every view stays 16-byte aligned for the
+    kernels; returns (offsets, total)."""
+    offsets, off = [], 0
+    for n in filter_sizes:
+        offsets.append(off)
+        off += (int(n) + 63) // 64 * 64
+    total = off if pad_to is None else max(off, int(pad_to))
+    return offsets, total
+
+
+class FilterGradientBucket:
+    """All filter gradients of a network in one fp32 tensor, reduced with a single all_reduce."""
+
+    def __init__(self, filter_sizes, device, pad_to=None):
+        import torch
+        self.sizes = [int(n) for n in filter_sizes]
+        self.offsets, self.total = filter_gradient_layout(self.sizes, pad_to)
+        self.buffer = torch.zeros(self.total, dtype=torch.float32, device=device)
+
+    def view(self, i):
+        return self.buffer[self.offsets[i]:self.offsets[i] + self.sizes[i]]
+
+    def all_reduce(self, group=None, async_op=False):
+        """Sum over ranks (no-op without an initialised process group or with one rank)."""
+        import torch.distributed as dist
+        if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
+            return None
+        return dist.all_reduce(self.buffer, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+
+
+def max_over_ranks(value, device=None, group=None):
+    """A timing taken on every rank -> the slowest rank's value (what a multi-GPU number must report)."""
+    import torch
+    import torch.distributed as dist
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return float(value)
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t.item())
