@@ -55,7 +55,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu_index)],
+                                          "-lms", "25", "-i", str(self.gpu_index)],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -91,61 +91,6 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------
-class ResNetStack:
-    """Buffers, seeded weights and the per-layer calls of the conv stack on one GPU."""
-
-    def __init__(self, batch, device, seed):
-        import torch
-        import portdnn_b200 as pd
-        from portdnn_b200 import workloads
-        self.pd, self.torch, self.workloads = pd, torch, workloads
-        self.layers = workloads.resnet50_v15(batch)
-        g = torch.Generator(device=device).manual_seed(seed)
-        self.weights, self.biases, sizes = {}, {}, {}
-        for l in self.layers:
-            p = l.params
-            if isinstance(l, workloads.ConvLayer):
-                fan_in = p.window_rows * p.window_cols * p.channels
-                w = torch.randn(fan_in * p.features, device=device, generator=g) * (2.0 / fan_in) ** 0.5  # He-normal
-                self.weights[l.name] = w.half()
-                self.biases[l.name] = (torch.randn(p.features, device=device, generator=g) * 0.01).half()
-                n_out = p.batch * p.out_rows * p.out_cols * p.features
-            else:
-                n_out = p.batch * p.out_rows * p.out_cols * p.channels
-            sizes[l.dst] = max(sizes.get(l.dst, 0), n_out)
-        self.buffers = {k: torch.empty(v, dtype=torch.float16, device=device) for k, v in sizes.items()}
-        self.buffers["input"] = torch.randn(batch * 224 * 224 * 3, device=device, generator=g).half()
-        self.flops = workloads.conv_flops(self.layers)
-        # caller-provided scratch (the stem's packed input), so that a step allocates nothing
-        self.workspaces = {}
-        for l in self.layers:
-            if isinstance(l, workloads.ConvLayer):
-                _, rec = pd.conv2d_workspace_size(pd.FORWARD, pd.F16, l.params, pd.ALGO_TILED)
-                if rec:
-                    self.workspaces[l.name] = torch.empty(rec, dtype=torch.float16, device=device)
-
-    def view(self, name, n):
-        return self.buffers[name][:n]
-
-    def run_layer(self, l):
-        pd, p = self.pd, l.params
-        if isinstance(l, self.workloads.ConvLayer):
-            n_in = p.batch * p.in_rows * p.in_cols * p.channels
-            n_out = p.batch * p.out_rows * p.out_cols * p.features
-            pd.conv2d(pd.FORWARD, self.view(l.src, n_in), self.weights[l.name], p, algorithm=pd.ALGO_TILED,
-                      out=self.view(l.dst, n_out), bias=self.biases[l.name], activation=l.activation,
-                      workspace=self.workspaces.get(l.name))
-        else:
-            n_in = p.batch * p.in_rows * p.in_cols * p.channels
-            n_out = p.batch * p.out_rows * p.out_cols * p.channels
-            pd.pooling(l.op, 0, self.view(l.src, n_in), p, out=self.view(l.dst, n_out))
-
-    def forward(self):
-        for l in self.layers:
-            self.run_layer(l)
-        return self.buffers["out"]
-
-
 def cpu_baseline_sample(seconds_target=12.0):
     """Times the CPU oracle's float forward conv on one ResNet stage-1 3x3 layer at a batch sized
     for ~10-20 s of CPU work; returns the cpu_baseline object."""
@@ -197,14 +142,19 @@ def run_gpu(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    net = ResNetStack(BATCH, device, seed=1234 + rank)  # each rank holds its own 256-image shard
+    train = args.workload == "train"
+    # each rank holds its own 256-image shard of the global batch (weak scaling)
+    net = workloads.ConvStackRunner(workloads.resnet50_v15(BATCH), device, seed=1234 + rank, training=train)
+    step = net.train_step if train else net.forward
+    step_flops = net.flops_train if train else net.flops_forward
     stream = torch.cuda.current_stream()
-    host_in = torch.empty(net.buffers["input"].numel(), dtype=torch.float16).pin_memory()
-    host_in.copy_(net.buffers["input"].cpu())
-    host_out = torch.empty(net.buffers["out"].numel(), dtype=torch.float16).pin_memory()
+    result = net.bucket.buffer if train else net.forward()  # what a step hands back to the host
+    host_in = torch.empty(net.input.numel(), dtype=torch.float16).pin_memory()
+    host_in.copy_(net.input.cpu())
+    host_out = torch.empty(result.numel(), dtype=result.dtype).pin_memory()
 
     for _ in range(max(args.warmup, 3)):
-        net.forward()
+        step()
     barrier()
     err = pd.device_error_record()
     if err[0] != 0:
@@ -219,7 +169,7 @@ def run_gpu(args):
     # graph is replayed per step, so that host-side launch cost (tensor-map encoding, ctypes) does
     # not sit between kernels; --no-graph times plain stream launches instead.
     graph = None
-    if not args.no_graph:
+    if not args.no_graph and not train:
         side = torch.cuda.Stream()
         side.wait_stream(stream)
         with torch.cuda.stream(side):
@@ -235,7 +185,7 @@ def run_gpu(args):
         barrier()
     else:
         l0 = pd.launch_count()
-        net.forward()
+        step()
         launches_per_step = pd.launch_count() - l0
         barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -244,7 +194,7 @@ def run_gpu(args):
         if graph is not None:
             graph.replay()
         else:
-            net.forward()
+            step()
     ev1.record(stream)
     barrier()
     ms = ev0.elapsed_time(ev1)
@@ -256,31 +206,32 @@ def run_gpu(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
-        net.buffers["input"].copy_(host_in, non_blocking=True)
+        net.input.copy_(host_in, non_blocking=True)
         if graph is not None:
             graph.replay()
         else:
-            net.forward()
-        host_out.copy_(net.buffers["out"], non_blocking=True)
+            step()
+        host_out.copy_(result, non_blocking=True)
     e1.record(stream)
     barrier()
     ms_e2e = e0.elapsed_time(e1)
 
     # ---- per-launch durations of the dominant kernel (the implicit-GEMM convolutions) ----
-    conv_layers = [l for l in net.layers if isinstance(l, workloads.ConvLayer)]
+    conv_ids = [i for i, l in enumerate(net.layers) if isinstance(l, workloads.ConvLayer)]
+    conv_layers = [net.layers[i] for i in conv_ids]
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in conv_layers]
     prof_steps = min(args.steps, 5)
     conv_ms = [0.0] * len(conv_layers)
     for _ in range(prof_steps):
-        i = 0
-        for l in net.layers:
-            if isinstance(l, workloads.ConvLayer):
-                evs[i][0].record(stream)
-                net.run_layer(l)
-                evs[i][1].record(stream)
-                i += 1
+        k = 0
+        for i in range(len(net.layers)):
+            if i in conv_ids:
+                evs[k][0].record(stream)
+                net.run_layer(i)
+                evs[k][1].record(stream)
+                k += 1
             else:
-                net.run_layer(l)
+                net.run_layer(i)
         torch.cuda.synchronize()
         for j, (a, b) in enumerate(evs):
             conv_ms[j] += a.elapsed_time(b) / prof_steps
@@ -295,11 +246,12 @@ def run_gpu(args):
         return
 
     peaks = load_peaks()
-    total_flops = net.flops * world * args.steps
+    total_flops = step_flops * world * args.steps
     value = total_flops / (ms * 1e-3) / 1e12
     e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
-    # tensor-core launches only: the stem (3 input channels) runs on the direct kernel
-    tc = [(l, t) for l, t in zip(conv_layers, conv_ms) if l.params.channels % 8 == 0]
+    # forward convolutions, one umma_gemm_kernel launch each (the stem's interval also holds its
+    # two small packing kernels)
+    tc = list(zip(conv_layers, conv_ms))
     tc_flops = sum(l.flops for l, _ in tc)
     tc_ms = sum(t for _, t in tc)
     achieved = tc_flops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else 0.0
@@ -310,20 +262,24 @@ def run_gpu(args):
         json.dump(per_layer, f, indent=1)
 
     line = {
-        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "metric": METRIC if not train else METRIC.replace("forward", "train_step"), "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": "ResNet-50 v1.5 conv stack forward, NHWC fp16, batch 256 per GPU, 53 convs with fused "
-                               "bias+ReLU, 3x3/2 max pool, global 7x7 average pool",
-                   "batch_per_gpu": BATCH, "global_batch": BATCH * world, "sharding": "batch, no forward collective",
+        "config": {"workload": ("ResNet-50 v1.5 conv stack forward, NHWC fp16, batch 256 per GPU, 53 convs with fused "
+                                "bias+ReLU, 3x3/2 max pool, global 7x7 average pool") if not train else
+                               ("ResNet-50 v1.5 training-step convs, NHWC fp16, batch 256 per GPU: forward, ReLU/pool "
+                                "gradients, filter backprop and input backprop of all 53 convs, one fp32 all-reduce "
+                                "of the filter gradients"),
+                   "batch_per_gpu": BATCH, "global_batch": BATCH * world,
+                   "sharding": "batch, no forward collective" if not train else "batch, one NCCL all-reduce per step",
                    "l2": "activations (103-411 MB per layer) exceed the 126 MB L2; no explicit flush",
-                   "flops_per_step_per_gpu": net.flops,
-                   "launch": "plain stream launches" if args.no_graph else "CUDA graph replay of one step"},
+                   "flops_per_step_per_gpu": step_flops,
+                   "launch": "plain stream launches" if graph is None else "CUDA graph replay of one step"},
         "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": host_in.numel() * 2,
-                "d2h_bytes_per_step": host_out.numel() * 2, "ms_per_step": round(ms_e2e / args.steps, 4)},
+                "d2h_bytes_per_step": host_out.numel() * host_out.element_size(), "ms_per_step": round(ms_e2e / args.steps, 4)},
         "gpu_launches": int(launches),
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "umma_gemm_kernel (52 implicit-GEMM conv launches per step)",
+        "roofline": {"bound": "tensor", "kernel": "umma_gemm_kernel (the 53 forward implicit-GEMM conv launches of a step)",
                      "achieved": round(achieved, 1), "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
                      "frac": round(achieved / peaks["tflops_sustained"], 4), "traffic": None,
                      "peak_source": "%s (sustained bf16 matmul)" % peaks["source"],
@@ -383,9 +339,11 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="forward", choices=["forward", "train"],
+                    help="forward: the headline conv stack; train: forward + both backprops + gradient all-reduce")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

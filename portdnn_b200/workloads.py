@@ -93,3 +93,146 @@ def mobilenet_v2_depthwise(batch):
 
 def conv_flops(layers):
     return sum(l.flops for l in layers if isinstance(l, ConvLayer))
+
+
+class ConvStackRunner:
+    """Runs a layer table on one GPU through the C ABI: forward only (activations ping-pong
+    between a few named buffers) or a training step (every activation kept; then, last layer
+    first, ReLU gradient -> filter backprop -> input backprop per convolution, max-pool gradient
+    for pooling layers, filter gradients written into one contiguous fp32 bucket and summed over
+    ranks with a single all-reduce).  The reference has no trainer; its samples chain layers the
+    same way on the host (tools/network.h)."""
+
+    def __init__(self, layers, device, seed, training=False, dtype=None):
+        import torch
+        from . import dist as pdist
+        self.torch, self.layers, self.training, self.device = torch, layers, training, device
+        self.dtype = dtype or torch.float16
+        self.code = api.F16 if self.dtype == torch.float16 else api.BF16 if self.dtype == torch.bfloat16 else api.F32
+        g = torch.Generator(device=device).manual_seed(seed)
+        self.weights, self.biases, self.workspaces = {}, {}, {}
+        first = layers[0].params
+        self.input = torch.randn(first.batch * first.in_rows * first.in_cols * first.channels, device=device,
+                                 generator=g).to(self.dtype)
+        # dataflow: which tensor (index of the producing layer, -1 = network input) each layer reads
+        current, self.src_idx, sizes = {layers[0].src: -1}, [], []
+        for i, l in enumerate(layers):
+            p = l.params
+            self.src_idx.append(current[l.src])
+            current[l.dst] = i
+            if isinstance(l, ConvLayer):
+                fan_in = p.window_rows * p.window_cols * p.channels
+                w = torch.randn(fan_in * p.features, device=device, generator=g) * (2.0 / fan_in) ** 0.5  # He-normal
+                self.weights[i] = w.to(self.dtype)
+                self.biases[i] = (torch.randn(p.features, device=device, generator=g) * 0.01).to(self.dtype)
+                sizes.append(p.batch * p.out_rows * p.out_cols * p.features)
+                _, rec = api.conv2d_workspace_size(api.FORWARD, self.code, p, api.ALGO_TILED)
+                if rec:
+                    self.workspaces[i] = torch.empty(rec, dtype=self.dtype, device=device)
+            else:
+                sizes.append(p.batch * p.out_rows * p.out_cols * p.channels)
+        self.sizes = sizes
+        self.flops_forward = conv_flops(layers)
+        if training:
+            self.acts = [torch.empty(n, dtype=self.dtype, device=device) for n in sizes]
+            self.grads = [None] * len(layers)
+            conv_ids = [i for i, l in enumerate(layers) if isinstance(l, ConvLayer)]
+            self.conv_ids = conv_ids
+            self.bucket = pdist.FilterGradientBucket([self.weights[i].numel() for i in conv_ids], device,
+                                                     pad_to=25_500_000)
+            self.scratch = torch.empty(max(sizes), dtype=self.dtype, device=device)
+            self.dw_tmp = torch.empty(max(self.weights[i].numel() for i in conv_ids), dtype=self.dtype, device=device)
+            last = conv_ids[-1]
+            self.dy_last = torch.randn(sizes[last], device=device, generator=g).to(self.dtype)
+            self.fbp_ws = {}
+            for i in conv_ids:
+                _, rec = api.conv2d_workspace_size(api.FILTER_BACKPROP, self.code, layers[i].params, api.ALGO_TILED)
+                if rec:
+                    self.fbp_ws[i] = rec
+            self.fbp_workspace = torch.empty(max(self.fbp_ws.values(), default=1), dtype=self.dtype, device=device)
+            # forward + filter backprop everywhere, input backprop everywhere but the first layer
+            self.flops_train = sum(l.flops * (3 if self.src_idx[i] != -1 else 2)
+                                   for i, l in enumerate(layers) if isinstance(l, ConvLayer))
+        else:
+            names = {}
+            for l, n in zip(layers, sizes):
+                names[l.dst] = max(names.get(l.dst, 0), n)
+            self.buffers = {k: torch.empty(v, dtype=self.dtype, device=device) for k, v in names.items()}
+
+    # ---- forward -------------------------------------------------------------------------------
+    def _out(self, i):
+        return self.acts[i] if self.training else self.buffers[self.layers[i].dst][:self.sizes[i]]
+
+    def _in(self, i):
+        j = self.src_idx[i]
+        return self.input if j < 0 else self._out(j)
+
+    def run_layer(self, i):
+        l, p = self.layers[i], self.layers[i].params
+        if isinstance(l, ConvLayer):
+            api.conv2d(api.FORWARD, self._in(i), self.weights[i], p, algorithm=api.ALGO_TILED, out=self._out(i),
+                       bias=self.biases[i], activation=l.activation, workspace=self.workspaces.get(i))
+        else:
+            api.pooling(l.op, 0, self._in(i), p, out=self._out(i))
+
+    def forward(self):
+        for i in range(len(self.layers)):
+            self.run_layer(i)
+        return self._out(len(self.layers) - 1)
+
+    # ---- backward ------------------------------------------------------------------------------
+    def _add_grad(self, j, producer):
+        """Routes a gradient into tensor j: the first contribution is written in place, later ones
+        are accumulated."""
+        if self.grads[j] is None:
+            self.grads[j] = self.torch.empty(self.sizes[j], dtype=self.dtype, device=self.device)
+            producer(self.grads[j])
+            self._fresh.add(j)
+        elif j not in self._fresh:
+            producer(self.grads[j])
+            self._fresh.add(j)
+        else:
+            tmp = self.scratch2[:self.sizes[j]]
+            producer(tmp)
+            api.scale_blend(tmp, 1.0, self.grads[j], 1.0, out=self.grads[j])
+
+    def backward(self):
+        torch = self.torch
+        if not hasattr(self, "scratch2"):
+            self.scratch2 = torch.empty_like(self.scratch)
+        self._fresh = set()
+        last = self.conv_ids[-1]
+        block_grad = {}
+        for i in reversed(range(len(self.layers))):
+            l, p, j = self.layers[i], self.layers[i].params, self.src_idx[i]
+            if i == last:
+                dy = self.dy_last
+            elif i in self._fresh:
+                dy = self.grads[i]
+            elif isinstance(l, ConvLayer) and l.name.endswith("_proj"):
+                dy = block_grad[l.name[:-5]]  # the shortcut receives its block's output gradient
+            else:
+                continue  # nothing downstream of this layer takes part in the step (the final pool)
+            if isinstance(l, ConvLayer):
+                if l.name.endswith("_1x1b"):
+                    block_grad[l.name[:-5]] = dy
+                g = self.scratch[:self.sizes[i]]
+                api.pointwise_grad(api.ACT_RELU, self.acts[i], dy, out=g)
+                k = self.conv_ids.index(i)
+                dw = self.dw_tmp[:self.weights[i].numel()]
+                api.conv2d(api.FILTER_BACKPROP, self._in(i), g, p, algorithm=api.ALGO_TILED, out=dw,
+                           workspace=self.fbp_workspace if i in self.fbp_ws else None)
+                self.bucket.view(k).copy_(dw)
+                if j >= 0:
+                    self._add_grad(j, lambda dst: api.conv2d(api.INPUT_BACKPROP, g, self.weights[i], p,
+                                                             algorithm=api.ALGO_TILED, out=dst))
+            elif l.op == api.POOL_AVERAGE:
+                if j >= 0:
+                    self._add_grad(j, lambda dst: api.pooling(l.op, 1, dy, p, out=dst))
+            elif j >= 0:
+                self._add_grad(j, lambda dst: api.pooling_max_grad(l.op, self._in(i), self.acts[i], dy, p, out=dst))
+
+    def train_step(self):
+        self.forward()
+        self.backward()
+        return self.bucket.all_reduce()
