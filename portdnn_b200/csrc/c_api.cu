@@ -25,6 +25,15 @@ int device_sm_count() {
       return;
     }
     sms = prop.major >= 10 ? prop.multiProcessorCount : -1;  // the kernels are sm_100a only
+    // Scratch that a call takes from the stream-ordered allocator goes back to the device's
+    // default pool; keep it there instead of returning it to the driver at the next
+    // synchronisation, or every such call pays for a fresh allocation.
+    cudaMemPool_t pool;
+    if (sms > 0 && cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+      unsigned long long keep = 1ull << 32;  // up to 4 GiB cached
+      cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    cudaGetLastError();
   });
   return sms;
 }

@@ -1314,6 +1314,178 @@ __global__ void __launch_bounds__(256) reduce_splits_kernel(const float* __restr
   }
 }
 
+// ---- filter backprop for very few input channels (network stems) ---------------------------------
+// Mirror image of conv_forward_small_c: with the input packed to CP channels per pixel and
+// padded, the gradient of filter row r is one GEMM  dWp[r][64][K] = Xr^T * dy, where a row of
+// Xr is the 128-byte packed run of 8 pixels x CP channels that output pixel reads for filter
+// row r.  The 64 rows of the result are exactly [s (8)][c (CP)], i.e. the packed filter layout;
+// the final kernel sums the pixel splits and drops the padding entries.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    unpack_small_c_filter_grad_kernel(const float* __restrict__ partial, T* __restrict__ dw, int splits, int R, int S,
+                                      int C, int K, int rows_per_tap) {
+  constexpr int CP = 16 / sizeof(T);
+  const size_t total = (size_t)R * S * C * K;
+  const size_t split_stride = (size_t)R * rows_per_tap * K;
+  for (size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
+    const int k = (int)(idx % K);
+    size_t t = idx / K;
+    const int c = (int)(t % C);
+    t /= C;
+    const int sidx = (int)(t % S);
+    const int r = (int)(t / S);
+    const size_t src = ((size_t)r * rows_per_tap + (size_t)sidx * CP + c) * K + k;
+    float sum = 0.f;
+    for (int sp = 0; sp < splits; ++sp) sum += partial[(size_t)sp * split_stride + src];
+    dw[idx] = from_f32<T>(sum);
+  }
+}
+
+struct SmallCFbpPlan {
+  FbpPlan f;
+  SmallCPlan sp;
+  size_t partial_bytes;
+};
+
+SmallCFbpPlan plan_small_c_fbp(int dtype, const PdnnConv2DParams& p, int sms) {
+  SmallCFbpPlan q;
+  const int epr = dtype == PDNN_F32 ? 32 : 64;
+  q.sp = plan_small_c(dtype, p);
+  FbpPlan& f = q.f;
+  choose_box(epr, p.out_cols, p.out_rows, p.batch, &f.tw, &f.th, &f.tn);
+  f.slabs_w = ceil_div(p.out_cols, f.tw);
+  f.slabs_h = ceil_div(p.out_rows, f.th);
+  f.slabs_n = ceil_div(p.batch, f.tn);
+  f.m_tiles = 1;
+  f.bn = std::min(dtype == PDNN_F32 ? 128 : 256, ceil_div(p.features, epr) * epr);
+  f.n_tiles = ceil_div(p.features, f.bn);
+  const long long out_tiles = (long long)f.n_tiles * p.window_rows;
+  const long long total_slabs = (long long)f.slabs_w * f.slabs_h * f.slabs_n;
+  long long want = std::max<long long>(1, (2ll * sms) / out_tiles);
+  want = std::min<long long>(want, std::max<long long>(1, total_slabs / 8));
+  want = std::min<long long>(want, 64);
+  f.slabs_per_split = (int)((total_slabs + want - 1) / want);
+  f.splits = (int)((total_slabs + f.slabs_per_split - 1) / f.slabs_per_split);
+  q.partial_bytes = (((size_t)f.splits * p.window_rows * epr * p.features * sizeof(float)) + 255) / 256 * 256;
+  return q;
+}
+
+// Returns PDNN_OK, an error, or -1 if a tensor map could not be encoded (the caller falls back to
+// the direct kernel).
+int conv_filter_backprop_small_c(int dtype, const void* x, const void* dy, void* dw, const PdnnConv2DParams& p,
+                                 void* ws, size_t ws_elems, cudaStream_t s) {
+  const size_t es = dtype_size(dtype);
+  const int sms = device_sm_count();
+  const int epr = dtype == PDNN_F32 ? 32 : 64;
+  const SmallCFbpPlan q = plan_small_c_fbp(dtype, p, sms);
+  const FbpPlan& f = q.f;
+  const size_t need = q.sp.xp_bytes + q.partial_bytes;
+  char* scratch = static_cast<char*>(ws);
+  bool own = false;
+  if (scratch == nullptr || ws_elems * es < need || ((uintptr_t)scratch & 255u)) {
+    if (cudaMallocAsync(reinterpret_cast<void**>(&scratch), need, s) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(PDNN_ALLOCATION_PROBLEM, "conv2d: cannot allocate %zu bytes of scratch for the packed input", need);
+    }
+    own = true;
+  }
+  char* xp = scratch;
+  float* partial = reinterpret_cast<float*>(scratch + q.sp.xp_bytes);
+  auto release = [&] {
+    if (own) cudaFreeAsync(scratch, s);
+  };
+  GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.a_mn = 1;
+  g.tw = f.tw;
+  g.th = f.th;
+  g.tn = f.tn;
+  g.etw = kTileM;
+  g.eth = g.etn = 1;
+  g.tiles_w = 1;
+  g.tiles_h = g.tiles_n = 1;
+  g.bn = f.bn;
+  g.n_tiles = f.n_tiles;
+  g.slabs_w = f.slabs_w;
+  g.slabs_h = f.slabs_h;
+  g.slabs_n = f.slabs_n;
+  g.splits = f.splits;
+  g.slabs_per_split = f.slabs_per_split;
+  set_operand_layout(g, dtype, 1);
+  const size_t row_pitch = (size_t)q.sp.Wp * 16;
+  const uint32_t box[4] = {(uint32_t)epr, (uint32_t)f.tw, (uint32_t)f.th, (uint32_t)f.tn};
+  for (int r = 0; r < p.stride_rows; ++r) {
+    const int Hq = ceil_div(q.sp.Hp - r, p.stride_rows);
+    const uint64_t dims[4] = {(uint64_t)epr, (uint64_t)p.out_cols, (uint64_t)std::max(Hq, 1), (uint64_t)p.batch};
+    const uint64_t st[3] = {(uint64_t)p.stride_cols * 16, (uint64_t)p.stride_rows * row_pitch,
+                            (uint64_t)q.sp.Hp * row_pitch};
+    if (!make_map(&g.a_map[r], dtype, true, xp + (size_t)r * row_pitch, dims, st, box)) {
+      release();
+      return -1;
+    }
+  }
+  for (int r = p.stride_rows; r < 4; ++r) g.a_map[r] = g.a_map[0];
+  {
+    g.b_mode = B_MN_4;
+    const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)p.out_cols, (uint64_t)p.out_rows, (uint64_t)p.batch};
+    const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.out_cols * p.features * es,
+                            (uint64_t)p.out_rows * p.out_cols * p.features * es};
+    if (!make_map(&g.b_map, dtype, true, dy, dims, st, box)) {
+      release();
+      return -1;
+    }
+  }
+  for (int r = 0; r < p.window_rows; ++r)
+    g.taps[r] = TapEntry{0, (short)(r / p.stride_rows), (short)(r % p.stride_rows), 0};
+  g.num_taps = p.window_rows;
+  set_epilogue(g, nullptr);
+  g.out = partial;
+  g.out_dtype = PDNN_F32;
+  g.ext_w = epr;  // the rows of a tap's result that exist: [s][c] of the packed filter
+  g.ext_h = g.ext_n = 1;
+  g.ext_cols = p.features;
+  g.stride_w = p.features;
+  g.tap_stride = (long long)epr * p.features;
+  g.split_stride = (long long)p.window_rows * epr * p.features;
+  g.vec_ok = 1;
+  {
+    const uint64_t od[4] = {(uint64_t)p.features, (uint64_t)epr, (uint64_t)p.window_rows, (uint64_t)f.splits};
+    const uint64_t os[3] = {(uint64_t)p.features * 4, (uint64_t)epr * p.features * 4,
+                            (uint64_t)p.window_rows * epr * p.features * 4};
+    if (!setup_store(g, dtype, od, os)) {
+      release();
+      return -1;
+    }
+  }
+  const size_t n_pix = (size_t)p.batch * q.sp.Hp * q.sp.Wp;
+  if (dtype == PDNN_F32)
+    pack_small_c_input_kernel<float><<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
+        static_cast<const float*>(x), reinterpret_cast<uint4*>(xp), p.batch, p.in_rows, p.in_cols, p.channels, q.sp.Hp,
+        q.sp.Wp, p.pad_rows, p.pad_cols);
+  else
+    pack_small_c_input_kernel<__half><<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
+        static_cast<const __half*>(x), reinterpret_cast<uint4*>(xp), p.batch, p.in_rows, p.in_cols, p.channels,
+        q.sp.Hp, q.sp.Wp, p.pad_rows, p.pad_cols);
+  int st = check_launch("conv2d small-channel packing");
+  if (st == PDNN_OK) st = launch_gemm(g, dtype, s);
+  if (st == PDNN_OK) {
+    const size_t n_out = (size_t)p.window_rows * p.window_cols * p.channels * p.features;
+    const unsigned grid = grid_for(n_out, 256, sms);
+    if (dtype == PDNN_F32)
+      unpack_small_c_filter_grad_kernel<float><<<grid, 256, 0, s>>>(partial, static_cast<float*>(dw), f.splits,
+                                                                    p.window_rows, p.window_cols, p.channels, p.features, epr);
+    else if (dtype == PDNN_F16)
+      unpack_small_c_filter_grad_kernel<__half><<<grid, 256, 0, s>>>(partial, static_cast<__half*>(dw), f.splits,
+                                                                     p.window_rows, p.window_cols, p.channels, p.features, epr);
+    else
+      unpack_small_c_filter_grad_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+          partial, static_cast<__nv_bfloat16*>(dw), f.splits, p.window_rows, p.window_cols, p.channels, p.features, epr);
+    st = check_launch("conv2d small-channel filter gradient unpack");
+  }
+  release();
+  return st;
+}
+
 int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, const PdnnConv2DParams& p, void* ws,
                          size_t ws_elems, cudaStream_t s) {
   const size_t es = dtype_size(dtype);
@@ -1444,6 +1616,7 @@ bool tc_conv_supported(int pass, int dtype, const void* in, const void* fil, con
                        const PdnnConv2DParams& p) {
   if (encode_fn() == nullptr) return false;
   if (pass == PDNN_FORWARD && small_c_applicable(dtype, p)) return aligned16(out);
+  if (pass == PDNN_FILTER_BACKPROP && small_c_applicable(dtype, p)) return aligned16(fil);
   if (!conv_common_ok(dtype, p)) return false;
   if (!aligned16(in) || !aligned16(fil) || !aligned16(out)) return false;
   for (int ph = 0; ph < p.stride_rows; ++ph)
@@ -1457,6 +1630,12 @@ size_t tc_conv_workspace_elems(int pass, int dtype, const PdnnConv2DParams& p) {
   if (pass == PDNN_FORWARD && small_c_applicable(dtype, p)) {
     const SmallCPlan sp = plan_small_c(dtype, p);
     return (sp.xp_bytes + sp.wp_bytes) / dtype_size(dtype);
+  }
+  if (pass == PDNN_FILTER_BACKPROP && small_c_applicable(dtype, p)) {
+    int sms = device_sm_count();
+    if (sms <= 0) sms = 148;
+    const SmallCFbpPlan q = plan_small_c_fbp(dtype, p, sms);
+    return (q.sp.xp_bytes + q.partial_bytes) / dtype_size(dtype);
   }
   if (pass != PDNN_FILTER_BACKPROP || !conv_common_ok(dtype, p) || p.filter_format != 0) return 0;
   int sms = device_sm_count();
@@ -1477,7 +1656,12 @@ int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, c
       }
       return conv_forward(dtype, in, fil, out, p, epi, s);
     case PDNN_INPUT_BACKPROP: return conv_input_backprop(dtype, in, fil, out, p, s);
-    case PDNN_FILTER_BACKPROP: return conv_filter_backprop(dtype, in, fil, out, p, ws, ws_elems, s);
+    case PDNN_FILTER_BACKPROP:
+      if (small_c_applicable(dtype, p)) {
+        const int st = conv_filter_backprop_small_c(dtype, in, fil, out, p, ws, ws_elems, s);
+        return st == -1 ? launch_direct_conv(pass, dtype, in, fil, out, p, nullptr, s) : st;
+      }
+      return conv_filter_backprop(dtype, in, fil, out, p, ws, ws_elems, s);
   }
   return fail(PDNN_INVALID_PARAMETER, "bad pass %d", pass);
 }

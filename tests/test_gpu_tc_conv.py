@@ -109,6 +109,21 @@ def test_filter_backprop_against_oracle(orc, dtype, shape):
     assert rel_err(dw, orc.conv2d(orc.FILTER_BACKPROP, x, dy, po)) <= TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("shape", [(2, 32, 32, 3, 64, 7, 2, None, 3), (2, 24, 24, 3, 64, 3, 1, True, None),
+                                   (3, 17, 19, 3, 32, 5, 2, True, None), (2, 20, 20, 1, 16, 3, 1, False, None)])
+def test_stem_forward_and_filter_backprop_few_channels(orc, dtype, shape):
+    """Network stems (C < 8): the packed-row tensor-core path, forward and filter gradient."""
+    n, h, w, c, k, win, st, same, pad = shape
+    p, po, x, wt, dy = _conv_case(orc, dtype, n, h, w, c, k, win, st, bool(same), pad)
+    y = to_host(pd.conv2d(pd.FORWARD, to_dev(x, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_IM2COL))
+    assert_no_device_error()
+    assert rel_err(y, orc.conv2d(orc.FORWARD, x, wt, po)) <= TOL[dtype]
+    dw = to_host(pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, dtype), to_dev(dy, dtype), p, algorithm=pd.ALGO_IM2COL))
+    assert_no_device_error()
+    assert rel_err(dw, orc.conv2d(orc.FILTER_BACKPROP, x, dy, po)) <= TOL[dtype]
+
+
 def test_filter_backprop_with_caller_workspace(orc):
     n, h, w, c, k, win, st = 8, 28, 28, 64, 64, 3, 1
     p, po, x, _, dy = _conv_case(orc, "f16", n, h, w, c, k, win, st)
