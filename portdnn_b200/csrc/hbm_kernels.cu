@@ -11,6 +11,7 @@
 
 #include <cfloat>
 #include <mutex>
+#include <type_traits>
 
 namespace pdnn {
 
@@ -429,6 +430,246 @@ __global__ void __launch_bounds__(kBlock) scale_blend_kernel(const T* __restrict
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// 3x3 windows, register-tiled: the overlapping-window operators above issue nine input loads per
+// output packet and are bound by L1 wavefronts long before HBM.  Here a thread owns one channel
+// packet and a strip of four output columns, walks down the output rows and keeps the three
+// input rows it needs in registers (one new row per step at stride 1, two at stride 2), so each
+// input packet is loaded once per strip instead of up to nine times.  Arithmetic is done on the
+// packet in its own type: half2 FMAs / maxima for fp16 (the reference also accumulates in the
+// tensor type), plain fp32 for float.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+struct Packet;
+template <>
+struct Packet<__half> {
+  __half2 v[4];
+  static __device__ __forceinline__ Packet load(const __half* p) {
+    const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+    Packet o;
+    o.v[0] = *reinterpret_cast<const __half2*>(&r.x);
+    o.v[1] = *reinterpret_cast<const __half2*>(&r.y);
+    o.v[2] = *reinterpret_cast<const __half2*>(&r.z);
+    o.v[3] = *reinterpret_cast<const __half2*>(&r.w);
+    return o;
+  }
+  static __device__ __forceinline__ Packet splat(float f) {
+    Packet o;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o.v[i] = __float2half2_rn(f);
+    return o;
+  }
+  __device__ __forceinline__ void fma(const Packet& a, const Packet& b) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __hfma2(a.v[i], b.v[i], v[i]);
+  }
+  __device__ __forceinline__ void max_ignore_nan(const Packet& a) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __hmax2(v[i], a.v[i]);
+  }
+  __device__ __forceinline__ void max_keep_nan(const Packet& a) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __hmax2_nan(v[i], a.v[i]);
+  }
+  __device__ __forceinline__ void store(__half* p) const {
+    uint4 r;
+    r.x = *reinterpret_cast<const uint32_t*>(&v[0]);
+    r.y = *reinterpret_cast<const uint32_t*>(&v[1]);
+    r.z = *reinterpret_cast<const uint32_t*>(&v[2]);
+    r.w = *reinterpret_cast<const uint32_t*>(&v[3]);
+    *reinterpret_cast<uint4*>(p) = r;
+  }
+};
+template <>
+struct Packet<__nv_bfloat16> {  // maxima only: bf16 products would lose too much in a packed sum
+  __nv_bfloat162 v[4];
+  static __device__ __forceinline__ Packet load(const __nv_bfloat16* p) {
+    const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+    Packet o;
+    o.v[0] = *reinterpret_cast<const __nv_bfloat162*>(&r.x);
+    o.v[1] = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+    o.v[2] = *reinterpret_cast<const __nv_bfloat162*>(&r.z);
+    o.v[3] = *reinterpret_cast<const __nv_bfloat162*>(&r.w);
+    return o;
+  }
+  static __device__ __forceinline__ Packet splat(float f) {
+    Packet o;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o.v[i] = __float2bfloat162_rn(f);
+    return o;
+  }
+  __device__ __forceinline__ void max_ignore_nan(const Packet& a) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __hmax2(v[i], a.v[i]);
+  }
+  __device__ __forceinline__ void max_keep_nan(const Packet& a) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __hmax2_nan(v[i], a.v[i]);
+  }
+  __device__ __forceinline__ void store(__nv_bfloat16* p) const {
+    uint4 r;
+    r.x = *reinterpret_cast<const uint32_t*>(&v[0]);
+    r.y = *reinterpret_cast<const uint32_t*>(&v[1]);
+    r.z = *reinterpret_cast<const uint32_t*>(&v[2]);
+    r.w = *reinterpret_cast<const uint32_t*>(&v[3]);
+    *reinterpret_cast<uint4*>(p) = r;
+  }
+};
+template <>
+struct Packet<float> {
+  float v[4];
+  static __device__ __forceinline__ Packet load(const float* p) {
+    const float4 r = __ldg(reinterpret_cast<const float4*>(p));
+    Packet o;
+    o.v[0] = r.x;
+    o.v[1] = r.y;
+    o.v[2] = r.z;
+    o.v[3] = r.w;
+    return o;
+  }
+  static __device__ __forceinline__ Packet splat(float f) {
+    Packet o;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o.v[i] = f;
+    return o;
+  }
+  __device__ __forceinline__ void fma(const Packet& a, const Packet& b) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = fmaf(a.v[i], b.v[i], v[i]);
+  }
+  __device__ __forceinline__ void max_ignore_nan(const Packet& a) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = a.v[i] > v[i] ? a.v[i] : v[i];
+  }
+  __device__ __forceinline__ void max_keep_nan(const Packet& a) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = (isnan(a.v[i]) || a.v[i] > v[i]) ? a.v[i] : v[i];
+  }
+  __device__ __forceinline__ void store(float* p) const {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+
+constexpr int kStripW = 4;       // output columns per thread
+constexpr int kStripBlock = 128;
+
+struct StripGeometry {
+  int in_rows, in_cols, out_rows, out_cols, channels, pad_rows, pad_cols, batch;
+  int rows_per_thread, wgroups, hchunks;
+};
+
+// MODE 0: depthwise 3x3 (needs Packet::fma); MODE 1: max ignoring NaN; MODE 2: max keeping NaN.
+template <typename T, int ST, int MODE>
+__global__ void __launch_bounds__(kStripBlock)
+    window3_strip_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, StripGeometry g,
+                         size_t n_threads) {
+  using P = Packet<T>;
+  constexpr int V = 16 / sizeof(T);
+  constexpr int NIN = (kStripW - 1) * ST + 3;
+  const size_t idx = (size_t)blockIdx.x * kStripBlock + threadIdx.x;
+  if (idx >= n_threads) return;
+  const int cvecs = g.channels / V;
+  const int cv = (int)(idx % cvecs);
+  size_t t = idx / cvecs;
+  const int wg = (int)(t % g.wgroups);
+  t /= g.wgroups;
+  const int hc = (int)(t % g.hchunks);
+  const int n = (int)(t / g.hchunks);
+  const int c = cv * V;
+  const int ow0 = wg * kStripW, iw0 = ow0 * ST - g.pad_cols;
+  const int oh_begin = hc * g.rows_per_thread, oh_end = min(oh_begin + g.rows_per_thread, g.out_rows);
+  const T* xn = x + (size_t)n * g.in_rows * g.in_cols * g.channels + c;
+  T* yn = y + (size_t)n * g.out_rows * g.out_cols * g.channels + c;
+  const float fill = MODE == 0 ? 0.f : lowest_of<T>();
+
+  P wt[3][3];
+  if (MODE == 0) {
+#pragma unroll
+    for (int r = 0; r < 3; ++r)
+#pragma unroll
+      for (int s2 = 0; s2 < 3; ++s2) wt[r][s2] = P::load(w + (size_t)(r * 3 + s2) * g.channels + c);
+  }
+  auto load_row = [&](P (&row)[NIN], int ih) {
+    const bool row_ok = ih >= 0 && ih < g.in_rows;
+    const T* xr = xn + (size_t)ih * g.in_cols * g.channels;
+#pragma unroll
+    for (int j = 0; j < NIN; ++j) {
+      const int iw = iw0 + j;
+      row[j] = (row_ok && iw >= 0 && iw < g.in_cols) ? P::load(xr + (size_t)iw * g.channels) : P::splat(fill);
+    }
+  };
+  P ra[NIN], rb[NIN], rc[NIN];
+  int ih0 = oh_begin * ST - g.pad_rows;
+  load_row(ra, ih0);
+  load_row(rb, ih0 + 1);
+  load_row(rc, ih0 + 2);
+  for (int oh = oh_begin; oh < oh_end; ++oh) {
+    // stride 1: the one new row of the next step is requested before this step's arithmetic, so
+    // that its latency hides behind it
+    P rn[ST == 1 ? NIN : 1];
+    if (ST == 1 && oh + 1 < oh_end) load_row(reinterpret_cast<P(&)[NIN]>(rn), ih0 + 3);
+#pragma unroll
+    for (int o = 0; o < kStripW; ++o) {
+      P acc = P::splat(fill);
+#pragma unroll
+      for (int s2 = 0; s2 < 3; ++s2) {
+        if constexpr (MODE == 0) {
+          acc.fma(ra[o * ST + s2], wt[0][s2]);
+          acc.fma(rb[o * ST + s2], wt[1][s2]);
+          acc.fma(rc[o * ST + s2], wt[2][s2]);
+        } else if constexpr (MODE == 1) {
+          acc.max_ignore_nan(ra[o * ST + s2]);
+          acc.max_ignore_nan(rb[o * ST + s2]);
+          acc.max_ignore_nan(rc[o * ST + s2]);
+        } else {
+          acc.max_keep_nan(ra[o * ST + s2]);
+          acc.max_keep_nan(rb[o * ST + s2]);
+          acc.max_keep_nan(rc[o * ST + s2]);
+        }
+      }
+      if (ow0 + o < g.out_cols) acc.store(yn + ((size_t)oh * g.out_cols + ow0 + o) * g.channels);
+    }
+    if (oh + 1 < oh_end) {
+      ih0 += ST;
+      if (ST == 1) {
+#pragma unroll
+        for (int j = 0; j < NIN; ++j) {
+          ra[j] = rb[j];
+          rb[j] = rc[j];
+          rc[j] = rn[j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < NIN; ++j) ra[j] = rc[j];
+        load_row(rb, ih0 + 1);
+        load_row(rc, ih0 + 2);
+      }
+    }
+  }
+}
+
+// Chooses how many output rows a thread walks: as many as possible while the launch still has
+// enough threads to fill the device.
+template <typename T, int MODE>
+int launch_window3_strip(const T* x, const T* w, T* y, int stride, StripGeometry g, int sms, cudaStream_t s) {
+  constexpr int V = 16 / sizeof(T);
+  g.wgroups = (g.out_cols + kStripW - 1) / kStripW;
+  const size_t per_row_chunk = (size_t)g.batch * g.wgroups * (g.channels / V);
+  const size_t want = (size_t)sms * 1024;
+  int rows = 16;
+  while (rows > 1 && per_row_chunk * ((g.out_rows + rows - 1) / rows) < want) rows >>= 1;
+  g.rows_per_thread = rows;
+  g.hchunks = (g.out_rows + rows - 1) / rows;
+  const size_t n_threads = per_row_chunk * g.hchunks;
+  const size_t blocks = (n_threads + kStripBlock - 1) / kStripBlock;
+  if (blocks > 0x7FFFFFFFull) return -1;
+  if (stride == 1)
+    window3_strip_kernel<T, 1, MODE><<<(unsigned)blocks, kStripBlock, 0, s>>>(x, w, y, g, n_threads);
+  else
+    window3_strip_kernel<T, 2, MODE><<<(unsigned)blocks, kStripBlock, 0, s>>>(x, w, y, g, n_threads);
+  return 0;
+}
+
 // ---- dispatch helpers -------------------------------------------------------------------------
 template <typename F>
 int dispatch_dtype(int dtype, F&& f) {
@@ -462,6 +703,14 @@ int launch_pooling(int op, int direction, int dtype, const void* in, void* out, 
     using T = decltype(tag);
     constexpr int VN = Vec16<T>::N;
     const bool vec = (p.channels % VN == 0) && aligned16(in) && aligned16(out);
+    if (direction == 0 && op != PDNN_POOL_AVERAGE && vec && p.window_rows == 3 && p.window_cols == 3 &&
+        p.stride_rows == p.stride_cols && (p.stride_rows == 1 || p.stride_rows == 2)) {
+      const StripGeometry g{p.in_rows, p.in_cols, p.out_rows, p.out_cols, p.channels, p.pad_rows, p.pad_cols, p.batch, 0, 0, 0};
+      const int r = op == PDNN_POOL_MAX
+                        ? launch_window3_strip<T, 1>(static_cast<const T*>(in), nullptr, static_cast<T*>(out), p.stride_rows, g, sms, s)
+                        : launch_window3_strip<T, 2>(static_cast<const T*>(in), nullptr, static_cast<T*>(out), p.stride_rows, g, sms, s);
+      if (r == 0) return check_launch("pooling (3x3 strips)");
+    }
     const size_t pixels = direction == 0 ? (size_t)p.batch * p.out_rows * p.out_cols
                                          : (size_t)p.batch * p.in_rows * p.in_cols;
     const size_t items = pixels * (p.channels / (vec ? VN : 1));
@@ -606,6 +855,15 @@ int launch_depthwise(int pass, int dtype, const void* in, const void* fil, void*
       }
       if (own) cudaFreeAsync(partial, s);
       return st;
+    }
+    if constexpr (!std::is_same<T, __nv_bfloat16>::value) {
+      if (pass == PDNN_FORWARD && vec && p.window_rows == 3 && p.window_cols == 3 && p.stride_rows == p.stride_cols &&
+          (p.stride_rows == 1 || p.stride_rows == 2)) {
+        const StripGeometry g{p.in_rows, p.in_cols, p.out_rows, p.out_cols, p.channels, p.pad_rows, p.pad_cols, p.batch, 0, 0, 0};
+        if (launch_window3_strip<T, 0>(static_cast<const T*>(in), static_cast<const T*>(fil), static_cast<T*>(out),
+                                       p.stride_rows, g, sms, s) == 0)
+          return check_launch("depthwise conv2d (3x3 strips)");
+      }
     }
     const size_t pixels = pass == PDNN_FORWARD ? (size_t)p.batch * p.out_rows * p.out_cols
                                                : (size_t)p.batch * p.in_rows * p.in_cols;
