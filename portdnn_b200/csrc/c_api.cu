@@ -92,6 +92,13 @@ int run_conv(int pass, int dtype, const void* in, const void* fil, void* out, co
   if (in == nullptr || fil == nullptr || out == nullptr) return fail(PDNN_INVALID_PARAMETER, "conv2d: null tensor");
   if (device_sm_count() <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "conv2d: no sm_100 CUDA device");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The Winograd tags run F(2x2,3x3) when the caller brought the scratch it needs; without it the
+  // implicit-GEMM kernel, which needs none, runs the layer instead of reporting
+  // InsufficientWorkspace (include/portdnn/internal/conv2d/winograd/launch.h:280).
+  if ((algorithm == PDNN_ALGO_WINOGRAD || algorithm == PDNN_ALGO_WINOGRAD_LARGE) &&
+      winograd_applicable(pass, dtype, *p) && ws != nullptr && ws_elems >= winograd_workspace_elems(pass, *p) &&
+      aligned16(ws) && aligned16(in) && aligned16(fil) && aligned16(out))
+    return launch_winograd(pass, dtype, in, fil, out, *p, epi, ws, ws_elems, s);
   if (algorithm != PDNN_ALGO_DIRECT && tc_conv_supported(pass, dtype, in, fil, out, *p))
     return tc_conv2d(pass, dtype, in, fil, out, *p, epi, ws, ws_elems, s);
   return launch_direct_conv(pass, dtype, in, fil, out, *p, epi, s);
@@ -131,7 +138,14 @@ int pdnn_conv2d_workspace_size(int pass, int dtype, const PdnnConv2DParams* para
   if (algorithm == PDNN_ALGO_DIRECT) return PDNN_OK;
   // The implicit-GEMM kernels read the tensors in place; only the filter backprop's split
   // reduction wants scratch, and it can do without (it then allocates for the call).
-  const size_t elems = tc_conv_workspace_elems(pass, dtype, *params);
+  size_t elems = tc_conv_workspace_elems(pass, dtype, *params);
+  // Winograd: 16 * (C*K + tiles*C + tiles*K), include/portdnn/conv2d/workspace_size.h:53-73.  It is
+  // reported as recommended, not required: without it the layer still runs (on the implicit GEMM).
+  if ((algorithm == PDNN_ALGO_WINOGRAD || algorithm == PDNN_ALGO_WINOGRAD_LARGE) &&
+      winograd_applicable(pass, dtype, *params)) {
+    const size_t w = winograd_workspace_elems(pass, *params);
+    if (w > elems) elems = w;
+  }
   if (recommended_elems) *recommended_elems = elems;
   return PDNN_OK;
 }

@@ -118,4 +118,10 @@ int launch_scale_blend(int dtype, const void* a, float alpha, const void* b, flo
 int launch_direct_conv(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
                        const PdnnConvEpilogue* epi, cudaStream_t s);
 
+// Winograd F(2x2,3x3) (winograd.cu): forward and input backprop of 3x3 stride-1 layers.
+bool winograd_applicable(int pass, int dtype, const PdnnConv2DParams& p);
+size_t winograd_workspace_elems(int pass, const PdnnConv2DParams& p);
+int launch_winograd(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
+                    const PdnnConvEpilogue* epi, void* ws, size_t ws_elems, cudaStream_t s);
+
 }  // namespace pdnn
