@@ -37,8 +37,25 @@ constexpr int kTileM = 128;
 constexpr int kABytes = kTileM * 128;  // one A stage: 128 rows of 128 bytes
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 227 * 1024;
+constexpr int kBarsPerGroup = 3 * kMaxStages + 4;  // full, empty, ready per stage; accumulator full / empty x 2
+constexpr int kBarBlockBytes = 512;                // barriers of two groups, the resident-B barrier, TMEM slot, abort flag
 
 __device__ unsigned g_error_record[4];
+
+// Optional timeline of CTA 0 (compiled in with -DPDNN_TC_TRACE, for kernel development only):
+// SM clock at a few points of each tile's life, read back with pdnn_debug_trace().
+#ifdef PDNN_TC_TRACE
+constexpr int kTraceTiles = 512, kTraceKinds = 8;
+__device__ long long g_trace[kTraceKinds * kTraceTiles];
+#define PDNN_TRACE(kind, idx)                                                                  \
+  do {                                                                                         \
+    if (blockIdx.x == 0 && (idx) < (unsigned)kTraceTiles) g_trace[(kind) * kTraceTiles + (idx)] = clock64(); \
+  } while (0)
+#else
+#define PDNN_TRACE(kind, idx) \
+  do {                        \
+  } while (0)
+#endif
 
 struct TapEntry {
   short dw, dh, a_map, b_tap;
@@ -78,9 +95,16 @@ struct alignas(64) GemmArgs {
   int vec_ok;  // rows are 16-byte aligned: packed stores allowed
   int tma_store;  // 1: the epilogue stages 128-byte column blocks in shared memory and stores them by TMA
   int cpb;        // output columns per 128-byte block: 64 (16-bit) or 32 (fp32)
-  int nsw;        // staging slices per epilogue warp (2 or 4)
-  int occ2;       // host-side: sized so that two CTAs share an SM
+  int nsw;        // staging slices per epilogue warp (1, 2 or 4)
+  int groups;     // pipelines per CTA (1 or 2; always 1 for the fp32 variant)
+  int acc_bufs;   // accumulator buffers per group (1 or 2)
+  int acc_stride; // TMEM columns between accumulator buffers
+  int bias_smem_bytes;  // size of the CTA's bias copy (fast epilogue only), a multiple of 128
   int epi_fast;   // 1: 16-bit output, alpha 1, bias/ReLU done on packed pairs (see epilogue_tile_tma_fast)
+  // 1: the whole B operand (every column tile, every reduction step) is copied into shared memory
+  // once per CTA and stays there; pipeline stages then carry A tiles only.
+  int b_res;
+  unsigned b_res_bytes;
 };
 
 struct TileCoord {
@@ -216,7 +240,8 @@ struct WarpStore {
 __device__ __forceinline__ void wait_slice_free(const WarpStore& ws, int lane) {
   if (lane == 0) {
     if (ws.nsw == 4) bulk_wait_group_read<3>();
-    else bulk_wait_group_read<1>();
+    else if (ws.nsw == 2) bulk_wait_group_read<1>();
+    else bulk_wait_group_read<0>();
   }
   __syncwarp();
 }
@@ -304,22 +329,30 @@ __device__ __forceinline__ P2 bits_pair(uint32_t v) {
 
 // Converts 32 accumulator columns of one row (four 16-byte chunks, numbered from chunk_base) and
 // writes them into the row's 128 bytes of the staging slice.
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// `bias_s` is the shared-space address of the CTA's copy of the bias vector (0: no bias); the copy
+// is padded with zeros up to a multiple of 64 columns.
 template <typename OutT>
-__device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bool zero, const OutT* bias, int col0,
-                                                   int ext_cols, int act, uint8_t* row_ptr, int row, int chunk_base) {
+__device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bool zero, uint32_t bias_s, int col0,
+                                                   int act, uint8_t* row_ptr, int row, int chunk_base) {
   using P2 = typename Pair<OutT>::type;
   const P2 zero2 = Pair<OutT>::splat(0.f), six2 = Pair<OutT>::splat(6.f);
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     uint4 bv = make_uint4(0u, 0u, 0u, 0u);
-    if (bias != nullptr && col0 + g * 8 + 8 <= ext_cols) bv = __ldg(reinterpret_cast<const uint4*>(bias + col0 + g * 8));
+    if (bias_s != 0u) bv = ld_shared_v4(bias_s + (uint32_t)(col0 + g * 8) * 2u);
     const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
     uint32_t o[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       P2 v = zero ? zero2
                   : Pair<OutT>::pack(__uint_as_float(acc[g * 8 + 2 * i]), __uint_as_float(acc[g * 8 + 2 * i + 1]));
-      if (bias != nullptr) v = __hadd2(v, bits_pair<P2>(bw[i]));
+      if (bias_s != 0u) v = __hadd2(v, bits_pair<P2>(bw[i]));
       if (act != PDNN_ACT_NONE) v = __hmax2(v, zero2);
       if (act == PDNN_ACT_RELU6) v = __hmin2(v, six2);
       o[i] = pair_bits(v);
@@ -336,9 +369,8 @@ __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bo
 template <typename OutT>
 __device__ __forceinline__ void epilogue_tile_tma_fast(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc,
                                                        int lane, bool zero, const WarpStore& ws,
-                                                       uint32_t& store_count) {
-  const OutT* bias = static_cast<const OutT*>(a.bias);
-  const int act = a.act, ext_cols = a.ext_cols;
+                                                       uint32_t& store_count, uint32_t bias_s) {
+  const int act = a.act;
   for (int c0 = 0; c0 < a.bn; c0 += 64, ++store_count) {
     const uint32_t slot = store_count & (uint32_t)(ws.nsw - 1);
     uint32_t acc0[32], acc1[32];
@@ -348,9 +380,11 @@ __device__ __forceinline__ void epilogue_tile_tma_fast(const GemmArgs& a, const 
     }
     wait_slice_free(ws, lane);
     if (!zero) tmem_wait_ld();
+    if (threadIdx.x == 64) PDNN_TRACE(6, store_count);
     uint8_t* row_ptr = ws.buf + slot * 4096u + (size_t)lane * 128;
-    fast_convert_store<OutT>(acc0, zero, bias, t.nf0 + c0, ext_cols, act, row_ptr, lane, 0);
-    fast_convert_store<OutT>(acc1, zero, bias, t.nf0 + c0 + 32, ext_cols, act, row_ptr, lane, 4);
+    fast_convert_store<OutT>(acc0, zero, bias_s, t.nf0 + c0, act, row_ptr, lane, 0);
+    fast_convert_store<OutT>(acc1, zero, bias_s, t.nf0 + c0 + 32, act, row_ptr, lane, 4);
+    if (threadIdx.x == 64) PDNN_TRACE(7, store_count);
     issue_slice_store(a, t, ws, slot, t.nf0 + c0, lane);
   }
 }
@@ -358,45 +392,84 @@ __device__ __forceinline__ void epilogue_tile_tma_fast(const GemmArgs& a, const 
 // EPI selects the epilogue compiled into the instantiation: 0 = direct stores from registers,
 // 1 = staged TMA store with fp32 arithmetic, 2 = staged TMA store with packed 16-bit arithmetic.
 // One epilogue per instantiation keeps each kernel's register allocation tight.
+//
+// A CTA runs up to two independent pipelines ("groups") side by side, each with its own TMA
+// producer warp, MMA issuer warp, four epilogue warps, ring of stages, accumulators in TMEM and
+// staging slices; group g takes every second tile of the CTA.  One thread can issue a
+// tcgen05.mma only every ~130 cycles once the barrier wait, the commit and the loop around four
+// MMAs are counted, which is two to three times the time the tensor pipe needs for a 128 x 64 or
+// 128 x 128 MMA; two issuers keep the pipe busy, and two epilogue teams halve the time a tile's
+// accumulator waits to be drained.  The resident B tiles, the bias copy and the TMEM allocation
+// are shared.  The fp32 (3xTF32) variant runs one group plus the four hi/lo split warps.
+//
+//   warp 6g + 0      producer of group g
+//   warp 6g + 1      MMA issuer of group g (warp 1 also owns the TMEM allocation)
+//   warps 6g + 2..5  epilogue of group g (warp % 4 selects the TMEM lane quarter)
+//   SPLIT: warps 6..9 are the hi/lo split warps of the only group
 template <bool SPLIT, int EPI, typename OutT>
-__global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const __grid_constant__ GemmArgs args) {
+__global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const __grid_constant__ GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const GemmArgs& a = args;
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
   uint8_t* smem = smem_raw + (base - raw_addr);
 
+  constexpr int kMaxGroups = SPLIT ? 1 : 2;
+  const int groups = SPLIT ? 1 : a.groups;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = SPLIT ? 0 : warp / 6;
+  const int role = SPLIT ? warp : warp - grp * 6;  // 0 producer, 1 issuer, 2..5 epilogue, 6..9 split (SPLIT)
+
   const uint32_t b_bytes = (uint32_t)a.bn * 128u;
   const uint32_t part_bytes = kABytes + b_bytes;              // one A tile + one B tile
-  const uint32_t stage_bytes = SPLIT ? 2u * part_bytes : part_bytes;
-  const int S = a.stages;
-  // two 16 KB staging tiles for the TMA-store epilogue, then the barrier block
-  const uint32_t staging_base = base + (uint32_t)S * stage_bytes;
-  const uint32_t staging_bytes = a.tma_store ? (uint32_t)a.nsw * 4u * 4096u : 0u;  // 4 warps x nsw slices
-  uint8_t* bar_mem = smem + (size_t)S * stage_bytes + staging_bytes;
-  const uint32_t bar_base = staging_base + staging_bytes;
-  auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(kMaxStages + s); };
-  auto ready_bar = [&](int s) { return bar_base + 8u * (uint32_t)(2 * kMaxStages + s); };
-  auto acc_full_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * kMaxStages + b); };
-  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (uint32_t)(3 * kMaxStages + 2 + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 8 * (3 * kMaxStages + 8));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * (3 * kMaxStages + 8) + 8);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool b_res = !SPLIT && a.b_res != 0;
+  const uint32_t res_bytes = b_res ? a.b_res_bytes : 0u;      // resident B tiles come first
+  const uint32_t stage_bytes = SPLIT ? 2u * part_bytes : (b_res ? (uint32_t)kABytes : part_bytes);
+  const int S = a.stages;                                     // stages per group
+  const uint32_t ring_bytes = (uint32_t)S * stage_bytes;
+  const uint32_t ring_base = base + res_bytes + (uint32_t)grp * ring_bytes;  // this group's ring
+  uint8_t* ring_mem = smem + res_bytes + (size_t)grp * ring_bytes;
+  // staging slices for the TMA-store epilogue (per group: 4 warps x nsw slices), then the barrier
+  // block, then the bias copy
+  const uint32_t group_staging = a.tma_store ? (uint32_t)a.nsw * 4u * 4096u : 0u;
+  const uint32_t staging_off = res_bytes + (uint32_t)groups * ring_bytes;
+  const uint32_t bar_off = staging_off + (uint32_t)groups * group_staging;
+  uint8_t* bar_mem = smem + bar_off;
+  const uint32_t bar_base = base + bar_off;
+  auto gbar = [&](int g, int i) { return bar_base + 8u * (uint32_t)(g * kBarsPerGroup + i); };
+  auto full_bar = [&](int s) { return gbar(grp, s); };
+  auto empty_bar = [&](int s) { return gbar(grp, kMaxStages + s); };
+  auto ready_bar = [&](int s) { return gbar(grp, 2 * kMaxStages + s); };
+  auto acc_full_bar = [&](int b) { return gbar(grp, 3 * kMaxStages + b); };
+  auto acc_empty_bar = [&](int b) { return gbar(grp, 3 * kMaxStages + 2 + b); };
+  const uint32_t bres_bar = bar_base + 8u * (uint32_t)(2 * kBarsPerGroup);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 8 * (2 * kBarsPerGroup + 1));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * (2 * kBarsPerGroup + 1) + 4);
+  const uint32_t bias_s = (EPI == 2 && a.bias != nullptr) ? bar_base + kBarBlockBytes : 0u;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-      mbar_init(ready_bar(s), 4);
+    for (int g = 0; g < kMaxGroups; ++g) {
+      for (int s = 0; s < kMaxStages; ++s) {
+        mbar_init(gbar(g, s), 1);
+        mbar_init(gbar(g, kMaxStages + s), 1);
+        mbar_init(gbar(g, 2 * kMaxStages + s), 4);
+      }
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(gbar(g, 3 * kMaxStages + b), 1);
+        mbar_init(gbar(g, 3 * kMaxStages + 2 + b), 4);
+      }
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(acc_full_bar(b), 1);
-      mbar_init(acc_empty_bar(b), 4);
-    }
+    mbar_init(bres_bar, 1);
     *abort_flag = 0;
     fence_barrier_init();
+  }
+  if (EPI == 2 && a.bias != nullptr) {
+    // the CTA's copy of the bias vector, zero beyond the last column
+    const OutT* bias = static_cast<const OutT*>(a.bias);
+    uint4* dst = reinterpret_cast<uint4*>(bar_mem + kBarBlockBytes);
+    const int chunks = a.bias_smem_bytes >> 4;
+    for (int i = threadIdx.x; i < chunks; i += blockDim.x)
+      dst[i] = (i * 8 + 8 <= a.ext_cols) ? __ldg(reinterpret_cast<const uint4*>(bias) + i) : make_uint4(0u, 0u, 0u, 0u);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), (uint32_t)a.tmem_cols);
@@ -406,12 +479,19 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t acc_stride = (uint32_t)a.tmem_cols / 2u;
+  // accumulator buffer b of group g starts at column (g * acc_bufs + b) * acc_stride
+  const uint32_t acc_bufs = (uint32_t)a.acc_bufs, acc_stride = (uint32_t)a.acc_stride;
+  const uint32_t grp_tmem = tmem_base + (uint32_t)grp * acc_bufs * acc_stride;
 
   const int total_tiles = a.a_mn ? a.n_tiles * a.tiles_w * a.num_taps * a.splits
                                  : a.n_tiles * a.tiles_w * a.tiles_h * a.tiles_n;
+  const int first_tile = (int)blockIdx.x + grp * (int)gridDim.x;
+  const int tile_step = groups * (int)gridDim.x;
+  const bool active = grp < groups;
 
-  if (warp == 0) {
+  if (!active) {
+    // a group that is switched off has nothing to do
+  } else if (role == 0) {
     // ------------------------------- TMA producer ------------------------------------------
     // One thread; the loop body is kept to a wait, an expect_tx and the copies, with all
     // coordinates advanced incrementally: a lone thread issues an instruction every few cycles
@@ -420,8 +500,33 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
       for (int i = 0; i < 4; ++i) prefetch_tensormap(&a.a_map[i]);
       prefetch_tensormap(&a.b_map);
       const int epr = a.epr, b_mode = a.b_mode, b_boxes = a.b_boxes, a_boxes = a.a_boxes, cblocks = a.cblocks;
-      const uint32_t a_box_bytes = a.a_box_bytes, b_box_bytes = a.b_box_bytes, tx_bytes = kABytes + b_bytes;
+      const uint32_t a_box_bytes = a.a_box_bytes, b_box_bytes = a.b_box_bytes,
+                     tx_bytes = b_res ? (uint32_t)kABytes : kABytes + b_bytes;
       const CUtensorMap* bmap = &a.b_map;
+      // one B tile of a forward-style GEMM (a_mn == 0): reduction block kc of tap btap, columns from nf0
+      auto load_b = [&](uint32_t sb, uint32_t fb, int kc, int nf0, int btap) {
+        switch (b_mode) {
+          case B_MN_3X: tma_load_4d(sb, bmap, fb, 0, kc, nf0 / epr, btap); break;
+          case B_MN_3:
+            for (int j = 0; j < b_boxes; ++j)
+              tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, nf0 + j * epr, kc, btap, 0);
+            break;
+          case B_K_3: tma_load_4d(sb, bmap, fb, kc, nf0, btap, 0); break;
+          case B_K_FHWC: tma_load_4d(sb, bmap, fb, kc, btap, nf0, 0); break;
+          default:  // B_MN_FHWC
+            for (int j = 0; j < b_boxes; ++j)
+              tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, nf0 + j * epr, btap, kc, 0);
+            break;
+        }
+      };
+      if (b_res && grp == 0 && (int)blockIdx.x < total_tiles) {
+        mbar_arrive_expect_tx(bres_bar, res_bytes);
+        uint32_t dst = base;
+        for (int nt = 0; nt < a.n_tiles; ++nt)
+          for (int tap = 0; tap < a.num_taps; ++tap)
+            for (int cb = 0, kc = 0; cb < cblocks; ++cb, kc += epr, dst += b_bytes)
+              load_b(dst, bres_bar, kc, nt * a.bn, a.taps[tap].b_tap);
+      }
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -431,8 +536,11 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
           ph ^= 1u;
         }
       };
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      [[maybe_unused]] unsigned ptile = 0;
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
         const TileCoord t = decode_tile(a, tile);
+        if (grp == 0) PDNN_TRACE(0, ptile);
+        ++ptile;
         if (!a.a_mn) {
           for (int tap = 0; tap < a.num_taps && ok; ++tap) {
             const TapEntry e = a.taps[tap];
@@ -446,22 +554,9 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
               }
               const uint32_t fb = full_bar(s);
               mbar_arrive_expect_tx(fb, tx_bytes);
-              const uint32_t sa = base + (uint32_t)s * stage_bytes;
-              const uint32_t sb = sa + kABytes;
+              const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
               tma_load_4d(sa, amap, fb, kc, aw, ah, t.n0);
-              switch (b_mode) {
-                case B_MN_3X: tma_load_4d(sb, bmap, fb, 0, kc, t.nf0 / epr, btap); break;
-                case B_MN_3:
-                  for (int j = 0; j < b_boxes; ++j)
-                    tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, t.nf0 + j * epr, kc, btap, 0);
-                  break;
-                case B_K_3: tma_load_4d(sb, bmap, fb, kc, t.nf0, btap, 0); break;
-                case B_K_FHWC: tma_load_4d(sb, bmap, fb, kc, btap, t.nf0, 0); break;
-                default:  // B_MN_FHWC
-                  for (int j = 0; j < b_boxes; ++j)
-                    tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, t.nf0 + j * epr, btap, kc, 0);
-                  break;
-              }
+              if (!b_res) load_b(sa + kABytes, fb, kc, t.nf0, btap);
               next_stage();
             }
           }
@@ -479,7 +574,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
             }
             const uint32_t fb = full_bar(s);
             mbar_arrive_expect_tx(fb, tx_bytes);
-            const uint32_t sa = base + (uint32_t)s * stage_bytes;
+            const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
             const uint32_t sb = sa + kABytes;
             const int kw = iw * a.tw, kh = ih * a.th, kn = in * a.tn + batch;
             for (int j = 0; j < a_boxes; ++j)
@@ -502,7 +597,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (role == 1) {
     // ------------------------------- MMA issuer ---------------------------------------------
     if (lane == 0) {
       // Descriptor words that do not change: everything but the 14-bit start address.
@@ -512,13 +607,17 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
       const uint32_t lo_off = part_bytes >> 4;
       int s = 0;
       uint32_t ph = 0, tcount = 0;
+      uint32_t buf = 0, aph = 0;  // accumulator buffer of this tile and the parity of its barriers
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+      if (b_res && first_tile < total_tiles) ok = mbar_wait(bres_bar, 0u, abort_flag, g_error_record, 0x600u);
+      const uint32_t res_tile_bytes = (uint32_t)(a.num_taps * a.cblocks) * b_bytes;  // one column tile's B
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++tcount) {
         const TileCoord t = decode_tile(a, tile);
-        const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
         if (!mbar_wait(acc_empty_bar((int)buf), aph ^ 1u, abort_flag, g_error_record, 0x200u + buf)) break;
+        uint32_t res_b = b_res ? base + (uint32_t)(t.nf0 / a.bn) * res_tile_bytes : 0u;
+        if (grp == 0) PDNN_TRACE(1, tcount);
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * acc_stride;
+        const uint32_t d_tmem = grp_tmem + buf * acc_stride;
         uint32_t accumulate = 0u;
         for (int ks = t.ks_begin; ks < t.ks_end; ++ks) {
           if (!mbar_wait(SPLIT ? ready_bar(s) : full_bar(s), ph, abort_flag, g_error_record, 0x300u + (unsigned)s)) {
@@ -526,11 +625,13 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sa = base + (uint32_t)s * stage_bytes;
+          if (grp == 0 && ks == t.ks_begin) PDNN_TRACE(2, tcount);
+          const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
           // start addresses stay below 2^18, so adding to the low word never carries into the
           // neighbouring descriptor field
           uint64_t da = a_desc0 + (uint64_t)(sa >> 4);
-          uint64_t db = b_desc0 + (uint64_t)((sa + kABytes) >> 4);
+          uint64_t db = b_desc0 + (uint64_t)((b_res ? res_b : sa + kABytes) >> 4);
+          res_b += b_bytes;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             if (SPLIT) {
@@ -551,32 +652,39 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
           }
         }
         if (!ok) break;
+        if (grp == 0) PDNN_TRACE(3, tcount);
         if (t.ks_end > t.ks_begin) mma_commit(acc_full_bar((int)buf));
         else mbar_arrive(acc_full_bar((int)buf));  // nothing to accumulate: the epilogue writes zeros
+        if (++buf == acc_bufs) {
+          buf = 0;
+          aph ^= 1u;
+        }
       }
     }
-  } else if (warp < 6) {
+  } else if (role < 6) {
     // ------------------------------- epilogue ------------------------------------------------
     const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
-    const int row = q * 32 + lane;
+    [[maybe_unused]] const int row = q * 32 + lane;
     uint32_t tcount = 0, store_count = 0;
-    const int wslot = warp - 2;  // 0..3: which staging slices this warp owns
+    const int wslot = role - 2;  // 0..3: which staging slices of the group this warp owns
     WarpStore ws;
     ws.nsw = a.nsw;
-    ws.buf = smem + (size_t)S * stage_bytes + (size_t)wslot * (size_t)a.nsw * 4096u;
-    ws.buf_addr = staging_base + (uint32_t)wslot * (uint32_t)a.nsw * 4096u;
+    const uint32_t my_staging = staging_off + (uint32_t)grp * group_staging + (uint32_t)wslot * (uint32_t)a.nsw * 4096u;
+    ws.buf = smem + my_staging;
+    ws.buf_addr = base + my_staging;
     ws.qw = (q * 32) % a.etw;
     ws.qh = ((q * 32) / a.etw) % a.eth;
     ws.qn = (q * 32) / (a.etw * a.eth);
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
+    uint32_t buf = 0, aph = 0;
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++tcount) {
       const TileCoord t = decode_tile(a, tile);
-      const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
       if (!mbar_wait(acc_full_bar((int)buf), aph, abort_flag, g_error_record, 0x400u + buf)) break;
       tc_fence_after_sync();
-      const uint32_t tmem_acc = tmem_base + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
+      if (warp == 2 && lane == 0) PDNN_TRACE(4, tcount);
+      const uint32_t tmem_acc = grp_tmem + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
       const bool zero = !(t.ks_end > t.ks_begin);
       if constexpr (EPI == 2) {
-        epilogue_tile_tma_fast<OutT>(a, t, tmem_acc, lane, zero, ws, store_count);
+        epilogue_tile_tma_fast<OutT>(a, t, tmem_acc, lane, zero, ws, store_count, bias_s);
       } else if constexpr (EPI == 1) {
         epilogue_tile_tma<OutT>(a, t, tmem_acc, lane, zero, ws, store_count);
       } else {
@@ -585,6 +693,11 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar((int)buf));
+      if (warp == 2 && lane == 0) PDNN_TRACE(5, tcount);
+      if (++buf == acc_bufs) {
+        buf = 0;
+        aph ^= 1u;
+      }
     }
     // the staging tiles must not be released while a store is still reading them
     if (EPI != 0 && lane == 0) bulk_wait_group<0>();
@@ -597,15 +710,15 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 192, 1) umma_gemm_kernel(const _
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+    for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
       const TileCoord t = decode_tile(a, tile);
       for (int ks = t.ks_begin; ks < t.ks_end; ++ks) {
         if (!mbar_wait(full_bar(s), ph, abort_flag, g_error_record, 0x500u + (unsigned)s)) {
           ok = false;
           break;
         }
-        uint4* hi = reinterpret_cast<uint4*>(smem + (size_t)s * stage_bytes);
-        uint4* lo = reinterpret_cast<uint4*>(smem + (size_t)s * stage_bytes + part_bytes);
+        uint4* hi = reinterpret_cast<uint4*>(ring_mem + (size_t)s * stage_bytes);
+        uint4* lo = reinterpret_cast<uint4*>(ring_mem + (size_t)s * stage_bytes + part_bytes);
         for (int c = tid; c < chunks; c += 128) {
           uint4 v = hi[c], h, l;
           h.x = v.x & 0xFFFFE000u;
@@ -725,13 +838,32 @@ void choose_box(int total, int W, int H, int N, int* tw, int* th, int* tn) {
     }
 }
 
-// Tiles with a short reduction are bound by the latency of their epilogue chain (TMEM read,
-// convert, stage, store), not by any throughput limit; two CTAs per SM overlap two such chains.
-// That needs at most 256 TMEM columns (bn <= 128) and half the shared memory per CTA.
-// PDNN_TC_OCC2=0/1 overrides the heuristic (for experiments).
-bool want_occ2(int ksteps, int cols) {
+constexpr size_t kMaxResidentB = 128 * 1024;
+
+// PDNN_TC_BRES=0 switches the resident-filter variant off (for experiments).
+bool b_resident_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("PDNN_TC_BRES");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  return on;
+}
+
+// PDNN_TC_GROUPS=1 runs one pipeline per CTA instead of two (for experiments).
+int group_count() {
+  static const int n = [] {
+    const char* e = getenv("PDNN_TC_GROUPS");
+    return e != nullptr && atoi(e) == 1 ? 1 : 2;
+  }();
+  return n;
+}
+
+// Tiles with a short reduction spend most of their time in the epilogue: column tiles of at most
+// 128 leave room for two accumulator buffers per pipeline, so that the next tile's MMAs overlap it.
+// PDNN_TC_NARROW=0/1 overrides the heuristic (for experiments).
+bool want_narrow(int ksteps, int cols) {
   static const int forced = [] {
-    const char* e = getenv("PDNN_TC_OCC2");
+    const char* e = getenv("PDNN_TC_NARROW");
     return e == nullptr ? -1 : atoi(e);
   }();
   if (forced >= 0) return forced != 0;
@@ -739,10 +871,8 @@ bool want_occ2(int ksteps, int cols) {
 }
 
 int pick_bn(long long row_tiles, int cols, int unit, int max_bn, int sms, int ksteps = 1 << 30) {
-  if (want_occ2(ksteps, cols)) {
-    max_bn = std::min(max_bn, 128);
-    sms *= 2;
-  }
+  if (want_narrow(ksteps, cols)) max_bn = std::min(max_bn, 128);
+  sms *= 2;  // two pipelines per CTA work on two tiles at a time
   // cost ~ waves * (bn + fixed overhead); unit: granularity the B loader needs
   int best_bn = unit;
   double best = 1e30;
@@ -825,29 +955,49 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
                      ? 1
                      : 0;
   }
-  const unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (compute_dtype == PDNN_F32 ? 2u : 1u);
-  // Tiles with few reduction steps are bound by their output: give them deeper store staging
-  // and a shallower load pipeline; long reductions get the opposite.
+  const bool split = compute_dtype == PDNN_F32;
+  g.groups = split ? 1 : group_count();
+  g.acc_stride = std::max(32, next_pow2(g.bn));
+  g.acc_bufs = g.groups * 2 * g.acc_stride <= 512 ? 2 : 1;
+  g.tmem_cols = next_pow2(g.groups * g.acc_bufs * g.acc_stride);
+  g.bias_smem_bytes = 0;
+  if (g.epi_fast && g.bias != nullptr) {
+    const int padded = ceil_div(g.n_tiles * g.bn, 64) * 64;
+    if (padded * 2 > 8192) g.epi_fast = 0;  // the general staged epilogue reads the bias from global memory
+    else g.bias_smem_bytes = padded * 2;
+  }
+  unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
   const int ksteps = g.a_mn ? g.slabs_per_split : g.num_taps * g.cblocks;
-  g.nsw = 2;
-  g.occ2 = 0;
-  if (!g.a_mn && compute_dtype != PDNN_F32 && g.tma_store && g.bn <= 128 && want_occ2(ksteps, g.ext_cols)) {
-    // two CTAs per SM: 113 KB each, 2 x 128 TMEM columns each
-    const int budget2 = 113 * 1024 - 2048 - 2 * 4 * 4096;
-    const int st2 = (int)(budget2 / stage);
-    if (st2 >= 2) {
-      g.occ2 = 1;
-      g.stages = std::min(kMaxStages, st2);
-      return true;
+  g.b_res = 0;
+  g.b_res_bytes = 0;
+  const int fixed = 1024 + kBarBlockBytes + g.bias_smem_bytes;
+  auto staging = [&](int nsw) { return g.tma_store ? g.groups * 4 * nsw * 4096 : 0; };
+  // A small filter (all taps, all column tiles) is kept in shared memory for the whole kernel:
+  // the filter tiles are the part of the L2 -> SM traffic that never changes.
+  if (!g.a_mn && !split && g.tma_store && g.b_batch_mul == 0 && b_resident_enabled()) {
+    const size_t res = (size_t)g.n_tiles * ksteps * g.bn * 128u;
+    if (res <= kMaxResidentB && res % 1024 == 0 &&
+        (kSmemBudget - fixed - (int)res - staging(1)) / (g.groups * kABytes) >= 2) {
+      g.b_res = 1;
+      g.b_res_bytes = (unsigned)res;
+      stage = kABytes;
     }
   }
-  if (g.tma_store && ksteps <= 8) {
-    const int stages_deep = (int)((kSmemBudget - 2048 - 4 * 4 * 4096) / stage);
-    if (stages_deep >= std::min(ksteps + 1, 3)) g.nsw = 4;
+  // Staging slices per epilogue warp: a second slice lets a warp convert one 128-byte column
+  // block while the store of the previous one still reads its slice; it is given up when the
+  // load rings would otherwise be shallower than three stages.
+  const int avail = kSmemBudget - fixed - (int)g.b_res_bytes;
+  auto stages_with = [&](int nsw) { return (avail - staging(nsw)) / (g.groups * (int)stage); };
+  g.nsw = stages_with(2) >= 3 ? 2 : 1;
+  g.stages = std::min(kMaxStages, stages_with(g.nsw));
+  if (g.stages < 2 && g.groups == 2) {  // very wide stages: one pipeline with a deeper ring
+    g.groups = 1;
+    g.acc_bufs = 2 * g.acc_stride <= 512 ? 2 : 1;
+    g.tmem_cols = next_pow2(g.acc_bufs * g.acc_stride);
+    g.nsw = stages_with(2) >= 3 ? 2 : 1;
+    g.stages = std::min(kMaxStages, stages_with(g.nsw));
   }
-  const int budget = kSmemBudget - 2048 - (g.tma_store ? g.nsw * 4 * 4096 : 0);
-  g.stages = std::max(2, std::min(kMaxStages, (int)(budget / stage)));
-  return true;
+  return g.stages >= 1;
 }
 
 using GemmKernel = void (*)(const GemmArgs);
@@ -877,12 +1027,13 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
                                  : (long long)g.n_tiles * g.tiles_w * g.tiles_h * g.tiles_n;
   if (total <= 0) return PDNN_OK;
   if (total > 0x7FFFFFFFll) return fail(PDNN_INDEX_EXCEEDED, "tensor-core gemm: too many tiles");
-  const unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
-  // Unless the plan is sized for two CTAs per SM (each then allocates at most 256 of the 512
-  // TMEM columns), ask for at least 120 KB so that CTAs never share an SM: a CTA that cannot get
-  // its TMEM columns would wait for them without a limit.
-  size_t smem = 1024 + (size_t)g.stages * stage + (g.tma_store ? g.nsw * 4 * 4096 : 0) + 512;
-  if (!(g.occ2 && g.tmem_cols <= 256)) smem = std::max<size_t>(smem, 120 * 1024);
+  const unsigned stage = g.b_res ? (unsigned)kABytes : (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
+  // At least 120 KB, so that two CTAs never share an SM: the second one would wait for TMEM
+  // columns the first one holds.
+  size_t smem = 1024 + (size_t)g.b_res_bytes + (size_t)g.groups * g.stages * stage +
+                (g.tma_store ? (size_t)g.groups * g.nsw * 4 * 4096 : 0) + kBarBlockBytes + (size_t)g.bias_smem_bytes;
+  smem = std::max<size_t>(smem, 120 * 1024);
+  if (smem > (size_t)kSmemBudget) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: plan needs %zu bytes of shared memory", smem);
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -899,8 +1050,8 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   GemmKernel kernel = select_kernel(split, epi, g.out_dtype);
   if (kernel == nullptr) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: no kernel for this output type");
   const int sms = device_sm_count();
-  const unsigned grid = (unsigned)std::min<long long>(total, (long long)sms * (g.occ2 ? 2 : 1));
-  kernel<<<grid, split ? 320 : 192, smem, s>>>(g);
+  const unsigned grid = (unsigned)std::min<long long>(total, (long long)sms);
+  kernel<<<grid, split ? 320 : 384, smem, s>>>(g);
   return check_launch("tensor-core gemm");
 }
 
@@ -1807,5 +1958,13 @@ int tc_read_error_record(unsigned out[4], int clear) {
   }
   return PDNN_OK;
 }
+
+#ifdef PDNN_TC_TRACE
+extern "C" int pdnn_debug_trace(long long* out, int words) {
+  cudaDeviceSynchronize();
+  const size_t n = std::min<size_t>((size_t)words, (size_t)kTraceKinds * kTraceTiles) * sizeof(long long);
+  return cudaMemcpyFromSymbol(out, g_trace, n) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 }  // namespace pdnn
