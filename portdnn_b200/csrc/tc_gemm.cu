@@ -57,8 +57,12 @@ __device__ long long g_trace[kTraceKinds * kTraceTiles];
   } while (0)
 #endif
 
+// One reduction step of a forward-style GEMM: which input map, at which pixel offset, against which
+// filter tap.  In halo mode an entry stands for `cnt` taps that differ only by one input row each
+// (dh, dh + 1, ...; filter taps b_tap, b_tap + b_step, ...): their A tiles are overlapping row
+// ranges of ONE copy of th + cnt - 1 input rows.
 struct TapEntry {
-  short dw, dh, a_map, b_tap;
+  short dw, dh, a_map, b_tap, cnt, b_step;
 };
 
 enum BMode { B_MN_3 = 0, B_K_3 = 1, B_K_FHWC = 2, B_MN_FHWC = 3, B_MN_4 = 4, B_K_4 = 5, B_MN_3X = 6 };
@@ -105,47 +109,78 @@ struct alignas(64) GemmArgs {
   // once per CTA and stays there; pipeline stages then carry A tiles only.
   int b_res;
   unsigned b_res_bytes;
+  // 1: halo mode (needs b_res, tn == 1, tw % 8 == 0): a stage holds th + cnt - 1 input rows of tw
+  // pixels and feeds the MMAs of cnt taps; halo_stage_bytes is the stage size.
+  int halo;
+  unsigned halo_stage_bytes;
+  int res_taps;  // filter taps per column tile in the resident copy (halo mode: the sum of cnt)
 };
 
 struct TileCoord {
-  int w0, h0, n0, nf0, tap, split;
+  int w0, h0, n0, nf0, nt, tap, split;  // nt: column-tile index, nf0 = nt * bn
   long long out_off;
   int ks_begin, ks_end;
 };
 
-__device__ __forceinline__ TileCoord decode_tile(const GemmArgs& a, int tile) {
-  TileCoord t;
-  const int nt = tile % a.n_tiles;
-  int r = tile / a.n_tiles;
-  t.nf0 = nt * a.bn;
-  if (!a.a_mn) {
-    const int mw = r % a.tiles_w;
-    r /= a.tiles_w;
-    const int mh = r % a.tiles_h;
-    const int mn = r / a.tiles_h;
-    t.w0 = mw * a.tw;
-    t.h0 = mh * a.th;
-    t.n0 = mn * a.tn;
-    t.tap = 0;
-    t.split = 0;
-    t.out_off = 0;
-    t.ks_begin = 0;
-    t.ks_end = a.num_taps * a.cblocks;
-  } else {
-    const int mt = r % a.tiles_w;
-    r /= a.tiles_w;
-    t.tap = r % a.num_taps;
-    t.split = r / a.num_taps;
-    t.w0 = mt * kTileM;
-    t.h0 = 0;
-    t.n0 = 0;
-    t.out_off = (long long)t.split * a.split_stride + (long long)t.tap * a.tap_stride;
-    const int total = a.slabs_w * a.slabs_h * a.slabs_n;
-    t.ks_begin = a.split_is_batch ? 0 : t.split * a.slabs_per_split;
-    t.ks_end = min(t.ks_begin + a.slabs_per_split, total);
+// Walks the tiles first, first + step, ... of one pipeline without a division per tile: the tile
+// index is kept as four mixed-radix digits (column tile, row-tile column, row-tile row or tap, the
+// rest) and the step is added digit by digit.  A lone thread pays several hundred cycles for the
+// six divisions a direct decode needs, which is a visible gap between two short tiles.
+struct TileWalker {
+  int r0, r1, r2;      // radices of digits 0..2; digit 3 is unbounded
+  int d0, d1, d2, d3;  // digits of the current tile
+  int s0, s1, s2, s3;  // digits of the step
+
+  __device__ __forceinline__ void init(const GemmArgs& a, int first, int step) {
+    r0 = a.n_tiles;
+    r1 = a.tiles_w;
+    r2 = a.a_mn ? a.num_taps : a.tiles_h;
+    d0 = first % r0, first /= r0;
+    d1 = first % r1, first /= r1;
+    d2 = first % r2, d3 = first / r2;
+    s0 = step % r0, step /= r0;
+    s1 = step % r1, step /= r1;
+    s2 = step % r2, s3 = step / r2;
   }
-  return t;
-}
+  __device__ __forceinline__ void advance() {
+    d0 += s0;
+    int c = d0 >= r0 ? 1 : 0;
+    d0 -= c ? r0 : 0;
+    d1 += s1 + c;
+    c = d1 >= r1 ? 1 : 0;
+    d1 -= c ? r1 : 0;
+    d2 += s2 + c;
+    c = d2 >= r2 ? 1 : 0;
+    d2 -= c ? r2 : 0;
+    d3 += s3 + c;
+  }
+  __device__ __forceinline__ TileCoord coord(const GemmArgs& a) const {
+    TileCoord t;
+    t.nt = d0;
+    t.nf0 = d0 * a.bn;
+    if (!a.a_mn) {
+      t.w0 = d1 * a.tw;
+      t.h0 = d2 * a.th;
+      t.n0 = d3 * a.tn;
+      t.tap = 0;
+      t.split = 0;
+      t.out_off = 0;
+      t.ks_begin = 0;
+      t.ks_end = a.num_taps * a.cblocks;
+    } else {
+      t.tap = d2;
+      t.split = d3;
+      t.w0 = d1 * kTileM;
+      t.h0 = 0;
+      t.n0 = 0;
+      t.out_off = (long long)t.split * a.split_stride + (long long)t.tap * a.tap_stride;
+      const int total = a.slabs_w * a.slabs_h * a.slabs_n;
+      t.ks_begin = a.split_is_batch ? 0 : t.split * a.slabs_per_split;
+      t.ks_end = min(t.ks_begin + a.slabs_per_split, total);
+    }
+    return t;
+  }
+};
 
 template <typename OutT, int N>
 __device__ __forceinline__ void store_chunk(const GemmArgs& a, const uint32_t (&acc)[N], bool zero, OutT* row_ptr,
@@ -331,7 +366,9 @@ __device__ __forceinline__ P2 bits_pair(uint32_t v) {
 // writes them into the row's 128 bytes of the staging slice.
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  // not volatile: the bias copy never changes after the start of the kernel, so the loads may be
+  // hoisted and batched freely
+  asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
 
@@ -342,17 +379,18 @@ __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bo
                                                    int act, uint8_t* row_ptr, int row, int chunk_base) {
   using P2 = typename Pair<OutT>::type;
   const P2 zero2 = Pair<OutT>::splat(0.f), six2 = Pair<OutT>::splat(6.f);
+  const bool has_bias = bias_s != 0u;
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     uint4 bv = make_uint4(0u, 0u, 0u, 0u);
-    if (bias_s != 0u) bv = ld_shared_v4(bias_s + (uint32_t)(col0 + g * 8) * 2u);
+    if (has_bias) bv = ld_shared_v4(bias_s + (uint32_t)(col0 + g * 8) * 2u);
     const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
     uint32_t o[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       P2 v = zero ? zero2
                   : Pair<OutT>::pack(__uint_as_float(acc[g * 8 + 2 * i]), __uint_as_float(acc[g * 8 + 2 * i + 1]));
-      if (bias_s != 0u) v = __hadd2(v, bits_pair<P2>(bw[i]));
+      if (has_bias) v = __hadd2(v, bits_pair<P2>(bw[i]));
       if (act != PDNN_ACT_NONE) v = __hmax2(v, zero2);
       if (act == PDNN_ACT_RELU6) v = __hmin2(v, six2);
       o[i] = pair_bits(v);
@@ -424,7 +462,9 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
   const uint32_t part_bytes = kABytes + b_bytes;              // one A tile + one B tile
   const bool b_res = !SPLIT && a.b_res != 0;
   const uint32_t res_bytes = b_res ? a.b_res_bytes : 0u;      // resident B tiles come first
-  const uint32_t stage_bytes = SPLIT ? 2u * part_bytes : (b_res ? (uint32_t)kABytes : part_bytes);
+  const bool halo = !SPLIT && a.halo != 0;
+  const uint32_t stage_bytes =
+      SPLIT ? 2u * part_bytes : (halo ? a.halo_stage_bytes : (b_res ? (uint32_t)kABytes : part_bytes));
   const int S = a.stages;                                     // stages per group
   const uint32_t ring_bytes = (uint32_t)S * stage_bytes;
   const uint32_t ring_base = base + res_bytes + (uint32_t)grp * ring_bytes;  // this group's ring
@@ -523,9 +563,13 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
         mbar_arrive_expect_tx(bres_bar, res_bytes);
         uint32_t dst = base;
         for (int nt = 0; nt < a.n_tiles; ++nt)
-          for (int tap = 0; tap < a.num_taps; ++tap)
-            for (int cb = 0, kc = 0; cb < cblocks; ++cb, kc += epr, dst += b_bytes)
-              load_b(dst, bres_bar, kc, nt * a.bn, a.taps[tap].b_tap);
+          for (int tap = 0; tap < a.num_taps; ++tap) {
+            const TapEntry e = a.taps[tap];
+            const int cnt = halo ? e.cnt : 1;
+            for (int g = 0; g < cnt; ++g)
+              for (int cb = 0, kc = 0; cb < cblocks; ++cb, kc += epr, dst += b_bytes)
+                load_b(dst, bres_bar, kc, nt * a.bn, e.b_tap + g * e.b_step);
+          }
       }
       int s = 0;
       uint32_t ph = 0;
@@ -537,9 +581,10 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
         }
       };
       [[maybe_unused]] unsigned ptile = 0;
-      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
-        const TileCoord t = decode_tile(a, tile);
-        if (grp == 0) PDNN_TRACE(0, ptile);
+      TileWalker walker;
+      walker.init(a, first_tile, tile_step);
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, walker.advance()) {
+        const TileCoord t = walker.coord(a);
         ++ptile;
         if (!a.a_mn) {
           for (int tap = 0; tap < a.num_taps && ok; ++tap) {
@@ -547,13 +592,14 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
             const CUtensorMap* amap = &a.a_map[e.a_map];
             const int aw = t.w0 + e.dw, ah = t.h0 + e.dh;
             const int btap = e.b_tap + t.n0 * a.b_batch_mul;
+            const uint32_t tx = halo ? (uint32_t)(a.th + e.cnt - 1) * (uint32_t)a.tw * 128u : tx_bytes;
             for (int cb = 0, kc = 0; cb < cblocks; ++cb, kc += epr) {
               if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g_error_record, 0x100u + (unsigned)s)) {
                 ok = false;
                 break;
               }
               const uint32_t fb = full_bar(s);
-              mbar_arrive_expect_tx(fb, tx_bytes);
+              mbar_arrive_expect_tx(fb, tx);
               const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
               tma_load_4d(sa, amap, fb, kc, aw, ah, t.n0);
               if (!b_res) load_b(sa + kABytes, fb, kc, t.nf0, btap);
@@ -610,45 +656,83 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       uint32_t buf = 0, aph = 0;  // accumulator buffer of this tile and the parity of its barriers
       bool ok = true;
       if (b_res && first_tile < total_tiles) ok = mbar_wait(bres_bar, 0u, abort_flag, g_error_record, 0x600u);
-      const uint32_t res_tile_bytes = (uint32_t)(a.num_taps * a.cblocks) * b_bytes;  // one column tile's B
-      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++tcount) {
-        const TileCoord t = decode_tile(a, tile);
+      const uint32_t res_tile_bytes = (uint32_t)(a.res_taps * a.cblocks) * b_bytes;  // one column tile's B
+      TileWalker walker;
+      walker.init(a, first_tile, tile_step);
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++tcount, walker.advance()) {
+        if (grp == 0) PDNN_TRACE(0, tcount);
+        const TileCoord t = walker.coord(a);
         if (!mbar_wait(acc_empty_bar((int)buf), aph ^ 1u, abort_flag, g_error_record, 0x200u + buf)) break;
-        uint32_t res_b = b_res ? base + (uint32_t)(t.nf0 / a.bn) * res_tile_bytes : 0u;
+        uint32_t res_b = b_res ? base + (uint32_t)t.nt * res_tile_bytes : 0u;
         if (grp == 0) PDNN_TRACE(1, tcount);
         tc_fence_after_sync();
         const uint32_t d_tmem = grp_tmem + buf * acc_stride;
         uint32_t accumulate = 0u;
-        for (int ks = t.ks_begin; ks < t.ks_end; ++ks) {
-          if (!mbar_wait(SPLIT ? ready_bar(s) : full_bar(s), ph, abort_flag, g_error_record, 0x300u + (unsigned)s)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          if (grp == 0 && ks == t.ks_begin) PDNN_TRACE(2, tcount);
-          const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
-          // start addresses stay below 2^18, so adding to the low word never carries into the
-          // neighbouring descriptor field
-          uint64_t da = a_desc0 + (uint64_t)(sa >> 4);
-          uint64_t db = b_desc0 + (uint64_t)((b_res ? res_b : sa + kABytes) >> 4);
-          res_b += b_bytes;
+        if (!SPLIT && !a.a_mn) {
+          // forward-style GEMM: one stage per (tap entry, reduction block); in halo mode a stage
+          // feeds the MMAs of all cnt taps of its entry
+          const uint32_t halo_row_bytes = (uint32_t)a.tw * 128u;
+          for (int tap = 0; tap < a.num_taps && ok; ++tap) {
+            const int cnt = halo ? a.taps[tap].cnt : 1;
+            for (int cb = 0; cb < a.cblocks; ++cb) {
+              if (!mbar_wait(full_bar(s), ph, abort_flag, g_error_record, 0x300u + (unsigned)s)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+              if (grp == 0 && tap == 0 && cb == 0) PDNN_TRACE(2, tcount);
+              const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
+              for (int g = 0; g < cnt; ++g) {
+                // start addresses stay below 2^18, so adding to the low word never carries into
+                // the neighbouring descriptor field
+                uint64_t da = a_desc0 + (uint64_t)((sa + (uint32_t)g * halo_row_bytes) >> 4);
+                uint64_t db = b_desc0 + (uint64_t)((b_res ? res_b + (uint32_t)(g * a.cblocks + cb) * b_bytes
+                                                          : sa + kABytes) >> 4);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            if (SPLIT) {
-              mma_tf32(d_tmem, da + lo_off, db, idesc, accumulate);
-              mma_tf32(d_tmem, da, db + lo_off, idesc, 1u);
-              mma_tf32(d_tmem, da, db, idesc, 1u);
-            } else {
-              mma_f16(d_tmem, da, db, idesc, accumulate);
+                for (int k = 0; k < 4; ++k) {
+                  mma_f16(d_tmem, da, db, idesc, accumulate);
+                  accumulate = 1u;
+                  da += a_kadv;
+                  db += b_kadv;
+                }
+              }
+              mma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+              if (++s == S) {
+                s = 0;
+                ph ^= 1u;
+              }
             }
-            accumulate = 1u;
-            da += a_kadv;
-            db += b_kadv;
+            res_b += (uint32_t)(cnt * a.cblocks) * b_bytes;
           }
-          mma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
-          if (++s == S) {
-            s = 0;
-            ph ^= 1u;
+        } else {
+          for (int ks = t.ks_begin; ks < t.ks_end; ++ks) {
+            if (!mbar_wait(SPLIT ? ready_bar(s) : full_bar(s), ph, abort_flag, g_error_record, 0x300u + (unsigned)s)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            if (grp == 0 && ks == t.ks_begin) PDNN_TRACE(2, tcount);
+            const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
+            uint64_t da = a_desc0 + (uint64_t)(sa >> 4);
+            uint64_t db = b_desc0 + (uint64_t)((sa + kABytes) >> 4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              if (SPLIT) {
+                mma_tf32(d_tmem, da + lo_off, db, idesc, accumulate);
+                mma_tf32(d_tmem, da, db + lo_off, idesc, 1u);
+                mma_tf32(d_tmem, da, db, idesc, 1u);
+              } else {
+                mma_f16(d_tmem, da, db, idesc, accumulate);
+              }
+              accumulate = 1u;
+              da += a_kadv;
+              db += b_kadv;
+            }
+            mma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+            if (++s == S) {
+              s = 0;
+              ph ^= 1u;
+            }
           }
         }
         if (!ok) break;
@@ -676,8 +760,10 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     ws.qh = ((q * 32) / a.etw) % a.eth;
     ws.qn = (q * 32) / (a.etw * a.eth);
     uint32_t buf = 0, aph = 0;
-    for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++tcount) {
-      const TileCoord t = decode_tile(a, tile);
+    TileWalker walker;
+    walker.init(a, first_tile, tile_step);
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++tcount, walker.advance()) {
+      const TileCoord t = walker.coord(a);
       if (!mbar_wait(acc_full_bar((int)buf), aph, abort_flag, g_error_record, 0x400u + buf)) break;
       tc_fence_after_sync();
       if (warp == 2 && lane == 0) PDNN_TRACE(4, tcount);
@@ -710,8 +796,10 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
-    for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
-      const TileCoord t = decode_tile(a, tile);
+    TileWalker walker;
+    walker.init(a, first_tile, tile_step);
+    for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, walker.advance()) {
+      const TileCoord t = walker.coord(a);
       for (int ks = t.ks_begin; ks < t.ks_end; ++ks) {
         if (!mbar_wait(full_bar(s), ph, abort_flag, g_error_record, 0x500u + (unsigned)s)) {
           ok = false;
@@ -849,6 +937,37 @@ bool b_resident_enabled() {
   return on;
 }
 
+constexpr int kPlanAgain = -2;  // internal: the halo plan does not fit, plan the layer without it
+
+// PDNN_TC_HALO=0 switches the halo variant off (for experiments).
+bool halo_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("PDNN_TC_HALO");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  return on;
+}
+
+// Row-tile box for halo mode: one image (tn == 1), tw a multiple of 8 so that a shift by one tile
+// row is a whole number of 1024-byte swizzle groups.  `rows` is the number of taps that share a
+// copy.  Picks the box that loads the fewest bytes per useful output pixel; returns false if every
+// candidate wastes more than 15% of its rows.
+bool choose_box_halo(int W, int H, int rows, int* tw, int* th) {
+  double best = 1e30;
+  for (int w = 8; w <= kTileM; w <<= 1) {
+    const int h = kTileM / w;
+    const double eff = ((double)W / (ceil_div(W, w) * w)) * ((double)H / (ceil_div(H, h) * h));
+    if (eff < 0.85) continue;
+    const double cost = (double)(h + rows - 1) / h / eff;
+    if (cost < best - 1e-9) {
+      best = cost;
+      *tw = w;
+      *th = h;
+    }
+  }
+  return best < 1e29;
+}
+
 // PDNN_TC_GROUPS=1 runs one pipeline per CTA instead of two (for experiments).
 int group_count() {
   static const int n = [] {
@@ -871,6 +990,12 @@ bool want_narrow(int ksteps, int cols) {
 }
 
 int pick_bn(long long row_tiles, int cols, int unit, int max_bn, int sms, int ksteps = 1 << 30) {
+  static const int forced_bn = [] {
+    const char* e = getenv("PDNN_TC_BN");  // experiments: force the column-tile width where it is legal
+    return e == nullptr ? 0 : atoi(e);
+  }();
+  if (forced_bn > 0 && forced_bn <= max_bn && forced_bn % unit == 0 && forced_bn % 64 == 0 && cols >= forced_bn)
+    return forced_bn;
   if (want_narrow(ksteps, cols)) max_bn = std::min(max_bn, 128);
   sms *= 2;  // two pipelines per CTA work on two tiles at a time
   // cost ~ waves * (bn + fixed overhead); unit: granularity the B loader needs
@@ -967,7 +1092,9 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
     else g.bias_smem_bytes = padded * 2;
   }
   unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
-  const int ksteps = g.a_mn ? g.slabs_per_split : g.num_taps * g.cblocks;
+  int ksteps = g.a_mn ? g.slabs_per_split : g.num_taps * g.cblocks;
+  if (!g.halo) g.res_taps = g.num_taps;
+  else ksteps = g.res_taps * g.cblocks;
   g.b_res = 0;
   g.b_res_bytes = 0;
   const int fixed = 1024 + kBarBlockBytes + g.bias_smem_bytes;
@@ -976,13 +1103,15 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   // the filter tiles are the part of the L2 -> SM traffic that never changes.
   if (!g.a_mn && !split && g.tma_store && g.b_batch_mul == 0 && b_resident_enabled()) {
     const size_t res = (size_t)g.n_tiles * ksteps * g.bn * 128u;
+    const int a_stage = g.halo ? (int)g.halo_stage_bytes : kABytes;
     if (res <= kMaxResidentB && res % 1024 == 0 &&
-        (kSmemBudget - fixed - (int)res - staging(1)) / (g.groups * kABytes) >= 2) {
+        (kSmemBudget - fixed - (int)res - staging(1)) / (g.groups * a_stage) >= 2) {
       g.b_res = 1;
       g.b_res_bytes = (unsigned)res;
-      stage = kABytes;
+      stage = (unsigned)a_stage;
     }
   }
+  if (g.halo && !g.b_res) return false;  // the caller plans the layer again without the halo
   // Staging slices per epilogue warp: a second slice lets a warp convert one 128-byte column
   // block while the store of the previous one still reads its slice; it is given up when the
   // load rings would otherwise be shallower than three stages.
@@ -1027,7 +1156,8 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
                                  : (long long)g.n_tiles * g.tiles_w * g.tiles_h * g.tiles_n;
   if (total <= 0) return PDNN_OK;
   if (total > 0x7FFFFFFFll) return fail(PDNN_INDEX_EXCEEDED, "tensor-core gemm: too many tiles");
-  const unsigned stage = g.b_res ? (unsigned)kABytes : (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
+  const unsigned stage = g.halo ? g.halo_stage_bytes
+                                 : g.b_res ? (unsigned)kABytes : (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
   // At least 120 KB, so that two CTAs never share an SM: the second one would wait for TMEM
   // columns the first one holds.
   size_t smem = 1024 + (size_t)g.b_res_bytes + (size_t)g.groups * g.stages * stage +
@@ -1117,7 +1247,7 @@ int finish_forward(GemmArgs& g, int dtype, void* y, const PdnnConv2DParams& p, c
   const uint64_t od[4] = {(uint64_t)p.features, (uint64_t)p.out_cols, (uint64_t)p.out_rows, (uint64_t)p.batch};
   const uint64_t os[3] = {(uint64_t)p.features * es, (uint64_t)p.out_cols * p.features * es,
                           (uint64_t)p.out_rows * p.out_cols * p.features * es};
-  if (!setup_store(g, dtype, od, os)) return PDNN_INVALID_PARAMETER;
+  if (!setup_store(g, dtype, od, os)) return g.halo ? kPlanAgain : PDNN_INVALID_PARAMETER;
   return launch_gemm(g, dtype, s);
 }
 
@@ -1191,7 +1321,7 @@ SmallCPlan plan_small_c(int dtype, const PdnnConv2DParams& p) {
 // Returns PDNN_OK, an error, or -1 if the tensor maps could not be encoded (the caller then uses
 // the direct kernel).
 int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const PdnnConv2DParams& p,
-                         const PdnnConvEpilogue* epi, void* ws, size_t ws_elems, cudaStream_t s) {
+                         const PdnnConvEpilogue* epi, void* ws, size_t ws_elems, cudaStream_t s, bool try_halo = true) {
   const size_t es = dtype_size(dtype);
   const int sms = device_sm_count();
   const int epr = dtype == PDNN_F32 ? 32 : 64;
@@ -1215,7 +1345,19 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
   GemmArgs g;
   std::memset(&g, 0, sizeof(g));
   g.a_mn = 0;
-  choose_box(kTileM, p.out_cols, p.out_rows, p.batch, &g.tw, &g.th, &g.tn);
+  // Filter rows of the same input-row parity read overlapping input rows: in halo mode each
+  // parity class is one reduction step over one copy.
+  const int rows_per_class = ceil_div(p.window_rows, p.stride_rows);
+  int hw = 0, hh = 0;
+  const bool halo = try_halo && halo_enabled() && dtype != PDNN_F32 && rows_per_class >= 2 &&
+                    p.window_rows >= p.stride_rows && choose_box_halo(p.out_cols, p.out_rows, rows_per_class, &hw, &hh);
+  if (halo) {
+    g.tw = hw;
+    g.th = hh;
+    g.tn = 1;
+  } else {
+    choose_box(kTileM, p.out_cols, p.out_rows, p.batch, &g.tw, &g.th, &g.tn);
+  }
   g.etw = g.tw;
   g.eth = g.th;
   g.etn = g.tn;
@@ -1230,16 +1372,31 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
     const int Hq = ceil_div(sp.Hp - q, p.stride_rows);
     const uint64_t dims[4] = {(uint64_t)epr, (uint64_t)p.out_cols, (uint64_t)std::max(Hq, 1), (uint64_t)p.batch};
     const uint64_t st[3] = {(uint64_t)p.stride_cols * 16, (uint64_t)p.stride_rows * row_pitch, (uint64_t)sp.Hp * row_pitch};
-    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)g.th, (uint32_t)g.tn};
+    // filter rows q, q + stride, ... read this parity class
+    const int cnt = (p.window_rows - q + p.stride_rows - 1) / p.stride_rows;
+    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)(halo ? g.th + cnt - 1 : g.th), (uint32_t)g.tn};
     if (!make_map(&g.a_map[q], dtype, false, xp + (size_t)q * row_pitch, dims, st, box)) {
       release();
       return -1;
     }
   }
   for (int q = p.stride_rows; q < 4; ++q) g.a_map[q] = g.a_map[0];
-  for (int r = 0; r < p.window_rows; ++r)
-    g.taps[r] = TapEntry{0, (short)(r / p.stride_rows), (short)(r % p.stride_rows), (short)r};
-  g.num_taps = p.window_rows;
+  if (halo) {
+    g.halo = 1;
+    g.res_taps = p.window_rows;
+    unsigned widest = 0;
+    for (int q = 0; q < p.stride_rows; ++q) {
+      const int cnt = (p.window_rows - q + p.stride_rows - 1) / p.stride_rows;
+      g.taps[q] = TapEntry{0, 0, (short)q, (short)q, (short)cnt, (short)p.stride_rows};
+      widest = std::max(widest, (unsigned)(g.tw * (g.th + cnt - 1) * 128));
+    }
+    g.num_taps = p.stride_rows;
+    g.halo_stage_bytes = (widest + 1023u) & ~1023u;
+  } else {
+    for (int r = 0; r < p.window_rows; ++r)
+      g.taps[r] = TapEntry{0, (short)(r / p.stride_rows), (short)(r % p.stride_rows), (short)r, 1, 0};
+    g.num_taps = p.window_rows;
+  }
   g.cblocks = 1;
   {
     g.b_mode = B_MN_3;
@@ -1272,11 +1429,12 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
   count_launch();
   if (st == PDNN_OK) st = finish_forward(g, dtype, y, p, epi, s);
   release();
+  if (st == kPlanAgain) return conv_forward_small_c(dtype, x, w, y, p, epi, ws, ws_elems, s, false);
   return st;
 }
 
 int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnConv2DParams& p,
-                 const PdnnConvEpilogue* epi, cudaStream_t s) {
+                 const PdnnConvEpilogue* epi, cudaStream_t s, bool try_halo = true) {
   GemmArgs g;
   std::memset(&g, 0, sizeof(g));
   const size_t es = dtype_size(dtype);
@@ -1284,7 +1442,22 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   g.a_mn = 0;
   const bool hwcf = p.filter_format == 0;
   const int epr = dtype == PDNN_F32 ? 32 : 64;
-  choose_box(kTileM, p.out_cols, p.out_rows, p.batch, &g.tw, &g.th, &g.tn);
+  // Stride-1 windows of two or more rows: the taps of one window column read overlapping input
+  // rows, so each column becomes one reduction step over one copy (halo mode), provided the whole
+  // filter can stay in shared memory.
+  int hw = 0, hh = 0;
+  const bool halo = try_halo && halo_enabled() && dtype != PDNN_F32 && p.stride_rows == 1 && p.stride_cols == 1 &&
+                    p.window_rows >= 2 &&
+                    (size_t)p.window_rows * p.window_cols * ceil_div(p.channels, epr) * 128u *
+                            (size_t)(ceil_div(p.features, 64) * 64) <= kMaxResidentB &&
+                    choose_box_halo(p.out_cols, p.out_rows, p.window_rows, &hw, &hh);
+  if (halo) {
+    g.tw = hw;
+    g.th = hh;
+    g.tn = 1;
+  } else {
+    choose_box(kTileM, p.out_cols, p.out_rows, p.batch, &g.tw, &g.th, &g.tn);
+  }
   g.etw = g.tw;
   g.eth = g.th;
   g.etn = g.tn;
@@ -1296,20 +1469,32 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
                  p.window_rows * p.window_cols * ceil_div(p.channels, epr));
   g.n_tiles = ceil_div(p.features, g.bn);
   set_operand_layout(g, dtype, hwcf ? 1 : 0);
-  const uint32_t abox[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)g.th, (uint32_t)g.tn};
+  const uint32_t abox[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)(halo ? g.th + p.window_rows - 1 : g.th),
+                            (uint32_t)g.tn};
   if (!make_parity_maps(g, dtype, false, x, p, abox)) return PDNN_INVALID_PARAMETER;
   // taps
   int nt = 0;
-  for (int r = 0; r < p.window_rows; ++r)
-    for (int c = 0; c < p.window_cols; ++c) {
-      const int hh = r - p.pad_rows, ww = c - p.pad_cols;
-      TapEntry e;
-      e.dh = (short)floor_div(hh, p.stride_rows);
-      e.dw = (short)floor_div(ww, p.stride_cols);
-      e.a_map = (short)(pos_mod(hh, p.stride_rows) * p.stride_cols + pos_mod(ww, p.stride_cols));
-      e.b_tap = (short)(r * p.window_cols + c);
-      g.taps[nt++] = e;
-    }
+  if (halo) {
+    g.halo = 1;
+    g.res_taps = p.window_rows * p.window_cols;
+    g.halo_stage_bytes = ((unsigned)(g.tw * (g.th + p.window_rows - 1) * 128) + 1023u) & ~1023u;
+    for (int c = 0; c < p.window_cols; ++c)  // window column c: rows 0 .. R-1 of the filter, taps c, c + S, ...
+      g.taps[nt++] = TapEntry{(short)(c - p.pad_cols), (short)(-p.pad_rows), 0, (short)c, (short)p.window_rows,
+                              (short)p.window_cols};
+  } else {
+    for (int r = 0; r < p.window_rows; ++r)
+      for (int c = 0; c < p.window_cols; ++c) {
+        const int hh = r - p.pad_rows, ww = c - p.pad_cols;
+        TapEntry e;
+        e.dh = (short)floor_div(hh, p.stride_rows);
+        e.dw = (short)floor_div(ww, p.stride_cols);
+        e.a_map = (short)(pos_mod(hh, p.stride_rows) * p.stride_cols + pos_mod(ww, p.stride_cols));
+        e.b_tap = (short)(r * p.window_cols + c);
+        e.cnt = 1;
+        e.b_step = 0;
+        g.taps[nt++] = e;
+      }
+  }
   g.num_taps = nt;
   g.cblocks = ceil_div(p.channels, epr);
   const uint64_t taps = (uint64_t)p.window_rows * p.window_cols;
@@ -1336,7 +1521,9 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     const uint32_t box[4] = {(uint32_t)epr, 1, (uint32_t)g.bn, 1};
     if (!make_map(&g.b_map, dtype, false, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
   }
-  return finish_forward(g, dtype, y, p, epi, s);
+  const int status = finish_forward(g, dtype, y, p, epi, s);
+  if (status == kPlanAgain) return conv_forward(dtype, x, w, y, p, epi, s, false);
+  return status;
 }
 
 int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, const PdnnConv2DParams& p,
