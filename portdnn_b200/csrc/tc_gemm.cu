@@ -106,7 +106,9 @@ struct alignas(64) GemmArgs {
   int bias_smem_bytes;  // size of the CTA's bias copy (fast epilogue only), a multiple of 128
   int epi_fast;   // 1: 16-bit output, alpha 1, bias/ReLU done on packed pairs (see epilogue_tile_tma_fast)
   // 1: the whole B operand (every column tile, every reduction step) is copied into shared memory
-  // once per CTA and stays there; pipeline stages then carry A tiles only.
+  // once per CTA and stays there; pipeline stages then carry A tiles only.  2: the same for the one
+  // column tile the CTA works on (the grid is then a multiple of n_tiles, so that the tiles
+  // blockIdx.x, blockIdx.x + gridDim.x, ... all share their column tile).
   int b_res;
   unsigned b_res_bytes;
   // 1: halo mode (needs b_res, tn == 1, tw % 8 == 0): a stage holds th + cnt - 1 input rows of tw
@@ -562,7 +564,9 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       if (b_res && grp == 0 && (int)blockIdx.x < total_tiles) {
         mbar_arrive_expect_tx(bres_bar, res_bytes);
         uint32_t dst = base;
-        for (int nt = 0; nt < a.n_tiles; ++nt)
+        const int nt_begin = a.b_res == 2 ? (int)blockIdx.x % a.n_tiles : 0;
+        const int nt_end = a.b_res == 2 ? nt_begin + 1 : a.n_tiles;
+        for (int nt = nt_begin; nt < nt_end; ++nt)
           for (int tap = 0; tap < a.num_taps; ++tap) {
             const TapEntry e = a.taps[tap];
             const int cnt = halo ? e.cnt : 1;
@@ -663,7 +667,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
         if (grp == 0) PDNN_TRACE(0, tcount);
         const TileCoord t = walker.coord(a);
         if (!mbar_wait(acc_empty_bar((int)buf), aph ^ 1u, abort_flag, g_error_record, 0x200u + buf)) break;
-        uint32_t res_b = b_res ? base + (uint32_t)t.nt * res_tile_bytes : 0u;
+        uint32_t res_b = a.b_res == 1 ? base + (uint32_t)t.nt * res_tile_bytes : base;
         if (grp == 0) PDNN_TRACE(1, tcount);
         tc_fence_after_sync();
         const uint32_t d_tmem = grp_tmem + buf * acc_stride;
@@ -1102,12 +1106,19 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   // A small filter (all taps, all column tiles) is kept in shared memory for the whole kernel:
   // the filter tiles are the part of the L2 -> SM traffic that never changes.
   if (!g.a_mn && !split && g.tma_store && g.b_batch_mul == 0 && b_resident_enabled()) {
-    const size_t res = (size_t)g.n_tiles * ksteps * g.bn * 128u;
+    const size_t res_tile = (size_t)ksteps * g.bn * 128u, res_all = res_tile * g.n_tiles;
     const int a_stage = g.halo ? (int)g.halo_stage_bytes : kABytes;
-    if (res <= kMaxResidentB && res % 1024 == 0 &&
-        (kSmemBudget - fixed - (int)res - staging(1)) / (g.groups * a_stage) >= 2) {
+    auto fits = [&](size_t res) {
+      return res <= kMaxResidentB && res % 1024 == 0 &&
+             (kSmemBudget - fixed - (int)res - staging(1)) / (g.groups * a_stage) >= 2;
+    };
+    if (fits(res_all)) {
       g.b_res = 1;
-      g.b_res_bytes = (unsigned)res;
+      g.b_res_bytes = (unsigned)res_all;
+      stage = (unsigned)a_stage;
+    } else if (!g.halo && g.n_tiles <= 16 && fits(res_tile)) {
+      g.b_res = 2;  // one column tile per CTA
+      g.b_res_bytes = (unsigned)res_tile;
       stage = (unsigned)a_stage;
     }
   }
@@ -1180,7 +1191,12 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   GemmKernel kernel = select_kernel(split, epi, g.out_dtype);
   if (kernel == nullptr) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: no kernel for this output type");
   const int sms = device_sm_count();
-  const unsigned grid = (unsigned)std::min<long long>(total, (long long)sms);
+  unsigned grid = (unsigned)std::min<long long>(total, (long long)sms);
+  if (g.b_res == 2) {
+    // every CTA stays on one column tile: tiles advance by a multiple of n_tiles
+    if (grid < (unsigned)g.n_tiles) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: grid smaller than the column tiles");
+    grid -= grid % (unsigned)g.n_tiles;
+  }
   kernel<<<grid, split ? 320 : 384, smem, s>>>(g);
   return check_launch("tensor-core gemm");
 }
