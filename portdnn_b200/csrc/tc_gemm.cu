@@ -116,6 +116,13 @@ struct alignas(64) GemmArgs {
   int halo;
   unsigned halo_stage_bytes;
   int res_taps;  // filter taps per column tile in the resident copy (halo mode: the sum of cnt)
+  // 1: pair mode.  The two pipelines of a CTA work on two neighbouring row tiles of the SAME column
+  // tile and share one ring: a stage holds both A tiles and one B tile, loaded by one producer,
+  // and is released when both issuers have read it.  The tile grid in tiles_w / tiles_h / tiles_n
+  // counts PAIRS along dimension pair_dim (1: w, 2: h, 3: n).  Halves the B bytes an SM pulls
+  // from L2 per MMA, which is what bounds long reductions over wide filters.
+  int pair, pair_dim;
+  int bias_tile_only;  // 1: the CTA keeps one column tile's bias slice (the grid is a multiple of n_tiles)
 };
 
 struct TileCoord {
@@ -161,9 +168,10 @@ struct TileWalker {
     t.nt = d0;
     t.nf0 = d0 * a.bn;
     if (!a.a_mn) {
-      t.w0 = d1 * a.tw;
-      t.h0 = d2 * a.th;
-      t.n0 = d3 * a.tn;
+      // in pair mode the paired dimension's digit counts pairs of tiles
+      t.w0 = (a.pair_dim == 1 ? 2 * d1 : d1) * a.tw;
+      t.h0 = (a.pair_dim == 2 ? 2 * d2 : d2) * a.th;
+      t.n0 = (a.pair_dim == 3 ? 2 * d3 : d3) * a.tn;
       t.tap = 0;
       t.split = 0;
       t.out_off = 0;
@@ -465,35 +473,44 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
   const bool b_res = !SPLIT && a.b_res != 0;
   const uint32_t res_bytes = b_res ? a.b_res_bytes : 0u;      // resident B tiles come first
   const bool halo = !SPLIT && a.halo != 0;
-  const uint32_t stage_bytes =
-      SPLIT ? 2u * part_bytes : (halo ? a.halo_stage_bytes : (b_res ? (uint32_t)kABytes : part_bytes));
+  const bool pair = !SPLIT && a.pair != 0;
+  const uint32_t stage_bytes = SPLIT  ? 2u * part_bytes
+                               : pair ? part_bytes + (uint32_t)kABytes
+                               : halo ? a.halo_stage_bytes
+                                      : (b_res ? (uint32_t)kABytes : part_bytes);
   const int S = a.stages;                                     // stages per group
   const uint32_t ring_bytes = (uint32_t)S * stage_bytes;
-  const uint32_t ring_base = base + res_bytes + (uint32_t)grp * ring_bytes;  // this group's ring
-  uint8_t* ring_mem = smem + res_bytes + (size_t)grp * ring_bytes;
+  const int rings = pair ? 1 : groups;                        // pair mode: one ring for both groups
+  const uint32_t ring_base = base + res_bytes + (pair ? 0u : (uint32_t)grp * ring_bytes);  // this group's ring
+  uint8_t* ring_mem = smem + res_bytes + (pair ? 0u : (size_t)grp * ring_bytes);
   // staging slices for the TMA-store epilogue (per group: 4 warps x nsw slices), then the barrier
   // block, then the bias copy
   const uint32_t group_staging = a.tma_store ? (uint32_t)a.nsw * 4u * 4096u : 0u;
-  const uint32_t staging_off = res_bytes + (uint32_t)groups * ring_bytes;
+  const uint32_t staging_off = res_bytes + (uint32_t)rings * ring_bytes;
   const uint32_t bar_off = staging_off + (uint32_t)groups * group_staging;
   uint8_t* bar_mem = smem + bar_off;
   const uint32_t bar_base = base + bar_off;
   auto gbar = [&](int g, int i) { return bar_base + 8u * (uint32_t)(g * kBarsPerGroup + i); };
-  auto full_bar = [&](int s) { return gbar(grp, s); };
-  auto empty_bar = [&](int s) { return gbar(grp, kMaxStages + s); };
+  const int ring_grp = pair ? 0 : grp;  // whose stage barriers this warp uses
+  auto full_bar = [&](int s) { return gbar(ring_grp, s); };
+  auto empty_bar = [&](int s) { return gbar(ring_grp, kMaxStages + s); };
   auto ready_bar = [&](int s) { return gbar(grp, 2 * kMaxStages + s); };
   auto acc_full_bar = [&](int b) { return gbar(grp, 3 * kMaxStages + b); };
   auto acc_empty_bar = [&](int b) { return gbar(grp, 3 * kMaxStages + 2 + b); };
   const uint32_t bres_bar = bar_base + 8u * (uint32_t)(2 * kBarsPerGroup);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 8 * (2 * kBarsPerGroup + 1));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * (2 * kBarsPerGroup + 1) + 4);
-  const uint32_t bias_s = (EPI == 2 && a.bias != nullptr) ? bar_base + kBarBlockBytes : 0u;
+  // with bias_tile_only the copy starts at the CTA's column tile; the address is biased so that
+  // indexing by absolute column still works
+  const int bias_col0 = a.bias_tile_only ? ((int)blockIdx.x % a.n_tiles) * a.bn : 0;
+  const uint32_t bias_s =
+      (EPI == 2 && a.bias != nullptr) ? bar_base + kBarBlockBytes - (uint32_t)bias_col0 * 2u : 0u;
 
   if (threadIdx.x == 0) {
     for (int g = 0; g < kMaxGroups; ++g) {
       for (int s = 0; s < kMaxStages; ++s) {
         mbar_init(gbar(g, s), 1);
-        mbar_init(gbar(g, kMaxStages + s), 1);
+        mbar_init(gbar(g, kMaxStages + s), pair ? 2 : 1);  // pair mode: both issuers release a stage
         mbar_init(gbar(g, 2 * kMaxStages + s), 4);
       }
       for (int b = 0; b < 2; ++b) {
@@ -510,8 +527,10 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     const OutT* bias = static_cast<const OutT*>(a.bias);
     uint4* dst = reinterpret_cast<uint4*>(bar_mem + kBarBlockBytes);
     const int chunks = a.bias_smem_bytes >> 4;
-    for (int i = threadIdx.x; i < chunks; i += blockDim.x)
-      dst[i] = (i * 8 + 8 <= a.ext_cols) ? __ldg(reinterpret_cast<const uint4*>(bias) + i) : make_uint4(0u, 0u, 0u, 0u);
+    for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
+      const int col = bias_col0 + i * 8;
+      dst[i] = (col + 8 <= a.ext_cols) ? __ldg(reinterpret_cast<const uint4*>(bias + col)) : make_uint4(0u, 0u, 0u, 0u);
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), (uint32_t)a.tmem_cols);
@@ -527,9 +546,13 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
 
   const int total_tiles = a.a_mn ? a.n_tiles * a.tiles_w * a.num_taps * a.splits
                                  : a.n_tiles * a.tiles_w * a.tiles_h * a.tiles_n;
-  const int first_tile = (int)blockIdx.x + grp * (int)gridDim.x;
-  const int tile_step = groups * (int)gridDim.x;
+  // pair mode: both groups walk the same tiles (each takes one row tile of the pair)
+  const int first_tile = (int)blockIdx.x + (pair ? 0 : grp * (int)gridDim.x);
+  const int tile_step = (pair ? 1 : groups) * (int)gridDim.x;
   const bool active = grp < groups;
+  // offset of this group's row tile inside the pair
+  const int sub_w = pair && a.pair_dim == 1 ? grp * a.tw : 0, sub_h = pair && a.pair_dim == 2 ? grp * a.th : 0,
+            sub_n = pair && a.pair_dim == 3 ? grp * a.tn : 0;
 
   if (!active) {
     // a group that is switched off has nothing to do
@@ -538,12 +561,15 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     // One thread; the loop body is kept to a wait, an expect_tx and the copies, with all
     // coordinates advanced incrementally: a lone thread issues an instruction every few cycles
     // at best, so every division or table lookup per step would show up as pipeline bubbles.
-    if (lane == 0) {
+    if (lane == 0 && !(pair && grp != 0)) {  // pair mode: group 0's producer fills the shared ring
       for (int i = 0; i < 4; ++i) prefetch_tensormap(&a.a_map[i]);
       prefetch_tensormap(&a.b_map);
       const int epr = a.epr, b_mode = a.b_mode, b_boxes = a.b_boxes, a_boxes = a.a_boxes, cblocks = a.cblocks;
       const uint32_t a_box_bytes = a.a_box_bytes, b_box_bytes = a.b_box_bytes,
-                     tx_bytes = b_res ? (uint32_t)kABytes : kABytes + b_bytes;
+                     tx_bytes = pair ? 2u * kABytes + b_bytes : (b_res ? (uint32_t)kABytes : kABytes + b_bytes);
+      // pair mode: where the second row tile of the pair starts, relative to the first
+      const int pair_dw = a.pair_dim == 1 ? a.tw : 0, pair_dh = a.pair_dim == 2 ? a.th : 0,
+                pair_dn = a.pair_dim == 3 ? a.tn : 0;
       const CUtensorMap* bmap = &a.b_map;
       // one B tile of a forward-style GEMM (a_mn == 0): reduction block kc of tap btap, columns from nf0
       auto load_b = [&](uint32_t sb, uint32_t fb, int kc, int nf0, int btap) {
@@ -606,7 +632,12 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
               mbar_arrive_expect_tx(fb, tx);
               const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
               tma_load_4d(sa, amap, fb, kc, aw, ah, t.n0);
-              if (!b_res) load_b(sa + kABytes, fb, kc, t.nf0, btap);
+              if (pair) {
+                tma_load_4d(sa + kABytes, amap, fb, kc, aw + pair_dw, ah + pair_dh, t.n0 + pair_dn);
+                load_b(sa + 2u * kABytes, fb, kc, t.nf0, btap);
+              } else if (!b_res) {
+                load_b(sa + kABytes, fb, kc, t.nf0, btap);
+              }
               next_stage();
             }
           }
@@ -686,12 +717,15 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
               tc_fence_after_sync();
               if (grp == 0 && tap == 0 && cb == 0) PDNN_TRACE(2, tcount);
               const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
+              // pair mode: [A of group 0 | A of group 1 | B]
+              const uint32_t my_a = pair ? sa + (uint32_t)grp * kABytes : sa;
+              const uint32_t my_b = pair ? sa + 2u * kABytes : sa + kABytes;
               for (int g = 0; g < cnt; ++g) {
                 // start addresses stay below 2^18, so adding to the low word never carries into
                 // the neighbouring descriptor field
-                uint64_t da = a_desc0 + (uint64_t)((sa + (uint32_t)g * halo_row_bytes) >> 4);
+                uint64_t da = a_desc0 + (uint64_t)((my_a + (uint32_t)g * halo_row_bytes) >> 4);
                 uint64_t db = b_desc0 + (uint64_t)((b_res ? res_b + (uint32_t)(g * a.cblocks + cb) * b_bytes
-                                                          : sa + kABytes) >> 4);
+                                                          : my_b) >> 4);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                   mma_f16(d_tmem, da, db, idesc, accumulate);
@@ -767,7 +801,10 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     TileWalker walker;
     walker.init(a, first_tile, tile_step);
     for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++tcount, walker.advance()) {
-      const TileCoord t = walker.coord(a);
+      TileCoord t = walker.coord(a);
+      t.w0 += sub_w;
+      t.h0 += sub_h;
+      t.n0 += sub_n;
       if (!mbar_wait(acc_full_bar((int)buf), aph, abort_flag, g_error_record, 0x400u + buf)) break;
       tc_fence_after_sync();
       if (warp == 2 && lane == 0) PDNN_TRACE(4, tcount);
@@ -972,6 +1009,15 @@ bool choose_box_halo(int W, int H, int rows, int* tw, int* th) {
   return best < 1e29;
 }
 
+// PDNN_TC_PAIR=0 switches pair mode off (for experiments).
+bool pair_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("PDNN_TC_PAIR");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  return on;
+}
+
 // PDNN_TC_GROUPS=1 runs one pipeline per CTA instead of two (for experiments).
 int group_count() {
   static const int n = [] {
@@ -1090,10 +1136,18 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   g.acc_bufs = g.groups * 2 * g.acc_stride <= 512 ? 2 : 1;
   g.tmem_cols = next_pow2(g.groups * g.acc_bufs * g.acc_stride);
   g.bias_smem_bytes = 0;
+  g.bias_tile_only = 0;
+  if (g.pair && (split || g.groups != 2 || !g.tma_store)) return false;  // the caller plans again without pairing
   if (g.epi_fast && g.bias != nullptr) {
     const int padded = ceil_div(g.n_tiles * g.bn, 64) * 64;
-    if (padded * 2 > 8192) g.epi_fast = 0;  // the general staged epilogue reads the bias from global memory
-    else g.bias_smem_bytes = padded * 2;
+    if (g.pair && g.n_tiles <= 16) {
+      g.bias_tile_only = 1;  // every byte counts towards a third stage
+      g.bias_smem_bytes = ceil_div(g.bn, 64) * 128;
+    } else if (padded * 2 > 8192) {
+      g.epi_fast = 0;  // the general staged epilogue reads the bias from global memory
+    } else {
+      g.bias_smem_bytes = padded * 2;
+    }
   }
   unsigned stage = (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
   int ksteps = g.a_mn ? g.slabs_per_split : g.num_taps * g.cblocks;
@@ -1105,6 +1159,14 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   auto staging = [&](int nsw) { return g.tma_store ? g.groups * 4 * nsw * 4096 : 0; };
   // A small filter (all taps, all column tiles) is kept in shared memory for the whole kernel:
   // the filter tiles are the part of the L2 -> SM traffic that never changes.
+  if (g.pair) {
+    stage = 2u * kABytes + (unsigned)g.bn * 128u;
+    const int avail = kSmemBudget - fixed;
+    auto stages_with = [&](int nsw) { return (avail - staging(nsw)) / (int)stage; };
+    g.nsw = stages_with(2) >= 4 ? 2 : 1;
+    g.stages = std::min(kMaxStages, stages_with(g.nsw));
+    return g.stages >= 2;
+  }
   if (!g.a_mn && !split && g.tma_store && g.b_batch_mul == 0 && b_resident_enabled()) {
     const size_t res_tile = (size_t)ksteps * g.bn * 128u, res_all = res_tile * g.n_tiles;
     const int a_stage = g.halo ? (int)g.halo_stage_bytes : kABytes;
@@ -1167,11 +1229,13 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
                                  : (long long)g.n_tiles * g.tiles_w * g.tiles_h * g.tiles_n;
   if (total <= 0) return PDNN_OK;
   if (total > 0x7FFFFFFFll) return fail(PDNN_INDEX_EXCEEDED, "tensor-core gemm: too many tiles");
-  const unsigned stage = g.halo ? g.halo_stage_bytes
-                                 : g.b_res ? (unsigned)kABytes : (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
+  const unsigned stage = g.pair   ? 2u * kABytes + (unsigned)g.bn * 128u
+                         : g.halo ? g.halo_stage_bytes
+                                  : g.b_res ? (unsigned)kABytes : (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
+  const int rings = g.pair ? 1 : g.groups;
   // At least 120 KB, so that two CTAs never share an SM: the second one would wait for TMEM
   // columns the first one holds.
-  size_t smem = 1024 + (size_t)g.b_res_bytes + (size_t)g.groups * g.stages * stage +
+  size_t smem = 1024 + (size_t)g.b_res_bytes + (size_t)rings * g.stages * stage +
                 (g.tma_store ? (size_t)g.groups * g.nsw * 4 * 4096 : 0) + kBarBlockBytes + (size_t)g.bias_smem_bytes;
   smem = std::max<size_t>(smem, 120 * 1024);
   if (smem > (size_t)kSmemBudget) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: plan needs %zu bytes of shared memory", smem);
@@ -1192,7 +1256,7 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   if (kernel == nullptr) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: no kernel for this output type");
   const int sms = device_sm_count();
   unsigned grid = (unsigned)std::min<long long>(total, (long long)sms);
-  if (g.b_res == 2) {
+  if (g.b_res == 2 || g.bias_tile_only) {
     // every CTA stays on one column tile: tiles advance by a multiple of n_tiles
     if (grid < (unsigned)g.n_tiles) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: grid smaller than the column tiles");
     grid -= grid % (unsigned)g.n_tiles;
@@ -1263,7 +1327,7 @@ int finish_forward(GemmArgs& g, int dtype, void* y, const PdnnConv2DParams& p, c
   const uint64_t od[4] = {(uint64_t)p.features, (uint64_t)p.out_cols, (uint64_t)p.out_rows, (uint64_t)p.batch};
   const uint64_t os[3] = {(uint64_t)p.features * es, (uint64_t)p.out_cols * p.features * es,
                           (uint64_t)p.out_rows * p.out_cols * p.features * es};
-  if (!setup_store(g, dtype, od, os)) return g.halo ? kPlanAgain : PDNN_INVALID_PARAMETER;
+  if (!setup_store(g, dtype, od, os)) return (g.halo || g.pair) ? kPlanAgain : PDNN_INVALID_PARAMETER;
   return launch_gemm(g, dtype, s);
 }
 
@@ -1481,8 +1545,30 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   g.tiles_h = ceil_div(p.out_rows, g.th);
   g.tiles_n = ceil_div(p.batch, g.tn);
   const long long row_tiles = (long long)g.tiles_w * g.tiles_h * g.tiles_n;
-  g.bn = pick_bn(row_tiles, p.features, hwcf ? epr : 16, dtype == PDNN_F32 ? 128 : 256, sms,
-                 p.window_rows * p.window_cols * ceil_div(p.channels, epr));
+  const int ksteps_all = p.window_rows * p.window_cols * ceil_div(p.channels, epr);
+  // Long reductions over filters too large to keep in shared memory are bound by the bytes an SM
+  // pulls from L2 per MMA: the two pipelines then share one B tile per stage (pair mode).  Measured
+  // on ResNet-50 shapes it pays from about 32 reduction steps, or from 16 with many column tiles;
+  // shorter reductions lose more to the unhidden epilogue of the 256-column accumulators.
+  const bool pairing = try_halo && !halo && pair_enabled() && dtype != PDNN_F32 && hwcf && p.features % 128 == 0 &&
+                       (ksteps_all >= 32 || (ksteps_all >= 16 && p.features >= 1024)) && row_tiles >= 2 &&
+                       (!epi || epi->beta == 0.f);
+  if (pairing) {
+    g.pair = 1;
+    g.bn = p.features % 256 == 0 ? 256 : 128;
+    if (g.tiles_w % 2 == 0) {
+      g.pair_dim = 1;
+      g.tiles_w /= 2;
+    } else if (g.tiles_h % 2 == 0) {
+      g.pair_dim = 2;
+      g.tiles_h /= 2;
+    } else {
+      g.pair_dim = 3;  // an odd count leaves the last pair half empty: loads read zeros, stores are clipped
+      g.tiles_n = ceil_div(g.tiles_n, 2);
+    }
+  } else {
+    g.bn = pick_bn(row_tiles, p.features, hwcf ? epr : 16, dtype == PDNN_F32 ? 128 : 256, sms, ksteps_all);
+  }
   g.n_tiles = ceil_div(p.features, g.bn);
   set_operand_layout(g, dtype, hwcf ? 1 : 0);
   const uint32_t abox[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)(halo ? g.th + p.window_rows - 1 : g.th),
