@@ -114,11 +114,12 @@ class MatmulSelector final : public Selector {
   }
 };
 
-/** The rules of the reference's DefaultSelector (src/conv2d/selector/default_selector.cc:49-128):
- * grouped -> Im2col; 1x1 stride 1 -> Matmul; 3x3 stride 1 -> WinogradLarge; 1x3 / 3x1 stride 1 ->
- * Winograd; forward tiled shapes -> Tiled; anything else -> Im2col.  On this implementation all
- * of those tags except Direct run the same tensor-core kernel, so the choice only matters for
- * code that inspects it. */
+/** The default selector of this implementation.  It follows the shape rules of the reference's
+ * DefaultSelector (src/conv2d/selector/default_selector.cc:49-128) - grouped -> Im2col; NCHW ->
+ * Direct; 1x1 stride 1 -> Matmul; forward tiled shapes -> Tiled; anything else -> Im2col - except
+ * that it never picks Winograd: every tag but Direct and the Winograd pair runs the same
+ * tensor-core implicit GEMM, which needs no workspace and is the fastest path for 16-bit data.
+ * fp32 callers with a workspace to spare can ask for WinogradSelector explicitly. */
 class B200Selector final : public Selector {
  public:
   Algorithm select_forward(Conv2DParams const& p) override {
@@ -137,9 +138,6 @@ class B200Selector final : public Selector {
     if (p.groups > 1) return Algorithm::Im2col;
     if (p.input_format == DataFormat::NCHW) return Algorithm::Direct;
     if (detail::pointwise_gemm(p)) return Algorithm::Matmul;
-    if (detail::square(p, 3, 1)) return Algorithm::WinogradLarge;
-    const bool stride1 = p.stride_rows == 1 && p.stride_cols == 1;
-    if (stride1 && (detail::window_is(p, 1, 3) || detail::window_is(p, 3, 1))) return Algorithm::Winograd;
     return Algorithm::NotSupported;
   }
 };

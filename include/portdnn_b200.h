@@ -44,8 +44,10 @@ typedef enum PdnnPass { PDNN_FORWARD = 0, PDNN_INPUT_BACKPROP = 1, PDNN_FILTER_B
 
 /* sycldnn::conv2d::Algorithm, include/portdnn/conv2d/algorithm.h:30-45.  Direct runs the
  * general SIMT kernel; Tiled, Im2col and Matmul run the tcgen05 implicit-GEMM kernel (which
- * needs no im2col buffer); Winograd and WinogradLarge run the fused F(2x2,3x3) kernel where it
- * applies and the implicit-GEMM kernel otherwise.  A shape the tensor-core kernels cannot take
+ * needs no im2col buffer); Winograd and WinogradLarge run Winograd F(2x2,3x3) (transforms around
+ * a batched tcgen05 matmul) on 3x3 stride-1 forward / input-backprop layers when the caller
+ * passes the workspace pdnn_conv2d_workspace_size recommends, and the implicit-GEMM kernel
+ * otherwise.  A shape the tensor-core kernels cannot take
  * (channel or feature count not a multiple of 8 elements of 16 bits / 4 of 32 bits) is routed
  * to the direct kernel whatever the algorithm. */
 typedef enum PdnnAlgorithm {
