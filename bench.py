@@ -26,6 +26,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "conv_tflops_resnet50_fp16_b256_forward"
+# dram__bytes_read.sum + dram__bytes_write.sum of the 53 conv launches of one forward step, from an
+# ncu capture of this script (profiles/bench_resnet50_forward_dram_traffic.md): 5111 MB read +
+# 3490 MB written = 8601 MB per step, against 11.76 GB of algorithmic bytes (input + filter + output
+# of every layer once) - the small feature maps are still in L2 when the next layer reads them.
+FORWARD_DRAM_BYTES_PER_LAUNCH = int(8601e6 / 53)
 UNIT = "TFLOP/s"
 BATCH = 256
 
@@ -299,7 +304,8 @@ def run_gpu(args):
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "umma_gemm_kernel (the 53 forward implicit-GEMM conv launches of a step)",
                      "achieved": round(achieved, 1), "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
-                     "frac": round(achieved / peaks["tflops_sustained"], 4), "traffic": None,
+                     "frac": round(achieved / peaks["tflops_sustained"], 4),
+                     "traffic": None if train else FORWARD_DRAM_BYTES_PER_LAUNCH,
                      "peak_source": "%s (sustained bf16 matmul)" % peaks["source"],
                      "avg_launch_ms": round(tc_ms / max(len(tc), 1), 4)},
         "cpu_baseline": cpu_baseline_sample(),
