@@ -174,19 +174,30 @@ def run_gpu(args):
     # graph is replayed per step, so that host-side launch cost (tensor-map encoding, ctypes) does
     # not sit between kernels; --no-graph times plain stream launches instead.
     graph = None
-    if not args.no_graph and not train:
+
+    def compute():  # the kernels of one step; the filter-gradient all-reduce of a training step stays outside the graph
+        net.forward()
+        if train:
+            net.backward()
+
+    def replay():
+        graph.replay()
+        if train:
+            net.bucket.all_reduce()
+
+    if not args.no_graph:
         side = torch.cuda.Stream()
         side.wait_stream(stream)
         with torch.cuda.stream(side):
-            net.forward()
+            compute()
         stream.wait_stream(side)
         torch.cuda.synchronize()
         l0 = pd.launch_count()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            net.forward()
+            compute()
         launches_per_step = pd.launch_count() - l0
-        graph.replay()
+        replay()
         barrier()
     else:
         l0 = pd.launch_count()
@@ -197,7 +208,7 @@ def run_gpu(args):
     ev0.record(stream)
     for _ in range(args.steps):
         if graph is not None:
-            graph.replay()
+            replay()
         else:
             step()
     ev1.record(stream)
@@ -231,7 +242,7 @@ def run_gpu(args):
                 staging.copy_(host_in, non_blocking=True)
                 uploaded[i + 1].record(copy_stream)
         if graph is not None:
-            graph.replay()
+            replay()
         else:
             step()
         host_out.copy_(result, non_blocking=True)
