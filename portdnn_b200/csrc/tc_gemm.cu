@@ -522,6 +522,17 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     *abort_flag = 0;
     fence_barrier_init();
   }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), (uint32_t)a.tmem_cols);
+    tmem_relinquish();
+  }
+  // Under programmatic dependent launch everything above overlaps the tail of the previous kernel
+  // in the stream; nothing before this point reads or writes global memory.  From here on the
+  // kernel touches tensors that kernel may have written (or may still be reading), so it waits
+  // for it.  The next kernel may be scheduled as soon as SMs free up: this grid is a single wave,
+  // so nothing of it is still waiting for an SM.
+  grid_dependency_wait();
+  grid_launch_dependents();
   if (EPI == 2 && a.bias != nullptr) {
     // the CTA's copy of the bias vector, zero beyond the last column
     const OutT* bias = static_cast<const OutT*>(a.bias);
@@ -531,10 +542,6 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       const int col = bias_col0 + i * 8;
       dst[i] = (col + 8 <= a.ext_cols) ? __ldg(reinterpret_cast<const uint4*>(bias + col)) : make_uint4(0u, 0u, 0u, 0u);
     }
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), (uint32_t)a.tmem_cols);
-    tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -1009,6 +1016,15 @@ bool choose_box_halo(int W, int H, int rows, int* tw, int* th) {
   return best < 1e29;
 }
 
+// PDNN_TC_PDL=0 launches the GEMM kernel without programmatic dependent launch (for experiments).
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("PDNN_TC_PDL");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  return on;
+}
+
 // PDNN_TC_PAIR=0 switches pair mode off (for experiments).
 bool pair_enabled() {
   static const bool on = [] {
@@ -1261,7 +1277,23 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
     if (grid < (unsigned)g.n_tiles) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: grid smaller than the column tiles");
     grid -= grid % (unsigned)g.n_tiles;
   }
-  kernel<<<grid, split ? 320 : 384, smem, s>>>(g);
+  // Programmatic dependent launch: the kernel's set-up may overlap the tail of the previous kernel
+  // in the stream (the kernel waits for that kernel before it touches any tensor it wrote).
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(split ? 320 : 384);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, g);
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return fail(PDNN_ALLOCATION_PROBLEM, "tensor-core gemm: launch failed: %s", cudaGetErrorString(le));
+  }
   return check_launch("tensor-core gemm");
 }
 

@@ -116,6 +116,14 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------------
+// A kernel launched with programmatic stream serialisation may start while its predecessor in the
+// stream is still running.  grid_dependency_wait() blocks until the predecessor has completed and
+// its writes are visible (a no-op for an ordinary launch); grid_launch_dependents() tells the
+// runtime that the successor may be scheduled as soon as resources free up.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- TMEM ----------------------------------------------------------------------------------------
 // Warp-wide. Writes the base address of `columns` (power of two, >= 32) TMEM columns to *smem_slot.
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t columns) {
