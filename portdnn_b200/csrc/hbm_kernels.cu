@@ -179,6 +179,159 @@ __global__ void __launch_bounds__(kBlock)
   }
 }
 
+// Max-pool gradient when the windows tile the input exactly (stride == window, no padding,
+// in == out * stride: the 2x2/2 pools of VGG).  Every input element belongs to exactly one window,
+// so one thread per output packet reads its window once, finds per channel the first element equal
+// to y (the same rule as above) and writes dy there and zero elsewhere: x, y and dy are read once
+// and dx is written once.
+template <typename T, int OP, int V, typename Index>
+__global__ void __launch_bounds__(kBlock)
+    pool_max_grad_tiled_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy,
+                               T* __restrict__ dx, PdnnPoolingParams p, Index n_items) {
+  const Index cvecs = (Index)(p.channels / V);
+  for (Index idx = (Index)blockIdx.x * kBlock + threadIdx.x; idx < n_items; idx += (Index)gridDim.x * kBlock) {
+    const Index cv = idx % cvecs;
+    Index t = idx / cvecs;
+    const int ow = (int)(t % (Index)p.out_cols);
+    t /= (Index)p.out_cols;
+    const int oh = (int)(t % (Index)p.out_rows);
+    const int n = (int)(t / (Index)p.out_rows);
+    float yv[V], dv[V];
+    load_vec<T, V>(y + (size_t)idx * V, yv);
+    load_vec<T, V>(dy + (size_t)idx * V, dv);
+    bool open[V];  // no element of the window has matched yet
+#pragma unroll
+    for (int i = 0; i < V; ++i) open[i] = true;
+    const size_t base = ((size_t)n * p.in_rows + (size_t)oh * p.stride_rows) * p.in_cols + (size_t)ow * p.stride_cols;
+    for (int r = 0; r < p.window_rows; ++r)
+      for (int c = 0; c < p.window_cols; ++c) {
+        const size_t off = ((base + (size_t)r * p.in_cols + c) * p.channels) + (size_t)cv * V;
+        float xv[V], g[V];
+        load_vec<T, V>(x + off, xv);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          const bool hit = open[i] && pool_equal<OP>(xv[i], yv[i]);
+          g[i] = hit ? dv[i] : 0.f;
+          open[i] = open[i] && !hit;
+        }
+        store_vec<T, V>(dx + off, g);
+      }
+  }
+}
+
+// V bytes (V = 4 or 8, address a multiple of V) <-> V words, through registers only.
+template <int V>
+__device__ __forceinline__ void store_bytes(unsigned char* p, const unsigned (&v)[V]) {
+  static_assert(V == 4 || V == 8, "packet of 4 or 8 channels");
+  const unsigned lo = v[0] | (v[1] << 8) | (v[2] << 16) | (v[3] << 24);
+  if constexpr (V == 8) {
+    const unsigned hi = v[4] | (v[5] << 8) | (v[6] << 16) | (v[7] << 24);
+    *reinterpret_cast<uint2*>(p) = make_uint2(lo, hi);
+  } else {
+    *reinterpret_cast<unsigned*>(p) = lo;
+  }
+}
+template <int V>
+__device__ __forceinline__ void load_bytes(const unsigned char* p, unsigned (&v)[V]) {
+  static_assert(V == 4 || V == 8, "packet of 4 or 8 channels");
+  unsigned lo, hi = 0u;
+  if constexpr (V == 8) {
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+    lo = raw.x;
+    hi = raw.y;
+  } else {
+    lo = __ldg(reinterpret_cast<const unsigned*>(p));
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = (lo >> (8 * i)) & 0xFFu;
+  if constexpr (V == 8) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[4 + i] = (hi >> (8 * i)) & 0xFFu;
+  }
+}
+
+// Max-pool gradient for overlapping windows, in two passes.  Pass 1 (one thread per output packet)
+// records for every output element which element of its window is the first maximum, as
+// 1 + row * window_cols + col in unclamped window coordinates (0: none).  Pass 2 (one thread per
+// input packet) visits the windows that hold the element, in the same order as
+// pool_max_grad_kernel, and adds dy where the recorded winner is this element.  The scan for an
+// earlier maximum, which pool_max_grad_kernel repeats for every (input, window) pair, is done once
+// per window.
+template <typename T, int OP, int V, typename Index>
+__global__ void __launch_bounds__(kBlock)
+    pool_winner_kernel(const T* __restrict__ x, const T* __restrict__ y, unsigned char* __restrict__ winner,
+                       PdnnPoolingParams p, Index n_items) {
+  const Index cvecs = (Index)(p.channels / V);
+  for (Index idx = (Index)blockIdx.x * kBlock + threadIdx.x; idx < n_items; idx += (Index)gridDim.x * kBlock) {
+    const Index cv = idx % cvecs;
+    Index t = idx / cvecs;
+    const int ow = (int)(t % (Index)p.out_cols);
+    t /= (Index)p.out_cols;
+    const int oh = (int)(t % (Index)p.out_rows);
+    const int n = (int)(t / (Index)p.out_rows);
+    const int ur = oh * p.stride_rows - p.pad_rows, uc = ow * p.stride_cols - p.pad_cols;  // unclamped origin
+    const int r0 = max(ur, 0), c0 = max(uc, 0);
+    const int r1 = min(ur + p.window_rows, p.in_rows), c1 = min(uc + p.window_cols, p.in_cols);
+    float yv[V];
+    load_vec<T, V>(y + (size_t)idx * V, yv);
+    unsigned win[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) win[i] = 0u;
+    const T* xn = x + (size_t)n * p.in_rows * p.in_cols * p.channels + (size_t)cv * V;
+    for (int r = r0; r < r1; ++r)
+      for (int c = c0; c < c1; ++c) {
+        float xv[V];
+        load_vec<T, V>(xn + ((size_t)r * p.in_cols + c) * p.channels, xv);
+        const unsigned id = (unsigned)(1 + (r - ur) * p.window_cols + (c - uc));
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+          if (win[i] == 0u && pool_equal<OP>(xv[i], yv[i])) win[i] = id;
+      }
+    store_bytes<V>(winner + (size_t)idx * V, win);
+  }
+}
+
+template <typename T, int V, typename Index>
+__global__ void __launch_bounds__(kBlock)
+    pool_max_grad_from_winner_kernel(const unsigned char* __restrict__ winner, const T* __restrict__ dy,
+                                     T* __restrict__ dx, PdnnPoolingParams p, Index n_items) {
+  const Index cvecs = (Index)(p.channels / V);
+  for (Index idx = (Index)blockIdx.x * kBlock + threadIdx.x; idx < n_items; idx += (Index)gridDim.x * kBlock) {
+    const Index cv = idx % cvecs;
+    Index t = idx / cvecs;
+    const int w = (int)(t % (Index)p.in_cols);
+    t /= (Index)p.in_cols;
+    const int h = (int)(t % (Index)p.in_rows);
+    const int n = (int)(t / (Index)p.in_rows);
+    float grad[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) grad[i] = 0.f;
+    const int hp = h + p.pad_rows, wp = w + p.pad_cols;
+    const int oh_lo = hp < p.window_rows ? 0 : (hp - p.window_rows) / p.stride_rows + 1;
+    const int oh_hi = min(hp / p.stride_rows + 1, p.out_rows);
+    const int ow_lo = wp < p.window_cols ? 0 : (wp - p.window_cols) / p.stride_cols + 1;
+    const int ow_hi = min(wp / p.stride_cols + 1, p.out_cols);
+    const size_t out_n = (size_t)n * p.out_rows * p.out_cols * p.channels + (size_t)cv * V;
+    for (int oh = oh_lo; oh < oh_hi; ++oh)
+      for (int ow = ow_lo; ow < ow_hi; ++ow) {
+        const size_t o = out_n + ((size_t)oh * p.out_cols + ow) * p.channels;
+        const unsigned me = (unsigned)(1 + (hp - oh * p.stride_rows) * p.window_cols + (wp - ow * p.stride_cols));
+        unsigned win[V];
+        load_bytes<V>(winner + o, win);
+        bool any = false;
+#pragma unroll
+        for (int i = 0; i < V; ++i) any |= win[i] == me;
+        if (!any) continue;
+        float dv[V];
+        load_vec<T, V>(dy + o, dv);
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+          if (win[i] == me) grad[i] += dv[i];
+      }
+    store_vec<T, V>(dx + (size_t)idx * V, grad);
+  }
+}
+
 // Average-pool gradient (src/pooling/kernels.h:312-366): dx[i] = sum_o dy[o] / valid(o).
 template <typename T, int V, typename Index>
 __global__ void __launch_bounds__(kBlock)
@@ -354,6 +507,95 @@ __global__ void __launch_bounds__(kFbpLanesF* kFbpLanesP)
       for (int l = 0; l < kFbpLanesP; ++l) sum += red[l][threadIdx.x][i];
       partial[((size_t)blockIdx.x * gridDim.y + tap) * F + f + i] = sum;
     }
+  }
+}
+
+// The same for a 3x3 window and one packet of channels per thread, all nine taps in one block:
+// dy is read once and the nine x packets of a pixel come from the same few cache lines, instead
+// of both tensors being streamed once per tap.  partial[slice][tap][f] as above.
+template <typename T, int V>
+__global__ void __launch_bounds__(kFbpLanesF* kFbpLanesP)
+    depthwise_filter_backprop_partial9_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                                              float* __restrict__ partial, PdnnDepthwiseConv2DParams p,
+                                              long long pixels_per_slice) {
+  __shared__ float red[kFbpLanesP * kFbpLanesF][V];  // [pixel lane][channel lane], blockDim.y x blockDim.x
+  const int F = p.channels;  // channel multiplier 1
+  const int lanes_f = blockDim.x, lanes_p = blockDim.y;
+  const int f = (blockIdx.z * lanes_f + threadIdx.x) * V;
+  const long long pixels = (long long)p.batch * p.out_rows * p.out_cols;
+  const long long begin = (long long)blockIdx.x * pixels_per_slice;
+  const long long end = begin + pixels_per_slice < pixels ? begin + pixels_per_slice : pixels;
+  float acc[9][V];
+#pragma unroll
+  for (int t = 0; t < 9; ++t)
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[t][i] = 0.f;
+  if (f < F) {
+    // pixel coordinates advance with the loop instead of being decoded every time
+    long long pix = begin + threadIdx.y;
+    int ow = (int)(pix % p.out_cols);
+    long long tt = pix / p.out_cols;
+    int oh = (int)(tt % p.out_rows);
+    int n = (int)(tt / p.out_rows);
+    for (; pix < end; pix += lanes_p) {
+      float dv[V];
+      load_vec<T, V>(dy + (size_t)pix * F + f, dv);
+      const int ih0 = oh * p.stride_rows - p.pad_rows, iw0 = ow * p.stride_cols - p.pad_cols;
+      const T* xn = x + (size_t)n * p.in_rows * p.in_cols * p.channels + f;
+      // Loads are made unconditional (coordinates clamped into the image, the product masked)
+      // and issued a row at a time, so that they overlap instead of each waiting behind a branch.
+#pragma unroll
+      for (int r = 0; r < 3; ++r) {
+        const int ih = ih0 + r;
+        const bool row_ok = ih >= 0 && ih < p.in_rows;
+        const T* xr = xn + (size_t)min(max(ih, 0), p.in_rows - 1) * p.in_cols * p.channels;
+        float xv[3][V];
+#pragma unroll
+        for (int c = 0; c < 3; ++c) load_vec<T, V>(xr + (size_t)min(max(iw0 + c, 0), p.in_cols - 1) * p.channels, xv[c]);
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+          const bool ok = row_ok && iw0 + c >= 0 && iw0 + c < p.in_cols;
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc[r * 3 + c][i] = fmaf(ok ? xv[c][i] : 0.f, dv[i], acc[r * 3 + c][i]);
+        }
+      }
+      ow += lanes_p;
+      while (ow >= p.out_cols) {
+        ow -= p.out_cols;
+        if (++oh == p.out_rows) {
+          oh = 0;
+          ++n;
+        }
+      }
+    }
+  }
+  // Reduction over the block's pixel lanes: first across the pixel lanes that share a warp
+  // (a warp is lanes_f channel lanes x 32 / lanes_f pixel lanes) by shuffles, then across the
+  // eight warps through shared memory.
+  const int tid = threadIdx.y * lanes_f + threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#pragma unroll
+  for (int t = 0; t < 9; ++t) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      float v = acc[t][i];
+      for (int off = lanes_f; off < 32; off <<= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+      acc[t][i] = v;
+    }
+    if (lane < lanes_f) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) red[warp * 32 + lane][i] = acc[t][i];
+    }
+    __syncthreads();
+    if (warp == 0 && lane < lanes_f && f < F) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kFbpLanesF * kFbpLanesP / 32; ++w) sum += red[w * 32 + lane][i];
+        partial[((size_t)blockIdx.x * 9 + t) * F + f + i] = sum;
+      }
+    }
+    __syncthreads();
   }
 }
 
@@ -556,6 +798,7 @@ constexpr int kStripBlock = 128;
 struct StripGeometry {
   int in_rows, in_cols, out_rows, out_cols, channels, pad_rows, pad_cols, batch;
   int rows_per_thread, wgroups, hchunks;
+  int flip;  // MODE 0: read the filter mirrored in both window axes (stride-1 input backprop)
 };
 
 // MODE 0: depthwise 3x3 (needs Packet::fma); MODE 1: max ignoring NaN; MODE 2: max keeping NaN.
@@ -587,7 +830,8 @@ __global__ void __launch_bounds__(kStripBlock)
 #pragma unroll
     for (int r = 0; r < 3; ++r)
 #pragma unroll
-      for (int s2 = 0; s2 < 3; ++s2) wt[r][s2] = P::load(w + (size_t)(r * 3 + s2) * g.channels + c);
+      for (int s2 = 0; s2 < 3; ++s2)
+        wt[r][s2] = P::load(w + (size_t)(g.flip ? (2 - r) * 3 + (2 - s2) : r * 3 + s2) * g.channels + c);
   }
   auto load_row = [&](P (&row)[NIN], int ih) {
     const bool row_ok = ih >= 0 && ih < g.in_rows;
@@ -753,6 +997,43 @@ int launch_pooling_max_grad(int op, int dtype, const void* x, const void* y, con
     using T = decltype(tag);
     constexpr int VN = Vec16<T>::N;
     const bool vec = (p.channels % VN == 0) && aligned16(x) && aligned16(y) && aligned16(dy) && aligned16(dx);
+    const size_t out_items = (size_t)p.batch * p.out_rows * p.out_cols * (p.channels / VN);
+    const size_t in_items = (size_t)p.batch * p.in_rows * p.in_cols * (p.channels / VN);
+    const bool small = in_items < 0xFFFFFFFFull - (size_t)sms * 32 * kBlock;
+    const T *xt = static_cast<const T*>(x), *yt = static_cast<const T*>(y), *dyt = static_cast<const T*>(dy);
+    T* dxt = static_cast<T*>(dx);
+    if (vec && small && p.pad_rows == 0 && p.pad_cols == 0 && p.stride_rows == p.window_rows &&
+        p.stride_cols == p.window_cols && p.in_rows == p.out_rows * p.stride_rows &&
+        p.in_cols == p.out_cols * p.stride_cols) {
+      // the windows tile the input: one pass
+      const unsigned g1 = grid_for(out_items, kBlock, sms);
+      if (op == PDNN_POOL_MAX)
+        pool_max_grad_tiled_kernel<T, PDNN_POOL_MAX, VN, unsigned><<<g1, kBlock, 0, s>>>(xt, yt, dyt, dxt, p, (unsigned)out_items);
+      else
+        pool_max_grad_tiled_kernel<T, PDNN_POOL_MAX_WITH_NAN, VN, unsigned><<<g1, kBlock, 0, s>>>(xt, yt, dyt, dxt, p, (unsigned)out_items);
+      return check_launch("pooling max gradient (tiling windows)");
+    }
+    if (vec && small && p.window_rows * p.window_cols < 255) {
+      // overlapping windows: winners first, then a gather; the winner map comes from the
+      // stream-ordered allocator
+      unsigned char* winner = nullptr;
+      const size_t bytes = out_items * VN;
+      if (cudaMallocAsync(reinterpret_cast<void**>(&winner), bytes, s) == cudaSuccess) {
+        const unsigned g1 = grid_for(out_items, kBlock, sms), g2 = grid_for(in_items, kBlock, sms);
+        if (op == PDNN_POOL_MAX)
+          pool_winner_kernel<T, PDNN_POOL_MAX, VN, unsigned><<<g1, kBlock, 0, s>>>(xt, yt, winner, p, (unsigned)out_items);
+        else
+          pool_winner_kernel<T, PDNN_POOL_MAX_WITH_NAN, VN, unsigned><<<g1, kBlock, 0, s>>>(xt, yt, winner, p, (unsigned)out_items);
+        int st = check_launch("pooling max gradient (winners)");
+        if (st == PDNN_OK) {
+          pool_max_grad_from_winner_kernel<T, VN, unsigned><<<g2, kBlock, 0, s>>>(winner, dyt, dxt, p, (unsigned)in_items);
+          st = check_launch("pooling max gradient (gather)");
+        }
+        cudaFreeAsync(winner, s);
+        return st;
+      }
+      cudaGetLastError();  // no scratch: fall through to the single-pass kernel
+    }
     const size_t items = (size_t)p.batch * p.in_rows * p.in_cols * (p.channels / (vec ? VN : 1));
     const unsigned grid = grid_for(items, kBlock, sms);
     const bool wide = items >= 0xFFFFFFFFull - (size_t)grid * kBlock;
@@ -788,11 +1069,34 @@ bool depthwise_params_ok(const PdnnDepthwiseConv2DParams& p) {
 
 // Number of pixel slices of the filter-backprop reduction: enough blocks to fill the device,
 // at least 256 pixels per slice.
+// The all-taps kernel runs 3x3 windows with whole channel packets.
+bool fbp_all_taps(const PdnnDepthwiseConv2DParams& p, int V) {
+  return V > 1 && p.window_rows == 3 && p.window_cols == 3 && p.channel_multiplier == 1;
+}
+
+// Channel lanes per block of the all-taps kernel: 4, 8, 16 or 32 (the block always has 256
+// threads), whichever wastes the fewest lanes on the last channel tile; ties go to the wider one.
+int fbp_channel_lanes(int packets) {
+  int best = 32;
+  double best_eff = 0;
+  for (int lanes = 32; lanes >= 4; lanes >>= 1) {
+    const int tiles = (packets + lanes - 1) / lanes;
+    const double eff = (double)packets / (tiles * lanes);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = lanes;
+    }
+  }
+  return best;
+}
+
 int fbp_slices(const PdnnDepthwiseConv2DParams& p, int V, int sms) {
   const long long pixels = (long long)p.batch * p.out_rows * p.out_cols;
   const int F = p.channels * p.channel_multiplier;
-  const int ftiles = (F + kFbpLanesF * V - 1) / (kFbpLanesF * V);
-  const long long other = (long long)p.window_rows * p.window_cols * ftiles;
+  const bool all_taps = fbp_all_taps(p, V);
+  const int lanes = all_taps ? fbp_channel_lanes(F / V) : kFbpLanesF;
+  const int ftiles = (F + lanes * V - 1) / (lanes * V);
+  const long long other = all_taps ? ftiles : (long long)p.window_rows * p.window_cols * ftiles;
   long long want = ((long long)sms * 8 + other - 1) / other;
   const long long cap = (pixels + 255) / 256;
   if (want > cap) want = cap;
@@ -800,6 +1104,28 @@ int fbp_slices(const PdnnDepthwiseConv2DParams& p, int V, int sms) {
   if (want > 1024) want = 1024;
   return (int)want;
 }
+
+// Stage 1 of the depthwise filter backprop: partial[slice][tap][f].
+template <typename T>
+void launch_fbp_partials(bool vec, const T* in, const T* dy, float* partial, const PdnnDepthwiseConv2DParams& p,
+                         int slices, cudaStream_t s) {
+  constexpr int VN = Vec16<T>::N;
+  const int V = vec ? VN : 1, F = p.channels * p.channel_multiplier;
+  const long long pixels = (long long)p.batch * p.out_rows * p.out_cols;
+  const long long per_slice = (pixels + slices - 1) / slices;
+  if (fbp_all_taps(p, V)) {
+    const int lanes = fbp_channel_lanes(F / V);
+    dim3 block(lanes, kFbpLanesF * kFbpLanesP / lanes);
+    dim3 grid(slices, 1, (F + lanes * V - 1) / (lanes * V));
+    depthwise_filter_backprop_partial9_kernel<T, VN><<<grid, block, 0, s>>>(in, dy, partial, p, per_slice);
+    return;
+  }
+  dim3 block(kFbpLanesF, kFbpLanesP);
+  dim3 grid(slices, p.window_rows * p.window_cols, (F + kFbpLanesF * V - 1) / (kFbpLanesF * V));
+  if (vec) depthwise_filter_backprop_partial_kernel<T, VN><<<grid, block, 0, s>>>(in, dy, partial, p, per_slice);
+  else depthwise_filter_backprop_partial_kernel<T, 1><<<grid, block, 0, s>>>(in, dy, partial, p, per_slice);
+}
+
 }  // namespace
 
 size_t depthwise_workspace_bytes(int pass, int dtype, const PdnnDepthwiseConv2DParams& p) {
@@ -838,16 +1164,7 @@ int launch_depthwise(int pass, int dtype, const void* in, const void* fil, void*
         }
         own = true;
       }
-      const long long pixels = (long long)p.batch * p.out_rows * p.out_cols;
-      const long long per_slice = (pixels + slices - 1) / slices;
-      dim3 block(kFbpLanesF, kFbpLanesP);
-      dim3 grid(slices, p.window_rows * p.window_cols, (F + kFbpLanesF * V - 1) / (kFbpLanesF * V));
-      if (vec)
-        depthwise_filter_backprop_partial_kernel<T, VN><<<grid, block, 0, s>>>(
-            static_cast<const T*>(in), static_cast<const T*>(fil), partial, p, per_slice);
-      else
-        depthwise_filter_backprop_partial_kernel<T, 1><<<grid, block, 0, s>>>(
-            static_cast<const T*>(in), static_cast<const T*>(fil), partial, p, per_slice);
+      launch_fbp_partials<T>(vec, static_cast<const T*>(in), static_cast<const T*>(fil), partial, p, slices, s);
       int st = check_launch("depthwise filter backprop (partial sums)");
       if (st == PDNN_OK) {
         reduce_slices_kernel<T><<<grid_for(n_out, kBlock, sms), kBlock, 0, s>>>(partial, static_cast<T*>(out), slices, n_out);
@@ -859,10 +1176,20 @@ int launch_depthwise(int pass, int dtype, const void* in, const void* fil, void*
     if constexpr (!std::is_same<T, __nv_bfloat16>::value) {
       if (pass == PDNN_FORWARD && vec && p.window_rows == 3 && p.window_cols == 3 && p.stride_rows == p.stride_cols &&
           (p.stride_rows == 1 || p.stride_rows == 2)) {
-        const StripGeometry g{p.in_rows, p.in_cols, p.out_rows, p.out_cols, p.channels, p.pad_rows, p.pad_cols, p.batch, 0, 0, 0};
+        const StripGeometry g{p.in_rows, p.in_cols, p.out_rows, p.out_cols, p.channels, p.pad_rows, p.pad_cols, p.batch, 0, 0, 0, 0};
         if (launch_window3_strip<T, 0>(static_cast<const T*>(in), static_cast<const T*>(fil), static_cast<T*>(out),
                                        p.stride_rows, g, sms, s) == 0)
           return check_launch("depthwise conv2d (3x3 strips)");
+      }
+      // Stride-1 input backprop is the forward operator on dy with the filter mirrored and the
+      // padding complemented: dx[h][w] = sum dy[h + pad - r][w + pad - s] * w[r][s].
+      if (pass == PDNN_INPUT_BACKPROP && vec && p.channel_multiplier == 1 && p.window_rows == 3 && p.window_cols == 3 &&
+          p.stride_rows == 1 && p.stride_cols == 1 && p.pad_rows <= 2 && p.pad_cols <= 2) {
+        const StripGeometry g{p.out_rows, p.out_cols, p.in_rows, p.in_cols, p.channels, 2 - p.pad_rows, 2 - p.pad_cols,
+                              p.batch, 0, 0, 0, 1};
+        if (launch_window3_strip<T, 0>(static_cast<const T*>(in), static_cast<const T*>(fil), static_cast<T*>(out), 1, g,
+                                       sms, s) == 0)
+          return check_launch("depthwise input backprop (3x3 strips)");
       }
     }
     const size_t pixels = pass == PDNN_FORWARD ? (size_t)p.batch * p.out_rows * p.out_cols
@@ -1034,18 +1361,9 @@ int launch_depthwise_filter_backprop_static(int dtype, const void* in, const voi
     int slices = fbp_slices(p, V, sms);
     const size_t fit = kStaticScratchBytes / (n_out * sizeof(float));
     if ((size_t)slices > fit) slices = (int)fit;
-    const long long pixels = (long long)p.batch * p.out_rows * p.out_cols;
-    const long long per_slice = (pixels + slices - 1) / slices;
-    dim3 block(kFbpLanesF, kFbpLanesP);
-    dim3 grid(slices, p.window_rows * p.window_cols, (F + kFbpLanesF * V - 1) / (kFbpLanesF * V));
     // Stage 1 writes every partial[slice][tap][f] it later reads, so the array's old contents
     // never leak into a result and nothing has to be cleared first.
-    if (vec)
-      depthwise_filter_backprop_partial_kernel<T, VN><<<grid, block, 0, s>>>(
-          static_cast<const T*>(in), static_cast<const T*>(dy), partial, p, per_slice);
-    else
-      depthwise_filter_backprop_partial_kernel<T, 1><<<grid, block, 0, s>>>(
-          static_cast<const T*>(in), static_cast<const T*>(dy), partial, p, per_slice);
+    launch_fbp_partials<T>(vec, static_cast<const T*>(in), static_cast<const T*>(dy), partial, p, slices, s);
     int st = check_launch("depthwise filter backprop, fixed scratch (partial sums)");
     if (st != PDNN_OK) return st;
     reduce_slices_kernel<T><<<grid_for(n_out, kBlock, sms), kBlock, 0, s>>>(partial, static_cast<T*>(dw), slices, n_out);
