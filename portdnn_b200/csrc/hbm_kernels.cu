@@ -278,15 +278,36 @@ __global__ void __launch_bounds__(kBlock)
 #pragma unroll
     for (int i = 0; i < V; ++i) win[i] = 0u;
     const T* xn = x + (size_t)n * p.in_rows * p.in_cols * p.channels + (size_t)cv * V;
-    for (int r = r0; r < r1; ++r)
-      for (int c = c0; c < c1; ++c) {
-        float xv[V];
-        load_vec<T, V>(xn + ((size_t)r * p.in_cols + c) * p.channels, xv);
-        const unsigned id = (unsigned)(1 + (r - ur) * p.window_cols + (c - uc));
+    if (p.window_rows == 3 && p.window_cols == 3) {
+      // 3x3: a row of three loads at a time, unconditional (clamped coordinates, masked match)
 #pragma unroll
-        for (int i = 0; i < V; ++i)
-          if (win[i] == 0u && pool_equal<OP>(xv[i], yv[i])) win[i] = id;
+      for (int r = 0; r < 3; ++r) {
+        const int ir = ur + r;
+        const bool row_ok = ir >= r0 && ir < r1;
+        const T* xr = xn + (size_t)min(max(ir, 0), p.in_rows - 1) * p.in_cols * p.channels;
+        float xv[3][V];
+#pragma unroll
+        for (int c = 0; c < 3; ++c) load_vec<T, V>(xr + (size_t)min(max(uc + c, 0), p.in_cols - 1) * p.channels, xv[c]);
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+          const bool ok = row_ok && uc + c >= c0 && uc + c < c1;
+          const unsigned id = (unsigned)(1 + r * 3 + c);
+#pragma unroll
+          for (int i = 0; i < V; ++i)
+            if (ok && win[i] == 0u && pool_equal<OP>(xv[c][i], yv[i])) win[i] = id;
+        }
       }
+    } else {
+      for (int r = r0; r < r1; ++r)
+        for (int c = c0; c < c1; ++c) {
+          float xv[V];
+          load_vec<T, V>(xn + ((size_t)r * p.in_cols + c) * p.channels, xv);
+          const unsigned id = (unsigned)(1 + (r - ur) * p.window_cols + (c - uc));
+#pragma unroll
+          for (int i = 0; i < V; ++i)
+            if (win[i] == 0u && pool_equal<OP>(xv[i], yv[i])) win[i] = id;
+        }
+    }
     store_bytes<V>(winner + (size_t)idx * V, win);
   }
 }
@@ -312,6 +333,32 @@ __global__ void __launch_bounds__(kBlock)
     const int ow_lo = wp < p.window_cols ? 0 : (wp - p.window_cols) / p.stride_cols + 1;
     const int ow_hi = min(wp / p.stride_cols + 1, p.out_cols);
     const size_t out_n = (size_t)n * p.out_rows * p.out_cols * p.channels + (size_t)cv * V;
+    if (oh_hi - oh_lo <= 2 && ow_hi - ow_lo <= 2) {
+      // At most 2 x 2 windows hold the element (window <= 2 * stride): all four winner words and
+      // all four dy packets are requested at once, with clamped coordinates and a mask, instead
+      // of one dependent pair of loads after another.
+      unsigned win[4][V];
+      float dv[4][V];
+      bool ok[4];
+      unsigned me[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int oh = oh_lo + (k >> 1), ow = ow_lo + (k & 1);
+        ok[k] = oh < oh_hi && ow < ow_hi;
+        const int ohc = min(oh, p.out_rows - 1), owc = min(ow, p.out_cols - 1);
+        const size_t o = out_n + ((size_t)ohc * p.out_cols + owc) * p.channels;
+        me[k] = (unsigned)(1 + (hp - oh * p.stride_rows) * p.window_cols + (wp - ow * p.stride_cols));
+        load_bytes<V>(winner + o, win[k]);
+        load_vec<T, V>(dy + o, dv[k]);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k)  // k = 2 * row + column: the same order as the loops below
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+          if (ok[k] && win[k][i] == me[k]) grad[i] += dv[k][i];
+      store_vec<T, V>(dx + (size_t)idx * V, grad);
+      continue;
+    }
     for (int oh = oh_lo; oh < oh_hi; ++oh)
       for (int ow = ow_lo; ow < ow_hi; ++ow) {
         const size_t o = out_n + ((size_t)oh * p.out_cols + ow) * p.channels;
