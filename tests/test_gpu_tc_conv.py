@@ -38,6 +38,15 @@ FWD_SHAPES = [
     (2, 15, 13, 24, 40, 3, 1, True, None),     # ragged rows, column tail
     (3, 9, 9, 16, 16, 5, 2, False, None),      # VALID
     (2, 10, 12, 72, 96, 1, 1, True, None),     # MobileNet-like widths
+    # the kernel's operand-staging variants
+    (2, 56, 56, 64, 64, 3, 1, False, None),    # halo mode (resident filter, 8x16 tiles), VALID: ragged 54x54 output
+    (1, 24, 40, 32, 64, 3, 1, True, None),     # halo mode, tile wider than tall, partial channel block
+    (2, 16, 16, 16, 32, 5, 1, True, None),     # halo mode with a 5x5 window
+    (3, 14, 14, 256, 1024, 1, 1, True, None),  # one resident filter column tile per CTA (8 column tiles)
+    (3, 14, 14, 256, 256, 3, 1, True, None),   # pair mode, 256-column tiles
+    (5, 7, 7, 512, 1024, 3, 1, True, None),    # pair mode, several column tiles, odd number of row tiles
+    (2, 14, 14, 1024, 2048, 1, 2, True, None), # pair mode on a stride-2 projection
+    (2, 28, 28, 512, 128, 1, 1, True, None),   # whole filter resident (128 KB)
 ]
 
 
