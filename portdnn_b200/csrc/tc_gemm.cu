@@ -1034,6 +1034,23 @@ bool pair_enabled() {
   return on;
 }
 
+// Experiments: PDNN_TC_PAIR_MIN = fewest reduction steps that pair, PDNN_TC_PAIR_BN=128 keeps pair
+// mode on 128-column tiles.
+int pair_min_steps() {
+  static const int n = [] {
+    const char* e = getenv("PDNN_TC_PAIR_MIN");
+    return e == nullptr ? 32 : atoi(e);
+  }();
+  return n;
+}
+bool pair_wide() {
+  static const bool on = [] {
+    const char* e = getenv("PDNN_TC_PAIR_BN");
+    return e == nullptr || atoi(e) != 128;
+  }();
+  return on;
+}
+
 // PDNN_TC_GROUPS=1 runs one pipeline per CTA instead of two (for experiments).
 int group_count() {
   static const int n = [] {
@@ -1580,14 +1597,14 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   const int ksteps_all = p.window_rows * p.window_cols * ceil_div(p.channels, epr);
   // Long reductions over filters too large to keep in shared memory are bound by the bytes an SM
   // pulls from L2 per MMA: the two pipelines then share one B tile per stage (pair mode).  Measured
-  // on ResNet-50 shapes it pays from about 32 reduction steps, or from 16 with many column tiles;
+  // on ResNet-50 shapes it pays from about 32 reduction steps, or from 16 with 512 or more features;
   // shorter reductions lose more to the unhidden epilogue of the 256-column accumulators.
   const bool pairing = try_halo && !halo && pair_enabled() && dtype != PDNN_F32 && hwcf && p.features % 128 == 0 &&
-                       (ksteps_all >= 32 || (ksteps_all >= 16 && p.features >= 1024)) && row_tiles >= 2 &&
+                       (ksteps_all >= pair_min_steps() || (ksteps_all >= 16 && p.features >= 512)) && row_tiles >= 2 &&
                        (!epi || epi->beta == 0.f);
   if (pairing) {
     g.pair = 1;
-    g.bn = p.features % 256 == 0 ? 256 : 128;
+    g.bn = (p.features % 256 == 0 && pair_wide()) ? 256 : 128;
     if (g.tiles_w % 2 == 0) {
       g.pair_dim = 1;
       g.tiles_w /= 2;
