@@ -123,6 +123,10 @@ struct alignas(64) GemmArgs {
   // from L2 per MMA, which is what bounds long reductions over wide filters.
   int pair, pair_dim;
   int bias_tile_only;  // 1: the CTA keeps one column tile's bias slice (the grid is a multiple of n_tiles)
+  // Geometry of a reduction step: bytes per A row (128, or 64 for the narrow few-channel stem
+  // layout), MMAs per step (row bytes / 32) and bytes of one step's B tile (bn * row bytes).
+  int a_row_bytes, kmmas;
+  unsigned b_step_bytes;
 };
 
 struct TileCoord {
@@ -468,7 +472,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
   const int grp = SPLIT ? 0 : warp / 6;
   const int role = SPLIT ? warp : warp - grp * 6;  // 0 producer, 1 issuer, 2..5 epilogue, 6..9 split (SPLIT)
 
-  const uint32_t b_bytes = (uint32_t)a.bn * 128u;
+  const uint32_t b_bytes = a.b_step_bytes;
   const uint32_t part_bytes = kABytes + b_bytes;              // one A tile + one B tile
   const bool b_res = !SPLIT && a.b_res != 0;
   const uint32_t res_bytes = b_res ? a.b_res_bytes : 0u;      // resident B tiles come first
@@ -629,7 +633,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
             const CUtensorMap* amap = &a.a_map[e.a_map];
             const int aw = t.w0 + e.dw, ah = t.h0 + e.dh;
             const int btap = e.b_tap + t.n0 * a.b_batch_mul;
-            const uint32_t tx = halo ? (uint32_t)(a.th + e.cnt - 1) * (uint32_t)a.tw * 128u : tx_bytes;
+            const uint32_t tx = halo ? (uint32_t)(a.th + e.cnt - 1) * (uint32_t)(a.tw * a.a_row_bytes) : tx_bytes;
             for (int cb = 0, kc = 0; cb < cblocks; ++cb, kc += epr) {
               if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g_error_record, 0x100u + (unsigned)s)) {
                 ok = false;
@@ -713,7 +717,8 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
         if (!SPLIT && !a.a_mn) {
           // forward-style GEMM: one stage per (tap entry, reduction block); in halo mode a stage
           // feeds the MMAs of all cnt taps of its entry
-          const uint32_t halo_row_bytes = (uint32_t)a.tw * 128u;
+          const uint32_t halo_row_bytes = (uint32_t)(a.tw * a.a_row_bytes);
+          const bool four = a.kmmas == 4;
           for (int tap = 0; tap < a.num_taps && ok; ++tap) {
             const int cnt = halo ? a.taps[tap].cnt : 1;
             for (int cb = 0; cb < a.cblocks; ++cb) {
@@ -733,13 +738,13 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
                 uint64_t da = a_desc0 + (uint64_t)((my_a + (uint32_t)g * halo_row_bytes) >> 4);
                 uint64_t db = b_desc0 + (uint64_t)((b_res ? res_b + (uint32_t)(g * a.cblocks + cb) * b_bytes
                                                           : my_b) >> 4);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  mma_f16(d_tmem, da, db, idesc, accumulate);
-                  accumulate = 1u;
-                  da += a_kadv;
-                  db += b_kadv;
+                mma_f16(d_tmem, da, db, idesc, accumulate);
+                mma_f16(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
+                if (four) {  // 128-byte rows: four 32-byte reduction slices per step; 64-byte rows: two
+                  mma_f16(d_tmem, da + 2 * a_kadv, db + 2 * b_kadv, idesc, 1u);
+                  mma_f16(d_tmem, da + 3 * a_kadv, db + 3 * b_kadv, idesc, 1u);
                 }
+                accumulate = 1u;
               }
               mma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
               if (++s == S) {
@@ -921,7 +926,7 @@ EncodeTiledFn encode_fn() {
 // MMA reads MN-major must be swizzled in 32-byte units (the only MN-major layout tcgen05 accepts
 // for tf32); everything else uses the ordinary 16-byte-unit pattern.
 bool make_map(CUtensorMap* map, int dtype, bool mn_major, const void* base, const uint64_t dims[4],
-              const uint64_t strides_bytes[3], const uint32_t box[4]) {
+              const uint64_t strides_bytes[3], const uint32_t box[4], bool rows64 = false) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) {
     fail(PDNN_ALLOCATION_PROBLEM, "cuTensorMapEncodeTiled is unavailable");
@@ -937,8 +942,10 @@ bool make_map(CUtensorMap* map, int dtype, bool mn_major, const void* base, cons
     b[i] = box[i];
   }
   for (int i = 0; i < 3; ++i) st[i] = strides_bytes[i];
-  const CUtensorMapSwizzle sw =
-      (dtype == PDNN_F32 && mn_major) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+  // rows64: the box is 64 bytes wide and lands as 64-byte rows swizzled in 16-byte units
+  const CUtensorMapSwizzle sw = rows64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                : (dtype == PDNN_F32 && mn_major) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                                                  : CU_TENSOR_MAP_SWIZZLE_128B;
   CUresult r = fn(map, dt, 4, const_cast<void*>(base), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -1014,6 +1021,15 @@ bool choose_box_halo(int W, int H, int rows, int* tw, int* th) {
     }
   }
   return best < 1e29;
+}
+
+// PDNN_TC_NARROW_STEM=0 keeps 8 channels per pixel in the few-channel stem path (for experiments).
+bool narrow_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("PDNN_TC_NARROW_STEM");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  return on;
 }
 
 // PDNN_TC_PDL=0 launches the GEMM kernel without programmatic dependent launch (for experiments).
@@ -1141,6 +1157,9 @@ void set_operand_layout(GemmArgs& g, int dtype, int b_mn) {
     g.b_boxes = 1;
     g.b_box_bytes = (unsigned)g.bn * 128u;
   }
+  g.a_row_bytes = 128;
+  g.kmmas = 4;
+  g.b_step_bytes = (unsigned)g.bn * 128u;
   g.idesc = make_idesc(dtype == PDNN_F32 ? 2 : (dtype == PDNN_BF16 ? 1 : 0), g.a_mn, b_mn, g.bn);
   g.tmem_cols = next_pow2(2 * g.bn);
 }
@@ -1201,7 +1220,7 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
     return g.stages >= 2;
   }
   if (!g.a_mn && !split && g.tma_store && g.b_batch_mul == 0 && b_resident_enabled()) {
-    const size_t res_tile = (size_t)ksteps * g.bn * 128u, res_all = res_tile * g.n_tiles;
+    const size_t res_tile = (size_t)ksteps * g.b_step_bytes, res_all = res_tile * g.n_tiles;
     const int a_stage = g.halo ? (int)g.halo_stage_bytes : kABytes;
     auto fits = [&](size_t res) {
       return res <= kMaxResidentB && res % 1024 == 0 &&
@@ -1410,10 +1429,31 @@ __global__ void __launch_bounds__(256) pack_small_c_input_kernel(const T* __rest
   }
 }
 
+// The same with 4 channels of 16 bits per pixel (8 bytes): half the bytes for a 3-channel image.
+__global__ void __launch_bounds__(256) pack_small_c_input_narrow_kernel(const unsigned short* __restrict__ x,
+                                                                       uint2* __restrict__ xp, int N, int H, int W,
+                                                                       int C, int Hp, int Wp, int pad_top,
+                                                                       int pad_left) {
+  const size_t total = (size_t)N * Hp * Wp;
+  for (size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
+    const int wp = (int)(idx % Wp);
+    const size_t t = idx / Wp;
+    const int hp = (int)(t % Hp);
+    const int n = (int)(t / Hp);
+    const int h = hp - pad_top, w = wp - pad_left;
+    unsigned v[4] = {0u, 0u, 0u, 0u};
+    if (h >= 0 && h < H && w >= 0 && w < W) {
+      const unsigned short* src = x + (((size_t)n * H + h) * W + w) * C;
+      for (int c = 0; c < C && c < 4; ++c) v[c] = src[c];
+    }
+    xp[idx] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
+  }
+}
+
+// Filter [R][S][C][K] -> [R][8][CP][K], zeros for s >= S and c >= C.
 template <typename T>
 __global__ void __launch_bounds__(256) pack_small_c_filter_kernel(const T* __restrict__ w, T* __restrict__ wp, int R,
-                                                                 int S, int C, int K) {
-  constexpr int CP = 16 / sizeof(T);
+                                                                 int S, int C, int K, int CP) {
   const size_t total = (size_t)R * 8 * CP * K;
   for (size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
     const int k = (int)(idx % K);
@@ -1496,15 +1536,33 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
   g.bn = pick_bn((long long)g.tiles_w * g.tiles_h * g.tiles_n, p.features, epr, dtype == PDNN_F32 ? 128 : 256, sms);
   g.n_tiles = ceil_div(p.features, g.bn);
   set_operand_layout(g, dtype, 1);
-  const size_t row_pitch = (size_t)sp.Wp * 16;
+  // Narrow layout (16-bit, at most 4 channels, even column stride, halo mode): 4 channels per pixel,
+  // so a filter row of 8 pixels is 64 bytes and a reduction step is two MMAs instead of four, with
+  // half the bytes to pack, load and multiply.  The tiles are 64-byte rows with the 64-byte
+  // swizzle; a pixel step of stride_cols * 8 bytes is still a multiple of TMA's 16 bytes.
+  const bool narrow = halo && narrow_enabled() && p.channels <= 4 && p.stride_cols % 2 == 0;
+  const int pix_bytes = narrow ? 8 : 16;
+  const int krows = narrow ? 32 : epr;            // reduction elements per step
+  const int Wp = narrow ? (sp.Wp + 1) / 2 * 2 : sp.Wp;  // narrow: rows stay 16-byte aligned
+  if (narrow) {
+    g.a_row_bytes = 64;
+    g.kmmas = 2;
+    g.a_sbo = 512;   // 8 rows of 64 bytes
+    g.a_layout = 4;  // 64-byte swizzle
+    g.b_lbo = (unsigned)krows * 128u;
+    g.b_box_bytes = (unsigned)krows * 128u;
+    g.b_step_bytes = (unsigned)g.bn * 64u;
+  }
+  const size_t row_pitch = (size_t)Wp * pix_bytes;
   for (int q = 0; q < p.stride_rows; ++q) {
     const int Hq = ceil_div(sp.Hp - q, p.stride_rows);
-    const uint64_t dims[4] = {(uint64_t)epr, (uint64_t)p.out_cols, (uint64_t)std::max(Hq, 1), (uint64_t)p.batch};
-    const uint64_t st[3] = {(uint64_t)p.stride_cols * 16, (uint64_t)p.stride_rows * row_pitch, (uint64_t)sp.Hp * row_pitch};
+    const uint64_t dims[4] = {(uint64_t)krows, (uint64_t)p.out_cols, (uint64_t)std::max(Hq, 1), (uint64_t)p.batch};
+    const uint64_t st[3] = {(uint64_t)p.stride_cols * pix_bytes, (uint64_t)p.stride_rows * row_pitch,
+                            (uint64_t)sp.Hp * row_pitch};
     // filter rows q, q + stride, ... read this parity class
     const int cnt = (p.window_rows - q + p.stride_rows - 1) / p.stride_rows;
-    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)(halo ? g.th + cnt - 1 : g.th), (uint32_t)g.tn};
-    if (!make_map(&g.a_map[q], dtype, false, xp + (size_t)q * row_pitch, dims, st, box)) {
+    const uint32_t box[4] = {(uint32_t)krows, (uint32_t)g.tw, (uint32_t)(halo ? g.th + cnt - 1 : g.th), (uint32_t)g.tn};
+    if (!make_map(&g.a_map[q], dtype, false, xp + (size_t)q * row_pitch, dims, st, box, narrow)) {
       release();
       return -1;
     }
@@ -1517,7 +1575,7 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
     for (int q = 0; q < p.stride_rows; ++q) {
       const int cnt = (p.window_rows - q + p.stride_rows - 1) / p.stride_rows;
       g.taps[q] = TapEntry{0, 0, (short)q, (short)q, (short)cnt, (short)p.stride_rows};
-      widest = std::max(widest, (unsigned)(g.tw * (g.th + cnt - 1) * 128));
+      widest = std::max(widest, (unsigned)(g.tw * (g.th + cnt - 1) * g.a_row_bytes));
     }
     g.num_taps = p.stride_rows;
     g.halo_stage_bytes = (widest + 1023u) & ~1023u;
@@ -1529,30 +1587,36 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
   g.cblocks = 1;
   {
     g.b_mode = B_MN_3;
-    const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)epr, (uint64_t)p.window_rows, 1};
-    const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)epr * p.features * es,
-                            (uint64_t)p.window_rows * epr * p.features * es};
-    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
+    const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)krows, (uint64_t)p.window_rows, 1};
+    const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)krows * p.features * es,
+                            (uint64_t)p.window_rows * krows * p.features * es};
+    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)krows, 1, 1};
     if (!make_map(&g.b_map, dtype, true, wpk, dims, st, box)) {
       release();
       return -1;
     }
   }
-  const size_t n_pix = (size_t)p.batch * sp.Hp * sp.Wp;
-  const size_t n_fil = (size_t)p.window_rows * epr * p.features;
+  const size_t n_pix = (size_t)p.batch * sp.Hp * Wp;
+  const size_t n_fil = (size_t)p.window_rows * krows * p.features;
   if (dtype == PDNN_F32) {
     pack_small_c_input_kernel<float><<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
         static_cast<const float*>(x), reinterpret_cast<uint4*>(xp), p.batch, p.in_rows, p.in_cols, p.channels, sp.Hp,
         sp.Wp, p.pad_rows, p.pad_cols);
     pack_small_c_filter_kernel<float><<<grid_for(n_fil, 256, sms), 256, 0, s>>>(
-        static_cast<const float*>(w), reinterpret_cast<float*>(wpk), p.window_rows, p.window_cols, p.channels, p.features);
+        static_cast<const float*>(w), reinterpret_cast<float*>(wpk), p.window_rows, p.window_cols, p.channels, p.features, 4);
   } else {
     // fp16 and bf16 are both moved as 16-bit words
-    pack_small_c_input_kernel<__half><<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
-        static_cast<const __half*>(x), reinterpret_cast<uint4*>(xp), p.batch, p.in_rows, p.in_cols, p.channels, sp.Hp,
-        sp.Wp, p.pad_rows, p.pad_cols);
+    if (narrow)
+      pack_small_c_input_narrow_kernel<<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
+          static_cast<const unsigned short*>(x), reinterpret_cast<uint2*>(xp), p.batch, p.in_rows, p.in_cols, p.channels,
+          sp.Hp, Wp, p.pad_rows, p.pad_cols);
+    else
+      pack_small_c_input_kernel<__half><<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
+          static_cast<const __half*>(x), reinterpret_cast<uint4*>(xp), p.batch, p.in_rows, p.in_cols, p.channels, sp.Hp,
+          sp.Wp, p.pad_rows, p.pad_cols);
     pack_small_c_filter_kernel<__half><<<grid_for(n_fil, 256, sms), 256, 0, s>>>(
-        static_cast<const __half*>(w), reinterpret_cast<__half*>(wpk), p.window_rows, p.window_cols, p.channels, p.features);
+        static_cast<const __half*>(w), reinterpret_cast<__half*>(wpk), p.window_rows, p.window_cols, p.channels, p.features,
+        narrow ? 4 : 8);
   }
   int st = check_launch("conv2d small-channel packing");
   count_launch();
