@@ -702,57 +702,89 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       uint32_t buf = 0, aph = 0;  // accumulator buffer of this tile and the parity of its barriers
       bool ok = true;
       if (b_res && first_tile < total_tiles) ok = mbar_wait(bres_bar, 0u, abort_flag, g_error_record, 0x600u);
-      const uint32_t res_tile_bytes = (uint32_t)(a.res_taps * a.cblocks) * b_bytes;  // one column tile's B
+      // Loop constants of the forward-style main loop, all in units of 16 bytes (the unit of a
+      // descriptor's address field).
+      struct {
+        uint32_t a_lo0, a_hi, b_lo0, b_hi;  // descriptor words without a start address
+        uint32_t ring16, stage16;           // this group's ring and the size of a stage
+        uint32_t my_a16, my_b16;            // this group's A tile and the B tile inside a stage
+        uint32_t halo_row16;                // halo mode: one tile row further down
+        uint32_t b_tap16, b_bytes16;        // resident B: next tap of the entry, next reduction block
+        uint32_t res16_base, res_tile16;    // resident B: first tile, tiles of one column tile
+        uint32_t cnts;                      // taps per entry, 4 bits each (1 outside halo mode)
+        int num_taps, cblocks;
+        bool four;
+      } fw;
+      fw.a_lo0 = (uint32_t)a_desc0;
+      fw.a_hi = (uint32_t)(a_desc0 >> 32);
+      fw.b_lo0 = (uint32_t)b_desc0;
+      fw.b_hi = (uint32_t)(b_desc0 >> 32);
+      fw.ring16 = ring_base >> 4;
+      fw.stage16 = stage_bytes >> 4;
+      fw.my_a16 = pair ? ((uint32_t)grp * kABytes) >> 4 : 0u;
+      fw.my_b16 = (pair ? 2u * kABytes : (uint32_t)kABytes) >> 4;
+      fw.halo_row16 = (uint32_t)(a.tw * a.a_row_bytes) >> 4;
+      fw.b_bytes16 = b_bytes >> 4;
+      fw.b_tap16 = (uint32_t)a.cblocks * (b_bytes >> 4);
+      fw.res16_base = base >> 4;
+      fw.res_tile16 = (uint32_t)(a.res_taps * a.cblocks) * (b_bytes >> 4);
+      fw.num_taps = a.num_taps;
+      fw.cblocks = a.cblocks;
+      fw.four = a.kmmas == 4;
+      fw.cnts = 0u;  // halo mode has at most 8 entries of at most 15 taps (checked by the host)
+      if (halo)
+        for (int i = 0; i < a.num_taps && i < 8; ++i) fw.cnts |= (uint32_t)(a.taps[i].cnt & 15) << (4 * i);
+      uint32_t sa16 = fw.ring16;  // start of the current stage
       TileWalker walker;
       walker.init(a, first_tile, tile_step);
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++tcount, walker.advance()) {
         if (grp == 0) PDNN_TRACE(0, tcount);
         const TileCoord t = walker.coord(a);
         if (!mbar_wait(acc_empty_bar((int)buf), aph ^ 1u, abort_flag, g_error_record, 0x200u + buf)) break;
-        uint32_t res_b = a.b_res == 1 ? base + (uint32_t)t.nt * res_tile_bytes : base;
         if (grp == 0) PDNN_TRACE(1, tcount);
         tc_fence_after_sync();
         const uint32_t d_tmem = grp_tmem + buf * acc_stride;
         uint32_t accumulate = 0u;
         if (!SPLIT && !a.a_mn) {
-          // forward-style GEMM: one stage per (tap entry, reduction block); in halo mode a stage
-          // feeds the MMAs of all cnt taps of its entry
-          const uint32_t halo_row_bytes = (uint32_t)(a.tw * a.a_row_bytes);
-          const bool four = a.kmmas == 4;
-          for (int tap = 0; tap < a.num_taps && ok; ++tap) {
-            const int cnt = halo ? a.taps[tap].cnt : 1;
-            for (int cb = 0; cb < a.cblocks; ++cb) {
+          // Forward-style GEMM: one stage per (tap entry, reduction block); in halo mode a stage
+          // feeds the MMAs of all cnt taps of its entry.  Everything in this loop is kept to
+          // 32-bit additions on values prepared outside it: the lone issuing thread is what bounds
+          // tiles of 64 or 128 columns, and it needs the tile's nt only (the walker's digit 0).
+          uint32_t res16 = fw.res16_base + (a.b_res == 1 ? (uint32_t)walker.d0 * fw.res_tile16 : 0u);
+          for (int tap = 0; tap < fw.num_taps && ok; ++tap) {
+            const int cnt = halo ? (int)((fw.cnts >> (4 * tap)) & 15u) : 1;
+            for (int cb = 0; cb < fw.cblocks; ++cb) {
               if (!mbar_wait(full_bar(s), ph, abort_flag, g_error_record, 0x300u + (unsigned)s)) {
                 ok = false;
                 break;
               }
               tc_fence_after_sync();
               if (grp == 0 && tap == 0 && cb == 0) PDNN_TRACE(2, tcount);
-              const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
-              // pair mode: [A of group 0 | A of group 1 | B]
-              const uint32_t my_a = pair ? sa + (uint32_t)grp * kABytes : sa;
-              const uint32_t my_b = pair ? sa + 2u * kABytes : sa + kABytes;
+              // start addresses stay below 2^18, so adding to the low descriptor word never carries
+              // into the neighbouring field
+              uint32_t a_lo = fw.a_lo0 + sa16 + fw.my_a16;
+              uint32_t b_lo = b_res ? fw.b_lo0 + res16 + (uint32_t)cb * fw.b_bytes16 : fw.b_lo0 + sa16 + fw.my_b16;
               for (int g = 0; g < cnt; ++g) {
-                // start addresses stay below 2^18, so adding to the low word never carries into
-                // the neighbouring descriptor field
-                uint64_t da = a_desc0 + (uint64_t)((my_a + (uint32_t)g * halo_row_bytes) >> 4);
-                uint64_t db = b_desc0 + (uint64_t)((b_res ? res_b + (uint32_t)(g * a.cblocks + cb) * b_bytes
-                                                          : my_b) >> 4);
+                const uint64_t da = ((uint64_t)fw.a_hi << 32) | a_lo, db = ((uint64_t)fw.b_hi << 32) | b_lo;
                 mma_f16(d_tmem, da, db, idesc, accumulate);
                 mma_f16(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
-                if (four) {  // 128-byte rows: four 32-byte reduction slices per step; 64-byte rows: two
+                if (fw.four) {  // 128-byte rows: four 32-byte reduction slices per step; 64-byte rows: two
                   mma_f16(d_tmem, da + 2 * a_kadv, db + 2 * b_kadv, idesc, 1u);
                   mma_f16(d_tmem, da + 3 * a_kadv, db + 3 * b_kadv, idesc, 1u);
                 }
                 accumulate = 1u;
+                a_lo += fw.halo_row16;
+                b_lo += fw.b_tap16;
               }
               mma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+              sa16 += fw.stage16;
               if (++s == S) {
                 s = 0;
                 ph ^= 1u;
+                sa16 = fw.ring16;
               }
             }
-            res_b += (uint32_t)(cnt * a.cblocks) * b_bytes;
+            res16 += (uint32_t)cnt * fw.b_tap16;
           }
         } else {
           for (int ks = t.ks_begin; ks < t.ks_end; ++ks) {
@@ -1518,8 +1550,8 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
   // parity class is one reduction step over one copy.
   const int rows_per_class = ceil_div(p.window_rows, p.stride_rows);
   int hw = 0, hh = 0;
-  const bool halo = try_halo && halo_enabled() && dtype != PDNN_F32 && rows_per_class >= 2 &&
-                    p.window_rows >= p.stride_rows && choose_box_halo(p.out_cols, p.out_rows, rows_per_class, &hw, &hh);
+  const bool halo = try_halo && halo_enabled() && dtype != PDNN_F32 && rows_per_class >= 2 && rows_per_class <= 15 &&
+                    p.stride_rows <= 8 && p.window_rows >= p.stride_rows && choose_box_halo(p.out_cols, p.out_rows, rows_per_class, &hw, &hh);
   if (halo) {
     g.tw = hw;
     g.th = hh;
@@ -1640,7 +1672,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   // filter can stay in shared memory.
   int hw = 0, hh = 0;
   const bool halo = try_halo && halo_enabled() && dtype != PDNN_F32 && p.stride_rows == 1 && p.stride_cols == 1 &&
-                    p.window_rows >= 2 &&
+                    p.window_rows >= 2 && p.window_rows <= 15 && p.window_cols <= 8 &&
                     (size_t)p.window_rows * p.window_cols * ceil_div(p.channels, epr) * 128u *
                             (size_t)(ceil_div(p.features, 64) * 64) <= kMaxResidentB &&
                     choose_box_halo(p.out_cols, p.out_rows, p.window_rows, &hw, &hh);
