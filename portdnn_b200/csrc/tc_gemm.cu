@@ -758,7 +758,8 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
                 ok = false;
                 break;
               }
-              tc_fence_after_sync();
+              // no tcgen05 fence here: the stage was written by TMA and is read by the MMA, both in
+              // the async proxy, and the mbarrier's complete_tx orders them
               if (grp == 0 && tap == 0 && cb == 0) PDNN_TRACE(2, tcount);
               // start addresses stay below 2^18, so adding to the low descriptor word never carries
               // into the neighbouring field
@@ -1774,7 +1775,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
 }
 
 int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, const PdnnConv2DParams& p,
-                        cudaStream_t s) {
+                        cudaStream_t s, bool try_halo = true) {
   const size_t es = dtype_size(dtype);
   const int sms = device_sm_count();
   const bool hwcf = p.filter_format == 0;
@@ -1789,7 +1790,21 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
       GemmArgs g;
       std::memset(&g, 0, sizeof(g));
       g.a_mn = 0;
-      choose_box(kTileM, Wq, Hq, p.batch, &g.tw, &g.th, &g.tn);
+      // Stride 1: the taps of one window column read overlapping rows of dy, as in the forward
+      // pass (halo mode), if the whole filter can stay in shared memory.
+      int hw = 0, hh = 0;
+      const bool halo = try_halo && halo_enabled() && dtype != PDNN_F32 && p.stride_rows == 1 && p.stride_cols == 1 &&
+                        p.window_rows >= 2 && p.window_rows <= 15 && p.window_cols <= 8 &&
+                        (size_t)p.window_rows * p.window_cols * ceil_div(p.features, epr) * 128u *
+                                (size_t)(ceil_div(p.channels, 64) * 64) <= kMaxResidentB &&
+                        choose_box_halo(Wq, Hq, p.window_rows, &hw, &hh);
+      if (halo) {
+        g.tw = hw;
+        g.th = hh;
+        g.tn = 1;
+      } else {
+        choose_box(kTileM, Wq, Hq, p.batch, &g.tw, &g.th, &g.tn);
+      }
       g.etw = g.tw;
       g.eth = g.th;
       g.etn = g.tn;
@@ -1804,12 +1819,23 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
         const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)p.out_cols, (uint64_t)p.out_rows, (uint64_t)p.batch};
         const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.out_cols * p.features * es,
                                 (uint64_t)p.out_rows * p.out_cols * p.features * es};
-        const uint32_t box[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)g.th, (uint32_t)g.tn};
+        const uint32_t box[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)(halo ? g.th + p.window_rows - 1 : g.th),
+                                 (uint32_t)g.tn};
         if (!make_map(&g.a_map[0], dtype, false, dy, dims, st, box)) return PDNN_INVALID_PARAMETER;
         for (int i = 1; i < 4; ++i) g.a_map[i] = g.a_map[0];
       }
       int nt = 0;
-      for (int r = 0; r < p.window_rows; ++r) {
+      if (halo) {
+        // window column c: filter rows R-1 .. 0 read dy rows pad - (R-1) .. pad, in that order
+        g.halo = 1;
+        g.res_taps = p.window_rows * p.window_cols;
+        g.halo_stage_bytes = ((unsigned)(g.tw * (g.th + p.window_rows - 1) * 128) + 1023u) & ~1023u;
+        for (int c = 0; c < p.window_cols; ++c)
+          g.taps[nt++] = TapEntry{(short)(p.pad_cols - c), (short)(p.pad_rows - (p.window_rows - 1)), 0,
+                                  (short)((p.window_rows - 1) * p.window_cols + c), (short)p.window_rows,
+                                  (short)(-p.window_cols)};
+      }
+      for (int r = 0; r < p.window_rows && !halo; ++r) {
         const int th = qh + p.pad_rows - r;
         if (pos_mod(th, p.stride_rows) != 0) continue;
         for (int c = 0; c < p.window_cols; ++c) {
@@ -1820,6 +1846,8 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
           e.dw = (short)floor_div(tw, p.stride_cols);
           e.a_map = 0;
           e.b_tap = (short)(r * p.window_cols + c);
+          e.cnt = 1;
+          e.b_step = 0;
           g.taps[nt++] = e;
         }
       }
@@ -1856,7 +1884,10 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
         const uint64_t os[3] = {(uint64_t)p.stride_cols * p.channels * es,
                                 (uint64_t)p.stride_rows * p.in_cols * p.channels * es,
                                 (uint64_t)p.in_rows * p.in_cols * p.channels * es};
-        if (!setup_store(g, dtype, od, os)) return PDNN_INVALID_PARAMETER;
+        if (!setup_store(g, dtype, od, os)) {
+          if (g.halo) return conv_input_backprop(dtype, dy, w, dx, p, s, false);  // plan again without the halo
+          return PDNN_INVALID_PARAMETER;
+        }
       }
       const int st_ = launch_gemm(g, dtype, s);
       if (st_ != PDNN_OK) return st_;
@@ -1883,7 +1914,7 @@ FbpPlan plan_filter_backprop(int dtype, const PdnnConv2DParams& p, int sms) {
   const long long total_slabs = (long long)f.slabs_w * f.slabs_h * f.slabs_n;
   long long want = std::max<long long>(1, (2ll * sms) / out_tiles);
   want = std::min<long long>(want, std::max<long long>(1, total_slabs / 8));  // at least 8 slabs per split
-  want = std::min<long long>(want, 64);
+  want = std::min<long long>(want, 512);
   f.slabs_per_split = (int)((total_slabs + want - 1) / want);
   f.splits = (int)((total_slabs + f.slabs_per_split - 1) / f.slabs_per_split);
   return f;
@@ -1948,7 +1979,7 @@ SmallCFbpPlan plan_small_c_fbp(int dtype, const PdnnConv2DParams& p, int sms) {
   const long long total_slabs = (long long)f.slabs_w * f.slabs_h * f.slabs_n;
   long long want = std::max<long long>(1, (2ll * sms) / out_tiles);
   want = std::min<long long>(want, std::max<long long>(1, total_slabs / 8));
-  want = std::min<long long>(want, 64);
+  want = std::min<long long>(want, 512);
   f.slabs_per_split = (int)((total_slabs + want - 1) / want);
   f.splits = (int)((total_slabs + f.slabs_per_split - 1) / f.slabs_per_split);
   q.partial_bytes = (((size_t)f.splits * p.window_rows * epr * p.features * sizeof(float)) + 255) / 256 * 256;

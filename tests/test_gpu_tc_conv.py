@@ -95,6 +95,10 @@ BWD_SHAPES = [
     (3, 7, 7, 512, 512, 3, 1, True, None),
     (2, 15, 13, 24, 40, 3, 1, True, None),
     (2, 17, 17, 16, 32, 5, 2, False, None),
+    (2, 56, 56, 64, 64, 3, 1, False, None),    # input backprop in halo mode, VALID (ragged rows)
+    (1, 24, 40, 32, 64, 3, 1, True, None),     # halo mode, wide tiles
+    (2, 16, 16, 16, 32, 5, 1, True, None),     # halo mode, 5x5 window
+    (2, 56, 56, 64, 256, 1, 1, True, None),    # 1x1: a single filter-gradient tile, many pixel splits
 ]
 
 
