@@ -27,10 +27,10 @@ sys.path.insert(0, ROOT)
 
 METRIC = "conv_tflops_resnet50_fp16_b256_forward"
 # dram__bytes_read.sum + dram__bytes_write.sum of the 53 conv launches of one forward step, from an
-# ncu capture of this script (profiles/bench_resnet50_forward_dram_traffic.md): 5111 MB read +
-# 3490 MB written = 8601 MB per step, against 11.76 GB of algorithmic bytes (input + filter + output
+# ncu capture of this script (profiles/bench_resnet50_forward_dram_traffic.md): 5003 MB read +
+# 3486 MB written = 8489 MB per step, against 11.76 GB of algorithmic bytes (input + filter + output
 # of every layer once) - the small feature maps are still in L2 when the next layer reads them.
-FORWARD_DRAM_BYTES_PER_LAUNCH = int(8601e6 / 53)
+FORWARD_DRAM_BYTES_PER_LAUNCH = int(8489e6 / 53)
 UNIT = "TFLOP/s"
 BATCH = 256
 
