@@ -93,6 +93,20 @@ typedef struct PdnnPoolingParams {
   int input_format;
 } PdnnPoolingParams;
 
+/* Mirror of sycldnn::softmax::SoftmaxParams (include/portdnn/softmax/params.h:27-54). */
+typedef struct PdnnSoftmaxParams {
+  int channels, batch, rows, cols;
+  int input_format; /* 0 = NHWC (the only layout implemented) */
+} PdnnSoftmaxParams;
+
+/* Mirror of sycldnn::batchnorm::BatchNormParams (include/portdnn/batchnorm/params.h:32-72). */
+typedef struct PdnnBatchNormParams {
+  int batch, rows, cols, channels;
+  int is_training; /* 0: frozen (population statistics handed in), 1: training */
+  float epsilon, momentum;
+  int input_format; /* 0 = NHWC (the only layout implemented) */
+} PdnnBatchNormParams;
+
 /* Optional fused epilogue of the forward convolution: out = act(alpha*conv + bias[k]) + beta*out_prev.
  * The reference has no fused form: it issues binaryop Add (tools/layer.h:100-125), a pointwise
  * launch (tools/layer.h:207-228) and the compat alpha/beta blend (include/portdnn/compat/scaling.hpp:202-281)
@@ -167,6 +181,30 @@ int pdnn_pooling(int op, int direction, int dtype, const void* input, void* outp
 int pdnn_pooling_max_grad(int op, int dtype, const void* input_data, const void* output_data,
                           const void* input_backprop, void* output_backprop,
                           const PdnnPoolingParams* params, void* stream);
+
+/* Replaces softmax::launch<T, Forward / Gradient> (include/portdnn/softmax/launch.h:64-165):
+ * y = exp(x - max) / sum exp(x - max) over the channels of each pixel.  direction 0: input = x,
+ * gradient unused.  direction 1: input = the forward OUTPUT y, gradient = dy,
+ * output = (dy - sum_c(dy * y)) * y.  No workspace is needed (the reference's is ignored). */
+int pdnn_softmax(int direction, int dtype, const void* input, const void* gradient, void* output,
+                 const PdnnSoftmaxParams* params, void* stream);
+
+/* Replaces batchnorm::launch<T, Backend, Forward> (include/portdnn/batchnorm/launch.h:222-330).
+ * output = (x - mean) / sqrt(variance + eps) * gamma + beta with the mean and variance HANDED IN,
+ * in both modes (include/portdnn/internal/batchnorm/launch_internal.h:95-158).  Training
+ * additionally writes running_mean = batch_mean * (1 - momentum) + mean * momentum and
+ * running_variance likewise from the biased batch variance; frozen ignores the running pointers. */
+int pdnn_batchnorm_forward(int dtype, const void* input, const void* beta, const void* gamma, const void* mean,
+                           const void* variance, void* running_mean, void* running_variance, void* output,
+                           const PdnnBatchNormParams* params, void* stream);
+
+/* Replaces batchnorm::launch<T, Backend, Gradient> (include/portdnn/batchnorm/launch.h:332-444):
+ * input gradient, beta gradient (sum dy) and gamma gradient.  Training uses the batch statistics
+ * of `input`; frozen uses pop_mean / pop_variance (ignored when training)
+ * (launch_internal.h:318-640). */
+int pdnn_batchnorm_gradient(int dtype, const void* input, const void* gradient, const void* gamma,
+                            const void* pop_mean, const void* pop_variance, void* beta_grad, void* gamma_grad,
+                            void* output, const PdnnBatchNormParams* params, void* stream);
 
 /* Replaces pointwise::launch forward / gradient (include/portdnn/pointwise/launch.h:61-179).
  * The gradient's first tensor is the forward OUTPUT, as the reference kernel treats it

@@ -200,6 +200,56 @@ def matmul(tl, tr, lhs, rhs, batches, m, k, n, beta=0.0, out=None):
     return res
 
 
+def _out(n):
+    a = np.empty(n, dtype=np.float32)
+    return a, a.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+
+
+def softmax_forward(x, channels):
+    x, px = _f(x)
+    y, py = _out(x.size)
+    lib().orc_softmax_forward(px, py, ctypes.c_size_t(x.size // channels), int(channels))
+    return y
+
+
+def softmax_grad(y, dy, channels):
+    y, py = _f(y)
+    dy, pdy = _f(dy)
+    dx, pdx = _out(y.size)
+    lib().orc_softmax_grad(py, pdy, pdx, ctypes.c_size_t(y.size // channels), int(channels))
+    return dx
+
+
+def batchnorm_forward(x, beta, gamma, mean, var, channels, eps=1e-3, momentum=0.9, training=False):
+    """-> (output, running_mean, running_variance); the last two are None unless training."""
+    x, px = _f(x)
+    beta, pb = _f(beta)
+    gamma, pg = _f(gamma)
+    mean, pm = _f(mean)
+    var, pv = _f(var)
+    out, po = _out(x.size)
+    rm, prm = _out(channels)
+    rv, prv = _out(channels)
+    lib().orc_batchnorm_forward(px, pb, pg, pm, pv, po, prm, prv, ctypes.c_size_t(x.size // channels), int(channels),
+                                ctypes.c_float(eps), ctypes.c_float(momentum), int(bool(training)))
+    return (out, rm, rv) if training else (out, None, None)
+
+
+def batchnorm_grad(x, dy, gamma, pop_mean, pop_var, channels, eps=1e-3, training=False):
+    """-> (input gradient, beta gradient, gamma gradient)."""
+    x, px = _f(x)
+    dy, pdy = _f(dy)
+    gamma, pg = _f(gamma)
+    pop_mean, pm = _f(pop_mean if pop_mean is not None else np.zeros(channels))
+    pop_var, pv = _f(pop_var if pop_var is not None else np.ones(channels))
+    out, po = _out(x.size)
+    bg, pbg = _out(channels)
+    gg, pgg = _out(channels)
+    lib().orc_batchnorm_grad(px, pdy, pg, pm, pv, pbg, pgg, po, ctypes.c_size_t(x.size // channels), int(channels),
+                             ctypes.c_float(eps), int(bool(training)))
+    return out, bg, gg
+
+
 def iota(size, max_val):
     """1, 2, ..., max_val, 1, 2, ... ; max_val < 1 means no wrap
     (reference test/gen/iota_initialised_data.h:45-79)."""

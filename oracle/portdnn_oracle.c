@@ -503,6 +503,111 @@ int orc_matmul(int tl, int tr, const float* lhs, const float* rhs, float* out, i
   return 0;
 }
 
+/* ------------------------------------------------------------------------- */
+/* softmax, batchnorm (NHWC: `rows` pixels of C channels)                     */
+/* ------------------------------------------------------------------------- */
+
+/* y = exp(x - max_c x) / sum_c exp(x - max_c x) per pixel: the reference's five passes
+ * (reduce Max, Sub, Exp, reduce Add, Div),
+ * include/portdnn/internal/softmax/launch_internal.h:45-115. */
+int orc_softmax_forward(const float* x, float* y, size_t rows, int C) {
+  for (size_t i = 0; i < rows; ++i) {
+    const float* xi = x + i * C;
+    float* yi = y + i * C;
+    float m = xi[0];
+    for (int c = 1; c < C; ++c) m = fmaxf(m, xi[c]);
+    float sum = 0.f;
+    for (int c = 0; c < C; ++c) {
+      yi[c] = expf(xi[c] - m);
+      sum += yi[c];
+    }
+    for (int c = 0; c < C; ++c) yi[c] = yi[c] / sum;
+  }
+  return 0;
+}
+
+/* dx = (dy - sum_c(dy * y)) * y, with y the forward OUTPUT passed as `input`
+ * (launch_internal.h:215-275: Mul, reduce Add, Sub, Mul). */
+int orc_softmax_grad(const float* y, const float* dy, float* dx, size_t rows, int C) {
+  for (size_t i = 0; i < rows; ++i) {
+    float sum = 0.f;
+    for (int c = 0; c < C; ++c) sum += dy[i * C + c] * y[i * C + c];
+    for (int c = 0; c < C; ++c) dx[i * C + c] = (dy[i * C + c] - sum) * y[i * C + c];
+  }
+  return 0;
+}
+
+/* Batchnorm forward (include/portdnn/internal/batchnorm/launch_internal.h:95-158,187-310).
+ * out = (x - mean) / sqrt(var + eps) * gamma + beta with the mean / variance HANDED IN, in both
+ * modes.  Training additionally writes run_mean = batch_mean * (1 - m) + mean * m and
+ * run_var = batch_var * (1 - m) + var * m, batch_var = mean((x - batch_mean)^2) (biased). */
+int orc_batchnorm_forward(const float* x, const float* beta, const float* gamma, const float* mean,
+                          const float* var, float* out, float* run_mean, float* run_var, size_t rows,
+                          int C, float eps, float momentum, int training) {
+  for (size_t i = 0; i < rows; ++i)
+    for (int c = 0; c < C; ++c)
+      out[i * C + c] = (x[i * C + c] - mean[c]) / sqrtf(var[c] + eps) * gamma[c] + beta[c];
+  if (!training) return 0;
+  for (int c = 0; c < C; ++c) {
+    double sum = 0.0;
+    for (size_t i = 0; i < rows; ++i) sum += x[i * C + c];
+    const float bm = (float)(sum / (double)rows);
+    double sq = 0.0;
+    for (size_t i = 0; i < rows; ++i) {
+      const float d = x[i * C + c] - bm;
+      sq += (double)d * d;
+    }
+    const float bv = (float)(sq / (double)rows);
+    run_mean[c] = bm * (1.f - momentum) + mean[c] * momentum;
+    run_var[c] = bv * (1.f - momentum) + var[c] * momentum;
+  }
+  return 0;
+}
+
+/* Batchnorm gradient (launch_internal.h:318-535 training, 537-640 frozen).
+ * Training: beta_grad = sum dy; with xc = x - batch_mean, v = batch_var + eps:
+ *   gamma_grad = sum(dy * xc) / sqrt(v)
+ *   out = ((dy - mean(dy)) - xc * (sum(dy * xc) / n / v)) * gamma / sqrt(v)
+ * Frozen (population mean / variance handed in), s = sqrt(pop_var + eps):
+ *   beta_grad = sum dy; gamma_grad = sum((x - pop_mean) * dy / s); out = dy * (gamma / s). */
+int orc_batchnorm_grad(const float* x, const float* dy, const float* gamma, const float* pop_mean,
+                       const float* pop_var, float* beta_grad, float* gamma_grad, float* out, size_t rows,
+                       int C, float eps, int training) {
+  for (int c = 0; c < C; ++c) {
+    double sdy = 0.0;
+    for (size_t i = 0; i < rows; ++i) sdy += dy[i * C + c];
+    beta_grad[c] = (float)sdy;
+    if (training) {
+      double sx = 0.0;
+      for (size_t i = 0; i < rows; ++i) sx += x[i * C + c];
+      const float bm = (float)(sx / (double)rows);
+      double sq = 0.0, sdx = 0.0;
+      for (size_t i = 0; i < rows; ++i) {
+        const float d = x[i * C + c] - bm;
+        sq += (double)d * d;
+        sdx += (double)dy[i * C + c] * d;
+      }
+      const float v = (float)(sq / (double)rows) + eps;
+      const float sd = sqrtf(v);
+      const float mean_dy = (float)sdy / (float)rows;
+      const float k = (float)sdx / (float)rows / v;
+      gamma_grad[c] = (float)sdx / sd;
+      for (size_t i = 0; i < rows; ++i) {
+        const float d = x[i * C + c] - bm;
+        out[i * C + c] = ((dy[i * C + c] - mean_dy) - d * k) * gamma[c] / sd;
+      }
+    } else {
+      const float sd = sqrtf(pop_var[c] + eps);
+      double sg = 0.0;
+      for (size_t i = 0; i < rows; ++i) sg += (double)((x[i * C + c] - pop_mean[c]) * dy[i * C + c] / sd);
+      gamma_grad[c] = (float)sg;
+      const float k = gamma[c] / sd;
+      for (size_t i = 0; i < rows; ++i) out[i * C + c] = dy[i * C + c] * k;
+    }
+  }
+  return 0;
+}
+
 /* TF-style padding (include/portdnn/helpers/padding.h:46-66): returns out size and
  * stores the low-side pad. */
 int orc_padding(int in, int window, int stride, int same, int* pad_low) {

@@ -57,6 +57,17 @@ class PoolingParams(ctypes.Structure):
                      "stride_cols", "batch", "channels", "pad_rows", "pad_cols", "input_format")
 
 
+class SoftmaxParams(ctypes.Structure):
+    """sycldnn::softmax::SoftmaxParams, include/portdnn/softmax/params.h:27-54."""
+    _fields_ = _ints("channels", "batch", "rows", "cols", "input_format")
+
+
+class BatchNormParams(ctypes.Structure):
+    """sycldnn::batchnorm::BatchNormParams, include/portdnn/batchnorm/params.h:32-72."""
+    _fields_ = _ints("batch", "rows", "cols", "channels", "is_training") + \
+        [("epsilon", ctypes.c_float), ("momentum", ctypes.c_float), ("input_format", ctypes.c_int)]
+
+
 class _Epilogue(ctypes.Structure):
     _fields_ = [("bias", ctypes.c_void_p), ("activation", ctypes.c_int), ("alpha", ctypes.c_float),
                 ("beta", ctypes.c_float)]
@@ -317,6 +328,54 @@ def matmul(lhs, rhs, batches, m, k, n, transpose_lhs=False, transpose_rhs=False,
     _check(lib().pdnn_matmul(_dtype_code(lhs), int(transpose_lhs), int(transpose_rhs), _ptr(lhs), _ptr(rhs), _ptr(out),
                              int(batches), int(m), int(k), int(n), ctypes.c_float(beta), _stream()))
     return out
+
+
+def softmax(inp, batch, rows, cols, channels, gradient=None, out=None):
+    """softmax::launch<T, Forward> (gradient None) or <T, Gradient> (inp = the forward output, gradient = dy),
+    include/portdnn/softmax/launch.h:64-165."""
+    torch = _torch()
+    _require_cuda(inp, gradient, out)
+    if inp.numel() != batch * rows * cols * channels:
+        raise ValueError("tensor size does not match the parameters")
+    if out is None:
+        out = torch.empty_like(inp)
+    p = SoftmaxParams(channels, batch, rows, cols, 0)
+    _check(lib().pdnn_softmax(0 if gradient is None else 1, _dtype_code(inp), _ptr(inp), _ptr(gradient), _ptr(out),
+                              ctypes.byref(p), _stream()))
+    return out
+
+
+def batchnorm_params(batch, rows, cols, channels, training, epsilon=1e-3, momentum=0.9):
+    return BatchNormParams(batch, rows, cols, channels, int(bool(training)), epsilon, momentum, 0)
+
+
+def batchnorm_forward(inp, beta, gamma, mean, variance, params, out=None):
+    """batchnorm::launch<T, Backend, Forward> (include/portdnn/batchnorm/launch.h:222-330)
+    -> (output, running_mean, running_variance); the last two are None for frozen parameters."""
+    torch = _torch()
+    _require_cuda(inp, beta, gamma, mean, variance, out)
+    if out is None:
+        out = torch.empty_like(inp)
+    rm = rv = None
+    if params.is_training:
+        rm, rv = torch.empty_like(mean), torch.empty_like(variance)
+    _check(lib().pdnn_batchnorm_forward(_dtype_code(inp), _ptr(inp), _ptr(beta), _ptr(gamma), _ptr(mean), _ptr(variance),
+                                        _ptr(rm), _ptr(rv), _ptr(out), ctypes.byref(params), _stream()))
+    return out, rm, rv
+
+
+def batchnorm_gradient(inp, gradient, gamma, params, pop_mean=None, pop_variance=None, out=None):
+    """batchnorm::launch<T, Backend, Gradient> (include/portdnn/batchnorm/launch.h:332-444)
+    -> (input gradient, beta gradient, gamma gradient)."""
+    torch = _torch()
+    _require_cuda(inp, gradient, gamma, pop_mean, pop_variance, out)
+    if out is None:
+        out = torch.empty_like(inp)
+    bg, gg = torch.empty_like(gamma), torch.empty_like(gamma)
+    _check(lib().pdnn_batchnorm_gradient(_dtype_code(inp), _ptr(inp), _ptr(gradient), _ptr(gamma), _ptr(pop_mean),
+                                         _ptr(pop_variance), _ptr(bg), _ptr(gg), _ptr(out), ctypes.byref(params),
+                                         _stream()))
+    return out, bg, gg
 
 
 def device_error_record(clear=True):

@@ -190,6 +190,29 @@ int pdnn_pooling_max_grad(int op, int dtype, const void* input_data, const void*
                                  static_cast<cudaStream_t>(stream));
 }
 
+int pdnn_softmax(int direction, int dtype, const void* input, const void* gradient, void* output,
+                 const PdnnSoftmaxParams* params, void* stream) {
+  if (params == nullptr) return fail(PDNN_INVALID_PARAMETER, "softmax: null params");
+  if (direction != 0 && direction != 1) return fail(PDNN_INVALID_PARAMETER, "softmax: direction must be 0 or 1");
+  return launch_softmax(direction, dtype, input, gradient, output, *params, static_cast<cudaStream_t>(stream));
+}
+
+int pdnn_batchnorm_forward(int dtype, const void* input, const void* beta, const void* gamma, const void* mean,
+                           const void* variance, void* running_mean, void* running_variance, void* output,
+                           const PdnnBatchNormParams* params, void* stream) {
+  if (params == nullptr) return fail(PDNN_INVALID_PARAMETER, "batchnorm: null params");
+  return launch_batchnorm_forward(dtype, input, beta, gamma, mean, variance, running_mean, running_variance, output,
+                                  *params, static_cast<cudaStream_t>(stream));
+}
+
+int pdnn_batchnorm_gradient(int dtype, const void* input, const void* gradient, const void* gamma,
+                            const void* pop_mean, const void* pop_variance, void* beta_grad, void* gamma_grad,
+                            void* output, const PdnnBatchNormParams* params, void* stream) {
+  if (params == nullptr) return fail(PDNN_INVALID_PARAMETER, "batchnorm: null params");
+  return launch_batchnorm_gradient(dtype, input, gradient, gamma, pop_mean, pop_variance, beta_grad, gamma_grad,
+                                   output, *params, static_cast<cudaStream_t>(stream));
+}
+
 int pdnn_pointwise(int op, int dtype, const void* input, void* output, size_t n_items, void* stream) {
   if (n_items != 0 && (input == nullptr || output == nullptr)) return fail(PDNN_INVALID_PARAMETER, "pointwise: null tensor");
   return launch_pointwise(op, dtype, input, output, n_items, static_cast<cudaStream_t>(stream));

@@ -118,6 +118,16 @@ int launch_scale_blend(int dtype, const void* a, float alpha, const void* b, flo
 int launch_direct_conv(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
                        const PdnnConvEpilogue* epi, cudaStream_t s);
 
+// softmax and batchnorm (norm_kernels.cu)
+int launch_softmax(int direction, int dtype, const void* input, const void* gradient, void* output,
+                   const PdnnSoftmaxParams& p, cudaStream_t s);
+int launch_batchnorm_forward(int dtype, const void* input, const void* beta, const void* gamma, const void* mean,
+                             const void* variance, void* running_mean, void* running_variance, void* output,
+                             const PdnnBatchNormParams& p, cudaStream_t s);
+int launch_batchnorm_gradient(int dtype, const void* input, const void* gradient, const void* gamma,
+                              const void* pop_mean, const void* pop_variance, void* beta_grad, void* gamma_grad,
+                              void* output, const PdnnBatchNormParams& p, cudaStream_t s);
+
 // Winograd F(2x2,3x3) (winograd.cu): forward and input backprop of 3x3 stride-1 layers.
 bool winograd_applicable(int pass, int dtype, const PdnnConv2DParams& p);
 size_t winograd_workspace_elems(int pass, const PdnnConv2DParams& p);

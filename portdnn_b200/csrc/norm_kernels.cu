@@ -1,0 +1,359 @@
+// Softmax and batchnorm (NHWC): the operators the reference's network wrappers need beside the
+// convolution path (tools/layer.h:128-205, 284-310).  HBM-bound; arithmetic in fp32, one rounding on
+// store.  The reference composes both from reduce / binaryop / pointwise launches
+// (include/portdnn/internal/softmax/launch_internal.h:45-275,
+// include/portdnn/internal/batchnorm/launch_internal.h:95-640); here each is one to three kernels.
+#include "common.cuh"
+
+namespace pdnn {
+namespace {
+
+constexpr int kBlock = 256;
+
+template <typename F>
+int dispatch(int dtype, F&& f) {
+  switch (dtype) {
+    case PDNN_F32: return f(float{});
+    case PDNN_F16: return f(__half{});
+    case PDNN_BF16: return f(__nv_bfloat16{});
+  }
+  return fail(PDNN_INVALID_PARAMETER, "unknown dtype %d", dtype);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+
+// One warp per pixel: y = exp(x - max) / sum exp(x - max) over the pixel's C channels.
+template <typename T>
+__global__ void __launch_bounds__(kBlock) softmax_forward_kernel(const T* __restrict__ x, T* __restrict__ y, size_t rows,
+                                                                 int C) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps = (size_t)gridDim.x * (kBlock / 32);
+  for (size_t row = (size_t)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const T* xr = x + row * C;
+    T* yr = y + row * C;
+    float m = -INFINITY;
+    for (int c = lane; c < C; c += 32) m = fmaxf(m, to_f32(xr[c]));
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int c = lane; c < C; c += 32) sum += expf(to_f32(xr[c]) - m);
+    sum = warp_sum(sum);
+    for (int c = lane; c < C; c += 32) yr[c] = from_f32<T>(expf(to_f32(xr[c]) - m) / sum);
+  }
+}
+
+// dx = (dy - sum_c(dy * y)) * y, y = the forward output.
+template <typename T>
+__global__ void __launch_bounds__(kBlock) softmax_grad_kernel(const T* __restrict__ y, const T* __restrict__ dy,
+                                                              T* __restrict__ dx, size_t rows, int C) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps = (size_t)gridDim.x * (kBlock / 32);
+  for (size_t row = (size_t)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const T* yr = y + row * C;
+    const T* gr = dy + row * C;
+    float sum = 0.f;
+    for (int c = lane; c < C; c += 32) sum += to_f32(gr[c]) * to_f32(yr[c]);
+    sum = warp_sum(sum);
+    for (int c = lane; c < C; c += 32) dx[row * C + c] = from_f32<T>((to_f32(gr[c]) - sum) * to_f32(yr[c]));
+  }
+}
+
+// out = (x - mean[c]) / sqrt(var[c] + eps) * gamma[c] + beta[c]
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+    batchnorm_apply_kernel(const T* __restrict__ x, const T* __restrict__ beta, const T* __restrict__ gamma,
+                           const T* __restrict__ mean, const T* __restrict__ var, T* __restrict__ out, size_t n, int C,
+                           float eps) {
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) {
+    const int c = (int)(i % C);
+    const float v = (to_f32(x[i]) - to_f32(mean[c])) / sqrtf(to_f32(var[c]) + eps) * to_f32(gamma[c]) + to_f32(beta[c]);
+    out[i] = from_f32<T>(v);
+  }
+}
+
+// Per-channel sums over the rows of one slice: partial[slice][0][c], partial[slice][1][c].
+//   MODE 0: sum x,                 sum dy
+//   MODE 1: sum (x - shift)^2,     sum dy * (x - shift)         shift = per-channel float
+//   MODE 2: sum dy,                sum (x - shift) * dy / scale shift, scale = per-channel float
+// dy may be NULL (its sums are then zero).  Block: 32 channel lanes x 8 row lanes.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kBlock)
+    batchnorm_sums_kernel(const T* __restrict__ x, const T* __restrict__ dy, const float* __restrict__ shift,
+                          const float* __restrict__ scale, float* __restrict__ partial, size_t rows, int C,
+                          size_t rows_per_slice) {
+  __shared__ float red[2][8][32];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.y * 32 + tx;
+  const size_t begin = (size_t)blockIdx.x * rows_per_slice;
+  const size_t end = begin + rows_per_slice < rows ? begin + rows_per_slice : rows;
+  float a = 0.f, b = 0.f;
+  if (c < C) {
+    const float sh = MODE == 0 ? 0.f : shift[c];
+    const float sc = MODE == 2 ? scale[c] : 1.f;
+    for (size_t r = begin + ty; r < end; r += 8) {
+      const float xv = to_f32(x[r * C + c]);
+      const float gv = dy != nullptr ? to_f32(dy[r * C + c]) : 0.f;
+      if (MODE == 0) {
+        a += xv;
+        b += gv;
+      } else if (MODE == 1) {
+        const float d = xv - sh;
+        a += d * d;
+        b += gv * d;
+      } else {
+        a += gv;
+        b += (xv - sh) * gv / sc;
+      }
+    }
+  }
+  red[0][ty][tx] = a;
+  red[1][ty][tx] = b;
+  __syncthreads();
+  if (ty < 2 && c < C) {
+    float sum = 0.f;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) sum += red[ty][l][tx];
+    partial[((size_t)blockIdx.x * 2 + ty) * C + c] = sum;
+  }
+}
+
+// totals[k][c] = sum over slices of partial[slice][k][c], optionally divided by `divide_by`.
+__global__ void __launch_bounds__(kBlock)
+    batchnorm_totals_kernel(const float* __restrict__ partial, float* __restrict__ totals, int slices, int C,
+                            float divide0, float divide1) {
+  const int i = blockIdx.x * kBlock + threadIdx.x;
+  if (i >= 2 * C) return;
+  const int k = i / C, c = i % C;
+  float sum = 0.f;
+  for (int s = 0; s < slices; ++s) sum += partial[((size_t)s * 2 + k) * C + c];
+  totals[i] = sum / (k == 0 ? divide0 : divide1);
+}
+
+// Training forward, last step: running = batch * (1 - m) + given * m.
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+    batchnorm_running_kernel(const float* __restrict__ batch_mean, const float* __restrict__ batch_var,
+                             const T* __restrict__ mean, const T* __restrict__ var, T* __restrict__ run_mean,
+                             T* __restrict__ run_var, int C, float momentum) {
+  const int c = blockIdx.x * kBlock + threadIdx.x;
+  if (c >= C) return;
+  run_mean[c] = from_f32<T>(batch_mean[c] * (1.f - momentum) + to_f32(mean[c]) * momentum);
+  run_var[c] = from_f32<T>(batch_var[c] * (1.f - momentum) + to_f32(var[c]) * momentum);
+}
+
+// Training gradient, elementwise step.  stats0 = [mean x | mean dy], stats1 = [var | sum dy * xc].
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+    batchnorm_grad_training_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ gamma,
+                                   const float* __restrict__ stats0, const float* __restrict__ stats1,
+                                   T* __restrict__ out, size_t n, int C, float rows, float eps) {
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) {
+    const int c = (int)(i % C);
+    const float v = stats1[c] + eps, sd = sqrtf(v);
+    const float k = stats1[C + c] / rows / v;
+    const float d = to_f32(x[i]) - stats0[c];
+    out[i] = from_f32<T>(((to_f32(dy[i]) - stats0[C + c]) - d * k) * to_f32(gamma[c]) / sd);
+  }
+}
+
+// Per-channel results of the gradients.  Training: beta_grad = mean dy * rows, gamma_grad =
+// sum(dy * xc) / sqrt(var + eps).  Frozen: the two sums as they are.
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+    batchnorm_param_grads_kernel(const float* __restrict__ stats0, const float* __restrict__ stats1,
+                                 T* __restrict__ beta_grad, T* __restrict__ gamma_grad, int C, float rows, float eps,
+                                 int training) {
+  const int c = blockIdx.x * kBlock + threadIdx.x;
+  if (c >= C) return;
+  if (training) {
+    beta_grad[c] = from_f32<T>(stats0[C + c] * rows);
+    gamma_grad[c] = from_f32<T>(stats1[C + c] / sqrtf(stats1[c] + eps));
+  } else {
+    beta_grad[c] = from_f32<T>(stats0[c]);
+    gamma_grad[c] = from_f32<T>(stats0[C + c]);
+  }
+}
+
+// Frozen gradient, elementwise step: out = dy * gamma / sqrt(pop_var + eps).
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+    batchnorm_grad_frozen_kernel(const T* __restrict__ dy, const T* __restrict__ gamma, const T* __restrict__ pop_var,
+                                 T* __restrict__ out, size_t n, int C, float eps) {
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) {
+    const int c = (int)(i % C);
+    out[i] = from_f32<T>(to_f32(dy[i]) * (to_f32(gamma[c]) / sqrtf(to_f32(pop_var[c]) + eps)));
+  }
+}
+
+// Channel vectors of T as float (shift / scale operands of the sums kernel).
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+    batchnorm_prepare_frozen_kernel(const T* __restrict__ pop_mean, const T* __restrict__ pop_var,
+                                    float* __restrict__ shift, float* __restrict__ scale, int C, float eps) {
+  const int c = blockIdx.x * kBlock + threadIdx.x;
+  if (c >= C) return;
+  shift[c] = to_f32(pop_mean[c]);
+  scale[c] = sqrtf(to_f32(pop_var[c]) + eps);
+}
+
+int slices_for(size_t rows, int C, int sms) {
+  const size_t ctiles = (size_t)(C + 31) / 32;
+  size_t want = ((size_t)sms * 8 + ctiles - 1) / ctiles;
+  const size_t cap = (rows + 63) / 64;
+  if (want > cap) want = cap;
+  if (want < 1) want = 1;
+  if (want > 4096) want = 4096;
+  return (int)want;
+}
+
+bool params_ok(int batch, int rows, int cols, int channels) { return batch > 0 && rows > 0 && cols > 0 && channels > 0; }
+
+// Scratch of one call: [partial: slices * 2 * C][stats0: 2C][stats1: 2C][shift: C][scale: C] floats.
+struct Scratch {
+  float *partial, *stats0, *stats1, *shift, *scale;
+  void* base;
+};
+
+int get_scratch(Scratch* sc, int slices, int C, cudaStream_t s) {
+  const size_t floats = (size_t)slices * 2 * C + 6 * (size_t)C;
+  if (cudaMallocAsync(&sc->base, floats * sizeof(float), s) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(PDNN_ALLOCATION_PROBLEM, "batchnorm: cannot allocate %zu bytes of scratch", floats * sizeof(float));
+  }
+  sc->partial = static_cast<float*>(sc->base);
+  sc->stats0 = sc->partial + (size_t)slices * 2 * C;
+  sc->stats1 = sc->stats0 + 2 * C;
+  sc->shift = sc->stats1 + 2 * C;
+  sc->scale = sc->shift + C;
+  return PDNN_OK;
+}
+
+}  // namespace
+
+int launch_softmax(int direction, int dtype, const void* input, const void* gradient, void* output,
+                   const PdnnSoftmaxParams& p, cudaStream_t s) {
+  // validate_params, include/portdnn/softmax/launch.h:40-50
+  if (!params_ok(p.batch, p.rows, p.cols, p.channels))
+    return fail(PDNN_INVALID_PARAMETER, "softmax: batch, rows, cols and channels must be positive");
+  if (p.input_format != 0) return fail(PDNN_INVALID_PARAMETER, "softmax: only NHWC is implemented");
+  if (input == nullptr || output == nullptr || (direction == 1 && gradient == nullptr))
+    return fail(PDNN_INVALID_PARAMETER, "softmax: null tensor");
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  const size_t rows = (size_t)p.batch * p.rows * p.cols;
+  const unsigned grid = grid_for(rows * 32, kBlock, sms);
+  return dispatch(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    if (direction == 0)
+      softmax_forward_kernel<T><<<grid, kBlock, 0, s>>>(static_cast<const T*>(input), static_cast<T*>(output), rows,
+                                                        p.channels);
+    else
+      softmax_grad_kernel<T><<<grid, kBlock, 0, s>>>(static_cast<const T*>(input), static_cast<const T*>(gradient),
+                                                     static_cast<T*>(output), rows, p.channels);
+    return check_launch(direction == 0 ? "softmax forward" : "softmax gradient");
+  });
+}
+
+int launch_batchnorm_forward(int dtype, const void* input, const void* beta, const void* gamma, const void* mean,
+                             const void* variance, void* running_mean, void* running_variance, void* output,
+                             const PdnnBatchNormParams& p, cudaStream_t s) {
+  if (!params_ok(p.batch, p.rows, p.cols, p.channels))
+    return fail(PDNN_INVALID_PARAMETER, "batchnorm: batch, rows, cols and channels must be positive");
+  if (p.input_format != 0) return fail(PDNN_INVALID_PARAMETER, "batchnorm: only NHWC is implemented");
+  if (!(p.epsilon > 0.f)) return fail(PDNN_INVALID_PARAMETER, "batchnorm: epsilon must be positive");
+  if (input == nullptr || beta == nullptr || gamma == nullptr || mean == nullptr || variance == nullptr ||
+      output == nullptr || (p.is_training && (running_mean == nullptr || running_variance == nullptr)))
+    return fail(PDNN_INVALID_PARAMETER, "batchnorm: null tensor");
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  const size_t rows = (size_t)p.batch * p.rows * p.cols, n = rows * p.channels;
+  const int C = p.channels;
+  return dispatch(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    batchnorm_apply_kernel<T><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
+        static_cast<const T*>(input), static_cast<const T*>(beta), static_cast<const T*>(gamma),
+        static_cast<const T*>(mean), static_cast<const T*>(variance), static_cast<T*>(output), n, C, p.epsilon);
+    int st = check_launch("batchnorm forward");
+    if (st != PDNN_OK || !p.is_training) return st;
+    // batch mean, then the biased batch variance around it, then the running statistics
+    const int slices = slices_for(rows, C, sms);
+    const size_t per_slice = (rows + slices - 1) / slices;
+    Scratch sc;
+    st = get_scratch(&sc, slices, C, s);
+    if (st != PDNN_OK) return st;
+    const dim3 grid(slices, (C + 31) / 32);
+    const unsigned cgrid = (2 * C + kBlock - 1) / kBlock;
+    batchnorm_sums_kernel<T, 0><<<grid, kBlock, 0, s>>>(static_cast<const T*>(input), nullptr, nullptr, nullptr,
+                                                       sc.partial, rows, C, per_slice);
+    batchnorm_totals_kernel<<<cgrid, kBlock, 0, s>>>(sc.partial, sc.stats0, slices, C, (float)rows, (float)rows);
+    batchnorm_sums_kernel<T, 1><<<grid, kBlock, 0, s>>>(static_cast<const T*>(input), nullptr, sc.stats0, nullptr,
+                                                       sc.partial, rows, C, per_slice);
+    batchnorm_totals_kernel<<<cgrid, kBlock, 0, s>>>(sc.partial, sc.stats1, slices, C, (float)rows, 1.f);
+    batchnorm_running_kernel<T><<<(C + kBlock - 1) / kBlock, kBlock, 0, s>>>(
+        sc.stats0, sc.stats1, static_cast<const T*>(mean), static_cast<const T*>(variance),
+        static_cast<T*>(running_mean), static_cast<T*>(running_variance), C, p.momentum);
+    st = check_launch("batchnorm forward (batch statistics)");
+    count_launch(4);
+    cudaFreeAsync(sc.base, s);
+    return st;
+  });
+}
+
+int launch_batchnorm_gradient(int dtype, const void* input, const void* gradient, const void* gamma,
+                              const void* pop_mean, const void* pop_variance, void* beta_grad, void* gamma_grad,
+                              void* output, const PdnnBatchNormParams& p, cudaStream_t s) {
+  if (!params_ok(p.batch, p.rows, p.cols, p.channels))
+    return fail(PDNN_INVALID_PARAMETER, "batchnorm: batch, rows, cols and channels must be positive");
+  if (p.input_format != 0) return fail(PDNN_INVALID_PARAMETER, "batchnorm: only NHWC is implemented");
+  if (!(p.epsilon > 0.f)) return fail(PDNN_INVALID_PARAMETER, "batchnorm: epsilon must be positive");
+  if (input == nullptr || gradient == nullptr || gamma == nullptr || beta_grad == nullptr || gamma_grad == nullptr ||
+      output == nullptr || (!p.is_training && (pop_mean == nullptr || pop_variance == nullptr)))
+    return fail(PDNN_INVALID_PARAMETER, "batchnorm gradient: null tensor");
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  const size_t rows = (size_t)p.batch * p.rows * p.cols, n = rows * p.channels;
+  const int C = p.channels;
+  return dispatch(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    const int slices = slices_for(rows, C, sms);
+    const size_t per_slice = (rows + slices - 1) / slices;
+    Scratch sc;
+    int st = get_scratch(&sc, slices, C, s);
+    if (st != PDNN_OK) return st;
+    const dim3 grid(slices, (C + 31) / 32);
+    const unsigned cgrid = (2 * C + kBlock - 1) / kBlock, c1grid = (C + kBlock - 1) / kBlock;
+    const T *x = static_cast<const T*>(input), *dy = static_cast<const T*>(gradient), *g = static_cast<const T*>(gamma);
+    if (p.is_training) {
+      batchnorm_sums_kernel<T, 0><<<grid, kBlock, 0, s>>>(x, dy, nullptr, nullptr, sc.partial, rows, C, per_slice);
+      batchnorm_totals_kernel<<<cgrid, kBlock, 0, s>>>(sc.partial, sc.stats0, slices, C, (float)rows, (float)rows);
+      batchnorm_sums_kernel<T, 1><<<grid, kBlock, 0, s>>>(x, dy, sc.stats0, nullptr, sc.partial, rows, C, per_slice);
+      batchnorm_totals_kernel<<<cgrid, kBlock, 0, s>>>(sc.partial, sc.stats1, slices, C, (float)rows, 1.f);
+      batchnorm_grad_training_kernel<T><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
+          x, dy, g, sc.stats0, sc.stats1, static_cast<T*>(output), n, C, (float)rows, p.epsilon);
+      count_launch(4);
+    } else {
+      batchnorm_prepare_frozen_kernel<T><<<c1grid, kBlock, 0, s>>>(static_cast<const T*>(pop_mean),
+                                                                 static_cast<const T*>(pop_variance), sc.shift, sc.scale,
+                                                                 C, p.epsilon);
+      batchnorm_sums_kernel<T, 2><<<grid, kBlock, 0, s>>>(x, dy, sc.shift, sc.scale, sc.partial, rows, C, per_slice);
+      batchnorm_totals_kernel<<<cgrid, kBlock, 0, s>>>(sc.partial, sc.stats0, slices, C, 1.f, 1.f);
+      batchnorm_grad_frozen_kernel<T><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
+          dy, g, static_cast<const T*>(pop_variance), static_cast<T*>(output), n, C, p.epsilon);
+      count_launch(3);
+    }
+    batchnorm_param_grads_kernel<T><<<c1grid, kBlock, 0, s>>>(sc.stats0, sc.stats1, static_cast<T*>(beta_grad),
+                                                             static_cast<T*>(gamma_grad), C, (float)rows, p.epsilon,
+                                                             p.is_training);
+    st = check_launch("batchnorm gradient");
+    cudaFreeAsync(sc.base, s);
+    return st;
+  });
+}
+
+}  // namespace pdnn
