@@ -6,34 +6,43 @@ import subprocess
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-SRC = os.path.join(ROOT, "tests", "cpp", "api_test.cc")
-EXE = os.path.join(ROOT, "tests", "cpp", "api_test")
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+# api_test: every operator through the sycldnn:: templates; network_test: the layer / network
+# wrappers of include/tools/ on a VGG-style and a ResNet-style stack.
+PROGRAMS = ["api_test", "network_test"]
 
 
-def _build():
+def _paths(name):
+    return os.path.join(ROOT, "tests", "cpp", name + ".cc"), os.path.join(ROOT, "tests", "cpp", name)
+
+
+def _build(name):
     from portdnn_b200 import build
     build.build()
-    deps = [SRC, os.path.join(ROOT, "include", "portdnn_b200.h")]
-    for d, _, files in os.walk(os.path.join(ROOT, "include", "portdnn")):
-        deps += [os.path.join(d, f) for f in files]
-    if os.path.exists(EXE) and all(os.path.getmtime(EXE) >= os.path.getmtime(d) for d in deps):
-        return
-    cmd = ["g++", "-std=c++17", "-Wall", "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(CUDA, "include"), SRC,
+    src, exe = _paths(name)
+    deps = [src, os.path.join(ROOT, "include", "portdnn_b200.h")]
+    for sub in ("portdnn", "tools"):
+        for d, _, files in os.walk(os.path.join(ROOT, "include", sub)):
+            deps += [os.path.join(d, f) for f in files]
+    if os.path.exists(exe) and all(os.path.getmtime(exe) >= os.path.getmtime(d) for d in deps):
+        return exe
+    cmd = ["g++", "-std=c++17", "-Wall", "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(CUDA, "include"), src,
            "-L" + os.path.join(ROOT, "portdnn_b200"), "-lportdnn_b200", "-L" + os.path.join(CUDA, "lib64"), "-lcudart",
-           "-Wl,-rpath," + os.path.join(ROOT, "portdnn_b200"), "-Wl,-rpath," + os.path.join(CUDA, "lib64"), "-o", EXE]
+           "-Wl,-rpath," + os.path.join(ROOT, "portdnn_b200"), "-Wl,-rpath," + os.path.join(CUDA, "lib64"), "-o", exe]
     res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     assert res.returncode == 0, res.stdout
+    return exe
 
 
-def test_headers_compile_and_link():
-    _build()
-    assert os.path.exists(EXE)
+@pytest.mark.parametrize("name", PROGRAMS)
+def test_headers_compile_and_link(name):
+    assert os.path.exists(_build(name))
 
 
 @pytest.mark.gpu
-def test_reference_style_program_passes():
-    _build()
-    res = subprocess.run([EXE], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
+@pytest.mark.parametrize("name", PROGRAMS)
+def test_reference_style_program_passes(name):
+    exe = _build(name)
+    res = subprocess.run([exe], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
     assert res.returncode == 0, res.stdout
     assert "all checks passed" in res.stdout
