@@ -64,6 +64,152 @@ __global__ void __launch_bounds__(kBlock) softmax_grad_kernel(const T* __restric
   }
 }
 
+// V consecutive elements as floats (one 16-byte access when V > 1).
+template <typename T, int V>
+__device__ __forceinline__ void load_v(const T* p, float (&v)[V]) {
+  if constexpr (V == 1) {
+    v[0] = to_f32(__ldg(p));
+  } else {
+    const Vec16<T> pk = load16(p);
+#pragma unroll
+    for (int i = 0; i < V; ++i) v[i] = to_f32(pk.get(i));
+  }
+}
+template <typename T, int V>
+__device__ __forceinline__ void store_v(T* p, const float (&v)[V]) {
+  if constexpr (V == 1) {
+    p[0] = from_f32<T>(v[0]);
+  } else {
+    Vec16<T> pk;
+#pragma unroll
+    for (int i = 0; i < V; ++i) pk.set(i, from_f32<T>(v[i]));
+    store16(p, pk);
+  }
+}
+
+// The elementwise steps on packets of V channels (C % V == 0, 16-byte aligned tensors): n counts
+// packets.  The per-channel operands are read as packets too (they stay in L1).
+template <typename T, int V>
+__global__ void __launch_bounds__(kBlock)
+    batchnorm_apply_vec_kernel(const T* __restrict__ x, const T* __restrict__ beta, const T* __restrict__ gamma,
+                               const T* __restrict__ mean, const T* __restrict__ var, T* __restrict__ out, size_t n,
+                               int C, float eps) {
+  const size_t cvecs = (size_t)(C / V);
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) {
+    const int c = (int)(i % cvecs) * V;
+    float xv[V], b[V], g[V], m[V], v[V], o[V];
+    load_v<T, V>(x + i * V, xv);
+    load_v<T, V>(beta + c, b);
+    load_v<T, V>(gamma + c, g);
+    load_v<T, V>(mean + c, m);
+    load_v<T, V>(var + c, v);
+#pragma unroll
+    for (int k = 0; k < V; ++k) o[k] = (xv[k] - m[k]) / sqrtf(v[k] + eps) * g[k] + b[k];
+    store_v<T, V>(out + i * V, o);
+  }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kBlock)
+    batchnorm_grad_training_vec_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ gamma,
+                                       const float* __restrict__ stats0, const float* __restrict__ stats1,
+                                       T* __restrict__ out, size_t n, int C, float rows, float eps) {
+  const size_t cvecs = (size_t)(C / V);
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) {
+    const int c = (int)(i % cvecs) * V;
+    float xv[V], gv[V], g[V], o[V];
+    load_v<T, V>(x + i * V, xv);
+    load_v<T, V>(dy + i * V, gv);
+    load_v<T, V>(gamma + c, g);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float v = stats1[c + k] + eps, sd = sqrtf(v);
+      const float kk = stats1[C + c + k] / rows / v;
+      o[k] = ((gv[k] - stats0[C + c + k]) - (xv[k] - stats0[c + k]) * kk) * g[k] / sd;
+    }
+    store_v<T, V>(out + i * V, o);
+  }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kBlock)
+    batchnorm_grad_frozen_vec_kernel(const T* __restrict__ dy, const T* __restrict__ gamma,
+                                     const T* __restrict__ pop_var, T* __restrict__ out, size_t n, int C, float eps) {
+  const size_t cvecs = (size_t)(C / V);
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) {
+    const int c = (int)(i % cvecs) * V;
+    float gv[V], g[V], v[V], o[V];
+    load_v<T, V>(dy + i * V, gv);
+    load_v<T, V>(gamma + c, g);
+    load_v<T, V>(pop_var + c, v);
+#pragma unroll
+    for (int k = 0; k < V; ++k) o[k] = gv[k] * (g[k] / sqrtf(v[k] + eps));
+    store_v<T, V>(out + i * V, o);
+  }
+}
+
+// The sums kernel on packets: lane tx of the block owns V channels; 32 lanes x 8 row lanes.
+template <typename T, int V, int MODE>
+__global__ void __launch_bounds__(kBlock)
+    batchnorm_sums_vec_kernel(const T* __restrict__ x, const T* __restrict__ dy, const float* __restrict__ shift,
+                              const float* __restrict__ scale, float* __restrict__ partial, size_t rows, int C,
+                              size_t rows_per_slice) {
+  __shared__ float red[2][8][32][V];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = (blockIdx.y * 32 + tx) * V;
+  const size_t begin = (size_t)blockIdx.x * rows_per_slice;
+  const size_t end = begin + rows_per_slice < rows ? begin + rows_per_slice : rows;
+  float a[V], b[V], sh[V], sc[V];
+#pragma unroll
+  for (int k = 0; k < V; ++k) a[k] = b[k] = 0.f, sh[k] = 0.f, sc[k] = 1.f;
+  if (c < C) {
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      if (MODE != 0) sh[k] = shift[c + k];
+      if (MODE == 2) sc[k] = scale[c + k];
+    }
+    for (size_t r = begin + ty; r < end; r += 8) {
+      float xv[V], gv[V];
+      load_v<T, V>(x + r * C + c, xv);
+      if (dy != nullptr) {
+        load_v<T, V>(dy + r * C + c, gv);
+      } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) gv[k] = 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        if (MODE == 0) {
+          a[k] += xv[k];
+          b[k] += gv[k];
+        } else if (MODE == 1) {
+          const float d = xv[k] - sh[k];
+          a[k] += d * d;
+          b[k] += gv[k] * d;
+        } else {
+          a[k] += gv[k];
+          b[k] += (xv[k] - sh[k]) * gv[k] / sc[k];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    red[0][ty][tx][k] = a[k];
+    red[1][ty][tx][k] = b[k];
+  }
+  __syncthreads();
+  if (ty < 2 && c < C) {
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      float sum = 0.f;
+#pragma unroll
+      for (int l = 0; l < 8; ++l) sum += red[ty][l][tx][k];
+      partial[((size_t)blockIdx.x * 2 + ty) * C + c + k] = sum;
+    }
+  }
+}
+
 // out = (x - mean[c]) / sqrt(var[c] + eps) * gamma[c] + beta[c]
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
@@ -202,8 +348,10 @@ __global__ void __launch_bounds__(kBlock)
   scale[c] = sqrtf(to_f32(pop_var[c]) + eps);
 }
 
-int slices_for(size_t rows, int C, int sms) {
-  const size_t ctiles = (size_t)(C + 31) / 32;
+// Row slices of the per-channel reductions: enough blocks to fill the device a few times over
+// (a block covers `block_channels` channels), at least 64 rows per slice.
+int slices_for(size_t rows, int C, int sms, int block_channels) {
+  const size_t ctiles = (size_t)(C + block_channels - 1) / block_channels;
   size_t want = ((size_t)sms * 8 + ctiles - 1) / ctiles;
   const size_t cap = (rows + 63) / 64;
   if (want > cap) want = cap;
@@ -276,24 +424,40 @@ int launch_batchnorm_forward(int dtype, const void* input, const void* beta, con
   const int C = p.channels;
   return dispatch(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
-    batchnorm_apply_kernel<T><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
-        static_cast<const T*>(input), static_cast<const T*>(beta), static_cast<const T*>(gamma),
-        static_cast<const T*>(mean), static_cast<const T*>(variance), static_cast<T*>(output), n, C, p.epsilon);
+    constexpr int VN = Vec16<T>::N;
+    const bool vec = C % VN == 0 && aligned16(input) && aligned16(output) && aligned16(beta) && aligned16(gamma) &&
+                     aligned16(mean) && aligned16(variance);
+    if (vec)
+      batchnorm_apply_vec_kernel<T, VN><<<grid_for(n / VN, kBlock, sms), kBlock, 0, s>>>(
+          static_cast<const T*>(input), static_cast<const T*>(beta), static_cast<const T*>(gamma),
+          static_cast<const T*>(mean), static_cast<const T*>(variance), static_cast<T*>(output), n / VN, C, p.epsilon);
+    else
+      batchnorm_apply_kernel<T><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
+          static_cast<const T*>(input), static_cast<const T*>(beta), static_cast<const T*>(gamma),
+          static_cast<const T*>(mean), static_cast<const T*>(variance), static_cast<T*>(output), n, C, p.epsilon);
     int st = check_launch("batchnorm forward");
     if (st != PDNN_OK || !p.is_training) return st;
     // batch mean, then the biased batch variance around it, then the running statistics
-    const int slices = slices_for(rows, C, sms);
+    const int slices = slices_for(rows, C, sms, vec ? 32 * VN : 32);
     const size_t per_slice = (rows + slices - 1) / slices;
     Scratch sc;
     st = get_scratch(&sc, slices, C, s);
     if (st != PDNN_OK) return st;
-    const dim3 grid(slices, (C + 31) / 32);
+    const dim3 grid(slices, (C + 31) / 32), vgrid(slices, (C / VN + 31) / 32);
     const unsigned cgrid = (2 * C + kBlock - 1) / kBlock;
-    batchnorm_sums_kernel<T, 0><<<grid, kBlock, 0, s>>>(static_cast<const T*>(input), nullptr, nullptr, nullptr,
-                                                       sc.partial, rows, C, per_slice);
+    if (vec)
+      batchnorm_sums_vec_kernel<T, VN, 0><<<vgrid, kBlock, 0, s>>>(static_cast<const T*>(input), nullptr, nullptr,
+                                                                  nullptr, sc.partial, rows, C, per_slice);
+    else
+      batchnorm_sums_kernel<T, 0><<<grid, kBlock, 0, s>>>(static_cast<const T*>(input), nullptr, nullptr, nullptr,
+                                                         sc.partial, rows, C, per_slice);
     batchnorm_totals_kernel<<<cgrid, kBlock, 0, s>>>(sc.partial, sc.stats0, slices, C, (float)rows, (float)rows);
-    batchnorm_sums_kernel<T, 1><<<grid, kBlock, 0, s>>>(static_cast<const T*>(input), nullptr, sc.stats0, nullptr,
-                                                       sc.partial, rows, C, per_slice);
+    if (vec)
+      batchnorm_sums_vec_kernel<T, VN, 1><<<vgrid, kBlock, 0, s>>>(static_cast<const T*>(input), nullptr, sc.stats0,
+                                                                  nullptr, sc.partial, rows, C, per_slice);
+    else
+      batchnorm_sums_kernel<T, 1><<<grid, kBlock, 0, s>>>(static_cast<const T*>(input), nullptr, sc.stats0, nullptr,
+                                                         sc.partial, rows, C, per_slice);
     batchnorm_totals_kernel<<<cgrid, kBlock, 0, s>>>(sc.partial, sc.stats1, slices, C, (float)rows, 1.f);
     batchnorm_running_kernel<T><<<(C + kBlock - 1) / kBlock, kBlock, 0, s>>>(
         sc.stats0, sc.stats1, static_cast<const T*>(mean), static_cast<const T*>(variance),
@@ -321,30 +485,44 @@ int launch_batchnorm_gradient(int dtype, const void* input, const void* gradient
   const int C = p.channels;
   return dispatch(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
-    const int slices = slices_for(rows, C, sms);
+    constexpr int VN = Vec16<T>::N;
+    const bool vec = C % VN == 0 && aligned16(input) && aligned16(gradient) && aligned16(output) && aligned16(gamma) &&
+                     (p.is_training || aligned16(pop_variance));
+    const int slices = slices_for(rows, C, sms, vec ? 32 * VN : 32);
     const size_t per_slice = (rows + slices - 1) / slices;
     Scratch sc;
     int st = get_scratch(&sc, slices, C, s);
     if (st != PDNN_OK) return st;
-    const dim3 grid(slices, (C + 31) / 32);
+    const dim3 grid(slices, (C + 31) / 32), vgrid(slices, (C / VN + 31) / 32);
     const unsigned cgrid = (2 * C + kBlock - 1) / kBlock, c1grid = (C + kBlock - 1) / kBlock;
     const T *x = static_cast<const T*>(input), *dy = static_cast<const T*>(gradient), *g = static_cast<const T*>(gamma);
     if (p.is_training) {
-      batchnorm_sums_kernel<T, 0><<<grid, kBlock, 0, s>>>(x, dy, nullptr, nullptr, sc.partial, rows, C, per_slice);
+      if (vec) batchnorm_sums_vec_kernel<T, VN, 0><<<vgrid, kBlock, 0, s>>>(x, dy, nullptr, nullptr, sc.partial, rows, C, per_slice);
+      else batchnorm_sums_kernel<T, 0><<<grid, kBlock, 0, s>>>(x, dy, nullptr, nullptr, sc.partial, rows, C, per_slice);
       batchnorm_totals_kernel<<<cgrid, kBlock, 0, s>>>(sc.partial, sc.stats0, slices, C, (float)rows, (float)rows);
-      batchnorm_sums_kernel<T, 1><<<grid, kBlock, 0, s>>>(x, dy, sc.stats0, nullptr, sc.partial, rows, C, per_slice);
+      if (vec) batchnorm_sums_vec_kernel<T, VN, 1><<<vgrid, kBlock, 0, s>>>(x, dy, sc.stats0, nullptr, sc.partial, rows, C, per_slice);
+      else batchnorm_sums_kernel<T, 1><<<grid, kBlock, 0, s>>>(x, dy, sc.stats0, nullptr, sc.partial, rows, C, per_slice);
       batchnorm_totals_kernel<<<cgrid, kBlock, 0, s>>>(sc.partial, sc.stats1, slices, C, (float)rows, 1.f);
-      batchnorm_grad_training_kernel<T><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
-          x, dy, g, sc.stats0, sc.stats1, static_cast<T*>(output), n, C, (float)rows, p.epsilon);
+      if (vec)
+        batchnorm_grad_training_vec_kernel<T, VN><<<grid_for(n / VN, kBlock, sms), kBlock, 0, s>>>(
+            x, dy, g, sc.stats0, sc.stats1, static_cast<T*>(output), n / VN, C, (float)rows, p.epsilon);
+      else
+        batchnorm_grad_training_kernel<T><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
+            x, dy, g, sc.stats0, sc.stats1, static_cast<T*>(output), n, C, (float)rows, p.epsilon);
       count_launch(4);
     } else {
       batchnorm_prepare_frozen_kernel<T><<<c1grid, kBlock, 0, s>>>(static_cast<const T*>(pop_mean),
                                                                  static_cast<const T*>(pop_variance), sc.shift, sc.scale,
                                                                  C, p.epsilon);
-      batchnorm_sums_kernel<T, 2><<<grid, kBlock, 0, s>>>(x, dy, sc.shift, sc.scale, sc.partial, rows, C, per_slice);
+      if (vec) batchnorm_sums_vec_kernel<T, VN, 2><<<vgrid, kBlock, 0, s>>>(x, dy, sc.shift, sc.scale, sc.partial, rows, C, per_slice);
+      else batchnorm_sums_kernel<T, 2><<<grid, kBlock, 0, s>>>(x, dy, sc.shift, sc.scale, sc.partial, rows, C, per_slice);
       batchnorm_totals_kernel<<<cgrid, kBlock, 0, s>>>(sc.partial, sc.stats0, slices, C, 1.f, 1.f);
-      batchnorm_grad_frozen_kernel<T><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
-          dy, g, static_cast<const T*>(pop_variance), static_cast<T*>(output), n, C, p.epsilon);
+      if (vec)
+        batchnorm_grad_frozen_vec_kernel<T, VN><<<grid_for(n / VN, kBlock, sms), kBlock, 0, s>>>(
+            dy, g, static_cast<const T*>(pop_variance), static_cast<T*>(output), n / VN, C, p.epsilon);
+      else
+        batchnorm_grad_frozen_kernel<T><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
+            dy, g, static_cast<const T*>(pop_variance), static_cast<T*>(output), n, C, p.epsilon);
       count_launch(3);
     }
     batchnorm_param_grads_kernel<T><<<c1grid, kBlock, 0, s>>>(sc.stats0, sc.stats1, static_cast<T*>(beta_grad),

@@ -56,4 +56,18 @@ ms=timeit(lambda: pd.pointwise(pd.ACT_RELU,x,out=y)); res.append(("relu_fwd f16 
 ms=timeit(lambda: pd.pointwise_grad(pd.ACT_RELU,x,y,out=y)); res.append(("relu_grad f16", ms, 6*n/ms/1e6))
 ms=timeit(lambda: pd.pointwise(pd.ACT_TANH,x,out=y)); res.append(("tanh_fwd f16", ms, 4*n/ms/1e6))
 ms=timeit(lambda: pd.bias_add(x,b,256,activation=pd.ACT_RELU,out=y)); res.append(("bias_relu f16", ms, 4*n/ms/1e6))
+# batchnorm (ResNet stage-1 activation, fp16) and softmax (ImageNet classifier head)
+nb,hb,cb=256,56,256
+xb=torch.randn(nb*hb*hb*cb,device='cuda').half(); dyb=torch.randn_like(xb)
+beta,gamma,mean=(torch.randn(cb,device='cuda').half() for _ in range(3)); var=(torch.rand(cb,device='cuda')+0.5).half()
+yb=torch.empty_like(xb)
+for training in (False, True):
+    pb=pd.batchnorm_params(nb,hb,hb,cb,training)
+    tag="training" if training else "frozen"
+    ms=timeit(lambda: pd.batchnorm_forward(xb,beta,gamma,mean,var,pb,out=yb)); res.append(("batchnorm_fwd %s f16 411MB"%tag, ms, (4 if not training else 8)*xb.numel()/ms/1e6))
+    ms=timeit(lambda: pd.batchnorm_gradient(xb,dyb,gamma,pb,pop_mean=mean,pop_variance=var,out=yb)); res.append(("batchnorm_grad %s f16"%tag, ms, (10 if training else 8)*xb.numel()/ms/1e6))
+xs=torch.randn(4096*1000,device='cuda').half(); ys=torch.empty_like(xs)
+ms=timeit(lambda: pd.softmax(xs,4096,1,1,1000,out=ys)); res.append(("softmax_fwd 4096x1000 f16 (8 MB, L2)", ms, 4*xs.numel()/ms/1e6))
+xs2=torch.randn(64*56*56*256,device='cuda').half(); ys2=torch.empty_like(xs2)
+ms=timeit(lambda: pd.softmax(xs2,64,56,56,256,out=ys2)); res.append(("softmax_fwd 64x56x56x256 f16", ms, 4*xs2.numel()/ms/1e6))
 for r in res: print("%-40s %8.4f ms %8.0f GB/s"%r)
