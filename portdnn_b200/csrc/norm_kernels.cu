@@ -95,7 +95,32 @@ __global__ void __launch_bounds__(kBlock)
                                const T* __restrict__ mean, const T* __restrict__ var, T* __restrict__ out, size_t n,
                                int C, float eps) {
   const size_t cvecs = (size_t)(C / V);
-  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) {
+  const size_t step = (size_t)gridDim.x * kBlock;
+  size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x;
+  if (step % cvecs == 0) {
+    // every packet of this thread belongs to the same channels (the host sizes the grid for
+    // this): the per-channel operands and the square root are taken once
+    if (i >= n) return;
+    const int c = (int)(i % cvecs) * V;
+    float b[V], g[V], m[V], sd[V];
+    load_v<T, V>(beta + c, b);
+    load_v<T, V>(gamma + c, g);
+    load_v<T, V>(mean + c, m);
+    load_v<T, V>(var + c, sd);
+    // 1 / sqrt(var + eps) once per channel: the division per element would make the kernel
+    // instruction-bound; the product differs from the quotient by at most one ulp of fp32
+#pragma unroll
+    for (int k = 0; k < V; ++k) sd[k] = 1.f / sqrtf(sd[k] + eps);
+    for (; i < n; i += step) {
+      float xv[V], o[V];
+      load_v<T, V>(x + i * V, xv);
+#pragma unroll
+      for (int k = 0; k < V; ++k) o[k] = (xv[k] - m[k]) * sd[k] * g[k] + b[k];
+      store_v<T, V>(out + i * V, o);
+    }
+    return;
+  }
+  for (; i < n; i += step) {
     const int c = (int)(i % cvecs) * V;
     float xv[V], b[V], g[V], m[V], v[V], o[V];
     load_v<T, V>(x + i * V, xv);
@@ -115,7 +140,32 @@ __global__ void __launch_bounds__(kBlock)
                                        const float* __restrict__ stats0, const float* __restrict__ stats1,
                                        T* __restrict__ out, size_t n, int C, float rows, float eps) {
   const size_t cvecs = (size_t)(C / V);
-  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) {
+  const size_t step = (size_t)gridDim.x * kBlock;
+  size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x;
+  if (step % cvecs == 0) {  // the thread's channels never change: per-channel terms taken once
+    if (i >= n) return;
+    const int c = (int)(i % cvecs) * V;
+    float g[V], mx[V], mdy[V], kk[V], sd[V];
+    load_v<T, V>(gamma + c, g);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float v = stats1[c + k] + eps;
+      sd[k] = sqrtf(v);
+      kk[k] = stats1[C + c + k] / rows / v;
+      mx[k] = stats0[c + k];
+      mdy[k] = stats0[C + c + k];
+    }
+    for (; i < n; i += step) {
+      float xv[V], gv[V], o[V];
+      load_v<T, V>(x + i * V, xv);
+      load_v<T, V>(dy + i * V, gv);
+#pragma unroll
+      for (int k = 0; k < V; ++k) o[k] = ((gv[k] - mdy[k]) - (xv[k] - mx[k]) * kk[k]) * g[k] / sd[k];
+      store_v<T, V>(out + i * V, o);
+    }
+    return;
+  }
+  for (; i < n; i += step) {
     const int c = (int)(i % cvecs) * V;
     float xv[V], gv[V], g[V], o[V];
     load_v<T, V>(x + i * V, xv);
@@ -136,7 +186,26 @@ __global__ void __launch_bounds__(kBlock)
     batchnorm_grad_frozen_vec_kernel(const T* __restrict__ dy, const T* __restrict__ gamma,
                                      const T* __restrict__ pop_var, T* __restrict__ out, size_t n, int C, float eps) {
   const size_t cvecs = (size_t)(C / V);
-  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (size_t)gridDim.x * kBlock) {
+  const size_t step = (size_t)gridDim.x * kBlock;
+  size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x;
+  if (step % cvecs == 0) {  // the thread's channels never change: scale taken once
+    if (i >= n) return;
+    const int c = (int)(i % cvecs) * V;
+    float g[V], v[V];
+    load_v<T, V>(gamma + c, g);
+    load_v<T, V>(pop_var + c, v);
+#pragma unroll
+    for (int k = 0; k < V; ++k) g[k] = g[k] / sqrtf(v[k] + eps);
+    for (; i < n; i += step) {
+      float gv[V], o[V];
+      load_v<T, V>(dy + i * V, gv);
+#pragma unroll
+      for (int k = 0; k < V; ++k) o[k] = gv[k] * g[k];
+      store_v<T, V>(out + i * V, o);
+    }
+    return;
+  }
+  for (; i < n; i += step) {
     const int c = (int)(i % cvecs) * V;
     float gv[V], g[V], v[V], o[V];
     load_v<T, V>(dy + i * V, gv);
@@ -360,6 +429,22 @@ int slices_for(size_t rows, int C, int sms, int block_channels) {
   return (int)want;
 }
 
+// Grid of an elementwise packet kernel whose threads should keep their channels: the number of
+// threads is made a multiple of the packets per pixel when that costs little.
+unsigned channel_stable_grid(size_t packets, int cvecs, int sms) {
+  unsigned grid = grid_for(packets, kBlock, sms);
+  // threads = grid * kBlock must be a multiple of cvecs: grid a multiple of cvecs / gcd(cvecs, kBlock)
+  int a = cvecs, b = kBlock;
+  while (b != 0) {
+    const int t = a % b;
+    a = b;
+    b = t;
+  }
+  const unsigned unit = (unsigned)(cvecs / a);
+  if (unit > 1 && grid > 4 * unit) grid -= grid % unit;
+  return grid;
+}
+
 bool params_ok(int batch, int rows, int cols, int channels) { return batch > 0 && rows > 0 && cols > 0 && channels > 0; }
 
 // Scratch of one call: [partial: slices * 2 * C][stats0: 2C][stats1: 2C][shift: C][scale: C] floats.
@@ -428,7 +513,7 @@ int launch_batchnorm_forward(int dtype, const void* input, const void* beta, con
     const bool vec = C % VN == 0 && aligned16(input) && aligned16(output) && aligned16(beta) && aligned16(gamma) &&
                      aligned16(mean) && aligned16(variance);
     if (vec)
-      batchnorm_apply_vec_kernel<T, VN><<<grid_for(n / VN, kBlock, sms), kBlock, 0, s>>>(
+      batchnorm_apply_vec_kernel<T, VN><<<channel_stable_grid(n / VN, C / VN, sms), kBlock, 0, s>>>(
           static_cast<const T*>(input), static_cast<const T*>(beta), static_cast<const T*>(gamma),
           static_cast<const T*>(mean), static_cast<const T*>(variance), static_cast<T*>(output), n / VN, C, p.epsilon);
     else
@@ -504,7 +589,7 @@ int launch_batchnorm_gradient(int dtype, const void* input, const void* gradient
       else batchnorm_sums_kernel<T, 1><<<grid, kBlock, 0, s>>>(x, dy, sc.stats0, nullptr, sc.partial, rows, C, per_slice);
       batchnorm_totals_kernel<<<cgrid, kBlock, 0, s>>>(sc.partial, sc.stats1, slices, C, (float)rows, 1.f);
       if (vec)
-        batchnorm_grad_training_vec_kernel<T, VN><<<grid_for(n / VN, kBlock, sms), kBlock, 0, s>>>(
+        batchnorm_grad_training_vec_kernel<T, VN><<<channel_stable_grid(n / VN, C / VN, sms), kBlock, 0, s>>>(
             x, dy, g, sc.stats0, sc.stats1, static_cast<T*>(output), n / VN, C, (float)rows, p.epsilon);
       else
         batchnorm_grad_training_kernel<T><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
@@ -518,7 +603,7 @@ int launch_batchnorm_gradient(int dtype, const void* input, const void* gradient
       else batchnorm_sums_kernel<T, 2><<<grid, kBlock, 0, s>>>(x, dy, sc.shift, sc.scale, sc.partial, rows, C, per_slice);
       batchnorm_totals_kernel<<<cgrid, kBlock, 0, s>>>(sc.partial, sc.stats0, slices, C, 1.f, 1.f);
       if (vec)
-        batchnorm_grad_frozen_vec_kernel<T, VN><<<grid_for(n / VN, kBlock, sms), kBlock, 0, s>>>(
+        batchnorm_grad_frozen_vec_kernel<T, VN><<<channel_stable_grid(n / VN, C / VN, sms), kBlock, 0, s>>>(
             dy, g, static_cast<const T*>(pop_variance), static_cast<T*>(output), n / VN, C, p.epsilon);
       else
         batchnorm_grad_frozen_kernel<T><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
