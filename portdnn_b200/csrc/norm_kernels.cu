@@ -29,6 +29,73 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// V consecutive elements as floats (one 16-byte access when V > 1).
+template <typename T, int V>
+__device__ __forceinline__ void load_v(const T* p, float (&v)[V]) {
+  if constexpr (V == 1) {
+    v[0] = to_f32(__ldg(p));
+  } else {
+    const Vec16<T> pk = load16(p);
+#pragma unroll
+    for (int i = 0; i < V; ++i) v[i] = to_f32(pk.get(i));
+  }
+}
+template <typename T, int V>
+__device__ __forceinline__ void store_v(T* p, const float (&v)[V]) {
+  if constexpr (V == 1) {
+    p[0] = from_f32<T>(v[0]);
+  } else {
+    Vec16<T> pk;
+#pragma unroll
+    for (int i = 0; i < V; ++i) pk.set(i, from_f32<T>(v[i]));
+    store16(p, pk);
+  }
+}
+
+// One warp per pixel, packets of V channels, at most R packets per lane (C <= 32 * R * V): the
+// pixel is read once and stays in registers through the three steps.
+template <typename T, int V, int R>
+__global__ void __launch_bounds__(kBlock) softmax_forward_vec_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                                     size_t rows, int C) {
+  const int lane = threadIdx.x & 31, packets = C / V;
+  const size_t warps = (size_t)gridDim.x * (kBlock / 32);
+  for (size_t row = (size_t)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const T* xr = x + row * C;
+    float v[R][V];
+    float m = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int pk = lane + 32 * r;
+      if (pk < packets) {
+        load_v<T, V>(xr + pk * V, v[r]);
+#pragma unroll
+        for (int k = 0; k < V; ++k) m = fmaxf(m, v[r][k]);
+      }
+    }
+    m = warp_max(m);
+    float sum = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (lane + 32 * r < packets) {
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          v[r][k] = expf(v[r][k] - m);
+          sum += v[r][k];
+        }
+      }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int pk = lane + 32 * r;
+      if (pk < packets) {
+#pragma unroll
+        for (int k = 0; k < V; ++k) v[r][k] = v[r][k] / sum;
+        store_v<T, V>(y + row * C + pk * V, v[r]);
+      }
+    }
+  }
+}
+
 // One warp per pixel: y = exp(x - max) / sum exp(x - max) over the pixel's C channels.
 template <typename T>
 __global__ void __launch_bounds__(kBlock) softmax_forward_kernel(const T* __restrict__ x, T* __restrict__ y, size_t rows,
@@ -61,29 +128,6 @@ __global__ void __launch_bounds__(kBlock) softmax_grad_kernel(const T* __restric
     for (int c = lane; c < C; c += 32) sum += to_f32(gr[c]) * to_f32(yr[c]);
     sum = warp_sum(sum);
     for (int c = lane; c < C; c += 32) dx[row * C + c] = from_f32<T>((to_f32(gr[c]) - sum) * to_f32(yr[c]));
-  }
-}
-
-// V consecutive elements as floats (one 16-byte access when V > 1).
-template <typename T, int V>
-__device__ __forceinline__ void load_v(const T* p, float (&v)[V]) {
-  if constexpr (V == 1) {
-    v[0] = to_f32(__ldg(p));
-  } else {
-    const Vec16<T> pk = load16(p);
-#pragma unroll
-    for (int i = 0; i < V; ++i) v[i] = to_f32(pk.get(i));
-  }
-}
-template <typename T, int V>
-__device__ __forceinline__ void store_v(T* p, const float (&v)[V]) {
-  if constexpr (V == 1) {
-    p[0] = from_f32<T>(v[0]);
-  } else {
-    Vec16<T> pk;
-#pragma unroll
-    for (int i = 0; i < V; ++i) pk.set(i, from_f32<T>(v[i]));
-    store16(p, pk);
   }
 }
 
@@ -483,7 +527,15 @@ int launch_softmax(int direction, int dtype, const void* input, const void* grad
   const unsigned grid = grid_for(rows * 32, kBlock, sms);
   return dispatch(dtype, [&](auto tag) {
     using T = decltype(tag);
-    if (direction == 0)
+    constexpr int VN = Vec16<T>::N;
+    const bool vec = p.channels % VN == 0 && aligned16(input) && aligned16(output);
+    if (direction == 0 && vec && p.channels <= 32 * VN)
+      softmax_forward_vec_kernel<T, VN, 1><<<grid, kBlock, 0, s>>>(static_cast<const T*>(input),
+                                                                  static_cast<T*>(output), rows, p.channels);
+    else if (direction == 0 && vec && p.channels <= 128 * VN)
+      softmax_forward_vec_kernel<T, VN, 4><<<grid, kBlock, 0, s>>>(static_cast<const T*>(input),
+                                                                  static_cast<T*>(output), rows, p.channels);
+    else if (direction == 0)
       softmax_forward_kernel<T><<<grid, kBlock, 0, s>>>(static_cast<const T*>(input), static_cast<T*>(output), rows,
                                                         p.channels);
     else
