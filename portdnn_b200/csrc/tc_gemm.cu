@@ -765,17 +765,36 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
               // into the neighbouring field
               uint32_t a_lo = fw.a_lo0 + sa16 + fw.my_a16;
               uint32_t b_lo = b_res ? fw.b_lo0 + res16 + (uint32_t)cb * fw.b_bytes16 : fw.b_lo0 + sa16 + fw.my_b16;
-              for (int g = 0; g < cnt; ++g) {
-                const uint64_t da = ((uint64_t)fw.a_hi << 32) | a_lo, db = ((uint64_t)fw.b_hi << 32) | b_lo;
-                mma_f16(d_tmem, da, db, idesc, accumulate);
-                mma_f16(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
-                if (fw.four) {  // 128-byte rows: four 32-byte reduction slices per step; 64-byte rows: two
+              if (fw.four) {  // 128-byte rows: four 32-byte reduction slices per tap
+                for (int g = 0; g < cnt; ++g) {
+                  const uint64_t da = ((uint64_t)fw.a_hi << 32) | a_lo, db = ((uint64_t)fw.b_hi << 32) | b_lo;
+                  mma_f16(d_tmem, da, db, idesc, accumulate);
+                  mma_f16(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
                   mma_f16(d_tmem, da + 2 * a_kadv, db + 2 * b_kadv, idesc, 1u);
                   mma_f16(d_tmem, da + 3 * a_kadv, db + 3 * b_kadv, idesc, 1u);
+                  accumulate = 1u;
+                  a_lo += fw.halo_row16;
+                  b_lo += fw.b_tap16;
                 }
-                accumulate = 1u;
-                a_lo += fw.halo_row16;
-                b_lo += fw.b_tap16;
+              } else {  // 64-byte rows (narrow stem): two slices per tap, two taps per trip
+                int g = 0;
+                for (; g + 1 < cnt; g += 2) {
+                  const uint64_t da = ((uint64_t)fw.a_hi << 32) | a_lo, db = ((uint64_t)fw.b_hi << 32) | b_lo;
+                  const uint64_t da2 = da + fw.halo_row16, db2 = db + fw.b_tap16;
+                  mma_f16(d_tmem, da, db, idesc, accumulate);
+                  mma_f16(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
+                  mma_f16(d_tmem, da2, db2, idesc, 1u);
+                  mma_f16(d_tmem, da2 + a_kadv, db2 + b_kadv, idesc, 1u);
+                  accumulate = 1u;
+                  a_lo += 2 * fw.halo_row16;
+                  b_lo += 2 * fw.b_tap16;
+                }
+                if (g < cnt) {
+                  const uint64_t da = ((uint64_t)fw.a_hi << 32) | a_lo, db = ((uint64_t)fw.b_hi << 32) | b_lo;
+                  mma_f16(d_tmem, da, db, idesc, accumulate);
+                  mma_f16(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
+                  accumulate = 1u;
+                }
               }
               mma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
               sa16 += fw.stage16;
