@@ -287,6 +287,63 @@ int main() {
     CHECK(close(got_mean, rm, 1e-4f) && close(got_var, rv, 1e-4f), "running statistics differ");
   }
 
+  // ---- the gradient launch forms of batchnorm and softmax ------------------------------------------
+  {
+    const int N = 2, HW = 5, C = 8;
+    const size_t n = size_t(N) * HW * HW * C, rows = size_t(N) * HW * HW;
+    const Vec x = random_vec(n, 1.f, 21), dy = random_vec(n, 1.f, 22), gamma = random_vec(C, 1.f, 23);
+    const Vec mean = random_vec(C, 0.5f, 24);
+    Vec var = random_vec(C, 0.4f, 25);
+    for (float& v : var) v += 1.f;
+    float *d_x = to_device(x), *d_dy = to_device(dy), *d_gamma = to_device(gamma), *d_mean = to_device(mean),
+          *d_var = to_device(var);
+    float *dx = device_buffer(n), *dbeta = device_buffer(C), *dgamma = device_buffer(C);
+    batchnorm::BatchNormParams bp{N, HW, HW, C, false, 1e-3f, 0.9f};
+    // frozen: eight-pointer form, dx = dy * gamma / sqrt(var + eps), dbeta = sum dy
+    SNNStatus st = batchnorm::launch<float, Backend, batchnorm::Gradient>(d_x, d_dy, d_gamma, d_mean, d_var, dbeta, dgamma,
+                                                                          dx, bp, backend);
+    CHECK(st.status == StatusCode::OK, "frozen batchnorm gradient: status %d", int(st.status));
+    st.event.wait_and_throw();
+    Vec got(n), got_beta(C), exp_dx(n), exp_beta(C, 0.f);
+    cudaMemcpy(got.data(), dx, n * sizeof(float), cudaMemcpyDeviceToHost);
+    cudaMemcpy(got_beta.data(), dbeta, C * sizeof(float), cudaMemcpyDeviceToHost);
+    for (size_t i = 0; i < n; ++i) {
+      exp_dx[i] = dy[i] * (gamma[i % C] / std::sqrt(var[i % C] + 1e-3f));
+      exp_beta[i % C] += dy[i];
+    }
+    CHECK(close(got, exp_dx, 1e-5f) && close(got_beta, exp_beta, 1e-4f), "frozen batchnorm gradient differs");
+    // training: six-pointer form; dbeta is again sum dy, and the input gradient sums to ~0 per channel
+    bp.is_training = true;
+    st = batchnorm::launch<float, Backend, batchnorm::Gradient>(d_x, d_dy, d_gamma, dbeta, dgamma, dx, bp, backend);
+    CHECK(st.status == StatusCode::OK, "training batchnorm gradient: status %d", int(st.status));
+    st.event.wait_and_throw();
+    cudaMemcpy(got.data(), dx, n * sizeof(float), cudaMemcpyDeviceToHost);
+    cudaMemcpy(got_beta.data(), dbeta, C * sizeof(float), cudaMemcpyDeviceToHost);
+    CHECK(close(got_beta, exp_beta, 1e-4f), "training batchnorm beta gradient differs");
+    for (int c = 0; c < C; ++c) {
+      double s = 0;
+      for (size_t r = 0; r < rows; ++r) s += got[r * C + c];
+      CHECK(std::fabs(s) < 1e-3, "training batchnorm input gradient of channel %d sums to %g", c, s);
+    }
+    // softmax gradient: rows of (dy - sum(dy*y)) * y sum to zero
+    softmax::SoftmaxParams sp{C, N, HW, HW};
+    float *y = device_buffer(n), *ws = device_buffer(rows);
+    st = softmax::launch<float, softmax::Forward, Backend>(d_x, ws, y, sp, backend);
+    CHECK(st.status == StatusCode::OK, "softmax forward: status %d", int(st.status));
+    st = softmax::launch<float, softmax::Gradient, Backend>(y, d_dy, ws, dx, sp, backend);
+    CHECK(st.status == StatusCode::OK, "softmax gradient: status %d", int(st.status));
+    st.event.wait_and_throw();
+    cudaMemcpy(got.data(), dx, n * sizeof(float), cudaMemcpyDeviceToHost);
+    for (size_t r = 0; r < rows; ++r) {
+      double s = 0;
+      for (int c = 0; c < C; ++c) s += got[r * C + c];
+      if (std::fabs(s) > 1e-5) {
+        CHECK(false, "softmax gradient row %zu sums to %g", r, s);
+        break;
+      }
+    }
+  }
+
   if (g_failures == 0) std::printf("all checks passed\n");
   return g_failures == 0 ? 0 : 1;
 }
