@@ -124,7 +124,11 @@ def test_filter_backprop_against_oracle(orc, dtype, shape):
 
 @pytest.mark.parametrize("dtype", ["f16", "bf16", "f32"])
 @pytest.mark.parametrize("shape", [(2, 32, 32, 3, 64, 7, 2, None, 3), (2, 24, 24, 3, 64, 3, 1, True, None),
-                                   (3, 17, 19, 3, 32, 5, 2, True, None), (2, 20, 20, 1, 16, 3, 1, False, None)])
+                                   (3, 17, 19, 3, 32, 5, 2, True, None), (2, 20, 20, 1, 16, 3, 1, False, None),
+                                   # one plain copy per tile (rows of 32, 64 and 128 pixel pairs)
+                                   (2, 56, 52, 3, 64, 7, 2, None, 3), (1, 112, 112, 3, 32, 7, 2, None, 3),
+                                   (1, 224, 224, 3, 64, 7, 2, None, 3), (2, 54, 54, 4, 16, 5, 2, True, None),
+                                   (2, 57, 57, 2, 24, 3, 2, False, None)])
 def test_stem_forward_and_filter_backprop_few_channels(orc, dtype, shape):
     """Network stems (C < 8): the packed-row tensor-core path, forward and filter gradient."""
     n, h, w, c, k, win, st, same, pad = shape
