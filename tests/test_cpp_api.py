@@ -8,8 +8,9 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 # api_test: every operator through the sycldnn:: templates; network_test: the layer / network
-# wrappers of include/tools/ on a VGG-style and a ResNet-style stack.
-PROGRAMS = ["api_test", "network_test"]
+# wrappers of include/tools/ on a VGG-style and a ResNet-style stack; compat_batchnorm_test: the
+# cuDNN-style batchnorm wrappers of include/portdnn/compat/batchnorm.hpp.
+PROGRAMS = ["api_test", "network_test", "compat_batchnorm_test"]
 
 
 def _paths(name):
