@@ -1,5 +1,6 @@
 // Pointwise activations with the launch forms of portDNN's include/portdnn/pointwise/launch.h:61-179.
-// Relu and Tanh are the reference's operators; Relu6 is an addition (MobileNet-v2).
+// Relu, Tanh, Exp, Log, Floor and Sqrt are the reference's operators (operators.h:30-45); Relu6 is
+// an addition (MobileNet-v2).  Floor has no gradient; asking for it returns InvalidParameter.
 #ifndef PORTDNN_B200_POINTWISE_LAUNCH_H_
 #define PORTDNN_B200_POINTWISE_LAUNCH_H_
 #include <vector>
@@ -18,6 +19,14 @@ template <typename Direction>
 struct Tanh {};
 template <typename Direction>
 struct Relu6 {};
+template <typename Direction>
+struct Exp {};
+template <typename Direction>
+struct Log {};
+template <typename Direction>
+struct Floor {};
+template <typename Direction>
+struct Sqrt {};
 
 namespace internal {
 template <template <typename> class Op>
@@ -28,6 +37,14 @@ template <>
 struct op_code<Tanh> { static constexpr int value = PDNN_ACT_TANH; };
 template <>
 struct op_code<Relu6> { static constexpr int value = PDNN_ACT_RELU6; };
+template <>
+struct op_code<Exp> { static constexpr int value = PDNN_PW_EXP; };
+template <>
+struct op_code<Log> { static constexpr int value = PDNN_PW_LOG; };
+template <>
+struct op_code<Floor> { static constexpr int value = PDNN_PW_FLOOR; };
+template <>
+struct op_code<Sqrt> { static constexpr int value = PDNN_PW_SQRT; };
 }  // namespace internal
 
 /** output[i] = op(input[i]). */

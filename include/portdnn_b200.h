@@ -66,6 +66,9 @@ typedef enum PdnnPoolOp { PDNN_POOL_MAX = 0, PDNN_POOL_MAX_WITH_NAN = 1, PDNN_PO
 /* sycldnn::pointwise::{Relu,Tanh}, include/portdnn/pointwise/operators.h.  PDNN_ACT_RELU6 has no
  * counterpart in the reference (min(max(x,0),6)); it exists for the MobileNet-v2 workload. */
 typedef enum PdnnActivation { PDNN_ACT_NONE = -1, PDNN_ACT_RELU = 0, PDNN_ACT_TANH = 1, PDNN_ACT_RELU6 = 2 } PdnnActivation;
+/* The remaining sycldnn::pointwise operators (Exp, Log, Floor, Sqrt): accepted by pdnn_pointwise
+ * and, except Floor, pdnn_pointwise_grad, which take either enum; not valid as a fused activation. */
+typedef enum PdnnPointwiseOp { PDNN_PW_EXP = 3, PDNN_PW_LOG = 4, PDNN_PW_FLOOR = 5, PDNN_PW_SQRT = 6 } PdnnPointwiseOp;
 
 /* Field-for-field mirror of sycldnn::conv2d::Conv2DParams (include/portdnn/conv2d/params.h:32-112).
  * input_format: 0 NHWC, 1 NCHW (include/portdnn/data_format.h:31-43); filter_format: 0 HWCF, 1 FCHW,
@@ -206,9 +209,10 @@ int pdnn_batchnorm_gradient(int dtype, const void* input, const void* gradient, 
                             const void* pop_mean, const void* pop_variance, void* beta_grad, void* gamma_grad,
                             void* output, const PdnnBatchNormParams* params, void* stream);
 
-/* Replaces pointwise::launch forward / gradient (include/portdnn/pointwise/launch.h:61-179).
- * The gradient's first tensor is the forward OUTPUT, as the reference kernel treats it
- * (src/pointwise/kernels.h:205-233). */
+/* Replaces pointwise::launch forward / gradient (include/portdnn/pointwise/launch.h:61-179); op is
+ * a PdnnActivation (not NONE) or a PdnnPointwiseOp.  The gradient's first tensor is the forward
+ * OUTPUT, as the reference kernel treats it (src/pointwise/kernels.h:205-233); Floor has no
+ * gradient (InvalidParameter), and Exp's is the reference's exp(v) + err (kernels.h:94-101). */
 int pdnn_pointwise(int op, int dtype, const void* input, void* output, size_t n_items, void* stream);
 int pdnn_pointwise_grad(int op, int dtype, const void* output_forward, const void* input_backprop,
                         void* output_backprop, size_t n_items, void* stream);

@@ -15,6 +15,7 @@ _LIB = None
 FORWARD, INPUT_BACKPROP, FILTER_BACKPROP = 0, 1, 2
 POOL_MAX, POOL_MAX_WITH_NAN, POOL_AVERAGE = 0, 1, 2
 RELU, TANH = 0, 1
+EXP, LOG, FLOOR, SQRT = 3, 4, 5, 6
 
 
 class ConvParams(ctypes.Structure):

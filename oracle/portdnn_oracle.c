@@ -55,7 +55,7 @@ typedef struct {
 
 enum { ORC_FORWARD = 0, ORC_INPUT_BACKPROP = 1, ORC_FILTER_BACKPROP = 2 };
 enum { ORC_POOL_MAX = 0, ORC_POOL_MAX_WITH_NAN = 1, ORC_POOL_AVERAGE = 2 };
-enum { ORC_RELU = 0, ORC_TANH = 1 };
+enum { ORC_RELU = 0, ORC_TANH = 1, ORC_EXP = 3, ORC_LOG = 4, ORC_FLOOR = 5, ORC_SQRT = 6 };  /* 2 is the GPU side's ReLU6 */
 
 /* ------------------------------------------------------------------------- */
 /* conv2d                                                                    */
@@ -456,18 +456,40 @@ int orc_pool_avg_grad(const float* dy, float* dx, const OrcPoolParams* p) {
 /* pointwise, bias, matmul, compat blend                                     */
 /* ------------------------------------------------------------------------- */
 
-/* relu = max(x,0); tanh (src/pointwise/kernels.h:47-78). */
+/* relu = max(x,0), tanh, exp, log, floor, sqrt (src/pointwise/kernels.h:47-137). */
 int orc_pointwise_forward(int op, const float* x, float* y, size_t n) {
-  for (size_t i = 0; i < n; ++i) y[i] = (op == ORC_RELU) ? fmaxf(x[i], 0.f) : tanhf(x[i]);
+  for (size_t i = 0; i < n; ++i) {
+    const float v = x[i];
+    switch (op) {
+      case ORC_RELU: y[i] = fmaxf(v, 0.f); break;
+      case ORC_TANH: y[i] = tanhf(v); break;
+      case ORC_EXP: y[i] = expf(v); break;
+      case ORC_LOG: y[i] = logf(v); break;
+      case ORC_FLOOR: y[i] = floorf(v); break;
+      case ORC_SQRT: y[i] = sqrtf(v); break;
+      default: return 1;
+    }
+  }
   return 0;
 }
 
-/* relu' = (v > 0 ? err : 0); tanh' = (1 - v*v) * err, with v the value handed in as
- * the first argument, which the kernel treats as the forward OUTPUT
- * (src/pointwise/kernels.h:53-78,205-233). */
+/* The gradients as the reference's kernels compute them, with v the value handed in as the
+ * first argument, which the kernel treats as the forward OUTPUT (src/pointwise/kernels.h:53-137,
+ * 205-233): relu' = (v > 0 ? err : 0); tanh' = (1 - v*v) * err; log' = (1 / v) * err;
+ * sqrt' = (0.5 / v) * err; exp' = exp(v) + err (sic: the reference marks it as to be corrected,
+ * kernels.h:94-101).  Floor has no gradient. */
 int orc_pointwise_grad(int op, const float* fwd, const float* err, float* out, size_t n) {
-  for (size_t i = 0; i < n; ++i)
-    out[i] = (op == ORC_RELU) ? (fwd[i] > 0.f ? err[i] : 0.f) : (1.f - fwd[i] * fwd[i]) * err[i];
+  for (size_t i = 0; i < n; ++i) {
+    const float v = fwd[i], e = err[i];
+    switch (op) {
+      case ORC_RELU: out[i] = v > 0.f ? e : 0.f; break;
+      case ORC_TANH: out[i] = (1.f - v * v) * e; break;
+      case ORC_EXP: out[i] = expf(v) + e; break;
+      case ORC_LOG: out[i] = (1.f / v) * e; break;
+      case ORC_SQRT: out[i] = (0.5f / v) * e; break;
+      default: return 1;
+    }
+  }
   return 0;
 }
 

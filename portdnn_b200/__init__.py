@@ -13,6 +13,7 @@ from .api import (  # noqa: F401
     ALGO_DIRECT, ALGO_TILED, ALGO_IM2COL, ALGO_WINOGRAD, ALGO_WINOGRAD_LARGE, ALGO_MATMUL,
     POOL_MAX, POOL_MAX_WITH_NAN, POOL_AVERAGE,
     ACT_NONE, ACT_RELU, ACT_TANH, ACT_RELU6,
+    PW_EXP, PW_LOG, PW_FLOOR, PW_SQRT,
     StatusCode, PortDNNError,
     Conv2DParams, DepthwiseConv2DParams, PoolingParams, SoftmaxParams, BatchNormParams,
     conv_params, depthwise_params, pool_params, calculate_padding,

@@ -16,6 +16,7 @@ F32, F16, BF16 = 0, 1, 2
 ALGO_DIRECT, ALGO_TILED, ALGO_IM2COL, ALGO_WINOGRAD, ALGO_WINOGRAD_LARGE, ALGO_MATMUL = 1, 2, 3, 4, 5, 6
 POOL_MAX, POOL_MAX_WITH_NAN, POOL_AVERAGE = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_TANH, ACT_RELU6 = -1, 0, 1, 2
+PW_EXP, PW_LOG, PW_FLOOR, PW_SQRT = 3, 4, 5, 6  # the other sycldnn::pointwise operators (pointwise() only)
 
 
 class StatusCode(enum.IntEnum):

@@ -660,6 +660,29 @@ __global__ void __launch_bounds__(kBlock)
 // ------------------------------------------------------------------------------------------
 // Pointwise, bias, blend
 // ------------------------------------------------------------------------------------------
+// src/pointwise/kernels.h:47-137: the activations plus exp, log, floor and sqrt.
+__device__ __forceinline__ float pointwise_forward_value(float v, int op) {
+  switch (op) {
+    case PDNN_PW_EXP: return expf(v);
+    case PDNN_PW_LOG: return logf(v);
+    case PDNN_PW_FLOOR: return floorf(v);
+    case PDNN_PW_SQRT: return sqrtf(v);
+    default: return apply_activation(v, op);
+  }
+}
+// v is the forward output, e the incoming gradient (src/pointwise/kernels.h:53-137, 205-233); the
+// exp case is the reference's formula as it stands (exp(v) + e, kernels.h:94-101).
+__device__ __forceinline__ float pointwise_grad_value(float v, float e, int op) {
+  switch (op) {
+    case PDNN_ACT_RELU: return v > 0.f ? e : 0.f;
+    case PDNN_ACT_TANH: return (1.f - v * v) * e;
+    case PDNN_PW_EXP: return expf(v) + e;
+    case PDNN_PW_LOG: return (1.f / v) * e;
+    case PDNN_PW_SQRT: return (0.5f / v) * e;
+    default: return (v > 0.f && v < 6.f) ? e : 0.f;  // ReLU6
+  }
+}
+
 template <typename T, int V, int MODE>  // MODE 0: forward, 1: gradient
 __global__ void __launch_bounds__(kBlock)
     pointwise_kernel(int op, const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, size_t n_packets) {
@@ -668,17 +691,12 @@ __global__ void __launch_bounds__(kBlock)
     load_vec<T, V>(a + i * V, av);
     if (MODE == 0) {
 #pragma unroll
-      for (int j = 0; j < V; ++j) res[j] = apply_activation(av[j], op);
+      for (int j = 0; j < V; ++j) res[j] = pointwise_forward_value(av[j], op);
     } else {
       float bv[V];
       load_vec<T, V>(b + i * V, bv);
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        // src/pointwise/kernels.h:53-78: a is the forward output, b the incoming gradient.
-        if (op == PDNN_ACT_RELU) res[j] = av[j] > 0.f ? bv[j] : 0.f;
-        else if (op == PDNN_ACT_TANH) res[j] = (1.f - av[j] * av[j]) * bv[j];
-        else res[j] = (av[j] > 0.f && av[j] < 6.f) ? bv[j] : 0.f;
-      }
+      for (int j = 0; j < V; ++j) res[j] = pointwise_grad_value(av[j], bv[j], op);
     }
     store_vec<T, V>(out + i * V, res);
   }
@@ -1266,7 +1284,7 @@ int launch_depthwise(int pass, int dtype, const void* in, const void* fil, void*
 }
 
 int launch_pointwise(int op, int dtype, const void* in, void* out, size_t n, cudaStream_t s) {
-  if (op < 0 || op > 2) return fail(PDNN_INVALID_PARAMETER, "pointwise: bad op");
+  if (op < 0 || op > PDNN_PW_SQRT) return fail(PDNN_INVALID_PARAMETER, "pointwise: bad op");
   if (n == 0) return PDNN_OK;
   const int sms = device_sm_count();
   if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
@@ -1285,7 +1303,8 @@ int launch_pointwise(int op, int dtype, const void* in, void* out, size_t n, cud
 }
 
 int launch_pointwise_grad(int op, int dtype, const void* fwd, const void* err, void* out, size_t n, cudaStream_t s) {
-  if (op < 0 || op > 2) return fail(PDNN_INVALID_PARAMETER, "pointwise: bad op");
+  if (op < 0 || op > PDNN_PW_SQRT || op == PDNN_PW_FLOOR)
+    return fail(PDNN_INVALID_PARAMETER, "pointwise: op %d has no gradient", op);
   if (n == 0) return PDNN_OK;
   const int sms = device_sm_count();
   if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
@@ -1305,6 +1324,7 @@ int launch_pointwise_grad(int op, int dtype, const void* fwd, const void* err, v
 int launch_bias_add(int dtype, const void* in, const void* bias, void* out, size_t rows, int channels, int act,
                     cudaStream_t s) {
   if (channels <= 0) return fail(PDNN_INVALID_PARAMETER, "bias: channels must be positive");
+  if (act < PDNN_ACT_NONE || act > PDNN_ACT_RELU6) return fail(PDNN_INVALID_PARAMETER, "bias: unknown activation %d", act);
   if (rows == 0) return PDNN_OK;
   const int sms = device_sm_count();
   if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");

@@ -233,6 +233,26 @@ int main() {
     pointwise::launch<float, pointwise::Relu, pointwise::Gradient>(pin, pin, pout, 4, backend).event.wait();
     r = to_host(pout, 4);
     CHECK(r[0] == 0.f && r[1] == 0.f && r[3] == 3.f, "relu gradient");
+    // the reference's other operators; its gradient tests feed the same ramp as both tensors, so
+    // log' = (1 / v) * v = 1 and sqrt' = (0.5 / v) * v = 0.5 (test/pointwise/{log,sqrt}_grad.cc)
+    std::vector<float> qv = {1.f, 2.f, 3.f, 4.f};
+    float* qin = to_device(qv);
+    pointwise::launch<float, pointwise::Sqrt, pointwise::Forward>(qin, pout, 4, backend).event.wait();
+    CHECK(to_host(pout, 4)[3] == 2.f, "sqrt");
+    pointwise::launch<float, pointwise::Log, pointwise::Forward>(qin, pout, 4, backend).event.wait();
+    CHECK(std::fabs(to_host(pout, 4)[1] - std::log(2.f)) < 1e-6f, "log");
+    pointwise::launch<float, pointwise::Exp, pointwise::Forward>(pin, pout, 4, backend).event.wait();
+    CHECK(std::fabs(to_host(pout, 4)[2] - std::exp(0.5f)) < 1e-6f, "exp");
+    pointwise::launch<float, pointwise::Floor, pointwise::Forward>(pin, pout, 4, backend).event.wait();
+    r = to_host(pout, 4);
+    CHECK(r[0] == -2.f && r[2] == 0.f && r[3] == 3.f, "floor");
+    pointwise::launch<float, pointwise::Log, pointwise::Gradient>(qin, qin, pout, 4, backend).event.wait();
+    CHECK(std::fabs(to_host(pout, 4)[2] - 1.f) < 1e-6f, "log gradient");
+    pointwise::launch<float, pointwise::Sqrt, pointwise::Gradient>(qin, qin, pout, 4, backend).event.wait();
+    CHECK(std::fabs(to_host(pout, 4)[2] - 0.5f) < 1e-6f, "sqrt gradient");
+    CHECK((pointwise::launch<float, pointwise::Floor, pointwise::Gradient>(qin, qin, pout, 4, backend).status ==
+           StatusCode::InvalidParameter),
+          "floor gradient accepted");
 
     binaryop::BinaryParams bp;
     bp.lhs_dims = {16, 2};

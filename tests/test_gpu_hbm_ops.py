@@ -113,6 +113,30 @@ def test_depthwise_filter_backprop_with_caller_workspace(orc):
 
 
 @pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("n", [1, 8, 9, 10, 4096, 100003])
+def test_pointwise_exp_log_floor_sqrt(orc, dtype, n):
+    """The reference's other pointwise operators (test/pointwise/{log,sqrt,floor}_*.cc shapes plus
+    larger ones), forward and gradient, against the oracle; Floor is bit-exact and has no gradient."""
+    rng = np.random.default_rng(17)
+    pos = rounded(rng.uniform(0.25, 4.0, n).astype(np.float32), dtype)   # log / sqrt want positive input
+    x = rounded(rng.uniform(-3.0, 3.0, n).astype(np.float32), dtype)
+    err = rounded(rng.standard_normal(n).astype(np.float32), dtype)
+    pd_, xd, ed = to_dev(pos, dtype), to_dev(x, dtype), to_dev(err, dtype)
+    tol = 1e-6 if dtype == "f32" else TOL[dtype]
+    assert np.array_equal(to_host(pd.pointwise(pd.PW_FLOOR, xd)), orc.pointwise_forward(orc.FLOOR, x))
+    assert rel_err(to_host(pd.pointwise(pd.PW_EXP, xd)), orc.pointwise_forward(orc.EXP, x)) <= tol
+    assert rel_err(to_host(pd.pointwise(pd.PW_LOG, pd_)), orc.pointwise_forward(orc.LOG, pos)) <= tol
+    assert rel_err(to_host(pd.pointwise(pd.PW_SQRT, pd_)), orc.pointwise_forward(orc.SQRT, pos)) <= tol
+    for op_gpu, op_orc, v, vd in ((pd.PW_EXP, orc.EXP, x, xd), (pd.PW_LOG, orc.LOG, pos, pd_),
+                                  (pd.PW_SQRT, orc.SQRT, pos, pd_)):
+        assert rel_err(to_host(pd.pointwise_grad(op_gpu, vd, ed)), orc.pointwise_grad(op_orc, v, err)) <= tol
+    with pytest.raises(pd.PortDNNError):
+        pd.pointwise_grad(pd.PW_FLOOR, xd, ed)
+    with pytest.raises(pd.PortDNNError):
+        pd.pointwise(7, xd)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
 @pytest.mark.parametrize("n", [1, 7, 4096, 100003, 1 << 20])
 def test_pointwise_bias_blend(orc, dtype, n):
     rng = np.random.default_rng(13)

@@ -134,3 +134,13 @@ def test_oracle_matmul_and_pointwise(orc):
     assert orc.pointwise_forward(orc.RELU, x).tolist() == [0.0, 0.0, 2.0]
     assert orc.pointwise_grad(orc.RELU, x, np.array([3.0, 3.0, 3.0], np.float32)).tolist() == [0.0, 0.0, 3.0]
     np.testing.assert_allclose(orc.pointwise_grad(orc.TANH, x, np.ones(3, np.float32)), 1 - x * x)
+    # test/pointwise/{log,sqrt}_grad.cc feed the ramp 1..n as both tensors: log' = (1/v)*v = 1 and
+    # sqrt' = (0.5/v)*v = 0.5 on every shape; floor_forward.cc, log_forward.cc, sqrt_forward.cc
+    for n in (1, 8, 9, 10):
+        r = np.arange(1, n + 1, dtype=np.float32)
+        np.testing.assert_allclose(orc.pointwise_grad(orc.LOG, r, r), np.ones(n), rtol=1e-6)
+        np.testing.assert_allclose(orc.pointwise_grad(orc.SQRT, r, r), np.full(n, 0.5), rtol=1e-6)
+        np.testing.assert_allclose(orc.pointwise_forward(orc.LOG, r), np.log(r.astype(np.float64)), rtol=1e-6, atol=1e-7)
+        np.testing.assert_allclose(orc.pointwise_forward(orc.SQRT, r), np.sqrt(r.astype(np.float64)), rtol=1e-6)
+        assert orc.pointwise_forward(orc.FLOOR, r - 0.5).tolist() == np.floor(r - 0.5).tolist()
+    np.testing.assert_allclose(orc.pointwise_grad(orc.EXP, x, np.ones(3, np.float32)), np.exp(x.astype(np.float64)) + 1, rtol=1e-6)
