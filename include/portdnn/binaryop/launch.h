@@ -1,8 +1,7 @@
-// Binary ops in the two forms the convolution path uses (portDNN's include/portdnn/binaryop/
-// launch.h:58-97, params.h:34-44): Add with a [rows, C] left side and a [1, C] right side (the
-// bias add of tools/layer.h:100-125) and elementwise / scalar Mul and Add (the compat layer's
-// alpha/beta blend).  General N-d broadcasting is outside the hot path and reports
-// InvalidParameter.
+// Binary operators with numpy-style broadcasting, after portDNN's include/portdnn/binaryop/
+// {operators.h:29-35, params.h:31-44, launch.h:58-97}: Add, Sub, Mul, Div over operands of at most
+// four extents each (an empty shape is a scalar).  The bias add of tools/layer.h:100-125 is the
+// case lhs_dims = {rows, C}, rhs_dims = {1, C}.
 #ifndef PORTDNN_B200_BINARYOP_LAUNCH_H_
 #define PORTDNN_B200_BINARYOP_LAUNCH_H_
 #include <vector>
@@ -13,8 +12,25 @@
 namespace sycldnn {
 namespace binaryop {
 
+static constexpr int MAX_DIMS = 4;
+
 struct Add {};
+struct Sub {};
 struct Mul {};
+struct Div {};
+
+namespace internal {
+template <typename Op>
+struct op_code;
+template <>
+struct op_code<Add> { static constexpr int value = PDNN_BINARY_ADD; };
+template <>
+struct op_code<Sub> { static constexpr int value = PDNN_BINARY_SUB; };
+template <>
+struct op_code<Mul> { static constexpr int value = PDNN_BINARY_MUL; };
+template <>
+struct op_code<Div> { static constexpr int value = PDNN_BINARY_DIV; };
+}  // namespace internal
 
 struct BinaryParams {
   std::vector<int> lhs_dims;
@@ -34,16 +50,9 @@ SNNStatus launch(typename Backend::template pointer_type<T const> lhs, typename 
                  typename Backend::template pointer_type<T> out, BinaryParams const& params, Backend& backend,
                  const std::vector<Event>& events = {}) {
   for (const Event& e : events) e.make_stream_wait(backend.get_queue());
-  const size_t ln = internal::count(params.lhs_dims), rn = internal::count(params.rhs_dims);
-  if (ln == 0 || rn == 0) return StatusCode::InvalidParameter;
-  int st = PDNN_INVALID_PARAMETER;
-  if (std::is_same<Op, Add>::value && rn < ln && !params.rhs_dims.empty() && ln % rn == 0 &&
-      params.rhs_dims.back() == int(rn)) {
-    // right side is one row of `rn` channels broadcast over every row of the left side
-    st = pdnn_bias_add(backend::dtype_of<T>::value, lhs, rhs, out, ln / rn, int(rn), PDNN_ACT_NONE, backend.get_queue());
-  } else if (std::is_same<Op, Add>::value && ln == rn) {
-    st = pdnn_scale_blend(backend::dtype_of<T>::value, lhs, 1.f, rhs, 1.f, out, ln, backend.get_queue());
-  }
+  const int st = pdnn_binaryop(internal::op_code<Op>::value, backend::dtype_of<T>::value, lhs, params.lhs_dims.data(),
+                               int(params.lhs_dims.size()), rhs, params.rhs_dims.data(), int(params.rhs_dims.size()),
+                               out, backend.get_queue());
   return SNNStatus{Event{backend.get_queue()}, StatusCode(st)};
 }
 

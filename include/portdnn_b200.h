@@ -223,6 +223,15 @@ int pdnn_pointwise_grad(int op, int dtype, const void* output_forward, const voi
 int pdnn_bias_add(int dtype, const void* input, const void* bias, void* output, size_t rows, int channels,
                   int activation, void* stream);
 
+/* Replaces binaryop::launch<T, Op> (include/portdnn/binaryop/launch.h:58-97, operators.h:29-35):
+ * output = lhs (op) rhs with numpy-style broadcasting.  Each operand has at most four extents
+ * (binaryop/params.h:31), none (n == 0) meaning a scalar; the shorter shape is padded with leading
+ * ones, each pair of extents must be equal or hold a one, the output takes the larger of each
+ * pair (include/portdnn/internal/binaryop/launch.h:34-57).  InvalidParameter otherwise. */
+typedef enum PdnnBinaryOp { PDNN_BINARY_ADD = 0, PDNN_BINARY_SUB = 1, PDNN_BINARY_MUL = 2, PDNN_BINARY_DIV = 3 } PdnnBinaryOp;
+int pdnn_binaryop(int op, int dtype, const void* lhs, const int* lhs_dims, int n_lhs_dims, const void* rhs,
+                  const int* rhs_dims, int n_rhs_dims, void* output, void* stream);
+
 /* out = alpha*a + beta*b elementwise (b may be NULL when beta == 0): the compat layer's
  * alpha/beta blend, include/portdnn/compat/scaling.hpp:202-281, as one pass. */
 int pdnn_scale_blend(int dtype, const void* a, float alpha, const void* b, float beta, void* out, size_t n_items,

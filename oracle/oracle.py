@@ -14,6 +14,7 @@ _LIB = None
 
 FORWARD, INPUT_BACKPROP, FILTER_BACKPROP = 0, 1, 2
 POOL_MAX, POOL_MAX_WITH_NAN, POOL_AVERAGE = 0, 1, 2
+ADD, SUB, MUL, DIV = 0, 1, 2, 3
 RELU, TANH = 0, 1
 EXP, LOG, FLOOR, SQRT = 3, 4, 5, 6
 
@@ -180,6 +181,23 @@ def pointwise_grad(op, fwd, err):
     err, pe = _f(err)
     out = np.empty_like(fwd)
     lib().orc_pointwise_grad(op, pf, pe, out.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), ctypes.c_size_t(fwd.size))
+    return out
+
+
+def binaryop(op, lhs, lhs_dims, rhs, rhs_dims):
+    """lhs (op) rhs with numpy-style broadcasting of at most four extents; raises ValueError for
+    shapes the reference rejects."""
+    lhs, pl = _f(lhs)
+    rhs, pr = _f(rhs)
+    ld = (ctypes.c_int * max(len(lhs_dims), 1))(*lhs_dims)
+    rd = (ctypes.c_int * max(len(rhs_dims), 1))(*rhs_dims)
+    if len(lhs_dims) > 4 or len(rhs_dims) > 4:
+        raise ValueError("binaryop: more than four extents")
+    pad = lambda d: [1] * (4 - len(d)) + list(d)
+    out = np.empty(int(np.prod([max(a, b) for a, b in zip(pad(lhs_dims), pad(rhs_dims))])), dtype=np.float32)
+    if lib().orc_binaryop(op, pl, ld, len(lhs_dims), pr, rd, len(rhs_dims),
+                          out.ctypes.data_as(ctypes.POINTER(ctypes.c_float))) != 0:
+        raise ValueError("binaryop: shapes %s and %s cannot be broadcast" % (list(lhs_dims), list(rhs_dims)))
     return out
 
 

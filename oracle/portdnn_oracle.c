@@ -55,6 +55,7 @@ typedef struct {
 
 enum { ORC_FORWARD = 0, ORC_INPUT_BACKPROP = 1, ORC_FILTER_BACKPROP = 2 };
 enum { ORC_POOL_MAX = 0, ORC_POOL_MAX_WITH_NAN = 1, ORC_POOL_AVERAGE = 2 };
+enum { ORC_ADD = 0, ORC_SUB = 1, ORC_MUL = 2, ORC_DIV = 3 };
 enum { ORC_RELU = 0, ORC_TANH = 1, ORC_EXP = 3, ORC_LOG = 4, ORC_FLOOR = 5, ORC_SQRT = 6 };  /* 2 is the GPU side's ReLU6 */
 
 /* ------------------------------------------------------------------------- */
@@ -490,6 +491,37 @@ int orc_pointwise_grad(int op, const float* fwd, const float* err, float* out, s
       default: return 1;
     }
   }
+  return 0;
+}
+
+/* Binary operators with numpy-style broadcasting over at most four extents: the shorter shape is
+ * padded with leading ones, each pair of extents must be equal or contain a one, and the output
+ * takes the larger of each pair (include/portdnn/internal/binaryop/launch.h:34-57, 79-115; the
+ * operators are src/binaryop/kernels.h Add / Sub / Mul / Div).  Returns 1 for shapes that cannot
+ * be broadcast, more than four extents, an empty operand or an unknown operator. */
+int orc_binaryop(int op, const float* lhs, const int* lhs_dims, int n_lhs, const float* rhs, const int* rhs_dims,
+                 int n_rhs, float* out) {
+  int ld[4] = {1, 1, 1, 1}, rd[4] = {1, 1, 1, 1}, od[4];
+  if (n_lhs < 0 || n_lhs > 4 || n_rhs < 0 || n_rhs > 4 || op < 0 || op > 3) return 1;
+  for (int i = 0; i < n_lhs; ++i) ld[4 - n_lhs + i] = lhs_dims[i];
+  for (int i = 0; i < n_rhs; ++i) rd[4 - n_rhs + i] = rhs_dims[i];
+  for (int i = 0; i < 4; ++i) {
+    if (ld[i] <= 0 || rd[i] <= 0) return 1;
+    if (ld[i] != rd[i] && ld[i] != 1 && rd[i] != 1) return 1;
+    od[i] = ld[i] > rd[i] ? ld[i] : rd[i];
+  }
+  size_t o = 0;
+  for (int a = 0; a < od[0]; ++a)
+    for (int b = 0; b < od[1]; ++b)
+      for (int c = 0; c < od[2]; ++c)
+        for (int d = 0; d < od[3]; ++d, ++o) {
+          const size_t li = (((size_t)(ld[0] == 1 ? 0 : a) * ld[1] + (ld[1] == 1 ? 0 : b)) * ld[2] +
+                             (ld[2] == 1 ? 0 : c)) * ld[3] + (ld[3] == 1 ? 0 : d);
+          const size_t ri = (((size_t)(rd[0] == 1 ? 0 : a) * rd[1] + (rd[1] == 1 ? 0 : b)) * rd[2] +
+                             (rd[2] == 1 ? 0 : c)) * rd[3] + (rd[3] == 1 ? 0 : d);
+          const float x = lhs[li], y = rhs[ri];
+          out[o] = op == ORC_ADD ? x + y : op == ORC_SUB ? x - y : op == ORC_MUL ? x * y : x / y;
+        }
   return 0;
 }
 

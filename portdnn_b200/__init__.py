@@ -13,12 +13,12 @@ from .api import (  # noqa: F401
     ALGO_DIRECT, ALGO_TILED, ALGO_IM2COL, ALGO_WINOGRAD, ALGO_WINOGRAD_LARGE, ALGO_MATMUL,
     POOL_MAX, POOL_MAX_WITH_NAN, POOL_AVERAGE,
     ACT_NONE, ACT_RELU, ACT_TANH, ACT_RELU6,
-    PW_EXP, PW_LOG, PW_FLOOR, PW_SQRT,
+    PW_EXP, PW_LOG, PW_FLOOR, PW_SQRT, BINARY_ADD, BINARY_SUB, BINARY_MUL, BINARY_DIV,
     StatusCode, PortDNNError,
     Conv2DParams, DepthwiseConv2DParams, PoolingParams, SoftmaxParams, BatchNormParams,
     conv_params, depthwise_params, pool_params, calculate_padding,
     conv2d, conv2d_workspace_size, conv2d_validate, depthwise_conv2d, pooling, pooling_max_grad,
-    pointwise, pointwise_grad, bias_add, scale_blend, matmul,
+    pointwise, pointwise_grad, bias_add, binaryop, scale_blend, matmul,
     softmax, batchnorm_params, batchnorm_forward, batchnorm_gradient,
     device_error_record, launch_count, lib, library_path,
 )

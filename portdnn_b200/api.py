@@ -16,6 +16,7 @@ F32, F16, BF16 = 0, 1, 2
 ALGO_DIRECT, ALGO_TILED, ALGO_IM2COL, ALGO_WINOGRAD, ALGO_WINOGRAD_LARGE, ALGO_MATMUL = 1, 2, 3, 4, 5, 6
 POOL_MAX, POOL_MAX_WITH_NAN, POOL_AVERAGE = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_TANH, ACT_RELU6 = -1, 0, 1, 2
+BINARY_ADD, BINARY_SUB, BINARY_MUL, BINARY_DIV = 0, 1, 2, 3
 PW_EXP, PW_LOG, PW_FLOOR, PW_SQRT = 3, 4, 5, 6  # the other sycldnn::pointwise operators (pointwise() only)
 
 
@@ -301,6 +302,26 @@ def bias_add(inp, bias, channels, activation=ACT_NONE, out=None):
         out = torch.empty_like(inp)
     _check(lib().pdnn_bias_add(_dtype_code(inp), _ptr(inp), _ptr(bias), _ptr(out),
                                ctypes.c_size_t(inp.numel() // channels), int(channels), int(activation), _stream()))
+    return out
+
+
+def binaryop(op, lhs, lhs_dims, rhs, rhs_dims, out=None):
+    """binaryop::launch<T, Op> (include/portdnn/binaryop/launch.h:58-97): lhs (op) rhs with numpy-style
+    broadcasting of at most four extents per operand; `op` is one of BINARY_ADD / SUB / MUL / DIV."""
+    torch = _torch()
+    _require_cuda(lhs, rhs, out)
+    lhs_dims, rhs_dims = [int(d) for d in lhs_dims], [int(d) for d in rhs_dims]
+    if out is None:
+        n = max(len(lhs_dims), len(rhs_dims))
+        pad = lambda d: [1] * (n - len(d)) + d
+        numel = 1
+        for x, y in zip(pad(lhs_dims), pad(rhs_dims)):
+            numel *= max(x, y, 0)
+        out = torch.empty(numel, dtype=lhs.dtype, device=lhs.device)
+    ld = (ctypes.c_int * max(len(lhs_dims), 1))(*lhs_dims)
+    rd = (ctypes.c_int * max(len(rhs_dims), 1))(*rhs_dims)
+    _check(lib().pdnn_binaryop(int(op), _dtype_code(lhs), _ptr(lhs), ld, len(lhs_dims), _ptr(rhs), rd, len(rhs_dims),
+                               _ptr(out), _stream()))
     return out
 
 

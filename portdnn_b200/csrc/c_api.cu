@@ -233,6 +233,14 @@ int pdnn_bias_add(int dtype, const void* input, const void* bias, void* output, 
   return launch_bias_add(dtype, input, bias, output, rows, channels, activation, static_cast<cudaStream_t>(stream));
 }
 
+int pdnn_binaryop(int op, int dtype, const void* lhs, const int* lhs_dims, int n_lhs_dims, const void* rhs,
+                  const int* rhs_dims, int n_rhs_dims, void* output, void* stream) {
+  if ((n_lhs_dims > 0 && lhs_dims == nullptr) || (n_rhs_dims > 0 && rhs_dims == nullptr))
+    return fail(PDNN_INVALID_PARAMETER, "binaryop: null extents");
+  return launch_binaryop(op, dtype, lhs, lhs_dims, n_lhs_dims, rhs, rhs_dims, n_rhs_dims, output,
+                         static_cast<cudaStream_t>(stream));
+}
+
 int pdnn_scale_blend(int dtype, const void* a, float alpha, const void* b, float beta, void* out, size_t n_items,
                      void* stream) {
   if (n_items != 0 && (a == nullptr || out == nullptr || (beta != 0.f && b == nullptr)))

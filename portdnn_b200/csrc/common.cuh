@@ -113,6 +113,8 @@ int launch_pointwise(int op, int dtype, const void* in, void* out, size_t n, cud
 int launch_pointwise_grad(int op, int dtype, const void* fwd, const void* err, void* out, size_t n, cudaStream_t s);
 int launch_bias_add(int dtype, const void* in, const void* bias, void* out, size_t rows, int channels, int act,
                     cudaStream_t s);
+int launch_binaryop(int op, int dtype, const void* lhs, const int* lhs_dims, int n_lhs, const void* rhs,
+                    const int* rhs_dims, int n_rhs, void* out, cudaStream_t s);
 int launch_scale_blend(int dtype, const void* a, float alpha, const void* b, float beta, void* out, size_t n,
                        cudaStream_t s);
 int launch_direct_conv(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,

@@ -1362,6 +1362,124 @@ int launch_scale_blend(int dtype, const void* a, float alpha, const void* b, flo
 }
 
 // ------------------------------------------------------------------------------------------
+// Binary operators with broadcasting
+// ------------------------------------------------------------------------------------------
+// out = lhs (op) rhs over an output of at most four extents; an operand's stride is 0 along the
+// extents it is broadcast over (include/portdnn/internal/binaryop/launch.h:34-115,
+// src/binaryop/kernels.h).  A thread owns V consecutive elements of the innermost extent: an
+// operand that runs along it is read as one packet, one that is broadcast along it as one scalar.
+struct BinaryGeometry {
+  unsigned od[4];       // output extents, outermost first
+  unsigned ls[4], rs[4];  // element strides of the operands
+};
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kBlock) binaryop_kernel(int op, const T* __restrict__ lhs, const T* __restrict__ rhs,
+                                                          T* __restrict__ out, BinaryGeometry g, size_t n_packets) {
+  const unsigned inner_packets = g.od[3] / V;
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n_packets; i += (size_t)gridDim.x * kBlock) {
+    // the output has fewer than 2^32 elements (checked by the host): 32-bit divisions
+    const unsigned p = (unsigned)i;
+    unsigned t = p / inner_packets;
+    const unsigned d3 = (p - t * inner_packets) * V;
+    unsigned q = t / g.od[2];
+    const unsigned d2 = t - q * g.od[2];
+    const unsigned d0 = q / g.od[1], d1 = q - d0 * g.od[1];
+    const size_t li = (size_t)d0 * g.ls[0] + (size_t)d1 * g.ls[1] + (size_t)d2 * g.ls[2] + (size_t)d3 * g.ls[3];
+    const size_t ri = (size_t)d0 * g.rs[0] + (size_t)d1 * g.rs[1] + (size_t)d2 * g.rs[2] + (size_t)d3 * g.rs[3];
+    float a[V], b[V], res[V];
+    if (V == 1 || g.ls[3] != 0) {
+      load_vec<T, V>(lhs + li, a);
+    } else {
+      const float v = to_f32(lhs[li]);
+#pragma unroll
+      for (int j = 0; j < V; ++j) a[j] = v;
+    }
+    if (V == 1 || g.rs[3] != 0) {
+      load_vec<T, V>(rhs + ri, b);
+    } else {
+      const float v = to_f32(rhs[ri]);
+#pragma unroll
+      for (int j = 0; j < V; ++j) b[j] = v;
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j)
+      res[j] = op == PDNN_BINARY_ADD ? a[j] + b[j] : op == PDNN_BINARY_SUB ? a[j] - b[j]
+               : op == PDNN_BINARY_MUL ? a[j] * b[j] : a[j] / b[j];
+    store_vec<T, V>(out + i * V, res);
+  }
+}
+
+int launch_binaryop(int op, int dtype, const void* lhs, const int* lhs_dims, int n_lhs, const void* rhs,
+                    const int* rhs_dims, int n_rhs, void* out, cudaStream_t s) {
+  if (op < PDNN_BINARY_ADD || op > PDNN_BINARY_DIV) return fail(PDNN_INVALID_PARAMETER, "binaryop: unknown operator %d", op);
+  if (n_lhs < 0 || n_lhs > 4 || n_rhs < 0 || n_rhs > 4)
+    return fail(PDNN_INVALID_PARAMETER, "binaryop: an operand has more than four extents");
+  long long ld[4] = {1, 1, 1, 1}, rd[4] = {1, 1, 1, 1}, od[4];
+  for (int i = 0; i < n_lhs; ++i) ld[4 - n_lhs + i] = lhs_dims[i];
+  for (int i = 0; i < n_rhs; ++i) rd[4 - n_rhs + i] = rhs_dims[i];
+  long long total = 1;
+  for (int i = 0; i < 4; ++i) {
+    if (ld[i] <= 0 || rd[i] <= 0) return fail(PDNN_INVALID_PARAMETER, "binaryop: operand size cannot be zero");
+    if (ld[i] != rd[i] && ld[i] != 1 && rd[i] != 1)
+      return fail(PDNN_INVALID_PARAMETER, "binaryop: extents %lld and %lld cannot be broadcast", ld[i], rd[i]);
+    od[i] = std::max(ld[i], rd[i]);
+    total *= od[i];
+    if (total > 0xFFFFFFFFll) return fail(PDNN_INDEX_EXCEEDED, "binaryop: more than 2^32 output elements");
+  }
+  if (lhs == nullptr || rhs == nullptr || out == nullptr) return fail(PDNN_INVALID_PARAMETER, "binaryop: null tensor");
+  // Merge neighbouring extents that both operands walk the same way (both run, or both stay): equal
+  // shapes collapse to one extent, the bias form to [rows, C].
+  long long cd[4], cl[4], cr[4];
+  int k = 0;
+  for (int i = 0; i < 4; ++i) {
+    if (od[i] == 1) continue;
+    const bool lb = ld[i] == 1, rb = rd[i] == 1;
+    if (k > 0 && lb == (cl[k - 1] == 1) && rb == (cr[k - 1] == 1)) {
+      cd[k - 1] *= od[i];
+      cl[k - 1] *= ld[i];
+      cr[k - 1] *= rd[i];
+    } else {
+      cd[k] = od[i];
+      cl[k] = ld[i];
+      cr[k] = rd[i];
+      ++k;
+    }
+  }
+  BinaryGeometry g;
+  long long lstride = 1, rstride = 1;
+  for (int i = 3, j = k - 1; i >= 0; --i, --j) {
+    if (j >= 0) {
+      g.od[i] = (unsigned)cd[j];
+      g.ls[i] = cl[j] == 1 ? 0u : (unsigned)lstride;
+      g.rs[i] = cr[j] == 1 ? 0u : (unsigned)rstride;
+      lstride *= cl[j];
+      rstride *= cr[j];
+    } else {
+      g.od[i] = 1u;
+      g.ls[i] = g.rs[i] = 0u;
+    }
+  }
+  const int sms = device_sm_count();
+  if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
+  return dispatch_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    constexpr int VN = Vec16<T>::N;
+    // packets need the innermost extent to be whole packets; every outer stride of an operand
+    // that runs along it is then a multiple of the packet too
+    const bool vec = g.od[3] % VN == 0 && aligned16(lhs) && aligned16(rhs) && aligned16(out);
+    const size_t n = (size_t)total;
+    if (vec)
+      binaryop_kernel<T, VN><<<grid_for(n / VN, kBlock, sms), kBlock, 0, s>>>(
+          op, static_cast<const T*>(lhs), static_cast<const T*>(rhs), static_cast<T*>(out), g, n / VN);
+    else
+      binaryop_kernel<T, 1><<<grid_for(n, kBlock, sms), kBlock, 0, s>>>(
+          op, static_cast<const T*>(lhs), static_cast<const T*>(rhs), static_cast<T*>(out), g, n);
+    return check_launch("binaryop");
+  });
+}
+
+// ------------------------------------------------------------------------------------------
 // Depthwise filter backprop for callers that must not allocate
 // ------------------------------------------------------------------------------------------
 // Some hosts of this library run where a device allocation is off the table: inside a framework

@@ -56,6 +56,13 @@ ms=timeit(lambda: pd.pointwise(pd.ACT_RELU,x,out=y)); res.append(("relu_fwd f16 
 ms=timeit(lambda: pd.pointwise_grad(pd.ACT_RELU,x,y,out=y)); res.append(("relu_grad f16", ms, 6*n/ms/1e6))
 ms=timeit(lambda: pd.pointwise(pd.ACT_TANH,x,out=y)); res.append(("tanh_fwd f16", ms, 4*n/ms/1e6))
 ms=timeit(lambda: pd.bias_add(x,b,256,activation=pd.ACT_RELU,out=y)); res.append(("bias_relu f16", ms, 4*n/ms/1e6))
+# binary operators: equal shapes (a residual add), per-channel row (the bias form), per-image per-channel scale
+z=torch.randn(n,device='cuda').half(); se=torch.rand(256*256,device='cuda').half()
+ms=timeit(lambda: pd.binaryop(pd.BINARY_ADD,x,[256,56,56,256],z,[256,56,56,256],out=y)); res.append(("binary add, equal shapes f16", ms, 6*n/ms/1e6))
+ms=timeit(lambda: pd.binaryop(pd.BINARY_MUL,x,[256*56*56,256],b,[1,256],out=y)); res.append(("binary mul, [rows,C] x [1,C] f16", ms, 4*n/ms/1e6))
+ms=timeit(lambda: pd.binaryop(pd.BINARY_MUL,x,[256,56*56,256],se,[256,1,256],out=y)); res.append(("binary mul, [N,HW,C] x [N,1,C] f16", ms, 4*n/ms/1e6))
+xa=x.abs()
+ms=timeit(lambda: pd.pointwise(pd.PW_SQRT,xa,out=y)); res.append(("sqrt_fwd f16", ms, 4*n/ms/1e6))
 # batchnorm (ResNet stage-1 activation, fp16) and softmax (ImageNet classifier head)
 nb,hb,cb=256,56,256
 xb=torch.randn(nb*hb*hb*cb,device='cuda').half(); dyb=torch.randn_like(xb)

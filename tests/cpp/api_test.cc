@@ -264,6 +264,31 @@ int main() {
     st.event.wait();
     const auto bo = to_host(dx, 32);
     CHECK(bo[0] == 101.f && bo[1] == 202.f && bo[31] == 232.f, "bias add");
+    // the other operators with broadcasting on both sides: x is the ramp 1..32 read as [16, 1, 2],
+    // the right side [1, 3, 1] holds 2, 4, 8 (test/binaryop/binaryop_{sub,mul,div}.cc style shapes)
+    {
+      binaryop::BinaryParams bq;
+      bq.lhs_dims = {16, 1, 2};
+      bq.rhs_dims = {1, 3, 1};
+      std::vector<float> pw = {2.f, 4.f, 8.f};
+      float *pwd = to_device(pw), *bout = dev_alloc(96 * sizeof(float));
+      st = binaryop::launch<float, binaryop::Div>(x, pwd, bout, bq, backend);
+      CHECK(st.status == StatusCode::OK, "div status");
+      st.event.wait();
+      auto dv = to_host(bout, 96);  // out[i][j][k] = x[2 i + k] / pw[j]
+      CHECK(dv[0] == 0.5f && dv[3] == 0.5f && dv[5] == 0.25f && dv[95] == 4.f, "div %g %g %g %g", dv[0], dv[3], dv[5], dv[95]);
+      st = binaryop::launch<float, binaryop::Sub>(x, pwd, bout, bq, backend);
+      st.event.wait();
+      dv = to_host(bout, 96);
+      CHECK(st.status == StatusCode::OK && dv[0] == -1.f && dv[95] == 24.f, "sub");
+      st = binaryop::launch<float, binaryop::Mul>(x, pwd, bout, bq, backend);
+      st.event.wait();
+      dv = to_host(bout, 96);
+      CHECK(st.status == StatusCode::OK && dv[1] == 4.f && dv[94] == 248.f, "mul");
+      bq.rhs_dims = {2, 3, 1};
+      CHECK((binaryop::launch<float, binaryop::Add>(x, pwd, bout, bq, backend).status == StatusCode::InvalidParameter),
+            "extents 16 and 2 broadcast");
+    }
 
     matmul::MatmulParams mp{2, 3, 4, 2, 0.f};
     const auto lv = iota(24, 0), rv = iota(16, 0);
