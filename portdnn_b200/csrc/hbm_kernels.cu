@@ -505,6 +505,93 @@ __global__ void __launch_bounds__(kBlock)
   }
 }
 
+// Input backprop of a 3x3 window with stride 2, multiplier 1, as a gather over dy that visits every
+// dy pixel once per thread column instead of testing nine taps per dx pixel.  With m = (h + pad) / 2
+// the two dx rows 2m - pad and 2m + 1 - pad read dy rows {m, m - 1} (filter rows 0 and 2) and {m}
+// (filter row 1); columns likewise.  A thread owns one packet of channels at one k and walks `rows`
+// values of m downwards: it loads dy[m][k-1], dy[m][k], keeps the two packets of row m - 1 from the
+// previous step, and writes the four dx pixels of the 2x2 block:
+//   dx(2m,   2k)   = d[m][k] w00 + d[m][k-1] w02 + d[m-1][k] w20 + d[m-1][k-1] w22
+//   dx(2m,   2k+1) = d[m][k] w01 + d[m-1][k] w21
+//   dx(2m+1, 2k)   = d[m][k] w10 + d[m][k-1] w12
+//   dx(2m+1, 2k+1) = d[m][k] w11                                   (coordinates before "- pad")
+struct IbpS2Geometry {
+  int H, W, Ho, Wo, C, pad_r, pad_c, N;
+  int M, K;     // values of m and k that touch a dx pixel
+  int rows;     // m values per thread
+  int strips;   // ceil(M / rows)
+};
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kBlock) depthwise_ibp_s2_kernel(const T* __restrict__ dy, const T* __restrict__ w,
+                                                                  T* __restrict__ dx, IbpS2Geometry g, unsigned n_items) {
+  const unsigned cvecs = (unsigned)(g.C / V);
+  for (unsigned idx = blockIdx.x * kBlock + threadIdx.x; idx < n_items; idx += gridDim.x * kBlock) {
+    const unsigned cv = idx % cvecs;
+    unsigned t = idx / cvecs;
+    const int k = (int)(t % (unsigned)g.K);
+    t /= (unsigned)g.K;
+    const int strip = (int)(t % (unsigned)g.strips), n = (int)(t / (unsigned)g.strips);
+    const int c = (int)cv * V;
+    float wf[9][V];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) load_vec<T, V>(w + (size_t)i * g.C + c, wf[i]);
+    const T* dyn = dy + (size_t)n * g.Ho * g.Wo * g.C + c;
+    T* dxn = dx + (size_t)n * g.H * g.W * g.C + c;
+    const bool k_ok = k < g.Wo, k1_ok = k >= 1 && k - 1 < g.Wo;
+    auto load_row = [&](int m, float (&a)[V], float (&b)[V]) {  // a = dy[m][k], b = dy[m][k-1]; zeros outside dy
+#pragma unroll
+      for (int i = 0; i < V; ++i) a[i] = b[i] = 0.f;
+      if (m < 0 || m >= g.Ho) return;
+      const T* row = dyn + (size_t)m * g.Wo * g.C;
+      if (k_ok) load_vec<T, V>(row + (size_t)k * g.C, a);
+      if (k1_ok) load_vec<T, V>(row + (size_t)(k - 1) * g.C, b);
+    };
+    const int m0 = strip * g.rows, m1 = min(m0 + g.rows, g.M);
+    float pk[V], pk1[V], ck[V], ck1[V];
+    load_row(m0 - 1, pk, pk1);
+    const int w0 = 2 * k - g.pad_c, w1 = w0 + 1;
+    const bool w0_ok = w0 >= 0 && w0 < g.W, w1_ok = w1 >= 0 && w1 < g.W;
+    for (int m = m0; m < m1; ++m) {
+      load_row(m, ck, ck1);
+      const int h0 = 2 * m - g.pad_r, h1 = h0 + 1;
+      float o[V];
+      if (h0 >= 0 && h0 < g.H) {
+        T* orow = dxn + (size_t)h0 * g.W * g.C;
+        if (w0_ok) {
+#pragma unroll
+          for (int i = 0; i < V; ++i)
+            o[i] = fmaf(ck[i], wf[0][i], fmaf(ck1[i], wf[2][i], fmaf(pk[i], wf[6][i], pk1[i] * wf[8][i])));
+          store_vec<T, V>(orow + (size_t)w0 * g.C, o);
+        }
+        if (w1_ok) {
+#pragma unroll
+          for (int i = 0; i < V; ++i) o[i] = fmaf(ck[i], wf[1][i], pk[i] * wf[7][i]);
+          store_vec<T, V>(orow + (size_t)w1 * g.C, o);
+        }
+      }
+      if (h1 >= 0 && h1 < g.H) {
+        T* orow = dxn + (size_t)h1 * g.W * g.C;
+        if (w0_ok) {
+#pragma unroll
+          for (int i = 0; i < V; ++i) o[i] = fmaf(ck[i], wf[3][i], ck1[i] * wf[5][i]);
+          store_vec<T, V>(orow + (size_t)w0 * g.C, o);
+        }
+        if (w1_ok) {
+#pragma unroll
+          for (int i = 0; i < V; ++i) o[i] = ck[i] * wf[4][i];
+          store_vec<T, V>(orow + (size_t)w1 * g.C, o);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        pk[i] = ck[i];
+        pk1[i] = ck1[i];
+      }
+    }
+  }
+}
+
 // Filter backprop, stage 1 (src/depthwise_conv2d/kernels.h:259-360 computes the same sum with
 // a work-group reduction): dW[r,s,f] = sum_{n,oh,ow} x[n,oh*st-pad+r,ow*st-pad+s,c] * dy[n,oh,ow,f].
 // blockIdx.x = slice of the N*Ho*Wo pixels, blockIdx.y = tap, blockIdx.z = tile of 32*V features.
@@ -1255,6 +1342,22 @@ int launch_depthwise(int pass, int dtype, const void* in, const void* fil, void*
         if (launch_window3_strip<T, 0>(static_cast<const T*>(in), static_cast<const T*>(fil), static_cast<T*>(out), 1, g,
                                        sms, s) == 0)
           return check_launch("depthwise input backprop (3x3 strips)");
+      }
+    }
+    if (pass == PDNN_INPUT_BACKPROP && vec && p.window_rows == 3 && p.window_cols == 3 && p.stride_rows == 2 &&
+        p.stride_cols == 2) {
+      IbpS2Geometry g{p.in_rows, p.in_cols, p.out_rows, p.out_cols, p.channels, p.pad_rows, p.pad_cols, p.batch,
+                      (p.in_rows - 1 + p.pad_rows) / 2 + 1, (p.in_cols - 1 + p.pad_cols) / 2 + 1, 0, 0};
+      // enough threads to fill the device a few times over, otherwise strips as long as possible
+      const size_t columns = (size_t)p.batch * g.K * (p.channels / VN);
+      g.rows = g.M;
+      while (g.rows > 4 && columns * ((g.M + g.rows - 1) / g.rows) < (size_t)sms * 2048) g.rows = (g.rows + 1) / 2;
+      g.strips = (g.M + g.rows - 1) / g.rows;
+      const size_t n_items = columns * g.strips;
+      if (n_items < 0xFFFF0000ull) {
+        depthwise_ibp_s2_kernel<T, VN><<<grid_for(n_items, kBlock, sms), kBlock, 0, s>>>(
+            static_cast<const T*>(in), static_cast<const T*>(fil), static_cast<T*>(out), g, (unsigned)n_items);
+        return check_launch("depthwise input backprop (3x3, stride 2)");
       }
     }
     const size_t pixels = pass == PDNN_FORWARD ? (size_t)p.batch * p.out_rows * p.out_cols

@@ -78,6 +78,7 @@ DW_SHAPES = [
     # n, h, w, c, mult, window, stride  (MobileNet-v2 layers at batch 2 + ragged)
     (2, 112, 112, 32, 1, 3, 1), (2, 112, 112, 96, 1, 3, 2), (2, 56, 56, 144, 1, 3, 2), (2, 14, 14, 576, 1, 3, 1),
     (2, 7, 7, 960, 1, 3, 1), (2, 9, 11, 6, 2, 3, 2), (1, 12, 12, 5, 1, 5, 1), (3, 8, 8, 8, 4, 3, 1),
+    (2, 15, 13, 16, 1, 3, 2), (3, 28, 30, 8, 1, 3, 2), (1, 5, 4, 32, 1, 3, 2),   # stride-2 gather kernel, odd extents
 ]
 
 
