@@ -379,6 +379,114 @@ __global__ void __launch_bounds__(kBlock)
   }
 }
 
+// The gather for 3x3 windows with stride 2, walking the windows instead of the input pixels.  With
+// m = (h + pad) / 2 the input rows 2m - pad and 2m + 1 - pad lie in windows {m - 1, m} (as their
+// rows 2 and 0) and {m} (row 1); columns likewise.  A thread owns a packet of channels at one
+// window column k and walks `rows` values of m: per step it loads the winner ids and dy of windows
+// (m, k-1) and (m, k), keeps those of row m - 1, and writes the 2x2 block of dx pixels.  Sums run
+// in the order (m-1,k-1), (m-1,k), (m,k-1), (m,k), the order of the general gather above.
+struct PoolS2Geometry {
+  int H, W, Ho, Wo, C, pad_r, pad_c, N;
+  int M, K, rows, strips;
+};
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kBlock)
+    pool_max_grad_s2_kernel(const unsigned char* __restrict__ winner, const T* __restrict__ dy, T* __restrict__ dx,
+                            PoolS2Geometry g, unsigned n_items) {
+  const unsigned cvecs = (unsigned)(g.C / V);
+  for (unsigned idx = blockIdx.x * kBlock + threadIdx.x; idx < n_items; idx += gridDim.x * kBlock) {
+    const unsigned cv = idx % cvecs;
+    unsigned t = idx / cvecs;
+    const int k = (int)(t % (unsigned)g.K);
+    t /= (unsigned)g.K;
+    const int strip = (int)(t % (unsigned)g.strips), n = (int)(t / (unsigned)g.strips);
+    const size_t c = (size_t)cv * V;
+    const size_t out_n = (size_t)n * g.Ho * g.Wo * g.C + c;
+    T* dxn = dx + (size_t)n * g.H * g.W * g.C + c;
+    const bool k_ok = k < g.Wo, k1_ok = k >= 1 && k - 1 < g.Wo;
+    // a = window (m, k), b = window (m, k - 1); id 0 (matches nothing) outside the output
+    auto load_row = [&](int m, unsigned (&wa)[V], float (&da)[V], unsigned (&wb)[V], float (&db)[V]) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        wa[i] = wb[i] = 0u;
+        da[i] = db[i] = 0.f;
+      }
+      if (m < 0 || m >= g.Ho) return;
+      const size_t row = out_n + (size_t)m * g.Wo * g.C;
+      if (k_ok) {
+        load_bytes<V>(winner + row + (size_t)k * g.C, wa);
+        load_vec<T, V>(dy + row + (size_t)k * g.C, da);
+      }
+      if (k1_ok) {
+        load_bytes<V>(winner + row + (size_t)(k - 1) * g.C, wb);
+        load_vec<T, V>(dy + row + (size_t)(k - 1) * g.C, db);
+      }
+    };
+    const int m0 = strip * g.rows, m1 = min(m0 + g.rows, g.M);
+    unsigned pwa[V], pwb[V], cwa[V], cwb[V];
+    float pda[V], pdb[V], cda[V], cdb[V];
+    load_row(m0 - 1, pwa, pda, pwb, pdb);
+    const int w0 = 2 * k - g.pad_c, w1 = w0 + 1;
+    const bool w0_ok = w0 >= 0 && w0 < g.W, w1_ok = w1 >= 0 && w1 < g.W;
+    for (int m = m0; m < m1; ++m) {
+      load_row(m, cwa, cda, cwb, cdb);
+      const int h0 = 2 * m - g.pad_r, h1 = h0 + 1;
+      float o[V];
+      if (h0 >= 0 && h0 < g.H) {
+        T* orow = dxn + (size_t)h0 * g.W * g.C;
+        if (w0_ok) {  // row 2 / 0, column 2 / 0 of the four windows
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            float v = 0.f;
+            if (pwb[i] == 9u) v += pdb[i];
+            if (pwa[i] == 7u) v += pda[i];
+            if (cwb[i] == 3u) v += cdb[i];
+            if (cwa[i] == 1u) v += cda[i];
+            o[i] = v;
+          }
+          store_vec<T, V>(orow + (size_t)w0 * g.C, o);
+        }
+        if (w1_ok) {  // column 1 of windows (m - 1, k) and (m, k)
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            float v = 0.f;
+            if (pwa[i] == 8u) v += pda[i];
+            if (cwa[i] == 2u) v += cda[i];
+            o[i] = v;
+          }
+          store_vec<T, V>(orow + (size_t)w1 * g.C, o);
+        }
+      }
+      if (h1 >= 0 && h1 < g.H) {
+        T* orow = dxn + (size_t)h1 * g.W * g.C;
+        if (w0_ok) {  // row 1 of windows (m, k - 1) and (m, k)
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            float v = 0.f;
+            if (cwb[i] == 6u) v += cdb[i];
+            if (cwa[i] == 4u) v += cda[i];
+            o[i] = v;
+          }
+          store_vec<T, V>(orow + (size_t)w0 * g.C, o);
+        }
+        if (w1_ok) {  // the centre of window (m, k)
+#pragma unroll
+          for (int i = 0; i < V; ++i) o[i] = cwa[i] == 5u ? cda[i] : 0.f;
+          store_vec<T, V>(orow + (size_t)w1 * g.C, o);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        pwa[i] = cwa[i];
+        pwb[i] = cwb[i];
+        pda[i] = cda[i];
+        pdb[i] = cdb[i];
+      }
+    }
+  }
+}
+
 // Average-pool gradient (src/pooling/kernels.h:312-366): dx[i] = sum_o dy[o] / valid(o).
 template <typename T, int V, typename Index>
 __global__ void __launch_bounds__(kBlock)
@@ -1177,7 +1285,18 @@ int launch_pooling_max_grad(int op, int dtype, const void* x, const void* y, con
         else
           pool_winner_kernel<T, PDNN_POOL_MAX_WITH_NAN, VN, unsigned><<<g1, kBlock, 0, s>>>(xt, yt, winner, p, (unsigned)out_items);
         int st = check_launch("pooling max gradient (winners)");
-        if (st == PDNN_OK) {
+        if (st == PDNN_OK && p.window_rows == 3 && p.window_cols == 3 && p.stride_rows == 2 && p.stride_cols == 2) {
+          PoolS2Geometry g{p.in_rows, p.in_cols, p.out_rows, p.out_cols, p.channels, p.pad_rows, p.pad_cols, p.batch,
+                           (p.in_rows - 1 + p.pad_rows) / 2 + 1, (p.in_cols - 1 + p.pad_cols) / 2 + 1, 0, 0};
+          const size_t columns = (size_t)p.batch * g.K * (p.channels / VN);
+          g.rows = g.M;
+          while (g.rows > 4 && columns * ((g.M + g.rows - 1) / g.rows) < (size_t)sms * 2048) g.rows = (g.rows + 1) / 2;
+          g.strips = (g.M + g.rows - 1) / g.rows;
+          const size_t n_items = columns * g.strips;
+          pool_max_grad_s2_kernel<T, VN><<<grid_for(n_items, kBlock, sms), kBlock, 0, s>>>(winner, dyt, dxt, g,
+                                                                                         (unsigned)n_items);
+          st = check_launch("pooling max gradient (3x3 / 2 gather)");
+        } else if (st == PDNN_OK) {
           pool_max_grad_from_winner_kernel<T, VN, unsigned><<<g2, kBlock, 0, s>>>(winner, dyt, dxt, p, (unsigned)in_items);
           st = check_launch("pooling max gradient (gather)");
         }

@@ -18,6 +18,9 @@ POOL_SHAPES = [
     (3, 7, 7, 2048, 7, 1, False),     # ResNet global average pool
     (2, 13, 9, 5, 3, 1, True),        # ragged: scalar path
     (1, 10, 11, 12, 5, 2, True),
+    (2, 15, 13, 16, 3, 2, True),      # 3x3/2 gather kernel: odd extents, padding on both sides
+    (3, 9, 12, 8, 3, 2, False),       # ... VALID
+    (1, 3, 3, 32, 3, 2, True),        # ... a single window row
 ]
 
 
