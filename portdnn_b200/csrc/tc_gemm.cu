@@ -1513,12 +1513,13 @@ __global__ void __launch_bounds__(256) pack_small_c_input_narrow_kernel(const un
                                                                        uint2* __restrict__ xp, int N, int H, int W,
                                                                        int C, int Hp, int Wp, int pad_top,
                                                                        int pad_left) {
-  const size_t total = (size_t)N * Hp * Wp;
-  for (size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
-    const int wp = (int)(idx % Wp);
-    const size_t t = idx / Wp;
-    const int hp = (int)(t % Hp);
-    const int n = (int)(t / Hp);
+  // 32-bit index arithmetic: the host only takes this path with fewer than 2^31 packed pixels
+  const unsigned total = (unsigned)N * (unsigned)Hp * (unsigned)Wp;
+  for (unsigned idx = blockIdx.x * 256u + threadIdx.x; idx < total; idx += gridDim.x * 256u) {
+    const unsigned t = idx / (unsigned)Wp;
+    const int wp = (int)(idx - t * (unsigned)Wp);
+    const int n = (int)(t / (unsigned)Hp);
+    const int hp = (int)(t - (unsigned)n * (unsigned)Hp);
     const int h = hp - pad_top, w = wp - pad_left;
     unsigned v[4] = {0u, 0u, 0u, 0u};
     if (h >= 0 && h < H && w >= 0 && w < W) {
@@ -1619,7 +1620,8 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
   // so a filter row of 8 pixels is 64 bytes and a reduction step is two MMAs instead of four, with
   // half the bytes to pack, load and multiply.  The tiles are 64-byte rows with the 64-byte
   // swizzle; a pixel step of stride_cols * 8 bytes is still a multiple of TMA's 16 bytes.
-  const bool narrow = halo && narrow_enabled() && p.channels <= 4 && p.stride_cols % 2 == 0;
+  const bool narrow = halo && narrow_enabled() && p.channels <= 4 && p.stride_cols % 2 == 0 &&
+                      (size_t)p.batch * sp.Hp * (sp.Wp + 1) < 0x7FFFFFFFull;
   const int pix_bytes = narrow ? 8 : 16;
   const int krows = narrow ? 32 : epr;            // reduction elements per step
   const int Wp = narrow ? (sp.Wp + 1) / 2 * 2 : sp.Wp;  // narrow: rows stay 16-byte aligned
