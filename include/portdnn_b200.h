@@ -138,6 +138,27 @@ int pdnn_conv2d_fused(int dtype, const void* input, const void* filter, void* ou
                       const PdnnConv2DParams* params, int algorithm, const PdnnConvEpilogue* epilogue,
                       void* workspace, size_t workspace_elems, void* stream);
 
+/* Optional fused forms of the two backprop passes.  The reference has none: a training step built
+ * on it runs pointwise::launch<Relu, Gradient> (include/portdnn/pointwise/launch.h:133-179) on every
+ * activation gradient and keeps filter gradients in the tensors' own type; the fused results match
+ * that chain.
+ *  - relu_forward_output (InputBackprop only; NULL = none): the forward output y_prev of the layer
+ *    whose ReLU precedes this convolution, same shape as dx.  The call returns
+ *    dx[i] = y_prev[i] > 0 ? dx[i] : 0, i.e. the gradient with respect to that layer's
+ *    pre-activation, which is what its own two backprop passes consume.
+ *  - output_f32 (FilterBackprop only): dW is written as fp32 even for fp16 / bf16 tensors, so that
+ *    it can land directly in the fp32 buffer a gradient all-reduce works on. */
+typedef struct PdnnBackpropFusion {
+  const void* relu_forward_output;
+  int output_f32;
+} PdnnBackpropFusion;
+
+/* As pdnn_conv2d for PDNN_INPUT_BACKPROP / PDNN_FILTER_BACKPROP, with the fused forms described at
+ * PdnnBackpropFusion (fusion == NULL: exactly pdnn_conv2d). */
+int pdnn_conv2d_backprop_fused(int pass, int dtype, const void* input, const void* filter, void* output,
+                               const PdnnConv2DParams* params, int algorithm, const PdnnBackpropFusion* fusion,
+                               void* workspace, size_t workspace_elems, void* stream);
+
 /* Replaces conv2d::query_workspace_size (include/portdnn/conv2d/workspace_size.h:158-163). Sizes in elements. */
 int pdnn_conv2d_workspace_size(int pass, int dtype, const PdnnConv2DParams* params, int algorithm,
                                size_t* required_elems, size_t* recommended_elems);

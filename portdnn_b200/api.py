@@ -70,6 +70,10 @@ class BatchNormParams(ctypes.Structure):
         [("epsilon", ctypes.c_float), ("momentum", ctypes.c_float), ("input_format", ctypes.c_int)]
 
 
+class _BackpropFusion(ctypes.Structure):
+    _fields_ = [("relu_forward_output", ctypes.c_void_p), ("output_f32", ctypes.c_int)]
+
+
 class _Epilogue(ctypes.Structure):
     _fields_ = [("bias", ctypes.c_void_p), ("activation", ctypes.c_int), ("alpha", ctypes.c_float),
                 ("beta", ctypes.c_float)]
@@ -184,19 +188,35 @@ def conv2d_workspace_size(pass_, dtype, params, algorithm):
 
 
 def conv2d(pass_, inp, fil, params, algorithm=ALGO_TILED, out=None, workspace=None, bias=None, activation=ACT_NONE,
-           alpha=1.0, beta=0.0):
+           alpha=1.0, beta=0.0, relu_forward_output=None, output_f32=False):
     """conv2d::launch<T, ConvType>(input, filter, output, params, selector, backend, workspace, size)
     (include/portdnn/conv2d/launch.h:59-72) with the selector's answer passed as ``algorithm``.
     Slots: Forward (x, w) -> y; InputBackprop (dy, w) -> dx; FilterBackprop (x, dy) -> dW.
-    bias / activation / alpha / beta select the fused forward epilogue."""
+    bias / activation / alpha / beta select the fused forward epilogue; relu_forward_output (InputBackprop)
+    and output_f32 (FilterBackprop) the fused backprop forms of PdnnBackpropFusion."""
     torch = _torch()
     _require_cuda(inp, fil, out, workspace, bias)
     n_in, n_fil, n_out = conv_sizes(pass_, params)
     if inp.numel() != n_in or fil.numel() != n_fil:
         raise ValueError("tensor sizes do not match the parameters: %d/%d, %d/%d" % (inp.numel(), n_in, fil.numel(), n_fil))
+    backprop_fused = relu_forward_output is not None or output_f32
+    if backprop_fused and (pass_ == FORWARD or (relu_forward_output is not None and pass_ != INPUT_BACKPROP) or
+                           (output_f32 and pass_ != FILTER_BACKPROP)):
+        raise ValueError("relu_forward_output belongs to the input backprop, output_f32 to the filter backprop")
+    _require_cuda(relu_forward_output)
     if out is None:
-        out = torch.empty(n_out, dtype=inp.dtype, device=inp.device)
+        out = torch.empty(n_out, dtype=torch.float32 if output_f32 else inp.dtype, device=inp.device)
+    if out.numel() != n_out or out.dtype != (torch.float32 if output_f32 else inp.dtype):
+        raise ValueError("output tensor does not match the parameters")
     ws_elems = workspace.numel() * workspace.element_size() // inp.element_size() if workspace is not None else 0
+    if backprop_fused:
+        if relu_forward_output is not None and relu_forward_output.numel() != n_out:
+            raise ValueError("relu_forward_output must have the shape of the input gradient")
+        fus = _BackpropFusion(relu_forward_output.data_ptr() if relu_forward_output is not None else None, int(output_f32))
+        _check(lib().pdnn_conv2d_backprop_fused(pass_, _dtype_code(inp), _ptr(inp), _ptr(fil), _ptr(out),
+                                                ctypes.byref(params), algorithm, ctypes.byref(fus), _ptr(workspace),
+                                                ctypes.c_size_t(ws_elems), _stream()))
+        return out
     fused = bias is not None or activation != ACT_NONE or alpha != 1.0 or beta != 0.0
     if fused:
         if pass_ != FORWARD:

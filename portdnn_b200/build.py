@@ -1,17 +1,22 @@
 """Builds libportdnn_b200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
 
+Each source is compiled to its own object (in parallel, only when it or a header changed) and
+the objects are linked into the shared library.
+
 Usage: python -m portdnn_b200.build [--force] [--verbose]
 """
 import os
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
+OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libportdnn_b200.so")
 SOURCES = ["c_api.cu", "hbm_kernels.cu", "direct_conv.cu", "tc_gemm.cu", "winograd.cu", "norm_kernels.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
-         "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-shared", "-cudart", "shared"]
+         "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
 
 
 def _nvcc():
@@ -21,24 +26,44 @@ def _nvcc():
     return "nvcc"
 
 
-def needs_build():
-    if not os.path.exists(LIB):
+def _headers():
+    return [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))] + \
+        [os.path.join(HERE, "..", "include", "portdnn_b200.h")]
+
+
+def _stale(target, deps):
+    if not os.path.exists(target):
         return True
-    t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "portdnn_b200.h")]
+    t = os.path.getmtime(target)
     return any(os.path.getmtime(d) > t for d in deps)
+
+
+def needs_build():
+    return _stale(LIB, [os.path.join(CSRC, s) for s in SOURCES] + _headers())
+
+
+def _run(cmd, verbose):
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if verbose or res.returncode != 0:
+        sys.stderr.write(res.stdout)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed: %s" % " ".join(cmd))
 
 
 def build(force=False, verbose=False):
     if not force and not needs_build():
         return LIB
-    cmd = [_nvcc()] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
-        [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB]
-    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
-    if verbose or res.returncode != 0:
-        sys.stderr.write(res.stdout)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed building %s" % LIB)
+    os.makedirs(OBJ, exist_ok=True)
+    nvcc, headers = _nvcc(), _headers()
+    jobs = []
+    for src in SOURCES:
+        path, obj = os.path.join(CSRC, src), os.path.join(OBJ, src[:-3] + ".o")
+        if force or _stale(obj, [path] + headers):
+            jobs.append([nvcc] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", path, "-o", obj])
+    with ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 1))) as pool:
+        list(pool.map(lambda c: _run(c, verbose), jobs))
+    objs = [os.path.join(OBJ, s[:-3] + ".o") for s in SOURCES]
+    _run([nvcc, "-shared", "-cudart", "shared", "-Xcompiler", "-fPIC"] + objs + ["-o", LIB], verbose)
     return LIB
 
 

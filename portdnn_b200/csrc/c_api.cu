@@ -13,29 +13,42 @@ char* last_error_buffer() {
   return buf;
 }
 
+int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return dev;
+}
+
+// SM count of the CURRENT device (-1 if it is not an sm_100 part), looked up once per device.
 int device_sm_count() {
-  static int sms = -2;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    int dev = 0;
+  static std::mutex mu;
+  static int table[kMaxDevices];
+  static bool known[kMaxDevices] = {};
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) return -1;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!known[dev]) {
     cudaDeviceProp prop;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
       cudaGetLastError();
-      sms = -1;
-      return;
+      return -1;
     }
-    sms = prop.major >= 10 ? prop.multiProcessorCount : -1;  // the kernels are sm_100a only
+    table[dev] = prop.major >= 10 ? prop.multiProcessorCount : -1;  // the kernels are sm_100a only
     // Scratch that a call takes from the stream-ordered allocator goes back to the device's
     // default pool; keep it there instead of returning it to the driver at the next
     // synchronisation, or every such call pays for a fresh allocation.
     cudaMemPool_t pool;
-    if (sms > 0 && cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+    if (table[dev] > 0 && cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
       unsigned long long keep = 1ull << 32;  // up to 4 GiB cached
       cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
     }
     cudaGetLastError();
-  });
-  return sms;
+    known[dev] = true;
+  }
+  return table[dev];
 }
 
 namespace {
@@ -84,8 +97,42 @@ int validate_conv(int pass, const PdnnConv2DParams* p, int algorithm) {
   return PDNN_OK;
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256) widen_to_f32_kernel(const T* __restrict__ in, float* __restrict__ out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) out[i] = to_f32(in[i]);
+}
+
+// The direct kernel with the fused backprop forms applied afterwards (shapes the tensor-core engine
+// does not take): the ReLU-gradient mask as a pointwise pass in place, an fp32 filter gradient
+// through a temporary in the tensors' own type.
+int run_direct_backprop(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
+                        const PdnnBackpropFusion* fusion, cudaStream_t s) {
+  const size_t es = dtype_size(dtype);
+  if (pass == PDNN_FILTER_BACKPROP && fusion != nullptr && fusion->output_f32 && dtype != PDNN_F32) {
+    const size_t n = (size_t)p.window_rows * p.window_cols * (p.channels / p.groups) * p.features;
+    void* tmp = nullptr;
+    if (cudaMallocAsync(&tmp, n * es, s) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(PDNN_ALLOCATION_PROBLEM, "conv2d: cannot allocate %zu bytes for the filter gradient", n * es);
+    }
+    int st = launch_direct_conv(pass, dtype, in, fil, tmp, p, nullptr, s);
+    if (st == PDNN_OK) {
+      const unsigned grid = grid_for(n, 256, device_sm_count());
+      if (dtype == PDNN_F16) widen_to_f32_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(tmp), static_cast<float*>(out), n);
+      else widen_to_f32_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(tmp), static_cast<float*>(out), n);
+      st = check_launch("filter gradient widening");
+    }
+    cudaFreeAsync(tmp, s);
+    return st;
+  }
+  const int st = launch_direct_conv(pass, dtype, in, fil, out, p, nullptr, s);
+  if (st != PDNN_OK || pass != PDNN_INPUT_BACKPROP || fusion == nullptr || fusion->relu_forward_output == nullptr) return st;
+  return launch_pointwise_grad(PDNN_ACT_RELU, dtype, fusion->relu_forward_output, out, out,
+                               (size_t)p.batch * p.in_rows * p.in_cols * p.channels, s);
+}
+
 int run_conv(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams* p, int algorithm,
-             const PdnnConvEpilogue* epi, void* ws, size_t ws_elems, void* stream) {
+             const PdnnConvEpilogue* epi, const PdnnBackpropFusion* fusion, void* ws, size_t ws_elems, void* stream) {
   int st = validate_conv(pass, p, algorithm);
   if (st != PDNN_OK) return st;
   if (dtype < PDNN_F32 || dtype > PDNN_BF16) return fail(PDNN_INVALID_PARAMETER, "conv2d: unknown dtype %d", dtype);
@@ -95,12 +142,15 @@ int run_conv(int pass, int dtype, const void* in, const void* fil, void* out, co
   // The Winograd tags run F(2x2,3x3) when the caller brought the scratch it needs; without it the
   // implicit-GEMM kernel, which needs none, runs the layer instead of reporting
   // InsufficientWorkspace (include/portdnn/internal/conv2d/winograd/launch.h:280).
-  if ((algorithm == PDNN_ALGO_WINOGRAD || algorithm == PDNN_ALGO_WINOGRAD_LARGE) &&
-      winograd_applicable(pass, dtype, *p) && ws != nullptr && ws_elems >= winograd_workspace_elems(pass, *p) &&
+  if ((algorithm == PDNN_ALGO_WINOGRAD || algorithm == PDNN_ALGO_WINOGRAD_LARGE) && fusion == nullptr &&
+      winograd_applicable(pass, dtype, *p) && ws != nullptr && ws_elems >= winograd_workspace_elems(pass, dtype, *p) &&
       aligned16(ws) && aligned16(in) && aligned16(fil) && aligned16(out))
     return launch_winograd(pass, dtype, in, fil, out, *p, epi, ws, ws_elems, s);
-  if (algorithm != PDNN_ALGO_DIRECT && tc_conv_supported(pass, dtype, in, fil, out, *p))
-    return tc_conv2d(pass, dtype, in, fil, out, *p, epi, ws, ws_elems, s);
+  if (algorithm != PDNN_ALGO_DIRECT && tc_conv_supported(pass, dtype, in, fil, out, *p)) {
+    const int st2 = tc_conv2d(pass, dtype, in, fil, out, *p, epi, fusion, ws, ws_elems, s);
+    if (st2 != kNeedsDirect) return st2;
+  }
+  if (pass != PDNN_FORWARD) return run_direct_backprop(pass, dtype, in, fil, out, *p, fusion, s);
   return launch_direct_conv(pass, dtype, in, fil, out, *p, epi, s);
 }
 
@@ -113,7 +163,17 @@ extern "C" {
 
 int pdnn_conv2d(int pass, int dtype, const void* input, const void* filter, void* output,
                 const PdnnConv2DParams* params, int algorithm, void* workspace, size_t workspace_elems, void* stream) {
-  return run_conv(pass, dtype, input, filter, output, params, algorithm, nullptr, workspace, workspace_elems, stream);
+  return run_conv(pass, dtype, input, filter, output, params, algorithm, nullptr, nullptr, workspace, workspace_elems,
+                  stream);
+}
+
+int pdnn_conv2d_backprop_fused(int pass, int dtype, const void* input, const void* filter, void* output,
+                               const PdnnConv2DParams* params, int algorithm, const PdnnBackpropFusion* fusion,
+                               void* workspace, size_t workspace_elems, void* stream) {
+  if (pass != PDNN_INPUT_BACKPROP && pass != PDNN_FILTER_BACKPROP)
+    return fail(PDNN_INVALID_PARAMETER, "conv2d: the fused backprop forms exist for the two backprop passes only");
+  return run_conv(pass, dtype, input, filter, output, params, algorithm, nullptr, fusion, workspace, workspace_elems,
+                  stream);
 }
 
 int pdnn_conv2d_fused(int dtype, const void* input, const void* filter, void* output, const PdnnConv2DParams* params,
@@ -121,8 +181,8 @@ int pdnn_conv2d_fused(int dtype, const void* input, const void* filter, void* ou
                       void* stream) {
   if (epilogue != nullptr && (epilogue->activation < PDNN_ACT_NONE || epilogue->activation > PDNN_ACT_RELU6))
     return fail(PDNN_INVALID_PARAMETER, "conv2d: unknown activation %d", epilogue->activation);
-  return run_conv(PDNN_FORWARD, dtype, input, filter, output, params, algorithm, epilogue, workspace, workspace_elems,
-                  stream);
+  return run_conv(PDNN_FORWARD, dtype, input, filter, output, params, algorithm, epilogue, nullptr, workspace,
+                  workspace_elems, stream);
 }
 
 int pdnn_conv2d_validate(int pass, const PdnnConv2DParams* params, int algorithm) {
@@ -143,7 +203,7 @@ int pdnn_conv2d_workspace_size(int pass, int dtype, const PdnnConv2DParams* para
   // reported as recommended, not required: without it the layer still runs (on the implicit GEMM).
   if ((algorithm == PDNN_ALGO_WINOGRAD || algorithm == PDNN_ALGO_WINOGRAD_LARGE) &&
       winograd_applicable(pass, dtype, *params)) {
-    const size_t w = winograd_workspace_elems(pass, *params);
+    const size_t w = winograd_workspace_elems(pass, dtype, *params);
     if (w > elems) elems = w;
   }
   if (recommended_elems) *recommended_elems = elems;

@@ -96,7 +96,10 @@ inline unsigned grid_for(size_t items, int block, int sm_count) {
   return (unsigned)(need < cap ? need : cap);
 }
 
-int device_sm_count();
+// Per-device state is kept in small tables indexed by the CUDA device ordinal.
+constexpr int kMaxDevices = 64;
+int current_device();    // ordinal of the current device, -1 on error
+int device_sm_count();   // SM count of the current device; -1 if it is not an sm_100 part
 
 // ---- operator launchers implemented in the .cu files ------------------------------------------
 int launch_pooling(int op, int direction, int dtype, const void* in, void* out, const PdnnPoolingParams& p,
@@ -132,7 +135,7 @@ int launch_batchnorm_gradient(int dtype, const void* input, const void* gradient
 
 // Winograd F(2x2,3x3) (winograd.cu): forward and input backprop of 3x3 stride-1 layers.
 bool winograd_applicable(int pass, int dtype, const PdnnConv2DParams& p);
-size_t winograd_workspace_elems(int pass, const PdnnConv2DParams& p);
+size_t winograd_workspace_elems(int pass, int dtype, const PdnnConv2DParams& p);
 int launch_winograd(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
                     const PdnnConvEpilogue* epi, void* ws, size_t ws_elems, cudaStream_t s);
 

@@ -1715,17 +1715,25 @@ constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB of fp32 partial sums
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 namespace {
-constexpr int kMaxDevices = 64;
 std::mutex g_static_scratch_mutex;
 float* g_static_scratch_ptr[kMaxDevices] = {};
 
 // The array's name is only a host-side handle: the address the kernels need has to be asked for,
-// once per device and with that device current.
-int static_scratch_for_current_device(float** out) {
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
-    cudaGetLastError();
-    return fail(PDNN_ALLOCATION_PROBLEM, "static scratch: no usable current device");
+// once per device and with that device current.  The kernels run on the device the stream belongs
+// to, so a stream of another device than the current one is refused (its launch would fail anyway)
+// rather than handed the current device's copy of the array.
+int static_scratch_for_current_device(float** out, cudaStream_t s) {
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) return fail(PDNN_ALLOCATION_PROBLEM, "static scratch: no usable current device");
+  if (s != nullptr && s != cudaStreamLegacy && s != cudaStreamPerThread) {
+    int stream_dev = dev;
+    if (cudaStreamGetDevice(s, &stream_dev) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(PDNN_INVALID_PARAMETER, "static scratch: not a valid stream");
+    }
+    if (stream_dev != dev)
+      return fail(PDNN_INVALID_PARAMETER, "static scratch: the stream belongs to device %d but device %d is current",
+                  stream_dev, dev);
   }
   std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
   if (g_static_scratch_ptr[dev] == nullptr) {
@@ -1757,7 +1765,7 @@ int launch_depthwise_filter_backprop_static(int dtype, const void* in, const voi
                 "scratch holds at most %zu",
                 n_out, kStaticScratchBytes / sizeof(float));
   float* partial = nullptr;
-  const int st0 = static_scratch_for_current_device(&partial);
+  const int st0 = static_scratch_for_current_device(&partial, s);
   if (st0 != PDNN_OK) return st0;
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);

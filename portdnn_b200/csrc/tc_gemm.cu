@@ -22,7 +22,6 @@
 #include "umma.cuh"
 
 #include <algorithm>
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -41,21 +40,6 @@ constexpr int kBarsPerGroup = 3 * kMaxStages + 4;  // full, empty, ready per sta
 constexpr int kBarBlockBytes = 512;                // barriers of two groups, the resident-B barrier, TMEM slot, abort flag
 
 __device__ unsigned g_error_record[4];
-
-// Optional timeline of CTA 0 (compiled in with -DPDNN_TC_TRACE, for kernel development only):
-// SM clock at a few points of each tile's life, read back with pdnn_debug_trace().
-#ifdef PDNN_TC_TRACE
-constexpr int kTraceTiles = 512, kTraceKinds = 8;
-__device__ long long g_trace[kTraceKinds * kTraceTiles];
-#define PDNN_TRACE(kind, idx)                                                                  \
-  do {                                                                                         \
-    if (blockIdx.x == 0 && (idx) < (unsigned)kTraceTiles) g_trace[(kind) * kTraceTiles + (idx)] = clock64(); \
-  } while (0)
-#else
-#define PDNN_TRACE(kind, idx) \
-  do {                        \
-  } while (0)
-#endif
 
 // One reduction step of a forward-style GEMM: which input map, at which pixel offset, against which
 // filter tap.  In halo mode an entry stands for `cnt` taps that differ only by one input row each
@@ -127,6 +111,14 @@ struct alignas(64) GemmArgs {
   // layout), MMAs per step (row bytes / 32) and bytes of one step's B tile (bn * row bytes).
   int a_row_bytes, kmmas;
   unsigned b_step_bytes;
+  // Fast epilogue only: the forward output of the layer whose ReLU the result is the gradient of,
+  // laid out exactly like `out` (stride_w / stride_h / stride_n).  Where it is not positive the
+  // result is replaced by zero: pointwise::launch<Relu, Gradient> applied on the way out.
+  const void* relu_mask;
+  int mask_smem_bytes;  // 256 bytes per epilogue warp for the sign bits of a 32-row block
+  // Time limit of one barrier wait; a wait that lasts longer means a lost arrival, and the CTA
+  // gives up (see umma::mbar_wait).
+  unsigned long long wait_limit_ns;
 };
 
 struct TileCoord {
@@ -388,9 +380,10 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
 
 // `bias_s` is the shared-space address of the CTA's copy of the bias vector (0: no bias); the copy
 // is padded with zeros up to a multiple of 64 columns.
-template <typename OutT>
+// `keep` (MASK only) holds one byte per 16-byte chunk of the row: bit e set = element e is kept.
+template <typename OutT, bool MASK>
 __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bool zero, uint32_t bias_s, int col0,
-                                                   int act, uint8_t* row_ptr, int row, int chunk_base) {
+                                                   int act, uint8_t* row_ptr, int row, int chunk_base, uint2 keep) {
   using P2 = typename Pair<OutT>::type;
   const P2 zero2 = Pair<OutT>::splat(0.f), six2 = Pair<OutT>::splat(6.f);
   const bool has_bias = bias_s != 0u;
@@ -409,6 +402,13 @@ __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bo
       if (act == PDNN_ACT_RELU6) v = __hmin2(v, six2);
       o[i] = pair_bits(v);
     }
+    if (MASK) {
+      const int c = chunk_base + g;
+      const uint32_t kb = ((c < 4 ? keep.x : keep.y) >> (8 * (c & 3))) & 0xFFu;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        o[i] &= ((kb >> (2 * i)) & 1u ? 0x0000FFFFu : 0u) | ((kb >> (2 * i + 1)) & 1u ? 0xFFFF0000u : 0u);
+    }
     *reinterpret_cast<uint4*>(row_ptr + (((chunk_base + g) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
@@ -418,10 +418,54 @@ __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bo
 // accumulators are rounded to the output type first and bias and activation are applied to
 // packed pairs in that type - the arithmetic of separate convolution, bias-add and activation
 // passes.
-template <typename OutT>
+// Sign bits of a 32-row x 64-column block of the ReLU mask tensor (16-bit elements), gathered with
+// coalesced loads: lane l reads 16-byte chunk l % 8 of rows l / 8, l / 8 + 4, ..., turns every chunk
+// into one byte (bit e = element e is positive) and leaves it in the warp's 256-byte table at
+// [row][chunk]; afterwards lane r reads the eight bytes of its own row r.  A positive 16-bit float
+// is a positive 16-bit integer, so the test is an integer compare (NaNs do not occur in a ReLU
+// output).  `q32` is the first row of the warp inside the row tile.
+__device__ __forceinline__ uint2 load_relu_keep_bits(const GemmArgs& a, const TileCoord& t, int q32, int col, int lane,
+                                                     uint8_t* table) {
+  const int sh_w = __ffs(a.etw) - 1, sh_h = __ffs(a.eth) - 1;
+  const uint16_t* mask = static_cast<const uint16_t*>(a.relu_mask);
+  const int chunk = lane & 7, c = col + chunk * 8;
+  uint4 v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int row = q32 + i * 4 + (lane >> 3);
+    const int w = t.w0 + (row & (a.etw - 1)), h = t.h0 + ((row >> sh_w) & (a.eth - 1)), n = t.n0 + (row >> (sh_w + sh_h));
+    const bool valid = w < a.ext_w && h < a.ext_h && n < a.ext_n && c < a.ext_cols;
+    v[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (valid)
+      v[i] = __ldg(reinterpret_cast<const uint4*>(mask + (long long)n * a.stride_n + (long long)h * a.stride_h +
+                                                  (long long)w * a.stride_w + c));
+  }
+  __syncwarp();  // the previous block's table has been read by every lane
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t wd[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+    uint32_t byte = 0u;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t m = __vcmpgts2(wd[k], 0u);  // 0xFFFF in every halfword that is > 0 as a signed integer
+      byte |= ((m & 1u) | ((m >> 15) & 2u)) << (2 * k);
+    }
+    table[(i * 4 + (lane >> 3)) * 8 + chunk] = (uint8_t)byte;
+  }
+  __syncwarp();
+  return *reinterpret_cast<const uint2*>(table + lane * 8);
+}
+
+// The common case of the staged epilogue, kept short because a lone warp per scheduler is
+// latency-bound: 16-bit output, alpha == 1, optional bias, activation none / ReLU / ReLU6.  The
+// accumulators are rounded to the output type first and bias and activation are applied to
+// packed pairs in that type - the arithmetic of separate convolution, bias-add and activation
+// passes.  MASK: the result is additionally zeroed wherever a.relu_mask is not positive.
+template <typename OutT, bool MASK>
 __device__ __forceinline__ void epilogue_tile_tma_fast(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc,
                                                        int lane, bool zero, const WarpStore& ws,
-                                                       uint32_t& store_count, uint32_t bias_s) {
+                                                       uint32_t& store_count, uint32_t bias_s, int q32,
+                                                       uint8_t* mask_table) {
   const int act = a.act;
 #pragma unroll 1
   for (int c0 = 0; c0 < a.bn; c0 += 64, ++store_count) {
@@ -431,19 +475,20 @@ __device__ __forceinline__ void epilogue_tile_tma_fast(const GemmArgs& a, const 
       tmem_ld_32x32(tmem_acc + (uint32_t)c0, acc0);
       tmem_ld_32x32(tmem_acc + (uint32_t)(c0 + 32), acc1);
     }
+    uint2 keep = make_uint2(0u, 0u);
+    if (MASK) keep = load_relu_keep_bits(a, t, q32, t.nf0 + c0, lane, mask_table);
     wait_slice_free(ws, lane);
     if (!zero) tmem_wait_ld();
-    if (threadIdx.x == 64) PDNN_TRACE(6, store_count);
     uint8_t* row_ptr = ws.buf + slot * 4096u + (size_t)lane * 128;
-    fast_convert_store<OutT>(acc0, zero, bias_s, t.nf0 + c0, act, row_ptr, lane, 0);
-    fast_convert_store<OutT>(acc1, zero, bias_s, t.nf0 + c0 + 32, act, row_ptr, lane, 4);
-    if (threadIdx.x == 64) PDNN_TRACE(7, store_count);
+    fast_convert_store<OutT, MASK>(acc0, zero, bias_s, t.nf0 + c0, act, row_ptr, lane, 0, keep);
+    fast_convert_store<OutT, MASK>(acc1, zero, bias_s, t.nf0 + c0 + 32, act, row_ptr, lane, 4, keep);
     issue_slice_store(a, t, ws, slot, t.nf0 + c0, lane);
   }
 }
 
 // EPI selects the epilogue compiled into the instantiation: 0 = direct stores from registers,
-// 1 = staged TMA store with fp32 arithmetic, 2 = staged TMA store with packed 16-bit arithmetic.
+// 1 = staged TMA store with fp32 arithmetic, 2 = staged TMA store with packed 16-bit arithmetic,
+// 3 = as 2 with the ReLU-gradient mask (GemmArgs::relu_mask).
 // One epilogue per instantiation keeps each kernel's register allocation tight.
 //
 // A CTA runs up to two independent pipelines ("groups") side by side, each with its own TMA
@@ -514,7 +559,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
   // indexing by absolute column still works
   const int bias_col0 = a.bias_tile_only ? ((int)blockIdx.x % a.n_tiles) * a.bn : 0;
   const uint32_t bias_s =
-      (EPI == 2 && a.bias != nullptr) ? bar_base + kBarBlockBytes - (uint32_t)bias_col0 * 2u : 0u;
+      (EPI >= 2 && a.bias != nullptr) ? bar_base + kBarBlockBytes - (uint32_t)bias_col0 * 2u : 0u;
 
   if (threadIdx.x == 0) {
     for (int g = 0; g < kMaxGroups; ++g) {
@@ -543,7 +588,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
   // so nothing of it is still waiting for an SM.
   grid_dependency_wait();
   grid_launch_dependents();
-  if (EPI == 2 && a.bias != nullptr) {
+  if (EPI >= 2 && a.bias != nullptr) {
     // the CTA's copy of the bias vector, zero beyond the last column
     const OutT* bias = static_cast<const OutT*>(a.bias);
     uint4* dst = reinterpret_cast<uint4*>(bar_mem + kBarBlockBytes);
@@ -633,13 +678,11 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
           ph ^= 1u;
         }
       };
-      [[maybe_unused]] unsigned ptile = 0;
       TileWalker walker;
       walker.init(a, first_tile, tile_step);
 #pragma unroll 1
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, walker.advance()) {
         const TileCoord t = walker.coord(a);
-        ++ptile;
         if (!a.a_mn) {
 #pragma unroll 1
           for (int tap = 0; tap < a.num_taps && ok; ++tap) {
@@ -650,7 +693,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
             const uint32_t tx = halo ? (uint32_t)(a.th + e.cnt - 1) * (uint32_t)(a.tw * a.a_row_bytes) : tx_bytes;
 #pragma unroll 1
             for (int cb = 0, kc = 0; cb < cblocks; ++cb, kc += epr) {
-              if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g_error_record, 0x100u + (unsigned)s)) {
+              if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g_error_record, a.wait_limit_ns, 0x100u + (unsigned)s)) {
                 ok = false;
                 break;
               }
@@ -676,7 +719,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
               in = t.ks_begin / (a.slabs_w * a.slabs_h);
 #pragma unroll 1
           for (int ks = t.ks_begin; ks < t.ks_end; ++ks) {
-            if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g_error_record, 0x100u + (unsigned)s)) {
+            if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g_error_record, a.wait_limit_ns, 0x100u + (unsigned)s)) {
               ok = false;
               break;
             }
@@ -716,10 +759,10 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       const uint32_t a_kadv = a.a_kadv >> 4, b_kadv = a.b_kadv >> 4, idesc = a.idesc;
       const uint32_t lo_off = part_bytes >> 4;
       int s = 0;
-      uint32_t ph = 0, tcount = 0;
+      uint32_t ph = 0;
       uint32_t buf = 0, aph = 0;  // accumulator buffer of this tile and the parity of its barriers
       bool ok = true;
-      if (b_res && first_tile < total_tiles) ok = mbar_wait(bres_bar, 0u, abort_flag, g_error_record, 0x600u);
+      if (b_res && first_tile < total_tiles) ok = mbar_wait(bres_bar, 0u, abort_flag, g_error_record, a.wait_limit_ns, 0x600u);
       // Loop constants of the forward-style main loop, all in units of 16 bytes (the unit of a
       // descriptor's address field).
       struct {
@@ -756,11 +799,9 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       TileWalker walker;
       walker.init(a, first_tile, tile_step);
 #pragma unroll 1
-      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++tcount, walker.advance()) {
-        if (grp == 0) PDNN_TRACE(0, tcount);
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, walker.advance()) {
         const TileCoord t = walker.coord(a);
-        if (!mbar_wait(acc_empty_bar((int)buf), aph ^ 1u, abort_flag, g_error_record, 0x200u + buf)) break;
-        if (grp == 0) PDNN_TRACE(1, tcount);
+        if (!mbar_wait(acc_empty_bar((int)buf), aph ^ 1u, abort_flag, g_error_record, a.wait_limit_ns, 0x200u + buf)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = grp_tmem + buf * acc_stride;
         uint32_t accumulate = 0u;
@@ -775,13 +816,12 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
             const int cnt = halo ? (int)((fw.cnts >> (4 * tap)) & 15u) : 1;
 #pragma unroll 1
             for (int cb = 0; cb < fw.cblocks; ++cb) {
-              if (!mbar_wait(full_bar(s), ph, abort_flag, g_error_record, 0x300u + (unsigned)s)) {
+              if (!mbar_wait(full_bar(s), ph, abort_flag, g_error_record, a.wait_limit_ns, 0x300u + (unsigned)s)) {
                 ok = false;
                 break;
               }
               // no tcgen05 fence here: the stage was written by TMA and is read by the MMA, both in
               // the async proxy, and the mbarrier's complete_tx orders them
-              if (grp == 0 && tap == 0 && cb == 0) PDNN_TRACE(2, tcount);
               // start addresses stay below 2^18, so adding to the low descriptor word never carries
               // into the neighbouring field
               uint32_t a_lo = fw.a_lo0 + sa16 + fw.my_a16;
@@ -832,12 +872,11 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
         } else {
 #pragma unroll 1
           for (int ks = t.ks_begin; ks < t.ks_end; ++ks) {
-            if (!mbar_wait(SPLIT ? ready_bar(s) : full_bar(s), ph, abort_flag, g_error_record, 0x300u + (unsigned)s)) {
+            if (!mbar_wait(SPLIT ? ready_bar(s) : full_bar(s), ph, abort_flag, g_error_record, a.wait_limit_ns, 0x300u + (unsigned)s)) {
               ok = false;
               break;
             }
             tc_fence_after_sync();
-            if (grp == 0 && ks == t.ks_begin) PDNN_TRACE(2, tcount);
             const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
             uint64_t da = a_desc0 + (uint64_t)(sa >> 4);
             uint64_t db = b_desc0 + (uint64_t)((sa + kABytes) >> 4);
@@ -862,7 +901,6 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
           }
         }
         if (!ok) break;
-        if (grp == 0) PDNN_TRACE(3, tcount);
         if (t.ks_end > t.ks_begin) mma_commit(acc_full_bar((int)buf));
         else mbar_arrive(acc_full_bar((int)buf));  // nothing to accumulate: the epilogue writes zeros
         if (++buf == acc_bufs) {
@@ -875,7 +913,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     // ------------------------------- epilogue ------------------------------------------------
     const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
     [[maybe_unused]] const int row = q * 32 + lane;
-    uint32_t tcount = 0, store_count = 0;
+    uint32_t store_count = 0;
     const int wslot = role - 2;  // 0..3: which staging slices of the group this warp owns
     WarpStore ws;
     ws.nsw = a.nsw;
@@ -889,18 +927,19 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     TileWalker walker;
     walker.init(a, first_tile, tile_step);
 #pragma unroll 1
-    for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++tcount, walker.advance()) {
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step, walker.advance()) {
       TileCoord t = walker.coord(a);
       t.w0 += sub_w;
       t.h0 += sub_h;
       t.n0 += sub_n;
-      if (!mbar_wait(acc_full_bar((int)buf), aph, abort_flag, g_error_record, 0x400u + buf)) break;
+      if (!mbar_wait(acc_full_bar((int)buf), aph, abort_flag, g_error_record, a.wait_limit_ns, 0x400u + buf)) break;
       tc_fence_after_sync();
-      if (warp == 2 && lane == 0) PDNN_TRACE(4, tcount);
       const uint32_t tmem_acc = grp_tmem + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
       const bool zero = !(t.ks_end > t.ks_begin);
-      if constexpr (EPI == 2) {
-        epilogue_tile_tma_fast<OutT>(a, t, tmem_acc, lane, zero, ws, store_count, bias_s);
+      if constexpr (EPI >= 2) {
+        // the sign-bit tables of the eight epilogue warps follow the bias copy
+        uint8_t* mask_table = bar_mem + kBarBlockBytes + a.bias_smem_bytes + (grp * 4 + wslot) * 256;
+        epilogue_tile_tma_fast<OutT, EPI == 3>(a, t, tmem_acc, lane, zero, ws, store_count, bias_s, q * 32, mask_table);
       } else if constexpr (EPI == 1) {
         epilogue_tile_tma<OutT>(a, t, tmem_acc, lane, zero, ws, store_count);
       } else {
@@ -909,7 +948,6 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar((int)buf));
-      if (warp == 2 && lane == 0) PDNN_TRACE(5, tcount);
       if (++buf == acc_bufs) {
         buf = 0;
         aph ^= 1u;
@@ -933,7 +971,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       const TileCoord t = walker.coord(a);
 #pragma unroll 1
       for (int ks = t.ks_begin; ks < t.ks_end; ++ks) {
-        if (!mbar_wait(full_bar(s), ph, abort_flag, g_error_record, 0x500u + (unsigned)s)) {
+        if (!mbar_wait(full_bar(s), ph, abort_flag, g_error_record, a.wait_limit_ns, 0x500u + (unsigned)s)) {
           ok = false;
           break;
         }
@@ -1062,25 +1100,7 @@ void choose_box(int total, int W, int H, int N, int* tw, int* th, int* tn) {
 
 constexpr size_t kMaxResidentB = 128 * 1024;
 
-// PDNN_TC_BRES=0 switches the resident-filter variant off (for experiments).
-bool b_resident_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("PDNN_TC_BRES");
-    return e == nullptr || atoi(e) != 0;
-  }();
-  return on;
-}
-
 constexpr int kPlanAgain = -2;  // internal: the halo plan does not fit, plan the layer without it
-
-// PDNN_TC_HALO=0 switches the halo variant off (for experiments).
-bool halo_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("PDNN_TC_HALO");
-    return e == nullptr || atoi(e) != 0;
-  }();
-  return on;
-}
 
 // Row-tile box for halo mode: one image (tn == 1), tw a multiple of 8 so that a shift by one tile
 // row is a whole number of 1024-byte swizzle groups.  `rows` is the number of taps that share a
@@ -1102,78 +1122,11 @@ bool choose_box_halo(int W, int H, int rows, int* tw, int* th) {
   return best < 1e29;
 }
 
-// PDNN_TC_NARROW_STEM=0 keeps 8 channels per pixel in the few-channel stem path (for experiments).
-bool narrow_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("PDNN_TC_NARROW_STEM");
-    return e == nullptr || atoi(e) != 0;
-  }();
-  return on;
-}
-
-// PDNN_TC_PDL=0 launches the GEMM kernel without programmatic dependent launch (for experiments).
-bool pdl_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("PDNN_TC_PDL");
-    return e == nullptr || atoi(e) != 0;
-  }();
-  return on;
-}
-
-// PDNN_TC_PAIR=0 switches pair mode off (for experiments).
-bool pair_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("PDNN_TC_PAIR");
-    return e == nullptr || atoi(e) != 0;
-  }();
-  return on;
-}
-
-// Experiments: PDNN_TC_PAIR_MIN = fewest reduction steps that pair, PDNN_TC_PAIR_BN=128 keeps pair
-// mode on 128-column tiles.
-int pair_min_steps() {
-  static const int n = [] {
-    const char* e = getenv("PDNN_TC_PAIR_MIN");
-    return e == nullptr ? 32 : atoi(e);
-  }();
-  return n;
-}
-bool pair_wide() {
-  static const bool on = [] {
-    const char* e = getenv("PDNN_TC_PAIR_BN");
-    return e == nullptr || atoi(e) != 128;
-  }();
-  return on;
-}
-
-// PDNN_TC_GROUPS=1 runs one pipeline per CTA instead of two (for experiments).
-int group_count() {
-  static const int n = [] {
-    const char* e = getenv("PDNN_TC_GROUPS");
-    return e != nullptr && atoi(e) == 1 ? 1 : 2;
-  }();
-  return n;
-}
-
 // Tiles with a short reduction spend most of their time in the epilogue: column tiles of at most
 // 128 leave room for two accumulator buffers per pipeline, so that the next tile's MMAs overlap it.
-// PDNN_TC_NARROW=0/1 overrides the heuristic (for experiments).
-bool want_narrow(int ksteps, int cols) {
-  static const int forced = [] {
-    const char* e = getenv("PDNN_TC_NARROW");
-    return e == nullptr ? -1 : atoi(e);
-  }();
-  if (forced >= 0) return forced != 0;
-  return ksteps <= 4 || cols <= 128;
-}
+bool want_narrow(int ksteps, int cols) { return ksteps <= 4 || cols <= 128; }
 
 int pick_bn(long long row_tiles, int cols, int unit, int max_bn, int sms, int ksteps = 1 << 30) {
-  static const int forced_bn = [] {
-    const char* e = getenv("PDNN_TC_BN");  // experiments: force the column-tile width where it is legal
-    return e == nullptr ? 0 : atoi(e);
-  }();
-  if (forced_bn > 0 && forced_bn <= max_bn && forced_bn % unit == 0 && forced_bn % 64 == 0 && cols >= forced_bn)
-    return forced_bn;
   if (want_narrow(ksteps, cols)) max_bn = std::min(max_bn, 128);
   sms *= 2;  // two pipelines per CTA work on two tiles at a time
   // cost ~ waves * (bn + fixed overhead); unit: granularity the B loader needs
@@ -1262,12 +1215,14 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
                      : 0;
   }
   const bool split = compute_dtype == PDNN_F32;
-  g.groups = split ? 1 : group_count();
+  g.groups = split ? 1 : 2;
   g.acc_stride = std::max(32, next_pow2(g.bn));
   g.acc_bufs = g.groups * 2 * g.acc_stride <= 512 ? 2 : 1;
   g.tmem_cols = next_pow2(g.groups * g.acc_bufs * g.acc_stride);
   g.bias_smem_bytes = 0;
   g.bias_tile_only = 0;
+  if (!g.epi_fast) g.relu_mask = nullptr;  // only the fast epilogue applies the mask; the caller checks
+  g.mask_smem_bytes = g.relu_mask != nullptr ? 8 * 256 : 0;
   if (g.pair && (split || g.groups != 2 || !g.tma_store)) return false;  // the caller plans again without pairing
   if (g.epi_fast && g.bias != nullptr) {
     const int padded = ceil_div(g.n_tiles * g.bn, 64) * 64;
@@ -1286,7 +1241,7 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   else ksteps = g.res_taps * g.cblocks;
   g.b_res = 0;
   g.b_res_bytes = 0;
-  const int fixed = 1024 + kBarBlockBytes + g.bias_smem_bytes;
+  const int fixed = 1024 + kBarBlockBytes + g.bias_smem_bytes + g.mask_smem_bytes;
   auto staging = [&](int nsw) { return g.tma_store ? g.groups * 4 * nsw * 4096 : 0; };
   // A small filter (all taps, all column tiles) is kept in shared memory for the whole kernel:
   // the filter tiles are the part of the L2 -> SM traffic that never changes.
@@ -1298,7 +1253,7 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
     g.stages = std::min(kMaxStages, stages_with(g.nsw));
     return g.stages >= 2;
   }
-  if (!g.a_mn && !split && g.tma_store && g.b_batch_mul == 0 && b_resident_enabled()) {
+  if (!g.a_mn && !split && g.tma_store && g.b_batch_mul == 0) {
     const size_t res_tile = (size_t)ksteps * g.b_step_bytes, res_all = res_tile * g.n_tiles;
     const int a_stage = g.halo ? (int)g.halo_stage_bytes : kABytes;
     auto fits = [&](size_t res) {
@@ -1344,10 +1299,12 @@ GemmKernel select_kernel(bool split, int epi, int out_dtype) {
   }
   switch (out_dtype) {
     case PDNN_F16:
-      return epi == 2 ? umma_gemm_kernel<false, 2, __half>
+      return epi == 3 ? umma_gemm_kernel<false, 3, __half>
+             : epi == 2 ? umma_gemm_kernel<false, 2, __half>
                       : epi == 1 ? umma_gemm_kernel<false, 1, __half> : umma_gemm_kernel<false, 0, __half>;
     case PDNN_BF16:
-      return epi == 2 ? umma_gemm_kernel<false, 2, __nv_bfloat16>
+      return epi == 3 ? umma_gemm_kernel<false, 3, __nv_bfloat16>
+             : epi == 2 ? umma_gemm_kernel<false, 2, __nv_bfloat16>
                       : epi == 1 ? umma_gemm_kernel<false, 1, __nv_bfloat16> : umma_gemm_kernel<false, 0, __nv_bfloat16>;
     default:
       return epi == 1 ? umma_gemm_kernel<false, 1, float> : epi == 0 ? umma_gemm_kernel<false, 0, float> : nullptr;
@@ -1367,22 +1324,31 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   // At least 120 KB, so that two CTAs never share an SM: the second one would wait for TMEM
   // columns the first one holds.
   size_t smem = 1024 + (size_t)g.b_res_bytes + (size_t)rings * g.stages * stage +
-                (g.tma_store ? (size_t)g.groups * g.nsw * 4 * 4096 : 0) + kBarBlockBytes + (size_t)g.bias_smem_bytes;
+                (g.tma_store ? (size_t)g.groups * g.nsw * 4 * 4096 : 0) + kBarBlockBytes + (size_t)g.bias_smem_bytes + (size_t)g.mask_smem_bytes;
   smem = std::max<size_t>(smem, 120 * 1024);
   if (smem > (size_t)kSmemBudget) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: plan needs %zu bytes of shared memory", smem);
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    for (int sp = 0; sp < 2; ++sp)
-      for (int epi = 0; epi < 3; ++epi)
-        for (int dt = 0; dt < 3; ++dt) {
-          GemmKernel k = select_kernel(sp != 0, epi, dt);
-          if (k != nullptr && attr_err == cudaSuccess)
-            attr_err = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-        }
-  });
-  if (attr_err != cudaSuccess) return fail(PDNN_ALLOCATION_PROBLEM, "cannot opt in to %d bytes of shared memory", kSmemBudget);
-  const int epi = g.epi_fast ? 2 : (g.tma_store ? 1 : 0);
+  // The opt-in to large dynamic shared memory is a per-device attribute of each kernel: it is made
+  // once for every device this process launches on, with that device current.
+  {
+    static std::mutex mu;
+    static bool opted_in[kMaxDevices] = {};
+    const int dev = current_device();
+    if (dev < 0 || dev >= kMaxDevices) return fail(PDNN_ALLOCATION_PROBLEM, "tensor-core gemm: no usable current device");
+    std::lock_guard<std::mutex> lock(mu);
+    if (!opted_in[dev]) {
+      for (int sp = 0; sp < 2; ++sp)
+        for (int epi = 0; epi < 4; ++epi)
+          for (int dt = 0; dt < 3; ++dt) {
+            GemmKernel k = select_kernel(sp != 0, epi, dt);
+            if (k != nullptr && cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) != cudaSuccess) {
+              cudaGetLastError();
+              return fail(PDNN_ALLOCATION_PROBLEM, "cannot opt in to %d bytes of shared memory", kSmemBudget);
+            }
+          }
+      opted_in[dev] = true;
+    }
+  }
+  const int epi = g.epi_fast ? (g.relu_mask != nullptr ? 3 : 2) : (g.tma_store ? 1 : 0);
   GemmKernel kernel = select_kernel(split, epi, g.out_dtype);
   if (kernel == nullptr) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: no kernel for this output type");
   const int sms = device_sm_count();
@@ -1403,8 +1369,10 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
-  const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, g);
+  cfg.numAttrs = 1;
+  GemmArgs args = g;
+  args.wait_limit_ns = kWaitLimitNs;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, args);
   if (le != cudaSuccess) {
     cudaGetLastError();
     return fail(PDNN_ALLOCATION_PROBLEM, "tensor-core gemm: launch failed: %s", cudaGetErrorString(le));
@@ -1598,7 +1566,7 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
   // parity class is one reduction step over one copy.
   const int rows_per_class = ceil_div(p.window_rows, p.stride_rows);
   int hw = 0, hh = 0;
-  const bool halo = try_halo && halo_enabled() && dtype != PDNN_F32 && rows_per_class >= 2 && rows_per_class <= 15 &&
+  const bool halo = try_halo && dtype != PDNN_F32 && rows_per_class >= 2 && rows_per_class <= 15 &&
                     p.stride_rows <= 8 && p.window_rows >= p.stride_rows && choose_box_halo(p.out_cols, p.out_rows, rows_per_class, &hw, &hh);
   if (halo) {
     g.tw = hw;
@@ -1620,7 +1588,7 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
   // so a filter row of 8 pixels is 64 bytes and a reduction step is two MMAs instead of four, with
   // half the bytes to pack, load and multiply.  The tiles are 64-byte rows with the 64-byte
   // swizzle; a pixel step of stride_cols * 8 bytes is still a multiple of TMA's 16 bytes.
-  const bool narrow = halo && narrow_enabled() && p.channels <= 4 && p.stride_cols % 2 == 0 &&
+  const bool narrow = halo && p.channels <= 4 && p.stride_cols % 2 == 0 &&
                       (size_t)p.batch * sp.Hp * (sp.Wp + 1) < 0x7FFFFFFFull;
   const int pix_bytes = narrow ? 8 : 16;
   const int krows = narrow ? 32 : epr;            // reduction elements per step
@@ -1720,7 +1688,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   // rows, so each column becomes one reduction step over one copy (halo mode), provided the whole
   // filter can stay in shared memory.
   int hw = 0, hh = 0;
-  const bool halo = try_halo && halo_enabled() && dtype != PDNN_F32 && p.stride_rows == 1 && p.stride_cols == 1 &&
+  const bool halo = try_halo && dtype != PDNN_F32 && p.stride_rows == 1 && p.stride_cols == 1 &&
                     p.window_rows >= 2 && p.window_rows <= 15 && p.window_cols <= 8 &&
                     (size_t)p.window_rows * p.window_cols * ceil_div(p.channels, epr) * 128u *
                             (size_t)(ceil_div(p.features, 64) * 64) <= kMaxResidentB &&
@@ -1744,12 +1712,12 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   // pulls from L2 per MMA: the two pipelines then share one B tile per stage (pair mode).  Measured
   // on ResNet-50 shapes it pays from about 32 reduction steps, or from 16 with 512 or more features;
   // shorter reductions lose more to the unhidden epilogue of the 256-column accumulators.
-  const bool pairing = try_halo && !halo && pair_enabled() && dtype != PDNN_F32 && hwcf && p.features % 128 == 0 &&
-                       (ksteps_all >= pair_min_steps() || (ksteps_all >= 16 && p.features >= 512)) && row_tiles >= 2 &&
+  const bool pairing = try_halo && !halo && dtype != PDNN_F32 && hwcf && p.features % 128 == 0 &&
+                       (ksteps_all >= 32 || (ksteps_all >= 16 && p.features >= 512)) && row_tiles >= 2 &&
                        (!epi || epi->beta == 0.f);
   if (pairing) {
     g.pair = 1;
-    g.bn = (p.features % 256 == 0 && pair_wide()) ? 256 : 128;
+    g.bn = p.features % 256 == 0 ? 256 : 128;
     if (g.tiles_w % 2 == 0) {
       g.pair_dim = 1;
       g.tiles_w /= 2;
@@ -1822,8 +1790,12 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   return status;
 }
 
+// relu_mask (may be null): the forward output of the layer that produced the tensor dx is the gradient
+// of; dx is zeroed wherever it is not positive (in the epilogue where the fast epilogue runs, else
+// by a pointwise pass afterwards).
 int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, const PdnnConv2DParams& p,
-                        cudaStream_t s, bool try_halo = true) {
+                        const void* relu_mask, cudaStream_t s, bool try_halo = true) {
+  bool mask_pending = false;  // some parity class could not apply the mask in its epilogue
   const size_t es = dtype_size(dtype);
   const int sms = device_sm_count();
   const bool hwcf = p.filter_format == 0;
@@ -1841,7 +1813,7 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
       // Stride 1: the taps of one window column read overlapping rows of dy, as in the forward
       // pass (halo mode), if the whole filter can stay in shared memory.
       int hw = 0, hh = 0;
-      const bool halo = try_halo && halo_enabled() && dtype != PDNN_F32 && p.stride_rows == 1 && p.stride_cols == 1 &&
+      const bool halo = try_halo && dtype != PDNN_F32 && p.stride_rows == 1 && p.stride_cols == 1 &&
                         p.window_rows >= 2 && p.window_rows <= 15 && p.window_cols <= 8 &&
                         (size_t)p.window_rows * p.window_cols * ceil_div(p.features, epr) * 128u *
                                 (size_t)(ceil_div(p.channels, 64) * 64) <= kMaxResidentB &&
@@ -1917,6 +1889,9 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
         if (!make_map(&g.b_map, dtype, true, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
       }
       set_epilogue(g, nullptr);
+      g.relu_mask = (relu_mask != nullptr && !mask_pending && aligned16(relu_mask))
+                        ? static_cast<const char*>(relu_mask) + ((size_t)qh * p.in_cols + qw) * p.channels * es
+                        : nullptr;
       g.out = static_cast<char*>(dx) + ((size_t)qh * p.in_cols + qw) * p.channels * es;
       g.out_dtype = dtype;
       g.ext_w = Wq;
@@ -1933,13 +1908,20 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
                                 (uint64_t)p.stride_rows * p.in_cols * p.channels * es,
                                 (uint64_t)p.in_rows * p.in_cols * p.channels * es};
         if (!setup_store(g, dtype, od, os)) {
-          if (g.halo) return conv_input_backprop(dtype, dy, w, dx, p, s, false);  // plan again without the halo
+          if (g.halo) return conv_input_backprop(dtype, dy, w, dx, p, relu_mask, s, false);  // plan again without the halo
           return PDNN_INVALID_PARAMETER;
         }
+      }
+      if (relu_mask != nullptr && g.relu_mask == nullptr) {
+        // An earlier class may already have masked its pixels; masking them again changes nothing.
+        mask_pending = true;
       }
       const int st_ = launch_gemm(g, dtype, s);
       if (st_ != PDNN_OK) return st_;
     }
+  if (mask_pending)
+    return launch_pointwise_grad(PDNN_ACT_RELU, dtype, relu_mask, dx, dx,
+                                 (size_t)p.batch * p.in_rows * p.in_cols * p.channels, s);
   return PDNN_OK;
 }
 
@@ -1984,9 +1966,9 @@ __global__ void __launch_bounds__(256) reduce_splits_kernel(const float* __restr
 // Xr is the 128-byte packed run of 8 pixels x CP channels that output pixel reads for filter
 // row r.  The 64 rows of the result are exactly [s (8)][c (CP)], i.e. the packed filter layout;
 // the final kernel sums the pixel splits and drops the padding entries.
-template <typename T>
+template <typename T, typename OutT = T>
 __global__ void __launch_bounds__(256)
-    unpack_small_c_filter_grad_kernel(const float* __restrict__ partial, T* __restrict__ dw, int splits, int R, int S,
+    unpack_small_c_filter_grad_kernel(const float* __restrict__ partial, OutT* __restrict__ dw, int splits, int R, int S,
                                       int C, int K, int rows_per_tap) {
   constexpr int CP = 16 / sizeof(T);
   const size_t total = (size_t)R * S * C * K;
@@ -2001,7 +1983,7 @@ __global__ void __launch_bounds__(256)
     const size_t src = ((size_t)r * rows_per_tap + (size_t)sidx * CP + c) * K + k;
     float sum = 0.f;
     for (int sp = 0; sp < splits; ++sp) sum += partial[(size_t)sp * split_stride + src];
-    dw[idx] = from_f32<T>(sum);
+    dw[idx] = from_f32<OutT>(sum);
   }
 }
 
@@ -2037,7 +2019,7 @@ SmallCFbpPlan plan_small_c_fbp(int dtype, const PdnnConv2DParams& p, int sms) {
 // Returns PDNN_OK, an error, or -1 if a tensor map could not be encoded (the caller falls back to
 // the direct kernel).
 int conv_filter_backprop_small_c(int dtype, const void* x, const void* dy, void* dw, const PdnnConv2DParams& p,
-                                 void* ws, size_t ws_elems, cudaStream_t s) {
+                                 bool out_f32, void* ws, size_t ws_elems, cudaStream_t s) {
   const size_t es = dtype_size(dtype);
   const int sms = device_sm_count();
   const int epr = dtype == PDNN_F32 ? 32 : 64;
@@ -2138,6 +2120,9 @@ int conv_filter_backprop_small_c(int dtype, const void* x, const void* dy, void*
     if (dtype == PDNN_F32)
       unpack_small_c_filter_grad_kernel<float><<<grid, 256, 0, s>>>(partial, static_cast<float*>(dw), f.splits,
                                                                     p.window_rows, p.window_cols, p.channels, p.features, epr);
+    else if (out_f32)  // 16-bit tensors (8 channels per packed pixel), fp32 gradient
+      unpack_small_c_filter_grad_kernel<__half, float><<<grid, 256, 0, s>>>(
+          partial, static_cast<float*>(dw), f.splits, p.window_rows, p.window_cols, p.channels, p.features, epr);
     else if (dtype == PDNN_F16)
       unpack_small_c_filter_grad_kernel<__half><<<grid, 256, 0, s>>>(partial, static_cast<__half*>(dw), f.splits,
                                                                      p.window_rows, p.window_cols, p.channels, p.features, epr);
@@ -2150,8 +2135,10 @@ int conv_filter_backprop_small_c(int dtype, const void* x, const void* dy, void*
   return st;
 }
 
-int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, const PdnnConv2DParams& p, void* ws,
-                         size_t ws_elems, cudaStream_t s) {
+// out_f32: dW is written as fp32 whatever the tensors' type (the split reduction, or the epilogue
+// when there is one split, produces it directly).
+int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, const PdnnConv2DParams& p, bool out_f32,
+                         void* ws, size_t ws_elems, cudaStream_t s) {
   const size_t es = dtype_size(dtype);
   const int sms = device_sm_count();
   const int epr = dtype == PDNN_F32 ? 32 : 64;
@@ -2216,7 +2203,7 @@ int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, con
     g.out_dtype = PDNN_F32;
   } else {
     g.out = dw;
-    g.out_dtype = dtype;
+    g.out_dtype = out_f32 ? PDNN_F32 : dtype;
   }
   g.ext_w = p.channels;
   g.ext_h = g.ext_n = 1;
@@ -2238,7 +2225,7 @@ int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, con
   int st = launch_gemm(g, dtype, s);
   if (st == PDNN_OK && f.splits > 1) {
     const unsigned grid = grid_for(n_out, 256, sms);
-    if (dtype == PDNN_F32) reduce_splits_kernel<float><<<grid, 256, 0, s>>>(partial, static_cast<float*>(dw), f.splits, n_out);
+    if (dtype == PDNN_F32 || out_f32) reduce_splits_kernel<float><<<grid, 256, 0, s>>>(partial, static_cast<float*>(dw), f.splits, n_out);
     else if (dtype == PDNN_F16) reduce_splits_kernel<__half><<<grid, 256, 0, s>>>(partial, static_cast<__half*>(dw), f.splits, n_out);
     else reduce_splits_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(partial, static_cast<__nv_bfloat16*>(dw), f.splits, n_out);
     st = check_launch("filter backprop split reduction");
@@ -2248,9 +2235,9 @@ int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, con
 }
 
 // ---- SIMT matmul ---------------------------------------------------------------------------------
-template <typename T>
+template <typename T, typename OutT = T>
 __global__ void __launch_bounds__(256) simt_matmul_kernel(const T* __restrict__ lhs, const T* __restrict__ rhs,
-                                                          T* __restrict__ out, int tl, int tr, int batches, int m, int k,
+                                                          OutT* __restrict__ out, int tl, int tr, int batches, int m, int k,
                                                           int n, float beta) {
   const size_t total = (size_t)batches * m * n;
   for (size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
@@ -2266,7 +2253,7 @@ __global__ void __launch_bounds__(256) simt_matmul_kernel(const T* __restrict__ 
       acc = fmaf(av, bv, acc);
     }
     if (beta != 0.f) acc += beta * to_f32(out[idx]);
-    out[idx] = from_f32<T>(acc);
+    out[idx] = from_f32<OutT>(acc);
   }
 }
 
@@ -2311,21 +2298,23 @@ size_t tc_conv_workspace_elems(int pass, int dtype, const PdnnConv2DParams& p) {
 }
 
 int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
-              const PdnnConvEpilogue* epi, void* ws, size_t ws_elems, cudaStream_t s) {
+              const PdnnConvEpilogue* epi, const PdnnBackpropFusion* fusion, void* ws, size_t ws_elems, cudaStream_t s) {
+  const void* relu_mask = fusion != nullptr ? fusion->relu_forward_output : nullptr;
+  const bool out_f32 = fusion != nullptr && fusion->output_f32 != 0 && dtype != PDNN_F32;
   switch (pass) {
     case PDNN_FORWARD:
       if (small_c_applicable(dtype, p)) {
         const int st = conv_forward_small_c(dtype, in, fil, out, p, epi, ws, ws_elems, s);
-        return st == -1 ? launch_direct_conv(pass, dtype, in, fil, out, p, epi, s) : st;
+        return st == -1 ? kNeedsDirect : st;
       }
       return conv_forward(dtype, in, fil, out, p, epi, s);
-    case PDNN_INPUT_BACKPROP: return conv_input_backprop(dtype, in, fil, out, p, s);
+    case PDNN_INPUT_BACKPROP: return conv_input_backprop(dtype, in, fil, out, p, relu_mask, s);
     case PDNN_FILTER_BACKPROP:
       if (small_c_applicable(dtype, p)) {
-        const int st = conv_filter_backprop_small_c(dtype, in, fil, out, p, ws, ws_elems, s);
-        return st == -1 ? launch_direct_conv(pass, dtype, in, fil, out, p, nullptr, s) : st;
+        const int st = conv_filter_backprop_small_c(dtype, in, fil, out, p, out_f32, ws, ws_elems, s);
+        return st == -1 ? kNeedsDirect : st;
       }
-      return conv_filter_backprop(dtype, in, fil, out, p, ws, ws_elems, s);
+      return conv_filter_backprop(dtype, in, fil, out, p, out_f32, ws, ws_elems, s);
   }
   return fail(PDNN_INVALID_PARAMETER, "bad pass %d", pass);
 }
@@ -2344,7 +2333,7 @@ bool tc_matmul_supported(int dtype, int tl, int tr, const void* lhs, const void*
 }
 
 int tc_matmul(int dtype, int tl, int tr, const void* lhs, const void* rhs, void* out, int batches, int m, int k, int n,
-              float beta, cudaStream_t s) {
+              float beta, cudaStream_t s, bool out_f32) {
   const size_t es = dtype_size(dtype);
   const int sms = device_sm_count();
   const int epr = dtype == PDNN_F32 ? 32 : 64;
@@ -2428,19 +2417,20 @@ int tc_matmul(int dtype, int tl, int tr, const void* lhs, const void* rhs, void*
   set_epilogue(g, nullptr);
   g.beta = beta;
   g.out = out;
-  g.out_dtype = dtype;
+  g.out_dtype = out_f32 ? PDNN_F32 : dtype;
   g.ext_cols = n;
   g.vec_ok = 1;
   {
+    const uint64_t eo = dtype_size(g.out_dtype);
     const uint64_t od[4] = {(uint64_t)n, (uint64_t)m, 1, (uint64_t)batches};
-    const uint64_t os[3] = {(uint64_t)n * es, (uint64_t)m * n * es, (uint64_t)m * n * es};
+    const uint64_t os[3] = {(uint64_t)n * eo, (uint64_t)m * n * eo, (uint64_t)m * n * eo};
     if (!setup_store(g, dtype, od, os)) return PDNN_INVALID_PARAMETER;
   }
   return launch_gemm(g, dtype, s);
 }
 
 int simt_matmul(int dtype, int tl, int tr, const void* lhs, const void* rhs, void* out, int batches, int m, int k, int n,
-                float beta, cudaStream_t s) {
+                float beta, cudaStream_t s, bool out_f32) {
   const int sms = device_sm_count();
   if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
   const size_t total = (size_t)batches * m * n;
@@ -2448,6 +2438,13 @@ int simt_matmul(int dtype, int tl, int tr, const void* lhs, const void* rhs, voi
   if (dtype == PDNN_F32)
     simt_matmul_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(lhs), static_cast<const float*>(rhs),
                                                     static_cast<float*>(out), tl, tr, batches, m, k, n, beta);
+  else if (out_f32 && dtype == PDNN_F16)
+    simt_matmul_kernel<__half, float><<<grid, 256, 0, s>>>(static_cast<const __half*>(lhs), static_cast<const __half*>(rhs),
+                                                            static_cast<float*>(out), tl, tr, batches, m, k, n, beta);
+  else if (out_f32 && dtype == PDNN_BF16)
+    simt_matmul_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(lhs),
+                                                                   static_cast<const __nv_bfloat16*>(rhs),
+                                                                   static_cast<float*>(out), tl, tr, batches, m, k, n, beta);
   else if (dtype == PDNN_F16)
     simt_matmul_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(lhs), static_cast<const __half*>(rhs),
                                                      static_cast<__half*>(out), tl, tr, batches, m, k, n, beta);
@@ -2472,12 +2469,5 @@ int tc_read_error_record(unsigned out[4], int clear) {
   return PDNN_OK;
 }
 
-#ifdef PDNN_TC_TRACE
-extern "C" int pdnn_debug_trace(long long* out, int words) {
-  cudaDeviceSynchronize();
-  const size_t n = std::min<size_t>((size_t)words, (size_t)kTraceKinds * kTraceTiles) * sizeof(long long);
-  return cudaMemcpyFromSymbol(out, g_trace, n) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 }  // namespace pdnn

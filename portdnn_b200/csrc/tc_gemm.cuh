@@ -13,17 +13,22 @@ bool tc_conv_supported(int pass, int dtype, const void* in, const void* fil, con
 // Scratch elements (of dtype) the pass needs: only the filter backprop's split reduction uses any.
 size_t tc_conv_workspace_elems(int pass, int dtype, const PdnnConv2DParams& p);
 
+// Returned by tc_conv2d when the tensor maps of a few-channel layer could not be encoded: the caller
+// runs the layer on the direct kernel instead.
+constexpr int kNeedsDirect = -1;
+
 int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
-              const PdnnConvEpilogue* epi, void* ws, size_t ws_elems, cudaStream_t s);
+              const PdnnConvEpilogue* epi, const PdnnBackpropFusion* fusion, void* ws, size_t ws_elems, cudaStream_t s);
 
 bool tc_matmul_supported(int dtype, int tl, int tr, const void* lhs, const void* rhs, const void* out, int batches,
                          int m, int k, int n);
+// out_f32: the product is written as fp32 whatever dtype is (beta then scales fp32 values).
 int tc_matmul(int dtype, int tl, int tr, const void* lhs, const void* rhs, void* out, int batches, int m, int k, int n,
-              float beta, cudaStream_t s);
+              float beta, cudaStream_t s, bool out_f32 = false);
 
 // General CUDA-core matmul for shapes the tensor-core engine cannot take.
 int simt_matmul(int dtype, int tl, int tr, const void* lhs, const void* rhs, void* out, int batches, int m, int k, int n,
-                float beta, cudaStream_t s);
+                float beta, cudaStream_t s, bool out_f32 = false);
 
 // Copies the device-side error record (4 words; word 0 == 0 means no error) to the host.
 // Synchronises the device.

@@ -50,14 +50,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Time limit of a single wait.  A stage of this pipeline completes in microseconds; a wait
-// that lasts a second means a lost arrival.
+// Default time limit of a single wait.  A stage of this pipeline completes in microseconds; a
+// wait that lasts a second means a lost arrival.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 
-// Waits for the phase with the given parity.  Returns false if the CTA is aborting or the
-// limit ran out (in which case it raises the abort flag and fills the error record).
+// Waits for the phase with the given parity, for at most limit_ns.  Returns false if the CTA is
+// aborting or the limit ran out (in which case it raises the abort flag and fills the error
+// record).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned* error_record, unsigned where) {
+                                          unsigned* error_record, uint64_t limit_ns, unsigned where) {
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -66,7 +67,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       const uint64_t now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         if (atomicCAS(error_record, 0u, (unsigned)kErrWaitTimeout) == 0u) {
           error_record[1] = blockIdx.x;

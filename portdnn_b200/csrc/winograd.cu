@@ -113,9 +113,11 @@ __global__ void __launch_bounds__(kBlock)
 }
 
 // One thread: one tile, one output column (feature, or channel for the backprop).
+// M is fp32 whatever T is: rounding the sixteen products to 16 bits before they are combined (with
+// cancellation) would cost the 16-bit types about a factor of two in accuracy.
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
-    wino_output_transform_kernel(const T* __restrict__ m, T* __restrict__ y, const T* __restrict__ bias, int act,
+    wino_output_transform_kernel(const float* __restrict__ m, T* __restrict__ y, const T* __restrict__ bias, int act,
                                  float alpha, float beta, WinoGeometry g, int cols, size_t n_items) {
   for (size_t idx = (size_t)blockIdx.x * kBlock + threadIdx.x; idx < n_items; idx += (size_t)gridDim.x * kBlock) {
     const int k = (int)(idx % cols);
@@ -128,7 +130,7 @@ __global__ void __launch_bounds__(kBlock)
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) mm[i][j] = to_f32(__ldg(m + (size_t)(i * 4 + j) * step + (size_t)tile * cols + k));
+      for (int j = 0; j < 4; ++j) mm[i][j] = __ldg(m + (size_t)(i * 4 + j) * step + (size_t)tile * cols + k);
     // t = A^T m (2x4), A^T = [[1,1,1,0],[0,1,-1,-1]]
     float t[2][4];
 #pragma unroll
@@ -182,23 +184,24 @@ bool winograd_applicable(int pass, int dtype, const PdnnConv2DParams& p) {
          p.channels % align == 0 && p.features % align == 0 && p.pad_rows <= 2 && p.pad_cols <= 2;
 }
 
-// Elements of scratch: 16 * (C*K + tiles*C + tiles*K), the reference's formula for
-// A = B = 4 (include/portdnn/conv2d/workspace_size.h:53-73).
-size_t winograd_workspace_elems(int pass, const PdnnConv2DParams& p) {
+// Elements (of dtype) of scratch: 16 * (C*K + tiles*C + tiles*K), the reference's formula for
+// A = B = 4 (include/portdnn/conv2d/workspace_size.h:53-73), with the last term counted twice for
+// 16-bit types because the products M are kept in fp32.
+size_t winograd_workspace_elems(int pass, int dtype, const PdnnConv2DParams& p) {
   const WinoGeometry g = geometry(pass, p);
   const size_t align = 64;  // keep every sub-buffer 16-byte aligned
   auto up = [&](size_t n) { return (n + align - 1) / align * align; };
   return up(16 * (size_t)g.channels * g.features) + up(16 * (size_t)g.tiles * g.channels) +
-         up(16 * (size_t)g.tiles * g.features);
+         up(16 * (size_t)g.tiles * g.features) * (sizeof(float) / dtype_size(dtype));
 }
 
 int launch_winograd(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
                     const PdnnConvEpilogue* epi, void* ws, size_t ws_elems, cudaStream_t s) {
   if (ws == nullptr || ws_elems == 0)
     return fail(PDNN_INSUFFICIENT_WORKSPACE, "winograd: a workspace is required (query pdnn_conv2d_workspace_size)");
-  if (ws_elems < winograd_workspace_elems(pass, p) || !aligned16(ws))
+  if (ws_elems < winograd_workspace_elems(pass, dtype, p) || !aligned16(ws))
     return fail(PDNN_INSUFFICIENT_WORKSPACE, "winograd: workspace of %zu elements, %zu needed", ws_elems,
-                winograd_workspace_elems(pass, p));
+                winograd_workspace_elems(pass, dtype, p));
   const int sms = device_sm_count();
   if (sms <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "no CUDA device");
   const WinoGeometry g = geometry(pass, p);
@@ -225,12 +228,12 @@ int launch_winograd(int pass, int dtype, const void* in, const void* fil, void* 
     if (st != PDNN_OK) return st;
     // 16 products [tiles x C] x [C x K]
     if (tc_matmul_supported(dtype, 0, 0, v, u, m, 16, (int)g.tiles, g.channels, g.features))
-      st = tc_matmul(dtype, 0, 0, v, u, m, 16, (int)g.tiles, g.channels, g.features, 0.f, s);
+      st = tc_matmul(dtype, 0, 0, v, u, m, 16, (int)g.tiles, g.channels, g.features, 0.f, s, /*out_f32=*/true);
     else
-      st = simt_matmul(dtype, 0, 0, v, u, m, 16, (int)g.tiles, g.channels, g.features, 0.f, s);
+      st = simt_matmul(dtype, 0, 0, v, u, m, 16, (int)g.tiles, g.channels, g.features, 0.f, s, /*out_f32=*/true);
     if (st != PDNN_OK) return st;
     wino_output_transform_kernel<T><<<grid_for(n_out, kBlock, sms), kBlock, 0, s>>>(
-        reinterpret_cast<const T*>(m), static_cast<T*>(out), static_cast<const T*>(bias), act, alpha, beta, g,
+        reinterpret_cast<const float*>(m), static_cast<T*>(out), static_cast<const T*>(bias), act, alpha, beta, g,
         g.features, n_out);
     return check_launch("winograd output transform");
   };

@@ -45,12 +45,18 @@ class FilterGradientBucket:
     def view(self, i):
         return self.buffer[self.offsets[i]:self.offsets[i] + self.sizes[i]]
 
-    def all_reduce(self, group=None, async_op=False):
-        """Sum over ranks (no-op without an initialised process group or with one rank)."""
+    def span(self, first, last):
+        """(start, stop) of the contiguous slice that holds the gradients of layers first..last."""
+        return self.offsets[first], self.offsets[last] + (self.sizes[last] + 63) // 64 * 64
+
+    def all_reduce(self, group=None, async_op=False, span=None):
+        """Sum over ranks of the whole buffer, or of one span of it (no-op without an initialised process
+        group or with one rank)."""
         import torch.distributed as dist
         if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
             return None
-        return dist.all_reduce(self.buffer, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+        t = self.buffer if span is None else self.buffer[span[0]:span[1]]
+        return dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
 
 
 def max_over_ranks(value, device=None, group=None):

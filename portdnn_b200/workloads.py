@@ -99,11 +99,16 @@ class ConvStackRunner:
     """Runs a layer table on one GPU through the C ABI: forward only (activations ping-pong
     between a few named buffers) or a training step (every activation kept; then, last layer
     first, ReLU gradient -> filter backprop -> input backprop per convolution, max-pool gradient
-    for pooling layers, filter gradients written into one contiguous fp32 bucket and summed over
-    ranks with a single all-reduce).  The reference has no trainer; its samples chain layers the
+    for pooling layers, filter gradients written as fp32 into one contiguous bucket and summed
+    over ranks, stage by stage or with a single all-reduce).  The reference has no trainer; its samples chain layers the
     same way on the host (tools/network.h)."""
 
-    def __init__(self, layers, device, seed, training=False, dtype=None):
+    def __init__(self, layers, device, seed, training=False, dtype=None, chunk=None, chunk_layers=0):
+        """chunk / chunk_layers (forward only): the first ``chunk_layers`` layers run depth-first over
+        slices of ``chunk`` images - all those layers on images 0..chunk-1, then on the next slice, and so
+        on - with their intermediate activations in slice-sized buffers that every slice reuses, so that a
+        layer's output is still in the L2 cache when the next layer reads it.  Results are identical to
+        the layer-by-layer order: every operator of the path is independent per image."""
         import torch
         from . import dist as pdist
         self.torch, self.layers, self.training, self.device = torch, layers, training, device
@@ -141,7 +146,6 @@ class ConvStackRunner:
             self.bucket = pdist.FilterGradientBucket([self.weights[i].numel() for i in conv_ids], device,
                                                      pad_to=25_500_000)
             self.scratch = torch.empty(max(sizes), dtype=self.dtype, device=device)
-            self.dw_tmp = torch.empty(max(self.weights[i].numel() for i in conv_ids), dtype=self.dtype, device=device)
             last = conv_ids[-1]
             self.dy_last = torch.randn(sizes[last], device=device, generator=g).to(self.dtype)
             self.fbp_ws = {}
@@ -158,6 +162,18 @@ class ConvStackRunner:
             for l, n in zip(layers, sizes):
                 names[l.dst] = max(names.get(l.dst, 0), n)
             self.buffers = {k: torch.empty(v, dtype=self.dtype, device=device) for k, v in names.items()}
+        self.chunk, self.chunk_layers = None, 0
+        if chunk and chunk_layers and not training and first.batch % chunk == 0 and chunk < first.batch:
+            self.chunk, self.chunk_layers, batch = chunk, chunk_layers, first.batch
+            # only the last layer of the depth-first part may be read by a later layer
+            assert all(j == chunk_layers - 1 or j >= chunk_layers for j in self.src_idx[chunk_layers:])
+            self.chunk_params, names = [], {}
+            for i in range(chunk_layers):
+                q = type(layers[i].params).from_buffer_copy(layers[i].params)
+                q.batch = chunk
+                self.chunk_params.append(q)
+                names[layers[i].dst] = max(names.get(layers[i].dst, 0), sizes[i] // batch * chunk)
+            self.chunk_buffers = {k: torch.empty(v, dtype=self.dtype, device=device) for k, v in names.items()}
 
     # ---- forward -------------------------------------------------------------------------------
     def _out(self, i):
@@ -175,20 +191,69 @@ class ConvStackRunner:
         else:
             api.pooling(l.op, 0, self._in(i), p, out=self._out(i))
 
+    def run_layer_slice(self, i, c):
+        """Layer i (one of the depth-first layers) on images [c * chunk, (c + 1) * chunk)."""
+        l, p, j = self.layers[i], self.chunk_params[i], self.src_idx[i]
+        batch = self.layers[0].params.batch
+        n_out = self.sizes[i] // batch * self.chunk
+        if j < 0:
+            n_in = self.input.numel() // batch * self.chunk
+            src = self.input[c * n_in:(c + 1) * n_in]
+        else:
+            src = self.chunk_buffers[self.layers[j].dst][:self.sizes[j] // batch * self.chunk]
+        if i == self.chunk_layers - 1:  # the part's result goes to its place in the full-batch tensor
+            dst = self._out(i)[c * n_out:(c + 1) * n_out]
+        else:
+            dst = self.chunk_buffers[l.dst][:n_out]
+        if isinstance(l, ConvLayer):
+            api.conv2d(api.FORWARD, src, self.weights[i], p, algorithm=api.ALGO_TILED, out=dst, bias=self.biases[i],
+                       activation=l.activation, workspace=self.workspaces.get(i))
+        else:
+            api.pooling(l.op, 0, src, p, out=dst)
+
     def forward(self):
-        for i in range(len(self.layers)):
+        first = 0
+        if self.chunk:
+            first = self.chunk_layers
+            for c in range(self.layers[0].params.batch // self.chunk):
+                for i in range(first):
+                    self.run_layer_slice(i, c)
+        for i in range(first, len(self.layers)):
             self.run_layer(i)
         return self._out(len(self.layers) - 1)
 
     # ---- backward ------------------------------------------------------------------------------
+    def _plan_backward(self):
+        """Which tensors get their ReLU-gradient mask applied inside the input backprop that produces
+        their gradient (one reader, a convolution's output, and nobody else needs the unmasked
+        gradient), and the segments of the backward pass: the layers of one stage, last stage first, each
+        with the slice of the gradient bucket it fills."""
+        layers = self.layers
+        readers = [0] * len(layers)
+        for j in self.src_idx:
+            if j >= 0:
+                readers[j] += 1
+        blocks_with_shortcut = {l.name[:-5] for l in layers if l.name.endswith("_proj")}
+        self.fuse_mask = [isinstance(l, ConvLayer) and readers[i] == 1 and
+                          not (l.name.endswith("_1x1b") and l.name[:-5] in blocks_with_shortcut)
+                          for i, l in enumerate(layers)]
+        stage_of = lambda l: l.name[:2] if l.name[0] == "s" and l.name[1].isdigit() else "stem"
+        self.segments = []
+        for i in reversed(range(len(layers))):
+            tag = stage_of(layers[i])
+            if not self.segments or self.segments[-1]["tag"] != tag:
+                self.segments.append({"tag": tag, "layers": []})
+            self.segments[-1]["layers"].append(i)
+        for seg in self.segments:
+            ks = [self.conv_ids.index(i) for i in seg["layers"] if i in self.weights]
+            seg["bucket"] = self.bucket.span(min(ks), max(ks)) if ks else None
+
     def _add_grad(self, j, producer):
         """Routes a gradient into tensor j: the first contribution is written in place, later ones
         are accumulated."""
         if self.grads[j] is None:
             self.grads[j] = self.torch.empty(self.sizes[j], dtype=self.dtype, device=self.device)
-            producer(self.grads[j])
-            self._fresh.add(j)
-        elif j not in self._fresh:
+        if j not in self._fresh:
             producer(self.grads[j])
             self._fresh.add(j)
         else:
@@ -196,41 +261,55 @@ class ConvStackRunner:
             producer(tmp)
             api.scale_blend(tmp, 1.0, self.grads[j], 1.0, out=self.grads[j])
 
-    def backward(self):
-        torch = self.torch
-        if not hasattr(self, "scratch2"):
-            self.scratch2 = torch.empty_like(self.scratch)
-        self._fresh = set()
+    def backward_begin(self):
+        if not hasattr(self, "segments"):
+            self._plan_backward()
+            self.scratch2 = self.torch.empty_like(self.scratch)
+        self._fresh, self._masked, self._block_grad = set(), set(), {}
+
+    def backward_segment(self, seg):
+        """The backward pass of one segment: per convolution (last first) the ReLU gradient - unless the
+        input backprop that produced the incoming gradient already applied it - then the filter backprop,
+        written as fp32 straight into the layer's slice of the gradient bucket, then the input backprop."""
         last = self.conv_ids[-1]
-        block_grad = {}
-        for i in reversed(range(len(self.layers))):
+        for i in seg["layers"]:
             l, p, j = self.layers[i], self.layers[i].params, self.src_idx[i]
             if i == last:
                 dy = self.dy_last
             elif i in self._fresh:
                 dy = self.grads[i]
             elif isinstance(l, ConvLayer) and l.name.endswith("_proj"):
-                dy = block_grad[l.name[:-5]]  # the shortcut receives its block's output gradient
+                dy = self._block_grad[l.name[:-5]]  # the shortcut receives its block's output gradient
             else:
                 continue  # nothing downstream of this layer takes part in the step (the final pool)
             if isinstance(l, ConvLayer):
                 if l.name.endswith("_1x1b"):
-                    block_grad[l.name[:-5]] = dy
-                g = self.scratch[:self.sizes[i]]
-                api.pointwise_grad(api.ACT_RELU, self.acts[i], dy, out=g)
+                    self._block_grad[l.name[:-5]] = dy
+                if i in self._masked:
+                    g = dy
+                else:
+                    g = self.scratch[:self.sizes[i]]
+                    api.pointwise_grad(api.ACT_RELU, self.acts[i], dy, out=g)
                 k = self.conv_ids.index(i)
-                dw = self.dw_tmp[:self.weights[i].numel()]
-                api.conv2d(api.FILTER_BACKPROP, self._in(i), g, p, algorithm=api.ALGO_TILED, out=dw,
+                api.conv2d(api.FILTER_BACKPROP, self._in(i), g, p, algorithm=api.ALGO_TILED, out=self.bucket.view(k),
+                           output_f32=self.dtype != self.torch.float32,
                            workspace=self.fbp_workspace if i in self.fbp_ws else None)
-                self.bucket.view(k).copy_(dw)
                 if j >= 0:
+                    mask = self.acts[j] if self.fuse_mask[j] else None
                     self._add_grad(j, lambda dst: api.conv2d(api.INPUT_BACKPROP, g, self.weights[i], p,
-                                                             algorithm=api.ALGO_TILED, out=dst))
+                                                             algorithm=api.ALGO_TILED, out=dst, relu_forward_output=mask))
+                    if mask is not None:
+                        self._masked.add(j)
             elif l.op == api.POOL_AVERAGE:
                 if j >= 0:
                     self._add_grad(j, lambda dst: api.pooling(l.op, 1, dy, p, out=dst))
             elif j >= 0:
                 self._add_grad(j, lambda dst: api.pooling_max_grad(l.op, self._in(i), self.acts[i], dy, p, out=dst))
+
+    def backward(self):
+        self.backward_begin()
+        for seg in self.segments:
+            self.backward_segment(seg)
 
     def train_step(self):
         self.forward()

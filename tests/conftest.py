@@ -43,8 +43,13 @@ def ulp_diff(a, b):
 
 
 def rel_err(got, ref):
-    """max |got - ref| / max |ref|: the relative error the parity tolerances are stated in."""
-    got = np.asarray(got, dtype=np.float64)
-    ref = np.asarray(ref, dtype=np.float64)
+    """The relative error the parity tolerances are stated in, taken two ways and the larger returned:
+    the max-norm  max |got - ref| / max |ref|,  and the element-wise  max_i |got_i - ref_i| /
+    (|ref_i| + rms(ref)).  The second keeps one large output from hiding errors on the small ones:
+    rel_err <= tol means |got_i - ref_i| <= tol * |ref_i| + tol * rms(ref) for every element."""
+    got = np.asarray(got, dtype=np.float64).ravel()
+    ref = np.asarray(ref, dtype=np.float64).ravel()
+    diff = np.abs(got - ref)
     scale = max(float(np.max(np.abs(ref))), 1e-30)
-    return float(np.max(np.abs(got - ref))) / scale
+    rms = max(float(np.sqrt(np.mean(ref * ref))), 1e-30)
+    return max(float(np.max(diff)) / scale, float(np.max(diff / (np.abs(ref) + rms))))

@@ -199,3 +199,36 @@ def test_full_size_layers_tensor_core_vs_direct_kernel(shape):
     y1 = pd.conv2d(pd.FORWARD, x, wt, p).float()
     y2 = pd.conv2d(pd.FORWARD, (x.float() * 0.5).half(), wt, p).float()
     assert ((y1 * 0.5 - y2).abs().max() / y1.abs().max()).item() <= 2e-3
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("shape", BWD_SHAPES + [(2, 20, 20, 24, 40, 3, 2, True, None), (3, 9, 9, 5, 7, 3, 1, True, None)])
+def test_fused_backprop_forms_against_oracle(orc, dtype, shape):
+    """PdnnBackpropFusion: the input backprop with the ReLU-gradient mask of the preceding layer
+    applied on the way out, and the filter backprop written as fp32, against the oracle chain
+    input backprop -> pointwise Relu Gradient (src/pointwise/kernels.h:205-233) and its fp32
+    filter gradient.  The last shape takes the direct kernel (channels not a multiple of 8)."""
+    n, h, w, c, k, win, st, same, pad = shape
+    p, po, x, wt, dy = _conv_case(orc, dtype, n, h, w, c, k, win, st, bool(same), pad)
+    rng = np.random.default_rng(31)
+    # forward output of the preceding layer: about half of it zero, as a ReLU leaves it
+    y_prev = rounded(np.maximum(rng.standard_normal(n * h * w * c), 0).astype(np.float32), dtype)
+    dx = to_host(pd.conv2d(pd.INPUT_BACKPROP, to_dev(dy, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_TILED,
+                           relu_forward_output=to_dev(y_prev, dtype)))
+    assert_no_device_error()
+    ref = orc.pointwise_grad(0, y_prev, orc.conv2d(orc.INPUT_BACKPROP, dy, wt, po))
+    assert rel_err(dx, ref) <= TOL[dtype]
+    assert not np.any(dx[y_prev <= 0] != 0)
+    dw = pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, dtype), to_dev(dy, dtype), p, algorithm=pd.ALGO_TILED,
+                   output_f32=dtype != "f32")
+    assert dw.dtype == torch.float32
+    assert_no_device_error()
+    assert rel_err(to_host(dw), orc.conv2d(orc.FILTER_BACKPROP, x, dy, po)) <= TOL[dtype]
+
+
+def test_fused_backprop_stem_filter_gradient_fp32(orc):
+    n, h, w, c, k, win, st = 2, 32, 32, 3, 64, 7, 2
+    p, po, x, _, dy = _conv_case(orc, "f16", n, h, w, c, k, win, st, None, 3)
+    dw = pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, "f16"), to_dev(dy, "f16"), p, algorithm=pd.ALGO_TILED, output_f32=True)
+    assert dw.dtype == torch.float32
+    assert rel_err(to_host(dw), orc.conv2d(orc.FILTER_BACKPROP, x, dy, po)) <= TOL["f16"]
