@@ -22,6 +22,9 @@
 #include "umma.cuh"
 
 #include <algorithm>
+#ifdef PDNN_TUNE
+#include <cstdlib>
+#endif
 #include <cstring>
 #include <mutex>
 
@@ -40,6 +43,28 @@ constexpr int kBarsPerGroup = 3 * kMaxStages + 4;  // full, empty, ready per sta
 constexpr int kBarBlockBytes = 512;                // barriers of two groups, the resident-B barrier, TMEM slot, abort flag
 
 __device__ unsigned g_error_record[4];
+
+// Plan overrides for kernel development: compiled in only with -DPDNN_TUNE (the library is never
+// built that way), in which case the named environment variable, when set, replaces the heuristic.
+#ifdef PDNN_TUNE
+int tune_knob(const char* name, int dflt) {
+  const char* e = getenv(name);
+  return e != nullptr && *e != 0 ? atoi(e) : dflt;
+}
+#define PDNN_KNOB(name, dflt) tune_knob(name, dflt)
+// Timeline of CTA 0: SM clock at a few points of each tile's life.
+constexpr int kTraceTiles = 512, kTraceKinds = 12;
+__device__ long long g_trace[kTraceKinds * kTraceTiles];
+#define PDNN_TRACE(kind, idx)                                                                                \
+  do {                                                                                                       \
+    if (blockIdx.x == 0 && (idx) < (unsigned)kTraceTiles) g_trace[(kind) * kTraceTiles + (idx)] = clock64(); \
+  } while (0)
+#else
+#define PDNN_KNOB(name, dflt) (dflt)
+#define PDNN_TRACE(kind, idx) \
+  do {                        \
+  } while (0)
+#endif
 
 // One reduction step of a forward-style GEMM: which input map, at which pixel offset, against which
 // filter tap.  In halo mode an entry stands for `cnt` taps that differ only by one input row each
@@ -368,38 +393,38 @@ __device__ __forceinline__ P2 bits_pair(uint32_t v) {
   return *reinterpret_cast<P2*>(&v);
 }
 
-// Converts 32 accumulator columns of one row (four 16-byte chunks, numbered from chunk_base) and
-// writes them into the row's 128 bytes of the staging slice.
+// Shared-memory load of 16 bytes.  Volatile so that it is issued where it is written: the bias
+// loads of a column block are batched ahead of the wait for the accumulators, and their latencies
+// overlap instead of each load sitting directly in front of its first use (a lone warp stalls on
+// every one of them: eight round trips cost more than the arithmetic of the block).
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   uint4 v;
-  // not volatile: the bias copy never changes after the start of the kernel, so the loads may be
-  // hoisted and batched freely
-  asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
 
-// `bias_s` is the shared-space address of the CTA's copy of the bias vector (0: no bias); the copy
-// is padded with zeros up to a multiple of 64 columns.
-// `keep` (MASK only) holds one byte per 16-byte chunk of the row: bit e set = element e is kept.
+// Converts 32 accumulator columns of one row (four 16-byte chunks, numbered from chunk_base) and
+// writes them into the row's 128 bytes of the staging slice.  `bv` holds the bias of those 32
+// columns (zeros without a bias).  `keep` (MASK only) holds one byte per 16-byte chunk of the
+// row: bit e set = element e is kept.
 template <typename OutT, bool MASK>
-__device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bool zero, uint32_t bias_s, int col0,
+__device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bool zero, bool has_bias, const uint4* bv,
                                                    int act, uint8_t* row_ptr, int row, int chunk_base, uint2 keep) {
   using P2 = typename Pair<OutT>::type;
   const P2 zero2 = Pair<OutT>::splat(0.f), six2 = Pair<OutT>::splat(6.f);
-  const bool has_bias = bias_s != 0u;
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
-    uint4 bv = make_uint4(0u, 0u, 0u, 0u);
-    if (has_bias) bv = ld_shared_v4(bias_s + (uint32_t)(col0 + g * 8) * 2u);
-    const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+    const uint32_t bw[4] = {bv[g].x, bv[g].y, bv[g].z, bv[g].w};
     uint32_t o[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       P2 v = zero ? zero2
                   : Pair<OutT>::pack(__uint_as_float(acc[g * 8 + 2 * i]), __uint_as_float(acc[g * 8 + 2 * i + 1]));
-      if (has_bias) v = __hadd2(v, bits_pair<P2>(bw[i]));
-      if (act != PDNN_ACT_NONE) v = __hmax2(v, zero2);
-      if (act == PDNN_ACT_RELU6) v = __hmin2(v, six2);
+      if (!MASK) {  // the gradient form has neither bias nor activation
+        if (has_bias) v = __hadd2(v, bits_pair<P2>(bw[i]));
+        if (act != PDNN_ACT_NONE) v = __hmax2(v, zero2);
+        if (act == PDNN_ACT_RELU6) v = __hmin2(v, six2);
+      }
       o[i] = pair_bits(v);
     }
     if (MASK) {
@@ -413,11 +438,6 @@ __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bo
   }
 }
 
-// The common case of the staged epilogue, kept short because a lone warp per scheduler is
-// latency-bound: 16-bit output, alpha == 1, optional bias, activation none / ReLU / ReLU6.  The
-// accumulators are rounded to the output type first and bias and activation are applied to
-// packed pairs in that type - the arithmetic of separate convolution, bias-add and activation
-// passes.
 // Sign bits of a 32-row x 64-column block of the ReLU mask tensor (16-bit elements), gathered with
 // coalesced loads: lane l reads 16-byte chunk l % 8 of rows l / 8, l / 8 + 4, ..., turns every chunk
 // into one byte (bit e = element e is positive) and leaves it in the warp's 256-byte table at
@@ -471,18 +491,29 @@ __device__ __forceinline__ void epilogue_tile_tma_fast(const GemmArgs& a, const 
   for (int c0 = 0; c0 < a.bn; c0 += 64, ++store_count) {
     const uint32_t slot = store_count & (uint32_t)(ws.nsw - 1);
     uint32_t acc0[32], acc1[32];
+    if (threadIdx.x == 64) PDNN_TRACE(7, store_count);
     if (!zero) {  // issued before waiting for the staging slice
       tmem_ld_32x32(tmem_acc + (uint32_t)c0, acc0);
       tmem_ld_32x32(tmem_acc + (uint32_t)(c0 + 32), acc1);
     }
+    // the block's bias, all eight loads in flight at once (and before the waits below)
+    uint4 bv[8];
+    const bool has_bias = !MASK && bias_s != 0u;
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+      bv[g] = has_bias ? ld_shared_v4(bias_s + (uint32_t)(t.nf0 + c0 + g * 8) * 2u) : make_uint4(0u, 0u, 0u, 0u);
     uint2 keep = make_uint2(0u, 0u);
     if (MASK) keep = load_relu_keep_bits(a, t, q32, t.nf0 + c0, lane, mask_table);
     wait_slice_free(ws, lane);
+    if (threadIdx.x == 64) PDNN_TRACE(8, store_count);
     if (!zero) tmem_wait_ld();
+    if (threadIdx.x == 64) PDNN_TRACE(9, store_count);
     uint8_t* row_ptr = ws.buf + slot * 4096u + (size_t)lane * 128;
-    fast_convert_store<OutT, MASK>(acc0, zero, bias_s, t.nf0 + c0, act, row_ptr, lane, 0, keep);
-    fast_convert_store<OutT, MASK>(acc1, zero, bias_s, t.nf0 + c0 + 32, act, row_ptr, lane, 4, keep);
+    fast_convert_store<OutT, MASK>(acc0, zero, has_bias, bv, act, row_ptr, lane, 0, keep);
+    fast_convert_store<OutT, MASK>(acc1, zero, has_bias, bv + 4, act, row_ptr, lane, 4, keep);
+    if (threadIdx.x == 64) PDNN_TRACE(10, store_count);
     issue_slice_store(a, t, ws, slot, t.nf0 + c0, lane);
+    if (threadIdx.x == 64) PDNN_TRACE(11, store_count);
   }
 }
 
@@ -519,7 +550,12 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
 
   constexpr int kMaxGroups = SPLIT ? 1 : 2;
   const int groups = SPLIT ? 1 : a.groups;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The warp index is broadcast from lane 0 so that the compiler can prove it, and everything derived
+  // from it (group, role, ring addresses, descriptor words), uniform across the warp: tcgen05.mma and
+  // the TMA copies take their operands from uniform registers, and values it cannot prove uniform
+  // cost a register-file round trip per operand per instruction on the one thread everything waits
+  // for.
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int grp = SPLIT ? 0 : warp / 6;
   const int role = SPLIT ? warp : warp - grp * 6;  // 0 producer, 1 issuer, 2..5 epilogue, 6..9 split (SPLIT)
 
@@ -623,9 +659,13 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     // One thread; the loop body is kept to a wait, an expect_tx and the copies, with all
     // coordinates advanced incrementally: a lone thread issues an instruction every few cycles
     // at best, so every division or table lookup per step would show up as pipeline bubbles.
-    if (lane == 0 && !(pair && grp != 0)) {  // pair mode: group 0's producer fills the shared ring
-      for (int i = 0; i < 4; ++i) prefetch_tensormap(&a.a_map[i]);
-      prefetch_tensormap(&a.b_map);
+    // The whole warp walks the tiles and waits on the barriers (every value stays warp-uniform); the
+    // warp_* wrappers elect the one lane that issues each copy.
+    if (!(pair && grp != 0)) {  // pair mode: group 0's producer fills the shared ring
+      if (lane == 0) {
+        for (int i = 0; i < 4; ++i) prefetch_tensormap(&a.a_map[i]);
+        prefetch_tensormap(&a.b_map);
+      }
       const int epr = a.epr, b_mode = a.b_mode, b_boxes = a.b_boxes, a_boxes = a.a_boxes, cblocks = a.cblocks;
       const uint32_t a_box_bytes = a.a_box_bytes, b_box_bytes = a.b_box_bytes,
                      tx_bytes = pair ? 2u * kABytes + b_bytes : (b_res ? (uint32_t)kABytes : kABytes + b_bytes);
@@ -636,23 +676,23 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       // one B tile of a forward-style GEMM (a_mn == 0): reduction block kc of tap btap, columns from nf0
       auto load_b = [&](uint32_t sb, uint32_t fb, int kc, int nf0, int btap) {
         switch (b_mode) {
-          case B_MN_3X: tma_load_4d(sb, bmap, fb, 0, kc, nf0 / epr, btap); break;
+          case B_MN_3X: warp_tma_load_4d(sb, bmap, fb, 0, kc, nf0 / epr, btap); break;
           case B_MN_3:
 #pragma unroll 1
             for (int j = 0; j < b_boxes; ++j)
-              tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, nf0 + j * epr, kc, btap, 0);
+              warp_tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, nf0 + j * epr, kc, btap, 0);
             break;
-          case B_K_3: tma_load_4d(sb, bmap, fb, kc, nf0, btap, 0); break;
-          case B_K_FHWC: tma_load_4d(sb, bmap, fb, kc, btap, nf0, 0); break;
+          case B_K_3: warp_tma_load_4d(sb, bmap, fb, kc, nf0, btap, 0); break;
+          case B_K_FHWC: warp_tma_load_4d(sb, bmap, fb, kc, btap, nf0, 0); break;
           default:  // B_MN_FHWC
 #pragma unroll 1
             for (int j = 0; j < b_boxes; ++j)
-              tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, nf0 + j * epr, btap, kc, 0);
+              warp_tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, nf0 + j * epr, btap, kc, 0);
             break;
         }
       };
       if (b_res && grp == 0 && (int)blockIdx.x < total_tiles) {
-        mbar_arrive_expect_tx(bres_bar, res_bytes);
+        warp_arrive_expect_tx(bres_bar, res_bytes);
         uint32_t dst = base;
         const int nt_begin = a.b_res == 2 ? (int)blockIdx.x % a.n_tiles : 0;
         const int nt_end = a.b_res == 2 ? nt_begin + 1 : a.n_tiles;
@@ -697,15 +737,17 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
                 ok = false;
                 break;
               }
-              const uint32_t fb = full_bar(s);
-              mbar_arrive_expect_tx(fb, tx);
-              const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
-              tma_load_4d(sa, amap, fb, kc, aw, ah, t.n0);
-              if (pair) {
-                tma_load_4d(sa + kABytes, amap, fb, kc, aw + pair_dw, ah + pair_dh, t.n0 + pair_dn);
-                load_b(sa + 2u * kABytes, fb, kc, t.nf0, btap);
-              } else if (!b_res) {
-                load_b(sa + kABytes, fb, kc, t.nf0, btap);
+              {
+                const uint32_t fb = full_bar(s);
+                warp_arrive_expect_tx(fb, tx);
+                const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
+                warp_tma_load_4d(sa, amap, fb, kc, aw, ah, t.n0);
+                if (pair) {
+                  warp_tma_load_4d(sa + kABytes, amap, fb, kc, aw + pair_dw, ah + pair_dh, t.n0 + pair_dn);
+                  load_b(sa + 2u * kABytes, fb, kc, t.nf0, btap);
+                } else if (!b_res) {
+                  load_b(sa + kABytes, fb, kc, t.nf0, btap);
+                }
               }
               next_stage();
             }
@@ -723,20 +765,22 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
               ok = false;
               break;
             }
-            const uint32_t fb = full_bar(s);
-            mbar_arrive_expect_tx(fb, tx_bytes);
-            const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
-            const uint32_t sb = sa + kABytes;
-            const int kw = iw * a.tw, kh = ih * a.th, kn = in * a.tn + batch;
+            {
+              const uint32_t fb = full_bar(s);
+              warp_arrive_expect_tx(fb, tx_bytes);
+              const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
+              const uint32_t sb = sa + kABytes;
+              const int kw = iw * a.tw, kh = ih * a.th, kn = in * a.tn + batch;
 #pragma unroll 1
-            for (int j = 0; j < a_boxes; ++j)
-              tma_load_4d(sa + (uint32_t)j * a_box_bytes, amap, fb, t.w0 + j * epr, kw + e.dw, kh + e.dh, kn);
-            if (b_mode == B_MN_4) {
+              for (int j = 0; j < a_boxes; ++j)
+                warp_tma_load_4d(sa + (uint32_t)j * a_box_bytes, amap, fb, t.w0 + j * epr, kw + e.dw, kh + e.dh, kn);
+              if (b_mode == B_MN_4) {
 #pragma unroll 1
-              for (int j = 0; j < b_boxes; ++j)
-                tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, t.nf0 + j * epr, kw, kh, kn);
-            } else {  // B_K_4
-              tma_load_4d(sb, bmap, fb, kw, t.nf0, 0, kn);
+                for (int j = 0; j < b_boxes; ++j)
+                  warp_tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, t.nf0 + j * epr, kw, kh, kn);
+              } else {  // B_K_4
+                warp_tma_load_4d(sb, bmap, fb, kw, t.nf0, 0, kn);
+              }
             }
             if (++iw == a.slabs_w) {
               iw = 0;
@@ -752,7 +796,9 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     }
   } else if (role == 1) {
     // ------------------------------- MMA issuer ---------------------------------------------
-    if (lane == 0) {
+    {
+      // The whole warp runs the loops on warp-uniform values; warp_mma_* / warp_commit elect the one
+      // lane that issues each instruction.
       // Descriptor words that do not change: everything but the 14-bit start address.
       const uint64_t a_desc0 = make_smem_desc(0, a.a_lbo, a.a_sbo, a.a_layout);
       const uint64_t b_desc0 = make_smem_desc(0, a.b_lbo, a.b_sbo, a.b_layout);
@@ -760,6 +806,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       const uint32_t lo_off = part_bytes >> 4;
       int s = 0;
       uint32_t ph = 0;
+      [[maybe_unused]] uint32_t tcount = 0;
       uint32_t buf = 0, aph = 0;  // accumulator buffer of this tile and the parity of its barriers
       bool ok = true;
       if (b_res && first_tile < total_tiles) ok = mbar_wait(bres_bar, 0u, abort_flag, g_error_record, a.wait_limit_ns, 0x600u);
@@ -801,7 +848,9 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
 #pragma unroll 1
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, walker.advance()) {
         const TileCoord t = walker.coord(a);
+        if (grp == 0) PDNN_TRACE(0, tcount);
         if (!mbar_wait(acc_empty_bar((int)buf), aph ^ 1u, abort_flag, g_error_record, a.wait_limit_ns, 0x200u + buf)) break;
+        if (grp == 0) PDNN_TRACE(1, tcount);
         tc_fence_after_sync();
         const uint32_t d_tmem = grp_tmem + buf * acc_stride;
         uint32_t accumulate = 0u;
@@ -820,6 +869,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
                 ok = false;
                 break;
               }
+              if (grp == 0 && tap == 0 && cb == 0) PDNN_TRACE(2, tcount);
               // no tcgen05 fence here: the stage was written by TMA and is read by the MMA, both in
               // the async proxy, and the mbarrier's complete_tx orders them
               // start addresses stay below 2^18, so adding to the low descriptor word never carries
@@ -830,10 +880,10 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
 #pragma unroll 1
                 for (int g = 0; g < cnt; ++g) {
                   const uint64_t da = ((uint64_t)fw.a_hi << 32) | a_lo, db = ((uint64_t)fw.b_hi << 32) | b_lo;
-                  mma_f16(d_tmem, da, db, idesc, accumulate);
-                  mma_f16(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
-                  mma_f16(d_tmem, da + 2 * a_kadv, db + 2 * b_kadv, idesc, 1u);
-                  mma_f16(d_tmem, da + 3 * a_kadv, db + 3 * b_kadv, idesc, 1u);
+                  warp_mma_f16(d_tmem, da, db, idesc, accumulate);
+                  warp_mma_f16(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
+                  warp_mma_f16(d_tmem, da + 2 * a_kadv, db + 2 * b_kadv, idesc, 1u);
+                  warp_mma_f16(d_tmem, da + 3 * a_kadv, db + 3 * b_kadv, idesc, 1u);
                   accumulate = 1u;
                   a_lo += fw.halo_row16;
                   b_lo += fw.b_tap16;
@@ -844,22 +894,22 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
                 for (; g + 1 < cnt; g += 2) {
                   const uint64_t da = ((uint64_t)fw.a_hi << 32) | a_lo, db = ((uint64_t)fw.b_hi << 32) | b_lo;
                   const uint64_t da2 = da + fw.halo_row16, db2 = db + fw.b_tap16;
-                  mma_f16(d_tmem, da, db, idesc, accumulate);
-                  mma_f16(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
-                  mma_f16(d_tmem, da2, db2, idesc, 1u);
-                  mma_f16(d_tmem, da2 + a_kadv, db2 + b_kadv, idesc, 1u);
+                  warp_mma_f16(d_tmem, da, db, idesc, accumulate);
+                  warp_mma_f16(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
+                  warp_mma_f16(d_tmem, da2, db2, idesc, 1u);
+                  warp_mma_f16(d_tmem, da2 + a_kadv, db2 + b_kadv, idesc, 1u);
                   accumulate = 1u;
                   a_lo += 2 * fw.halo_row16;
                   b_lo += 2 * fw.b_tap16;
                 }
                 if (g < cnt) {
                   const uint64_t da = ((uint64_t)fw.a_hi << 32) | a_lo, db = ((uint64_t)fw.b_hi << 32) | b_lo;
-                  mma_f16(d_tmem, da, db, idesc, accumulate);
-                  mma_f16(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
+                  warp_mma_f16(d_tmem, da, db, idesc, accumulate);
+                  warp_mma_f16(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
                   accumulate = 1u;
                 }
               }
-              mma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+              warp_commit(empty_bar(s));  // frees the stage once these MMAs have read it
               sa16 += fw.stage16;
               if (++s == S) {
                 s = 0;
@@ -883,17 +933,17 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               if (SPLIT) {
-                mma_tf32(d_tmem, da + lo_off, db, idesc, accumulate);
-                mma_tf32(d_tmem, da, db + lo_off, idesc, 1u);
-                mma_tf32(d_tmem, da, db, idesc, 1u);
+                warp_mma_tf32(d_tmem, da + lo_off, db, idesc, accumulate);
+                warp_mma_tf32(d_tmem, da, db + lo_off, idesc, 1u);
+                warp_mma_tf32(d_tmem, da, db, idesc, 1u);
               } else {
-                mma_f16(d_tmem, da, db, idesc, accumulate);
+                warp_mma_f16(d_tmem, da, db, idesc, accumulate);
               }
               accumulate = 1u;
               da += a_kadv;
               db += b_kadv;
             }
-            mma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+            warp_commit(empty_bar(s));  // frees the stage once these MMAs have read it
             if (++s == S) {
               s = 0;
               ph ^= 1u;
@@ -901,8 +951,10 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
           }
         }
         if (!ok) break;
-        if (t.ks_end > t.ks_begin) mma_commit(acc_full_bar((int)buf));
-        else mbar_arrive(acc_full_bar((int)buf));  // nothing to accumulate: the epilogue writes zeros
+        if (grp == 0) PDNN_TRACE(3, tcount);
+        ++tcount;
+        if (t.ks_end > t.ks_begin) warp_commit(acc_full_bar((int)buf));
+        else if (elect_one()) mbar_arrive(acc_full_bar((int)buf));  // nothing to accumulate: the epilogue writes zeros
         if (++buf == acc_bufs) {
           buf = 0;
           aph ^= 1u;
@@ -914,6 +966,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
     [[maybe_unused]] const int row = q * 32 + lane;
     uint32_t store_count = 0;
+    [[maybe_unused]] uint32_t tcount = 0;
     const int wslot = role - 2;  // 0..3: which staging slices of the group this warp owns
     WarpStore ws;
     ws.nsw = a.nsw;
@@ -932,8 +985,10 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       t.w0 += sub_w;
       t.h0 += sub_h;
       t.n0 += sub_n;
+      if (warp == 2 && lane == 0) PDNN_TRACE(6, tcount);
       if (!mbar_wait(acc_full_bar((int)buf), aph, abort_flag, g_error_record, a.wait_limit_ns, 0x400u + buf)) break;
       tc_fence_after_sync();
+      if (warp == 2 && lane == 0) PDNN_TRACE(4, tcount);
       const uint32_t tmem_acc = grp_tmem + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
       const bool zero = !(t.ks_end > t.ks_begin);
       if constexpr (EPI >= 2) {
@@ -948,6 +1003,8 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar((int)buf));
+      if (warp == 2 && lane == 0) PDNN_TRACE(5, tcount);
+      ++tcount;
       if (++buf == acc_bufs) {
         buf = 0;
         aph ^= 1u;
@@ -1127,6 +1184,8 @@ bool choose_box_halo(int W, int H, int rows, int* tw, int* th) {
 bool want_narrow(int ksteps, int cols) { return ksteps <= 4 || cols <= 128; }
 
 int pick_bn(long long row_tiles, int cols, int unit, int max_bn, int sms, int ksteps = 1 << 30) {
+  const int forced = PDNN_KNOB("PDNN_BN", 0);
+  if (forced > 0 && forced <= max_bn && forced % unit == 0 && forced % 64 == 0 && cols >= forced) return forced;
   if (want_narrow(ksteps, cols)) max_bn = std::min(max_bn, 128);
   sms *= 2;  // two pipelines per CTA work on two tiles at a time
   // cost ~ waves * (bn + fixed overhead); unit: granularity the B loader needs
@@ -1215,7 +1274,14 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
                      : 0;
   }
   const bool split = compute_dtype == PDNN_F32;
-  g.groups = split ? 1 : 2;
+  // Two pipelines per CTA, except for 256-column tiles outside pair mode with a reduction of 8 steps or
+  // more: their MMAs take 128 cycles each, which one issuer sustains, and a single pipeline leaves
+  // TMEM for a second accumulator buffer, so that the epilogue overlaps the next tile.
+  {
+    const int steps = g.a_mn ? g.slabs_per_split : g.num_taps * g.cblocks * (g.halo ? 3 : 1);
+    const int dflt = (!g.a_mn && !g.pair && g.bn == 256 && steps >= 8) ? 1 : 2;
+    g.groups = split ? 1 : PDNN_KNOB("PDNN_GROUPS", dflt);
+  }
   g.acc_stride = std::max(32, next_pow2(g.bn));
   g.acc_bufs = g.groups * 2 * g.acc_stride <= 512 ? 2 : 1;
   g.tmem_cols = next_pow2(g.groups * g.acc_bufs * g.acc_stride);
@@ -1250,7 +1316,8 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
     const int avail = kSmemBudget - fixed;
     auto stages_with = [&](int nsw) { return (avail - staging(nsw)) / (int)stage; };
     g.nsw = stages_with(2) >= 4 ? 2 : 1;
-    g.stages = std::min(kMaxStages, stages_with(g.nsw));
+    g.nsw = PDNN_KNOB("PDNN_NSW", g.nsw);
+    g.stages = std::min(PDNN_KNOB("PDNN_STAGES", kMaxStages), stages_with(g.nsw));
     return g.stages >= 2;
   }
   if (!g.a_mn && !split && g.tma_store && g.b_batch_mul == 0) {
@@ -1258,9 +1325,11 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
     const int a_stage = g.halo ? (int)g.halo_stage_bytes : kABytes;
     auto fits = [&](size_t res) {
       return res <= kMaxResidentB && res % 1024 == 0 &&
-             (kSmemBudget - fixed - (int)res - staging(1)) / (g.groups * a_stage) >= 2;
+             (kSmemBudget - fixed - (int)res - staging(1)) / (g.groups * a_stage) >= (g.halo ? 2 : 3);
     };
-    if (fits(res_all)) {
+    const int bres_knob = PDNN_KNOB("PDNN_BRES", -1);  // 0: never resident, 2: per-column-tile only
+    if (bres_knob == 0 && !g.halo) {
+    } else if (fits(res_all) && bres_knob != 2) {
       g.b_res = 1;
       g.b_res_bytes = (unsigned)res_all;
       stage = (unsigned)a_stage;
@@ -1277,7 +1346,8 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   const int avail = kSmemBudget - fixed - (int)g.b_res_bytes;
   auto stages_with = [&](int nsw) { return (avail - staging(nsw)) / (g.groups * (int)stage); };
   g.nsw = stages_with(2) >= 3 ? 2 : 1;
-  g.stages = std::min(kMaxStages, stages_with(g.nsw));
+  g.nsw = PDNN_KNOB("PDNN_NSW", g.nsw);
+  g.stages = std::min(PDNN_KNOB("PDNN_STAGES", kMaxStages), stages_with(g.nsw));
   if (g.stages < 2 && g.groups == 2) {  // very wide stages: one pipeline with a deeper ring
     g.groups = 1;
     g.acc_bufs = 2 * g.acc_stride <= 512 ? 2 : 1;
@@ -1688,7 +1758,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   // rows, so each column becomes one reduction step over one copy (halo mode), provided the whole
   // filter can stay in shared memory.
   int hw = 0, hh = 0;
-  const bool halo = try_halo && dtype != PDNN_F32 && p.stride_rows == 1 && p.stride_cols == 1 &&
+  const bool halo = try_halo && PDNN_KNOB("PDNN_HALO", 1) && dtype != PDNN_F32 && p.stride_rows == 1 && p.stride_cols == 1 &&
                     p.window_rows >= 2 && p.window_rows <= 15 && p.window_cols <= 8 &&
                     (size_t)p.window_rows * p.window_cols * ceil_div(p.channels, epr) * 128u *
                             (size_t)(ceil_div(p.features, 64) * 64) <= kMaxResidentB &&
@@ -1708,16 +1778,25 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   g.tiles_n = ceil_div(p.batch, g.tn);
   const long long row_tiles = (long long)g.tiles_w * g.tiles_h * g.tiles_n;
   const int ksteps_all = p.window_rows * p.window_cols * ceil_div(p.channels, epr);
-  // Long reductions over filters too large to keep in shared memory are bound by the bytes an SM
-  // pulls from L2 per MMA: the two pipelines then share one B tile per stage (pair mode).  Measured
-  // on ResNet-50 shapes it pays from about 32 reduction steps, or from 16 with 512 or more features;
-  // shorter reductions lose more to the unhidden epilogue of the 256-column accumulators.
-  const bool pairing = try_halo && !halo && dtype != PDNN_F32 && hwcf && p.features % 128 == 0 &&
-                       (ksteps_all >= 32 || (ksteps_all >= 16 && p.features >= 512)) && row_tiles >= 2 &&
-                       (!epi || epi->beta == 0.f);
+  // Long reductions over filters too large to keep in shared memory are bound by the bytes that
+  // pass through an SM's shared memory per MMA (the operand reads of the tensor core and the TMA
+  // fills share its 128 bytes per cycle): the two pipelines then share one B tile per stage (pair
+  // mode).  Measured on ResNet-50 shapes it pays ...
+  const int pair_knob = PDNN_KNOB("PDNN_PAIR", -1);  // 0: never, 1: whenever legal
+  // ... from 16 reduction steps on for filters of 128 features and from 32 on for wider ones (which
+  // do better as single 256-column tiles on one double-buffered pipeline until then), provided the
+  // pairs still fill the device: a grid of fewer pair tiles than SMs leaves SMs idle that single
+  // tiles would use.
+  const int pair_bn_auto = (p.features % 256 == 0 && p.features >= 512) ? 256 : 128;
+  const bool pair_auto = ksteps_all >= (p.features >= 256 ? 32 : 16) &&
+                         (row_tiles / 2) * ceil_div(p.features, pair_bn_auto) >= sms;
+  const bool pair_wanted = pair_knob < 0 ? pair_auto : pair_knob != 0;
+  const bool pairing = try_halo && !halo && dtype != PDNN_F32 && hwcf && p.features % 128 == 0 && pair_wanted &&
+                       row_tiles >= 2 && (!epi || epi->beta == 0.f);
   if (pairing) {
     g.pair = 1;
-    g.bn = p.features % 256 == 0 ? 256 : 128;
+    // 128-column tiles leave room for two accumulator buffers per pipeline; narrow filters use them
+    g.bn = (p.features % 256 == 0 && PDNN_KNOB("PDNN_PAIR_BN", pair_bn_auto) == 256) ? 256 : 128;
     if (g.tiles_w % 2 == 0) {
       g.pair_dim = 1;
       g.tiles_w /= 2;
@@ -2469,5 +2548,13 @@ int tc_read_error_record(unsigned out[4], int clear) {
   return PDNN_OK;
 }
 
+
+#ifdef PDNN_TUNE
+extern "C" int pdnn_debug_trace(long long* out, int words) {
+  cudaDeviceSynchronize();
+  const size_t n = std::min<size_t>((size_t)words, (size_t)kTraceKinds * kTraceTiles) * sizeof(long long);
+  return cudaMemcpyFromSymbol(out, g_trace, n) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 }  // namespace pdnn

@@ -80,6 +80,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// True in exactly one lane of the (fully active) warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- TMA -----------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
                                             int c2, int c3) {
@@ -196,6 +209,29 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
 // has completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- whole-warp forms ------------------------------------------------------------------------------
+// Called by all 32 lanes of a warp with warp-uniform arguments; one elected lane issues the
+// instruction.  Keeping the surrounding loop convergent lets the compiler hold descriptors, barrier
+// addresses and coordinates in uniform registers, which is where these instructions read them.
+__device__ __forceinline__ void warp_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  if (elect_one()) mma_f16(d_tmem, a_desc, b_desc, idesc, accumulate);
+}
+__device__ __forceinline__ void warp_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  if (elect_one()) mma_tf32(d_tmem, a_desc, b_desc, idesc, accumulate);
+}
+__device__ __forceinline__ void warp_commit(uint32_t bar) {
+  if (elect_one()) mma_commit(bar);
+}
+__device__ __forceinline__ void warp_tma_load_4d(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                                 int c2, int c3) {
+  if (elect_one()) tma_load_4d(smem_dst, map, bar, c0, c1, c2, c3);
+}
+__device__ __forceinline__ void warp_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  if (elect_one()) mbar_arrive_expect_tx(bar, bytes);
 }
 
 // ---- descriptors ---------------------------------------------------------------------------------
