@@ -371,7 +371,7 @@ def run_layer_mode(args):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         pd.conv2d(pd.FORWARD, x, wt, p, algorithm=args.algorithm, out=y, bias=b, activation=pd.ACT_RELU,
-                  workspace=None if args.algorithm == pd.ALGO_TILED else
+                  workspace=None if args.algorithm in (pd.ALGO_TILED, pd.ALGO_IM2COL) else
                   torch.empty(max(pd.conv2d_workspace_size(pd.FORWARD, {"f16": 1, "bf16": 2, "f32": 0}[args.dtype], p,
                                                            args.algorithm)[1], 1), device="cuda", dtype=dt))
         e1.record()
@@ -688,7 +688,7 @@ def main():
     ap.add_argument("--layer", type=int, nargs=7, metavar=("N", "H", "W", "C", "K", "WINDOW", "STRIDE"),
                     help="time one forward convolution layer (fused bias + ReLU) and exit")
     ap.add_argument("--dtype", default="f16", choices=["f16", "bf16", "f32"])
-    ap.add_argument("--algorithm", type=int, default=2, help="PdnnAlgorithm for --layer (2 tiled = implicit GEMM, 4 Winograd)")
+    ap.add_argument("--algorithm", type=int, default=3, help="PdnnAlgorithm for --layer (3 im2col tag = implicit GEMM, 4 Winograd)")
     ap.add_argument("--reps", type=int, default=3)
     args = ap.parse_args()
     if args.impl == "reference":

@@ -17,7 +17,7 @@ enum class ConvolutionMode { CROSS_CORRELATION = 0, CONVOLUTION };
 class ConvolutionDescriptor {
  public:
   StatusCode set2d(int pad_h, int pad_w, int stride_h, int stride_w, int dilation_h, int dilation_w,
-                   ConvolutionMode mode) {
+                   ConvolutionMode mode = ConvolutionMode::CROSS_CORRELATION) {
     if (pad_h < 0 || pad_w < 0 || stride_h <= 0 || stride_w <= 0 || dilation_h != 1 || dilation_w != 1 ||
         mode != ConvolutionMode::CROSS_CORRELATION)
       return StatusCode::InvalidParameter;
@@ -53,42 +53,53 @@ inline StatusCode setConvolutionNdDescriptor(ConvolutionDescriptor& desc, int nu
 }
 inline StatusCode setConvolutionGroupCount(ConvolutionDescriptor& desc, int groups) { return desc.setGroupCount(groups); }
 
-/** Filter extents are given as k, c, h, w whatever the layout. */
+/** Filter extents are given as k, c, h, w whatever the layout.  As in the reference
+ * (include/portdnn/compat/convolution.hpp:278-369) the descriptor keeps a FilterFormat of its own,
+ * derived from the DataFormat it is set with: NCHW -> FCHW, NHWC -> HWCF. */
 class FilterDescriptor {
  public:
   StatusCode set4d(DataFormat format, int k, int c, int h, int w) {
     if (k <= 0 || c <= 0 || h <= 0 || w <= 0) return StatusCode::InvalidParameter;
-    format_ = format;
+    if (format != DataFormat::NCHW && format != DataFormat::NHWC) return StatusCode::InvalidParameter;
+    format_ = format == DataFormat::NCHW ? FilterFormat::FCHW : FilterFormat::HWCF;
     k_ = k;
     c_ = c;
     h_ = h;
     w_ = w;
     return StatusCode::OK;
   }
-  DataFormat getFormat() const { return format_; }
+  FilterFormat getFormat() const { return format_; }
   size_t getSize() const { return size_t(k_) * c_ * h_ * w_; }
+  StatusCode get4dDescriptorDims(int* k, int* c, int* h, int* w) const {
+    if (k == nullptr || c == nullptr || h == nullptr || w == nullptr) return StatusCode::InvalidParameter;
+    *k = k_;
+    *c = c_;
+    *h = h_;
+    *w = w_;
+    return StatusCode::OK;
+  }
+  StatusCode getFilter4dDescriptor(SNNDataType* dataType, FilterFormat* format, int* k, int* c, int* h, int* w) const {
+    if (dataType == nullptr || format == nullptr) return StatusCode::InvalidParameter;
+    *dataType = SNNDataType::SNN_FLOAT;
+    *format = format_;
+    return get4dDescriptorDims(k, c, h, w);
+  }
   int k() const { return k_; }
   int c() const { return c_; }
   int h() const { return h_; }
   int w() const { return w_; }
 
  private:
-  DataFormat format_ = DataFormat::NCHW;
+  FilterFormat format_ = FilterFormat::FCHW;
   int k_ = 0, c_ = 0, h_ = 0, w_ = 0;
 };
 inline StatusCode setFilter4dDescriptor(FilterDescriptor& desc, SNNDataType, DataFormat format, int k, int c, int h,
                                         int w) {
   return desc.set4d(format, k, c, h, w);
 }
-inline StatusCode getFilter4dDescriptor(FilterDescriptor const& desc, SNNDataType* dataType, DataFormat* format, int* k,
+inline StatusCode getFilter4dDescriptor(FilterDescriptor const& desc, SNNDataType* dataType, FilterFormat* format, int* k,
                                         int* c, int* h, int* w) {
-  *dataType = SNNDataType::SNN_FLOAT;
-  *format = desc.getFormat();
-  *k = desc.k();
-  *c = desc.c();
-  *h = desc.h();
-  *w = desc.w();
-  return StatusCode::OK;
+  return desc.getFilter4dDescriptor(dataType, format, k, c, h, w);
 }
 
 /** out = 1 + (in + 2*pad - window) / stride (dilation is 1), convolution.hpp:403-431. */
@@ -121,7 +132,7 @@ inline conv2d::Conv2DParams descToSnnParams(TensorDescriptor const& x, TensorDes
   p.dilation_rows = p.dilation_cols = 1;
   p.groups = conv.groups();
   p.input_format = x.getFormat();
-  p.filter_format = x.getFormat() == DataFormat::NHWC ? FilterFormat::HWCF : FilterFormat::FCHW;
+  p.filter_format = w.getFormat();  // the filter descriptor's own format, convolution.hpp:466-495
   p.group_format = BatchFormat::STRIDED;
   return p;
 }

@@ -196,7 +196,8 @@ size_t pdnn_noalloc_scratch_bytes(void);
 
 /* Replaces pooling::launch, two-pointer form (include/portdnn/pooling/launch.h:112-180,
  * src/pooling/launch_pooling.cc:89-165): forward for every op (input -> output) and the
- * average gradient (direction 1: input = dy, output = dx).  NHWC only. */
+ * average gradient (direction 1: input = dy, output = dx).  input_format 1 (NCHW) runs the NHWC
+ * kernel between two transposes in scratch from the stream-ordered allocator. */
 int pdnn_pooling(int op, int direction, int dtype, const void* input, void* output,
                  const PdnnPoolingParams* params, void* stream);
 
@@ -257,6 +258,14 @@ int pdnn_binaryop(int op, int dtype, const void* lhs, const int* lhs_dims, int n
  * alpha/beta blend, include/portdnn/compat/scaling.hpp:202-281, as one pass. */
 int pdnn_scale_blend(int dtype, const void* a, float alpha, const void* b, float beta, void* out, size_t n_items,
                      void* stream);
+
+/* Replaces transpose::launch and convert_nhwc_to_nchw / convert_nchw_to_nhwc
+ * (include/portdnn/transpose/launch.h:66-233): output extent d is dims[permutation[d]] and
+ * out[i_permutation[0]][i_permutation[1]]... = in[i_0][i_1]...  Elements are moved as raw words of
+ * elem_bytes (1, 2, 4 or 8) bytes, as the reference does (include/portdnn/internal/transpose/launch.h:47-83);
+ * up to six dimensions; not in place. */
+int pdnn_transpose(int elem_bytes, const void* input, void* output, const int* dims, int n_dims, const int* permutation,
+                   void* stream);
 
 /* Replaces matmul::launch / Backend::matmul / Backend::batch_matmul
  * (include/portdnn/matmul/launch.h:37-90, include/portdnn/backend/backend_interface.h:78-118):

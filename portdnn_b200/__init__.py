@@ -18,7 +18,7 @@ from .api import (  # noqa: F401
     Conv2DParams, DepthwiseConv2DParams, PoolingParams, SoftmaxParams, BatchNormParams,
     conv_params, depthwise_params, pool_params, calculate_padding,
     conv2d, conv2d_workspace_size, conv2d_validate, depthwise_conv2d, pooling, pooling_max_grad,
-    pointwise, pointwise_grad, bias_add, binaryop, scale_blend, matmul,
+    pointwise, pointwise_grad, bias_add, binaryop, scale_blend, matmul, transpose,
     softmax, batchnorm_params, batchnorm_forward, batchnorm_gradient,
     device_error_record, launch_count, lib, library_path,
 )

@@ -187,7 +187,7 @@ def conv2d_workspace_size(pass_, dtype, params, algorithm):
     return req.value, rec.value
 
 
-def conv2d(pass_, inp, fil, params, algorithm=ALGO_TILED, out=None, workspace=None, bias=None, activation=ACT_NONE,
+def conv2d(pass_, inp, fil, params, algorithm=ALGO_IM2COL, out=None, workspace=None, bias=None, activation=ACT_NONE,
            alpha=1.0, beta=0.0, relu_forward_output=None, output_f32=False):
     """conv2d::launch<T, ConvType>(input, filter, output, params, selector, backend, workspace, size)
     (include/portdnn/conv2d/launch.h:59-72) with the selector's answer passed as ``algorithm``.
@@ -369,6 +369,23 @@ def matmul(lhs, rhs, batches, m, k, n, transpose_lhs=False, transpose_rhs=False,
         out = torch.empty(batches * m * n, dtype=lhs.dtype, device=lhs.device)
     _check(lib().pdnn_matmul(_dtype_code(lhs), int(transpose_lhs), int(transpose_rhs), _ptr(lhs), _ptr(rhs), _ptr(out),
                              int(batches), int(m), int(k), int(n), ctypes.c_float(beta), _stream()))
+    return out
+
+
+def transpose(inp, dims, permutation, out=None):
+    """transpose::launch<T> (include/portdnn/transpose/launch.h:66-111): output extent d is dims[permutation[d]]."""
+    torch = _torch()
+    _require_cuda(inp, out)
+    dims, permutation = [int(d) for d in dims], [int(d) for d in permutation]
+    n = 1
+    for d in dims:
+        n *= d
+    if inp.numel() != n or len(dims) != len(permutation):
+        raise ValueError("tensor size does not match the dimensions")
+    if out is None:
+        out = torch.empty_like(inp)
+    cd, cp = (ctypes.c_int * len(dims))(*dims), (ctypes.c_int * len(dims))(*permutation)
+    _check(lib().pdnn_transpose(inp.element_size(), _ptr(inp), _ptr(out), cd, len(dims), cp, _stream()))
     return out
 
 

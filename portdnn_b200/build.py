@@ -14,7 +14,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libportdnn_b200.so")
-SOURCES = ["c_api.cu", "hbm_kernels.cu", "direct_conv.cu", "tc_gemm.cu", "winograd.cu", "norm_kernels.cu"]
+SOURCES = ["c_api.cu", "hbm_kernels.cu", "direct_conv.cu", "tc_gemm.cu", "winograd.cu", "norm_kernels.cu",
+           "layout_kernels.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
 

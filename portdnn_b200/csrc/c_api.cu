@@ -89,11 +89,27 @@ int validate_conv(int pass, const PdnnConv2DParams* p, int algorithm) {
     return fail(PDNN_INVALID_ALGORITHM, "conv2d: NCHW is only supported by the direct algorithm");
   if (p->groups > 1 && algorithm != PDNN_ALGO_IM2COL)
     return fail(PDNN_INVALID_ALGORITHM, "conv2d: grouped convolution is only supported by the im2col algorithm");
-  // Per-algorithm applicability, as the reference's launchers report it.
+  // Per-algorithm applicability, with the status codes of the reference's launchers.
+  const bool square = p->window_rows == p->window_cols && p->stride_rows == p->stride_cols;
   if (algorithm == PDNN_ALGO_MATMUL &&
-      !(p->window_rows == 1 && p->window_cols == 1 && p->stride_rows == 1 && p->stride_cols == 1 && p->pad_rows == 0 &&
-        p->pad_cols == 0))
-    return fail(PDNN_INVALID_ALGORITHM, "conv2d: the matmul algorithm needs a 1x1 window, stride 1 and no padding");
+      !(p->window_rows == 1 && p->window_cols == 1 && p->stride_rows == 1 && p->stride_cols == 1))
+    // include/portdnn/conv2d/implementation/matmul.h:95-104 (SNN_VALIDATE_PARAM)
+    return fail(PDNN_INVALID_PARAMETER, "conv2d: Matmul can only be used for 1x1 NHWC convolutions with stride 1.");
+  if (algorithm == PDNN_ALGO_TILED) {
+    // src/conv2d/tiled/launch_tiled.cc:164-273: no filter backprop; forward and input backprop for
+    // square windows 1 and 3 with stride 1 or 2 and window 5 with stride 1
+    const int w = p->window_rows, st = p->stride_rows;
+    const bool listed = square && ((w == 1 || w == 3) ? (st == 1 || st == 2) : (w == 5 && st == 1));
+    if (pass == PDNN_FILTER_BACKPROP || !listed)
+      return fail(PDNN_INVALID_ALGORITHM, "conv2d: the tiled algorithm does not cover this window / stride / pass");
+  }
+  if (algorithm == PDNN_ALGO_WINOGRAD || algorithm == PDNN_ALGO_WINOGRAD_LARGE) {
+    // include/portdnn/internal/conv2d/winograd/launch.h:298-396: 3x3 (both tags), 3x1 and 1x3 (Winograd only)
+    const bool w33 = p->window_rows == 3 && p->window_cols == 3;
+    const bool w31 = (p->window_rows == 3 && p->window_cols == 1) || (p->window_rows == 1 && p->window_cols == 3);
+    if (!(w33 || (algorithm == PDNN_ALGO_WINOGRAD && w31)))
+      return fail(PDNN_INVALID_ALGORITHM, "conv2d: the Winograd algorithms need a 3x3 (or 3x1 / 1x3) window");
+  }
   return PDNN_OK;
 }
 
@@ -131,6 +147,9 @@ int run_direct_backprop(int pass, int dtype, const void* in, const void* fil, vo
                                (size_t)p.batch * p.in_rows * p.in_cols * p.channels, s);
 }
 
+int dispatch_conv(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams* p, int algorithm,
+                  const PdnnConvEpilogue* epi, const PdnnBackpropFusion* fusion, void* ws, size_t ws_elems, cudaStream_t s);
+
 int run_conv(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams* p, int algorithm,
              const PdnnConvEpilogue* epi, const PdnnBackpropFusion* fusion, void* ws, size_t ws_elems, void* stream) {
   int st = validate_conv(pass, p, algorithm);
@@ -139,6 +158,23 @@ int run_conv(int pass, int dtype, const void* in, const void* fil, void* out, co
   if (in == nullptr || fil == nullptr || out == nullptr) return fail(PDNN_INVALID_PARAMETER, "conv2d: null tensor");
   if (device_sm_count() <= 0) return fail(PDNN_ALLOCATION_PROBLEM, "conv2d: no sm_100 CUDA device");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (p->input_format == 1) {
+    // NCHW tensors with an FCHW filter (the only pairing validate_conv lets through): the NHWC
+    // kernels between two transposes.  The reference's NCHW path is its direct kernel
+    // (src/conv2d/direct/kernels_nchw.h:28,157,300), which computes the same sums.
+    if (fusion != nullptr && fusion->relu_forward_output != nullptr)
+      return fail(PDNN_INVALID_PARAMETER, "conv2d: the fused ReLU-gradient form needs NHWC tensors");
+    const bool read_out = epi != nullptr && epi->beta != 0.f;
+    return conv2d_nchw(pass, dtype, in, fil, out, *p, read_out, s,
+                       [&](const void* a, const void* b, void* c, const PdnnConv2DParams& q) {
+                         return dispatch_conv(pass, dtype, a, b, c, &q, PDNN_ALGO_TILED, epi, fusion, nullptr, 0, s);
+                       });
+  }
+  return dispatch_conv(pass, dtype, in, fil, out, p, algorithm, epi, fusion, ws, ws_elems, s);
+}
+
+int dispatch_conv(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams* p, int algorithm,
+                  const PdnnConvEpilogue* epi, const PdnnBackpropFusion* fusion, void* ws, size_t ws_elems, cudaStream_t s) {
   // The Winograd tags run F(2x2,3x3) when the caller brought the scratch it needs; without it the
   // implicit-GEMM kernel, which needs none, runs the layer instead of reporting
   // InsufficientWorkspace (include/portdnn/internal/conv2d/winograd/launch.h:280).
@@ -237,7 +273,18 @@ size_t pdnn_depthwise_workspace_bytes(int pass, int dtype, const PdnnDepthwiseCo
 int pdnn_pooling(int op, int direction, int dtype, const void* input, void* output, const PdnnPoolingParams* params,
                  void* stream) {
   if (params == nullptr || input == nullptr || output == nullptr) return fail(PDNN_INVALID_PARAMETER, "pooling: null argument");
-  return launch_pooling(op, direction, dtype, input, output, *params, static_cast<cudaStream_t>(stream));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (params->input_format == 1) {  // NCHW (the reference has it for the forward pass, src/pooling/kernels.h:418-482)
+    if (dtype < PDNN_F32 || dtype > PDNN_BF16) return fail(PDNN_INVALID_PARAMETER, "pooling: unknown dtype %d", dtype);
+    const size_t in_px = (size_t)params->in_rows * params->in_cols, out_px = (size_t)params->out_rows * params->out_cols;
+    const void* ins[1] = {input};
+    const size_t rows[1] = {direction == 0 ? in_px : out_px};
+    return pooling_nchw(dtype, ins, rows, 1, output, direction == 0 ? out_px : in_px, *params, s,
+                        [&](const void* const* t, void* o, const PdnnPoolingParams& q) {
+                          return launch_pooling(op, direction, dtype, t[0], o, q, s);
+                        });
+  }
+  return launch_pooling(op, direction, dtype, input, output, *params, s);
 }
 
 int pdnn_pooling_max_grad(int op, int dtype, const void* input_data, const void* output_data,
@@ -246,8 +293,18 @@ int pdnn_pooling_max_grad(int op, int dtype, const void* input_data, const void*
   if (params == nullptr || input_data == nullptr || output_data == nullptr || input_backprop == nullptr ||
       output_backprop == nullptr)
     return fail(PDNN_INVALID_PARAMETER, "pooling: null argument");
-  return launch_pooling_max_grad(op, dtype, input_data, output_data, input_backprop, output_backprop, *params,
-                                 static_cast<cudaStream_t>(stream));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (params->input_format == 1) {
+    if (dtype < PDNN_F32 || dtype > PDNN_BF16) return fail(PDNN_INVALID_PARAMETER, "pooling: unknown dtype %d", dtype);
+    const size_t in_px = (size_t)params->in_rows * params->in_cols, out_px = (size_t)params->out_rows * params->out_cols;
+    const void* ins[3] = {input_data, output_data, input_backprop};
+    const size_t rows[3] = {in_px, out_px, out_px};
+    return pooling_nchw(dtype, ins, rows, 3, output_backprop, in_px, *params, s,
+                        [&](const void* const* t, void* o, const PdnnPoolingParams& q) {
+                          return launch_pooling_max_grad(op, dtype, t[0], t[1], t[2], o, q, s);
+                        });
+  }
+  return launch_pooling_max_grad(op, dtype, input_data, output_data, input_backprop, output_backprop, *params, s);
 }
 
 int pdnn_softmax(int direction, int dtype, const void* input, const void* gradient, void* output,
@@ -306,6 +363,13 @@ int pdnn_scale_blend(int dtype, const void* a, float alpha, const void* b, float
   if (n_items != 0 && (a == nullptr || out == nullptr || (beta != 0.f && b == nullptr)))
     return fail(PDNN_INVALID_PARAMETER, "blend: null tensor");
   return launch_scale_blend(dtype, a, alpha, b, beta, out, n_items, static_cast<cudaStream_t>(stream));
+}
+
+int pdnn_transpose(int elem_bytes, const void* input, void* output, const int* dims, int n_dims, const int* permutation,
+                   void* stream) {
+  if (input == nullptr || output == nullptr || dims == nullptr || permutation == nullptr)
+    return fail(PDNN_INVALID_PARAMETER, "transpose: null argument");
+  return launch_transpose(elem_bytes, input, output, dims, n_dims, permutation, static_cast<cudaStream_t>(stream));
 }
 
 int pdnn_matmul(int dtype, int transpose_lhs, int transpose_rhs, const void* lhs, const void* rhs, void* output,

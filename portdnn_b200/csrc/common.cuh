@@ -9,6 +9,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <functional>
 
 #include "../../include/portdnn_b200.h"
 
@@ -122,6 +123,20 @@ int launch_scale_blend(int dtype, const void* a, float alpha, const void* b, flo
                        cudaStream_t s);
 int launch_direct_conv(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
                        const PdnnConvEpilogue* epi, cudaStream_t s);
+
+// Transposition and the NCHW forms built on it (layout_kernels.cu).  elem_bytes is 1, 2, 4 or 8;
+// out[i_perm[0]][i_perm[1]]... = in[i_0][i_1]... with output extent d = dims[perm[d]].
+int launch_transpose(int elem_bytes, const void* in, void* out, const int* dims, int n_dims, const int* perm,
+                     cudaStream_t s);
+// Runs `run` on NHWC / HWCF copies of the NCHW / FCHW tensors of a convolution pass and brings the
+// result back; read_out: the previous contents of `out` are needed (a beta blend).
+using ConvRunner = std::function<int(const void* in, const void* fil, void* out, const PdnnConv2DParams& nhwc_params)>;
+int conv2d_nchw(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p, bool read_out,
+                cudaStream_t s, const ConvRunner& run);
+// The same for pooling: n_inputs tensors of input_rows[i] spatial positions per (image, channel).
+using PoolRunner = std::function<int(const void* const* nhwc_inputs, void* nhwc_out, const PdnnPoolingParams& nhwc_params)>;
+int pooling_nchw(int dtype, const void* const* inputs, const size_t* input_rows, int n_inputs, void* out, size_t out_rows,
+                 const PdnnPoolingParams& p, cudaStream_t s, const PoolRunner& run);
 
 // softmax and batchnorm (norm_kernels.cu)
 int launch_softmax(int direction, int dtype, const void* input, const void* gradient, void* output,

@@ -131,7 +131,7 @@ class ConvStackRunner:
                 self.weights[i] = w.to(self.dtype)
                 self.biases[i] = (torch.randn(p.features, device=device, generator=g) * 0.01).to(self.dtype)
                 sizes.append(p.batch * p.out_rows * p.out_cols * p.features)
-                _, rec = api.conv2d_workspace_size(api.FORWARD, self.code, p, api.ALGO_TILED)
+                _, rec = api.conv2d_workspace_size(api.FORWARD, self.code, p, api.ALGO_IM2COL)
                 if rec:
                     self.workspaces[i] = torch.empty(rec, dtype=self.dtype, device=device)
             else:
@@ -150,7 +150,7 @@ class ConvStackRunner:
             self.dy_last = torch.randn(sizes[last], device=device, generator=g).to(self.dtype)
             self.fbp_ws = {}
             for i in conv_ids:
-                _, rec = api.conv2d_workspace_size(api.FILTER_BACKPROP, self.code, layers[i].params, api.ALGO_TILED)
+                _, rec = api.conv2d_workspace_size(api.FILTER_BACKPROP, self.code, layers[i].params, api.ALGO_IM2COL)
                 if rec:
                     self.fbp_ws[i] = rec
             self.fbp_workspace = torch.empty(max(self.fbp_ws.values(), default=1), dtype=self.dtype, device=device)
@@ -186,7 +186,7 @@ class ConvStackRunner:
     def run_layer(self, i):
         l, p = self.layers[i], self.layers[i].params
         if isinstance(l, ConvLayer):
-            api.conv2d(api.FORWARD, self._in(i), self.weights[i], p, algorithm=api.ALGO_TILED, out=self._out(i),
+            api.conv2d(api.FORWARD, self._in(i), self.weights[i], p, algorithm=api.ALGO_IM2COL, out=self._out(i),
                        bias=self.biases[i], activation=l.activation, workspace=self.workspaces.get(i))
         else:
             api.pooling(l.op, 0, self._in(i), p, out=self._out(i))
@@ -206,7 +206,7 @@ class ConvStackRunner:
         else:
             dst = self.chunk_buffers[l.dst][:n_out]
         if isinstance(l, ConvLayer):
-            api.conv2d(api.FORWARD, src, self.weights[i], p, algorithm=api.ALGO_TILED, out=dst, bias=self.biases[i],
+            api.conv2d(api.FORWARD, src, self.weights[i], p, algorithm=api.ALGO_IM2COL, out=dst, bias=self.biases[i],
                        activation=l.activation, workspace=self.workspaces.get(i))
         else:
             api.pooling(l.op, 0, src, p, out=dst)
@@ -291,13 +291,13 @@ class ConvStackRunner:
                     g = self.scratch[:self.sizes[i]]
                     api.pointwise_grad(api.ACT_RELU, self.acts[i], dy, out=g)
                 k = self.conv_ids.index(i)
-                api.conv2d(api.FILTER_BACKPROP, self._in(i), g, p, algorithm=api.ALGO_TILED, out=self.bucket.view(k),
+                api.conv2d(api.FILTER_BACKPROP, self._in(i), g, p, algorithm=api.ALGO_IM2COL, out=self.bucket.view(k),
                            output_f32=self.dtype != self.torch.float32,
                            workspace=self.fbp_workspace if i in self.fbp_ws else None)
                 if j >= 0:
                     mask = self.acts[j] if self.fuse_mask[j] else None
                     self._add_grad(j, lambda dst: api.conv2d(api.INPUT_BACKPROP, g, self.weights[i], p,
-                                                             algorithm=api.ALGO_TILED, out=dst, relu_forward_output=mask))
+                                                             algorithm=api.ALGO_IM2COL, out=dst, relu_forward_output=mask))
                     if mask is not None:
                         self._masked.add(j)
             elif l.op == api.POOL_AVERAGE:

@@ -50,9 +50,33 @@ def test_validate_params_like_reference(L):
     assert pd.conv2d_validate(pd.FORWARD, p, pd.ALGO_IM2COL) == pd.StatusCode.OK
     p = pd.conv_params(1, 8, 8, 4, 4, 3, 1)
     assert pd.conv2d_validate(pd.FORWARD, p, 0) == pd.StatusCode.InvalidAlgorithm   # NotSupported
-    assert pd.conv2d_validate(pd.FORWARD, p, pd.ALGO_MATMUL) == pd.StatusCode.InvalidAlgorithm  # 3x3 is no matmul
+    assert pd.conv2d_validate(pd.FORWARD, p, pd.ALGO_MATMUL) == pd.StatusCode.InvalidParameter  # 3x3 is no matmul
     p.input_format, p.filter_format = 1, 1          # NCHW: Direct only
     assert pd.conv2d_validate(pd.FORWARD, p, pd.ALGO_TILED) == pd.StatusCode.InvalidAlgorithm
+
+
+def test_algorithm_tags_report_the_reference_status(L):
+    """Which (algorithm, window, stride, pass) combinations the reference's launchers refuse, and how:
+    src/conv2d/tiled/launch_tiled.cc:164-273 (InvalidAlgorithm), include/portdnn/internal/conv2d/winograd/launch.h:298-396
+    (InvalidAlgorithm), include/portdnn/conv2d/implementation/matmul.h:95-104 (InvalidParameter)."""
+    OK, IA, IP = pd.StatusCode.OK, pd.StatusCode.InvalidAlgorithm, pd.StatusCode.InvalidParameter
+    cases = [
+        # window, stride, pass, algorithm, expected
+        (3, 1, pd.FORWARD, pd.ALGO_TILED, OK), (3, 2, pd.INPUT_BACKPROP, pd.ALGO_TILED, OK), (5, 1, pd.FORWARD, pd.ALGO_TILED, OK),
+        (5, 2, pd.FORWARD, pd.ALGO_TILED, IA), (7, 1, pd.FORWARD, pd.ALGO_TILED, IA), (3, 1, pd.FILTER_BACKPROP, pd.ALGO_TILED, IA),
+        (3, 1, pd.FORWARD, pd.ALGO_WINOGRAD, OK), (3, 1, pd.FILTER_BACKPROP, pd.ALGO_WINOGRAD_LARGE, OK),
+        (5, 1, pd.FORWARD, pd.ALGO_WINOGRAD, IA), (1, 1, pd.FORWARD, pd.ALGO_WINOGRAD_LARGE, IA),
+        (1, 1, pd.FORWARD, pd.ALGO_MATMUL, OK), (1, 2, pd.FORWARD, pd.ALGO_MATMUL, IP), (3, 1, pd.INPUT_BACKPROP, pd.ALGO_MATMUL, IP),
+        (7, 2, pd.FILTER_BACKPROP, pd.ALGO_IM2COL, OK), (11, 4, pd.FORWARD, pd.ALGO_DIRECT, OK),
+    ]
+    for window, stride, pass_, algo, want in cases:
+        p = pd.conv_params(2, 16, 16, 8, 8, window, stride)
+        assert pd.conv2d_validate(pass_, p, algo) == want, (window, stride, pass_, algo)
+    p = pd.conv_params(2, 16, 16, 8, 8, 3, 1)
+    p.window_cols = 1   # 3x1: Winograd only
+    assert pd.conv2d_validate(pd.FORWARD, p, pd.ALGO_WINOGRAD) == OK
+    assert pd.conv2d_validate(pd.FORWARD, p, pd.ALGO_WINOGRAD_LARGE) == IA
+    assert pd.conv2d_validate(pd.FORWARD, p, pd.ALGO_TILED) == IA
 
 
 def test_padding_helper_matches_oracle(orc):
@@ -67,7 +91,7 @@ def test_padding_helper_matches_oracle(orc):
 def test_workspace_size_direct_is_zero(L):
     p = pd.conv_params(4, 16, 16, 8, 8, 3, 1)
     assert pd.conv2d_workspace_size(pd.FORWARD, pd.F32, p, pd.ALGO_DIRECT) == (0, 0)
-    req, rec = pd.conv2d_workspace_size(pd.FORWARD, pd.F16, p, pd.ALGO_TILED)
+    req, rec = pd.conv2d_workspace_size(pd.FORWARD, pd.F16, p, pd.ALGO_IM2COL)
     assert req == 0   # implicit GEMM reads the tensors in place
 
 

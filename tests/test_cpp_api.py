@@ -9,8 +9,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 # api_test: every operator through the sycldnn:: templates; network_test: the layer / network
 # wrappers of include/tools/ on a VGG-style and a ResNet-style stack; compat_batchnorm_test: the
-# cuDNN-style batchnorm wrappers of include/portdnn/compat/batchnorm.hpp.
-PROGRAMS = ["api_test", "network_test", "compat_batchnorm_test"]
+# cuDNN-style batchnorm wrappers of include/portdnn/compat/batchnorm.hpp; compat_conv_test: the cuDNN-style
+# convolution / pooling calls on the cases of the reference's test/compat/*.cc.
+PROGRAMS = ["api_test", "network_test", "compat_batchnorm_test", "compat_conv_test", "event_dependency_test"]
 
 
 def _paths(name):
@@ -21,7 +22,7 @@ def _build(name):
     from portdnn_b200 import build
     build.build()
     src, exe = _paths(name)
-    deps = [src, os.path.join(ROOT, "include", "portdnn_b200.h")]
+    deps = [src, os.path.join(ROOT, "include", "portdnn_b200.h"), os.path.join(ROOT, "tests", "cpp", "compat_kat.inc")]
     for sub in ("portdnn", "tools"):
         for d, _, files in os.walk(os.path.join(ROOT, "include", sub)):
             deps += [os.path.join(d, f) for f in files]

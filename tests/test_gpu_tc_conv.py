@@ -55,7 +55,7 @@ FWD_SHAPES = [
 def test_forward_against_oracle(orc, dtype, shape):
     n, h, w, c, k, win, st, same, pad = shape
     p, po, x, wt, _ = _conv_case(orc, dtype, n, h, w, c, k, win, st, bool(same), pad)
-    y = to_host(pd.conv2d(pd.FORWARD, to_dev(x, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_TILED))
+    y = to_host(pd.conv2d(pd.FORWARD, to_dev(x, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_IM2COL))
     assert_no_device_error()
     assert rel_err(y, orc.conv2d(orc.FORWARD, x, wt, po)) <= TOL[dtype]
 
@@ -81,7 +81,7 @@ def test_forward_fused_epilogue(orc, dtype):
     conv = orc.conv2d(orc.FORWARD, x, wt, po)
     ref = np.maximum(0.5 * conv + np.tile(bias, n * h * w), 0) + 0.25 * prev
     out = to_dev(prev, dtype)
-    pd.conv2d(pd.FORWARD, to_dev(x, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_TILED, out=out,
+    pd.conv2d(pd.FORWARD, to_dev(x, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_IM2COL, out=out,
               bias=to_dev(bias, dtype), activation=pd.ACT_RELU, alpha=0.5, beta=0.25)
     assert_no_device_error()
     assert rel_err(to_host(out), ref) <= TOL[dtype]
@@ -107,7 +107,7 @@ BWD_SHAPES = [
 def test_input_backprop_against_oracle(orc, dtype, shape):
     n, h, w, c, k, win, st, same, pad = shape
     p, po, _, wt, dy = _conv_case(orc, dtype, n, h, w, c, k, win, st, bool(same), pad)
-    dx = to_host(pd.conv2d(pd.INPUT_BACKPROP, to_dev(dy, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_TILED))
+    dx = to_host(pd.conv2d(pd.INPUT_BACKPROP, to_dev(dy, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_IM2COL))
     assert_no_device_error()
     assert rel_err(dx, orc.conv2d(orc.INPUT_BACKPROP, dy, wt, po)) <= TOL[dtype]
 
@@ -117,7 +117,7 @@ def test_input_backprop_against_oracle(orc, dtype, shape):
 def test_filter_backprop_against_oracle(orc, dtype, shape):
     n, h, w, c, k, win, st, same, pad = shape
     p, po, x, _, dy = _conv_case(orc, dtype, n, h, w, c, k, win, st, bool(same), pad)
-    dw = to_host(pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, dtype), to_dev(dy, dtype), p, algorithm=pd.ALGO_TILED))
+    dw = to_host(pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, dtype), to_dev(dy, dtype), p, algorithm=pd.ALGO_IM2COL))
     assert_no_device_error()
     assert rel_err(dw, orc.conv2d(orc.FILTER_BACKPROP, x, dy, po)) <= TOL[dtype]
 
@@ -144,10 +144,10 @@ def test_stem_forward_and_filter_backprop_few_channels(orc, dtype, shape):
 def test_filter_backprop_with_caller_workspace(orc):
     n, h, w, c, k, win, st = 8, 28, 28, 64, 64, 3, 1
     p, po, x, _, dy = _conv_case(orc, "f16", n, h, w, c, k, win, st)
-    _, rec = pd.conv2d_workspace_size(pd.FILTER_BACKPROP, pd.F16, p, pd.ALGO_TILED)
+    _, rec = pd.conv2d_workspace_size(pd.FILTER_BACKPROP, pd.F16, p, pd.ALGO_IM2COL)
     assert rec > 0
     ws = torch.empty(rec, dtype=torch.float16, device="cuda")
-    dw = to_host(pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, "f16"), to_dev(dy, "f16"), p, algorithm=pd.ALGO_TILED,
+    dw = to_host(pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, "f16"), to_dev(dy, "f16"), p, algorithm=pd.ALGO_IM2COL,
                            workspace=ws))
     assert_no_device_error()
     assert rel_err(dw, orc.conv2d(orc.FILTER_BACKPROP, x, dy, po)) <= TOL["f16"]
@@ -191,7 +191,7 @@ def test_full_size_layers_tensor_core_vs_direct_kernel(shape):
     wt = ((torch.rand(win * win * c * k, device="cuda", generator=g) * 2 - 1) * (1.0 / (win * win * c)) ** 0.5).half()
     dy = torch.randn(n * p.out_rows * p.out_cols * k, device="cuda", generator=g).half()
     for pass_, a, b in ((pd.FORWARD, x, wt), (pd.INPUT_BACKPROP, dy, wt), (pd.FILTER_BACKPROP, x, dy)):
-        fast = pd.conv2d(pass_, a, b, p, algorithm=pd.ALGO_TILED).float()
+        fast = pd.conv2d(pass_, a, b, p, algorithm=pd.ALGO_IM2COL).float()
         slow = pd.conv2d(pass_, a, b, p, algorithm=pd.ALGO_DIRECT).float()
         assert_no_device_error()
         err = (fast - slow).abs().max().item() / slow.abs().max().item()
@@ -213,13 +213,13 @@ def test_fused_backprop_forms_against_oracle(orc, dtype, shape):
     rng = np.random.default_rng(31)
     # forward output of the preceding layer: about half of it zero, as a ReLU leaves it
     y_prev = rounded(np.maximum(rng.standard_normal(n * h * w * c), 0).astype(np.float32), dtype)
-    dx = to_host(pd.conv2d(pd.INPUT_BACKPROP, to_dev(dy, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_TILED,
+    dx = to_host(pd.conv2d(pd.INPUT_BACKPROP, to_dev(dy, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_IM2COL,
                            relu_forward_output=to_dev(y_prev, dtype)))
     assert_no_device_error()
     ref = orc.pointwise_grad(0, y_prev, orc.conv2d(orc.INPUT_BACKPROP, dy, wt, po))
     assert rel_err(dx, ref) <= TOL[dtype]
     assert not np.any(dx[y_prev <= 0] != 0)
-    dw = pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, dtype), to_dev(dy, dtype), p, algorithm=pd.ALGO_TILED,
+    dw = pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, dtype), to_dev(dy, dtype), p, algorithm=pd.ALGO_IM2COL,
                    output_f32=dtype != "f32")
     assert dw.dtype == torch.float32
     assert_no_device_error()
@@ -229,6 +229,6 @@ def test_fused_backprop_forms_against_oracle(orc, dtype, shape):
 def test_fused_backprop_stem_filter_gradient_fp32(orc):
     n, h, w, c, k, win, st = 2, 32, 32, 3, 64, 7, 2
     p, po, x, _, dy = _conv_case(orc, "f16", n, h, w, c, k, win, st, None, 3)
-    dw = pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, "f16"), to_dev(dy, "f16"), p, algorithm=pd.ALGO_TILED, output_f32=True)
+    dw = pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, "f16"), to_dev(dy, "f16"), p, algorithm=pd.ALGO_IM2COL, output_f32=True)
     assert dw.dtype == torch.float32
     assert rel_err(to_host(dw), orc.conv2d(orc.FILTER_BACKPROP, x, dy, po)) <= TOL["f16"]
