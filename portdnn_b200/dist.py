@@ -68,3 +68,53 @@ def max_over_ranks(value, device=None, group=None):
     t = torch.tensor([float(value)], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return float(t.item())
+
+
+class RankFailure(RuntimeError):
+    """Raised on the surviving ranks when a rank reported a failure, or never reported at all, before
+    a collective of the step."""
+
+
+class StepGuard:
+    """Host-side agreement before the filter-gradient all-reduce: every rank posts the outcome of its
+    backward pass to a key-value store (torch.distributed's TCPStore or any object with set / get /
+    wait) and reads the others' before it enters the collective.  A rank that raised posts "failed";
+    a rank that died posts nothing and the others' wait runs out.  Either way the survivors raise
+    RankFailure instead of blocking inside a collective that can never complete.  The reference is
+    single-device and has no counterpart."""
+
+    def __init__(self, store, rank, world_size, timeout_s=5.0):
+        self.store, self.rank, self.world, self.timeout_s = store, rank, world_size, timeout_s
+
+    def _key(self, step, rank):
+        return "pdnn/step%d/rank%d" % (step, rank)
+
+    def report(self, step, ok=True, reason=""):
+        self.store.set(self._key(step, self.rank), "ok" if ok else "failed:" + reason)
+
+    def check(self, step):
+        """Blocks until every rank has reported for `step` (at most timeout_s per rank) and raises
+        RankFailure if one failed or stayed silent."""
+        import datetime
+        for r in range(self.world):
+            key = self._key(step, r)
+            try:
+                self.store.wait([key], datetime.timedelta(seconds=self.timeout_s))
+            except Exception as e:  # the store's wait raises on time-out
+                raise RankFailure("rank %d did not report for step %d within %.1f s" % (r, step, self.timeout_s)) from e
+            val = self.store.get(key)
+            val = val.decode() if isinstance(val, bytes) else str(val)
+            if val != "ok":
+                raise RankFailure("rank %d reported %s in step %d" % (r, val, step))
+
+    def guarded_all_reduce(self, bucket, step, compute):
+        """Runs compute() (the rank's backward pass), reports its outcome, checks the others and only
+        then sums the bucket.  A local exception is reported before it propagates."""
+        try:
+            compute()
+        except Exception as e:
+            self.report(step, False, type(e).__name__)
+            raise
+        self.report(step, True)
+        self.check(step)
+        return bucket.all_reduce()

@@ -75,3 +75,50 @@ def test_two_ranks_sum_their_filter_gradients():
     port = 29000 + (os.getpid() % 2000)
     mp.spawn(_worker, args=(world, port, out), nprocs=world, join=True)
     assert dict(out) == {0: True, 1: True}
+
+
+def _failing_worker(rank, world, port, out, mode):
+    """Host-injected failures: rank 1 raises in its backward pass ("raise") or leaves without a word
+    ("silent"); rank 0 must get RankFailure before the collective instead of blocking in it."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    store = dist.TCPStore("127.0.0.1", port + 1, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=20))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        guard = pdist.StepGuard(store, rank, world, timeout_s=2.0)
+        bucket = pdist.FilterGradientBucket([8], "cpu")
+
+        def backward():
+            if rank == 1 and mode == "raise":
+                raise ValueError("injected")
+            bucket.view(0).fill_(1.0)
+
+        # step 0 goes through on both ranks
+        guard.guarded_all_reduce(bucket, 0, lambda: bucket.view(0).fill_(float(rank + 1)))
+        step0_ok = bucket.view(0).tolist() == [3.0] * 8
+        if rank == 1 and mode == "silent":
+            out[rank] = ("left", step0_ok)
+            return
+        try:
+            guard.guarded_all_reduce(bucket, 1, backward)
+            out[rank] = ("no error", step0_ok)
+        except pdist.RankFailure as e:
+            out[rank] = ("RankFailure", step0_ok, str(e))
+        except ValueError:
+            out[rank] = ("raised", step0_ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["raise", "silent"])
+def test_a_failed_rank_is_noticed_before_the_collective(mode):
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    port = 31000 + (os.getpid() % 2000) + (0 if mode == "raise" else 7)
+    mp.spawn(_failing_worker, args=(world, port, out, mode), nprocs=world, join=True)
+    res = dict(out)
+    assert res[0][0] == "RankFailure" and res[0][1], res
+    assert res[1][0] == ("raised" if mode == "raise" else "left") and res[1][1], res
+    assert ("rank 1" in res[0][2]), res
