@@ -24,6 +24,7 @@ Other modes (they print their own tables, not the JSON line):
     python bench.py --layer N H W C K WINDOW STRIDE [--dtype f16|bf16|f32] [--reps R]   one conv layer
     python bench.py --hbm-table          every HBM-bound operator, one line each
     python bench.py --layers             the JSON line, then per-layer times of the forward stack
+    python bench.py --workload vgg16 | mobilenet | layer0     the other benchmark configurations
 """
 import argparse
 import json
@@ -383,6 +384,66 @@ def run_layer_mode(args):
     print("device error record", pd.device_error_record())
 
 
+def run_other_workload(args):
+    """The other benchmark configurations, one JSON line each (not the headline): --workload vgg16 is the
+    VGG-16 conv stack in fp32 (3xTF32), batch 64, forward and training step; --workload mobilenet is the
+    dense convolutions of MobileNet-v2 in fp16, batch 128 (its depthwise layers are in the `hbm` block of the
+    default run); --workload layer0 is the single 3x3 56x56x256->256 fp32 layer at batch 1."""
+    import torch
+    import portdnn_b200 as pd
+    from portdnn_b200 import workloads
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    peaks = load_peaks()
+    out = {"workload": args.workload, "unit": UNIT, "steps": args.steps}
+    if args.workload == "layer0":
+        p = pd.conv_params(1, 56, 56, 256, 256, 3, 1)
+        g = torch.Generator(device=device).manual_seed(0)
+        x = (torch.rand(56 * 56 * 256, device=device, generator=g) * 2 - 1)
+        w = (torch.rand(9 * 256 * 256, device=device, generator=g) * 2 - 1) * (1.0 / 2304) ** 0.5
+        y = torch.empty(56 * 56 * 256, device=device)
+        flops = 2 * 56 * 56 * 9 * 256 * 256
+        for algo, name in ((pd.ALGO_IM2COL, "implicit_gemm_3xtf32"), (pd.ALGO_WINOGRAD, "winograd_f2x2_unfused")):
+            _, rec = pd.conv2d_workspace_size(pd.FORWARD, pd.F32, p, algo)
+            ws = torch.empty(max(rec, 1), device=device)
+            fn = lambda: pd.conv2d(pd.FORWARD, x, w, p, algorithm=algo, out=y, workspace=ws)
+            for _ in range(5):
+                fn()
+            ms = timed(torch, fn, max(args.steps, 50))
+            out[name] = {"us": round(ms * 1e3, 2), "value": round(flops / (ms * 1e-3) / 1e12, 2)}
+        print(json.dumps(out))
+        return
+    if args.workload == "vgg16":
+        layers, dtype, batch = workloads.vgg16(64), torch.float32, 64
+    else:
+        layers, dtype, batch = workloads.mobilenet_v2_convs(128), torch.float16, 128
+    net = workloads.ConvStackRunner(layers, device, seed=7, dtype=dtype)
+    for _ in range(3):
+        net.forward()
+    step = capture_graph(torch, net.forward).replay
+    for _ in range(3):
+        step()
+    ms = timed(torch, step, args.steps)
+    out.update({"dtype": "f32 (3xTF32)" if dtype == torch.float32 else "f16", "batch": batch,
+                "forward": {"ms_per_step": round(ms, 4), "value": round(net.flops_forward / (ms * 1e-3) / 1e12, 2),
+                            "flops_per_step": net.flops_forward}})
+    if args.workload == "vgg16":
+        del net
+        tnet = workloads.ConvStackRunner(layers, device, seed=7, dtype=dtype, training=True)
+        for _ in range(2):
+            tnet.forward()
+            tnet.backward()
+        ms_t = timed(torch, lambda: (tnet.forward(), tnet.backward()), max(3, args.steps // 4))
+        out["train"] = {"ms_per_step": round(ms_t, 4), "value": round(tnet.flops_train / (ms_t * 1e-3) / 1e12, 2),
+                        "flops_per_step": tnet.flops_train}
+        # fp32 is credited at direct FLOPs against a third of the TF32 peak (half the bf16 peak)
+        out["frac_of_tf32_peak_over_3"] = round(out["forward"]["value"] / (peaks["tflops_burst"] / 2 / 3), 3)
+    err = pd.device_error_record()
+    if err[0] != 0:
+        raise SystemExit("bench.py: tensor-core kernel reported %s" % err)
+    print(json.dumps(out))
+
+
 # ------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------
@@ -404,6 +465,7 @@ def run_gpu(args):
     if world > 1:
         dist.barrier()
     import portdnn_b200 as pd
+    from portdnn_b200 import dist as pdist
     from portdnn_b200 import workloads
     peaks = load_peaks()
 
@@ -554,6 +616,8 @@ def run_gpu(args):
         tnet.backward()
         train_launches = pd.launch_count() - l0
         side = torch.cuda.Stream()
+        # the gradient sum goes through the library's own C-ABI collective (pdnn_allreduce_filter_grads)
+        comm = pdist.GradientComm(rank, world) if world > 1 else None
         if args.no_graph:
             fwd_step, seg_steps = tnet.forward, [(lambda s=s: tnet.backward_segment(s)) for s in tnet.segments]
         else:
@@ -579,7 +643,7 @@ def run_gpu(args):
                     ready[k].record(stream)
                     side.wait_event(ready[k])
                     with torch.cuda.stream(side):
-                        tnet.bucket.all_reduce(span=seg["bucket"])
+                        tnet.bucket.all_reduce(span=seg["bucket"], comm=comm)
             stream.wait_stream(side)
 
         tsteps = max(5, min(args.steps, 20))
@@ -594,8 +658,9 @@ def run_gpu(args):
         train = {"ms_per_step": round(ms_train, 4), "value": round(tnet.flops_train * world / (ms_train * 1e-3) / 1e12, 2),
                  "unit": UNIT, "steps": tsteps, "launches": int(train_launches),
                  "allreduce_ms": round(max(ms_train - ms_train_local, 0.0), 4),
-                 "allreduce": "fp32 filter gradients, %d floats, one NCCL all-reduce per stage (5 per step) on a second "
-                              "stream, started when that stage's filter backprop is done" % tnet.bucket.total,
+                 "allreduce": "fp32 filter gradients, %d floats, one pdnn_allreduce_filter_grads (ncclAllReduce) per stage "
+                              "(5 per step) on a second stream, started when that stage's filter backprop is done"
+                              % tnet.bucket.total,
                  "flops_per_step_per_gpu": tnet.flops_train,
                  "frac_of_sustained_peak_per_gpu": round(tnet.flops_train / (ms_train * 1e-3) / 1e12 / peaks["tflops_sustained"], 4)}
 
@@ -679,8 +744,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="forward", choices=["forward", "train"],
-                    help="forward: the headline conv stack; train: report the training step as the headline value")
+    ap.add_argument("--workload", default="forward", choices=["forward", "train", "vgg16", "mobilenet", "layer0"],
+                    help="forward: the headline conv stack; train: report the training step as the headline value; "
+                         "vgg16 / mobilenet / layer0: the other benchmark configurations, one line each")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying a CUDA graph")
     ap.add_argument("--quick", action="store_true", help="only the headline measurement (no sustained / train / hbm / parity / cpu legs)")
     ap.add_argument("--layers", action="store_true", help="after the JSON line, print per-layer times of the forward stack")
@@ -695,6 +761,8 @@ def main():
         run_reference(args)
     elif args.layer:
         run_layer_mode(args)
+    elif args.workload in ("vgg16", "mobilenet", "layer0"):
+        run_other_workload(args)
     else:
         run_gpu(args)
 

@@ -273,6 +273,19 @@ int pdnn_transpose(int elem_bytes, const void* input, void* output, const int* d
 int pdnn_matmul(int dtype, int transpose_lhs, int transpose_rhs, const void* lhs, const void* rhs, void* output,
                 int batches, int m, int k, int n, float beta, void* stream);
 
+/* The collective of the batch-sharded path; no counterpart in the reference, which is single-device.
+ * Each rank's filter-backprop pass leaves fp32 gradients for its shard of the batch in one contiguous
+ * buffer; pdnn_allreduce_filter_grads sums `count` floats of it over the ranks in place with
+ * ncclAllReduce on `stream` (any sub-range of the buffer may be reduced on its own, so a caller can
+ * start a stage's reduction while the backward pass continues on another stream).
+ * pdnn_comm_unique_id fills 128 bytes on rank 0; every rank passes the same bytes to pdnn_comm_init
+ * with its CUDA device current.  NCCL is looked up in the process at the first call
+ * (PDNN_ALLOCATION_PROBLEM if libnccl.so.2 cannot be found). */
+int pdnn_comm_unique_id(void* id128);
+int pdnn_comm_init(void** comm, const void* id128, int world_size, int rank);
+int pdnn_allreduce_filter_grads(void* comm, float* gradients, size_t count, void* stream);
+int pdnn_comm_destroy(void* comm);
+
 /* Reads (and optionally clears) the 4-word record the tensor-core kernels fill when one of
  * their bounded waits gives up instead of spinning: word 0 is 0 when nothing went wrong, else
  * 1 (wait timed out), word 1 the CTA, word 2 the wait site, word 3 the phase parity.

@@ -15,7 +15,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libportdnn_b200.so")
 SOURCES = ["c_api.cu", "hbm_kernels.cu", "direct_conv.cu", "tc_gemm.cu", "winograd.cu", "norm_kernels.cu",
-           "layout_kernels.cu"]
+           "layout_kernels.cu", "collective.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
 
@@ -64,7 +64,7 @@ def build(force=False, verbose=False):
     with ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 1))) as pool:
         list(pool.map(lambda c: _run(c, verbose), jobs))
     objs = [os.path.join(OBJ, s[:-3] + ".o") for s in SOURCES]
-    _run([nvcc, "-shared", "-cudart", "shared", "-Xcompiler", "-fPIC"] + objs + ["-o", LIB], verbose)
+    _run([nvcc, "-shared", "-cudart", "shared", "-Xcompiler", "-fPIC"] + objs + ["-ldl", "-o", LIB], verbose)
     return LIB
 
 

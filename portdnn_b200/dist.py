@@ -49,14 +49,60 @@ class FilterGradientBucket:
         """(start, stop) of the contiguous slice that holds the gradients of layers first..last."""
         return self.offsets[first], self.offsets[last] + (self.sizes[last] + 63) // 64 * 64
 
-    def all_reduce(self, group=None, async_op=False, span=None):
+    def all_reduce(self, group=None, async_op=False, span=None, comm=None):
         """Sum over ranks of the whole buffer, or of one span of it (no-op without an initialised process
-        group or with one rank)."""
+        group or with one rank).  comm: a GradientComm, to go through the library's own C-ABI collective
+        instead of torch.distributed."""
+        if comm is not None:
+            return comm.all_reduce(self.buffer if span is None else self.buffer[span[0]:span[1]])
         import torch.distributed as dist
         if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
             return None
         t = self.buffer if span is None else self.buffer[span[0]:span[1]]
         return dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+
+
+class GradientComm:
+    """The library's own communicator for the filter-gradient all-reduce (pdnn_comm_* /
+    pdnn_allreduce_filter_grads): NCCL reached through the C ABI rather than through torch.distributed.
+    `exchange(id_bytes_or_None) -> id_bytes` hands rank 0's 128-byte id to every rank: by default it is
+    a torch.distributed broadcast over the initialised process group."""
+
+    def __init__(self, rank, world_size, exchange=None):
+        import ctypes
+        from . import api
+        self._api, self._ct, self.world = api, ctypes, world_size
+        L = api.lib()
+        buf = (ctypes.c_char * 128)()
+        if rank == 0:
+            api._check(L.pdnn_comm_unique_id(buf))
+        ident = (exchange or self._broadcast)(bytes(buf) if rank == 0 else None)
+        self._comm = ctypes.c_void_p()
+        api._check(L.pdnn_comm_init(ctypes.byref(self._comm), ident, world_size, rank))
+
+    @staticmethod
+    def _broadcast(ident):
+        import torch
+        import torch.distributed as dist
+        t = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if ident is not None:
+            t.copy_(torch.frombuffer(bytearray(ident), dtype=torch.uint8))
+        dist.broadcast(t, src=0)
+        return bytes(t.cpu().numpy().tobytes())
+
+    def all_reduce(self, tensor):
+        """Sums a contiguous fp32 CUDA tensor over the ranks in place, on the current stream."""
+        import torch
+        if tensor.dtype != torch.float32 or not tensor.is_cuda or not tensor.is_contiguous():
+            raise ValueError("the gradient buffer must be a contiguous fp32 CUDA tensor")
+        self._api._check(self._api.lib().pdnn_allreduce_filter_grads(
+            self._comm, self._ct.c_void_p(tensor.data_ptr()), self._ct.c_size_t(tensor.numel()),
+            self._ct.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def destroy(self):
+        if self._comm:
+            self._api._check(self._api.lib().pdnn_comm_destroy(self._comm))
+            self._comm = None
 
 
 def max_over_ranks(value, device=None, group=None):

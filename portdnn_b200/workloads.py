@@ -91,6 +91,27 @@ def mobilenet_v2_depthwise(batch):
     return [api.depthwise_params(batch, s, s, c, 1, 3, st, True) for (s, c, st) in shapes]
 
 
+def mobilenet_v2_convs(batch):
+    """The dense convolutions of MobileNet-v2 at 224x224: the 3x3/2 stem and, per inverted-residual block,
+    the 1x1 expansion (ReLU6; absent when the expansion factor is 1) and the linear 1x1 projection.
+    Schedule (t, c, n, s) = (1,16,1,1)(6,24,2,2)(6,32,3,2)(6,64,4,2)(6,96,3,1)(6,160,3,2)(6,320,1,1).  The
+    depthwise layers between them are mobilenet_v2_depthwise(); each layer here reads one buffer and
+    writes the other, which is all a timing run needs."""
+    layers = [ConvLayer("stem", api.conv_params(batch, 224, 224, 3, 32, 3, 2), "input", "a", api.ACT_RELU6)]
+    size, cin, k = 112, 32, 0
+    for t, c, n, s in ((1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 3, 2), (6, 64, 4, 2), (6, 96, 3, 1), (6, 160, 3, 2), (6, 320, 1, 1)):
+        for i in range(n):
+            stride = s if i == 0 else 1
+            k += 1
+            hidden = cin * t
+            if t != 1:
+                layers.append(ConvLayer("b%d_expand" % k, api.conv_params(batch, size, size, cin, hidden, 1, 1), "a", "b", api.ACT_RELU6))
+            size //= stride  # the depthwise layer in between changes the resolution
+            layers.append(ConvLayer("b%d_project" % k, api.conv_params(batch, size, size, hidden, c, 1, 1), "b", "a", api.ACT_NONE))
+            cin = c
+    return layers
+
+
 def conv_flops(layers):
     return sum(l.flops for l in layers if isinstance(l, ConvLayer))
 
@@ -123,7 +144,7 @@ class ConvStackRunner:
         current, self.src_idx, sizes = {layers[0].src: -1}, [], []
         for i, l in enumerate(layers):
             p = l.params
-            self.src_idx.append(current[l.src])
+            self.src_idx.append(current.get(l.src, -2))  # -2: a buffer nobody has written (timing-only tables)
             current[l.dst] = i
             if isinstance(l, ConvLayer):
                 fan_in = p.window_rows * p.window_cols * p.channels
@@ -181,7 +202,13 @@ class ConvStackRunner:
 
     def _in(self, i):
         j = self.src_idx[i]
-        return self.input if j < 0 else self._out(j)
+        p = self.layers[i].params
+        n_in = p.batch * p.in_rows * p.in_cols * p.channels
+        if j == -2:  # read the named buffer as it is
+            return self.buffers[self.layers[i].src][:n_in]
+        t = self.input if j < 0 else self._out(j)
+        # timing-only tables leave out layers in between (a strided depthwise layer): read what fits
+        return t if t.numel() == n_in else t[:n_in]
 
     def run_layer(self, i):
         l, p = self.layers[i], self.layers[i].params
