@@ -1829,6 +1829,12 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     }
   } else {
     g.bn = pick_bn(row_tiles, p.features, hwcf ? epr : 16, dtype == PDNN_F32 ? 128 : 256, sms, ksteps_all);
+    // A single tap with a long reduction into exactly 256 features: one 256-column tile per row tile
+    // reads the input once instead of twice and runs as one double-buffered pipeline (measured 12%
+    // faster than two 128-column pipelines on 14x14x1024 -> 256).
+    if (dtype != PDNN_F32 && !halo && PDNN_KNOB("PDNN_BN", 0) == 0 && p.window_rows * p.window_cols == 1 &&
+        ksteps_all >= 16 && p.features == 256 && row_tiles >= 2 * sms)
+      g.bn = 256;
   }
   g.n_tiles = ceil_div(p.features, g.bn);
   set_operand_layout(g, dtype, hwcf ? 1 : 0);
