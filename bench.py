@@ -367,14 +367,30 @@ def run_layer_mode(args):
     b = torch.zeros(k, device="cuda").to(dt)
     y = torch.empty(n * p.out_rows * p.out_cols * k, device="cuda", dtype=dt)
     flops = 2 * n * p.out_rows * p.out_cols * win * win * c * k
+    ws = None
+    if args.algorithm not in (pd.ALGO_TILED, pd.ALGO_IM2COL):
+        ws = torch.empty(max(pd.conv2d_workspace_size(pd.FORWARD, {"f16": 1, "bf16": 2, "f32": 0}[args.dtype], p,
+                                                      args.algorithm)[1], 1), device="cuda", dtype=dt)
+    if args.conv_pass == "forward":
+        run = lambda: pd.conv2d(pd.FORWARD, x, wt, p, algorithm=args.algorithm, out=y, bias=b, activation=pd.ACT_RELU,
+                                workspace=ws)
+    elif args.conv_pass == "input_backprop":  # with the ReLU-gradient mask of the producing layer fused in
+        dx = torch.empty_like(x)
+        mask = torch.relu(x) if dt != torch.float32 else None
+        run = lambda: pd.conv2d(pd.INPUT_BACKPROP, y, wt, p, algorithm=args.algorithm, out=dx, workspace=ws,
+                                relu_forward_output=mask)
+        y.copy_(torch.randn(y.numel(), device="cuda").to(dt))
+    else:  # filter backprop into fp32 gradients, as the training step asks for them
+        dw = torch.empty(wt.numel(), device="cuda", dtype=torch.float32)
+        y.copy_(torch.randn(y.numel(), device="cuda").to(dt))
+        f32_out = dt != torch.float32
+        run = lambda: pd.conv2d(pd.FILTER_BACKPROP, x, y, p, algorithm=args.algorithm, out=dw if f32_out else None,
+                                workspace=ws, output_f32=f32_out)
     evs = []
     for _ in range(args.reps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        pd.conv2d(pd.FORWARD, x, wt, p, algorithm=args.algorithm, out=y, bias=b, activation=pd.ACT_RELU,
-                  workspace=None if args.algorithm in (pd.ALGO_TILED, pd.ALGO_IM2COL) else
-                  torch.empty(max(pd.conv2d_workspace_size(pd.FORWARD, {"f16": 1, "bf16": 2, "f32": 0}[args.dtype], p,
-                                                           args.algorithm)[1], 1), device="cuda", dtype=dt))
+        run()
         e1.record()
         evs.append((e0, e1))
     torch.cuda.synchronize()
@@ -753,6 +769,8 @@ def main():
     ap.add_argument("--hbm-table", action="store_true", help="print every HBM-bound operator's bandwidth and exit")
     ap.add_argument("--layer", type=int, nargs=7, metavar=("N", "H", "W", "C", "K", "WINDOW", "STRIDE"),
                     help="time one forward convolution layer (fused bias + ReLU) and exit")
+    ap.add_argument("--pass", dest="conv_pass", default="forward", choices=["forward", "input_backprop", "filter_backprop"],
+                    help="which convolution pass --layer runs")
     ap.add_argument("--dtype", default="f16", choices=["f16", "bf16", "f32"])
     ap.add_argument("--algorithm", type=int, default=3, help="PdnnAlgorithm for --layer (3 im2col tag = implicit GEMM, 4 Winograd)")
     ap.add_argument("--reps", type=int, default=3)

@@ -147,10 +147,15 @@ int pdnn_conv2d_fused(int dtype, const void* input, const void* filter, void* ou
  *    dx[i] = y_prev[i] > 0 ? dx[i] : 0, i.e. the gradient with respect to that layer's
  *    pre-activation, which is what its own two backprop passes consume.
  *  - output_f32 (FilterBackprop only): dW is written as fp32 even for fp16 / bf16 tensors, so that
- *    it can land directly in the fp32 buffer a gradient all-reduce works on. */
+ *    it can land directly in the fp32 buffer a gradient all-reduce works on.
+ *  - accumulate (InputBackprop only): dx already holds the gradient that arrived through another
+ *    reader of the tensor (a shortcut branch); this call adds its own to it, dx += conv_backprop(dy, w),
+ *    and the mask of relu_forward_output, when given, applies to the sum - the reference chain of
+ *    an input backprop into a temporary, binaryop::launch<Add> and the ReLU gradient. */
 typedef struct PdnnBackpropFusion {
   const void* relu_forward_output;
   int output_f32;
+  int accumulate;
 } PdnnBackpropFusion;
 
 /* As pdnn_conv2d for PDNN_INPUT_BACKPROP / PDNN_FILTER_BACKPROP, with the fused forms described at

@@ -71,7 +71,7 @@ class BatchNormParams(ctypes.Structure):
 
 
 class _BackpropFusion(ctypes.Structure):
-    _fields_ = [("relu_forward_output", ctypes.c_void_p), ("output_f32", ctypes.c_int)]
+    _fields_ = [("relu_forward_output", ctypes.c_void_p), ("output_f32", ctypes.c_int), ("accumulate", ctypes.c_int)]
 
 
 class _Epilogue(ctypes.Structure):
@@ -188,21 +188,24 @@ def conv2d_workspace_size(pass_, dtype, params, algorithm):
 
 
 def conv2d(pass_, inp, fil, params, algorithm=ALGO_IM2COL, out=None, workspace=None, bias=None, activation=ACT_NONE,
-           alpha=1.0, beta=0.0, relu_forward_output=None, output_f32=False):
+           alpha=1.0, beta=0.0, relu_forward_output=None, output_f32=False, accumulate=False):
     """conv2d::launch<T, ConvType>(input, filter, output, params, selector, backend, workspace, size)
     (include/portdnn/conv2d/launch.h:59-72) with the selector's answer passed as ``algorithm``.
     Slots: Forward (x, w) -> y; InputBackprop (dy, w) -> dx; FilterBackprop (x, dy) -> dW.
-    bias / activation / alpha / beta select the fused forward epilogue; relu_forward_output (InputBackprop)
-    and output_f32 (FilterBackprop) the fused backprop forms of PdnnBackpropFusion."""
+    bias / activation / alpha / beta select the fused forward epilogue; relu_forward_output and accumulate
+    (InputBackprop: dx += ..., then the mask) and output_f32 (FilterBackprop) the fused backprop forms of
+    PdnnBackpropFusion."""
     torch = _torch()
     _require_cuda(inp, fil, out, workspace, bias)
     n_in, n_fil, n_out = conv_sizes(pass_, params)
     if inp.numel() != n_in or fil.numel() != n_fil:
         raise ValueError("tensor sizes do not match the parameters: %d/%d, %d/%d" % (inp.numel(), n_in, fil.numel(), n_fil))
-    backprop_fused = relu_forward_output is not None or output_f32
-    if backprop_fused and (pass_ == FORWARD or (relu_forward_output is not None and pass_ != INPUT_BACKPROP) or
+    backprop_fused = relu_forward_output is not None or output_f32 or accumulate
+    if backprop_fused and (pass_ == FORWARD or ((relu_forward_output is not None or accumulate) and pass_ != INPUT_BACKPROP) or
                            (output_f32 and pass_ != FILTER_BACKPROP)):
-        raise ValueError("relu_forward_output belongs to the input backprop, output_f32 to the filter backprop")
+        raise ValueError("relu_forward_output / accumulate belong to the input backprop, output_f32 to the filter backprop")
+    if accumulate and out is None:
+        raise ValueError("accumulate needs the tensor to add to as out")
     _require_cuda(relu_forward_output)
     if out is None:
         out = torch.empty(n_out, dtype=torch.float32 if output_f32 else inp.dtype, device=inp.device)
@@ -212,7 +215,8 @@ def conv2d(pass_, inp, fil, params, algorithm=ALGO_IM2COL, out=None, workspace=N
     if backprop_fused:
         if relu_forward_output is not None and relu_forward_output.numel() != n_out:
             raise ValueError("relu_forward_output must have the shape of the input gradient")
-        fus = _BackpropFusion(relu_forward_output.data_ptr() if relu_forward_output is not None else None, int(output_f32))
+        fus = _BackpropFusion(relu_forward_output.data_ptr() if relu_forward_output is not None else None, int(output_f32),
+                              int(accumulate))
         _check(lib().pdnn_conv2d_backprop_fused(pass_, _dtype_code(inp), _ptr(inp), _ptr(fil), _ptr(out),
                                                 ctypes.byref(params), algorithm, ctypes.byref(fus), _ptr(workspace),
                                                 ctypes.c_size_t(ws_elems), _stream()))

@@ -141,10 +141,22 @@ int run_direct_backprop(int pass, int dtype, const void* in, const void* fil, vo
     cudaFreeAsync(tmp, s);
     return st;
   }
-  const int st = launch_direct_conv(pass, dtype, in, fil, out, p, nullptr, s);
+  const size_t n_dx = (size_t)p.batch * p.in_rows * p.in_cols * p.channels;
+  int st;
+  if (pass == PDNN_INPUT_BACKPROP && fusion != nullptr && fusion->accumulate) {
+    void* tmp = nullptr;
+    if (cudaMallocAsync(&tmp, n_dx * es, s) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(PDNN_ALLOCATION_PROBLEM, "conv2d: cannot allocate %zu bytes for the input gradient", n_dx * es);
+    }
+    st = launch_direct_conv(pass, dtype, in, fil, tmp, p, nullptr, s);
+    if (st == PDNN_OK) st = launch_scale_blend(dtype, tmp, 1.f, out, 1.f, out, n_dx, s);
+    cudaFreeAsync(tmp, s);
+  } else {
+    st = launch_direct_conv(pass, dtype, in, fil, out, p, nullptr, s);
+  }
   if (st != PDNN_OK || pass != PDNN_INPUT_BACKPROP || fusion == nullptr || fusion->relu_forward_output == nullptr) return st;
-  return launch_pointwise_grad(PDNN_ACT_RELU, dtype, fusion->relu_forward_output, out, out,
-                               (size_t)p.batch * p.in_rows * p.in_cols * p.channels, s);
+  return launch_pointwise_grad(PDNN_ACT_RELU, dtype, fusion->relu_forward_output, out, out, n_dx, s);
 }
 
 int dispatch_conv(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams* p, int algorithm,
@@ -162,8 +174,8 @@ int run_conv(int pass, int dtype, const void* in, const void* fil, void* out, co
     // NCHW tensors with an FCHW filter (the only pairing validate_conv lets through): the NHWC
     // kernels between two transposes.  The reference's NCHW path is its direct kernel
     // (src/conv2d/direct/kernels_nchw.h:28,157,300), which computes the same sums.
-    if (fusion != nullptr && fusion->relu_forward_output != nullptr)
-      return fail(PDNN_INVALID_PARAMETER, "conv2d: the fused ReLU-gradient form needs NHWC tensors");
+    if (fusion != nullptr && (fusion->relu_forward_output != nullptr || fusion->accumulate))
+      return fail(PDNN_INVALID_PARAMETER, "conv2d: the fused input-backprop forms need NHWC tensors");
     const bool read_out = epi != nullptr && epi->beta != 0.f;
     return conv2d_nchw(pass, dtype, in, fil, out, *p, read_out, s,
                        [&](const void* a, const void* b, void* c, const PdnnConv2DParams& q) {
@@ -208,6 +220,10 @@ int pdnn_conv2d_backprop_fused(int pass, int dtype, const void* input, const voi
                                void* workspace, size_t workspace_elems, void* stream) {
   if (pass != PDNN_INPUT_BACKPROP && pass != PDNN_FILTER_BACKPROP)
     return fail(PDNN_INVALID_PARAMETER, "conv2d: the fused backprop forms exist for the two backprop passes only");
+  if (fusion != nullptr && pass == PDNN_FILTER_BACKPROP && (fusion->accumulate || fusion->relu_forward_output != nullptr))
+    return fail(PDNN_INVALID_PARAMETER, "conv2d: relu_forward_output and accumulate belong to the input backprop");
+  if (fusion != nullptr && pass == PDNN_INPUT_BACKPROP && fusion->output_f32)
+    return fail(PDNN_INVALID_PARAMETER, "conv2d: output_f32 belongs to the filter backprop");
   return run_conv(pass, dtype, input, filter, output, params, algorithm, nullptr, fusion, workspace, workspace_elems,
                   stream);
 }

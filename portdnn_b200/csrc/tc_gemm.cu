@@ -140,6 +140,7 @@ struct alignas(64) GemmArgs {
   // laid out exactly like `out` (stride_w / stride_h / stride_n).  Where it is not positive the
   // result is replaced by zero: pointwise::launch<Relu, Gradient> applied on the way out.
   const void* relu_mask;
+  int accumulate;  // packed 16-bit epilogues, no bias: the block already in the output is added (before the mask)
   int mask_smem_bytes;  // 256 bytes per epilogue warp for the sign bits of a 32-row block
   // Time limit of one barrier wait; a wait that lasts longer means a lost arrival, and the CTA
   // gives up (see umma::mbar_wait).
@@ -397,6 +398,11 @@ __device__ __forceinline__ P2 bits_pair(uint32_t v) {
 // loads of a column block are batched ahead of the wait for the accumulators, and their latencies
 // overlap instead of each load sitting directly in front of its first use (a lone warp stalls on
 // every one of them: eight round trips cost more than the arithmetic of the block).
+__device__ __forceinline__ uint4 ld_global_v4(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+  return v;
+}
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -420,8 +426,8 @@ __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bo
     for (int i = 0; i < 4; ++i) {
       P2 v = zero ? zero2
                   : Pair<OutT>::pack(__uint_as_float(acc[g * 8 + 2 * i]), __uint_as_float(acc[g * 8 + 2 * i + 1]));
-      if (!MASK) {  // the gradient form has neither bias nor activation
-        if (has_bias) v = __hadd2(v, bits_pair<P2>(bw[i]));
+      if (has_bias) v = __hadd2(v, bits_pair<P2>(bw[i]));  // the bias, or what the output held before
+      if (!MASK) {  // the gradient form has no activation
         if (act != PDNN_ACT_NONE) v = __hmax2(v, zero2);
         if (act == PDNN_ACT_RELU6) v = __hmin2(v, six2);
       }
@@ -506,10 +512,23 @@ __device__ __forceinline__ void epilogue_tile_tma_fast(const GemmArgs& a, const 
     }
     // the block's bias, all eight loads in flight at once (and before the waits below)
     uint4 bv[8];
-    const bool has_bias = !MASK && bias_s != 0u;
+    const bool add_prev = a.accumulate != 0, has_bias = add_prev || (!MASK && bias_s != 0u);
+    if (add_prev) {
+      // accumulating form: the lane's own row of the block that is in the output already (128 bytes)
+      const int sh_w = __ffs(a.etw) - 1, sh_h = __ffs(a.eth) - 1, row = q32 + lane;
+      const int w = t.w0 + (row & (a.etw - 1)), h = t.h0 + ((row >> sh_w) & (a.eth - 1)), n = t.n0 + (row >> (sh_w + sh_h));
+      const uint16_t* prev = nullptr;
+      if (w < a.ext_w && h < a.ext_h && n < a.ext_n)
+        prev = static_cast<const uint16_t*>(a.out) + (long long)n * a.stride_n + (long long)h * a.stride_h +
+               (long long)w * a.stride_w + t.nf0 + c0;
 #pragma unroll
-    for (int g = 0; g < 8; ++g)
-      bv[g] = has_bias ? ld_shared_v4(bias_s + (uint32_t)(t.nf0 + c0 + g * 8) * 2u) : make_uint4(0u, 0u, 0u, 0u);
+      for (int g = 0; g < 8; ++g)
+        bv[g] = (prev != nullptr && t.nf0 + c0 + g * 8 < a.ext_cols) ? ld_global_v4(prev + g * 8) : make_uint4(0u, 0u, 0u, 0u);
+    } else {
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+        bv[g] = has_bias ? ld_shared_v4(bias_s + (uint32_t)(t.nf0 + c0 + g * 8) * 2u) : make_uint4(0u, 0u, 0u, 0u);
+    }
     uint2 keep = make_uint2(0u, 0u);
     if (MASK) {
       // this block's loads were issued one block ago (or before the accumulator wait); turn them
@@ -1899,7 +1918,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
 // of; dx is zeroed wherever it is not positive (in the epilogue where the fast epilogue runs, else
 // by a pointwise pass afterwards).
 int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, const PdnnConv2DParams& p,
-                        const void* relu_mask, cudaStream_t s, bool try_halo = true) {
+                        const void* relu_mask, bool accumulate, cudaStream_t s, bool try_halo = true) {
   bool mask_pending = false;  // some parity class could not apply the mask in its epilogue
   const size_t es = dtype_size(dtype);
   const int sms = device_sm_count();
@@ -2042,8 +2061,17 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
         const uint64_t os[3] = {(uint64_t)p.stride_cols * p.channels * es,
                                 (uint64_t)p.stride_rows * p.in_cols * p.channels * es,
                                 (uint64_t)p.in_rows * p.in_cols * p.channels * es};
-        if (!setup_store(g, dtype, od, os)) {
-          if (g.halo || g.pair) return conv_input_backprop(dtype, dy, w, dx, p, relu_mask, s, false);  // plan again without the halo / pairing
+        // Accumulating form (dx += ...): inside the packed 16-bit epilogue when that runs, else through
+        // the general epilogue's beta.
+        g.accumulate = accumulate ? 1 : 0;
+        bool planned = setup_store(g, dtype, od, os);
+        if (planned && accumulate && !g.epi_fast) {
+          g.accumulate = 0;
+          g.beta = 1.f;
+          planned = setup_store(g, dtype, od, os);
+        }
+        if (!planned) {
+          if (g.halo || g.pair) return conv_input_backprop(dtype, dy, w, dx, p, relu_mask, accumulate, s, false);  // plan again without the halo / pairing
           return PDNN_INVALID_PARAMETER;
         }
       }
@@ -2445,7 +2473,8 @@ int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, c
         return st == -1 ? kNeedsDirect : st;
       }
       return conv_forward(dtype, in, fil, out, p, epi, s);
-    case PDNN_INPUT_BACKPROP: return conv_input_backprop(dtype, in, fil, out, p, relu_mask, s);
+    case PDNN_INPUT_BACKPROP:
+      return conv_input_backprop(dtype, in, fil, out, p, relu_mask, fusion != nullptr && fusion->accumulate != 0, s);
     case PDNN_FILTER_BACKPROP:
       if (small_c_applicable(dtype, p)) {
         const int st = conv_filter_backprop_small_c(dtype, in, fil, out, p, out_f32, ws, ws_elems, s);

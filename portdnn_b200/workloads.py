@@ -124,8 +124,12 @@ class ConvStackRunner:
     over ranks, stage by stage or with a single all-reduce).  The reference has no trainer; its samples chain layers the
     same way on the host (tools/network.h)."""
 
-    def __init__(self, layers, device, seed, training=False, dtype=None, chunk=None, chunk_layers=0):
-        """chunk / chunk_layers (forward only): the first ``chunk_layers`` layers run depth-first over
+    def __init__(self, layers, device, seed, training=False, dtype=None, chunk=None, chunk_layers=0,
+                 fuse_accumulate=True):
+        """fuse_accumulate (training): a gradient with several contributions is summed (and masked) inside the
+        input backprops that bring them (PdnnBackpropFusion.accumulate); False keeps the unfused chain of an
+        input backprop into a temporary, an add and a ReLU-gradient pass.
+        chunk / chunk_layers (forward only): the first ``chunk_layers`` layers run depth-first over
         slices of ``chunk`` images - all those layers on images 0..chunk-1, then on the next slice, and so
         on - with their intermediate activations in slice-sized buffers that every slice reuses, so that a
         layer's output is still in the L2 cache when the next layer reads it.  Results are identical to
@@ -133,6 +137,7 @@ class ConvStackRunner:
         import torch
         from . import dist as pdist
         self.torch, self.layers, self.training, self.device = torch, layers, training, device
+        self.fuse_accumulate = fuse_accumulate
         self.dtype = dtype or torch.float16
         self.code = api.F16 if self.dtype == torch.float16 else api.BF16 if self.dtype == torch.bfloat16 else api.F32
         g = torch.Generator(device=device).manual_seed(seed)
@@ -251,17 +256,19 @@ class ConvStackRunner:
 
     # ---- backward ------------------------------------------------------------------------------
     def _plan_backward(self):
-        """Which tensors get their ReLU-gradient mask applied inside the input backprop that produces
-        their gradient (one reader, a convolution's output, and nobody else needs the unmasked
-        gradient), and the segments of the backward pass: the layers of one stage, last stage first, each
-        with the slice of the gradient bucket it fills."""
+        """Which tensors get their ReLU-gradient mask applied inside the input backprop that completes
+        their gradient (a convolution's output whose unmasked gradient nobody else needs; with several
+        readers the last one to arrive adds to the others' sum and masks it), and the segments of the
+        backward pass: the layers of one stage, last stage first, each with the slice of the gradient
+        bucket it fills."""
         layers = self.layers
         readers = [0] * len(layers)
         for j in self.src_idx:
             if j >= 0:
                 readers[j] += 1
         blocks_with_shortcut = {l.name[:-5] for l in layers if l.name.endswith("_proj")}
-        self.fuse_mask = [isinstance(l, ConvLayer) and readers[i] == 1 and
+        self.readers = readers
+        self.fuse_mask = [isinstance(l, ConvLayer) and (readers[i] == 1 or (readers[i] > 1 and self.fuse_accumulate)) and
                           not (l.name.endswith("_1x1b") and l.name[:-5] in blocks_with_shortcut)
                           for i, l in enumerate(layers)]
         stage_of = lambda l: l.name[:2] if l.name[0] == "s" and l.name[1].isdigit() else "stem"
@@ -277,22 +284,23 @@ class ConvStackRunner:
 
     def _add_grad(self, j, producer):
         """Routes a gradient into tensor j: the first contribution is written in place, later ones
-        are accumulated."""
+        are accumulated.  producer(dst, accumulate) writes (or adds) its gradient into dst, or returns
+        False if it cannot add in place, in which case it is asked again for a temporary."""
         if self.grads[j] is None:
             self.grads[j] = self.torch.empty(self.sizes[j], dtype=self.dtype, device=self.device)
         if j not in self._fresh:
-            producer(self.grads[j])
+            producer(self.grads[j], False)
             self._fresh.add(j)
-        else:
+        elif producer(self.grads[j], True) is False:
             tmp = self.scratch2[:self.sizes[j]]
-            producer(tmp)
+            producer(tmp, False)
             api.scale_blend(tmp, 1.0, self.grads[j], 1.0, out=self.grads[j])
 
     def backward_begin(self):
         if not hasattr(self, "segments"):
             self._plan_backward()
             self.scratch2 = self.torch.empty_like(self.scratch)
-        self._fresh, self._masked, self._block_grad = set(), set(), {}
+        self._fresh, self._masked, self._block_grad, self._arrived = set(), set(), {}, {}
 
     def backward_segment(self, seg):
         """The backward pass of one segment: per convolution (last first) the ReLU gradient - unless the
@@ -322,16 +330,28 @@ class ConvStackRunner:
                            output_f32=self.dtype != self.torch.float32,
                            workspace=self.fbp_workspace if i in self.fbp_ws else None)
                 if j >= 0:
-                    mask = self.acts[j] if self.fuse_mask[j] else None
-                    self._add_grad(j, lambda dst: api.conv2d(api.INPUT_BACKPROP, g, self.weights[i], p,
-                                                             algorithm=api.ALGO_IM2COL, out=dst, relu_forward_output=mask))
+                    # The ReLU mask of tensor j goes into the input backprop that completes its gradient:
+                    # the only one, or the last of several, which then also adds to what the others left.
+                    self._arrived[j] = self._arrived.get(j, 0) + 1
+                    last_reader = self._arrived[j] == self.readers[j]
+                    mask = self.acts[j] if self.fuse_mask[j] and last_reader else None
+
+                    def ibp(dst, accumulate, g=g, i=i, p=p, mask=mask):
+                        if accumulate and not self.fuse_accumulate:
+                            return False
+                        api.conv2d(api.INPUT_BACKPROP, g, self.weights[i], p, algorithm=api.ALGO_IM2COL, out=dst,
+                                   relu_forward_output=mask if (accumulate or dst is self.grads[j]) else None,
+                                   accumulate=accumulate)
+
+                    self._add_grad(j, ibp)
                     if mask is not None:
                         self._masked.add(j)
             elif l.op == api.POOL_AVERAGE:
                 if j >= 0:
-                    self._add_grad(j, lambda dst: api.pooling(l.op, 1, dy, p, out=dst))
+                    self._add_grad(j, lambda dst, acc: False if acc else api.pooling(l.op, 1, dy, p, out=dst))
             elif j >= 0:
-                self._add_grad(j, lambda dst: api.pooling_max_grad(l.op, self._in(i), self.acts[i], dy, p, out=dst))
+                self._add_grad(j, lambda dst, acc: False if acc else
+                               api.pooling_max_grad(l.op, self._in(i), self.acts[i], dy, p, out=dst))
 
     def backward(self):
         self.backward_begin()

@@ -226,6 +226,33 @@ def test_fused_backprop_forms_against_oracle(orc, dtype, shape):
     assert rel_err(to_host(dw), orc.conv2d(orc.FILTER_BACKPROP, x, dy, po)) <= TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("masked", [True, False])
+@pytest.mark.parametrize("shape", BWD_SHAPES + [(2, 20, 20, 24, 40, 3, 2, True, None), (3, 9, 9, 5, 7, 3, 1, True, None),
+                                                (4, 28, 28, 128, 256, 1, 2, True, None), (2, 14, 14, 512, 256, 1, 1, True, None)])
+def test_accumulating_input_backprop_against_oracle(orc, dtype, masked, shape):
+    """PdnnBackpropFusion::accumulate: dx already holds the gradient from another reader of the tensor;
+    the call adds its own and (optionally) masks the sum, against the oracle chain input backprop ->
+    add -> pointwise Relu Gradient.  Pixels outside every parity class of a strided layer keep
+    (masked) what was there."""
+    n, h, w, c, k, win, st, same, pad = shape
+    p, po, x, wt, dy = _conv_case(orc, dtype, n, h, w, c, k, win, st, bool(same), pad)
+    rng = np.random.default_rng(77)
+    y_prev = rounded(np.maximum(rng.standard_normal(n * h * w * c), 0).astype(np.float32), dtype)
+    before = rounded(rng.standard_normal(n * h * w * c).astype(np.float32), dtype)
+    dx = to_dev(before, dtype)
+    pd.conv2d(pd.INPUT_BACKPROP, to_dev(dy, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_IM2COL, out=dx,
+              relu_forward_output=to_dev(y_prev, dtype) if masked else None, accumulate=True)
+    assert_no_device_error()
+    ref = before + orc.conv2d(orc.INPUT_BACKPROP, dy, wt, po)
+    if masked:
+        ref = orc.pointwise_grad(0, y_prev, ref)
+    got = to_host(dx)
+    assert rel_err(got, ref) <= TOL[dtype]
+    if masked:
+        assert not np.any(got[y_prev <= 0] != 0)
+
+
 def test_fused_backprop_stem_filter_gradient_fp32(orc):
     n, h, w, c, k, win, st = 2, 32, 32, 3, 64, 7, 2
     p, po, x, _, dy = _conv_case(orc, "f16", n, h, w, c, k, win, st, None, 3)
