@@ -973,6 +973,20 @@ struct Packet<__half> {
 #pragma unroll
     for (int i = 0; i < 4; ++i) v[i] = __hmax2_nan(v[i], a.v[i]);
   }
+  // Winner bookkeeping of the max-pool gradient: wherever this packet equals `m` (or both are NaN,
+  // keep_nan), the two 16-bit lanes of win[i] take `id`.  Visiting the window backwards leaves the
+  // first match.
+  __device__ __forceinline__ void mark_equal(const Packet& m, unsigned id, bool keep_nan, unsigned (&win)[4]) const {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      unsigned mask = __heq2_mask(v[i], m.v[i]);
+      if (keep_nan) mask |= __hneu2_mask(v[i], v[i]) & __hneu2_mask(m.v[i], m.v[i]);
+      win[i] = (win[i] & ~mask) | ((id * 0x00010001u) & mask);
+    }
+  }
+  static __device__ __forceinline__ void store_winners(unsigned char* p, const unsigned (&win)[4]) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(__byte_perm(win[0], win[1], 0x6420), __byte_perm(win[2], win[3], 0x6420));
+  }
   __device__ __forceinline__ void store(__half* p) const {
     uint4 r;
     r.x = *reinterpret_cast<const uint32_t*>(&v[0]);
@@ -1007,6 +1021,20 @@ struct Packet<__nv_bfloat16> {  // maxima only: bf16 products would lose too muc
   __device__ __forceinline__ void max_keep_nan(const Packet& a) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) v[i] = __hmax2_nan(v[i], a.v[i]);
+  }
+  // Winner bookkeeping of the max-pool gradient: wherever this packet equals `m` (or both are NaN,
+  // keep_nan), the two 16-bit lanes of win[i] take `id`.  Visiting the window backwards leaves the
+  // first match.
+  __device__ __forceinline__ void mark_equal(const Packet& m, unsigned id, bool keep_nan, unsigned (&win)[4]) const {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      unsigned mask = __heq2_mask(v[i], m.v[i]);
+      if (keep_nan) mask |= __hneu2_mask(v[i], v[i]) & __hneu2_mask(m.v[i], m.v[i]);
+      win[i] = (win[i] & ~mask) | ((id * 0x00010001u) & mask);
+    }
+  }
+  static __device__ __forceinline__ void store_winners(unsigned char* p, const unsigned (&win)[4]) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(__byte_perm(win[0], win[1], 0x6420), __byte_perm(win[2], win[3], 0x6420));
   }
   __device__ __forceinline__ void store(__nv_bfloat16* p) const {
     uint4 r;
@@ -1047,6 +1075,14 @@ struct Packet<float> {
 #pragma unroll
     for (int i = 0; i < 4; ++i) v[i] = (isnan(a.v[i]) || a.v[i] > v[i]) ? a.v[i] : v[i];
   }
+  __device__ __forceinline__ void mark_equal(const Packet& m, unsigned id, bool keep_nan, unsigned (&win)[4]) const {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (v[i] == m.v[i] || (keep_nan && isnan(v[i]) && isnan(m.v[i]))) win[i] = id;
+  }
+  static __device__ __forceinline__ void store_winners(unsigned char* p, const unsigned (&win)[4]) {
+    *reinterpret_cast<unsigned*>(p) = win[0] | (win[1] << 8) | (win[2] << 16) | (win[3] << 24);
+  }
   __device__ __forceinline__ void store(float* p) const {
     *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
   }
@@ -1067,7 +1103,10 @@ struct StripGeometry {
   int flip;  // MODE 0: read the filter mirrored in both window axes (stride-1 input backprop)
 };
 
-// MODE 0: depthwise 3x3 (needs Packet::fma); MODE 1: max ignoring NaN; MODE 2: max keeping NaN.
+// MODE 0: depthwise 3x3 (needs Packet::fma); MODE 1: max ignoring NaN; MODE 2: max keeping NaN;
+// MODE 3 / 4: as 1 / 2, but instead of the maximum the kernel writes, one byte per element, which
+// element of the window is the first to equal it (1 + row * 3 + col, the winner map of the max-pool
+// gradient); y then points at bytes.
 template <typename T, int ST, int MODE>
 __global__ void __launch_bounds__(kStripBlock)
     window3_strip_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, StripGeometry g,
@@ -1092,8 +1131,8 @@ __global__ void __launch_bounds__(kStripBlock)
   T* yn = y + (size_t)n * g.out_rows * g.out_cols * g.channels + c;
   const float fill = MODE == 0 ? 0.f : lowest_of<T>();
 
-  P wt[3][3];
-  if (MODE == 0) {
+  P wt[MODE == 0 ? 3 : 1][3];
+  if constexpr (MODE == 0) {
 #pragma unroll
     for (int r = 0; r < 3; ++r)
 #pragma unroll
@@ -1128,7 +1167,7 @@ __global__ void __launch_bounds__(kStripBlock)
           acc.fma(ra[o * ST + s2], wt[0][s2]);
           acc.fma(rb[o * ST + s2], wt[1][s2]);
           acc.fma(rc[o * ST + s2], wt[2][s2]);
-        } else if constexpr (MODE == 1) {
+        } else if constexpr (MODE == 1 || MODE == 3) {
           acc.max_ignore_nan(ra[o * ST + s2]);
           acc.max_ignore_nan(rb[o * ST + s2]);
           acc.max_ignore_nan(rc[o * ST + s2]);
@@ -1138,7 +1177,28 @@ __global__ void __launch_bounds__(kStripBlock)
           acc.max_keep_nan(rc[o * ST + s2]);
         }
       }
-      if (ow0 + o < g.out_cols) acc.store(yn + ((size_t)oh * g.out_cols + ow0 + o) * g.channels);
+      if constexpr (MODE >= 3) {
+        // the window backwards, so that the first element equal to the maximum is the one that stays;
+        // elements outside the image never win
+        unsigned win[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int r = 2; r >= 0; --r) {
+          const int ih = ih0 + r;
+          if (ih < 0 || ih >= g.in_rows) continue;
+#pragma unroll
+          for (int s2 = 2; s2 >= 0; --s2) {
+            const int iw = iw0 + o * ST + s2;
+            if (iw < 0 || iw >= g.in_cols) continue;
+            const P& e = r == 0 ? ra[o * ST + s2] : r == 1 ? rb[o * ST + s2] : rc[o * ST + s2];
+            e.mark_equal(acc, (unsigned)(1 + r * 3 + s2), MODE == 4, win);
+          }
+        }
+        if (ow0 + o < g.out_cols)
+          P::store_winners(reinterpret_cast<unsigned char*>(y) +
+                               (((size_t)n * g.out_rows + oh) * g.out_cols + ow0 + o) * g.channels + c, win);
+      } else {
+        if (ow0 + o < g.out_cols) acc.store(yn + ((size_t)oh * g.out_cols + ow0 + o) * g.channels);
+      }
     }
     if (oh + 1 < oh_end) {
       ih0 += ST;
@@ -1288,7 +1348,17 @@ int launch_pooling_max_grad(int op, int dtype, const void* x, const void* y, con
       const size_t bytes = out_items * VN;
       if (cudaMallocAsync(reinterpret_cast<void**>(&winner), bytes, s) == cudaSuccess) {
         const unsigned g1 = grid_for(out_items, kBlock, sms), g2 = grid_for(in_items, kBlock, sms);
-        if (op == PDNN_POOL_MAX)
+        bool winners_done = false;
+        if (p.window_rows == 3 && p.window_cols == 3 && p.stride_rows == p.stride_cols &&
+            (p.stride_rows == 1 || p.stride_rows == 2)) {
+          // the forward pool's strip walk, writing the winner map instead of the maxima
+          const StripGeometry sg{p.in_rows, p.in_cols, p.out_rows, p.out_cols, p.channels, p.pad_rows, p.pad_cols, p.batch, 0, 0, 0};
+          T* wmap = reinterpret_cast<T*>(winner);
+          winners_done = (op == PDNN_POOL_MAX ? launch_window3_strip<T, 3>(xt, nullptr, wmap, p.stride_rows, sg, sms, s)
+                                              : launch_window3_strip<T, 4>(xt, nullptr, wmap, p.stride_rows, sg, sms, s)) == 0;
+        }
+        if (winners_done) {
+        } else if (op == PDNN_POOL_MAX)
           pool_winner_kernel<T, PDNN_POOL_MAX, VN, unsigned><<<g1, kBlock, 0, s>>>(xt, yt, winner, p, (unsigned)out_items);
         else
           pool_winner_kernel<T, PDNN_POOL_MAX_WITH_NAN, VN, unsigned><<<g1, kBlock, 0, s>>>(xt, yt, winner, p, (unsigned)out_items);

@@ -59,6 +59,27 @@ def test_max_pool_random_values_and_nan(orc):
 
 
 @pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("stride", [1, 2])
+def test_max_pool_grad_3x3_ties_nan_and_signed_zeros(orc, dtype, stride):
+    """The 3x3 winner map (strip kernel) with ties, NaNs and signed zeros, both operators."""
+    n, h, w, c, win = 2, 19, 21, 16, 3
+    rng = np.random.default_rng(18)
+    x = rounded(rng.integers(-2, 3, size=n * h * w * c).astype(np.float32) * 0.5, dtype)
+    x[::41] = np.nan
+    x[7::29] = -0.0
+    p, po = pd.pool_params(n, h, w, c, win, stride, True), orc.pool_params(n, h, w, c, win, stride, True)
+    for op in (pd.POOL_MAX, pd.POOL_MAX_WITH_NAN):
+        y = to_host(pd.pooling(op, 0, to_dev(x, dtype), p))
+        y_ref = orc.pool_forward(op, x, po)
+        assert np.array_equal(np.isnan(y), np.isnan(y_ref))
+        assert np.array_equal(y[~np.isnan(y)], y_ref[~np.isnan(y_ref)])
+        dy = rounded(rng.integers(1, 4, size=y_ref.size).astype(np.float32), dtype)
+        dx = to_host(pd.pooling_max_grad(op, to_dev(x, dtype), to_dev(y_ref, dtype), to_dev(dy, dtype), p))
+        dx_ref = orc.pool_max_grad(op, x, y_ref, dy, po)
+        assert np.array_equal(dx, rounded(dx_ref, dtype)), (op, np.abs(dx - dx_ref).max())
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
 @pytest.mark.parametrize("shape", POOL_SHAPES)
 def test_avg_pool_forward_and_grad(orc, dtype, shape):
     n, h, w, c, win, st, same = shape
