@@ -148,10 +148,14 @@ int pdnn_conv2d_fused(int dtype, const void* input, const void* filter, void* ou
  *    pre-activation, which is what its own two backprop passes consume.
  *  - output_f32 (FilterBackprop only): dW is written as fp32 even for fp16 / bf16 tensors, so that
  *    it can land directly in the fp32 buffer a gradient all-reduce works on.
- *  - accumulate (InputBackprop only): dx already holds the gradient that arrived through another
+ *  - accumulate: InputBackprop: dx already holds the gradient that arrived through another
  *    reader of the tensor (a shortcut branch); this call adds its own to it, dx += conv_backprop(dy, w),
  *    and the mask of relu_forward_output, when given, applies to the sum - the reference chain of
- *    an input backprop into a temporary, binaryop::launch<Add> and the ReLU gradient. */
+ *    an input backprop into a temporary, binaryop::launch<Add> and the ReLU gradient.
+ *    FilterBackprop: dW += gradient (gradient accumulation over micro-batches, or into a buffer the
+ *    caller zeroed).  With fp32 gradients the pixel splits of the kernel add their tiles to dW
+ *    directly (TMA reduction) instead of writing partial sums for a second kernel, so no workspace
+ *    is used and the order of the float additions is not fixed from run to run. */
 typedef struct PdnnBackpropFusion {
   const void* relu_forward_output;
   int output_f32;

@@ -193,7 +193,7 @@ def conv2d(pass_, inp, fil, params, algorithm=ALGO_IM2COL, out=None, workspace=N
     (include/portdnn/conv2d/launch.h:59-72) with the selector's answer passed as ``algorithm``.
     Slots: Forward (x, w) -> y; InputBackprop (dy, w) -> dx; FilterBackprop (x, dy) -> dW.
     bias / activation / alpha / beta select the fused forward epilogue; relu_forward_output and accumulate
-    (InputBackprop: dx += ..., then the mask) and output_f32 (FilterBackprop) the fused backprop forms of
+    (InputBackprop: dx += ..., then the mask; FilterBackprop: dW += ...) and output_f32 (FilterBackprop) the fused backprop forms of
     PdnnBackpropFusion."""
     torch = _torch()
     _require_cuda(inp, fil, out, workspace, bias)
@@ -201,9 +201,9 @@ def conv2d(pass_, inp, fil, params, algorithm=ALGO_IM2COL, out=None, workspace=N
     if inp.numel() != n_in or fil.numel() != n_fil:
         raise ValueError("tensor sizes do not match the parameters: %d/%d, %d/%d" % (inp.numel(), n_in, fil.numel(), n_fil))
     backprop_fused = relu_forward_output is not None or output_f32 or accumulate
-    if backprop_fused and (pass_ == FORWARD or ((relu_forward_output is not None or accumulate) and pass_ != INPUT_BACKPROP) or
+    if backprop_fused and (pass_ == FORWARD or (relu_forward_output is not None and pass_ != INPUT_BACKPROP) or
                            (output_f32 and pass_ != FILTER_BACKPROP)):
-        raise ValueError("relu_forward_output / accumulate belong to the input backprop, output_f32 to the filter backprop")
+        raise ValueError("relu_forward_output belongs to the input backprop, output_f32 to the filter backprop")
     if accumulate and out is None:
         raise ValueError("accumulate needs the tensor to add to as out")
     _require_cuda(relu_forward_output)

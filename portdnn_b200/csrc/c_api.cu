@@ -114,8 +114,10 @@ int validate_conv(int pass, const PdnnConv2DParams* p, int algorithm) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) widen_to_f32_kernel(const T* __restrict__ in, float* __restrict__ out, size_t n) {
-  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) out[i] = to_f32(in[i]);
+__global__ void __launch_bounds__(256) widen_to_f32_kernel(const T* __restrict__ in, float* __restrict__ out, size_t n,
+                                                           bool accumulate) {
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256)
+    out[i] = (accumulate ? out[i] : 0.f) + to_f32(in[i]);
 }
 
 // The direct kernel with the fused backprop forms applied afterwards (shapes the tensor-core engine
@@ -124,6 +126,19 @@ __global__ void __launch_bounds__(256) widen_to_f32_kernel(const T* __restrict__
 int run_direct_backprop(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
                         const PdnnBackpropFusion* fusion, cudaStream_t s) {
   const size_t es = dtype_size(dtype);
+  if (pass == PDNN_FILTER_BACKPROP && fusion != nullptr && fusion->accumulate && !(fusion->output_f32 && dtype != PDNN_F32)) {
+    // dW += gradient in the tensors' own type: the gradient into a temporary, then one blend
+    const size_t n = (size_t)p.window_rows * p.window_cols * (p.channels / p.groups) * p.features;
+    void* tmp = nullptr;
+    if (cudaMallocAsync(&tmp, n * es, s) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(PDNN_ALLOCATION_PROBLEM, "conv2d: cannot allocate %zu bytes for the filter gradient", n * es);
+    }
+    int st = launch_direct_conv(pass, dtype, in, fil, tmp, p, nullptr, s);
+    if (st == PDNN_OK) st = launch_scale_blend(dtype, tmp, 1.f, out, 1.f, out, n, s);
+    cudaFreeAsync(tmp, s);
+    return st;
+  }
   if (pass == PDNN_FILTER_BACKPROP && fusion != nullptr && fusion->output_f32 && dtype != PDNN_F32) {
     const size_t n = (size_t)p.window_rows * p.window_cols * (p.channels / p.groups) * p.features;
     void* tmp = nullptr;
@@ -134,8 +149,8 @@ int run_direct_backprop(int pass, int dtype, const void* in, const void* fil, vo
     int st = launch_direct_conv(pass, dtype, in, fil, tmp, p, nullptr, s);
     if (st == PDNN_OK) {
       const unsigned grid = grid_for(n, 256, device_sm_count());
-      if (dtype == PDNN_F16) widen_to_f32_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(tmp), static_cast<float*>(out), n);
-      else widen_to_f32_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(tmp), static_cast<float*>(out), n);
+      if (dtype == PDNN_F16) widen_to_f32_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(tmp), static_cast<float*>(out), n, fusion->accumulate != 0);
+      else widen_to_f32_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(tmp), static_cast<float*>(out), n, fusion->accumulate != 0);
       st = check_launch("filter gradient widening");
     }
     cudaFreeAsync(tmp, s);
@@ -220,8 +235,8 @@ int pdnn_conv2d_backprop_fused(int pass, int dtype, const void* input, const voi
                                void* workspace, size_t workspace_elems, void* stream) {
   if (pass != PDNN_INPUT_BACKPROP && pass != PDNN_FILTER_BACKPROP)
     return fail(PDNN_INVALID_PARAMETER, "conv2d: the fused backprop forms exist for the two backprop passes only");
-  if (fusion != nullptr && pass == PDNN_FILTER_BACKPROP && (fusion->accumulate || fusion->relu_forward_output != nullptr))
-    return fail(PDNN_INVALID_PARAMETER, "conv2d: relu_forward_output and accumulate belong to the input backprop");
+  if (fusion != nullptr && pass == PDNN_FILTER_BACKPROP && fusion->relu_forward_output != nullptr)
+    return fail(PDNN_INVALID_PARAMETER, "conv2d: relu_forward_output belongs to the input backprop");
   if (fusion != nullptr && pass == PDNN_INPUT_BACKPROP && fusion->output_f32)
     return fail(PDNN_INVALID_PARAMETER, "conv2d: output_f32 belongs to the filter backprop");
   return run_conv(pass, dtype, input, filter, output, params, algorithm, nullptr, fusion, workspace, workspace_elems,

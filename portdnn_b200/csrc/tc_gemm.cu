@@ -141,6 +141,7 @@ struct alignas(64) GemmArgs {
   // result is replaced by zero: pointwise::launch<Relu, Gradient> applied on the way out.
   const void* relu_mask;
   int accumulate;  // packed 16-bit epilogues, no bias: the block already in the output is added (before the mask)
+  int reduce_add;  // staged fp32 epilogue of the filter backprop: every pixel split adds its tile to the output
   int mask_smem_bytes;  // 256 bytes per epilogue warp for the sign bits of a 32-row block
   // Time limit of one barrier wait; a wait that lasts longer means a lost arrival, and the CTA
   // gives up (see umma::mbar_wait).
@@ -318,8 +319,9 @@ __device__ __forceinline__ void issue_slice_store(const GemmArgs& a, const TileC
   fence_proxy_async_smem();
   __syncwarp();
   if (lane == 0) {
-    const int c2 = (a.a_mn ? t.tap : t.h0) + ws.qh, c3 = (a.a_mn ? t.split : t.n0) + ws.qn;
-    tma_store_4d(&a.out_map, ws.buf_addr + slot * 4096u, col, t.w0 + ws.qw, c2, c3);
+    const int c2 = (a.a_mn ? t.tap : t.h0) + ws.qh, c3 = (a.a_mn ? (a.reduce_add ? 0 : t.split) : t.n0) + ws.qn;
+    if (a.reduce_add) tma_reduce_add_4d(&a.out_map, ws.buf_addr + slot * 4096u, col, t.w0 + ws.qw, c2, c3);
+    else tma_store_4d(&a.out_map, ws.buf_addr + slot * 4096u, col, t.w0 + ws.qw, c2, c3);
     bulk_commit_group();
   }
 }
@@ -2117,9 +2119,9 @@ FbpPlan plan_filter_backprop(int dtype, const PdnnConv2DParams& p, int sms) {
 
 template <typename T>
 __global__ void __launch_bounds__(256) reduce_splits_kernel(const float* __restrict__ partial, T* __restrict__ out,
-                                                            int splits, size_t n) {
+                                                            int splits, size_t n, bool accumulate) {
   for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
-    float sum = 0.f;
+    float sum = accumulate ? to_f32(out[i]) : 0.f;
     for (int sp = 0; sp < splits; ++sp) sum += partial[(size_t)sp * n + i];
     out[i] = from_f32<T>(sum);
   }
@@ -2134,7 +2136,7 @@ __global__ void __launch_bounds__(256) reduce_splits_kernel(const float* __restr
 template <typename T, typename OutT = T>
 __global__ void __launch_bounds__(256)
     unpack_small_c_filter_grad_kernel(const float* __restrict__ partial, OutT* __restrict__ dw, int splits, int R, int S,
-                                      int C, int K, int rows_per_tap) {
+                                      int C, int K, int rows_per_tap, bool accumulate) {
   constexpr int CP = 16 / sizeof(T);
   const size_t total = (size_t)R * S * C * K;
   const size_t split_stride = (size_t)R * rows_per_tap * K;
@@ -2146,7 +2148,7 @@ __global__ void __launch_bounds__(256)
     const int sidx = (int)(t % S);
     const int r = (int)(t / S);
     const size_t src = ((size_t)r * rows_per_tap + (size_t)sidx * CP + c) * K + k;
-    float sum = 0.f;
+    float sum = accumulate ? to_f32(dw[idx]) : 0.f;
     for (int sp = 0; sp < splits; ++sp) sum += partial[(size_t)sp * split_stride + src];
     dw[idx] = from_f32<OutT>(sum);
   }
@@ -2184,7 +2186,7 @@ SmallCFbpPlan plan_small_c_fbp(int dtype, const PdnnConv2DParams& p, int sms) {
 // Returns PDNN_OK, an error, or -1 if a tensor map could not be encoded (the caller falls back to
 // the direct kernel).
 int conv_filter_backprop_small_c(int dtype, const void* x, const void* dy, void* dw, const PdnnConv2DParams& p,
-                                 bool out_f32, void* ws, size_t ws_elems, cudaStream_t s) {
+                                 bool out_f32, bool accumulate, void* ws, size_t ws_elems, cudaStream_t s) {
   const size_t es = dtype_size(dtype);
   const int sms = device_sm_count();
   const int epr = dtype == PDNN_F32 ? 32 : 64;
@@ -2284,16 +2286,16 @@ int conv_filter_backprop_small_c(int dtype, const void* x, const void* dy, void*
     const unsigned grid = grid_for(n_out, 256, sms);
     if (dtype == PDNN_F32)
       unpack_small_c_filter_grad_kernel<float><<<grid, 256, 0, s>>>(partial, static_cast<float*>(dw), f.splits,
-                                                                    p.window_rows, p.window_cols, p.channels, p.features, epr);
+                                                                    p.window_rows, p.window_cols, p.channels, p.features, epr, accumulate);
     else if (out_f32)  // 16-bit tensors (8 channels per packed pixel), fp32 gradient
       unpack_small_c_filter_grad_kernel<__half, float><<<grid, 256, 0, s>>>(
-          partial, static_cast<float*>(dw), f.splits, p.window_rows, p.window_cols, p.channels, p.features, epr);
+          partial, static_cast<float*>(dw), f.splits, p.window_rows, p.window_cols, p.channels, p.features, epr, accumulate);
     else if (dtype == PDNN_F16)
       unpack_small_c_filter_grad_kernel<__half><<<grid, 256, 0, s>>>(partial, static_cast<__half*>(dw), f.splits,
-                                                                     p.window_rows, p.window_cols, p.channels, p.features, epr);
+                                                                     p.window_rows, p.window_cols, p.channels, p.features, epr, accumulate);
     else
       unpack_small_c_filter_grad_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
-          partial, static_cast<__nv_bfloat16*>(dw), f.splits, p.window_rows, p.window_cols, p.channels, p.features, epr);
+          partial, static_cast<__nv_bfloat16*>(dw), f.splits, p.window_rows, p.window_cols, p.channels, p.features, epr, accumulate);
     st = check_launch("conv2d small-channel filter gradient unpack");
   }
   release();
@@ -2302,8 +2304,11 @@ int conv_filter_backprop_small_c(int dtype, const void* x, const void* dy, void*
 
 // out_f32: dW is written as fp32 whatever the tensors' type (the split reduction, or the epilogue
 // when there is one split, produces it directly).
+// accumulate: dW += the gradient.  With fp32 gradients every pixel split adds its tiles to dW by TMA
+// reduction (no partial sums, no second kernel; the order of the float additions is then not fixed);
+// otherwise the split reduction adds to what dW held.
 int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, const PdnnConv2DParams& p, bool out_f32,
-                         void* ws, size_t ws_elems, cudaStream_t s) {
+                         bool accumulate, void* ws, size_t ws_elems, cudaStream_t s, bool try_reduce = true) {
   const size_t es = dtype_size(dtype);
   const int sms = device_sm_count();
   const int epr = dtype == PDNN_F32 ? 32 : 64;
@@ -2353,7 +2358,9 @@ int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, con
   const size_t n_out = (size_t)nt * p.channels * p.features;
   float* partial = nullptr;
   bool own = false;
-  if (f.splits > 1) {
+  const bool reduce = try_reduce && accumulate && (out_f32 || dtype == PDNN_F32) && aligned16(dw);
+  const bool use_partial = !reduce && (f.splits > 1 || accumulate);
+  if (use_partial) {
     const size_t need_bytes = (size_t)f.splits * n_out * sizeof(float);
     if (ws != nullptr && ws_elems * es >= need_bytes && aligned16(ws)) {
       partial = static_cast<float*>(ws);
@@ -2368,7 +2375,8 @@ int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, con
     g.out_dtype = PDNN_F32;
   } else {
     g.out = dw;
-    g.out_dtype = out_f32 ? PDNN_F32 : dtype;
+    g.out_dtype = (out_f32 || reduce) ? PDNN_F32 : dtype;
+    g.reduce_add = reduce ? 1 : 0;
   }
   g.ext_w = p.channels;
   g.ext_h = g.ext_n = 1;
@@ -2380,19 +2388,21 @@ int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, con
   g.vec_ok = 1;
   {
     const uint64_t eo = dtype_size(g.out_dtype);
-    const uint64_t od[4] = {(uint64_t)p.features, (uint64_t)p.channels, (uint64_t)nt, (uint64_t)f.splits};
+    const uint64_t od[4] = {(uint64_t)p.features, (uint64_t)p.channels, (uint64_t)nt, (uint64_t)(reduce ? 1 : f.splits)};
     const uint64_t os[3] = {(uint64_t)p.features * eo, (uint64_t)p.channels * p.features * eo, (uint64_t)n_out * eo};
     if (!setup_store(g, dtype, od, os)) {
       if (own) cudaFreeAsync(partial, s);
       return PDNN_INVALID_PARAMETER;
     }
+    // only the staged TMA epilogue can add; anything else goes through partial sums
+    if (reduce && !g.tma_store) return conv_filter_backprop(dtype, x, dy, dw, p, out_f32, accumulate, ws, ws_elems, s, false);
   }
   int st = launch_gemm(g, dtype, s);
-  if (st == PDNN_OK && f.splits > 1) {
+  if (st == PDNN_OK && use_partial) {
     const unsigned grid = grid_for(n_out, 256, sms);
-    if (dtype == PDNN_F32 || out_f32) reduce_splits_kernel<float><<<grid, 256, 0, s>>>(partial, static_cast<float*>(dw), f.splits, n_out);
-    else if (dtype == PDNN_F16) reduce_splits_kernel<__half><<<grid, 256, 0, s>>>(partial, static_cast<__half*>(dw), f.splits, n_out);
-    else reduce_splits_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(partial, static_cast<__nv_bfloat16*>(dw), f.splits, n_out);
+    if (dtype == PDNN_F32 || out_f32) reduce_splits_kernel<float><<<grid, 256, 0, s>>>(partial, static_cast<float*>(dw), f.splits, n_out, accumulate);
+    else if (dtype == PDNN_F16) reduce_splits_kernel<__half><<<grid, 256, 0, s>>>(partial, static_cast<__half*>(dw), f.splits, n_out, accumulate);
+    else reduce_splits_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(partial, static_cast<__nv_bfloat16*>(dw), f.splits, n_out, accumulate);
     st = check_launch("filter backprop split reduction");
   }
   if (own) cudaFreeAsync(partial, s);
@@ -2466,6 +2476,7 @@ int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, c
               const PdnnConvEpilogue* epi, const PdnnBackpropFusion* fusion, void* ws, size_t ws_elems, cudaStream_t s) {
   const void* relu_mask = fusion != nullptr ? fusion->relu_forward_output : nullptr;
   const bool out_f32 = fusion != nullptr && fusion->output_f32 != 0 && dtype != PDNN_F32;
+  const bool accumulate = fusion != nullptr && fusion->accumulate != 0;
   switch (pass) {
     case PDNN_FORWARD:
       if (small_c_applicable(dtype, p)) {
@@ -2474,13 +2485,13 @@ int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, c
       }
       return conv_forward(dtype, in, fil, out, p, epi, s);
     case PDNN_INPUT_BACKPROP:
-      return conv_input_backprop(dtype, in, fil, out, p, relu_mask, fusion != nullptr && fusion->accumulate != 0, s);
+      return conv_input_backprop(dtype, in, fil, out, p, relu_mask, accumulate, s);
     case PDNN_FILTER_BACKPROP:
       if (small_c_applicable(dtype, p)) {
-        const int st = conv_filter_backprop_small_c(dtype, in, fil, out, p, out_f32, ws, ws_elems, s);
+        const int st = conv_filter_backprop_small_c(dtype, in, fil, out, p, out_f32, accumulate, ws, ws_elems, s);
         return st == -1 ? kNeedsDirect : st;
       }
-      return conv_filter_backprop(dtype, in, fil, out, p, out_f32, ws, ws_elems, s);
+      return conv_filter_backprop(dtype, in, fil, out, p, out_f32, accumulate, ws, ws_elems, s);
   }
   return fail(PDNN_INVALID_PARAMETER, "bad pass %d", pass);
 }

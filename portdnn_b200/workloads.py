@@ -307,6 +307,9 @@ class ConvStackRunner:
         input backprop that produced the incoming gradient already applied it - then the filter backprop,
         written as fp32 straight into the layer's slice of the gradient bucket, then the input backprop."""
         last = self.conv_ids[-1]
+        if self.fuse_accumulate and seg["bucket"] is not None and self.dtype != self.torch.float32:
+            # the filter backprops of this segment add their pixel splits straight into the bucket
+            self.bucket.buffer[seg["bucket"][0]:seg["bucket"][1]].zero_()
         for i in seg["layers"]:
             l, p, j = self.layers[i], self.layers[i].params, self.src_idx[i]
             if i == last:
@@ -326,8 +329,10 @@ class ConvStackRunner:
                     g = self.scratch[:self.sizes[i]]
                     api.pointwise_grad(api.ACT_RELU, self.acts[i], dy, out=g)
                 k = self.conv_ids.index(i)
+                f32_out = self.dtype != self.torch.float32
+                add = self.fuse_accumulate and f32_out
                 api.conv2d(api.FILTER_BACKPROP, self._in(i), g, p, algorithm=api.ALGO_IM2COL, out=self.bucket.view(k),
-                           output_f32=self.dtype != self.torch.float32,
+                           output_f32=f32_out, accumulate=add,
                            workspace=self.fbp_workspace if i in self.fbp_ws else None)
                 if j >= 0:
                     # The ReLU mask of tensor j goes into the input backprop that completes its gradient:

@@ -253,6 +253,31 @@ def test_accumulating_input_backprop_against_oracle(orc, dtype, masked, shape):
         assert not np.any(got[y_prev <= 0] != 0)
 
 
+@pytest.mark.parametrize("dtype", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("f32_out", [True, False])
+@pytest.mark.parametrize("shape", BWD_SHAPES + [(2, 32, 32, 3, 64, 7, 2, None, 3), (3, 9, 9, 5, 7, 3, 1, True, None)])
+def test_accumulating_filter_backprop_against_oracle(orc, dtype, f32_out, shape):
+    """PdnnBackpropFusion::accumulate for the filter backprop: dW += gradient, twice in a row onto a
+    non-zero start (fp32 gradients: the pixel splits add their tiles by TMA reduction; otherwise the
+    split reduction adds)."""
+    if dtype == "f32" and f32_out:
+        pytest.skip("fp32 tensors always have fp32 gradients")
+    n, h, w, c, k, win, st, same, pad = shape
+    p, po, x, wt, dy = _conv_case(orc, dtype, n, h, w, c, k, win, st, same if same is None else bool(same), pad)
+    rng = np.random.default_rng(91)
+    out_kind = "f32" if (f32_out or dtype == "f32") else dtype
+    before = rounded(rng.standard_normal(wt.size).astype(np.float32), out_kind)
+    dw = to_dev(before, out_kind)
+    for _ in range(2):
+        pd.conv2d(pd.FILTER_BACKPROP, to_dev(x, dtype), to_dev(dy, dtype), p, algorithm=pd.ALGO_IM2COL, out=dw,
+                  output_f32=f32_out, accumulate=True)
+    assert_no_device_error()
+    grad = orc.conv2d(orc.FILTER_BACKPROP, x, dy, po)
+    # the 16-bit accumulator rounds after each addition; compare against the same chain
+    ref = rounded(rounded(before + grad, out_kind) + grad, out_kind) if out_kind != "f32" else before + 2 * grad
+    assert rel_err(to_host(dw), ref) <= 2 * TOL[dtype]
+
+
 def test_fused_backprop_stem_filter_gradient_fp32(orc):
     n, h, w, c, k, win, st = 2, 32, 32, 3, 64, 7, 2
     p, po, x, _, dy = _conv_case(orc, "f16", n, h, w, c, k, win, st, None, 3)
