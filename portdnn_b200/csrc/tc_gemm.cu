@@ -89,6 +89,7 @@ struct alignas(64) GemmArgs {
   int tw, th, tn;    // a_mn == 0: pixel box of a row tile; a_mn == 1: pixel box of a reduction slab
   int etw, eth, etn; // pixel box of a row tile as the epilogue sees it
   int num_taps;
+  int tap_pack;      // a_mn == 1: taps per tile (2: the second 64 rows of the A tile are the next tap's channels)
   int cblocks;       // a_mn == 0: reduction blocks per tap
   int slabs_w, slabs_h, slabs_n, splits, slabs_per_split, split_is_batch;  // a_mn == 1
   int b_batch_mul;
@@ -166,7 +167,7 @@ struct TileWalker {
   __device__ __forceinline__ void init(const GemmArgs& a, int first, int step) {
     r0 = a.n_tiles;
     r1 = a.tiles_w;
-    r2 = a.a_mn ? a.num_taps : a.tiles_h;
+    r2 = a.a_mn ? (a.num_taps + a.tap_pack - 1) / a.tap_pack : a.tiles_h;
     d0 = first % r0, first /= r0;
     d1 = first % r1, first /= r1;
     d2 = first % r2, d3 = first / r2;
@@ -201,12 +202,12 @@ struct TileWalker {
       t.ks_begin = 0;
       t.ks_end = a.num_taps * a.cblocks;
     } else {
-      t.tap = d2;
+      t.tap = d2 * a.tap_pack;
       t.split = d3;
       t.w0 = d1 * kTileM;
-      t.h0 = 0;
+      t.h0 = a.tap_pack > 1 ? t.tap : 0;  // packed taps: the tap is the second digit of a row's position
       t.n0 = 0;
-      t.out_off = (long long)t.split * a.split_stride + (long long)t.tap * a.tap_stride;
+      t.out_off = (long long)t.split * a.split_stride + (a.tap_pack > 1 ? 0ll : (long long)t.tap * a.tap_stride);
       const int total = a.slabs_w * a.slabs_h * a.slabs_n;
       t.ks_begin = a.split_is_batch ? 0 : t.split * a.slabs_per_split;
       t.ks_end = min(t.ks_begin + a.slabs_per_split, total);
@@ -320,7 +321,8 @@ __device__ __forceinline__ void issue_slice_store(const GemmArgs& a, const TileC
   __syncwarp();
   if (lane == 0) {
     const int c2 = (a.a_mn ? t.tap : t.h0) + ws.qh, c3 = (a.a_mn ? (a.reduce_add ? 0 : t.split) : t.n0) + ws.qn;
-    if (a.reduce_add) tma_reduce_add_4d(&a.out_map, ws.buf_addr + slot * 4096u, col, t.w0 + ws.qw, c2, c3);
+    if (a.a_mn && c2 >= a.num_taps) {  // packed taps, odd count: the last tile's second half has no tap
+    } else if (a.reduce_add) tma_reduce_add_4d(&a.out_map, ws.buf_addr + slot * 4096u, col, t.w0 + ws.qw, c2, c3);
     else tma_store_4d(&a.out_map, ws.buf_addr + slot * 4096u, col, t.w0 + ws.qw, c2, c3);
     bulk_commit_group();
   }
@@ -676,7 +678,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
   const uint32_t acc_bufs = (uint32_t)a.acc_bufs, acc_stride = (uint32_t)a.acc_stride;
   const uint32_t grp_tmem = tmem_base + (uint32_t)grp * acc_bufs * acc_stride;
 
-  const int total_tiles = a.a_mn ? a.n_tiles * a.tiles_w * a.num_taps * a.splits
+  const int total_tiles = a.a_mn ? a.n_tiles * a.tiles_w * ((a.num_taps + a.tap_pack - 1) / a.tap_pack) * a.splits
                                  : a.n_tiles * a.tiles_w * a.tiles_h * a.tiles_n;
   // pair mode: both groups walk the same tiles (each takes one row tile of the pair)
   const int first_tile = (int)blockIdx.x + (pair ? 0 : grp * (int)gridDim.x);
@@ -789,6 +791,12 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
         } else {
           const TapEntry e = a.taps[t.tap];
           const CUtensorMap* amap = &a.a_map[e.a_map];
+          // packed taps: the second box holds the same channels as seen by the next tap (none: a box
+          // beyond the last channel, which TMA fills with zeros)
+          const bool packed = a.tap_pack > 1, second = packed && t.tap + 1 < a.num_taps;
+          const TapEntry e2 = a.taps[second ? t.tap + 1 : t.tap];
+          const CUtensorMap* amap2 = &a.a_map[e2.a_map];
+          const int c2nd = second ? t.w0 : 0x40000000;
           const int batch = a.split_is_batch ? t.split : 0;
           // slab coordinates of ks_begin, then advanced like an odometer
           int iw = t.ks_begin % a.slabs_w, ih = (t.ks_begin / a.slabs_w) % a.slabs_h,
@@ -805,9 +813,14 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
               const uint32_t sa = ring_base + (uint32_t)s * stage_bytes;
               const uint32_t sb = sa + kABytes;
               const int kw = iw * a.tw, kh = ih * a.th, kn = in * a.tn + batch;
+              if (packed) {
+                warp_tma_load_4d(sa, amap, fb, t.w0, kw + e.dw, kh + e.dh, kn);
+                warp_tma_load_4d(sa + a_box_bytes, amap2, fb, c2nd, kw + e2.dw, kh + e2.dh, kn);
+              } else {
 #pragma unroll 1
-              for (int j = 0; j < a_boxes; ++j)
-                warp_tma_load_4d(sa + (uint32_t)j * a_box_bytes, amap, fb, t.w0 + j * epr, kw + e.dw, kh + e.dh, kn);
+                for (int j = 0; j < a_boxes; ++j)
+                  warp_tma_load_4d(sa + (uint32_t)j * a_box_bytes, amap, fb, t.w0 + j * epr, kw + e.dw, kh + e.dh, kn);
+              }
               if (b_mode == B_MN_4) {
 #pragma unroll 1
                 for (int j = 0; j < b_boxes; ++j)
@@ -1424,7 +1437,8 @@ GemmKernel select_kernel(bool split, int epi, int out_dtype) {
 
 int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   const bool split = dtype == PDNN_F32;
-  const long long total = g.a_mn ? (long long)g.n_tiles * g.tiles_w * g.num_taps * g.splits
+  const int tap_pack = std::max(g.tap_pack, 1);
+  const long long total = g.a_mn ? (long long)g.n_tiles * g.tiles_w * ((g.num_taps + tap_pack - 1) / tap_pack) * g.splits
                                  : (long long)g.n_tiles * g.tiles_w * g.tiles_h * g.tiles_n;
   if (total <= 0) return PDNN_OK;
   if (total > 0x7FFFFFFFll) return fail(PDNN_INDEX_EXCEEDED, "tensor-core gemm: too many tiles");
@@ -1482,6 +1496,7 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   GemmArgs args = g;
+  args.tap_pack = tap_pack;
   args.wait_limit_ns = kWaitLimitNs;
   const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, args);
   if (le != cudaSuccess) {
@@ -2091,7 +2106,7 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
 }
 
 struct FbpPlan {
-  int tw, th, tn, slabs_w, slabs_h, slabs_n, splits, slabs_per_split, m_tiles, n_tiles, bn;
+  int tw, th, tn, slabs_w, slabs_h, slabs_n, splits, slabs_per_split, m_tiles, n_tiles, bn, tap_pack;
 };
 
 FbpPlan plan_filter_backprop(int dtype, const PdnnConv2DParams& p, int sms) {
@@ -2107,7 +2122,10 @@ FbpPlan plan_filter_backprop(int dtype, const PdnnConv2DParams& p, int sms) {
   // reduction of the next (measured over the ResNet-50 layers: 9% less time than 256-column tiles)
   f.bn = std::min(std::min(max_bn, PDNN_KNOB("PDNN_FBP_BN", 128)), ceil_div(p.features, epr) * epr);
   f.n_tiles = ceil_div(p.features, f.bn);
-  const long long out_tiles = (long long)f.m_tiles * f.n_tiles * p.window_rows * p.window_cols;
+  // At most 64 channels and several taps: a tile holds two taps, the second 64 accumulator rows being
+  // the same channels as the next tap sees them, instead of rows that no channel uses.
+  f.tap_pack = (PDNN_KNOB("PDNN_FBP_PACK", 1) && dtype != PDNN_F32 && p.channels <= 64 && p.window_rows * p.window_cols >= 2) ? 2 : 1;
+  const long long out_tiles = (long long)f.m_tiles * f.n_tiles * ceil_div(p.window_rows * p.window_cols, f.tap_pack);
   const long long total_slabs = (long long)f.slabs_w * f.slabs_h * f.slabs_n;
   long long want = std::max<long long>(1, ((long long)PDNN_KNOB("PDNN_FBP_WANT", 2) * sms) / out_tiles);
   want = std::min<long long>(want, std::max<long long>(1, total_slabs / 8));  // at least 8 slabs per split
@@ -2170,6 +2188,7 @@ SmallCFbpPlan plan_small_c_fbp(int dtype, const PdnnConv2DParams& p, int sms) {
   f.slabs_h = ceil_div(p.out_rows, f.th);
   f.slabs_n = ceil_div(p.batch, f.tn);
   f.m_tiles = 1;
+  f.tap_pack = 1;
   f.bn = std::min(dtype == PDNN_F32 ? 128 : 256, ceil_div(p.features, epr) * epr);
   f.n_tiles = ceil_div(p.features, f.bn);
   const long long out_tiles = (long long)f.n_tiles * p.window_rows;
@@ -2385,6 +2404,13 @@ int conv_filter_backprop(int dtype, const void* x, const void* dy, void* dw, con
   g.stride_h = g.stride_n = 0;
   g.split_stride = (long long)n_out;
   g.tap_stride = (long long)p.channels * p.features;
+  g.tap_pack = f.tap_pack;
+  if (f.tap_pack == 2) {  // rows 64..127 of a tile are channels 0..63 of the next tap
+    g.etw = 64;
+    g.eth = 2;
+    g.ext_h = nt;
+    g.stride_h = g.tap_stride;
+  }
   g.vec_ok = 1;
   {
     const uint64_t eo = dtype_size(g.out_dtype);
