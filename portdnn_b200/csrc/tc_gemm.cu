@@ -2188,10 +2188,10 @@ SmallCFbpPlan plan_small_c_fbp(int dtype, const PdnnConv2DParams& p, int sms) {
   f.slabs_h = ceil_div(p.out_rows, f.th);
   f.slabs_n = ceil_div(p.batch, f.tn);
   f.m_tiles = 1;
-  f.tap_pack = 1;
+  f.tap_pack = (dtype != PDNN_F32 && p.window_rows >= 2) ? 2 : 1;  // 64 packed rows per filter row: two per tile
   f.bn = std::min(dtype == PDNN_F32 ? 128 : 256, ceil_div(p.features, epr) * epr);
   f.n_tiles = ceil_div(p.features, f.bn);
-  const long long out_tiles = (long long)f.n_tiles * p.window_rows;
+  const long long out_tiles = (long long)f.n_tiles * ceil_div(p.window_rows, f.tap_pack);
   const long long total_slabs = (long long)f.slabs_w * f.slabs_h * f.slabs_n;
   long long want = std::max<long long>(1, (2ll * sms) / out_tiles);
   want = std::min<long long>(want, std::max<long long>(1, total_slabs / 8));
@@ -2279,6 +2279,13 @@ int conv_filter_backprop_small_c(int dtype, const void* x, const void* dy, void*
   g.stride_w = p.features;
   g.tap_stride = (long long)epr * p.features;
   g.split_stride = (long long)p.window_rows * epr * p.features;
+  g.tap_pack = f.tap_pack;
+  if (f.tap_pack == 2) {  // two filter rows per tile: 2 x 64 accumulator rows
+    g.etw = 64;
+    g.eth = 2;
+    g.ext_h = p.window_rows;
+    g.stride_h = g.tap_stride;
+  }
   g.vec_ok = 1;
   {
     const uint64_t od[4] = {(uint64_t)p.features, (uint64_t)epr, (uint64_t)p.window_rows, (uint64_t)f.splits};
