@@ -841,6 +841,146 @@ __global__ void __launch_bounds__(kFbpLanesF* kFbpLanesP)
   }
 }
 
+// The 3x3 filter gradient with one 32-bit word of channels per lane (two 16-bit channels or one
+// fp32 channel): a warp covers 128 contiguous bytes of a pixel, walks whole output rows and keeps
+// the 9 x (1 or 2) sums of its channels in registers across all its rows.  Few registers, so the SM
+// holds enough warps to cover the load latency (the packet form above keeps 72 sums per thread and
+// runs at one block per SM), and every load instruction of a warp is one full line.  The 3x3 window
+// of x slides along the row.  partial[slice][tap][f] as above; a
+// block is eight warps of one channel group, slice = blockIdx.x.
+template <typename T>
+struct WordOf;
+template <>
+struct WordOf<float> {
+  static constexpr int E = 1;
+  static __device__ __forceinline__ void unpack(unsigned w, float (&v)[1]) { v[0] = __uint_as_float(w); }
+};
+template <>
+struct WordOf<__half> {
+  static constexpr int E = 2;
+  static __device__ __forceinline__ void unpack(unsigned w, float (&v)[2]) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    v[0] = f.x;
+    v[1] = f.y;
+  }
+};
+template <>
+struct WordOf<__nv_bfloat16> {
+  static constexpr int E = 2;
+  static __device__ __forceinline__ void unpack(unsigned w, float (&v)[2]) {
+    v[0] = __uint_as_float(w << 16);
+    v[1] = __uint_as_float(w & 0xFFFF0000u);
+  }
+};
+
+template <typename T, int ST>
+__global__ void __launch_bounds__(256, 3)
+    depthwise_filter_backprop_rows_kernel(const T* __restrict__ x, const T* __restrict__ dy, float* __restrict__ partial,
+                                          PdnnDepthwiseConv2DParams p) {
+  constexpr int E = WordOf<T>::E;
+  // U output columns per trip: their ST * U new input columns and U dy words are requested together
+  // (a warp has to keep a dozen lines in flight to cover the latency), the CARRY columns the next
+  // trip's first window shares with this one stay in registers.
+  constexpr int U = ST == 1 ? 4 : 2, CARRY = 3 - ST, NEW = U * ST;
+  __shared__ float red[8][9 * E][32];
+  const int F = p.channels, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned wstride = (unsigned)(F / E);  // 32-bit words per pixel
+  const unsigned lw = min((unsigned)(blockIdx.y * 32 + lane), wstride - 1u);  // idle lanes repeat the last word
+  // 32-bit word indices from the tensors' bases (the host only takes this path below 2^32 words)
+  const unsigned* __restrict__ xw = reinterpret_cast<const unsigned*>(x);
+  const unsigned* __restrict__ dw = reinterpret_cast<const unsigned*>(dy);
+  float acc[9][E];
+#pragma unroll
+  for (int t = 0; t < 9; ++t)
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[t][e] = 0.f;
+  const unsigned units = (unsigned)(p.batch * p.out_rows);
+  for (unsigned u = blockIdx.x * 8u + (unsigned)warp; u < units; u += gridDim.x * 8u) {
+    const int oh = (int)(u % (unsigned)p.out_rows), n = (int)(u / (unsigned)p.out_rows);
+    const int ih0 = oh * ST - p.pad_rows;
+    const bool rows_inside = ih0 >= 0 && ih0 + 2 < p.in_rows;
+    unsigned xrow[3];  // word index of column 0 of the three input rows (clamped into the image)
+    bool rok[3];
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+      const int ih = ih0 + r;
+      rok[r] = ih >= 0 && ih < p.in_rows;
+      xrow[r] = (unsigned)((n * p.in_rows + min(max(ih, 0), p.in_rows - 1)) * p.in_cols) * wstride + lw;
+    }
+    const unsigned drow = (unsigned)((n * p.out_rows + oh) * p.out_cols) * wstride + lw;
+    float win[CARRY + NEW][3][E];
+    auto load_col_checked = [&](int iw, float (&col)[3][E]) {
+      const bool cok = iw >= 0 && iw < p.in_cols;
+      const unsigned off = (unsigned)min(max(iw, 0), p.in_cols - 1) * wstride;
+#pragma unroll
+      for (int r = 0; r < 3; ++r) {
+        WordOf<T>::unpack(__ldg(xw + xrow[r] + off), col[r]);
+        if (!(cok && rok[r])) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) col[r][e] = 0.f;
+        }
+      }
+    };
+#pragma unroll
+    for (int k = 0; k < CARRY; ++k) load_col_checked(k - p.pad_cols, win[k]);
+    for (int ow = 0; ow < p.out_cols; ow += U) {
+      const int iw_new = ow * ST - p.pad_cols + CARRY;
+      float dv[U][E];
+      if (rows_inside && iw_new >= 0 && iw_new + NEW <= p.in_cols && ow + U <= p.out_cols) {
+        // interior: no masks, one index addition per load
+        unsigned off = (unsigned)iw_new * wstride;
+#pragma unroll
+        for (int j = 0; j < NEW; ++j, off += wstride)
+#pragma unroll
+          for (int r = 0; r < 3; ++r) WordOf<T>::unpack(__ldg(xw + xrow[r] + off), win[CARRY + j][r]);
+        unsigned doff = drow + (unsigned)ow * wstride;
+#pragma unroll
+        for (int uu = 0; uu < U; ++uu, doff += wstride) WordOf<T>::unpack(__ldg(dw + doff), dv[uu]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < NEW; ++j) load_col_checked(iw_new + j, win[CARRY + j]);
+#pragma unroll
+        for (int uu = 0; uu < U; ++uu) {
+          WordOf<T>::unpack(__ldg(dw + drow + (unsigned)min(ow + uu, p.out_cols - 1) * wstride), dv[uu]);
+          if (ow + uu >= p.out_cols) {
+#pragma unroll
+            for (int e = 0; e < E; ++e) dv[uu][e] = 0.f;
+          }
+        }
+      }
+#pragma unroll
+      for (int uu = 0; uu < U; ++uu)
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+          for (int c3 = 0; c3 < 3; ++c3)
+#pragma unroll
+            for (int e = 0; e < E; ++e) acc[r * 3 + c3][e] = fmaf(win[uu * ST + c3][r][e], dv[uu][e], acc[r * 3 + c3][e]);
+#pragma unroll
+      for (int k = 0; k < CARRY; ++k)
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+          for (int e = 0; e < E; ++e) win[k][r][e] = win[NEW + k][r][e];
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < 9; ++t)
+#pragma unroll
+    for (int e = 0; e < E; ++e) red[warp][t * E + e][lane] = acc[t][e];
+  __syncthreads();
+  for (int i = threadIdx.x; i < 9 * E * 32; i += 256) {
+    const int l = i & 31, te = i >> 5, t = te / E, e = te % E;
+    const int ch = (blockIdx.y * 32 + l) * E + e;
+    if (ch < F) {
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) sum += red[w][te][l];
+      partial[((size_t)blockIdx.x * 9 + t) * F + ch] = sum;
+    }
+  }
+}
+
 // Stage 2: dW[i] = sum over slices of partial[slice][i], in slice order (deterministic).
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
@@ -1454,25 +1594,50 @@ int fbp_slices(const PdnnDepthwiseConv2DParams& p, int V, int sms) {
   return (int)want;
 }
 
-// Stage 1 of the depthwise filter backprop: partial[slice][tap][f].
+// Stage 1 of the depthwise filter backprop: partial[slice][tap][f].  Returns the number of slices written.
 template <typename T>
-void launch_fbp_partials(bool vec, const T* in, const T* dy, float* partial, const PdnnDepthwiseConv2DParams& p,
+int launch_fbp_partials(bool vec, const T* in, const T* dy, float* partial, const PdnnDepthwiseConv2DParams& p,
                          int slices, cudaStream_t s) {
   constexpr int VN = Vec16<T>::N;
   const int V = vec ? VN : 1, F = p.channels * p.channel_multiplier;
   const long long pixels = (long long)p.batch * p.out_rows * p.out_cols;
   const long long per_slice = (pixels + slices - 1) / slices;
+  constexpr int E = 4 / (int)sizeof(T);
+  const unsigned long long x_words = (unsigned long long)p.batch * p.in_rows * p.in_cols * (F / E);
+  if (p.window_rows == 3 && p.window_cols == 3 && p.channel_multiplier == 1 && F % E == 0 && aligned16(in) && aligned16(dy) &&
+      p.stride_rows == p.stride_cols && (p.stride_rows == 1 || p.stride_rows == 2) && x_words < 0xFFFFFFFFull) {
+    // whole output rows per warp, one 32-bit word of channels per lane
+    const long long units = (long long)p.batch * p.out_rows;
+    const int groups = (F / E + 31) / 32;
+    // one wave of blocks, as long as the scratch holds that many slices
+    const int sms = device_sm_count();
+    int per_sm = 0;
+    const cudaError_t oe = p.stride_rows == 1
+        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, depthwise_filter_backprop_rows_kernel<T, 1>, 256, 0)
+        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, depthwise_filter_backprop_rows_kernel<T, 2>, 256, 0);
+    if (oe != cudaSuccess || per_sm < 1) {
+      cudaGetLastError();
+      per_sm = 2;
+    }
+    const long long wave = std::max(1, per_sm * sms / groups);
+    const unsigned gx = (unsigned)std::min<long long>(std::min<long long>(slices, wave), (units + 7) / 8);
+    dim3 grid(gx, groups);
+    if (p.stride_rows == 1) depthwise_filter_backprop_rows_kernel<T, 1><<<grid, 256, 0, s>>>(in, dy, partial, p);
+    else depthwise_filter_backprop_rows_kernel<T, 2><<<grid, 256, 0, s>>>(in, dy, partial, p);
+    return (int)gx;
+  }
   if (fbp_all_taps(p, V)) {
     const int lanes = fbp_channel_lanes(F / V);
     dim3 block(lanes, kFbpLanesF * kFbpLanesP / lanes);
     dim3 grid(slices, 1, (F + lanes * V - 1) / (lanes * V));
     depthwise_filter_backprop_partial9_kernel<T, VN><<<grid, block, 0, s>>>(in, dy, partial, p, per_slice);
-    return;
+    return slices;
   }
   dim3 block(kFbpLanesF, kFbpLanesP);
   dim3 grid(slices, p.window_rows * p.window_cols, (F + kFbpLanesF * V - 1) / (kFbpLanesF * V));
   if (vec) depthwise_filter_backprop_partial_kernel<T, VN><<<grid, block, 0, s>>>(in, dy, partial, p, per_slice);
   else depthwise_filter_backprop_partial_kernel<T, 1><<<grid, block, 0, s>>>(in, dy, partial, p, per_slice);
+  return slices;
 }
 
 }  // namespace
@@ -1513,10 +1678,10 @@ int launch_depthwise(int pass, int dtype, const void* in, const void* fil, void*
         }
         own = true;
       }
-      launch_fbp_partials<T>(vec, static_cast<const T*>(in), static_cast<const T*>(fil), partial, p, slices, s);
+      const int written = launch_fbp_partials<T>(vec, static_cast<const T*>(in), static_cast<const T*>(fil), partial, p, slices, s);
       int st = check_launch("depthwise filter backprop (partial sums)");
       if (st == PDNN_OK) {
-        reduce_slices_kernel<T><<<grid_for(n_out, kBlock, sms), kBlock, 0, s>>>(partial, static_cast<T*>(out), slices, n_out);
+        reduce_slices_kernel<T><<<grid_for(n_out, kBlock, sms), kBlock, 0, s>>>(partial, static_cast<T*>(out), written, n_out);
         st = check_launch("depthwise filter backprop (slice reduction)");
       }
       if (own) cudaFreeAsync(partial, s);
@@ -1856,10 +2021,10 @@ int launch_depthwise_filter_backprop_static(int dtype, const void* in, const voi
     if ((size_t)slices > fit) slices = (int)fit;
     // Stage 1 writes every partial[slice][tap][f] it later reads, so the array's old contents
     // never leak into a result and nothing has to be cleared first.
-    launch_fbp_partials<T>(vec, static_cast<const T*>(in), static_cast<const T*>(dy), partial, p, slices, s);
+    const int written = launch_fbp_partials<T>(vec, static_cast<const T*>(in), static_cast<const T*>(dy), partial, p, slices, s);
     int st = check_launch("depthwise filter backprop, fixed scratch (partial sums)");
     if (st != PDNN_OK) return st;
-    reduce_slices_kernel<T><<<grid_for(n_out, kBlock, sms), kBlock, 0, s>>>(partial, static_cast<T*>(dw), slices, n_out);
+    reduce_slices_kernel<T><<<grid_for(n_out, kBlock, sms), kBlock, 0, s>>>(partial, static_cast<T*>(dw), written, n_out);
     return check_launch("depthwise filter backprop, fixed scratch (slice reduction)");
   });
 }
