@@ -141,6 +141,8 @@ struct alignas(64) GemmArgs {
   // laid out exactly like `out` (stride_w / stride_h / stride_n).  Where it is not positive the
   // result is replaced by zero: pointwise::launch<Relu, Gradient> applied on the way out.
   const void* relu_mask;
+  CUtensorMap mask_map;  // the mask tensor with the geometry of out_map (set when relu_mask is)
+  int mask_slots;        // 4 KB mask slots per epilogue warp: 2 where shared memory allows, else 1
   int accumulate;  // packed 16-bit epilogues, no bias: the block already in the output is added (before the mask)
   int reduce_add;  // staged fp32 epilogue of the filter backprop: every pixel split adds its tile to the output
   int mask_smem_bytes;  // 256 bytes per epilogue warp for the sign bits of a 32-row block
@@ -415,11 +417,10 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
 
 // Converts 32 accumulator columns of one row (four 16-byte chunks, numbered from chunk_base) and
 // writes them into the row's 128 bytes of the staging slice.  `bv` holds the bias of those 32
-// columns (zeros without a bias).  `keep` (MASK only) holds one byte per 16-byte chunk of the
-// row: bit e set = element e is kept.
+// columns (zeros without a bias), `mk` (MASK only) the keep masks of those columns.
 template <typename OutT, bool MASK>
 __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bool zero, bool has_bias, const uint4* bv,
-                                                   int act, uint8_t* row_ptr, int row, int chunk_base, uint2 keep) {
+                                                   int act, uint8_t* row_ptr, int row, int chunk_base, const uint4* mk) {
   using P2 = typename Pair<OutT>::type;
   const P2 zero2 = Pair<OutT>::splat(0.f), six2 = Pair<OutT>::splat(6.f);
 #pragma unroll
@@ -437,61 +438,50 @@ __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bo
       }
       o[i] = pair_bits(v);
     }
-    if (MASK) {
-      const int c = chunk_base + g;
-      const uint32_t kb = ((c < 4 ? keep.x : keep.y) >> (8 * (c & 3))) & 0xFFu;
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        o[i] &= ((kb >> (2 * i)) & 1u ? 0x0000FFFFu : 0u) | ((kb >> (2 * i + 1)) & 1u ? 0xFFFF0000u : 0u);
+    if (MASK) {  // mk: 0xFFFF in every halfword whose mask element is positive
+      o[0] &= mk[g].x;
+      o[1] &= mk[g].y;
+      o[2] &= mk[g].z;
+      o[3] &= mk[g].w;
     }
     *reinterpret_cast<uint4*>(row_ptr + (((chunk_base + g) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
-// Sign bits of a 32-row x 64-column block of the ReLU mask tensor (16-bit elements), gathered with
-// coalesced loads: lane l reads 16-byte chunk l % 8 of rows l / 8, l / 8 + 4, ... (issue_mask_loads),
-// turns every chunk into one byte (bit e = element e is positive) and leaves it in the warp's
-// 256-byte table at [row][chunk]; afterwards lane r reads the eight bytes of its own row r
-// (finish_mask).  The loads of a block are issued one block ahead - the first block of a tile before
-// the wait for its accumulator - so that their latency hides behind the work in between.  A
-// positive 16-bit float is a positive 16-bit integer, so the test is an integer compare (NaNs do
-// not occur in a ReLU output).  `q32` is the first row of the warp inside the row tile.
-struct MaskLoads {
-  uint4 v[8];
+// The ReLU mask of a 32-row x 64-column block (16-bit elements) comes into the warp's mask slot in
+// shared memory by TMA, through a tensor map with the geometry and swizzle of the output map, so a
+// lane finds its row's 128 bytes where it will put its own results in the staging slice.  A positive
+// 16-bit float is a positive 16-bit integer, so "mask > 0" is one packed integer compare per pair
+// (NaNs do not occur in a ReLU output).  Requests run one or two blocks ahead of the block being
+// worked on (as many as the warp has slots), across tile boundaries: a slot is requested again as
+// soon as its words have been taken out.
+struct MaskSlot {
+  uint32_t addr;       // shared-memory address of the warp's first 4 KB slot
+  uint32_t bar;        // mbarrier of the first slot (one per slot, 8 bytes apart)
+  uint32_t nslots;     // 1 or 2: how many blocks ahead the requests run
+  uint32_t issued, consumed;
+  // the block the next request is for: the warp's blocks in the order it will work on them
+  TileWalker walker;
+  int tile, c0, tile_step, total_tiles, sub_w, sub_h, sub_n;
 };
 
-__device__ __forceinline__ void issue_mask_loads(const GemmArgs& a, const TileCoord& t, int q32, int col, int lane,
-                                                 MaskLoads& m) {
-  const int sh_w = __ffs(a.etw) - 1, sh_h = __ffs(a.eth) - 1;
-  const uint16_t* mask = static_cast<const uint16_t*>(a.relu_mask);
-  const int c = col + (lane & 7) * 8;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int row = q32 + i * 4 + (lane >> 3);
-    const int w = t.w0 + (row & (a.etw - 1)), h = t.h0 + ((row >> sh_w) & (a.eth - 1)), n = t.n0 + (row >> (sh_w + sh_h));
-    const bool valid = w < a.ext_w && h < a.ext_h && n < a.ext_n && c < a.ext_cols;
-    m.v[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (valid)
-      m.v[i] = __ldg(reinterpret_cast<const uint4*>(mask + (long long)n * a.stride_n + (long long)h * a.stride_h +
-                                                    (long long)w * a.stride_w + c));
+// Requests the mask of the next block that has none yet (if any is left).
+__device__ __forceinline__ void request_mask_block(const GemmArgs& a, const WarpStore& ws, MaskSlot& ms) {
+  if (ms.tile >= ms.total_tiles) return;
+  const TileCoord t = ms.walker.coord(a);
+  const uint32_t slot = ms.issued % ms.nslots;
+  if (elect_one()) {
+    mbar_arrive_expect_tx(ms.bar + 8u * slot, 4096u);
+    tma_load_4d(ms.addr + slot * 4096u, &a.mask_map, ms.bar + 8u * slot, t.nf0 + ms.c0, t.w0 + ms.sub_w + ws.qw,
+                t.h0 + ms.sub_h + ws.qh, t.n0 + ms.sub_n + ws.qn);
   }
-}
-
-__device__ __forceinline__ uint2 finish_mask(const MaskLoads& m, int lane, uint8_t* table) {
-  __syncwarp();  // the previous block's table has been read by every lane
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const uint32_t wd[4] = {m.v[i].x, m.v[i].y, m.v[i].z, m.v[i].w};
-    uint32_t byte = 0u;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const uint32_t hit = __vcmpgts2(wd[k], 0u);  // 0xFFFF in every halfword that is > 0 as a signed integer
-      byte |= ((hit & 1u) | ((hit >> 15) & 2u)) << (2 * k);
-    }
-    table[(i * 4 + (lane >> 3)) * 8 + (lane & 7)] = (uint8_t)byte;
+  ++ms.issued;
+  ms.c0 += 64;
+  if (ms.c0 >= a.bn) {
+    ms.c0 = 0;
+    ms.tile += ms.tile_step;
+    ms.walker.advance();
   }
-  __syncwarp();
-  return *reinterpret_cast<const uint2*>(table + lane * 8);
 }
 
 // The common case of the staged epilogue, kept short because a lone warp per scheduler is
@@ -500,10 +490,10 @@ __device__ __forceinline__ uint2 finish_mask(const MaskLoads& m, int lane, uint8
 // packed pairs in that type - the arithmetic of separate convolution, bias-add and activation
 // passes.  MASK: the result is additionally zeroed wherever a.relu_mask is not positive.
 template <typename OutT, bool MASK>
-__device__ __forceinline__ void epilogue_tile_tma_fast(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc,
+__device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc,
                                                        int lane, bool zero, const WarpStore& ws,
-                                                       uint32_t& store_count, uint32_t bias_s, int q32,
-                                                       uint8_t* mask_table, MaskLoads& mask_loads) {
+                                                       uint32_t& store_count, uint32_t bias_s, int q32, MaskSlot& ms,
+                                                       volatile int* abort_flag) {
   const int act = a.act;
 #pragma unroll 1
   for (int c0 = 0; c0 < a.bn; c0 += 64, ++store_count) {
@@ -533,24 +523,35 @@ __device__ __forceinline__ void epilogue_tile_tma_fast(const GemmArgs& a, const 
       for (int g = 0; g < 8; ++g)
         bv[g] = has_bias ? ld_shared_v4(bias_s + (uint32_t)(t.nf0 + c0 + g * 8) * 2u) : make_uint4(0u, 0u, 0u, 0u);
     }
-    uint2 keep = make_uint2(0u, 0u);
+    uint4 mk[MASK ? 8 : 1];
     if (MASK) {
-      // this block's loads were issued one block ago (or before the accumulator wait); turn them
-      // into bits, then request the next block's
-      keep = finish_mask(mask_loads, lane, mask_table);
-      if (c0 + 64 < a.bn) issue_mask_loads(a, t, q32, t.nf0 + c0 + 64, lane, mask_loads);
+      // this block's mask was requested earlier: take the lane's row out of the slot as keep masks,
+      // then let the next request reuse the slot
+      const uint32_t mslot = ms.consumed % ms.nslots;
+      if (!mbar_wait(ms.bar + 8u * mslot, (ms.consumed / ms.nslots) & 1u, abort_flag, g_error_record, a.wait_limit_ns, 0x700u))
+        return false;
+      const uint32_t row_addr = ms.addr + mslot * 4096u + (uint32_t)lane * 128u;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const uint4 m = ld_shared_v4(row_addr + (uint32_t)((g ^ (lane & 7)) << 4));
+        mk[g] = make_uint4(__vcmpgts2(m.x, 0u), __vcmpgts2(m.y, 0u), __vcmpgts2(m.z, 0u), __vcmpgts2(m.w, 0u));
+      }
+      __syncwarp();  // every lane holds its masks: the slot may be overwritten
+      ++ms.consumed;
+      request_mask_block(a, ws, ms);
     }
     wait_slice_free(ws, lane);
     if (threadIdx.x == 64) PDNN_TRACE(8, store_count);
     if (!zero) tmem_wait_ld();
     if (threadIdx.x == 64) PDNN_TRACE(9, store_count);
     uint8_t* row_ptr = ws.buf + slot * 4096u + (size_t)lane * 128;
-    fast_convert_store<OutT, MASK>(acc0, zero, has_bias, bv, act, row_ptr, lane, 0, keep);
-    fast_convert_store<OutT, MASK>(acc1, zero, has_bias, bv + 4, act, row_ptr, lane, 4, keep);
+    fast_convert_store<OutT, MASK>(acc0, zero, has_bias, bv, act, row_ptr, lane, 0, mk);
+    fast_convert_store<OutT, MASK>(acc1, zero, has_bias, bv + 4, act, row_ptr, lane, 4, MASK ? mk + 4 : mk);
     if (threadIdx.x == 64) PDNN_TRACE(10, store_count);
     issue_slice_store(a, t, ws, slot, t.nf0 + c0, lane);
     if (threadIdx.x == 64) PDNN_TRACE(11, store_count);
   }
+  return true;
 }
 
 // EPI selects the epilogue compiled into the instantiation: 0 = direct stores from registers,
@@ -612,7 +613,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
   uint8_t* ring_mem = smem + res_bytes + (pair ? 0u : (size_t)grp * ring_bytes);
   // staging slices for the TMA-store epilogue (per group: 4 warps x nsw slices), then the barrier
   // block, then the bias copy
-  const uint32_t group_staging = a.tma_store ? (uint32_t)a.nsw * 4u * 4096u : 0u;
+  const uint32_t group_staging = a.tma_store ? ((uint32_t)a.nsw + (EPI == 3 ? (uint32_t)a.mask_slots : 0u)) * 4u * 4096u : 0u;
   const uint32_t staging_off = res_bytes + (uint32_t)rings * ring_bytes;
   const uint32_t bar_off = staging_off + (uint32_t)groups * group_staging;
   uint8_t* bar_mem = smem + bar_off;
@@ -646,6 +647,8 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       }
     }
     mbar_init(bres_bar, 1);
+    if (EPI == 3)  // one barrier per epilogue warp for its mask slot, after the bias copy
+      for (int i = 0; i < 16; ++i) mbar_init(bar_base + (uint32_t)kBarBlockBytes + (uint32_t)a.bias_smem_bytes + 8u * (uint32_t)i, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -1017,15 +1020,32 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     const int wslot = role - 2;  // 0..3: which staging slices of the group this warp owns
     WarpStore ws;
     ws.nsw = a.nsw;
-    const uint32_t my_staging = staging_off + (uint32_t)grp * group_staging + (uint32_t)wslot * (uint32_t)a.nsw * 4096u;
+    const uint32_t warp_slices = (uint32_t)a.nsw + (EPI == 3 ? (uint32_t)a.mask_slots : 0u);  // the last ones are the mask slots
+    const uint32_t my_staging = staging_off + (uint32_t)grp * group_staging + (uint32_t)wslot * warp_slices * 4096u;
     ws.buf = smem + my_staging;
     ws.buf_addr = base + my_staging;
+    [[maybe_unused]] MaskSlot mask_slot;
+    mask_slot.addr = base + my_staging + (uint32_t)a.nsw * 4096u;
+    mask_slot.bar = bar_base + (uint32_t)kBarBlockBytes + (uint32_t)a.bias_smem_bytes + 16u * (uint32_t)(grp * 4 + wslot);
+    mask_slot.nslots = (uint32_t)a.mask_slots;
+    mask_slot.issued = mask_slot.consumed = 0;
     ws.qw = (q * 32) % a.etw;
     ws.qh = ((q * 32) / a.etw) % a.eth;
     ws.qn = (q * 32) / (a.etw * a.eth);
     uint32_t buf = 0, aph = 0;
     TileWalker walker;
     walker.init(a, first_tile, tile_step);
+    if constexpr (EPI == 3) {
+      mask_slot.walker = walker;
+      mask_slot.tile = first_tile;
+      mask_slot.c0 = 0;
+      mask_slot.tile_step = tile_step;
+      mask_slot.total_tiles = total_tiles;
+      mask_slot.sub_w = sub_w;
+      mask_slot.sub_h = sub_h;
+      mask_slot.sub_n = sub_n;
+      for (uint32_t i = 0; i < mask_slot.nslots; ++i) request_mask_block(a, ws, mask_slot);
+    }
 #pragma unroll 1
     for (int tile = first_tile; tile < total_tiles; tile += tile_step, walker.advance()) {
       TileCoord t = walker.coord(a);
@@ -1033,22 +1053,15 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       t.h0 += sub_h;
       t.n0 += sub_n;
       if (warp == 2 && lane == 0) PDNN_TRACE(6, tcount);
-      [[maybe_unused]] MaskLoads mask_loads;
-      if constexpr (EPI == 3) issue_mask_loads(a, t, q * 32, t.nf0, lane, mask_loads);  // before the wait: the tile is known
       if (!mbar_wait(acc_full_bar((int)buf), aph, abort_flag, g_error_record, a.wait_limit_ns, 0x400u + buf)) break;
       tc_fence_after_sync();
       if (warp == 2 && lane == 0) PDNN_TRACE(4, tcount);
       const uint32_t tmem_acc = grp_tmem + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
       const bool zero = !(t.ks_end > t.ks_begin);
       if constexpr (EPI >= 2) {
-        // the sign-bit tables of the eight epilogue warps follow the bias copy
-        uint8_t* mask_table = bar_mem + kBarBlockBytes + a.bias_smem_bytes + (grp * 4 + wslot) * 256;
-        if constexpr (EPI == 3) {
-          epilogue_tile_tma_fast<OutT, true>(a, t, tmem_acc, lane, zero, ws, store_count, bias_s, q * 32, mask_table, mask_loads);
-        } else {
-          MaskLoads unused;
-          epilogue_tile_tma_fast<OutT, false>(a, t, tmem_acc, lane, zero, ws, store_count, bias_s, q * 32, mask_table, unused);
-        }
+        if (!epilogue_tile_tma_fast<OutT, EPI == 3>(a, t, tmem_acc, lane, zero, ws, store_count, bias_s, q * 32, mask_slot,
+                                                    abort_flag))
+          break;
       } else if constexpr (EPI == 1) {
         epilogue_tile_tma<OutT>(a, t, tmem_acc, lane, zero, ws, store_count);
       } else {
@@ -1326,6 +1339,10 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
                   (g.bias == nullptr || aligned16(g.bias)))
                      ? 1
                      : 0;
+    // the mask tensor is read through a map with the geometry of the output map
+    if (g.epi_fast && g.relu_mask != nullptr &&
+        !make_map(&g.mask_map, g.out_dtype, false, g.relu_mask, out_dims, out_strides, box))
+      g.relu_mask = nullptr;
   }
   const bool split = compute_dtype == PDNN_F32;
   // Two pipelines per CTA, except for 256-column tiles outside pair mode with a reduction of 8 steps or
@@ -1342,7 +1359,7 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   g.bias_smem_bytes = 0;
   g.bias_tile_only = 0;
   if (!g.epi_fast) g.relu_mask = nullptr;  // only the fast epilogue applies the mask; the caller checks
-  g.mask_smem_bytes = g.relu_mask != nullptr ? 8 * 256 : 0;
+  g.mask_smem_bytes = g.relu_mask != nullptr ? 128 : 0;  // the mask slots' barriers; the slots count as staging
   if (g.pair && (split || g.groups != 2 || !g.tma_store)) return false;  // the caller plans again without pairing
   if (g.epi_fast && g.bias != nullptr) {
     const int padded = ceil_div(g.n_tiles * g.bn, 64) * 64;
@@ -1362,7 +1379,8 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   g.b_res = 0;
   g.b_res_bytes = 0;
   const int fixed = 1024 + kBarBlockBytes + g.bias_smem_bytes + g.mask_smem_bytes;
-  auto staging = [&](int nsw) { return g.tma_store ? g.groups * 4 * nsw * 4096 : 0; };
+  g.mask_slots = g.relu_mask != nullptr ? 1 : 0;
+  auto staging = [&](int nsw) { return g.tma_store ? g.groups * 4 * (nsw + g.mask_slots) * 4096 : 0; };
   // A small filter (all taps, all column tiles) is kept in shared memory for the whole kernel:
   // the filter tiles are the part of the L2 -> SM traffic that never changes.
   if (g.pair) {
@@ -1371,6 +1389,10 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
     auto stages_with = [&](int nsw) { return (avail - staging(nsw)) / (int)stage; };
     g.nsw = stages_with(2) >= 4 ? 2 : 1;
     g.nsw = PDNN_KNOB("PDNN_NSW", g.nsw);
+    if (g.mask_slots == 1) {  // a second mask slot per warp where four stages remain
+      g.mask_slots = 2;
+      if (stages_with(g.nsw) < 4) g.mask_slots = 1;
+    }
     g.stages = std::min(PDNN_KNOB("PDNN_STAGES", kMaxStages), stages_with(g.nsw));
     return g.stages >= 2;
   }
@@ -1401,6 +1423,10 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   auto stages_with = [&](int nsw) { return (avail - staging(nsw)) / (g.groups * (int)stage); };
   g.nsw = stages_with(2) >= 3 ? 2 : 1;
   g.nsw = PDNN_KNOB("PDNN_NSW", g.nsw);
+  if (g.mask_slots == 1) {  // a second mask slot per warp where four stages remain
+    g.mask_slots = PDNN_KNOB("PDNN_MASK_SLOTS", 2);
+    if (g.mask_slots == 2 && stages_with(g.nsw) < 4) g.mask_slots = 1;
+  }
   g.stages = std::min(PDNN_KNOB("PDNN_STAGES", kMaxStages), stages_with(g.nsw));
   if (g.stages < 2 && g.groups == 2) {  // very wide stages: one pipeline with a deeper ring
     g.groups = 1;
@@ -1449,7 +1475,8 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   // At least 120 KB, so that two CTAs never share an SM: the second one would wait for TMEM
   // columns the first one holds.
   size_t smem = 1024 + (size_t)g.b_res_bytes + (size_t)rings * g.stages * stage +
-                (g.tma_store ? (size_t)g.groups * g.nsw * 4 * 4096 : 0) + kBarBlockBytes + (size_t)g.bias_smem_bytes + (size_t)g.mask_smem_bytes;
+                (g.tma_store ? (size_t)g.groups * (g.nsw + g.mask_slots) * 4 * 4096 : 0) + kBarBlockBytes +
+                (size_t)g.bias_smem_bytes + (size_t)g.mask_smem_bytes;
   smem = std::max<size_t>(smem, 120 * 1024);
   if (smem > (size_t)kSmemBudget) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: plan needs %zu bytes of shared memory", smem);
   // The opt-in to large dynamic shared memory is a per-device attribute of each kernel: it is made
