@@ -339,7 +339,7 @@ def parity_check(torch, pd, workloads, net, images=(0, BATCH - 1), tol=2e-2):
                 y = orc.conv2d(orc.FORWARD, x, net.weights[i].float().cpu().numpy(), po)
                 y = torch.from_numpy(y).half().float().numpy().reshape(-1, p.features)
                 y = torch.from_numpy(y + net.biases[i].float().cpu().numpy()[None, :]).half().float().numpy().ravel()
-                ref = np.maximum(y, 0)
+                ref = np.maximum(y, 0) if l.activation == pd.ACT_RELU else y
             else:
                 po = orc.PoolParams(*[getattr(p, f) for f, _ in p._fields_])
                 po.batch = 1
@@ -717,7 +717,7 @@ def run_gpu(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)",
         "data": "synthetic",
         "config": {"workload": "ResNet-50 v1.5 conv stack forward, NHWC fp16, batch 256 per GPU, 53 convs with fused "
-                               "bias+ReLU, 3x3/2 max pool, global 7x7 average pool" if not train_only else
+                               "bias (+ReLU on all but the 4 projection shortcuts), 3x3/2 max pool, global 7x7 average pool" if not train_only else
                                "ResNet-50 v1.5 training-step convs, NHWC fp16, batch 256 per GPU (the `train` object)",
                    "batch_per_gpu": BATCH, "global_batch": BATCH * world, "sharding": "batch, no forward collective",
                    "l2": "activations (103-411 MB per layer) exceed the 126 MB L2; no explicit flush",

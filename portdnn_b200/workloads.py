@@ -43,7 +43,8 @@ def resnet50_v15(batch):
     """ResNet-50 v1.5 conv stack: 7x7/2 stem (explicit pad 3, the reference's 230x230 VALID entry,
     bench/conv2d/resnet_params.def:122), 3x3/2 SAME max pool, bottleneck stages [3,4,6,3] with mid
     widths 64/128/256/512 and expansion 4, stride 2 on the 3x3 of the first block of stages 2-4,
-    1x1 projection shortcuts on first blocks, global 7x7 average pool.  Buffers are named; a
+    1x1 projection shortcuts on first blocks (bias only: the shortcut branch of the network has no
+    ReLU of its own), global 7x7 average pool.  Buffers are named; a
     layer reads ``src`` and writes ``dst``."""
     layers = []
     layers.append(ConvLayer("stem", api.conv_params(batch, 224, 224, 3, 64, 7, 2, pad=3), "input", "a"))
@@ -58,7 +59,8 @@ def resnet50_v15(batch):
             t1, t2, t3, t4 = free[0], free[1], free[2], free[3]
             tag = "s%db%d" % (stage, blk + 1)
             if blk == 0:
-                layers.append(ConvLayer(tag + "_proj", api.conv_params(batch, size, size, cin, cout, 1, stride), cur, t4))
+                layers.append(ConvLayer(tag + "_proj", api.conv_params(batch, size, size, cin, cout, 1, stride), cur, t4,
+                                        api.ACT_NONE))
             layers.append(ConvLayer(tag + "_1x1a", api.conv_params(batch, size, size, cin, mid, 1, 1), cur, t1))
             layers.append(ConvLayer(tag + "_3x3", api.conv_params(batch, size, size, mid, mid, 3, stride), t1, t2))
             size_out = size // stride
@@ -266,10 +268,9 @@ class ConvStackRunner:
         for j in self.src_idx:
             if j >= 0:
                 readers[j] += 1
-        blocks_with_shortcut = {l.name[:-5] for l in layers if l.name.endswith("_proj")}
         self.readers = readers
-        self.fuse_mask = [isinstance(l, ConvLayer) and (readers[i] == 1 or (readers[i] > 1 and self.fuse_accumulate)) and
-                          not (l.name.endswith("_1x1b") and l.name[:-5] in blocks_with_shortcut)
+        self.fuse_mask = [isinstance(l, ConvLayer) and l.activation == api.ACT_RELU and
+                          (readers[i] == 1 or (readers[i] > 1 and self.fuse_accumulate))
                           for i, l in enumerate(layers)]
         stage_of = lambda l: l.name[:2] if l.name[0] == "s" and l.name[1].isdigit() else "stem"
         self.segments = []
@@ -321,13 +322,14 @@ class ConvStackRunner:
             else:
                 continue  # nothing downstream of this layer takes part in the step (the final pool)
             if isinstance(l, ConvLayer):
-                if l.name.endswith("_1x1b"):
-                    self._block_grad[l.name[:-5]] = dy
-                if i in self._masked:
+                if i in self._masked or l.activation == api.ACT_NONE:
                     g = dy
                 else:
                     g = self.scratch[:self.sizes[i]]
                     api.pointwise_grad(api.ACT_RELU, self.acts[i], dy, out=g)
+                if l.name.endswith("_1x1b"):
+                    # the block's output gradient after its ReLU: what the shortcut branch receives too
+                    self._block_grad[l.name[:-5]] = g
                 k = self.conv_ids.index(i)
                 f32_out = self.dtype != self.torch.float32
                 add = self.fuse_accumulate and f32_out

@@ -41,13 +41,13 @@ def opool(orc, p):
 
 
 def oracle_layer(orc, net, i, x, round_out):
-    """Layer i of the runner's table on the host array x: conv + bias + ReLU, or the pool."""
+    """Layer i of the runner's table on the host array x: conv + bias (+ ReLU), or the pool."""
     l, p = net.layers[i], net.layers[i].params
     if isinstance(l, workloads.ConvLayer):
         y = orc.conv2d(orc.FORWARD, x, host(net.weights[i]), oparams(orc, p))
         y = round_out(y)                                            # the convolution's own rounding
         y = round_out(y.reshape(-1, p.features) + host(net.biases[i])[None, :]).ravel()   # bias add
-        return np.maximum(y, 0)                                     # ReLU
+        return np.maximum(y, 0) if l.activation == pd.ACT_RELU else y   # ReLU
     return orc.pool_forward(l.op, x, opool(orc, p))
 
 
@@ -133,12 +133,13 @@ def test_resnet50_train_step_gradients(orc):
         else:
             continue
         if isinstance(l, workloads.ConvLayer):
-            if l.name.endswith("_1x1b"):
-                block_grad[l.name[:-5]] = dy
             # ReLU gradient (src/pointwise/kernels.h:205-233), unless the producing input backprop applied it
-            g = dy if masked else orc.pointwise_grad(0, host(net.acts[i]), dy)
+            # or the layer has no ReLU (the projection shortcuts)
+            g = dy if (masked or l.activation == pd.ACT_NONE) else orc.pointwise_grad(0, host(net.acts[i]), dy)
             if masked:  # a masked gradient is zero wherever the activation is: the mask really was applied
                 assert not np.any(dy[host(net.acts[i]) <= 0] != 0), l.name
+            if l.name.endswith("_1x1b"):
+                block_grad[l.name[:-5]] = g  # the shortcut branch receives the block's gradient after its ReLU
             x = host(net.input if j < 0 else net.acts[j])
             dw_ref = orc.conv2d(orc.FILTER_BACKPROP, x, g, oparams(orc, p))
             e = rel_err(host(net.bucket.view(net.conv_ids.index(i))), dw_ref)
