@@ -151,7 +151,10 @@ int pdnn_conv2d_fused(int dtype, const void* input, const void* filter, void* ou
  *  - accumulate: InputBackprop: dx already holds the gradient that arrived through another
  *    reader of the tensor (a shortcut branch); this call adds its own to it, dx += conv_backprop(dy, w),
  *    and the mask of relu_forward_output, when given, applies to the sum - the reference chain of
- *    an input backprop into a temporary, binaryop::launch<Add> and the ReLU gradient.
+ *    an input backprop into a temporary, binaryop::launch<Add> and the ReLU gradient.  The value 2
+ *    says that dx already carries that mask (every earlier contribution applied it): the result is
+ *    the same, but positions a strided convolution does not reach are left untouched instead of
+ *    being read, masked and written again.
  *    FilterBackprop: dW += gradient (gradient accumulation over micro-batches, or into a buffer the
  *    caller zeroed).  With fp32 gradients the pixel splits of the kernel add their tiles to dW
  *    directly (TMA reduction) instead of writing partial sums for a second kernel, so no workspace

@@ -216,7 +216,7 @@ def conv2d(pass_, inp, fil, params, algorithm=ALGO_IM2COL, out=None, workspace=N
         if relu_forward_output is not None and relu_forward_output.numel() != n_out:
             raise ValueError("relu_forward_output must have the shape of the input gradient")
         fus = _BackpropFusion(relu_forward_output.data_ptr() if relu_forward_output is not None else None, int(output_f32),
-                              int(accumulate))
+                              int(accumulate))  # accumulate: False / True, or 2 (dx already carries the mask)
         _check(lib().pdnn_conv2d_backprop_fused(pass_, _dtype_code(inp), _ptr(inp), _ptr(fil), _ptr(out),
                                                 ctypes.byref(params), algorithm, ctypes.byref(fus), _ptr(workspace),
                                                 ctypes.c_size_t(ws_elems), _stream()))

@@ -1961,8 +1961,11 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
 // relu_mask (may be null): the forward output of the layer that produced the tensor dx is the gradient
 // of; dx is zeroed wherever it is not positive (in the epilogue where the fast epilogue runs, else
 // by a pointwise pass afterwards).
+// accumulate: 0 dx = result; 1 dx += result (the mask then applies to the sum); 2 as 1 where dx already
+// carries the same mask, so that positions this convolution does not reach (parity classes without a
+// tap) are left as they are.
 int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, const PdnnConv2DParams& p,
-                        const void* relu_mask, bool accumulate, cudaStream_t s, bool try_halo = true) {
+                        const void* relu_mask, int accumulate, cudaStream_t s, bool try_halo = true) {
   bool mask_pending = false;  // some parity class could not apply the mask in its epilogue
   const size_t es = dtype_size(dtype);
   const int sms = device_sm_count();
@@ -2005,6 +2008,7 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
       for (int r = 0; r < p.window_rows; ++r)
         for (int c = 0; c < p.window_cols; ++c)
           if (pos_mod(qh + p.pad_rows - r, p.stride_rows) == 0 && pos_mod(qw + p.pad_cols - c, p.stride_cols) == 0) ++class_taps;
+      if (class_taps == 0 && accumulate == 2) continue;  // nothing to add, and what is there is masked already
       const int ksteps_all = class_taps * ceil_div(p.features, epr);
       // Pair mode as in the forward pass (two row tiles share the filter tile of a stage); the output
       // columns are the channels here.
@@ -2536,7 +2540,7 @@ int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, c
               const PdnnConvEpilogue* epi, const PdnnBackpropFusion* fusion, void* ws, size_t ws_elems, cudaStream_t s) {
   const void* relu_mask = fusion != nullptr ? fusion->relu_forward_output : nullptr;
   const bool out_f32 = fusion != nullptr && fusion->output_f32 != 0 && dtype != PDNN_F32;
-  const bool accumulate = fusion != nullptr && fusion->accumulate != 0;
+  const int accumulate = fusion != nullptr ? fusion->accumulate : 0;
   switch (pass) {
     case PDNN_FORWARD:
       if (small_c_applicable(dtype, p)) {
@@ -2548,10 +2552,10 @@ int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, c
       return conv_input_backprop(dtype, in, fil, out, p, relu_mask, accumulate, s);
     case PDNN_FILTER_BACKPROP:
       if (small_c_applicable(dtype, p)) {
-        const int st = conv_filter_backprop_small_c(dtype, in, fil, out, p, out_f32, accumulate, ws, ws_elems, s);
+        const int st = conv_filter_backprop_small_c(dtype, in, fil, out, p, out_f32, accumulate != 0, ws, ws_elems, s);
         return st == -1 ? kNeedsDirect : st;
       }
-      return conv_filter_backprop(dtype, in, fil, out, p, out_f32, accumulate, ws, ws_elems, s);
+      return conv_filter_backprop(dtype, in, fil, out, p, out_f32, accumulate != 0, ws, ws_elems, s);
   }
   return fail(PDNN_INVALID_PARAMETER, "bad pass %d", pass);
 }

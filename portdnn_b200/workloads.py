@@ -337,18 +337,17 @@ class ConvStackRunner:
                            output_f32=f32_out, accumulate=add,
                            workspace=self.fbp_workspace if i in self.fbp_ws else None)
                 if j >= 0:
-                    # The ReLU mask of tensor j goes into the input backprop that completes its gradient:
-                    # the only one, or the last of several, which then also adds to what the others left.
-                    self._arrived[j] = self._arrived.get(j, 0) + 1
-                    last_reader = self._arrived[j] == self.readers[j]
-                    mask = self.acts[j] if self.fuse_mask[j] and last_reader else None
+                    # The ReLU mask of tensor j goes into every input backprop that contributes to its
+                    # gradient (the mask of a sum is the sum of the masked terms), so a later contribution
+                    # adds to a gradient that is masked already and may skip what it does not reach.
+                    mask = self.acts[j] if self.fuse_mask[j] else None
 
                     def ibp(dst, accumulate, g=g, i=i, p=p, mask=mask):
                         if accumulate and not self.fuse_accumulate:
                             return False
                         api.conv2d(api.INPUT_BACKPROP, g, self.weights[i], p, algorithm=api.ALGO_IM2COL, out=dst,
                                    relu_forward_output=mask if (accumulate or dst is self.grads[j]) else None,
-                                   accumulate=accumulate)
+                                   accumulate=(2 if mask is not None else 1) if accumulate else 0)
 
                     self._add_grad(j, ibp)
                     if mask is not None:

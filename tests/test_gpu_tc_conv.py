@@ -227,7 +227,7 @@ def test_fused_backprop_forms_against_oracle(orc, dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", ["f16", "bf16", "f32"])
-@pytest.mark.parametrize("masked", [True, False])
+@pytest.mark.parametrize("masked", [True, False, "premasked"])
 @pytest.mark.parametrize("shape", BWD_SHAPES + [(2, 20, 20, 24, 40, 3, 2, True, None), (3, 9, 9, 5, 7, 3, 1, True, None),
                                                 (4, 28, 28, 128, 256, 1, 2, True, None), (2, 14, 14, 512, 256, 1, 1, True, None)])
 def test_accumulating_input_backprop_against_oracle(orc, dtype, masked, shape):
@@ -240,9 +240,11 @@ def test_accumulating_input_backprop_against_oracle(orc, dtype, masked, shape):
     rng = np.random.default_rng(77)
     y_prev = rounded(np.maximum(rng.standard_normal(n * h * w * c), 0).astype(np.float32), dtype)
     before = rounded(rng.standard_normal(n * h * w * c).astype(np.float32), dtype)
+    if masked == "premasked":  # accumulate = 2: dx already carries the mask, untouched positions may be skipped
+        before = orc.pointwise_grad(0, y_prev, before)
     dx = to_dev(before, dtype)
     pd.conv2d(pd.INPUT_BACKPROP, to_dev(dy, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_IM2COL, out=dx,
-              relu_forward_output=to_dev(y_prev, dtype) if masked else None, accumulate=True)
+              relu_forward_output=to_dev(y_prev, dtype) if masked else None, accumulate=2 if masked == "premasked" else True)
     assert_no_device_error()
     ref = before + orc.conv2d(orc.INPUT_BACKPROP, dy, wt, po)
     if masked:
