@@ -22,9 +22,6 @@
 #include "umma.cuh"
 
 #include <algorithm>
-#ifdef PDNN_TUNE
-#include <cstdlib>
-#endif
 #include <cstring>
 #include <mutex>
 
@@ -43,28 +40,6 @@ constexpr int kBarsPerGroup = 3 * kMaxStages + 4;  // full, empty, ready per sta
 constexpr int kBarBlockBytes = 512;                // barriers of two groups, the resident-B barrier, TMEM slot, abort flag
 
 __device__ unsigned g_error_record[4];
-
-// Plan overrides for kernel development: compiled in only with -DPDNN_TUNE (the library is never
-// built that way), in which case the named environment variable, when set, replaces the heuristic.
-#ifdef PDNN_TUNE
-int tune_knob(const char* name, int dflt) {
-  const char* e = getenv(name);
-  return e != nullptr && *e != 0 ? atoi(e) : dflt;
-}
-#define PDNN_KNOB(name, dflt) tune_knob(name, dflt)
-// Timeline of CTA 0: SM clock at a few points of each tile's life.
-constexpr int kTraceTiles = 512, kTraceKinds = 12;
-__device__ long long g_trace[kTraceKinds * kTraceTiles];
-#define PDNN_TRACE(kind, idx)                                                                                \
-  do {                                                                                                       \
-    if (blockIdx.x == 0 && (idx) < (unsigned)kTraceTiles) g_trace[(kind) * kTraceTiles + (idx)] = clock64(); \
-  } while (0)
-#else
-#define PDNN_KNOB(name, dflt) (dflt)
-#define PDNN_TRACE(kind, idx) \
-  do {                        \
-  } while (0)
-#endif
 
 // One reduction step of a forward-style GEMM: which input map, at which pixel offset, against which
 // filter tap.  In halo mode an entry stands for `cnt` taps that differ only by one input row each
@@ -499,7 +474,6 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
   for (int c0 = 0; c0 < a.bn; c0 += 64, ++store_count) {
     const uint32_t slot = store_count & (uint32_t)(ws.nsw - 1);
     uint32_t acc0[32], acc1[32];
-    if (threadIdx.x == 64) PDNN_TRACE(7, store_count);
     if (!zero) {  // issued before waiting for the staging slice
       tmem_ld_32x32(tmem_acc + (uint32_t)c0, acc0);
       tmem_ld_32x32(tmem_acc + (uint32_t)(c0 + 32), acc1);
@@ -541,15 +515,11 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
       request_mask_block(a, ws, ms);
     }
     wait_slice_free(ws, lane);
-    if (threadIdx.x == 64) PDNN_TRACE(8, store_count);
     if (!zero) tmem_wait_ld();
-    if (threadIdx.x == 64) PDNN_TRACE(9, store_count);
     uint8_t* row_ptr = ws.buf + slot * 4096u + (size_t)lane * 128;
     fast_convert_store<OutT, MASK>(acc0, zero, has_bias, bv, act, row_ptr, lane, 0, mk);
     fast_convert_store<OutT, MASK>(acc1, zero, has_bias, bv + 4, act, row_ptr, lane, 4, MASK ? mk + 4 : mk);
-    if (threadIdx.x == 64) PDNN_TRACE(10, store_count);
     issue_slice_store(a, t, ws, slot, t.nf0 + c0, lane);
-    if (threadIdx.x == 64) PDNN_TRACE(11, store_count);
   }
   return true;
 }
@@ -856,7 +826,6 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       const uint32_t lo_off = part_bytes >> 4;
       int s = 0;
       uint32_t ph = 0;
-      [[maybe_unused]] uint32_t tcount = 0;
       uint32_t buf = 0, aph = 0;  // accumulator buffer of this tile and the parity of its barriers
       bool ok = true;
       if (b_res && first_tile < total_tiles) ok = mbar_wait(bres_bar, 0u, abort_flag, g_error_record, a.wait_limit_ns, 0x600u);
@@ -898,9 +867,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
 #pragma unroll 1
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, walker.advance()) {
         const TileCoord t = walker.coord(a);
-        if (grp == 0) PDNN_TRACE(0, tcount);
         if (!mbar_wait(acc_empty_bar((int)buf), aph ^ 1u, abort_flag, g_error_record, a.wait_limit_ns, 0x200u + buf)) break;
-        if (grp == 0) PDNN_TRACE(1, tcount);
         tc_fence_after_sync();
         const uint32_t d_tmem = grp_tmem + buf * acc_stride;
         uint32_t accumulate = 0u;
@@ -919,7 +886,6 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
                 ok = false;
                 break;
               }
-              if (grp == 0 && tap == 0 && cb == 0) PDNN_TRACE(2, tcount);
               // no tcgen05 fence here: the stage was written by TMA and is read by the MMA, both in
               // the async proxy, and the mbarrier's complete_tx orders them
               // start addresses stay below 2^18, so adding to the low descriptor word never carries
@@ -1001,8 +967,6 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
           }
         }
         if (!ok) break;
-        if (grp == 0) PDNN_TRACE(3, tcount);
-        ++tcount;
         if (t.ks_end > t.ks_begin) warp_commit(acc_full_bar((int)buf));
         else if (elect_one()) mbar_arrive(acc_full_bar((int)buf));  // nothing to accumulate: the epilogue writes zeros
         if (++buf == acc_bufs) {
@@ -1016,7 +980,6 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
     [[maybe_unused]] const int row = q * 32 + lane;
     uint32_t store_count = 0;
-    [[maybe_unused]] uint32_t tcount = 0;
     const int wslot = role - 2;  // 0..3: which staging slices of the group this warp owns
     WarpStore ws;
     ws.nsw = a.nsw;
@@ -1052,10 +1015,8 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       t.w0 += sub_w;
       t.h0 += sub_h;
       t.n0 += sub_n;
-      if (warp == 2 && lane == 0) PDNN_TRACE(6, tcount);
       if (!mbar_wait(acc_full_bar((int)buf), aph, abort_flag, g_error_record, a.wait_limit_ns, 0x400u + buf)) break;
       tc_fence_after_sync();
-      if (warp == 2 && lane == 0) PDNN_TRACE(4, tcount);
       const uint32_t tmem_acc = grp_tmem + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
       const bool zero = !(t.ks_end > t.ks_begin);
       if constexpr (EPI >= 2) {
@@ -1070,8 +1031,6 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar((int)buf));
-      if (warp == 2 && lane == 0) PDNN_TRACE(5, tcount);
-      ++tcount;
       if (++buf == acc_bufs) {
         buf = 0;
         aph ^= 1u;
@@ -1251,8 +1210,6 @@ bool choose_box_halo(int W, int H, int rows, int* tw, int* th) {
 bool want_narrow(int ksteps, int cols) { return ksteps <= 4 || cols <= 128; }
 
 int pick_bn(long long row_tiles, int cols, int unit, int max_bn, int sms, int ksteps = 1 << 30) {
-  const int forced = PDNN_KNOB("PDNN_BN", 0);
-  if (forced > 0 && forced <= max_bn && forced % unit == 0 && forced % 64 == 0 && cols >= forced) return forced;
   if (want_narrow(ksteps, cols)) max_bn = std::min(max_bn, 128);
   sms *= 2;  // two pipelines per CTA work on two tiles at a time
   // cost ~ waves * (bn + fixed overhead); unit: granularity the B loader needs
@@ -1351,7 +1308,7 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   {
     const int steps = g.a_mn ? g.slabs_per_split : g.num_taps * g.cblocks * (g.halo ? 3 : 1);
     const int dflt = (!g.a_mn && !g.pair && g.bn == 256 && steps >= 8) ? 1 : 2;
-    g.groups = split ? 1 : PDNN_KNOB("PDNN_GROUPS", dflt);
+    g.groups = split ? 1 : dflt;
   }
   g.acc_stride = std::max(32, next_pow2(g.bn));
   g.acc_bufs = g.groups * 2 * g.acc_stride <= 512 ? 2 : 1;
@@ -1388,12 +1345,11 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
     const int avail = kSmemBudget - fixed;
     auto stages_with = [&](int nsw) { return (avail - staging(nsw)) / (int)stage; };
     g.nsw = stages_with(2) >= 4 ? 2 : 1;
-    g.nsw = PDNN_KNOB("PDNN_NSW", g.nsw);
     if (g.mask_slots == 1) {  // a second mask slot per warp where four stages remain
       g.mask_slots = 2;
       if (stages_with(g.nsw) < 4) g.mask_slots = 1;
     }
-    g.stages = std::min(PDNN_KNOB("PDNN_STAGES", kMaxStages), stages_with(g.nsw));
+    g.stages = std::min(kMaxStages, stages_with(g.nsw));
     return g.stages >= 2;
   }
   if (!g.a_mn && !split && g.tma_store && g.b_batch_mul == 0) {
@@ -1403,9 +1359,7 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
       return res <= kMaxResidentB && res % 1024 == 0 &&
              (kSmemBudget - fixed - (int)res - staging(1)) / (g.groups * a_stage) >= (g.halo ? 2 : 3);
     };
-    const int bres_knob = PDNN_KNOB("PDNN_BRES", -1);  // 0: never resident, 2: per-column-tile only
-    if (bres_knob == 0 && !g.halo) {
-    } else if (fits(res_all) && bres_knob != 2) {
+    if (fits(res_all)) {
       g.b_res = 1;
       g.b_res_bytes = (unsigned)res_all;
       stage = (unsigned)a_stage;
@@ -1422,12 +1376,11 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   const int avail = kSmemBudget - fixed - (int)g.b_res_bytes;
   auto stages_with = [&](int nsw) { return (avail - staging(nsw)) / (g.groups * (int)stage); };
   g.nsw = stages_with(2) >= 3 ? 2 : 1;
-  g.nsw = PDNN_KNOB("PDNN_NSW", g.nsw);
   if (g.mask_slots == 1) {  // a second mask slot per warp where four stages remain
-    g.mask_slots = PDNN_KNOB("PDNN_MASK_SLOTS", 2);
-    if (g.mask_slots == 2 && stages_with(g.nsw) < 4) g.mask_slots = 1;
+    g.mask_slots = 2;
+    if (stages_with(g.nsw) < 4) g.mask_slots = 1;
   }
-  g.stages = std::min(PDNN_KNOB("PDNN_STAGES", kMaxStages), stages_with(g.nsw));
+  g.stages = std::min(kMaxStages, stages_with(g.nsw));
   if (g.stages < 2 && g.groups == 2) {  // very wide stages: one pipeline with a deeper ring
     g.groups = 1;
     g.acc_bufs = 2 * g.acc_stride <= 512 ? 2 : 1;
@@ -1841,7 +1794,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   // rows, so each column becomes one reduction step over one copy (halo mode), provided the whole
   // filter can stay in shared memory.
   int hw = 0, hh = 0;
-  const bool halo = try_halo && PDNN_KNOB("PDNN_HALO", 1) && dtype != PDNN_F32 && p.stride_rows == 1 && p.stride_cols == 1 &&
+  const bool halo = try_halo && dtype != PDNN_F32 && p.stride_rows == 1 && p.stride_cols == 1 &&
                     p.window_rows >= 2 && p.window_rows <= 15 && p.window_cols <= 8 &&
                     (size_t)p.window_rows * p.window_cols * ceil_div(p.channels, epr) * 128u *
                             (size_t)(ceil_div(p.features, 64) * 64) <= kMaxResidentB &&
@@ -1864,22 +1817,20 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   // Long reductions over filters too large to keep in shared memory are bound by the bytes that
   // pass through an SM's shared memory per MMA (the operand reads of the tensor core and the TMA
   // fills share its 128 bytes per cycle): the two pipelines then share one B tile per stage (pair
-  // mode).  Measured on ResNet-50 shapes it pays ...
-  const int pair_knob = PDNN_KNOB("PDNN_PAIR", -1);  // 0: never, 1: whenever legal
-  // ... from 16 reduction steps on for filters of 128 features and from 32 on for wider ones (which
+  // mode).  Measured on ResNet-50 shapes it pays from 16 reduction steps on for filters of 128
+  // features and from 32 on for wider ones (which
   // do better as single 256-column tiles on one double-buffered pipeline until then), provided the
   // pairs still fill the device: a grid of fewer pair tiles than SMs leaves SMs idle that single
   // tiles would use.
   const int pair_bn_auto = (p.features % 256 == 0 && p.features >= 512) ? 256 : 128;
   const bool pair_auto = ksteps_all >= (p.features >= 256 ? 32 : 16) &&
                          (row_tiles / 2) * ceil_div(p.features, pair_bn_auto) >= sms;
-  const bool pair_wanted = pair_knob < 0 ? pair_auto : pair_knob != 0;
-  const bool pairing = try_halo && !halo && dtype != PDNN_F32 && hwcf && p.features % 128 == 0 && pair_wanted &&
+  const bool pairing = try_halo && !halo && dtype != PDNN_F32 && hwcf && p.features % 128 == 0 && pair_auto &&
                        row_tiles >= 2 && (!epi || epi->beta == 0.f);
   if (pairing) {
     g.pair = 1;
     // 128-column tiles leave room for two accumulator buffers per pipeline; narrow filters use them
-    g.bn = (p.features % 256 == 0 && PDNN_KNOB("PDNN_PAIR_BN", pair_bn_auto) == 256) ? 256 : 128;
+    g.bn = pair_bn_auto;
     if (g.tiles_w % 2 == 0) {
       g.pair_dim = 1;
       g.tiles_w /= 2;
@@ -1895,7 +1846,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     // A single tap with a long reduction into exactly 256 features: one 256-column tile per row tile
     // reads the input once instead of twice and runs as one double-buffered pipeline (measured 12%
     // faster than two 128-column pipelines on 14x14x1024 -> 256).
-    if (dtype != PDNN_F32 && !halo && PDNN_KNOB("PDNN_BN", 0) == 0 && p.window_rows * p.window_cols == 1 &&
+    if (dtype != PDNN_F32 && !halo && p.window_rows * p.window_cols == 1 &&
         ksteps_all >= 16 && p.features == 256 && row_tiles >= 2 * sms)
       g.bn = 256;
   }
@@ -2012,16 +1963,15 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
       const int ksteps_all = class_taps * ceil_div(p.features, epr);
       // Pair mode as in the forward pass (two row tiles share the filter tile of a stage); the output
       // columns are the channels here.
-      const int pair_knob = PDNN_KNOB("PDNN_PAIR", -1);
       // 128-column tiles throughout (the epilogue of this pass is the longer one when it applies the
       // ReLU mask, and two accumulator buffers hide it), pairs from 16 reduction steps on.
       const int pair_bn_auto = 128;
       const bool pair_auto = ksteps_all >= 16 && (row_tiles / 2) * ceil_div(p.channels, pair_bn_auto) >= sms;
       const bool pairing = try_halo && !halo && dtype != PDNN_F32 && hwcf && p.channels % 128 == 0 && row_tiles >= 2 &&
-                           (pair_knob < 0 ? pair_auto : pair_knob != 0);
+                           pair_auto;
       if (pairing) {
         g.pair = 1;
-        g.bn = (p.channels % 256 == 0 && PDNN_KNOB("PDNN_PAIR_BN", pair_bn_auto) == 256) ? 256 : 128;
+        g.bn = pair_bn_auto;
         if (g.tiles_w % 2 == 0) {
           g.pair_dim = 1;
           g.tiles_w /= 2;
@@ -2151,14 +2101,14 @@ FbpPlan plan_filter_backprop(int dtype, const PdnnConv2DParams& p, int sms) {
   const int max_bn = dtype == PDNN_F32 ? 128 : 256;
   // 128-column tiles: two accumulator buffers per pipeline, so the fp32 epilogue of one tile overlaps the
   // reduction of the next (measured over the ResNet-50 layers: 9% less time than 256-column tiles)
-  f.bn = std::min(std::min(max_bn, PDNN_KNOB("PDNN_FBP_BN", 128)), ceil_div(p.features, epr) * epr);
+  f.bn = std::min(std::min(max_bn, 128), ceil_div(p.features, epr) * epr);
   f.n_tiles = ceil_div(p.features, f.bn);
   // At most 64 channels and several taps: a tile holds two taps, the second 64 accumulator rows being
   // the same channels as the next tap sees them, instead of rows that no channel uses.
-  f.tap_pack = (PDNN_KNOB("PDNN_FBP_PACK", 1) && dtype != PDNN_F32 && p.channels <= 64 && p.window_rows * p.window_cols >= 2) ? 2 : 1;
+  f.tap_pack = (dtype != PDNN_F32 && p.channels <= 64 && p.window_rows * p.window_cols >= 2) ? 2 : 1;
   const long long out_tiles = (long long)f.m_tiles * f.n_tiles * ceil_div(p.window_rows * p.window_cols, f.tap_pack);
   const long long total_slabs = (long long)f.slabs_w * f.slabs_h * f.slabs_n;
-  long long want = std::max<long long>(1, ((long long)PDNN_KNOB("PDNN_FBP_WANT", 2) * sms) / out_tiles);
+  long long want = std::max<long long>(1, (2ll * sms) / out_tiles);
   want = std::min<long long>(want, std::max<long long>(1, total_slabs / 8));  // at least 8 slabs per split
   want = std::min<long long>(want, 512);
   f.slabs_per_split = (int)((total_slabs + want - 1) / want);
@@ -2711,12 +2661,5 @@ int tc_read_error_record(unsigned out[4], int clear) {
 }
 
 
-#ifdef PDNN_TUNE
-extern "C" int pdnn_debug_trace(long long* out, int words) {
-  cudaDeviceSynchronize();
-  const size_t n = std::min<size_t>((size_t)words, (size_t)kTraceKinds * kTraceTiles) * sizeof(long long);
-  return cudaMemcpyFromSymbol(out, g_trace, n) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 }  // namespace pdnn
