@@ -64,6 +64,7 @@ struct alignas(64) GemmArgs {
   int tw, th, tn;    // a_mn == 0: pixel box of a row tile; a_mn == 1: pixel box of a reduction slab
   int etw, eth, etn; // pixel box of a row tile as the epilogue sees it
   int num_taps;
+  int cta_pair;      // 1: run by umma_gemm_pair2_kernel (clusters of two CTAs, 256 x 256 tiles)
   int tap_pack;      // a_mn == 1: taps per tile (2: the second 64 rows of the A tile are the next tap's channels)
   int cblocks;       // a_mn == 0: reduction blocks per tap
   int slabs_w, slabs_h, slabs_n, splits, slabs_per_split, split_is_batch;  // a_mn == 1
@@ -1098,6 +1099,223 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
   if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)a.tmem_cols);
 }
 
+// ------------------------------------------------------------------------------------------------
+// CTA-pair variant (tcgen05 cta_group::2) of the forward-style GEMM with a long reduction and 256
+// output columns per tile.  A cluster of two CTAs works on a tile of 256 rows (two neighbouring row
+// tiles, as in pair mode) x 256 columns: each CTA loads its own 128 rows of A and 128 of the 256
+// columns of B per stage, the CTA of rank 0 issues MMAs of 256 x 256 x 16 that read both shared
+// memories, and each CTA finds its 128 rows of the accumulator in its own tensor memory (two
+// buffers of 256 columns, so the epilogue overlaps the next tile).  Per MMA an SM reads 4 KB of A and
+// 4 KB of B from shared memory for 128 cycles of math, against 12 KB for a 128 x 256 tile of one CTA.
+//   warp 0  producer (both CTAs: own A rows, own half of B; the bytes of both count on rank 0's barrier)
+//   warp 1  MMA issuer (rank 0 only; warp 1 of both CTAs owns the TMEM allocation)
+//   warps 2..5  epilogue of the CTA's own 128 rows (packed 16-bit epilogue with TMA stores)
+// Barriers live at the same offsets in both CTAs: full[s] is used in rank 0 only; empty[s] and
+// acc_full[b] are signalled in both CTAs by the issuer's commits; acc_empty[b] of rank 0 collects the
+// eight epilogue warps of the pair.
+template <typename OutT>
+__global__ void __launch_bounds__(192, 1) umma_gemm_pair2_kernel(const __grid_constant__ GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  const GemmArgs& a = args;
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0), lane = (int)(threadIdx.x & 31);
+  const uint32_t rank = cluster_cta_rank();
+  const bool leader = rank == 0;
+  const int S = a.stages;
+  constexpr uint32_t kStage = 2u * kABytes;  // A tile 16 KB + half of the B tile 16 KB
+  const uint32_t staging_off = (uint32_t)S * kStage;
+  const uint32_t bar_off = staging_off + (uint32_t)a.nsw * 4u * 4096u;
+  uint8_t* bar_mem = smem + bar_off;
+  const uint32_t bar_base = base + bar_off;
+  auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(kMaxStages + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (uint32_t)(2 * kMaxStages + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (uint32_t)(2 * kMaxStages + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 8 * (2 * kMaxStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * (2 * kMaxStages + 4) + 4);
+  const uint32_t bias_s = a.bias != nullptr ? bar_base + (uint32_t)kBarBlockBytes : 0u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 8);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&a.a_map[0]);
+    prefetch_tensormap(&a.b_map);
+    prefetch_tensormap(&a.out_map);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), 512u);
+    tmem_relinquish_pair();
+  }
+  // the peer's barriers are initialised before anything of this CTA signals them
+  tc_fence_before_sync();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_wait();
+  grid_launch_dependents();
+  if (a.bias != nullptr) {
+    const OutT* bias = static_cast<const OutT*>(a.bias);
+    uint4* dst = reinterpret_cast<uint4*>(bar_mem + kBarBlockBytes);
+    const int chunks = a.bias_smem_bytes >> 4;
+    for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (i * 8 + 8 <= a.ext_cols) v = __ldg(reinterpret_cast<const uint4*>(bias) + i);
+      dst[i] = v;
+    }
+  }
+  __syncthreads();
+
+  const int total_tiles = a.n_tiles * a.tiles_w * a.tiles_h * a.tiles_n;  // tiles of 256 rows
+  const int first_tile = (int)(blockIdx.x >> 1), tile_step = (int)(gridDim.x >> 1);
+  // this CTA's 128 rows inside the 256-row tile
+  const int sub_w = a.pair_dim == 1 ? (int)rank * a.tw : 0, sub_h = a.pair_dim == 2 ? (int)rank * a.th : 0,
+            sub_n = a.pair_dim == 3 ? (int)rank * a.tn : 0;
+
+  if (warp == 0) {
+    // ------------------------------- producer ------------------------------------------------
+    const int epr = a.epr, cblocks = a.cblocks;
+    const CUtensorMap* bmap = &a.b_map;
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    TileWalker walker;
+    walker.init(a, first_tile, tile_step);
+#pragma unroll 1
+    for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, walker.advance()) {
+      const TileCoord t = walker.coord(a);
+      const int nf0 = t.nf0 + (int)rank * 128;  // this CTA's half of the tile's columns
+#pragma unroll 1
+      for (int tap = 0; tap < a.num_taps && ok; ++tap) {
+        const TapEntry e = a.taps[tap];
+        const CUtensorMap* amap = &a.a_map[e.a_map];
+        const int aw = t.w0 + sub_w + e.dw, ah = t.h0 + sub_h + e.dh, an = t.n0 + sub_n;
+#pragma unroll 1
+        for (int cb = 0, kc = 0; cb < cblocks; ++cb, kc += epr) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g_error_record, a.wait_limit_ns, 0x900u + (unsigned)s)) {
+            ok = false;
+            break;
+          }
+          const uint32_t fb = full_bar(s);
+          if (leader) warp_arrive_expect_tx(fb, 2u * kStage);  // the bytes of both CTAs
+          const uint32_t sa = base + (uint32_t)s * kStage;
+          warp_tma_load_4d_pair(sa, amap, fb, kc, aw, ah, an);
+          warp_tma_load_4d_pair(sa + kABytes, bmap, fb, 0, kc, nf0 / epr, e.b_tap);  // two 64-column blocks
+          if (++s == S) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (rank 0) --------------------------------------
+    if (leader) {
+      const uint64_t a_desc0 = make_smem_desc(0, a.a_lbo, a.a_sbo, a.a_layout);
+      const uint64_t b_desc0 = make_smem_desc(0, a.b_lbo, a.b_sbo, a.b_layout);
+      const uint32_t a_kadv = a.a_kadv >> 4, b_kadv = a.b_kadv >> 4, idesc = a.idesc;
+      const int steps = a.num_taps * a.cblocks;
+      int s = 0;
+      uint32_t ph = 0, buf = 0, aph = 0;
+      bool ok = true;
+#pragma unroll 1
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
+        if (!mbar_wait(acc_empty_bar((int)buf), aph ^ 1u, abort_flag, g_error_record, a.wait_limit_ns, 0xA00u + buf)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * 256u;
+        uint32_t accumulate = 0u;
+#pragma unroll 1
+        for (int ks = 0; ks < steps; ++ks) {
+          if (!mbar_wait(full_bar(s), ph, abort_flag, g_error_record, a.wait_limit_ns, 0xB00u + (unsigned)s)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = (base + (uint32_t)s * kStage) & 0x3FFFFu;  // offset inside the CTA's shared memory
+          const uint64_t da = a_desc0 + (uint64_t)(sa >> 4), db = b_desc0 + (uint64_t)((sa + kABytes) >> 4);
+          warp_mma_f16_pair(d_tmem, da, db, idesc, accumulate);
+          warp_mma_f16_pair(d_tmem, da + a_kadv, db + b_kadv, idesc, 1u);
+          warp_mma_f16_pair(d_tmem, da + 2 * a_kadv, db + 2 * b_kadv, idesc, 1u);
+          warp_mma_f16_pair(d_tmem, da + 3 * a_kadv, db + 3 * b_kadv, idesc, 1u);
+          accumulate = 1u;
+          warp_commit_pair(empty_bar(s), cluster_map_shared(empty_bar(s), 1u));  // both CTAs may refill the stage
+          if (++s == S) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (!ok) break;
+        warp_commit_pair(acc_full_bar((int)buf), cluster_map_shared(acc_full_bar((int)buf), 1u));
+        if (++buf == 2u) {
+          buf = 0;
+          aph ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (own 128 rows) ----------------------------------
+    const int q = warp & 3;  // TMEM lanes [32q, 32q+32)
+    const int wslot = warp - 2;
+    uint32_t store_count = 0;
+    WarpStore ws;
+    ws.nsw = a.nsw;
+    const uint32_t my_staging = staging_off + (uint32_t)wslot * (uint32_t)a.nsw * 4096u;
+    ws.buf = smem + my_staging;
+    ws.buf_addr = base + my_staging;
+    ws.qw = (q * 32) % a.etw;
+    ws.qh = ((q * 32) / a.etw) % a.eth;
+    ws.qn = (q * 32) / (a.etw * a.eth);
+    MaskSlot unused_mask;
+    uint32_t buf = 0, aph = 0;
+    TileWalker walker;
+    walker.init(a, first_tile, tile_step);
+#pragma unroll 1
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step, walker.advance()) {
+      TileCoord t = walker.coord(a);
+      t.w0 += sub_w;
+      t.h0 += sub_h;
+      t.n0 += sub_n;
+      if (!mbar_wait(acc_full_bar((int)buf), aph, abort_flag, g_error_record, a.wait_limit_ns, 0xC00u + buf)) break;
+      tc_fence_after_sync();
+      const uint32_t tmem_acc = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u;
+      if (!epilogue_tile_tma_fast<OutT, false>(a, t, tmem_acc, lane, false, ws, store_count, bias_s, q * 32, unused_mask,
+                                               abort_flag))
+        break;
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_bar((int)buf) & kPeerBitMask);  // rank 0 collects both CTAs
+      if (++buf == 2u) {
+        buf = 0;
+        aph ^= 1u;
+      }
+    }
+    if (lane == 0) bulk_wait_group<0>();
+  }
+
+  // ------------------------------- teardown ---------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) {
+    }
+    __syncthreads();
+  }
+  // neither CTA leaves (and frees its shared and tensor memory) while the other may still use them
+  cluster_sync_all();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, 512u);
+}
+
 // ================================================================================================
 // Host side: tensor maps and launch plans
 // ================================================================================================
@@ -1317,10 +1535,10 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   g.bias_tile_only = 0;
   if (!g.epi_fast) g.relu_mask = nullptr;  // only the fast epilogue applies the mask; the caller checks
   g.mask_smem_bytes = g.relu_mask != nullptr ? 128 : 0;  // the mask slots' barriers; the slots count as staging
-  if (g.pair && (split || g.groups != 2 || !g.tma_store)) return false;  // the caller plans again without pairing
+  if (g.pair && !g.cta_pair && (split || g.groups != 2 || !g.tma_store)) return false;  // the caller plans again without pairing
   if (g.epi_fast && g.bias != nullptr) {
     const int padded = ceil_div(g.n_tiles * g.bn, 64) * 64;
-    if (g.pair && g.n_tiles <= 16) {
+    if (g.pair && !g.cta_pair && g.n_tiles <= 16) {
       g.bias_tile_only = 1;  // every byte counts towards a third stage
       g.bias_smem_bytes = ceil_div(g.bn, 64) * 128;
     } else if (padded * 2 > 8192) {
@@ -1340,6 +1558,19 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   auto staging = [&](int nsw) { return g.tma_store ? g.groups * 4 * (nsw + g.mask_slots) * 4096 : 0; };
   // A small filter (all taps, all column tiles) is kept in shared memory for the whole kernel:
   // the filter tiles are the part of the L2 -> SM traffic that never changes.
+  if (g.cta_pair) {
+    // one pipeline per CTA: a stage is the CTA's A tile and its half of the B tile
+    if (split || !g.tma_store || !g.epi_fast || g.relu_mask != nullptr || g.bn != 256) return false;
+    g.groups = 1;
+    g.acc_bufs = 2;
+    g.acc_stride = 256;
+    g.tmem_cols = 512;
+    const int avail = kSmemBudget - fixed, stage2 = 2 * kABytes;
+    auto stages_with = [&](int nsw) { return (avail - 4 * nsw * 4096) / stage2; };
+    g.nsw = stages_with(2) >= 6 ? 2 : 1;
+    g.stages = std::min(kMaxStages, stages_with(g.nsw));
+    return g.stages >= 4;
+  }
   if (g.pair) {
     stage = 2u * kABytes + (unsigned)g.bn * 128u;
     const int avail = kSmemBudget - fixed;
@@ -1414,6 +1645,54 @@ GemmKernel select_kernel(bool split, int epi, int out_dtype) {
   }
 }
 
+// Launch of the CTA-pair kernel: clusters of two CTAs, one cluster per pair of SMs.
+int launch_gemm_pair2(const GemmArgs& g, long long total_pairs, cudaStream_t s) {
+  GemmKernel kernel = g.out_dtype == PDNN_F16 ? umma_gemm_pair2_kernel<__half> : umma_gemm_pair2_kernel<__nv_bfloat16>;
+  const size_t smem = 1024 + (size_t)g.stages * 2 * kABytes + (size_t)g.nsw * 4 * 4096 + kBarBlockBytes + (size_t)g.bias_smem_bytes;
+  if (smem > (size_t)kSmemBudget) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: plan needs %zu bytes of shared memory", smem);
+  {
+    static std::mutex mu;
+    static bool opted_in[kMaxDevices] = {};
+    const int dev = current_device();
+    if (dev < 0 || dev >= kMaxDevices) return fail(PDNN_ALLOCATION_PROBLEM, "tensor-core gemm: no usable current device");
+    std::lock_guard<std::mutex> lock(mu);
+    if (!opted_in[dev]) {
+      if (cudaFuncSetAttribute(umma_gemm_pair2_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) != cudaSuccess ||
+          cudaFuncSetAttribute(umma_gemm_pair2_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(PDNN_ALLOCATION_PROBLEM, "cannot opt in to %d bytes of shared memory", kSmemBudget);
+      }
+      opted_in[dev] = true;
+    }
+  }
+  const int sms = device_sm_count();
+  unsigned grid = (unsigned)std::min<long long>(2 * total_pairs, (long long)sms);
+  grid -= grid % 2u;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  GemmArgs args = g;
+  args.tap_pack = 1;
+  args.wait_limit_ns = kWaitLimitNs;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, args);
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return fail(PDNN_ALLOCATION_PROBLEM, "tensor-core gemm (CTA pairs): launch failed: %s", cudaGetErrorString(le));
+  }
+  return check_launch("tensor-core gemm (CTA pairs)");
+}
+
 int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   const bool split = dtype == PDNN_F32;
   const int tap_pack = std::max(g.tap_pack, 1);
@@ -1421,6 +1700,7 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
                                  : (long long)g.n_tiles * g.tiles_w * g.tiles_h * g.tiles_n;
   if (total <= 0) return PDNN_OK;
   if (total > 0x7FFFFFFFll) return fail(PDNN_INDEX_EXCEEDED, "tensor-core gemm: too many tiles");
+  if (g.cta_pair) return launch_gemm_pair2(g, total, s);
   const unsigned stage = g.pair   ? 2u * kABytes + (unsigned)g.bn * 128u
                          : g.halo ? g.halo_stage_bytes
                                   : g.b_res ? (unsigned)kABytes : (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
@@ -1782,7 +2062,7 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
 }
 
 int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnConv2DParams& p,
-                 const PdnnConvEpilogue* epi, cudaStream_t s, bool try_halo = true) {
+                 const PdnnConvEpilogue* epi, cudaStream_t s, bool try_halo = true, bool try_cta_pair = true) {
   GemmArgs g;
   std::memset(&g, 0, sizeof(g));
   const size_t es = dtype_size(dtype);
@@ -1827,10 +2107,17 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
                          (row_tiles / 2) * ceil_div(p.features, pair_bn_auto) >= sms;
   const bool pairing = try_halo && !halo && dtype != PDNN_F32 && hwcf && p.features % 128 == 0 && pair_auto &&
                        row_tiles >= 2 && (!epi || epi->beta == 0.f);
+  // Pairs of row tiles with 256 columns go to clusters of two CTAs (umma_gemm_pair2_kernel) when the
+  // epilogue is the plain packed one: half the B operand reads per SM, double-buffered accumulators.
+  // Measured on the ResNet-50 shapes: 3x3 layers gain 10-18 % (256 at 14x14: 0.0558 -> 0.0496 ms); 1x1
+  // layers, whose tiles are short, lose 6-10 % against two pipelines per CTA and stay there.
+  const bool cta_pair = try_cta_pair && pairing && p.features % 256 == 0 && sms % 2 == 0 &&
+                        p.window_rows * p.window_cols > 1 && (row_tiles / 2) * (p.features / 256) >= sms / 2;
   if (pairing) {
     g.pair = 1;
+    g.cta_pair = cta_pair ? 1 : 0;
     // 128-column tiles leave room for two accumulator buffers per pipeline; narrow filters use them
-    g.bn = pair_bn_auto;
+    g.bn = cta_pair ? 256 : pair_bn_auto;
     if (g.tiles_w % 2 == 0) {
       g.pair_dim = 1;
       g.tiles_w /= 2;
@@ -1852,6 +2139,8 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   }
   g.n_tiles = ceil_div(p.features, g.bn);
   set_operand_layout(g, dtype, hwcf ? 1 : 0);
+  if (g.cta_pair)  // MMAs of 256 rows (128 per CTA) x 256 columns
+    g.idesc = make_idesc(dtype == PDNN_BF16 ? 1 : 0, 0, 1, 256, 256);
   const uint32_t abox[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)(halo ? g.th + p.window_rows - 1 : g.th),
                             (uint32_t)g.tn};
   if (!make_parity_maps(g, dtype, false, x, p, abox)) return PDNN_INVALID_PARAMETER;
@@ -1888,7 +2177,8 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     g.b_mode = B_MN_3X;
     const uint64_t dims[4] = {(uint64_t)epr, (uint64_t)p.channels, (uint64_t)(p.features / epr), taps};
     const uint64_t st[3] = {(uint64_t)p.features * es, 128, (uint64_t)p.channels * p.features * es};
-    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, (uint32_t)(g.bn / epr), 1};
+    // (a CTA pair: each CTA copies its own half of the tile's columns)
+    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, (uint32_t)((g.cta_pair ? g.bn / 2 : g.bn) / epr), 1};
     if (!make_map(&g.b_map, dtype, true, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
   } else if (hwcf) {
     g.b_mode = B_MN_3;
@@ -1905,7 +2195,8 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     if (!make_map(&g.b_map, dtype, false, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
   }
   const int status = finish_forward(g, dtype, y, p, epi, s);
-  if (status == kPlanAgain) return conv_forward(dtype, x, w, y, p, epi, s, false);
+  if (status == kPlanAgain)  // first without the CTA pairs, then without halo / pair mode
+    return g.cta_pair ? conv_forward(dtype, x, w, y, p, epi, s, try_halo, false) : conv_forward(dtype, x, w, y, p, epi, s, false, false);
   return status;
 }
 

@@ -240,6 +240,78 @@ __device__ __forceinline__ void warp_arrive_expect_tx(uint32_t bar, uint32_t byt
   if (elect_one()) mbar_arrive_expect_tx(bar, bytes);
 }
 
+// ---- CTA pairs (cta_group::2) --------------------------------------------------------------------
+// Two CTAs of a cluster work on one 256-row tile: each holds its own 128 rows of A and half of the
+// columns of B in its shared memory and receives its 128 rows of the accumulator in its tensor
+// memory; the MMAs are issued by the CTA of rank 0 only, and read both shared memories.  A shared
+// memory address of the same offset in the CTA of rank 0 is the own address with bit 24 cleared.
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address of `addr` (an own shared-memory address) in the CTA of rank `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_slot, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(columns)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t base, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
+}
+// TMA load into the own shared memory whose bytes are counted by the barrier of the CTA of rank 0.
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                                 int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_dst), "l"(map), "r"(bar & kPeerBitMask), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at `cluster_addr` (any CTA of the cluster) once all MMAs issued so far are done.
+__device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void warp_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  if (elect_one()) mma_f16_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+}
+// Both CTAs of the pair learn that the MMAs issued so far are done.
+__device__ __forceinline__ void warp_commit_pair(uint32_t bar, uint32_t peer_bar) {
+  if (elect_one()) {
+    mma_commit_pair(bar);
+    mma_commit_pair(peer_bar);
+  }
+}
+__device__ __forceinline__ void warp_tma_load_4d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                                      int c1, int c2, int c3) {
+  if (elect_one()) tma_load_4d_pair(smem_dst, map, bar, c0, c1, c2, c3);
+}
+
 // ---- descriptors ---------------------------------------------------------------------------------
 // Shared-memory matrix descriptor, 128-byte swizzle.  Addresses and offsets are in bytes here and
 // stored in units of 16 bytes; bits [46,48) = 1 marks the sm_100 format, bits [61,64) hold the
@@ -258,9 +330,9 @@ __host__ __device__ inline uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, 
   return d;
 }
 
-// Instruction descriptor for kind::f16 / kind::tf32 with fp32 accumulation, M = 128.
+// Instruction descriptor for kind::f16 / kind::tf32 with fp32 accumulation, M = 128 (256 for a CTA pair).
 // format: 0 = f16, 1 = bf16, 2 = tf32.  *_mn: operand is MN-major (1) or K-major (0).
-__host__ __device__ inline uint32_t make_idesc(int format, int a_mn, int b_mn, int n) {
+__host__ __device__ inline uint32_t make_idesc(int format, int a_mn, int b_mn, int n, int m = 128) {
   uint32_t d = 0;
   d |= 1u << 4;                         // D format: f32
   d |= (uint32_t)(format & 7) << 7;     // A format
@@ -268,7 +340,7 @@ __host__ __device__ inline uint32_t make_idesc(int format, int a_mn, int b_mn, i
   d |= (uint32_t)(a_mn & 1) << 15;
   d |= (uint32_t)(b_mn & 1) << 16;
   d |= (uint32_t)((n >> 3) & 0x3F) << 17;
-  d |= (uint32_t)((128 >> 4) & 0x1F) << 24;
+  d |= (uint32_t)((m >> 4) & 0x1F) << 24;
   return d;
 }
 

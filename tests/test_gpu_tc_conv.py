@@ -87,6 +87,40 @@ def test_forward_fused_epilogue(orc, dtype):
     assert rel_err(to_host(out), ref) <= TOL[dtype]
 
 
+# Shapes large enough for the plans that need the whole device busy: clusters of two CTAs on 256 x 256
+# tiles (long reduction, features a multiple of 256, at least 74 pairs of row tiles).
+CTA_PAIR_SHAPES = [
+    (128, 14, 14, 512, 512, 3, 1, True, None),
+    (128, 14, 14, 2048, 512, 1, 1, True, None),
+    (256, 28, 28, 256, 256, 3, 2, True, None),   # stride 2: one tensor map per input parity
+    (131, 7, 7, 512, 512, 3, 1, True, None),     # an odd number of row tiles: the last pair is half empty
+]
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("shape", CTA_PAIR_SHAPES)
+def test_forward_cta_pair_plan_against_direct_kernel_and_oracle(orc, dtype, shape):
+    """Forward layers that run on clusters of two CTAs (tcgen05 cta_group::2): the whole output against
+    the CUDA-core direct kernel, and the first and last images against the oracle, with bias + ReLU."""
+    n, h, w, c, k, win, st, same, pad = shape
+    p, po, x, wt, _ = _conv_case(orc, dtype, n, h, w, c, k, win, st, bool(same), pad)
+    rng = np.random.default_rng(3)
+    b = rounded(rng.standard_normal(k).astype(np.float32) * 0.1, dtype)
+    xd, wd, bd = to_dev(x, dtype), to_dev(wt, dtype), to_dev(b, dtype)
+    y = pd.conv2d(pd.FORWARD, xd, wd, p, algorithm=pd.ALGO_IM2COL, bias=bd, activation=pd.ACT_RELU)
+    assert_no_device_error()
+    slow = pd.conv2d(pd.FORWARD, xd, wd, p, algorithm=pd.ALGO_DIRECT).float()
+    slow = torch.relu((slow.view(-1, k) + bd.float()[None, :])).view(-1)
+    err = ((y.float() - slow).abs().max() / slow.abs().max()).item()
+    assert err <= TOL[dtype], err
+    per_in, per_out = h * w * c, p.out_rows * p.out_cols * k
+    p1 = orc.conv_params(1, h, w, c, k, win, st, bool(same), pad)
+    for img in (0, n - 1):
+        ref = orc.conv2d(orc.FORWARD, x[img * per_in:(img + 1) * per_in], wt, p1)
+        ref = np.maximum(rounded(ref, dtype).reshape(-1, k) + b[None, :], 0).ravel()
+        assert rel_err(to_host(y[img * per_out:(img + 1) * per_out]), ref) <= TOL[dtype], img
+
+
 BWD_SHAPES = [
     (2, 28, 28, 128, 128, 3, 1, True, None),
     (2, 28, 28, 64, 256, 1, 1, True, None),
