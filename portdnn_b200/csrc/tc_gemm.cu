@@ -605,22 +605,25 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
   const uint32_t bias_s =
       (EPI >= 2 && a.bias != nullptr) ? bar_base + kBarBlockBytes - (uint32_t)bias_col0 * 2u : 0u;
 
-  if (threadIdx.x == 0) {
-    for (int g = 0; g < kMaxGroups; ++g) {
-      for (int s = 0; s < kMaxStages; ++s) {
-        mbar_init(gbar(g, s), 1);
-        mbar_init(gbar(g, kMaxStages + s), pair ? 2 : 1);  // pair mode: both issuers release a stage
-        mbar_init(gbar(g, 2 * kMaxStages + s), 4);
-      }
-      for (int b = 0; b < 2; ++b) {
-        mbar_init(gbar(g, 3 * kMaxStages + b), 1);
-        mbar_init(gbar(g, 3 * kMaxStages + 2 + b), 4);
-      }
-    }
+  // One barrier per thread (a single thread initialising all of them costs about a microsecond of
+  // every launch): full, empty and ready per stage, accumulator full / empty per buffer, per group.
+  if ((int)threadIdx.x < kMaxGroups * kBarsPerGroup) {
+    const int g = (int)threadIdx.x / kBarsPerGroup, j = (int)threadIdx.x % kBarsPerGroup;
+    const uint32_t count = j < kMaxStages                ? 1u
+                           : j < 2 * kMaxStages          ? (pair ? 2u : 1u)  // pair mode: both issuers release a stage
+                           : j < 3 * kMaxStages          ? 4u
+                           : j < 3 * kMaxStages + 2      ? 1u
+                                                         : 4u;
+    mbar_init(gbar(g, j), count);
+    fence_barrier_init();
+  } else if ((int)threadIdx.x == kMaxGroups * kBarsPerGroup) {
     mbar_init(bres_bar, 1);
-    if (EPI == 3)  // one barrier per epilogue warp for its mask slot, after the bias copy
-      for (int i = 0; i < 16; ++i) mbar_init(bar_base + (uint32_t)kBarBlockBytes + (uint32_t)a.bias_smem_bytes + 8u * (uint32_t)i, 1);
     *abort_flag = 0;
+    fence_barrier_init();
+  } else if (EPI == 3 && (int)threadIdx.x < kMaxGroups * kBarsPerGroup + 17) {
+    // one barrier per mask slot of the epilogue warps, after the bias copy
+    const int i = (int)threadIdx.x - kMaxGroups * kBarsPerGroup - 1;
+    mbar_init(bar_base + (uint32_t)kBarBlockBytes + (uint32_t)a.bias_smem_bytes + 8u * (uint32_t)i, 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -1137,16 +1140,10 @@ __global__ void __launch_bounds__(192, 1) umma_gemm_pair2_kernel(const __grid_co
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * (2 * kMaxStages + 4) + 4);
   const uint32_t bias_s = a.bias != nullptr ? bar_base + (uint32_t)kBarBlockBytes : 0u;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kMaxStages; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(acc_full_bar(b), 1);
-      mbar_init(acc_empty_bar(b), 8);
-    }
-    *abort_flag = 0;
+  if ((int)threadIdx.x < 2 * kMaxStages + 4) {  // one barrier per thread
+    const int j = (int)threadIdx.x;
+    mbar_init(bar_base + 8u * (uint32_t)j, j >= 2 * kMaxStages + 2 ? 8u : 1u);
+    if (j == 0) *abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 0 && lane == 0) {
