@@ -219,6 +219,15 @@ int pdnn_pooling_max_grad(int op, int dtype, const void* input_data, const void*
                           const void* input_backprop, void* output_backprop,
                           const PdnnPoolingParams* params, void* stream);
 
+/* The same followed by pointwise::launch<Relu, Gradient> with input_data as the forward tensor, in one
+ * call (no reference counterpart): for a pooled tensor that is the output of a ReLU, output_backprop is
+ * the gradient with respect to that ReLU's input, i.e. elements of input_data that are not positive
+ * receive nothing.  For 3x3 windows it costs nothing extra: a window whose maximum is not positive
+ * simply has no winner. */
+int pdnn_pooling_max_grad_relu(int op, int dtype, const void* input_data, const void* output_data,
+                               const void* input_backprop, void* output_backprop,
+                               const PdnnPoolingParams* params, void* stream);
+
 /* Replaces softmax::launch<T, Forward / Gradient> (include/portdnn/softmax/launch.h:64-165):
  * y = exp(x - max) / sum exp(x - max) over the channels of each pixel.  direction 0: input = x,
  * gradient unused.  direction 1: input = the forward OUTPUT y, gradient = dy,

@@ -285,14 +285,16 @@ def pooling(op, direction, inp, params, out=None):
     return out
 
 
-def pooling_max_grad(op, input_data, output_data, input_backprop, params, out=None):
+def pooling_max_grad(op, input_data, output_data, input_backprop, params, out=None, relu_input=False):
     """pooling::launch<T, Max|MaxWithNan, Backpropagate>, four-pointer form
-    (include/portdnn/pooling/launch.h:182-257): (x, y, dy) -> dx."""
+    (include/portdnn/pooling/launch.h:182-257): (x, y, dy) -> dx.  relu_input: x is a ReLU's output and
+    dx is to be the gradient with respect to that ReLU's input (pdnn_pooling_max_grad_relu)."""
     torch = _torch()
     _require_cuda(input_data, output_data, input_backprop, out)
     if out is None:
         out = torch.empty(input_data.numel(), dtype=input_data.dtype, device=input_data.device)
-    _check(lib().pdnn_pooling_max_grad(op, _dtype_code(input_data), _ptr(input_data), _ptr(output_data),
+    fn = lib().pdnn_pooling_max_grad_relu if relu_input else lib().pdnn_pooling_max_grad
+    _check(fn(op, _dtype_code(input_data), _ptr(input_data), _ptr(output_data),
                                        _ptr(input_backprop), _ptr(out), ctypes.byref(params), _stream()))
     return out
 

@@ -318,9 +318,9 @@ int pdnn_pooling(int op, int direction, int dtype, const void* input, void* outp
   return launch_pooling(op, direction, dtype, input, output, *params, s);
 }
 
-int pdnn_pooling_max_grad(int op, int dtype, const void* input_data, const void* output_data,
-                          const void* input_backprop, void* output_backprop, const PdnnPoolingParams* params,
-                          void* stream) {
+namespace {
+int run_pooling_max_grad(int op, int dtype, const void* input_data, const void* output_data, const void* input_backprop,
+                         void* output_backprop, const PdnnPoolingParams* params, bool relu_input, void* stream) {
   if (params == nullptr || input_data == nullptr || output_data == nullptr || input_backprop == nullptr ||
       output_backprop == nullptr)
     return fail(PDNN_INVALID_PARAMETER, "pooling: null argument");
@@ -332,10 +332,23 @@ int pdnn_pooling_max_grad(int op, int dtype, const void* input_data, const void*
     const size_t rows[3] = {in_px, out_px, out_px};
     return pooling_nchw(dtype, ins, rows, 3, output_backprop, in_px, *params, s,
                         [&](const void* const* t, void* o, const PdnnPoolingParams& q) {
-                          return launch_pooling_max_grad(op, dtype, t[0], t[1], t[2], o, q, s);
+                          return launch_pooling_max_grad(op, dtype, t[0], t[1], t[2], o, q, relu_input, s);
                         });
   }
-  return launch_pooling_max_grad(op, dtype, input_data, output_data, input_backprop, output_backprop, *params, s);
+  return launch_pooling_max_grad(op, dtype, input_data, output_data, input_backprop, output_backprop, *params, relu_input, s);
+}
+}  // namespace
+
+int pdnn_pooling_max_grad(int op, int dtype, const void* input_data, const void* output_data,
+                          const void* input_backprop, void* output_backprop, const PdnnPoolingParams* params,
+                          void* stream) {
+  return run_pooling_max_grad(op, dtype, input_data, output_data, input_backprop, output_backprop, params, false, stream);
+}
+
+int pdnn_pooling_max_grad_relu(int op, int dtype, const void* input_data, const void* output_data,
+                               const void* input_backprop, void* output_backprop, const PdnnPoolingParams* params,
+                               void* stream) {
+  return run_pooling_max_grad(op, dtype, input_data, output_data, input_backprop, output_backprop, params, true, stream);
 }
 
 int pdnn_softmax(int direction, int dtype, const void* input, const void* gradient, void* output,

@@ -106,7 +106,7 @@ int device_sm_count();   // SM count of the current device; -1 if it is not an s
 int launch_pooling(int op, int direction, int dtype, const void* in, void* out, const PdnnPoolingParams& p,
                    cudaStream_t s);
 int launch_pooling_max_grad(int op, int dtype, const void* x, const void* y, const void* dy, void* dx,
-                            const PdnnPoolingParams& p, cudaStream_t s);
+                            const PdnnPoolingParams& p, bool relu_input, cudaStream_t s);
 int launch_depthwise(int pass, int dtype, const void* in, const void* fil, void* out,
                      const PdnnDepthwiseConv2DParams& p, void* ws, size_t ws_bytes, cudaStream_t s);
 size_t depthwise_workspace_bytes(int pass, int dtype, const PdnnDepthwiseConv2DParams& p);

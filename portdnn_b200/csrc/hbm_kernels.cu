@@ -1124,6 +1124,11 @@ struct Packet<__half> {
       win[i] = (win[i] & ~mask) | ((id * 0x00010001u) & mask);
     }
   }
+  // Clears the winner wherever the maximum `m` is not positive (the ReLU gradient of the pooled tensor).
+  static __device__ __forceinline__ void keep_positive(const Packet& m, unsigned (&win)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) win[i] &= __hgt2_mask(m.v[i], splat(0.f).v[0]);
+  }
   static __device__ __forceinline__ void store_winners(unsigned char* p, const unsigned (&win)[4]) {
     *reinterpret_cast<uint2*>(p) = make_uint2(__byte_perm(win[0], win[1], 0x6420), __byte_perm(win[2], win[3], 0x6420));
   }
@@ -1173,6 +1178,11 @@ struct Packet<__nv_bfloat16> {  // maxima only: bf16 products would lose too muc
       win[i] = (win[i] & ~mask) | ((id * 0x00010001u) & mask);
     }
   }
+  // Clears the winner wherever the maximum `m` is not positive (the ReLU gradient of the pooled tensor).
+  static __device__ __forceinline__ void keep_positive(const Packet& m, unsigned (&win)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) win[i] &= __hgt2_mask(m.v[i], splat(0.f).v[0]);
+  }
   static __device__ __forceinline__ void store_winners(unsigned char* p, const unsigned (&win)[4]) {
     *reinterpret_cast<uint2*>(p) = make_uint2(__byte_perm(win[0], win[1], 0x6420), __byte_perm(win[2], win[3], 0x6420));
   }
@@ -1220,6 +1230,11 @@ struct Packet<float> {
     for (int i = 0; i < 4; ++i)
       if (v[i] == m.v[i] || (keep_nan && isnan(v[i]) && isnan(m.v[i]))) win[i] = id;
   }
+  static __device__ __forceinline__ void keep_positive(const Packet& m, unsigned (&win)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (!(m.v[i] > 0.f)) win[i] = 0u;
+  }
   static __device__ __forceinline__ void store_winners(unsigned char* p, const unsigned (&win)[4]) {
     *reinterpret_cast<unsigned*>(p) = win[0] | (win[1] << 8) | (win[2] << 16) | (win[3] << 24);
   }
@@ -1241,6 +1256,7 @@ struct StripGeometry {
   int in_rows, in_cols, out_rows, out_cols, channels, pad_rows, pad_cols, batch;
   int rows_per_thread, wgroups, hchunks;
   int flip;  // MODE 0: read the filter mirrored in both window axes (stride-1 input backprop)
+  int positive_only;  // MODE 3 / 4: a window whose maximum is not positive has no winner
 };
 
 // MODE 0: depthwise 3x3 (needs Packet::fma); MODE 1: max ignoring NaN; MODE 2: max keeping NaN;
@@ -1333,6 +1349,7 @@ __global__ void __launch_bounds__(kStripBlock)
             e.mark_equal(acc, (unsigned)(1 + r * 3 + s2), MODE == 4, win);
           }
         }
+        if (g.positive_only) P::keep_positive(acc, win);
         if (ow0 + o < g.out_cols)
           P::store_winners(reinterpret_cast<unsigned char*>(y) +
                                (((size_t)n * g.out_rows + oh) * g.out_cols + ow0 + o) * g.channels + c, win);
@@ -1454,8 +1471,27 @@ int launch_pooling(int op, int direction, int dtype, const void* in, void* out, 
   });
 }
 
+namespace {
+int pooling_max_grad_impl(int op, int dtype, const void* x, const void* y, const void* dy, void* dx,
+                          const PdnnPoolingParams& p, bool positive_only, bool* positive_applied, cudaStream_t s);
+}
+
+// relu_input: x is the output of a ReLU and dx is to be the gradient with respect to that ReLU's
+// input: elements that are not positive receive nothing.  Where the winner map comes from the strip
+// kernel this costs nothing (a window whose maximum is not positive has no winner); elsewhere a
+// ReLU-gradient pass follows.
 int launch_pooling_max_grad(int op, int dtype, const void* x, const void* y, const void* dy, void* dx,
-                            const PdnnPoolingParams& p, cudaStream_t s) {
+                            const PdnnPoolingParams& p, bool relu_input, cudaStream_t s) {
+  bool applied = false;
+  int st = pooling_max_grad_impl(op, dtype, x, y, dy, dx, p, relu_input, &applied, s);
+  if (st == PDNN_OK && relu_input && !applied)
+    st = launch_pointwise_grad(PDNN_ACT_RELU, dtype, x, dx, dx, (size_t)p.batch * p.in_rows * p.in_cols * p.channels, s);
+  return st;
+}
+
+namespace {
+int pooling_max_grad_impl(int op, int dtype, const void* x, const void* y, const void* dy, void* dx,
+                          const PdnnPoolingParams& p, bool positive_only, bool* positive_applied, cudaStream_t s) {
   if (!pool_params_ok(p)) return fail(PDNN_INVALID_PARAMETER, "pooling: non-positive size or negative padding");
   if (p.input_format != 0) return fail(PDNN_INVALID_PARAMETER, "pooling: only NHWC is implemented");
   if (op != PDNN_POOL_MAX && op != PDNN_POOL_MAX_WITH_NAN) return fail(PDNN_INVALID_PARAMETER, "max gradient: bad op");
@@ -1492,12 +1528,14 @@ int launch_pooling_max_grad(int op, int dtype, const void* x, const void* y, con
         if (p.window_rows == 3 && p.window_cols == 3 && p.stride_rows == p.stride_cols &&
             (p.stride_rows == 1 || p.stride_rows == 2)) {
           // the forward pool's strip walk, writing the winner map instead of the maxima
-          const StripGeometry sg{p.in_rows, p.in_cols, p.out_rows, p.out_cols, p.channels, p.pad_rows, p.pad_cols, p.batch, 0, 0, 0};
+          const StripGeometry sg{p.in_rows, p.in_cols, p.out_rows, p.out_cols, p.channels, p.pad_rows, p.pad_cols, p.batch, 0, 0, 0,
+                                 0, positive_only ? 1 : 0};
           T* wmap = reinterpret_cast<T*>(winner);
           winners_done = (op == PDNN_POOL_MAX ? launch_window3_strip<T, 3>(xt, nullptr, wmap, p.stride_rows, sg, sms, s)
                                               : launch_window3_strip<T, 4>(xt, nullptr, wmap, p.stride_rows, sg, sms, s)) == 0;
         }
         if (winners_done) {
+          *positive_applied = positive_only;
         } else if (op == PDNN_POOL_MAX)
           pool_winner_kernel<T, PDNN_POOL_MAX, VN, unsigned><<<g1, kBlock, 0, s>>>(xt, yt, winner, p, (unsigned)out_items);
         else
@@ -1548,6 +1586,7 @@ int launch_pooling_max_grad(int op, int dtype, const void* x, const void* y, con
     return check_launch("pooling max gradient");
   });
 }
+}  // namespace
 
 namespace {
 bool depthwise_params_ok(const PdnnDepthwiseConv2DParams& p) {

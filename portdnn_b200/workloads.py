@@ -356,8 +356,13 @@ class ConvStackRunner:
                 if j >= 0:
                     self._add_grad(j, lambda dst, acc: False if acc else api.pooling(l.op, 1, dy, p, out=dst))
             elif j >= 0:
+                # a pooled ReLU output with no other reader: its ReLU gradient rides on the pool gradient
+                relu = (isinstance(self.layers[j], ConvLayer) and self.layers[j].activation == api.ACT_RELU and
+                        self.readers[j] == 1 and self.fuse_accumulate)
                 self._add_grad(j, lambda dst, acc: False if acc else
-                               api.pooling_max_grad(l.op, self._in(i), self.acts[i], dy, p, out=dst))
+                               api.pooling_max_grad(l.op, self._in(i), self.acts[i], dy, p, out=dst, relu_input=relu))
+                if relu:
+                    self._masked.add(j)
 
     def backward(self):
         self.backward_begin()

@@ -41,6 +41,22 @@ def test_max_pool_forward_and_grad_bit_exact(orc, dtype, shape):
     assert np.array_equal(to_host(dx), rounded(dx_ref, dtype))
 
 
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("shape", POOL_SHAPES)
+def test_max_pool_grad_with_relu_gradient(orc, dtype, shape):
+    """pdnn_pooling_max_grad_relu = max-pool gradient followed by pointwise Relu Gradient on the pooled
+    tensor (src/pointwise/kernels.h:205-233), for a ReLU output with many exact zeros."""
+    n, h, w, c, win, st, same = shape
+    rng = np.random.default_rng(17)
+    x = rounded(np.maximum(rng.integers(-4, 5, size=n * h * w * c), 0).astype(np.float32) * 0.5, dtype)
+    p, po = pd.pool_params(n, h, w, c, win, st, same), orc.pool_params(n, h, w, c, win, st, same)
+    y_ref = orc.pool_forward(orc.POOL_MAX, x, po)
+    dy = rounded(rng.integers(1, 4, size=y_ref.size).astype(np.float32), dtype)
+    dx = pd.pooling_max_grad(pd.POOL_MAX, to_dev(x, dtype), to_dev(y_ref, dtype), to_dev(dy, dtype), p, relu_input=True)
+    ref = orc.pointwise_grad(0, x, orc.pool_max_grad(orc.POOL_MAX, x, y_ref, dy, po))
+    assert np.array_equal(to_host(dx), rounded(ref, dtype))
+
+
 def test_max_pool_random_values_and_nan(orc):
     n, h, w, c, win, st = 2, 17, 19, 8, 3, 2
     rng = np.random.default_rng(8)
