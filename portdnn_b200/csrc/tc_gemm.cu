@@ -64,6 +64,7 @@ struct alignas(64) GemmArgs {
   int tw, th, tn;    // a_mn == 0: pixel box of a row tile; a_mn == 1: pixel box of a reduction slab
   int etw, eth, etn; // pixel box of a row tile as the epilogue sees it
   int num_taps;
+  int b_presplit;    // fp32 (3xTF32): B arrives split into hi and lo parts (b_map, b_map_lo); only A is split in the kernel
   int cta_pair;      // 1: run by umma_gemm_pair2_kernel (clusters of two CTAs, 256 x 256 tiles)
   int tap_pack;      // a_mn == 1: taps per tile (2: the second 64 rows of the A tile are the next tap's channels)
   int cblocks;       // a_mn == 0: reduction blocks per tap
@@ -118,6 +119,7 @@ struct alignas(64) GemmArgs {
   // result is replaced by zero: pointwise::launch<Relu, Gradient> applied on the way out.
   const void* relu_mask;
   CUtensorMap mask_map;  // the mask tensor with the geometry of out_map (set when relu_mask is)
+  CUtensorMap b_map_lo;  // b_presplit: the lo parts of B, same geometry as b_map
   int mask_slots;        // 4 KB mask slots per epilogue warp: 2 where shared memory allows, else 1
   int accumulate;  // packed 16-bit epilogues, no bias: the block already in the output is added (before the mask)
   int reduce_add;  // staged fp32 epilogue of the filter backprop: every pixel split adds its tile to the output
@@ -680,14 +682,16 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
         prefetch_tensormap(&a.b_map);
       }
       const int epr = a.epr, b_mode = a.b_mode, b_boxes = a.b_boxes, a_boxes = a.a_boxes, cblocks = a.cblocks;
+      const bool presplit = SPLIT && a.b_presplit != 0;
       const uint32_t a_box_bytes = a.a_box_bytes, b_box_bytes = a.b_box_bytes,
-                     tx_bytes = pair ? 2u * kABytes + b_bytes : (b_res ? (uint32_t)kABytes : kABytes + b_bytes);
+                     tx_bytes = pair ? 2u * kABytes + b_bytes
+                                     : (b_res ? (uint32_t)kABytes : kABytes + (presplit ? 2u * b_bytes : b_bytes));
       // pair mode: where the second row tile of the pair starts, relative to the first
       const int pair_dw = a.pair_dim == 1 ? a.tw : 0, pair_dh = a.pair_dim == 2 ? a.th : 0,
                 pair_dn = a.pair_dim == 3 ? a.tn : 0;
       const CUtensorMap* bmap = &a.b_map;
       // one B tile of a forward-style GEMM (a_mn == 0): reduction block kc of tap btap, columns from nf0
-      auto load_b = [&](uint32_t sb, uint32_t fb, int kc, int nf0, int btap) {
+      auto load_b_from = [&](const CUtensorMap* bmap, uint32_t sb, uint32_t fb, int kc, int nf0, int btap) {
         switch (b_mode) {
           case B_MN_3X: warp_tma_load_4d(sb, bmap, fb, 0, kc, nf0 / epr, btap); break;
           case B_MN_3:
@@ -704,6 +708,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
             break;
         }
       };
+      auto load_b = [&](uint32_t sb, uint32_t fb, int kc, int nf0, int btap) { load_b_from(bmap, sb, fb, kc, nf0, btap); };
       if (b_res && grp == 0 && (int)blockIdx.x < total_tiles) {
         warp_arrive_expect_tx(bres_bar, res_bytes);
         uint32_t dst = base;
@@ -760,6 +765,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
                   load_b(sa + 2u * kABytes, fb, kc, t.nf0, btap);
                 } else if (!b_res) {
                   load_b(sa + kABytes, fb, kc, t.nf0, btap);
+                  if (presplit) load_b_from(&a.b_map_lo, sa + part_bytes + kABytes, fb, kc, t.nf0, btap);
                 }
               }
               next_stage();
@@ -1047,7 +1053,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     // hi keeps the 19 leading bits (what the tensor core reads of an fp32 word); lo = x - hi is
     // exact in fp32.  Element positions do not change, so the swizzle is irrelevant here.
     const int tid = threadIdx.x - 6 * 32;  // 0..127
-    const int chunks = (int)(part_bytes >> 4);
+    const int chunks = (int)((a.b_presplit ? (uint32_t)kABytes : part_bytes) >> 4);  // A comes first in a part
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
@@ -2058,6 +2064,16 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
   return st;
 }
 
+// hi keeps the 19 leading bits of an fp32 word (what the tensor core reads of it), lo = x - hi is exact.
+__global__ void __launch_bounds__(256) split_hi_lo_kernel(const float* __restrict__ x, float* __restrict__ hi,
+                                                          float* __restrict__ lo, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
+    const float v = x[i], h = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+    hi[i] = h;
+    lo[i] = v - h;
+  }
+}
+
 int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnConv2DParams& p,
                  const PdnnConvEpilogue* epi, cudaStream_t s, bool try_halo = true, bool try_cta_pair = true) {
   GemmArgs g;
@@ -2167,31 +2183,56 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   g.num_taps = nt;
   g.cblocks = ceil_div(p.channels, epr);
   const uint64_t taps = (uint64_t)p.window_rows * p.window_cols;
-  if (hwcf && p.features % epr == 0) {
-    // All 128-byte column blocks of the tile in one copy: the block index is a tensor dimension
-    // of its own (stride 128 bytes), placed after the reduction rows so that the blocks land
-    // one after another in shared memory.
-    g.b_mode = B_MN_3X;
-    const uint64_t dims[4] = {(uint64_t)epr, (uint64_t)p.channels, (uint64_t)(p.features / epr), taps};
-    const uint64_t st[3] = {(uint64_t)p.features * es, 128, (uint64_t)p.channels * p.features * es};
-    // (a CTA pair: each CTA copies its own half of the tile's columns)
-    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, (uint32_t)((g.cta_pair ? g.bn / 2 : g.bn) / epr), 1};
-    if (!make_map(&g.b_map, dtype, true, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
-  } else if (hwcf) {
-    g.b_mode = B_MN_3;
-    const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)p.channels, taps, 1};
-    const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.channels * p.features * es,
-                            taps * p.channels * p.features * es};
-    const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
-    if (!make_map(&g.b_map, dtype, true, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
-  } else {
+  // fp32 (3xTF32) with enough work to pay for one extra pass over the filter: the filter is split into
+  // its hi and lo parts once, ahead of the GEMM, and both arrive by TMA; the kernel's split warps then
+  // only have the A tiles to split (a third less shared-memory traffic per stage).
+  const size_t filter_elems = (size_t)taps * p.channels * p.features;
+  float* w_split = nullptr;
+  if (dtype == PDNN_F32 && (size_t)p.batch * p.out_rows * p.out_cols >= 2048 && aligned16(w)) {
+    if (cudaMallocAsync(reinterpret_cast<void**>(&w_split), 2 * filter_elems * sizeof(float), s) == cudaSuccess) {
+      split_hi_lo_kernel<<<grid_for(filter_elems, 256, sms), 256, 0, s>>>(static_cast<const float*>(w), w_split,
+                                                                            w_split + filter_elems, filter_elems);
+      count_launch();
+      g.b_presplit = 1;
+    } else {
+      cudaGetLastError();
+      w_split = nullptr;
+    }
+  }
+  auto make_b_map = [&](CUtensorMap* map, const void* base) {
+    if (hwcf && p.features % epr == 0) {
+      // All 128-byte column blocks of the tile in one copy: the block index is a tensor dimension
+      // of its own (stride 128 bytes), placed after the reduction rows so that the blocks land
+      // one after another in shared memory.
+      g.b_mode = B_MN_3X;
+      const uint64_t dims[4] = {(uint64_t)epr, (uint64_t)p.channels, (uint64_t)(p.features / epr), taps};
+      const uint64_t st[3] = {(uint64_t)p.features * es, 128, (uint64_t)p.channels * p.features * es};
+      // (a CTA pair: each CTA copies its own half of the tile's columns)
+      const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, (uint32_t)((g.cta_pair ? g.bn / 2 : g.bn) / epr), 1};
+      return make_map(map, dtype, true, base, dims, st, box);
+    }
+    if (hwcf) {
+      g.b_mode = B_MN_3;
+      const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)p.channels, taps, 1};
+      const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.channels * p.features * es,
+                              taps * p.channels * p.features * es};
+      const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
+      return make_map(map, dtype, true, base, dims, st, box);
+    }
     g.b_mode = B_K_FHWC;
     const uint64_t dims[4] = {(uint64_t)p.channels, taps, (uint64_t)p.features, 1};
     const uint64_t st[3] = {(uint64_t)p.channels * es, taps * p.channels * es, taps * p.channels * p.features * es};
     const uint32_t box[4] = {(uint32_t)epr, 1, (uint32_t)g.bn, 1};
-    if (!make_map(&g.b_map, dtype, false, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+    return make_map(map, dtype, false, base, dims, st, box);
+  };
+  const bool maps_ok = make_b_map(&g.b_map, w_split != nullptr ? static_cast<const void*>(w_split) : w) &&
+                       (w_split == nullptr || make_b_map(&g.b_map_lo, w_split + filter_elems));
+  if (!maps_ok) {
+    if (w_split != nullptr) cudaFreeAsync(w_split, s);
+    return PDNN_INVALID_PARAMETER;
   }
   const int status = finish_forward(g, dtype, y, p, epi, s);
+  if (w_split != nullptr) cudaFreeAsync(w_split, s);
   if (status == kPlanAgain)  // first without the CTA pairs, then without halo / pair mode
     return g.cta_pair ? conv_forward(dtype, x, w, y, p, epi, s, try_halo, false) : conv_forward(dtype, x, w, y, p, epi, s, false, false);
   return status;
@@ -2210,6 +2251,26 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
   const int sms = device_sm_count();
   const bool hwcf = p.filter_format == 0;
   const int epr = dtype == PDNN_F32 ? 32 : 64;
+  // fp32: the filter split into hi and lo parts ahead of the GEMMs, as in the forward pass
+  const size_t filter_elems = (size_t)p.window_rows * p.window_cols * p.channels * p.features;
+  float* w_split = nullptr;
+  if (dtype == PDNN_F32 && (size_t)p.batch * p.in_rows * p.in_cols >= 2048 && aligned16(w) &&
+      cudaMallocAsync(reinterpret_cast<void**>(&w_split), 2 * filter_elems * sizeof(float), s) == cudaSuccess) {
+    split_hi_lo_kernel<<<grid_for(filter_elems, 256, sms), 256, 0, s>>>(static_cast<const float*>(w), w_split,
+                                                                          w_split + filter_elems, filter_elems);
+    count_launch();
+  } else if (dtype == PDNN_F32) {
+    cudaGetLastError();
+    w_split = nullptr;
+  }
+  struct Release {
+    float* ptr;
+    cudaStream_t s;
+    ~Release() {
+      if (ptr != nullptr) cudaFreeAsync(ptr, s);
+    }
+  } release{w_split, s};
+  const void* w_hi = w_split != nullptr ? static_cast<const void*>(w_split) : w;
   // dx is produced one output parity class at a time: positions h = sr*i + qh, w = sc*j + qw only
   // receive taps with r = (qh + pad) mod sr, s = (qw + pad) mod sc, and within a class the
   // relation between i and the dy row is a plain shift.
@@ -2320,14 +2381,19 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
         const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.channels * p.features * es,
                                 taps * p.channels * p.features * es};
         const uint32_t box[4] = {(uint32_t)epr, (uint32_t)g.bn, 1, 1};
-        if (!make_map(&g.b_map, dtype, false, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+        if (!make_map(&g.b_map, dtype, false, w_hi, dims, st, box)) return PDNN_INVALID_PARAMETER;
+        if (w_split != nullptr && !make_map(&g.b_map_lo, dtype, false, w_split + filter_elems, dims, st, box))
+          return PDNN_INVALID_PARAMETER;
       } else {
         g.b_mode = B_MN_FHWC;
         const uint64_t dims[4] = {(uint64_t)p.channels, taps, (uint64_t)p.features, 1};
         const uint64_t st[3] = {(uint64_t)p.channels * es, taps * p.channels * es, taps * p.channels * p.features * es};
         const uint32_t box[4] = {(uint32_t)epr, 1, (uint32_t)epr, 1};
-        if (!make_map(&g.b_map, dtype, true, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+        if (!make_map(&g.b_map, dtype, true, w_hi, dims, st, box)) return PDNN_INVALID_PARAMETER;
+        if (w_split != nullptr && !make_map(&g.b_map_lo, dtype, true, w_split + filter_elems, dims, st, box))
+          return PDNN_INVALID_PARAMETER;
       }
+      g.b_presplit = w_split != nullptr ? 1 : 0;
       set_epilogue(g, nullptr);
       g.relu_mask = (relu_mask != nullptr && !mask_pending && aligned16(relu_mask))
                         ? static_cast<const char*>(relu_mask) + ((size_t)qh * p.in_cols + qw) * p.channels * es
