@@ -64,7 +64,7 @@ struct alignas(64) GemmArgs {
   int tw, th, tn;    // a_mn == 0: pixel box of a row tile; a_mn == 1: pixel box of a reduction slab
   int etw, eth, etn; // pixel box of a row tile as the epilogue sees it
   int num_taps;
-  int b_presplit;    // fp32 (3xTF32): B arrives split into hi and lo parts (b_map, b_map_lo); only A is split in the kernel
+  int b_presplit;    // fp32 (3xTF32): the lo part of B arrives by TMA too (b_map_lo); only A is split in the kernel
   int cta_pair;      // 1: run by umma_gemm_pair2_kernel (clusters of two CTAs, 256 x 256 tiles)
   int tap_pack;      // a_mn == 1: taps per tile (2: the second 64 rows of the A tile are the next tap's channels)
   int cblocks;       // a_mn == 0: reduction blocks per tap
@@ -1050,8 +1050,9 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     if (EPI != 0 && lane == 0) bulk_wait_group<0>();
   } else if (SPLIT) {
     // ------------------------------- hi/lo split (fp32 as 3xTF32) ----------------------------
-    // hi keeps the 19 leading bits (what the tensor core reads of an fp32 word); lo = x - hi is
-    // exact in fp32.  Element positions do not change, so the swizzle is irrelevant here.
+    // hi is the 19 leading bits of an fp32 word, which is all the tensor core reads of it, so the
+    // landed tile serves as the hi part as it is; lo = x - hi is exact in fp32 and is written to the
+    // second part of the stage.  Element positions do not change, so the swizzle is irrelevant here.
     const int tid = threadIdx.x - 6 * 32;  // 0..127
     const int chunks = (int)((a.b_presplit ? (uint32_t)kABytes : part_bytes) >> 4);  // A comes first in a part
     int s = 0;
@@ -1080,8 +1081,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
           l.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(h.y));
           l.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(h.z));
           l.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(h.w));
-          hi[c] = h;
-          lo[c] = l;
+          lo[c] = l;  // the hi part stays as it is: the tensor core reads the 19 leading bits of an fp32 word only
         }
         fence_proxy_async_smem();
         __syncwarp();
@@ -2064,13 +2064,12 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
   return st;
 }
 
-// hi keeps the 19 leading bits of an fp32 word (what the tensor core reads of it), lo = x - hi is exact.
-__global__ void __launch_bounds__(256) split_hi_lo_kernel(const float* __restrict__ x, float* __restrict__ hi,
-                                                          float* __restrict__ lo, size_t n) {
+// The lo part of a 3xTF32 operand: the tensor core reads the 19 leading bits of an fp32 word (hi, which
+// therefore needs no copy); lo = x - hi is exact in fp32.
+__global__ void __launch_bounds__(256) split_lo_kernel(const float* __restrict__ x, float* __restrict__ lo, size_t n) {
   for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
-    const float v = x[i], h = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
-    hi[i] = h;
-    lo[i] = v - h;
+    const float v = x[i];
+    lo[i] = v - __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
   }
 }
 
@@ -2183,15 +2182,14 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   g.num_taps = nt;
   g.cblocks = ceil_div(p.channels, epr);
   const uint64_t taps = (uint64_t)p.window_rows * p.window_cols;
-  // fp32 (3xTF32) with enough work to pay for one extra pass over the filter: the filter is split into
-  // its hi and lo parts once, ahead of the GEMM, and both arrive by TMA; the kernel's split warps then
-  // only have the A tiles to split (a third less shared-memory traffic per stage).
+  // fp32 (3xTF32) with enough work to pay for one extra pass over the filter: the lo part of the filter
+  // is computed once, ahead of the GEMM, and arrives by TMA like the filter itself (whose words serve as
+  // the hi part); the kernel's split warps then only have the A tiles to split.
   const size_t filter_elems = (size_t)taps * p.channels * p.features;
   float* w_split = nullptr;
   if (dtype == PDNN_F32 && (size_t)p.batch * p.out_rows * p.out_cols >= 2048 && aligned16(w)) {
-    if (cudaMallocAsync(reinterpret_cast<void**>(&w_split), 2 * filter_elems * sizeof(float), s) == cudaSuccess) {
-      split_hi_lo_kernel<<<grid_for(filter_elems, 256, sms), 256, 0, s>>>(static_cast<const float*>(w), w_split,
-                                                                            w_split + filter_elems, filter_elems);
+    if (cudaMallocAsync(reinterpret_cast<void**>(&w_split), filter_elems * sizeof(float), s) == cudaSuccess) {
+      split_lo_kernel<<<grid_for(filter_elems, 256, sms), 256, 0, s>>>(static_cast<const float*>(w), w_split, filter_elems);
       count_launch();
       g.b_presplit = 1;
     } else {
@@ -2225,8 +2223,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     const uint32_t box[4] = {(uint32_t)epr, 1, (uint32_t)g.bn, 1};
     return make_map(map, dtype, false, base, dims, st, box);
   };
-  const bool maps_ok = make_b_map(&g.b_map, w_split != nullptr ? static_cast<const void*>(w_split) : w) &&
-                       (w_split == nullptr || make_b_map(&g.b_map_lo, w_split + filter_elems));
+  const bool maps_ok = make_b_map(&g.b_map, w) && (w_split == nullptr || make_b_map(&g.b_map_lo, w_split));
   if (!maps_ok) {
     if (w_split != nullptr) cudaFreeAsync(w_split, s);
     return PDNN_INVALID_PARAMETER;
@@ -2251,13 +2248,12 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
   const int sms = device_sm_count();
   const bool hwcf = p.filter_format == 0;
   const int epr = dtype == PDNN_F32 ? 32 : 64;
-  // fp32: the filter split into hi and lo parts ahead of the GEMMs, as in the forward pass
+  // fp32: the lo part of the filter computed ahead of the GEMMs, as in the forward pass
   const size_t filter_elems = (size_t)p.window_rows * p.window_cols * p.channels * p.features;
   float* w_split = nullptr;
   if (dtype == PDNN_F32 && (size_t)p.batch * p.in_rows * p.in_cols >= 2048 && aligned16(w) &&
-      cudaMallocAsync(reinterpret_cast<void**>(&w_split), 2 * filter_elems * sizeof(float), s) == cudaSuccess) {
-    split_hi_lo_kernel<<<grid_for(filter_elems, 256, sms), 256, 0, s>>>(static_cast<const float*>(w), w_split,
-                                                                          w_split + filter_elems, filter_elems);
+      cudaMallocAsync(reinterpret_cast<void**>(&w_split), filter_elems * sizeof(float), s) == cudaSuccess) {
+    split_lo_kernel<<<grid_for(filter_elems, 256, sms), 256, 0, s>>>(static_cast<const float*>(w), w_split, filter_elems);
     count_launch();
   } else if (dtype == PDNN_F32) {
     cudaGetLastError();
@@ -2270,7 +2266,7 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
       if (ptr != nullptr) cudaFreeAsync(ptr, s);
     }
   } release{w_split, s};
-  const void* w_hi = w_split != nullptr ? static_cast<const void*>(w_split) : w;
+
   // dx is produced one output parity class at a time: positions h = sr*i + qh, w = sc*j + qw only
   // receive taps with r = (qh + pad) mod sr, s = (qw + pad) mod sc, and within a class the
   // relation between i and the dy row is a plain shift.
@@ -2381,16 +2377,16 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
         const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.channels * p.features * es,
                                 taps * p.channels * p.features * es};
         const uint32_t box[4] = {(uint32_t)epr, (uint32_t)g.bn, 1, 1};
-        if (!make_map(&g.b_map, dtype, false, w_hi, dims, st, box)) return PDNN_INVALID_PARAMETER;
-        if (w_split != nullptr && !make_map(&g.b_map_lo, dtype, false, w_split + filter_elems, dims, st, box))
+        if (!make_map(&g.b_map, dtype, false, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+        if (w_split != nullptr && !make_map(&g.b_map_lo, dtype, false, w_split, dims, st, box))
           return PDNN_INVALID_PARAMETER;
       } else {
         g.b_mode = B_MN_FHWC;
         const uint64_t dims[4] = {(uint64_t)p.channels, taps, (uint64_t)p.features, 1};
         const uint64_t st[3] = {(uint64_t)p.channels * es, taps * p.channels * es, taps * p.channels * p.features * es};
         const uint32_t box[4] = {(uint32_t)epr, 1, (uint32_t)epr, 1};
-        if (!make_map(&g.b_map, dtype, true, w_hi, dims, st, box)) return PDNN_INVALID_PARAMETER;
-        if (w_split != nullptr && !make_map(&g.b_map_lo, dtype, true, w_split + filter_elems, dims, st, box))
+        if (!make_map(&g.b_map, dtype, true, w, dims, st, box)) return PDNN_INVALID_PARAMETER;
+        if (w_split != nullptr && !make_map(&g.b_map_lo, dtype, true, w_split, dims, st, box))
           return PDNN_INVALID_PARAMETER;
       }
       g.b_presplit = w_split != nullptr ? 1 : 0;
