@@ -1843,26 +1843,22 @@ int finish_forward(GemmArgs& g, int dtype, void* y, const PdnnConv2DParams& p, c
 // pixel, and the tensor map walks output pixels with a stride of stride_cols pixels, so rows
 // overlap.  The reduction runs over filter rows: R steps of 64 (32) elements.  The filter is
 // repacked the same way ([R][8][CP][K], zeros in the padding).
+// One thread per packed pixel; the grid is (row segments, padded rows, images), so no thread divides.
 template <typename T>
 __global__ void __launch_bounds__(256) pack_small_c_input_kernel(const T* __restrict__ x, uint4* __restrict__ xp, int N,
                                                                 int H, int W, int C, int Hp, int Wp, int pad_top,
                                                                 int pad_left) {
   constexpr int CP = 16 / sizeof(T);
-  const size_t total = (size_t)N * Hp * Wp;
-  for (size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (size_t)gridDim.x * 256) {
-    const int wp = (int)(idx % Wp);
-    const size_t t = idx / Wp;
-    const int hp = (int)(t % Hp);
-    const int n = (int)(t / Hp);
-    const int h = hp - pad_top, w = wp - pad_left;
-    Vec16<T> pk;
-    pk.raw = make_uint4(0u, 0u, 0u, 0u);
-    if (h >= 0 && h < H && w >= 0 && w < W) {
-      const T* src = x + (((size_t)n * H + h) * W + w) * C;
-      for (int c = 0; c < C && c < CP; ++c) pk.set(c, src[c]);
-    }
-    xp[idx] = pk.raw;
+  const int wp = (int)(blockIdx.x * 256u + threadIdx.x), hp = (int)blockIdx.y, n = (int)blockIdx.z;
+  if (wp >= Wp) return;
+  const int h = hp - pad_top, w = wp - pad_left;
+  Vec16<T> pk;
+  pk.raw = make_uint4(0u, 0u, 0u, 0u);
+  if (h >= 0 && h < H && w >= 0 && w < W) {
+    const T* src = x + (((size_t)n * H + h) * W + w) * C;
+    for (int c = 0; c < C && c < CP; ++c) pk.set(c, src[c]);
   }
+  xp[((size_t)n * Hp + hp) * Wp + wp] = pk.raw;
 }
 
 // The same with 4 channels of 16 bits per pixel (8 bytes): half the bytes for a 3-channel image.
@@ -1870,21 +1866,15 @@ __global__ void __launch_bounds__(256) pack_small_c_input_narrow_kernel(const un
                                                                        uint2* __restrict__ xp, int N, int H, int W,
                                                                        int C, int Hp, int Wp, int pad_top,
                                                                        int pad_left) {
-  // 32-bit index arithmetic: the host only takes this path with fewer than 2^31 packed pixels
-  const unsigned total = (unsigned)N * (unsigned)Hp * (unsigned)Wp;
-  for (unsigned idx = blockIdx.x * 256u + threadIdx.x; idx < total; idx += gridDim.x * 256u) {
-    const unsigned t = idx / (unsigned)Wp;
-    const int wp = (int)(idx - t * (unsigned)Wp);
-    const int n = (int)(t / (unsigned)Hp);
-    const int hp = (int)(t - (unsigned)n * (unsigned)Hp);
-    const int h = hp - pad_top, w = wp - pad_left;
-    unsigned v[4] = {0u, 0u, 0u, 0u};
-    if (h >= 0 && h < H && w >= 0 && w < W) {
-      const unsigned short* src = x + (((size_t)n * H + h) * W + w) * C;
-      for (int c = 0; c < C && c < 4; ++c) v[c] = src[c];
-    }
-    xp[idx] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
+  const int wp = (int)(blockIdx.x * 256u + threadIdx.x), hp = (int)blockIdx.y, n = (int)blockIdx.z;
+  if (wp >= Wp) return;
+  const int h = hp - pad_top, w = wp - pad_left;
+  unsigned v[4] = {0u, 0u, 0u, 0u};
+  if (h >= 0 && h < H && w >= 0 && w < W) {
+    const unsigned short* src = x + (((size_t)n * H + h) * W + w) * C;
+    for (int c = 0; c < C && c < 4; ++c) v[c] = src[c];
   }
+  xp[((size_t)n * Hp + hp) * Wp + wp] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
 }
 
 // Filter [R][S][C][K] -> [R][8][CP][K], zeros for s >= S and c >= C.
@@ -1906,7 +1896,8 @@ __global__ void __launch_bounds__(256) pack_small_c_filter_kernel(const T* __res
 bool small_c_applicable(int dtype, const PdnnConv2DParams& p) {
   const int cp = 16 / (int)dtype_size(dtype);
   return p.input_format == 0 && p.filter_format == 0 && p.groups == 1 && p.channels < cp && p.window_cols <= 8 &&
-         p.window_rows <= kMaxTaps && p.stride_rows <= 4 && p.stride_cols <= 4 && p.features % cp == 0;
+         p.window_rows <= kMaxTaps && p.stride_rows <= 4 && p.stride_cols <= 4 && p.features % cp == 0 &&
+         p.batch <= 65535 && (p.out_rows - 1) * p.stride_rows + p.window_rows <= 65535;  // the repack's grid
 }
 
 struct SmallCPlan {
@@ -2034,10 +2025,9 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
       return -1;
     }
   }
-  const size_t n_pix = (size_t)p.batch * sp.Hp * Wp;
   const size_t n_fil = (size_t)p.window_rows * krows * p.features;
   if (dtype == PDNN_F32) {
-    pack_small_c_input_kernel<float><<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
+    pack_small_c_input_kernel<float><<<dim3((unsigned)ceil_div(sp.Wp, 256), (unsigned)sp.Hp, (unsigned)p.batch), 256, 0, s>>>(
         static_cast<const float*>(x), reinterpret_cast<uint4*>(xp), p.batch, p.in_rows, p.in_cols, p.channels, sp.Hp,
         sp.Wp, p.pad_rows, p.pad_cols);
     pack_small_c_filter_kernel<float><<<grid_for(n_fil, 256, sms), 256, 0, s>>>(
@@ -2045,11 +2035,11 @@ int conv_forward_small_c(int dtype, const void* x, const void* w, void* y, const
   } else {
     // fp16 and bf16 are both moved as 16-bit words
     if (narrow)
-      pack_small_c_input_narrow_kernel<<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
+      pack_small_c_input_narrow_kernel<<<dim3((unsigned)ceil_div(Wp, 256), (unsigned)sp.Hp, (unsigned)p.batch), 256, 0, s>>>(
           static_cast<const unsigned short*>(x), reinterpret_cast<uint2*>(xp), p.batch, p.in_rows, p.in_cols, p.channels,
           sp.Hp, Wp, p.pad_rows, p.pad_cols);
     else
-      pack_small_c_input_kernel<__half><<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
+      pack_small_c_input_kernel<__half><<<dim3((unsigned)ceil_div(sp.Wp, 256), (unsigned)sp.Hp, (unsigned)p.batch), 256, 0, s>>>(
           static_cast<const __half*>(x), reinterpret_cast<uint4*>(xp), p.batch, p.in_rows, p.in_cols, p.channels, sp.Hp,
           sp.Wp, p.pad_rows, p.pad_cols);
     pack_small_c_filter_kernel<__half><<<grid_for(n_fil, 256, sms), 256, 0, s>>>(
@@ -2627,13 +2617,12 @@ int conv_filter_backprop_small_c(int dtype, const void* x, const void* dy, void*
       return -1;
     }
   }
-  const size_t n_pix = (size_t)p.batch * q.sp.Hp * q.sp.Wp;
   if (dtype == PDNN_F32)
-    pack_small_c_input_kernel<float><<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
+    pack_small_c_input_kernel<float><<<dim3((unsigned)ceil_div(q.sp.Wp, 256), (unsigned)q.sp.Hp, (unsigned)p.batch), 256, 0, s>>>(
         static_cast<const float*>(x), reinterpret_cast<uint4*>(xp), p.batch, p.in_rows, p.in_cols, p.channels, q.sp.Hp,
         q.sp.Wp, p.pad_rows, p.pad_cols);
   else
-    pack_small_c_input_kernel<__half><<<grid_for(n_pix, 256, sms), 256, 0, s>>>(
+    pack_small_c_input_kernel<__half><<<dim3((unsigned)ceil_div(q.sp.Wp, 256), (unsigned)q.sp.Hp, (unsigned)p.batch), 256, 0, s>>>(
         static_cast<const __half*>(x), reinterpret_cast<uint4*>(xp), p.batch, p.in_rows, p.in_cols, p.channels,
         q.sp.Hp, q.sp.Wp, p.pad_rows, p.pad_cols);
   int st = check_launch("conv2d small-channel packing");
