@@ -527,6 +527,22 @@ __global__ void __launch_bounds__(kBlock)
   }
 }
 
+// The same when one window covers the whole image (global pooling): every pixel of an image
+// receives dy / (rows * cols); one division by a runtime value per thread instead of the window walk.
+template <typename T, int V>
+__global__ void __launch_bounds__(kBlock)
+    pool_avg_grad_global_kernel(const T* __restrict__ dy, T* __restrict__ dx, unsigned cvecs, unsigned per_image,
+                                float count, unsigned n_items) {
+  for (unsigned idx = blockIdx.x * kBlock + threadIdx.x; idx < n_items; idx += gridDim.x * kBlock) {
+    const unsigned n = idx / per_image, cv = idx % cvecs;  // per_image is a multiple of cvecs
+    float dv[V];
+    load_vec<T, V>(dy + ((size_t)n * cvecs + cv) * V, dv);
+#pragma unroll
+    for (int i = 0; i < V; ++i) dv[i] = dv[i] / count;  // the division of the general kernel, for equal results
+    store_vec<T, V>(dx + (size_t)idx * V, dv);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // Depthwise convolution.  Filter [R][S][C][mult], output channel c*mult+m
 // (src/depthwise_conv2d/kernels.h:58-125).  The packet form needs mult == 1.
@@ -1443,6 +1459,14 @@ int launch_pooling(int op, int direction, int dtype, const void* in, void* out, 
     const size_t pixels = direction == 0 ? (size_t)p.batch * p.out_rows * p.out_cols
                                          : (size_t)p.batch * p.in_rows * p.in_cols;
     const size_t items = pixels * (p.channels / (vec ? VN : 1));
+    if (direction == 1 && vec && p.out_rows == 1 && p.out_cols == 1 && p.pad_rows == 0 && p.pad_cols == 0 &&
+        p.window_rows == p.in_rows && p.window_cols == p.in_cols && items < 0xFFFF0000ull) {
+      const unsigned cvecs = (unsigned)(p.channels / VN);
+      pool_avg_grad_global_kernel<T, VN><<<grid_for(items, kBlock, sms), kBlock, 0, s>>>(
+          static_cast<const T*>(in), static_cast<T*>(out), cvecs, (unsigned)(p.in_rows * p.in_cols) * cvecs,
+          (float)(p.in_rows * p.in_cols), (unsigned)items);
+      return check_launch("pooling average gradient (global)");
+    }
     const unsigned grid = grid_for(items, kBlock, sms);
     const bool wide = items >= 0xFFFFFFFFull - (size_t)grid * kBlock;
     auto go = [&](auto vtag, auto itag) {
