@@ -123,7 +123,7 @@ struct alignas(64) GemmArgs {
   int mask_slots;        // 4 KB mask slots per epilogue warp: 2 where shared memory allows, else 1
   int accumulate;  // packed 16-bit epilogues, no bias: the block already in the output is added (before the mask)
   int reduce_add;  // staged fp32 epilogue of the filter backprop: every pixel split adds its tile to the output
-  int mask_smem_bytes;  // 256 bytes per epilogue warp for the sign bits of a 32-row block
+  int mask_smem_bytes;  // the barriers of the epilogue warps' mask slots (the slots themselves follow the staging slices)
   // Time limit of one barrier wait; a wait that lasts longer means a lost arrival, and the CTA
   // gives up (see umma::mbar_wait).
   unsigned long long wait_limit_ns;

@@ -301,7 +301,7 @@ class ConvStackRunner:
         if not hasattr(self, "segments"):
             self._plan_backward()
             self.scratch2 = self.torch.empty_like(self.scratch)
-        self._fresh, self._masked, self._block_grad, self._arrived = set(), set(), {}, {}
+        self._fresh, self._masked, self._block_grad = set(), set(), {}
 
     def backward_segment(self, seg):
         """The backward pass of one segment: per convolution (last first) the ReLU gradient - unless the
