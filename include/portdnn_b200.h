@@ -119,6 +119,10 @@ typedef struct PdnnConvEpilogue {
   int activation;    /* PdnnActivation */
   float alpha;       /* scales the convolution result; 1 = plain */
   float beta;        /* scales the previous contents of out; 0 = overwrite */
+  void* relu_bitmask; /* optional second output (NULL = none), NHWC with features % 8 == 0: one bit per
+                         output element, bit (i % 8) of byte (i / 8) for element i, set where the result is
+                         positive - the ReLU mask a later input backprop needs, at a sixteenth of the bytes
+                         (PdnnBackpropFusion::relu_bitmask) */
 } PdnnConvEpilogue;
 
 /* Replaces conv2d::launch -> sublaunch -> launch_{direct,tiled,im2col,winograd,matmul}
@@ -158,11 +162,15 @@ int pdnn_conv2d_fused(int dtype, const void* input, const void* filter, void* ou
  *    FilterBackprop: dW += gradient (gradient accumulation over micro-batches, or into a buffer the
  *    caller zeroed).  With fp32 gradients the pixel splits of the kernel add their tiles to dW
  *    directly (TMA reduction) instead of writing partial sums for a second kernel, so no workspace
- *    is used and the order of the float additions is not fixed from run to run. */
+ *    is used and the order of the float additions is not fixed from run to run.
+ *  - relu_bitmask (InputBackprop only, 16-bit tensors, channels % 8 == 0): the same mask as
+ *    relu_forward_output > 0 in the one-bit-per-element form PdnnConvEpilogue::relu_bitmask writes;
+ *    give one or the other. */
 typedef struct PdnnBackpropFusion {
   const void* relu_forward_output;
   int output_f32;
   int accumulate;
+  const void* relu_bitmask;
 } PdnnBackpropFusion;
 
 /* As pdnn_conv2d for PDNN_INPUT_BACKPROP / PDNN_FILTER_BACKPROP, with the fused forms described at

@@ -13,6 +13,11 @@ char* last_error_buffer() {
   return buf;
 }
 
+bool& bitmask_written_flag() {
+  static thread_local bool written = false;
+  return written;
+}
+
 int current_device() {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess) {
@@ -170,7 +175,9 @@ int run_direct_backprop(int pass, int dtype, const void* in, const void* fil, vo
   } else {
     st = launch_direct_conv(pass, dtype, in, fil, out, p, nullptr, s);
   }
-  if (st != PDNN_OK || pass != PDNN_INPUT_BACKPROP || fusion == nullptr || fusion->relu_forward_output == nullptr) return st;
+  if (st != PDNN_OK || pass != PDNN_INPUT_BACKPROP || fusion == nullptr) return st;
+  if (fusion->relu_bitmask != nullptr) return launch_relu_grad_bits(dtype, fusion->relu_bitmask, out, n_dx, s);
+  if (fusion->relu_forward_output == nullptr) return st;
   return launch_pointwise_grad(PDNN_ACT_RELU, dtype, fusion->relu_forward_output, out, out, n_dx, s);
 }
 
@@ -189,8 +196,10 @@ int run_conv(int pass, int dtype, const void* in, const void* fil, void* out, co
     // NCHW tensors with an FCHW filter (the only pairing validate_conv lets through): the NHWC
     // kernels between two transposes.  The reference's NCHW path is its direct kernel
     // (src/conv2d/direct/kernels_nchw.h:28,157,300), which computes the same sums.
-    if (fusion != nullptr && (fusion->relu_forward_output != nullptr || fusion->accumulate))
+    if (fusion != nullptr && (fusion->relu_forward_output != nullptr || fusion->relu_bitmask != nullptr || fusion->accumulate))
       return fail(PDNN_INVALID_PARAMETER, "conv2d: the fused input-backprop forms need NHWC tensors");
+    if (epi != nullptr && epi->relu_bitmask != nullptr)
+      return fail(PDNN_INVALID_PARAMETER, "conv2d: a ReLU bitmask needs NHWC tensors");
     const bool read_out = epi != nullptr && epi->beta != 0.f;
     return conv2d_nchw(pass, dtype, in, fil, out, *p, read_out, s,
                        [&](const void* a, const void* b, void* c, const PdnnConv2DParams& q) {
@@ -235,8 +244,12 @@ int pdnn_conv2d_backprop_fused(int pass, int dtype, const void* input, const voi
                                void* workspace, size_t workspace_elems, void* stream) {
   if (pass != PDNN_INPUT_BACKPROP && pass != PDNN_FILTER_BACKPROP)
     return fail(PDNN_INVALID_PARAMETER, "conv2d: the fused backprop forms exist for the two backprop passes only");
-  if (fusion != nullptr && pass == PDNN_FILTER_BACKPROP && fusion->relu_forward_output != nullptr)
-    return fail(PDNN_INVALID_PARAMETER, "conv2d: relu_forward_output belongs to the input backprop");
+  if (fusion != nullptr && pass == PDNN_FILTER_BACKPROP && (fusion->relu_forward_output != nullptr || fusion->relu_bitmask != nullptr))
+    return fail(PDNN_INVALID_PARAMETER, "conv2d: relu_forward_output / relu_bitmask belong to the input backprop");
+  if (fusion != nullptr && fusion->relu_bitmask != nullptr &&
+      (fusion->relu_forward_output != nullptr || params == nullptr || params->channels % 8 != 0 || dtype == PDNN_F32))
+    return fail(PDNN_INVALID_PARAMETER,
+                "conv2d: relu_bitmask stands in for relu_forward_output (16-bit tensors, a multiple of 8 channels)");
   if (fusion != nullptr && pass == PDNN_INPUT_BACKPROP && fusion->output_f32)
     return fail(PDNN_INVALID_PARAMETER, "conv2d: output_f32 belongs to the filter backprop");
   return run_conv(pass, dtype, input, filter, output, params, algorithm, nullptr, fusion, workspace, workspace_elems,
@@ -248,8 +261,17 @@ int pdnn_conv2d_fused(int dtype, const void* input, const void* filter, void* ou
                       void* stream) {
   if (epilogue != nullptr && (epilogue->activation < PDNN_ACT_NONE || epilogue->activation > PDNN_ACT_RELU6))
     return fail(PDNN_INVALID_PARAMETER, "conv2d: unknown activation %d", epilogue->activation);
-  return run_conv(PDNN_FORWARD, dtype, input, filter, output, params, algorithm, epilogue, nullptr, workspace,
-                  workspace_elems, stream);
+  const bool want_bits = epilogue != nullptr && epilogue->relu_bitmask != nullptr;
+  if (want_bits && params != nullptr && (params->features % 8 != 0 || params->input_format != 0))
+    return fail(PDNN_INVALID_PARAMETER, "conv2d: a ReLU bitmask needs NHWC tensors and a multiple of 8 features");
+  bitmask_written_flag() = false;
+  const int st = run_conv(PDNN_FORWARD, dtype, input, filter, output, params, algorithm, epilogue, nullptr, workspace,
+                          workspace_elems, stream);
+  if (st != PDNN_OK || !want_bits || bitmask_written_flag()) return st;
+  // the kernel that ran has no bitmask form: one pass over the output
+  return launch_relu_bitmask(dtype, output, epilogue->relu_bitmask,
+                             (size_t)params->batch * params->out_rows * params->out_cols * params->features,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int pdnn_conv2d_validate(int pass, const PdnnConv2DParams* params, int algorithm) {

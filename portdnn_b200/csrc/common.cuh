@@ -119,6 +119,10 @@ int launch_bias_add(int dtype, const void* in, const void* bias, void* out, size
                     cudaStream_t s);
 int launch_binaryop(int op, int dtype, const void* lhs, const int* lhs_dims, int n_lhs, const void* rhs,
                     const int* rhs_dims, int n_rhs, void* out, cudaStream_t s);
+int launch_relu_bitmask(int dtype, const void* y, void* bits, size_t n, cudaStream_t s);
+int launch_relu_grad_bits(int dtype, const void* bits, void* dx, size_t n, cudaStream_t s);
+// Set by the tensor-core launch when its epilogue wrote the bitmask the caller asked for (thread-local).
+bool& bitmask_written_flag();
 int launch_scale_blend(int dtype, const void* a, float alpha, const void* b, float beta, void* out, size_t n,
                        cudaStream_t s);
 int launch_direct_conv(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,

@@ -2092,4 +2092,51 @@ int launch_depthwise_filter_backprop_static(int dtype, const void* in, const voi
   });
 }
 
+// ------------------------------------------------------------------------------------------
+// One-bit-per-element ReLU masks (bit e of byte i / 8 for element i: "positive"), the general forms
+// beside the tensor-core epilogues that write and read them: from a tensor, and applied to a gradient.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kBlock) relu_bitmask_kernel(const T* __restrict__ y, unsigned char* __restrict__ bits,
+                                                              size_t n_bytes) {
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n_bytes; i += (size_t)gridDim.x * kBlock) {
+    unsigned b = 0u;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) b |= (to_f32(y[i * 8 + e]) > 0.f ? 1u : 0u) << e;
+    bits[i] = (unsigned char)b;
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(kBlock) relu_grad_bits_kernel(const unsigned char* __restrict__ bits, T* __restrict__ dx,
+                                                                size_t n_bytes) {
+  for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < n_bytes; i += (size_t)gridDim.x * kBlock) {
+    const unsigned b = bits[i];
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (!((b >> e) & 1u)) dx[i * 8 + e] = from_f32<T>(0.f);
+  }
+}
+
+int launch_relu_bitmask(int dtype, const void* y, void* bits, size_t n, cudaStream_t s) {
+  if (n % 8) return fail(PDNN_INVALID_PARAMETER, "relu bitmask: the element count must be a multiple of 8");
+  const int sms = device_sm_count();
+  return dispatch_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    relu_bitmask_kernel<T><<<grid_for(n / 8, kBlock, sms), kBlock, 0, s>>>(static_cast<const T*>(y),
+                                                                          static_cast<unsigned char*>(bits), n / 8);
+    return check_launch("relu bitmask");
+  });
+}
+
+int launch_relu_grad_bits(int dtype, const void* bits, void* dx, size_t n, cudaStream_t s) {
+  if (n % 8) return fail(PDNN_INVALID_PARAMETER, "relu bitmask: the element count must be a multiple of 8");
+  const int sms = device_sm_count();
+  return dispatch_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    relu_grad_bits_kernel<T><<<grid_for(n / 8, kBlock, sms), kBlock, 0, s>>>(static_cast<const unsigned char*>(bits),
+                                                                            static_cast<T*>(dx), n / 8);
+    return check_launch("relu gradient from a bitmask");
+  });
+}
+
 }  // namespace pdnn

@@ -120,6 +120,11 @@ struct alignas(64) GemmArgs {
   const void* relu_mask;
   CUtensorMap mask_map;  // the mask tensor with the geometry of out_map (set when relu_mask is)
   CUtensorMap b_map_lo;  // b_presplit: the lo parts of B, same geometry as b_map
+  // One bit per output element, bit e of byte (element offset / 8): "the element is positive".
+  // bitmask_out (packed forward epilogue): written beside the output, for a later input backprop;
+  // mask_bits (mask epilogue): the ReLU mask in that form, read instead of the mask tensor.
+  void* bitmask_out;
+  const void* mask_bits;
   int mask_slots;        // 4 KB mask slots per epilogue warp: 2 where shared memory allows, else 1
   int accumulate;  // packed 16-bit epilogues, no bias: the block already in the output is added (before the mask)
   int reduce_add;  // staged fp32 epilogue of the filter backprop: every pixel split adds its tile to the output
@@ -397,14 +402,17 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
 // writes them into the row's 128 bytes of the staging slice.  `bv` holds the bias of those 32
 // columns (zeros without a bias), `mk` (MASK only) the keep masks of those columns.
 template <typename OutT, bool MASK>
-__device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bool zero, bool has_bias, const uint4* bv,
-                                                   int act, uint8_t* row_ptr, int row, int chunk_base, const uint4* mk) {
+__device__ __forceinline__ uint32_t fast_convert_store(const uint32_t (&acc)[32], bool zero, bool has_bias, const uint4* bv,
+                                                       int act, uint8_t* row_ptr, int row, int chunk_base, const uint4* mk,
+                                                       bool want_bits = false) {
   using P2 = typename Pair<OutT>::type;
   const P2 zero2 = Pair<OutT>::splat(0.f), six2 = Pair<OutT>::splat(6.f);
+  uint32_t bits = 0u;  // want_bits: bit c = column c of these 32 is positive (a positive 16-bit float is a positive integer)
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     const uint32_t bw[4] = {bv[g].x, bv[g].y, bv[g].z, bv[g].w};
     uint32_t o[4];
+    [[maybe_unused]] uint32_t pos[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       P2 v = zero ? zero2
@@ -415,6 +423,12 @@ __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bo
         if (act == PDNN_ACT_RELU6) v = __hmin2(v, six2);
       }
       o[i] = pair_bits(v);
+      if (!MASK && want_bits) pos[i] = __hgt2_mask(v, zero2);  // 0xFFFF per positive half
+    }
+    if (!MASK && want_bits) {
+      // one distinct bit per element, then the two halves folded: elements 2i (low halves) and 2i + 1
+      const uint32_t c = (pos[0] & 0x00020001u) | (pos[1] & 0x00080004u) | (pos[2] & 0x00200010u) | (pos[3] & 0x00800040u);
+      bits |= ((c | (c >> 16)) & 0xFFu) << (g * 8);
     }
     if (MASK) {  // mk: 0xFFFF in every halfword whose mask element is positive
       o[0] &= mk[g].x;
@@ -423,6 +437,32 @@ __device__ __forceinline__ void fast_convert_store(const uint32_t (&acc)[32], bo
       o[3] &= mk[g].w;
     }
     *reinterpret_cast<uint4*>(row_ptr + (((chunk_base + g) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  return bits;
+}
+
+// Element offset of the lane's row of the tile in the output tensor (row = q32 + lane), or -1 if the row
+// lies outside the tensor.
+__device__ __forceinline__ long long row_element_offset(const GemmArgs& a, const TileCoord& t, int q32, int lane) {
+  const int sh_w = __ffs(a.etw) - 1, sh_h = __ffs(a.eth) - 1, row = q32 + lane;
+  const int w = t.w0 + (row & (a.etw - 1)), h = t.h0 + ((row >> sh_w) & (a.eth - 1)), n = t.n0 + (row >> (sh_w + sh_h));
+  if (!(w < a.ext_w && h < a.ext_h && n < a.ext_n)) return -1;
+  return (long long)n * a.stride_n + (long long)h * a.stride_h + (long long)w * a.stride_w;
+}
+
+// 64 mask bits of a row -> keep masks of the eight 16-byte chunks (0xFFFF per kept halfword).
+__device__ __forceinline__ void expand_mask_bits(uint2 bits, uint4 (&mk)[8]) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const uint32_t b = ((g < 4 ? bits.x : bits.y) >> (8 * (g & 3))) & 0xFFu;
+    uint32_t m[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // a one-bit field read as a signed number is 0 or all ones
+      const int lo = ((int)(b << (31 - 2 * i))) >> 31, hi = ((int)(b << (30 - 2 * i))) >> 31;
+      m[i] = __byte_perm((uint32_t)lo, (uint32_t)hi, 0x5410);
+    }
+    mk[g] = make_uint4(m[0], m[1], m[2], m[3]);
   }
 }
 
@@ -473,6 +513,16 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
                                                        uint32_t& store_count, uint32_t bias_s, int q32, MaskSlot& ms,
                                                        volatile int* abort_flag) {
   const int act = a.act;
+  const bool bit_mask = MASK && a.mask_bits != nullptr, emit_bits = !MASK && a.bitmask_out != nullptr;
+  const long long row_off = (a.accumulate != 0 || bit_mask || emit_bits) ? row_element_offset(a, t, q32, lane) : -1;
+  // mask bits of the lane's row for every 64-column block of the tile, requested up front
+  uint2 pre[4] = {make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u)};
+  if (bit_mask && row_off >= 0) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+      if (b * 64 < a.bn && t.nf0 + b * 64 < a.ext_cols)
+        pre[b] = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(a.mask_bits) + ((row_off + t.nf0 + b * 64) >> 3)));
+  }
 #pragma unroll 1
   for (int c0 = 0; c0 < a.bn; c0 += 64, ++store_count) {
     const uint32_t slot = store_count & (uint32_t)(ws.nsw - 1);
@@ -486,12 +536,7 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
     const bool add_prev = a.accumulate != 0, has_bias = add_prev || (!MASK && bias_s != 0u);
     if (add_prev) {
       // accumulating form: the lane's own row of the block that is in the output already (128 bytes)
-      const int sh_w = __ffs(a.etw) - 1, sh_h = __ffs(a.eth) - 1, row = q32 + lane;
-      const int w = t.w0 + (row & (a.etw - 1)), h = t.h0 + ((row >> sh_w) & (a.eth - 1)), n = t.n0 + (row >> (sh_w + sh_h));
-      const uint16_t* prev = nullptr;
-      if (w < a.ext_w && h < a.ext_h && n < a.ext_n)
-        prev = static_cast<const uint16_t*>(a.out) + (long long)n * a.stride_n + (long long)h * a.stride_h +
-               (long long)w * a.stride_w + t.nf0 + c0;
+      const uint16_t* prev = row_off >= 0 ? static_cast<const uint16_t*>(a.out) + row_off + t.nf0 + c0 : nullptr;
 #pragma unroll
       for (int g = 0; g < 8; ++g)
         bv[g] = (prev != nullptr && t.nf0 + c0 + g * 8 < a.ext_cols) ? ld_global_v4(prev + g * 8) : make_uint4(0u, 0u, 0u, 0u);
@@ -500,8 +545,11 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
       for (int g = 0; g < 8; ++g)
         bv[g] = has_bias ? ld_shared_v4(bias_s + (uint32_t)(t.nf0 + c0 + g * 8) * 2u) : make_uint4(0u, 0u, 0u, 0u);
     }
-    uint4 mk[MASK ? 8 : 1];
-    if (MASK) {
+    uint4 mk[8];
+    if (bit_mask) {
+      const int blk = c0 >> 6;
+      expand_mask_bits(blk == 0 ? pre[0] : blk == 1 ? pre[1] : blk == 2 ? pre[2] : pre[3], mk);
+    } else if (MASK) {
       // this block's mask was requested earlier: take the lane's row out of the slot as keep masks,
       // then let the next request reuse the slot
       const uint32_t mslot = ms.consumed % ms.nslots;
@@ -511,7 +559,10 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
 #pragma unroll
       for (int g = 0; g < 8; ++g) {
         const uint4 m = ld_shared_v4(row_addr + (uint32_t)((g ^ (lane & 7)) << 4));
-        mk[g] = make_uint4(__vcmpgts2(m.x, 0u), __vcmpgts2(m.y, 0u), __vcmpgts2(m.z, 0u), __vcmpgts2(m.w, 0u));
+        using P2 = typename Pair<OutT>::type;
+        const P2 zero2 = Pair<OutT>::splat(0.f);
+        mk[g] = make_uint4(__hgt2_mask(bits_pair<P2>(m.x), zero2), __hgt2_mask(bits_pair<P2>(m.y), zero2),
+                           __hgt2_mask(bits_pair<P2>(m.z), zero2), __hgt2_mask(bits_pair<P2>(m.w), zero2));
       }
       __syncwarp();  // every lane holds its masks: the slot may be overwritten
       ++ms.consumed;
@@ -520,8 +571,10 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
     wait_slice_free(ws, lane);
     if (!zero) tmem_wait_ld();
     uint8_t* row_ptr = ws.buf + slot * 4096u + (size_t)lane * 128;
-    fast_convert_store<OutT, MASK>(acc0, zero, has_bias, bv, act, row_ptr, lane, 0, mk);
-    fast_convert_store<OutT, MASK>(acc1, zero, has_bias, bv + 4, act, row_ptr, lane, 4, MASK ? mk + 4 : mk);
+    const uint32_t lo_bits = fast_convert_store<OutT, MASK>(acc0, zero, has_bias, bv, act, row_ptr, lane, 0, mk, emit_bits);
+    const uint32_t hi_bits = fast_convert_store<OutT, MASK>(acc1, zero, has_bias, bv + 4, act, row_ptr, lane, 4, mk + 4, emit_bits);
+    if (emit_bits && row_off >= 0 && t.nf0 + c0 < a.ext_cols)
+      *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.bitmask_out) + ((row_off + t.nf0 + c0) >> 3)) = make_uint2(lo_bits, hi_bits);
     issue_slice_store(a, t, ws, slot, t.nf0 + c0, lane);
   }
   return true;
@@ -1017,7 +1070,8 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       mask_slot.sub_w = sub_w;
       mask_slot.sub_h = sub_h;
       mask_slot.sub_n = sub_n;
-      for (uint32_t i = 0; i < mask_slot.nslots; ++i) request_mask_block(a, ws, mask_slot);
+      if (a.mask_bits == nullptr)
+        for (uint32_t i = 0; i < mask_slot.nslots; ++i) request_mask_block(a, ws, mask_slot);
     }
 #pragma unroll 1
     for (int tile = first_tile; tile < total_tiles; tile += tile_step, walker.advance()) {
@@ -1518,9 +1572,14 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
                      ? 1
                      : 0;
     // the mask tensor is read through a map with the geometry of the output map
-    if (g.epi_fast && g.relu_mask != nullptr &&
+    if (g.epi_fast && g.relu_mask != nullptr && g.mask_bits == nullptr &&
         !make_map(&g.mask_map, g.out_dtype, false, g.relu_mask, out_dims, out_strides, box))
       g.relu_mask = nullptr;
+  }
+  // the one-bit-per-element forms work on whole 64-column blocks of the packed epilogue
+  if (!(g.epi_fast && g.ext_cols % 64 == 0)) {
+    g.bitmask_out = nullptr;
+    if (g.mask_bits != nullptr) g.relu_mask = g.mask_bits = nullptr;
   }
   const bool split = compute_dtype == PDNN_F32;
   // Two pipelines per CTA, except for 256-column tiles outside pair mode with a reduction of 8 steps or
@@ -1557,7 +1616,7 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
   g.b_res = 0;
   g.b_res_bytes = 0;
   const int fixed = 1024 + kBarBlockBytes + g.bias_smem_bytes + g.mask_smem_bytes;
-  g.mask_slots = g.relu_mask != nullptr ? 1 : 0;
+  g.mask_slots = (g.relu_mask != nullptr && g.mask_bits == nullptr) ? 1 : 0;
   auto staging = [&](int nsw) { return g.tma_store ? g.groups * 4 * (nsw + g.mask_slots) * 4096 : 0; };
   // A small filter (all taps, all column tiles) is kept in shared memory for the whole kernel:
   // the filter tiles are the part of the L2 -> SM traffic that never changes.
@@ -1693,6 +1752,7 @@ int launch_gemm_pair2(const GemmArgs& g, long long total_pairs, cudaStream_t s) 
     cudaGetLastError();
     return fail(PDNN_ALLOCATION_PROBLEM, "tensor-core gemm (CTA pairs): launch failed: %s", cudaGetErrorString(le));
   }
+  if (g.bitmask_out != nullptr) bitmask_written_flag() = true;
   return check_launch("tensor-core gemm (CTA pairs)");
 }
 
@@ -1766,10 +1826,12 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
     cudaGetLastError();
     return fail(PDNN_ALLOCATION_PROBLEM, "tensor-core gemm: launch failed: %s", cudaGetErrorString(le));
   }
+  if (g.bitmask_out != nullptr) bitmask_written_flag() = true;
   return check_launch("tensor-core gemm");
 }
 
 void set_epilogue(GemmArgs& g, const PdnnConvEpilogue* epi) {
+  g.bitmask_out = nullptr;
   g.bias = nullptr;
   g.act = PDNN_ACT_NONE;
   g.alpha = 1.f;
@@ -1779,6 +1841,7 @@ void set_epilogue(GemmArgs& g, const PdnnConvEpilogue* epi) {
     g.act = epi->activation;
     g.alpha = epi->alpha;
     g.beta = epi->beta;
+    g.bitmask_out = epi->relu_bitmask;
   }
 }
 
@@ -2232,7 +2295,8 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
 // carries the same mask, so that positions this convolution does not reach (parity classes without a
 // tap) are left as they are.
 int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, const PdnnConv2DParams& p,
-                        const void* relu_mask, int accumulate, cudaStream_t s, bool try_halo = true) {
+                        const void* relu_mask, const void* mask_bits, int accumulate, cudaStream_t s,
+                        bool try_halo = true) {
   bool mask_pending = false;  // some parity class could not apply the mask in its epilogue
   const size_t es = dtype_size(dtype);
   const int sms = device_sm_count();
@@ -2384,6 +2448,11 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
       g.relu_mask = (relu_mask != nullptr && !mask_pending && aligned16(relu_mask))
                         ? static_cast<const char*>(relu_mask) + ((size_t)qh * p.in_cols + qw) * p.channels * es
                         : nullptr;
+      if (mask_bits != nullptr && !mask_pending && p.channels % 64 == 0 && ((uintptr_t)mask_bits & 7u) == 0) {
+        // the mask as one bit per element: the class's first pixel starts ((qh * W + qw) * C) / 8 bytes in
+        g.mask_bits = static_cast<const char*>(mask_bits) + ((size_t)qh * p.in_cols + qw) * p.channels / 8;
+        g.relu_mask = g.mask_bits;  // "a mask is applied in the epilogue"
+      }
       g.out = static_cast<char*>(dx) + ((size_t)qh * p.in_cols + qw) * p.channels * es;
       g.out_dtype = dtype;
       g.ext_w = Wq;
@@ -2409,17 +2478,19 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
           planned = setup_store(g, dtype, od, os);
         }
         if (!planned) {
-          if (g.halo || g.pair) return conv_input_backprop(dtype, dy, w, dx, p, relu_mask, accumulate, s, false);  // plan again without the halo / pairing
+          if (g.halo || g.pair) return conv_input_backprop(dtype, dy, w, dx, p, relu_mask, mask_bits, accumulate, s, false);  // plan again without the halo / pairing
           return PDNN_INVALID_PARAMETER;
         }
       }
-      if (relu_mask != nullptr && g.relu_mask == nullptr) {
+      if ((relu_mask != nullptr || mask_bits != nullptr) && g.relu_mask == nullptr) {
         // An earlier class may already have masked its pixels; masking them again changes nothing.
         mask_pending = true;
       }
       const int st_ = launch_gemm(g, dtype, s);
       if (st_ != PDNN_OK) return st_;
     }
+  if (mask_pending && mask_bits != nullptr)
+    return launch_relu_grad_bits(dtype, mask_bits, dx, (size_t)p.batch * p.in_rows * p.in_cols * p.channels, s);
   if (mask_pending)
     return launch_pointwise_grad(PDNN_ACT_RELU, dtype, relu_mask, dx, dx,
                                  (size_t)p.batch * p.in_rows * p.in_cols * p.channels, s);
@@ -2838,7 +2909,8 @@ int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, c
       }
       return conv_forward(dtype, in, fil, out, p, epi, s);
     case PDNN_INPUT_BACKPROP:
-      return conv_input_backprop(dtype, in, fil, out, p, relu_mask, accumulate, s);
+      return conv_input_backprop(dtype, in, fil, out, p, relu_mask, fusion != nullptr ? fusion->relu_bitmask : nullptr,
+                                 accumulate, s);
     case PDNN_FILTER_BACKPROP:
       if (small_c_applicable(dtype, p)) {
         const int st = conv_filter_backprop_small_c(dtype, in, fil, out, p, out_f32, accumulate != 0, ws, ws_elems, s);

@@ -127,8 +127,10 @@ class ConvStackRunner:
     same way on the host (tools/network.h)."""
 
     def __init__(self, layers, device, seed, training=False, dtype=None, chunk=None, chunk_layers=0,
-                 fuse_accumulate=True):
-        """fuse_accumulate (training): a gradient with several contributions is summed (and masked) inside the
+                 fuse_accumulate=True, bitmasks=True):
+        """bitmasks (training, 16-bit): every convolution with a ReLU also writes the sign bits of its output (one
+        bit per element), and the input backprops read those instead of the output tensor for the ReLU mask.
+        fuse_accumulate (training): a gradient with several contributions is summed (and masked) inside the
         input backprops that bring them (PdnnBackpropFusion.accumulate); False keeps the unfused chain of an
         input backprop into a temporary, an add and a ReLU-gradient pass.
         chunk / chunk_layers (forward only): the first ``chunk_layers`` layers run depth-first over
@@ -140,6 +142,7 @@ class ConvStackRunner:
         from . import dist as pdist
         self.torch, self.layers, self.training, self.device = torch, layers, training, device
         self.fuse_accumulate = fuse_accumulate
+        self.use_bits = bool(bitmasks and training and self.dtype_is_16bit(dtype, torch))
         self.dtype = dtype or torch.float16
         self.code = api.F16 if self.dtype == torch.float16 else api.BF16 if self.dtype == torch.bfloat16 else api.F32
         g = torch.Generator(device=device).manual_seed(seed)
@@ -168,6 +171,11 @@ class ConvStackRunner:
         self.flops_forward = conv_flops(layers)
         if training:
             self.acts = [torch.empty(n, dtype=self.dtype, device=device) for n in sizes]
+            # sign bits of the ReLU outputs (a sixteenth of the tensors' bytes), where the layer shape allows
+            self.bits = {i: torch.empty(sizes[i] // 8, dtype=torch.uint8, device=device)
+                         for i, l in enumerate(layers)
+                         if self.use_bits and isinstance(l, ConvLayer) and l.activation == api.ACT_RELU and
+                         l.params.features % 8 == 0 and self._bitmask_pays(l)}
             self.grads = [None] * len(layers)
             conv_ids = [i for i, l in enumerate(layers) if isinstance(l, ConvLayer)]
             self.conv_ids = conv_ids
@@ -203,6 +211,20 @@ class ConvStackRunner:
                 names[layers[i].dst] = max(names.get(layers[i].dst, 0), sizes[i] // batch * chunk)
             self.chunk_buffers = {k: torch.empty(v, dtype=self.dtype, device=device) for k, v in names.items()}
 
+    @staticmethod
+    def _bitmask_pays(l):
+        """Reading the sign bits instead of the output tensor saves every input backprop 5-20 us; writing them
+        costs the forward layer next to nothing where its epilogue has slack (1x1 reductions, 3x3 layers:
+        0.4-2.7 us) and 4-19 us in the 1x1 expansions, whose epilogue is the whole layer - there the two
+        cancel, so those keep the tensor form.  The stem's output is masked inside the pool gradient."""
+        p = l.params
+        expansion = p.window_rows == 1 and p.features >= 4 * p.channels
+        return not expansion and l.src != "input"
+
+    @staticmethod
+    def dtype_is_16bit(dtype, torch):
+        return dtype is None or dtype in (torch.float16, torch.bfloat16)
+
     # ---- forward -------------------------------------------------------------------------------
     def _out(self, i):
         return self.acts[i] if self.training else self.buffers[self.layers[i].dst][:self.sizes[i]]
@@ -221,7 +243,8 @@ class ConvStackRunner:
         l, p = self.layers[i], self.layers[i].params
         if isinstance(l, ConvLayer):
             api.conv2d(api.FORWARD, self._in(i), self.weights[i], p, algorithm=api.ALGO_IM2COL, out=self._out(i),
-                       bias=self.biases[i], activation=l.activation, workspace=self.workspaces.get(i))
+                       bias=self.biases[i], activation=l.activation, workspace=self.workspaces.get(i),
+                       relu_bitmask=self.bits.get(i) if self.training else None)
         else:
             api.pooling(l.op, 0, self._in(i), p, out=self._out(i))
 
@@ -342,11 +365,15 @@ class ConvStackRunner:
                     # adds to a gradient that is masked already and may skip what it does not reach.
                     mask = self.acts[j] if self.fuse_mask[j] else None
 
-                    def ibp(dst, accumulate, g=g, i=i, p=p, mask=mask):
+                    bits = self.bits.get(j) if mask is not None else None
+
+                    def ibp(dst, accumulate, g=g, i=i, p=p, mask=mask, bits=bits):
                         if accumulate and not self.fuse_accumulate:
                             return False
+                        masked = mask is not None and (accumulate or dst is self.grads[j])
                         api.conv2d(api.INPUT_BACKPROP, g, self.weights[i], p, algorithm=api.ALGO_IM2COL, out=dst,
-                                   relu_forward_output=mask if (accumulate or dst is self.grads[j]) else None,
+                                   relu_forward_output=mask if (masked and bits is None) else None,
+                                   relu_bitmask=bits if masked else None,
                                    accumulate=(2 if mask is not None else 1) if accumulate else 0)
 
                     self._add_grad(j, ibp)

@@ -314,6 +314,55 @@ def test_accumulating_filter_backprop_against_oracle(orc, dtype, f32_out, shape)
     assert rel_err(to_host(dw), ref) <= 2 * TOL[dtype]
 
 
+def _pack_bits(mask):
+    """numpy bool array -> the library's bitmask bytes (bit i % 8 of byte i / 8)."""
+    return np.packbits(mask.astype(np.uint8), bitorder="little")
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("shape", [(2, 28, 28, 128, 128, 3, 1, True, None), (2, 28, 28, 64, 256, 1, 1, True, None),
+                                   (2, 15, 13, 24, 40, 3, 1, True, None), (2, 28, 28, 256, 512, 1, 2, True, None),
+                                   (128, 14, 14, 512, 512, 3, 1, True, None), (2, 32, 32, 3, 64, 7, 2, None, 3)])
+def test_forward_writes_the_relu_bitmask(orc, dtype, shape):
+    """PdnnConvEpilogue::relu_bitmask: bit i is set exactly where output element i is positive, whichever kernel
+    ran (packed epilogue of the tensor-core kernels, the CTA-pair kernel, or the pass over the output)."""
+    n, h, w, c, k, win, st, same, pad = shape
+    p, po, x, wt, _ = _conv_case(orc, dtype, n, h, w, c, k, win, st, same if same is None else bool(same), pad)
+    rng = np.random.default_rng(5)
+    b = rounded(rng.standard_normal(k).astype(np.float32) * 0.1, dtype)
+    n_out = n * p.out_rows * p.out_cols * k
+    bits = torch.full((n_out // 8,), 0xAA, dtype=torch.uint8, device="cuda")
+    y = pd.conv2d(pd.FORWARD, to_dev(x, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_IM2COL, bias=to_dev(b, dtype),
+                  activation=pd.ACT_RELU, relu_bitmask=bits)
+    assert_no_device_error()
+    assert np.array_equal(bits.cpu().numpy(), _pack_bits(to_host(y) > 0))
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("accumulate", [0, 1, 2])
+@pytest.mark.parametrize("shape", BWD_SHAPES + [(2, 20, 20, 24, 40, 3, 2, True, None), (4, 28, 28, 128, 256, 1, 2, True, None),
+                                                (2, 14, 14, 512, 256, 1, 1, True, None)])
+def test_input_backprop_with_the_relu_bitmask_equals_the_tensor_form(orc, dtype, accumulate, shape):
+    """PdnnBackpropFusion::relu_bitmask gives bit for bit what relu_forward_output gives."""
+    n, h, w, c, k, win, st, same, pad = shape
+    p, po, x, wt, dy = _conv_case(orc, dtype, n, h, w, c, k, win, st, bool(same), pad)
+    if c % 8:
+        pytest.skip("the bitmask needs a multiple of 8 channels")
+    rng = np.random.default_rng(41)
+    y_prev = rounded(np.maximum(rng.standard_normal(n * h * w * c), 0).astype(np.float32), dtype)
+    before = orc.pointwise_grad(0, y_prev, rounded(rng.standard_normal(n * h * w * c).astype(np.float32), dtype))
+    bits = torch.from_numpy(_pack_bits(y_prev > 0)).cuda()
+    results = []
+    for kw in ({"relu_forward_output": to_dev(y_prev, dtype)}, {"relu_bitmask": bits}):
+        dx = to_dev(before, dtype)
+        pd.conv2d(pd.INPUT_BACKPROP, to_dev(dy, dtype), to_dev(wt, dtype), p, algorithm=pd.ALGO_IM2COL, out=dx,
+                  accumulate=accumulate, **kw)
+        assert_no_device_error()
+        results.append(to_host(dx))
+    assert np.array_equal(results[0], results[1])
+    assert not np.any(results[1][y_prev <= 0] != 0)
+
+
 def test_fused_backprop_stem_filter_gradient_fp32(orc):
     n, h, w, c, k, win, st = 2, 32, 32, 3, 64, 7, 2
     p, po, x, _, dy = _conv_case(orc, "f16", n, h, w, c, k, win, st, None, 3)
