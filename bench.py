@@ -229,8 +229,8 @@ def timed(torch, fn, reps, barrier=None):
 
 
 def hbm_operators(torch, pd, workloads, peak_gbs, full=False):
-    """GB/s of the HBM-bound operators on the benchmark networks' shapes: CUDA events over 20 launches
-    after 3 warm-ups, algorithmic bytes (every tensor once; the max-pool gradient reads x, y, dy and writes
+    """GB/s of the HBM-bound operators on the benchmark networks' shapes: CUDA events over three replays
+    of a CUDA graph of 20 launches, after warm-ups, algorithmic bytes (every tensor once; the max-pool gradient reads x, y, dy and writes
     dx; counters of bench/depthwise_conv2d/base_depthwise_convolution_fixture.h:77-79 and
     bench/pooling/base_pooling_fixture.h:72-73) / time.  Tensors are larger than the 126 MB L2 except
     where the name says so."""
@@ -239,7 +239,11 @@ def hbm_operators(torch, pd, workloads, peak_gbs, full=False):
     def add(name, fn, nbytes):
         for _ in range(3):
             fn()
-        ms = timed(torch, fn, 20)
+        # 20 launches replayed as one CUDA graph: a host loop cannot issue the short kernels (5-15 us) as
+        # fast as they run, and its time would be the host's
+        graph = capture_graph(torch, lambda: [fn() for _ in range(20)])
+        graph.replay()
+        ms = timed(torch, graph.replay, 3) / 20
         rows.append({"op": name, "ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 0),
                      "frac": round(nbytes / ms / 1e6 / peak_gbs, 3)})
         return ms

@@ -870,6 +870,10 @@ template <>
 struct WordOf<float> {
   static constexpr int E = 1;
   static __device__ __forceinline__ void unpack(unsigned w, float (&v)[1]) { v[0] = __uint_as_float(w); }
+  // acc += a * b, element by element, on packed words
+  static __device__ __forceinline__ void fma(float (&acc)[1], unsigned a, unsigned b) {
+    acc[0] = fmaf(__uint_as_float(a), __uint_as_float(b), acc[0]);
+  }
 };
 template <>
 struct WordOf<__half> {
@@ -879,6 +883,18 @@ struct WordOf<__half> {
     v[0] = f.x;
     v[1] = f.y;
   }
+  // The mixed-precision multiply-add takes the 16-bit operands as they are (the product of two halves
+  // is exact in fp32, so the result equals convert-then-fmaf): no conversions, and the window stays
+  // packed, one register per word.  Measured against unpacking on arrival (two conversions per word,
+  // fp32 window): 0.113 -> 0.098 ms on 56x56x144; the packed fp32 multiply-add (two lanes per
+  // instruction on an unpacked window) was slower than either.
+  static __device__ __forceinline__ void fma(float (&acc)[2], unsigned a, unsigned b) {
+    asm("{\n\t.reg .b16 al, ah, bl, bh;\n\t"
+        "mov.b32 {al, ah}, %2;\n\tmov.b32 {bl, bh}, %3;\n\t"
+        "fma.rn.f32.f16 %0, al, bl, %0;\n\tfma.rn.f32.f16 %1, ah, bh, %1;\n\t}"
+        : "+f"(acc[0]), "+f"(acc[1])
+        : "r"(a), "r"(b));
+  }
 };
 template <>
 struct WordOf<__nv_bfloat16> {
@@ -887,18 +903,26 @@ struct WordOf<__nv_bfloat16> {
     v[0] = __uint_as_float(w << 16);
     v[1] = __uint_as_float(w & 0xFFFF0000u);
   }
+  static __device__ __forceinline__ void fma(float (&acc)[2], unsigned a, unsigned b) {
+    asm("{\n\t.reg .b16 al, ah, bl, bh;\n\t"
+        "mov.b32 {al, ah}, %2;\n\tmov.b32 {bl, bh}, %3;\n\t"
+        "fma.rn.f32.bf16 %0, al, bl, %0;\n\tfma.rn.f32.bf16 %1, ah, bh, %1;\n\t}"
+        : "+f"(acc[0]), "+f"(acc[1])
+        : "r"(a), "r"(b));
+  }
 };
 
+constexpr int kFbpRowsWarps = 8, kFbpRowsBlocks = 3;  // 80 registers per thread, 24 warps per SM
 template <typename T, int ST>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(kFbpRowsWarps * 32, kFbpRowsBlocks)
     depthwise_filter_backprop_rows_kernel(const T* __restrict__ x, const T* __restrict__ dy, float* __restrict__ partial,
-                                          PdnnDepthwiseConv2DParams p) {
+                                          PdnnDepthwiseConv2DParams p, int segs, int seg_cols) {
   constexpr int E = WordOf<T>::E;
   // U output columns per trip: their ST * U new input columns and U dy words are requested together
   // (a warp has to keep a dozen lines in flight to cover the latency), the CARRY columns the next
   // trip's first window shares with this one stay in registers.
   constexpr int U = ST == 1 ? 4 : 2, CARRY = 3 - ST, NEW = U * ST;
-  __shared__ float red[8][9 * E][32];
+  __shared__ float red[kFbpRowsWarps][9 * E][32];
   const int F = p.channels, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const unsigned wstride = (unsigned)(F / E);  // 32-bit words per pixel
   const unsigned lw = min((unsigned)(blockIdx.y * 32 + lane), wstride - 1u);  // idle lanes repeat the last word
@@ -910,9 +934,14 @@ __global__ void __launch_bounds__(256, 3)
   for (int t = 0; t < 9; ++t)
 #pragma unroll
     for (int e = 0; e < E; ++e) acc[t][e] = 0.f;
-  const unsigned units = (unsigned)(p.batch * p.out_rows);
-  for (unsigned u = blockIdx.x * 8u + (unsigned)warp; u < units; u += gridDim.x * 8u) {
-    const int oh = (int)(u % (unsigned)p.out_rows), n = (int)(u / (unsigned)p.out_rows);
+  // A unit of work is one segment (seg_cols columns, a multiple of U) of one output row: whole rows
+  // are too coarse to spread evenly over a wave of warps (6.05 rows per warp cost as much as 7).
+  const unsigned units = (unsigned)(p.batch * p.out_rows * segs);
+  for (unsigned u = blockIdx.x * (unsigned)kFbpRowsWarps + (unsigned)warp; u < units; u += gridDim.x * (unsigned)kFbpRowsWarps) {
+    const int seg = (int)(u % (unsigned)segs);
+    const unsigned row = u / (unsigned)segs;
+    const int oh = (int)(row % (unsigned)p.out_rows), n = (int)(row / (unsigned)p.out_rows);
+    const int ow_begin = seg * seg_cols, ow_end = min(ow_begin + seg_cols, p.out_cols);
     const int ih0 = oh * ST - p.pad_rows;
     const bool rows_inside = ih0 >= 0 && ih0 + 2 < p.in_rows;
     unsigned xrow[3];  // word index of column 0 of the three input rows (clamped into the image)
@@ -924,60 +953,78 @@ __global__ void __launch_bounds__(256, 3)
       xrow[r] = (unsigned)((n * p.in_rows + min(max(ih, 0), p.in_rows - 1)) * p.in_cols) * wstride + lw;
     }
     const unsigned drow = (unsigned)((n * p.out_rows + oh) * p.out_cols) * wstride + lw;
-    float win[CARRY + NEW][3][E];
-    auto load_col_checked = [&](int iw, float (&col)[3][E]) {
-      const bool cok = iw >= 0 && iw < p.in_cols;
+    // The window stays packed (one register per pixel and row); words from outside the tensors are
+    // requested at a clamped index and replaced by zero.
+    unsigned win[CARRY + NEW][3];
+    auto fetch_col = [&](int iw, unsigned (&col)[3]) {
       const unsigned off = (unsigned)min(max(iw, 0), p.in_cols - 1) * wstride;
 #pragma unroll
-      for (int r = 0; r < 3; ++r) {
-        WordOf<T>::unpack(__ldg(xw + xrow[r] + off), col[r]);
-        if (!(cok && rok[r])) {
+      for (int r = 0; r < 3; ++r) col[r] = __ldg(xw + xrow[r] + off);
+    };
+    auto zero_outside = [&](int iw, unsigned (&col)[3]) {
+      const bool cok = iw >= 0 && iw < p.in_cols;
 #pragma unroll
-          for (int e = 0; e < E; ++e) col[r][e] = 0.f;
-        }
-      }
+      for (int r = 0; r < 3; ++r)
+        if (!(cok && rok[r])) col[r] = 0u;
     };
 #pragma unroll
-    for (int k = 0; k < CARRY; ++k) load_col_checked(k - p.pad_cols, win[k]);
-    for (int ow = 0; ow < p.out_cols; ow += U) {
+    for (int k = 0; k < CARRY; ++k) {
+      fetch_col(ow_begin * ST - p.pad_cols + k, win[k]);
+      zero_outside(ow_begin * ST - p.pad_cols + k, win[k]);
+    }
+    // The words of a trip are requested one trip ahead, so that their latency passes behind the
+    // previous trip's arithmetic (16 requests per lane in flight).
+    unsigned nx[NEW][3], nd[U];
+    auto interior = [&](int ow) {
       const int iw_new = ow * ST - p.pad_cols + CARRY;
-      float dv[U][E];
-      if (rows_inside && iw_new >= 0 && iw_new + NEW <= p.in_cols && ow + U <= p.out_cols) {
-        // interior: no masks, one index addition per load
+      return rows_inside && iw_new >= 0 && iw_new + NEW <= p.in_cols && ow + U <= p.out_cols;
+    };
+    auto fetch = [&](int ow) {
+      const int iw_new = ow * ST - p.pad_cols + CARRY;
+      if (interior(ow)) {  // no clamps, one index addition per load
         unsigned off = (unsigned)iw_new * wstride;
 #pragma unroll
         for (int j = 0; j < NEW; ++j, off += wstride)
 #pragma unroll
-          for (int r = 0; r < 3; ++r) WordOf<T>::unpack(__ldg(xw + xrow[r] + off), win[CARRY + j][r]);
+          for (int r = 0; r < 3; ++r) nx[j][r] = __ldg(xw + xrow[r] + off);
         unsigned doff = drow + (unsigned)ow * wstride;
 #pragma unroll
-        for (int uu = 0; uu < U; ++uu, doff += wstride) WordOf<T>::unpack(__ldg(dw + doff), dv[uu]);
+        for (int uu = 0; uu < U; ++uu, doff += wstride) nd[uu] = __ldg(dw + doff);
       } else {
 #pragma unroll
-        for (int j = 0; j < NEW; ++j) load_col_checked(iw_new + j, win[CARRY + j]);
+        for (int j = 0; j < NEW; ++j) fetch_col(iw_new + j, nx[j]);
 #pragma unroll
-        for (int uu = 0; uu < U; ++uu) {
-          WordOf<T>::unpack(__ldg(dw + drow + (unsigned)min(ow + uu, p.out_cols - 1) * wstride), dv[uu]);
-          if (ow + uu >= p.out_cols) {
-#pragma unroll
-            for (int e = 0; e < E; ++e) dv[uu][e] = 0.f;
-          }
-        }
+        for (int uu = 0; uu < U; ++uu) nd[uu] = __ldg(dw + drow + (unsigned)min(ow + uu, p.out_cols - 1) * wstride);
       }
+    };
+    fetch(ow_begin);
+    for (int ow = ow_begin; ow < ow_end; ow += U) {
+      const int iw_new = ow * ST - p.pad_cols + CARRY;
+      unsigned dv[U];
+#pragma unroll
+      for (int j = 0; j < NEW; ++j)
+#pragma unroll
+        for (int r = 0; r < 3; ++r) win[CARRY + j][r] = nx[j][r];
+#pragma unroll
+      for (int uu = 0; uu < U; ++uu) dv[uu] = nd[uu];
+      if (!interior(ow)) {
+#pragma unroll
+        for (int j = 0; j < NEW; ++j) zero_outside(iw_new + j, win[CARRY + j]);
+#pragma unroll
+        for (int uu = 0; uu < U; ++uu)
+          if (ow + uu >= p.out_cols) dv[uu] = 0u;
+      }
+      if (ow + U < ow_end) fetch(ow + U);
 #pragma unroll
       for (int uu = 0; uu < U; ++uu)
 #pragma unroll
         for (int r = 0; r < 3; ++r)
 #pragma unroll
-          for (int c3 = 0; c3 < 3; ++c3)
-#pragma unroll
-            for (int e = 0; e < E; ++e) acc[r * 3 + c3][e] = fmaf(win[uu * ST + c3][r][e], dv[uu][e], acc[r * 3 + c3][e]);
+          for (int c3 = 0; c3 < 3; ++c3) WordOf<T>::fma(acc[r * 3 + c3], win[uu * ST + c3][r], dv[uu]);
 #pragma unroll
       for (int k = 0; k < CARRY; ++k)
 #pragma unroll
-        for (int r = 0; r < 3; ++r)
-#pragma unroll
-          for (int e = 0; e < E; ++e) win[k][r][e] = win[NEW + k][r][e];
+        for (int r = 0; r < 3; ++r) win[k][r] = win[NEW + k][r];
     }
   }
 #pragma unroll
@@ -985,13 +1032,13 @@ __global__ void __launch_bounds__(256, 3)
 #pragma unroll
     for (int e = 0; e < E; ++e) red[warp][t * E + e][lane] = acc[t][e];
   __syncthreads();
-  for (int i = threadIdx.x; i < 9 * E * 32; i += 256) {
+  for (int i = threadIdx.x; i < 9 * E * 32; i += kFbpRowsWarps * 32) {
     const int l = i & 31, te = i >> 5, t = te / E, e = te % E;
     const int ch = (blockIdx.y * 32 + l) * E + e;
     if (ch < F) {
       float sum = 0.f;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) sum += red[w][te][l];
+      for (int w = 0; w < kFbpRowsWarps; ++w) sum += red[w][te][l];
       partial[((size_t)blockIdx.x * 9 + t) * F + ch] = sum;
     }
   }
@@ -1111,6 +1158,14 @@ struct Packet<__half> {
     o.v[3] = *reinterpret_cast<const __half2*>(&r.w);
     return o;
   }
+  static __device__ __forceinline__ Packet from_raw(const uint4& r) {
+    Packet o;
+    o.v[0] = *reinterpret_cast<const __half2*>(&r.x);
+    o.v[1] = *reinterpret_cast<const __half2*>(&r.y);
+    o.v[2] = *reinterpret_cast<const __half2*>(&r.z);
+    o.v[3] = *reinterpret_cast<const __half2*>(&r.w);
+    return o;
+  }
   static __device__ __forceinline__ Packet splat(float f) {
     Packet o;
 #pragma unroll
@@ -1221,6 +1276,14 @@ struct Packet<float> {
     o.v[1] = r.y;
     o.v[2] = r.z;
     o.v[3] = r.w;
+    return o;
+  }
+  static __device__ __forceinline__ Packet from_raw(const uint4& r) {
+    Packet o;
+    o.v[0] = __uint_as_float(r.x);
+    o.v[1] = __uint_as_float(r.y);
+    o.v[2] = __uint_as_float(r.z);
+    o.v[3] = __uint_as_float(r.w);
     return o;
   }
   static __device__ __forceinline__ Packet splat(float f) {
@@ -1392,6 +1455,159 @@ __global__ void __launch_bounds__(kStripBlock)
   }
 }
 
+// Depthwise 3x3 as the strip walk above (MODE 0), with the rows a thread will need PF steps from now
+// already on their way: every step's new rows are requested by cp.async into shared-memory slots
+// of the thread's own (PF + 1 groups of ST rows; nobody else reads them, so no barrier), and only
+// cp.async.wait_group stands between the request and the copy into registers.  The strip kernel
+// keeps its requests in registers, which limits a thread to one row in flight and an SM to about
+// 36 KB; the copies here cost no registers while they fly.  (The nine filter packets stay in
+// registers: fetched from shared memory tap by tap the kernel was a quarter slower at stride 1.)
+// Measured on MobileNet-v2 at batch 128 (fp16, graph replay): 112x112x32 0.064 -> 0.043 ms, 112x112x96/2
+// 0.074 -> 0.067 ms, 56x56x144 0.068 -> 0.046 ms, the 17 layers 0.46 -> 0.36 ms.
+template <typename T, int ST, int PF>
+__global__ void __launch_bounds__(kStripBlock, 3)
+    depthwise3_async_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, StripGeometry g,
+                            size_t n_threads) {
+  using P = Packet<T>;
+  constexpr int V = 16 / sizeof(T);
+  constexpr int kStripW = StripWidth<ST>::value;
+  constexpr int NIN = (kStripW - 1) * ST + 3;
+  constexpr int GROUP = ST * NIN;  // packets one step brings in
+  constexpr int SLOTS = PF + 1;
+  constexpr uint32_t kPacketPitch = kStripBlock * 16;  // bytes between two packets of one thread
+  extern __shared__ uint4 dw_async_smem[];
+  const size_t idx = (size_t)blockIdx.x * kStripBlock + threadIdx.x;
+  if (idx >= n_threads) return;
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dw_async_smem) + threadIdx.x * 16u;
+  const int cvecs = g.channels / V;
+  const int cv = (int)(idx % cvecs);
+  size_t t = idx / cvecs;
+  const int wg = (int)(t % g.wgroups);
+  t /= g.wgroups;
+  const int hc = (int)(t % g.hchunks);
+  const int n = (int)(t / g.hchunks);
+  const int c = cv * V;
+  const int ow0 = wg * kStripW, iw0 = ow0 * ST - g.pad_cols;
+  const int oh_begin = hc * g.rows_per_thread, oh_end = min(oh_begin + g.rows_per_thread, g.out_rows);
+  const int nsteps = oh_end - oh_begin;
+  const T* xn = x + (size_t)n * g.in_rows * g.in_cols * g.channels + c;
+  T* yn = y + (size_t)n * g.out_rows * g.out_cols * g.channels + c;
+  const int ih_first = oh_begin * ST - g.pad_rows;
+
+  auto lds = [](uint32_t addr) {
+    uint4 r;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+    return P::from_raw(r);
+  };
+  P wt[3][3];
+#pragma unroll
+  for (int r = 0; r < 3; ++r)
+#pragma unroll
+    for (int s2 = 0; s2 < 3; ++s2)
+      wt[r][s2] = P::load(w + (size_t)(g.flip ? (2 - r) * 3 + (2 - s2) : r * 3 + s2) * g.channels + c);
+  // requests the rows step k (>= 1) adds to the window; always one commit, so that the groups count steps
+  auto request = [&](int k) {
+    if (k < nsteps) {
+      const uint32_t slot = ring + (uint32_t)((k % SLOTS) * GROUP) * kPacketPitch;
+#pragma unroll
+      for (int i = 0; i < ST; ++i) {
+        const int ih = ih_first + 3 + (k - 1) * ST + i;
+        const bool row_ok = ih >= 0 && ih < g.in_rows;
+        const T* xr = xn + (size_t)(row_ok ? ih : 0) * g.in_cols * g.channels;
+#pragma unroll
+        for (int j = 0; j < NIN; ++j) {
+          const int iw = iw0 + j;
+          const bool ok = row_ok && iw >= 0 && iw < g.in_cols;
+          // outside the image: zero bytes are read and the packet is filled with zeros
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(slot + (uint32_t)(i * NIN + j) * kPacketPitch),
+                       "l"(ok ? xr + (size_t)iw * g.channels : xn), "r"(ok ? 16 : 0)
+                       : "memory");
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  auto load_row = [&](P (&row)[NIN], int ih) {
+    const bool row_ok = ih >= 0 && ih < g.in_rows;
+    const T* xr = xn + (size_t)ih * g.in_cols * g.channels;
+#pragma unroll
+    for (int j = 0; j < NIN; ++j) {
+      const int iw = iw0 + j;
+      row[j] = (row_ok && iw >= 0 && iw < g.in_cols) ? P::load(xr + (size_t)iw * g.channels) : P::splat(0.f);
+    }
+  };
+  P ra[NIN], rb[NIN], rc[NIN];
+  load_row(ra, ih_first);
+  load_row(rb, ih_first + 1);
+  load_row(rc, ih_first + 2);
+#pragma unroll
+  for (int k = 1; k <= PF; ++k) request(k);
+  // One step: the window is rows r0, r1, r2; afterwards the rows the next step adds replace the ones
+  // it no longer needs, in place (the callers rotate the roles instead of moving 18 packets).
+  auto step = [&](int k, P (&r0)[NIN], P (&r1)[NIN], P (&r2)[NIN]) {
+    const int oh = oh_begin + k;
+    P acc[kStripW];
+#pragma unroll
+    for (int o = 0; o < kStripW; ++o) acc[o] = P::splat(0.f);
+#pragma unroll
+    for (int s2 = 0; s2 < 3; ++s2) {
+#pragma unroll
+      for (int o = 0; o < kStripW; ++o) {
+        acc[o].fma(r0[o * ST + s2], wt[0][s2]);
+        acc[o].fma(r1[o * ST + s2], wt[1][s2]);
+        acc[o].fma(r2[o * ST + s2], wt[2][s2]);
+      }
+    }
+#pragma unroll
+    for (int o = 0; o < kStripW; ++o)
+      if (ow0 + o < g.out_cols) acc[o].store(yn + ((size_t)oh * g.out_cols + ow0 + o) * g.channels);
+    // The slot of step k (copied to registers one step ago and consumed just now) takes step
+    // k + PF + 1; then everything but the newest PF groups has landed, step k + 1 among it.
+    request(k + PF + 1);
+    asm volatile("cp.async.wait_group %0;" ::"n"(PF) : "memory");
+    if (k + 1 < nsteps) {
+      const uint32_t slot = ring + (uint32_t)(((k + 1) % SLOTS) * GROUP) * kPacketPitch;
+#pragma unroll
+      for (int j = 0; j < NIN; ++j) {
+        r0[j] = lds(slot + (uint32_t)j * kPacketPitch);                           // stride 1: the next window is r1, r2, r0
+        if constexpr (ST == 2) r1[j] = lds(slot + (uint32_t)(NIN + j) * kPacketPitch);  // stride 2: r2, r0, r1
+      }
+    }
+  };
+#pragma unroll 1
+  for (int k = 0; k < nsteps; k += 3) {
+    step(k, ra, rb, rc);
+    if constexpr (ST == 1) {
+      if (k + 1 < nsteps) step(k + 1, rb, rc, ra);
+      if (k + 2 < nsteps) step(k + 2, rc, ra, rb);
+    } else {
+      if (k + 1 < nsteps) step(k + 1, rc, ra, rb);
+      if (k + 2 < nsteps) step(k + 2, rb, rc, ra);
+    }
+  }
+}
+
+template <typename T, int ST, int PF>
+bool launch_depthwise3_async(const T* x, const T* w, T* y, const StripGeometry& g, size_t n_threads, unsigned blocks,
+                             cudaStream_t s) {
+  constexpr int NIN = (StripWidth<ST>::value - 1) * ST + 3;
+  constexpr size_t kSmem = (size_t)((PF + 1) * ST * NIN) * kStripBlock * 16;
+  auto kernel = depthwise3_async_kernel<T, ST, PF>;
+  static bool attr_set[kMaxDevices] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDevices) return false;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    attr_set[dev] = true;
+  }
+  kernel<<<blocks, kStripBlock, kSmem, s>>>(x, w, y, g, n_threads);
+  return true;
+}
+
 // Chooses how many output rows a thread walks: as many as possible while the launch still has
 // enough threads to fill the device.
 template <typename T, int MODE>
@@ -1400,14 +1616,27 @@ int launch_window3_strip(const T* x, const T* w, T* y, int stride, StripGeometry
   const int strip_w = stride == 1 ? StripWidth<1>::value : StripWidth<2>::value;
   g.wgroups = (g.out_cols + strip_w - 1) / strip_w;
   const size_t per_row_chunk = (size_t)g.batch * g.wgroups * (g.channels / V);
-  const size_t want = (size_t)sms * 1024;
   int rows = 16;
-  while (rows > 1 && per_row_chunk * ((g.out_rows + rows - 1) / rows) < want) rows >>= 1;
+  if constexpr (MODE == 0) {
+    // the prefetching kernel: two waves of its 384 threads per SM, walks of at most 16 rows
+    const size_t want = (size_t)sms * 768;
+    const int chunks = (int)std::min<size_t>((want + per_row_chunk - 1) / per_row_chunk, (size_t)g.out_rows);
+    rows = std::min(16, (g.out_rows + chunks - 1) / chunks);
+  } else {
+    const size_t want = (size_t)sms * 1024;
+    while (rows > 1 && per_row_chunk * ((g.out_rows + rows - 1) / rows) < want) rows >>= 1;
+  }
   g.rows_per_thread = rows;
   g.hchunks = (g.out_rows + rows - 1) / rows;
   const size_t n_threads = per_row_chunk * g.hchunks;
   const size_t blocks = (n_threads + kStripBlock - 1) / kStripBlock;
   if (blocks > 0x7FFFFFFFull) return -1;
+  if constexpr (MODE == 0) {
+    // (falls through to the strip kernel if the shared-memory attribute cannot be set)
+    if (stride == 1 ? launch_depthwise3_async<T, 1, 2>(x, w, y, g, n_threads, (unsigned)blocks, s)
+                    : launch_depthwise3_async<T, 2, 1>(x, w, y, g, n_threads, (unsigned)blocks, s))
+      return 0;
+  }
   if (stride == 1)
     window3_strip_kernel<T, 1, MODE><<<(unsigned)blocks, kStripBlock, 0, s>>>(x, w, y, g, n_threads);
   else
@@ -1676,17 +1905,23 @@ int launch_fbp_partials(bool vec, const T* in, const T* dy, float* partial, cons
     const int sms = device_sm_count();
     int per_sm = 0;
     const cudaError_t oe = p.stride_rows == 1
-        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, depthwise_filter_backprop_rows_kernel<T, 1>, 256, 0)
-        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, depthwise_filter_backprop_rows_kernel<T, 2>, 256, 0);
+        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, depthwise_filter_backprop_rows_kernel<T, 1>, kFbpRowsWarps * 32, 0)
+        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, depthwise_filter_backprop_rows_kernel<T, 2>, kFbpRowsWarps * 32, 0);
     if (oe != cudaSuccess || per_sm < 1) {
       cudaGetLastError();
       per_sm = 2;
     }
     const long long wave = std::max(1, per_sm * sms / groups);
-    const unsigned gx = (unsigned)std::min<long long>(std::min<long long>(slices, wave), (units + 7) / 8);
+    const unsigned gx = (unsigned)std::min<long long>(std::min<long long>(slices, wave), (units + kFbpRowsWarps - 1) / kFbpRowsWarps);
     dim3 grid(gx, groups);
-    if (p.stride_rows == 1) depthwise_filter_backprop_rows_kernel<T, 1><<<grid, 256, 0, s>>>(in, dy, partial, p);
-    else depthwise_filter_backprop_rows_kernel<T, 2><<<grid, 256, 0, s>>>(in, dy, partial, p);
+    // rows are cut into up to four segments until a warp has a dozen units to walk
+    const int trip = p.stride_rows == 1 ? 4 : 2;  // the kernel's U
+    int segs = 1;
+    while (segs < 4 && units * segs < (long long)gx * kFbpRowsWarps * 12 && (p.out_cols + 2 * segs - 1) / (2 * segs) >= 2 * trip) segs *= 2;
+    const int seg_cols = ((p.out_cols + segs - 1) / segs + trip - 1) / trip * trip;
+    segs = (p.out_cols + seg_cols - 1) / seg_cols;
+    if (p.stride_rows == 1) depthwise_filter_backprop_rows_kernel<T, 1><<<grid, kFbpRowsWarps * 32, 0, s>>>(in, dy, partial, p, segs, seg_cols);
+    else depthwise_filter_backprop_rows_kernel<T, 2><<<grid, kFbpRowsWarps * 32, 0, s>>>(in, dy, partial, p, segs, seg_cols);
     return (int)gx;
   }
   if (fbp_all_taps(p, V)) {
