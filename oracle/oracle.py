@@ -69,7 +69,7 @@ def padding(inp, window, stride, same):
 
 
 def conv_params(batch, in_rows, in_cols, channels, features, window, stride, same=True, pad=None,
-                window_cols=None, stride_cols=None, groups=1):
+                window_cols=None, stride_cols=None, groups=1, group_format=0):
     """Build params the way the reference's tests do (helpers::add_padding_to,
     include/portdnn/helpers/padding.h:76-88); ``pad`` overrides with an explicit low-side pad
     and out = (in + 2*pad - window)/stride + 1 like the compat API
@@ -84,7 +84,7 @@ def conv_params(batch, in_rows, in_cols, channels, features, window, stride, sam
         orow = (in_rows + 2 * pad - window) // stride + 1
         ocol = (in_cols + 2 * pad - wc) // sc + 1
     return ConvParams(channels, features, batch, in_rows, in_cols, window, wc, stride, sc, orow, ocol,
-                      prow, pcol, 1, 1, groups, 0, 0, 0)
+                      prow, pcol, 1, 1, groups, 0, 0, group_format)
 
 
 def depthwise_params(batch, in_rows, in_cols, channels, mult, window, stride, same=True):

@@ -67,10 +67,17 @@ enum { ORC_RELU = 0, ORC_TANH = 1, ORC_EXP = 3, ORC_LOG = 4, ORC_FLOOR = 5, ORC_
  * (cross-correlation, implicit high-side padding).  Groups follow the im2col
  * driver's convention (include/portdnn/internal/conv2d/im2col.h:90-137): group g
  * reads channels [g*C/G,(g+1)*C/G) and writes features [g*K/G,(g+1)*K/G); the
- * filter is [R][S][C/G][K]. Accumulates in double. */
+ * filter is [R][S][C/G][K].  With group_format INTERLEAVED the group is the fastest
+ * index of the channel and feature axes instead (channel c of group g is element
+ * c*G+g of a pixel, feature k of group g is element k*G+g of the filter's last axis
+ * and of an output pixel), as test/conv2d/group_convolution_fixture.h:41-77 lays the
+ * tensors out and include/portdnn/batch_format.h:33-47 defines it.  Accumulates in double. */
 static void conv_forward(const float* x, const float* w, float* y, const OrcConvParams* p) {
   const int C = p->channels, K = p->features, G = p->groups > 0 ? p->groups : 1;
   const int Cg = C / G, Kg = K / G;
+  /* element strides of (group, index within the group) on the channel and feature axes */
+  const int il = p->group_format == 1;
+  const int cgs = il ? 1 : Cg, ccs = il ? G : 1, kgs = il ? 1 : Kg, kks = il ? G : 1;
   const long rows_total = (long)p->batch * p->out_rows;
 #pragma omp parallel
   {
@@ -90,10 +97,10 @@ static void conv_forward(const float* x, const float* w, float* y, const OrcConv
             const float* wp = w + ((size_t)r * p->window_cols + s) * Cg * K;
             for (int g = 0; g < G; ++g) {
               for (int c = 0; c < Cg; ++c) {
-                const double xv = xp[g * Cg + c];
-                const float* wk = wp + (size_t)c * K + g * Kg;
-                double* ak = acc + g * Kg;
-                for (int k = 0; k < Kg; ++k) ak[k] += xv * (double)wk[k];
+                const double xv = xp[g * cgs + c * ccs];
+                const float* wk = wp + (size_t)c * K + g * kgs;
+                double* ak = acc + g * kgs;
+                for (int k = 0; k < Kg; ++k) ak[k * kks] += xv * (double)wk[k * kks];
               }
             }
           }
@@ -192,6 +199,7 @@ int orc_conv2d(int pass, const float* in, const float* fil, float* out, const Or
   const int G = p->groups > 0 ? p->groups : 1;
   if (G != 1 && pass != ORC_FORWARD) return -1;
   if (p->channels % G || p->features % G) return -1;
+  if (p->group_format != 0 && (p->group_format != 1 || G == 1)) return -1;
   switch (pass) {
     case ORC_FORWARD: conv_forward(in, fil, out, p); return 0;
     case ORC_INPUT_BACKPROP: conv_input_backprop(in, fil, out, p); return 0;

@@ -117,7 +117,7 @@ def calculate_padding(inp, window, stride, same):
 
 
 def conv_params(batch, in_rows, in_cols, channels, features, window, stride, same=True, pad=None, groups=1,
-                filter_format=0):
+                filter_format=0, group_format=0):
     """Params as helpers::add_padding_to builds them (include/portdnn/helpers/padding.h:76-88); an explicit
     ``pad`` gives the compat API's symmetric form (include/portdnn/compat/convolution.hpp:411-415)."""
     if pad is None:
@@ -128,7 +128,7 @@ def conv_params(batch, in_rows, in_cols, channels, features, window, stride, sam
         orow = (in_rows + 2 * pad - window) // stride + 1
         ocol = (in_cols + 2 * pad - window) // stride + 1
     return Conv2DParams(channels, features, batch, in_rows, in_cols, window, window, stride, stride, orow, ocol,
-                        prow, pcol, 1, 1, groups, 0, filter_format, 0)
+                        prow, pcol, 1, 1, groups, 0, filter_format, group_format)
 
 
 def depthwise_params(batch, in_rows, in_cols, channels, mult, window, stride, same=True):

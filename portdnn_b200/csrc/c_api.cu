@@ -218,6 +218,9 @@ int dispatch_conv(int pass, int dtype, const void* in, const void* fil, void* ou
       winograd_applicable(pass, dtype, *p) && ws != nullptr && ws_elems >= winograd_workspace_elems(pass, dtype, *p) &&
       aligned16(ws) && aligned16(in) && aligned16(fil) && aligned16(out))
     return launch_winograd(pass, dtype, in, fil, out, *p, epi, ws, ws_elems, s);
+  if (pass == PDNN_FORWARD && p->groups > 1 && tc_grouped_conv_supported(dtype, in, fil, out, *p) &&
+      (epi == nullptr || epi->relu_bitmask == nullptr))
+    return tc_grouped_conv_forward(dtype, in, fil, out, *p, epi, s);
   if (algorithm != PDNN_ALGO_DIRECT && tc_conv_supported(pass, dtype, in, fil, out, *p)) {
     const int st2 = tc_conv2d(pass, dtype, in, fil, out, *p, epi, fusion, ws, ws_elems, s);
     if (st2 != kNeedsDirect) return st2;

@@ -38,7 +38,11 @@ __global__ void __launch_bounds__(kBlock)
     t /= p.out_cols;
     const int oh = (int)(t % p.out_rows);
     const int n = (int)(t / p.out_rows);
-    const int g = k / Kg;
+    // STRIDED groups: a group's channels and features are contiguous; INTERLEAVED: the group is the
+    // fastest index of both axes (include/portdnn/batch_format.h:33-47)
+    const bool interleaved = p.group_format == 1;
+    const int g = interleaved ? k % G : k / Kg;
+    const int c_first = interleaved ? g : g * Cg, c_step = interleaved ? G : 1;
     float acc = 0.f;
     for (int r = 0; r < p.window_rows; ++r) {
       const int ih = oh * p.stride_rows - p.pad_rows + r;
@@ -46,8 +50,8 @@ __global__ void __launch_bounds__(kBlock)
       for (int s = 0; s < p.window_cols; ++s) {
         const int iw = ow * p.stride_cols - p.pad_cols + s;
         if (iw < 0 || iw >= p.in_cols) continue;
-        const T* xp = x + (((size_t)n * p.in_rows + ih) * p.in_cols + iw) * p.channels + (size_t)g * Cg;
-        for (int c = 0; c < Cg; ++c) acc = fmaf(to_f32(__ldg(xp + c)), to_f32(__ldg(w + fi(r, s, c, k))), acc);
+        const T* xp = x + (((size_t)n * p.in_rows + ih) * p.in_cols + iw) * p.channels + c_first;
+        for (int c = 0; c < Cg; ++c) acc = fmaf(to_f32(__ldg(xp + c * c_step)), to_f32(__ldg(w + fi(r, s, c, k))), acc);
       }
     }
     float v = e.alpha * acc;

@@ -1858,18 +1858,25 @@ bool conv_common_ok(int dtype, const PdnnConv2DParams& p) {
 
 // One tensor map per input parity of x ([C, W', H', N] view of the pixels with h % sr == ph,
 // w % sc == pw).  Returns false if a parity class is empty.
+// Leading dimensions, in elements, of tensors that are channel slices of wider ones (one group of a
+// grouped convolution): between two pixels of x, two rows of the HWCF filter matrix, two pixels of y.
+// Zero stands for the dense value (channels, features, features).
+struct ConvLd {
+  int x, w, y;
+};
+
 bool make_parity_maps(GemmArgs& g, int dtype, bool mn_major, const void* x, const PdnnConv2DParams& p,
-                      const uint32_t box[4]) {
+                      const uint32_t box[4], int x_ld = 0) {
   const size_t es = dtype_size(dtype);
+  const uint64_t ld = x_ld > 0 ? (uint64_t)x_ld : (uint64_t)p.channels;
   for (int ph = 0; ph < p.stride_rows; ++ph)
     for (int pw = 0; pw < p.stride_cols; ++pw) {
       const int Hq = ceil_div(p.in_rows - ph, p.stride_rows), Wq = ceil_div(p.in_cols - pw, p.stride_cols);
       if (Hq <= 0 || Wq <= 0) return false;
       const uint64_t dims[4] = {(uint64_t)p.channels, (uint64_t)Wq, (uint64_t)Hq, (uint64_t)p.batch};
-      const uint64_t st[3] = {(uint64_t)p.stride_cols * p.channels * es,
-                              (uint64_t)p.stride_rows * p.in_cols * p.channels * es,
-                              (uint64_t)p.in_rows * p.in_cols * p.channels * es};
-      const char* base = static_cast<const char*>(x) + ((size_t)ph * p.in_cols + pw) * p.channels * es;
+      const uint64_t st[3] = {(uint64_t)p.stride_cols * ld * es, (uint64_t)p.stride_rows * p.in_cols * ld * es,
+                              (uint64_t)p.in_rows * p.in_cols * ld * es};
+      const char* base = static_cast<const char*>(x) + ((size_t)ph * p.in_cols + pw) * ld * es;
       if (!make_map(&g.a_map[ph * p.stride_cols + pw], dtype, mn_major, base, dims, st, box)) return false;
     }
   for (int i = p.stride_rows * p.stride_cols; i < 4; ++i) g.a_map[i] = g.a_map[0];
@@ -1878,8 +1885,9 @@ bool make_parity_maps(GemmArgs& g, int dtype, bool mn_major, const void* x, cons
 
 // Output side of a forward convolution: y is [N, Ho, Wo, K].
 int finish_forward(GemmArgs& g, int dtype, void* y, const PdnnConv2DParams& p, const PdnnConvEpilogue* epi,
-                   cudaStream_t s) {
+                   cudaStream_t s, int y_ld = 0) {
   const size_t es = dtype_size(dtype);
+  const long long ld = y_ld > 0 ? y_ld : p.features;
   set_epilogue(g, epi);
   g.out = y;
   g.out_dtype = dtype;
@@ -1887,13 +1895,12 @@ int finish_forward(GemmArgs& g, int dtype, void* y, const PdnnConv2DParams& p, c
   g.ext_h = p.out_rows;
   g.ext_n = p.batch;
   g.ext_cols = p.features;
-  g.stride_w = p.features;
-  g.stride_h = (long long)p.out_cols * p.features;
-  g.stride_n = (long long)p.out_rows * p.out_cols * p.features;
+  g.stride_w = ld;
+  g.stride_h = (long long)p.out_cols * ld;
+  g.stride_n = (long long)p.out_rows * p.out_cols * ld;
   g.vec_ok = 1;
   const uint64_t od[4] = {(uint64_t)p.features, (uint64_t)p.out_cols, (uint64_t)p.out_rows, (uint64_t)p.batch};
-  const uint64_t os[3] = {(uint64_t)p.features * es, (uint64_t)p.out_cols * p.features * es,
-                          (uint64_t)p.out_rows * p.out_cols * p.features * es};
+  const uint64_t os[3] = {(uint64_t)ld * es, (uint64_t)p.out_cols * ld * es, (uint64_t)p.out_rows * p.out_cols * ld * es};
   if (!setup_store(g, dtype, od, os)) return (g.halo || g.pair) ? kPlanAgain : PDNN_INVALID_PARAMETER;
   return launch_gemm(g, dtype, s);
 }
@@ -2127,7 +2134,10 @@ __global__ void __launch_bounds__(256) split_lo_kernel(const float* __restrict__
 }
 
 int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnConv2DParams& p,
-                 const PdnnConvEpilogue* epi, cudaStream_t s, bool try_halo = true, bool try_cta_pair = true) {
+                 const PdnnConvEpilogue* epi, cudaStream_t s, bool try_halo = true, bool try_cta_pair = true,
+                 const ConvLd* ld = nullptr) {
+  const int x_ld = ld != nullptr ? ld->x : 0, y_ld = ld != nullptr ? ld->y : 0;
+  const uint64_t w_ld = ld != nullptr && ld->w > 0 ? (uint64_t)ld->w : (uint64_t)p.features;
   GemmArgs g;
   std::memset(&g, 0, sizeof(g));
   const size_t es = dtype_size(dtype);
@@ -2208,7 +2218,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     g.idesc = make_idesc(dtype == PDNN_BF16 ? 1 : 0, 0, 1, 256, 256);
   const uint32_t abox[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)(halo ? g.th + p.window_rows - 1 : g.th),
                             (uint32_t)g.tn};
-  if (!make_parity_maps(g, dtype, false, x, p, abox)) return PDNN_INVALID_PARAMETER;
+  if (!make_parity_maps(g, dtype, false, x, p, abox, x_ld)) return PDNN_INVALID_PARAMETER;
   // taps
   int nt = 0;
   if (halo) {
@@ -2240,7 +2250,8 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
   // the hi part); the kernel's split warps then only have the A tiles to split.
   const size_t filter_elems = (size_t)taps * p.channels * p.features;
   float* w_split = nullptr;
-  if (dtype == PDNN_F32 && (size_t)p.batch * p.out_rows * p.out_cols >= 2048 && aligned16(w)) {
+  if (dtype == PDNN_F32 && (size_t)p.batch * p.out_rows * p.out_cols >= 2048 && aligned16(w) &&
+      (!hwcf || w_ld == (uint64_t)p.features)) {  // (a column slice of a wider filter is not one contiguous run)
     if (cudaMallocAsync(reinterpret_cast<void**>(&w_split), filter_elems * sizeof(float), s) == cudaSuccess) {
       split_lo_kernel<<<grid_for(filter_elems, 256, sms), 256, 0, s>>>(static_cast<const float*>(w), w_split, filter_elems);
       count_launch();
@@ -2257,7 +2268,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
       // one after another in shared memory.
       g.b_mode = B_MN_3X;
       const uint64_t dims[4] = {(uint64_t)epr, (uint64_t)p.channels, (uint64_t)(p.features / epr), taps};
-      const uint64_t st[3] = {(uint64_t)p.features * es, 128, (uint64_t)p.channels * p.features * es};
+      const uint64_t st[3] = {w_ld * es, 128, (uint64_t)p.channels * w_ld * es};
       // (a CTA pair: each CTA copies its own half of the tile's columns)
       const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, (uint32_t)((g.cta_pair ? g.bn / 2 : g.bn) / epr), 1};
       return make_map(map, dtype, true, base, dims, st, box);
@@ -2265,8 +2276,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     if (hwcf) {
       g.b_mode = B_MN_3;
       const uint64_t dims[4] = {(uint64_t)p.features, (uint64_t)p.channels, taps, 1};
-      const uint64_t st[3] = {(uint64_t)p.features * es, (uint64_t)p.channels * p.features * es,
-                              taps * p.channels * p.features * es};
+      const uint64_t st[3] = {w_ld * es, (uint64_t)p.channels * w_ld * es, taps * p.channels * w_ld * es};
       const uint32_t box[4] = {(uint32_t)epr, (uint32_t)epr, 1, 1};
       return make_map(map, dtype, true, base, dims, st, box);
     }
@@ -2281,10 +2291,11 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     if (w_split != nullptr) cudaFreeAsync(w_split, s);
     return PDNN_INVALID_PARAMETER;
   }
-  const int status = finish_forward(g, dtype, y, p, epi, s);
+  const int status = finish_forward(g, dtype, y, p, epi, s, y_ld);
   if (w_split != nullptr) cudaFreeAsync(w_split, s);
   if (status == kPlanAgain)  // first without the CTA pairs, then without halo / pair mode
-    return g.cta_pair ? conv_forward(dtype, x, w, y, p, epi, s, try_halo, false) : conv_forward(dtype, x, w, y, p, epi, s, false, false);
+    return g.cta_pair ? conv_forward(dtype, x, w, y, p, epi, s, try_halo, false, ld)
+                      : conv_forward(dtype, x, w, y, p, epi, s, false, false, ld);
   return status;
 }
 
@@ -2874,6 +2885,50 @@ bool tc_conv_supported(int pass, int dtype, const void* in, const void* fil, con
       if (p.in_rows - ph <= 0 || p.in_cols - pw <= 0) return false;
   if (pass == PDNN_FILTER_BACKPROP && p.filter_format != 0) return false;
   return true;
+}
+
+// Grouped forward convolution (STRIDED groups: group g reads channels [g*C/G, (g+1)*C/G) and writes
+// features [g*K/G, (g+1)*K/G), include/portdnn/internal/conv2d/im2col.h:90-137) as one implicit GEMM
+// per group on channel slices of the tensors: the tensor maps take the slices' leading dimensions,
+// nothing is copied or transposed.
+bool tc_grouped_conv_supported(int dtype, const void* in, const void* fil, const void* out, const PdnnConv2DParams& p) {
+  if (encode_fn() == nullptr || p.groups <= 1 || p.group_format != 0) return false;
+  if (p.channels % p.groups || p.features % p.groups) return false;
+  PdnnConv2DParams q = p;
+  q.channels = p.channels / p.groups;
+  q.features = p.features / p.groups;
+  q.groups = 1;
+  if (!conv_common_ok(dtype, q) || small_c_applicable(dtype, q)) return false;
+  if (!aligned16(in) || !aligned16(fil) || !aligned16(out)) return false;
+  for (int ph = 0; ph < p.stride_rows; ++ph)
+    for (int pw = 0; pw < p.stride_cols; ++pw)
+      if (p.in_rows - ph <= 0 || p.in_cols - pw <= 0) return false;
+  return true;
+}
+
+int tc_grouped_conv_forward(int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
+                            const PdnnConvEpilogue* epi, cudaStream_t s) {
+  const size_t es = dtype_size(dtype);
+  PdnnConv2DParams q = p;
+  q.channels = p.channels / p.groups;
+  q.features = p.features / p.groups;
+  q.groups = 1;
+  const bool hwcf = p.filter_format == 0;
+  const ConvLd ld{p.channels, hwcf ? p.features : 0, p.features};
+  const size_t fhwc_group = (size_t)q.features * p.window_rows * p.window_cols * q.channels;
+  for (int g = 0; g < p.groups; ++g) {
+    PdnnConvEpilogue e;
+    if (epi != nullptr) {
+      e = *epi;
+      if (e.bias != nullptr) e.bias = static_cast<const char*>(e.bias) + (size_t)g * q.features * es;
+    }
+    const char* xg = static_cast<const char*>(in) + (size_t)g * q.channels * es;
+    const char* wg = static_cast<const char*>(fil) + (hwcf ? (size_t)g * q.features : (size_t)g * fhwc_group) * es;
+    char* yg = static_cast<char*>(out) + (size_t)g * q.features * es;
+    const int st = conv_forward(dtype, xg, wg, yg, q, epi != nullptr ? &e : nullptr, s, true, true, &ld);
+    if (st != PDNN_OK) return st;
+  }
+  return PDNN_OK;
 }
 
 size_t tc_conv_workspace_elems(int pass, int dtype, const PdnnConv2DParams& p) {

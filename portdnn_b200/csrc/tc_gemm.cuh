@@ -20,6 +20,12 @@ constexpr int kNeedsDirect = -1;
 int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
               const PdnnConvEpilogue* epi, const PdnnBackpropFusion* fusion, void* ws, size_t ws_elems, cudaStream_t s);
 
+// Grouped forward convolution with STRIDED groups whose per-group channel and feature counts meet
+// tc_conv_supported's alignment rules: one implicit GEMM per group on channel slices of the tensors.
+bool tc_grouped_conv_supported(int dtype, const void* in, const void* fil, const void* out, const PdnnConv2DParams& p);
+int tc_grouped_conv_forward(int dtype, const void* in, const void* fil, void* out, const PdnnConv2DParams& p,
+                            const PdnnConvEpilogue* epi, cudaStream_t s);
+
 bool tc_matmul_supported(int dtype, int tl, int tr, const void* lhs, const void* rhs, const void* out, int batches,
                          int m, int k, int n);
 // out_f32: the product is written as fp32 whatever dtype is (beta then scales fp32 values).

@@ -1,10 +1,12 @@
 """Extract the reference's known-answer vectors of grouped forward convolution
 (test/conv2d/forward_window*_stride*_groups*.cc) into tests/golden/grouped_conv2d_kat.npz.
 
-Only the STRIDED group format is kept (channels and features of a group are contiguous): the
-INTERLEAVED cases are skipped by the reference itself on backends without an interleaved matmul
-(test/conv2d/group_convolution_fixture.h:161-166), which is what this implementation is.
-Case table columns: window, stride, groups, N, H, W, C, features, same, fhwc, max_val, offset, length.
+Both group formats are kept: STRIDED (channels and features of a group are contiguous) and INTERLEAVED
+(the group is the fastest index of both axes; HWCF filters only).  The expected values are in the order
+the library writes them; the fixture (test/conv2d/group_convolution_fixture.h:41-77) reorders the iota
+input and filter for the INTERLEAVED cases, and the replaying tests do the same.
+Case table columns: window, stride, groups, N, H, W, C, features, same, fhwc, max_val, offset, length,
+interleaved.
 
 Usage:  python tests/golden/make_golden_grouped.py --reference <portDNN checkout>
 """
@@ -34,15 +36,14 @@ def main():
             continue
         window, stride, groups = (int(v) for v in m.groups())
         for _, name, body in CASE_RE.findall(open(os.path.join(d, fn)).read()):
-            if "BatchFormat::STRIDED" not in body:
-                continue
+            interleaved = 1 if "BatchFormat::INTERLEAVED" in body else 0
             exp = _floats(re.search(r"exp_out\s*=\s*\{(.*?)\};", body, re.S).group(1))
             n, h, w, c = (int(v) for v in re.search(r"in_shape\s*=\s*\{\{(.*?)\}\}", body).group(1).split(","))
             feat = int(re.search(r"features\s*=\s*(\d+)", body).group(1))
             same = 1 if "PaddingMode::SAME" in body else 0
             fhwc = 1 if "FilterFormat::FHWC" in body else 0
             max_val = float(re.search(r"max_input_val\s*=\s*([0-9.eE+-]+)", body).group(1))
-            rows.append([window, stride, groups, n, h, w, c, feat, same, fhwc, max_val, off, exp.size])
+            rows.append([window, stride, groups, n, h, w, c, feat, same, fhwc, max_val, off, exp.size, interleaved])
             chunks.append(exp)
             off += exp.size
     table = np.asarray(rows, dtype=np.float64)

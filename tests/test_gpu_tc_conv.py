@@ -87,6 +87,44 @@ def test_forward_fused_epilogue(orc, dtype):
     assert rel_err(to_host(out), ref) <= TOL[dtype]
 
 
+GROUPED_SHAPES = [
+    # n, h, w, c, k, window, stride, groups
+    (2, 14, 14, 64, 128, 3, 1, 2),
+    (3, 28, 28, 128, 128, 3, 2, 4),   # stride 2: one tensor map per input parity and group
+    (2, 9, 11, 96, 48, 1, 1, 3),      # 16 features per group: partial column tiles
+    (1, 16, 16, 256, 256, 3, 1, 32),  # ResNeXt-like: 8 channels per group
+]
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+@pytest.mark.parametrize("fhwc", [False, True])
+@pytest.mark.parametrize("shape", GROUPED_SHAPES)
+def test_grouped_forward_on_tensor_cores(orc, dtype, fhwc, shape):
+    """STRIDED groups with at least 8 channels and features per group: one implicit GEMM per group on
+    channel slices (as many launches as groups), against the oracle's grouped convolution; bias and
+    ReLU go through the same slices."""
+    n, h, w, c, k, win, st, groups = shape
+    rng = np.random.default_rng(11)
+    p = pd.conv_params(n, h, w, c, k, win, st, groups=groups, filter_format=2 if fhwc else 0)
+    po = orc.conv_params(n, h, w, c, k, win, st, groups=groups)
+    cg = c // groups
+    x = rounded(rng.uniform(-1, 1, n * h * w * c).astype(np.float32), dtype)
+    wt = rounded((rng.uniform(-1, 1, win * win * cg * k) * np.sqrt(1.0 / (win * win * cg))).astype(np.float32), dtype)
+    bias = rounded(rng.standard_normal(k).astype(np.float32), dtype)
+    ref = np.maximum(orc.conv2d(orc.FORWARD, x, wt, po).reshape(-1, k) + bias, 0).ravel()
+    w_dev = wt
+    if fhwc:  # [K][R][S][C/G]: a group's filters are a contiguous run of rows
+        w_dev = np.ascontiguousarray(wt.reshape(win * win * cg, k).T)
+    before = pd.launch_count()
+    y = to_host(pd.conv2d(pd.FORWARD, to_dev(x, dtype), to_dev(w_dev, dtype), p, algorithm=pd.ALGO_IM2COL,
+                          bias=to_dev(bias, dtype), activation=pd.ACT_RELU))
+    launches = pd.launch_count() - before
+    assert_no_device_error()
+    assert rel_err(y, ref) <= TOL[dtype]
+    # fp32 adds a filter-splitting launch per group where the filter slice is contiguous (FHWC)
+    assert launches in (groups, 2 * groups), launches
+
+
 # Shapes large enough for the plans that need the whole device busy: clusters of two CTAs on 256 x 256
 # tiles (long reduction, features a multiple of 256, at least 74 pairs of row tiles).
 CTA_PAIR_SHAPES = [
