@@ -401,10 +401,10 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
 // Converts 32 accumulator columns of one row (four 16-byte chunks, numbered from chunk_base) and
 // writes them into the row's 128 bytes of the staging slice.  `bv` holds the bias of those 32
 // columns (zeros without a bias), `mk` (MASK only) the keep masks of those columns.
-template <typename OutT, bool MASK>
+template <typename OutT, bool MASK, bool BITS = false>
 __device__ __forceinline__ uint32_t fast_convert_store(const uint32_t (&acc)[32], bool zero, bool has_bias, const uint4* bv,
-                                                       int act, uint8_t* row_ptr, int row, int chunk_base, const uint4* mk,
-                                                       bool want_bits = false) {
+                                                       int act, uint8_t* row_ptr, int row, int chunk_base, const uint4* mk) {
+  constexpr bool want_bits = BITS && !MASK;
   using P2 = typename Pair<OutT>::type;
   const P2 zero2 = Pair<OutT>::splat(0.f), six2 = Pair<OutT>::splat(6.f);
   uint32_t bits = 0u;  // want_bits: bit c = column c of these 32 is positive (a positive 16-bit float is a positive integer)
@@ -423,9 +423,9 @@ __device__ __forceinline__ uint32_t fast_convert_store(const uint32_t (&acc)[32]
         if (act == PDNN_ACT_RELU6) v = __hmin2(v, six2);
       }
       o[i] = pair_bits(v);
-      if (!MASK && want_bits) pos[i] = __hgt2_mask(v, zero2);  // 0xFFFF per positive half
+      if constexpr (want_bits) pos[i] = __hgt2_mask(v, zero2);  // 0xFFFF per positive half
     }
-    if (!MASK && want_bits) {
+    if constexpr (want_bits) {
       // one distinct bit per element, then the two halves folded: elements 2i (low halves) and 2i + 1
       const uint32_t c = (pos[0] & 0x00020001u) | (pos[1] & 0x00080004u) | (pos[2] & 0x00200010u) | (pos[3] & 0x00800040u);
       bits |= ((c | (c >> 16)) & 0xFFu) << (g * 8);
@@ -506,22 +506,33 @@ __device__ __forceinline__ void request_mask_block(const GemmArgs& a, const Warp
 // latency-bound: 16-bit output, alpha == 1, optional bias, activation none / ReLU / ReLU6.  The
 // accumulators are rounded to the output type first and bias and activation are applied to
 // packed pairs in that type - the arithmetic of separate convolution, bias-add and activation
-// passes.  MASK: the result is additionally zeroed wherever a.relu_mask is not positive.
-template <typename OutT, bool MASK>
+// passes.  MASK: the result is additionally zeroed wherever a.relu_mask is not positive.  BITS: the
+// sign bits of the result are written to a.bitmask_out.  (Both are compile-time forms: as run-time
+// branches of one instantiation they cost the plain forward epilogue 7 % of the ResNet-50 step.)
+template <typename OutT, bool MASK, bool BITS = false>
 __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc,
                                                        int lane, bool zero, const WarpStore& ws,
                                                        uint32_t& store_count, uint32_t bias_s, int q32, MaskSlot& ms,
                                                        volatile int* abort_flag) {
   const int act = a.act;
-  const bool bit_mask = MASK && a.mask_bits != nullptr, emit_bits = !MASK && a.bitmask_out != nullptr;
-  const long long row_off = (a.accumulate != 0 || bit_mask || emit_bits) ? row_element_offset(a, t, q32, lane) : -1;
+  static_assert(!(MASK && BITS), "one form per instantiation");
+  const bool bit_mask = MASK && a.mask_bits != nullptr;
+  constexpr bool emit_bits = BITS;
+  long long row_off = -1;
+  if constexpr (MASK || BITS) {
+    if (a.accumulate != 0 || bit_mask || emit_bits) row_off = row_element_offset(a, t, q32, lane);
+  }
   // mask bits of the lane's row for every 64-column block of the tile, requested up front
-  uint2 pre[4] = {make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u)};
-  if (bit_mask && row_off >= 0) {
+  [[maybe_unused]] uint2 pre[MASK ? 4 : 1];
+  if constexpr (MASK) {
 #pragma unroll
-    for (int b = 0; b < 4; ++b)
-      if (b * 64 < a.bn && t.nf0 + b * 64 < a.ext_cols)
-        pre[b] = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(a.mask_bits) + ((row_off + t.nf0 + b * 64) >> 3)));
+    for (int b = 0; b < 4; ++b) pre[b] = make_uint2(0u, 0u);
+    if (bit_mask && row_off >= 0) {
+#pragma unroll
+      for (int b = 0; b < 4; ++b)
+        if (b * 64 < a.bn && t.nf0 + b * 64 < a.ext_cols)
+          pre[b] = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(a.mask_bits) + ((row_off + t.nf0 + b * 64) >> 3)));
+    }
   }
 #pragma unroll 1
   for (int c0 = 0; c0 < a.bn; c0 += 64, ++store_count) {
@@ -536,7 +547,8 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
     const bool add_prev = a.accumulate != 0, has_bias = add_prev || (!MASK && bias_s != 0u);
     if (add_prev) {
       // accumulating form: the lane's own row of the block that is in the output already (128 bytes)
-      const uint16_t* prev = row_off >= 0 ? static_cast<const uint16_t*>(a.out) + row_off + t.nf0 + c0 : nullptr;
+      const long long off = (MASK || BITS) ? row_off : row_element_offset(a, t, q32, lane);
+      const uint16_t* prev = off >= 0 ? static_cast<const uint16_t*>(a.out) + off + t.nf0 + c0 : nullptr;
 #pragma unroll
       for (int g = 0; g < 8; ++g)
         bv[g] = (prev != nullptr && t.nf0 + c0 + g * 8 < a.ext_cols) ? ld_global_v4(prev + g * 8) : make_uint4(0u, 0u, 0u, 0u);
@@ -545,11 +557,12 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
       for (int g = 0; g < 8; ++g)
         bv[g] = has_bias ? ld_shared_v4(bias_s + (uint32_t)(t.nf0 + c0 + g * 8) * 2u) : make_uint4(0u, 0u, 0u, 0u);
     }
-    uint4 mk[8];
-    if (bit_mask) {
+    uint4 mk[MASK ? 8 : 1];
+    if constexpr (MASK) {
+     if (bit_mask) {
       const int blk = c0 >> 6;
       expand_mask_bits(blk == 0 ? pre[0] : blk == 1 ? pre[1] : blk == 2 ? pre[2] : pre[3], mk);
-    } else if (MASK) {
+     } else {
       // this block's mask was requested earlier: take the lane's row out of the slot as keep masks,
       // then let the next request reuse the slot
       const uint32_t mslot = ms.consumed % ms.nslots;
@@ -567,14 +580,17 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
       __syncwarp();  // every lane holds its masks: the slot may be overwritten
       ++ms.consumed;
       request_mask_block(a, ws, ms);
+     }
     }
     wait_slice_free(ws, lane);
     if (!zero) tmem_wait_ld();
     uint8_t* row_ptr = ws.buf + slot * 4096u + (size_t)lane * 128;
-    const uint32_t lo_bits = fast_convert_store<OutT, MASK>(acc0, zero, has_bias, bv, act, row_ptr, lane, 0, mk, emit_bits);
-    const uint32_t hi_bits = fast_convert_store<OutT, MASK>(acc1, zero, has_bias, bv + 4, act, row_ptr, lane, 4, mk + 4, emit_bits);
-    if (emit_bits && row_off >= 0 && t.nf0 + c0 < a.ext_cols)
-      *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.bitmask_out) + ((row_off + t.nf0 + c0) >> 3)) = make_uint2(lo_bits, hi_bits);
+    const uint32_t lo_bits = fast_convert_store<OutT, MASK, BITS>(acc0, zero, has_bias, bv, act, row_ptr, lane, 0, mk);
+    const uint32_t hi_bits = fast_convert_store<OutT, MASK, BITS>(acc1, zero, has_bias, bv + 4, act, row_ptr, lane, 4, MASK ? mk + 4 : mk);
+    if constexpr (emit_bits) {
+      if (row_off >= 0 && t.nf0 + c0 < a.ext_cols)
+        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.bitmask_out) + ((row_off + t.nf0 + c0) >> 3)) = make_uint2(lo_bits, hi_bits);
+    }
     issue_slice_store(a, t, ws, slot, t.nf0 + c0, lane);
   }
   return true;
@@ -582,7 +598,8 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
 
 // EPI selects the epilogue compiled into the instantiation: 0 = direct stores from registers,
 // 1 = staged TMA store with fp32 arithmetic, 2 = staged TMA store with packed 16-bit arithmetic,
-// 3 = as 2 with the ReLU-gradient mask (GemmArgs::relu_mask).
+// 3 = as 2 with the ReLU-gradient mask (GemmArgs::relu_mask), 4 = as 2 writing the sign bits of the
+// result (GemmArgs::bitmask_out).
 // One epilogue per instantiation keeps each kernel's register allocation tight.
 //
 // A CTA runs up to two independent pipelines ("groups") side by side, each with its own TMA
@@ -1084,7 +1101,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       const uint32_t tmem_acc = grp_tmem + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
       const bool zero = !(t.ks_end > t.ks_begin);
       if constexpr (EPI >= 2) {
-        if (!epilogue_tile_tma_fast<OutT, EPI == 3>(a, t, tmem_acc, lane, zero, ws, store_count, bias_s, q * 32, mask_slot,
+        if (!epilogue_tile_tma_fast<OutT, EPI == 3, EPI == 4>(a, t, tmem_acc, lane, zero, ws, store_count, bias_s, q * 32, mask_slot,
                                                     abort_flag))
           break;
       } else if constexpr (EPI == 1) {
@@ -1176,7 +1193,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
 // Barriers live at the same offsets in both CTAs: full[s] is used in rank 0 only; empty[s] and
 // acc_full[b] are signalled in both CTAs by the issuer's commits; acc_empty[b] of rank 0 collects the
 // eight epilogue warps of the pair.
-template <typename OutT>
+template <typename OutT, bool BITS>
 __global__ void __launch_bounds__(192, 1) umma_gemm_pair2_kernel(const __grid_constant__ GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const GemmArgs& a = args;
@@ -1345,7 +1362,7 @@ __global__ void __launch_bounds__(192, 1) umma_gemm_pair2_kernel(const __grid_co
       if (!mbar_wait(acc_full_bar((int)buf), aph, abort_flag, g_error_record, a.wait_limit_ns, 0xC00u + buf)) break;
       tc_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u;
-      if (!epilogue_tile_tma_fast<OutT, false>(a, t, tmem_acc, lane, false, ws, store_count, bias_s, q * 32, unused_mask,
+      if (!epilogue_tile_tma_fast<OutT, false, BITS>(a, t, tmem_acc, lane, false, ws, store_count, bias_s, q * 32, unused_mask,
                                                abort_flag))
         break;
       tc_fence_before_sync();
@@ -1695,11 +1712,13 @@ GemmKernel select_kernel(bool split, int epi, int out_dtype) {
   }
   switch (out_dtype) {
     case PDNN_F16:
-      return epi == 3 ? umma_gemm_kernel<false, 3, __half>
+      return epi == 4 ? umma_gemm_kernel<false, 4, __half>
+             : epi == 3 ? umma_gemm_kernel<false, 3, __half>
              : epi == 2 ? umma_gemm_kernel<false, 2, __half>
                       : epi == 1 ? umma_gemm_kernel<false, 1, __half> : umma_gemm_kernel<false, 0, __half>;
     case PDNN_BF16:
-      return epi == 3 ? umma_gemm_kernel<false, 3, __nv_bfloat16>
+      return epi == 4 ? umma_gemm_kernel<false, 4, __nv_bfloat16>
+             : epi == 3 ? umma_gemm_kernel<false, 3, __nv_bfloat16>
              : epi == 2 ? umma_gemm_kernel<false, 2, __nv_bfloat16>
                       : epi == 1 ? umma_gemm_kernel<false, 1, __nv_bfloat16> : umma_gemm_kernel<false, 0, __nv_bfloat16>;
     default:
@@ -1709,7 +1728,10 @@ GemmKernel select_kernel(bool split, int epi, int out_dtype) {
 
 // Launch of the CTA-pair kernel: clusters of two CTAs, one cluster per pair of SMs.
 int launch_gemm_pair2(const GemmArgs& g, long long total_pairs, cudaStream_t s) {
-  GemmKernel kernel = g.out_dtype == PDNN_F16 ? umma_gemm_pair2_kernel<__half> : umma_gemm_pair2_kernel<__nv_bfloat16>;
+  const bool bits = g.bitmask_out != nullptr;
+  GemmKernel kernel = g.out_dtype == PDNN_F16 ? (bits ? umma_gemm_pair2_kernel<__half, true> : umma_gemm_pair2_kernel<__half, false>)
+                                              : (bits ? umma_gemm_pair2_kernel<__nv_bfloat16, true>
+                                                      : umma_gemm_pair2_kernel<__nv_bfloat16, false>);
   const size_t smem = 1024 + (size_t)g.stages * 2 * kABytes + (size_t)g.nsw * 4 * 4096 + kBarBlockBytes + (size_t)g.bias_smem_bytes;
   if (smem > (size_t)kSmemBudget) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: plan needs %zu bytes of shared memory", smem);
   {
@@ -1719,8 +1741,12 @@ int launch_gemm_pair2(const GemmArgs& g, long long total_pairs, cudaStream_t s) 
     if (dev < 0 || dev >= kMaxDevices) return fail(PDNN_ALLOCATION_PROBLEM, "tensor-core gemm: no usable current device");
     std::lock_guard<std::mutex> lock(mu);
     if (!opted_in[dev]) {
-      if (cudaFuncSetAttribute(umma_gemm_pair2_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) != cudaSuccess ||
-          cudaFuncSetAttribute(umma_gemm_pair2_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) != cudaSuccess) {
+      bool ok = true;
+      for (GemmKernel k : {GemmKernel(umma_gemm_pair2_kernel<__half, false>), GemmKernel(umma_gemm_pair2_kernel<__half, true>),
+                           GemmKernel(umma_gemm_pair2_kernel<__nv_bfloat16, false>),
+                           GemmKernel(umma_gemm_pair2_kernel<__nv_bfloat16, true>)})
+        ok = ok && cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) == cudaSuccess;
+      if (!ok) {
         cudaGetLastError();
         return fail(PDNN_ALLOCATION_PROBLEM, "cannot opt in to %d bytes of shared memory", kSmemBudget);
       }
@@ -1785,7 +1811,7 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
     std::lock_guard<std::mutex> lock(mu);
     if (!opted_in[dev]) {
       for (int sp = 0; sp < 2; ++sp)
-        for (int epi = 0; epi < 4; ++epi)
+        for (int epi = 0; epi < 5; ++epi)
           for (int dt = 0; dt < 3; ++dt) {
             GemmKernel k = select_kernel(sp != 0, epi, dt);
             if (k != nullptr && cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) != cudaSuccess) {
@@ -1796,7 +1822,7 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
       opted_in[dev] = true;
     }
   }
-  const int epi = g.epi_fast ? (g.relu_mask != nullptr ? 3 : 2) : (g.tma_store ? 1 : 0);
+  const int epi = g.epi_fast ? (g.relu_mask != nullptr ? 3 : g.bitmask_out != nullptr ? 4 : 2) : (g.tma_store ? 1 : 0);
   GemmKernel kernel = select_kernel(split, epi, g.out_dtype);
   if (kernel == nullptr) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: no kernel for this output type");
   const int sms = device_sm_count();
