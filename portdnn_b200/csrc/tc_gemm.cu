@@ -509,25 +509,25 @@ __device__ __forceinline__ void request_mask_block(const GemmArgs& a, const Warp
 // passes.  MASK: the result is additionally zeroed wherever a.relu_mask is not positive.  BITS: the
 // sign bits of the result are written to a.bitmask_out.  (Both are compile-time forms: as run-time
 // branches of one instantiation they cost the plain forward epilogue 7 % of the ResNet-50 step.)
-template <typename OutT, bool MASK, bool BITS = false>
+template <typename OutT, bool MASK, bool BITS = false, bool MBITS = false>
 __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const TileCoord& t, uint32_t tmem_acc,
                                                        int lane, bool zero, const WarpStore& ws,
                                                        uint32_t& store_count, uint32_t bias_s, int q32, MaskSlot& ms,
                                                        volatile int* abort_flag) {
   const int act = a.act;
-  static_assert(!(MASK && BITS), "one form per instantiation");
-  const bool bit_mask = MASK && a.mask_bits != nullptr;
+  static_assert(!(MASK && BITS) && (MASK || !MBITS), "one form per instantiation");
+  constexpr bool bit_mask = MBITS;  // the mask arrives as one bit per element (a.mask_bits), not as a tensor
   constexpr bool emit_bits = BITS;
   long long row_off = -1;
   if constexpr (MASK || BITS) {
     if (a.accumulate != 0 || bit_mask || emit_bits) row_off = row_element_offset(a, t, q32, lane);
   }
   // mask bits of the lane's row for every 64-column block of the tile, requested up front
-  [[maybe_unused]] uint2 pre[MASK ? 4 : 1];
-  if constexpr (MASK) {
+  [[maybe_unused]] uint2 pre[MBITS ? 4 : 1];
+  if constexpr (MBITS) {
 #pragma unroll
     for (int b = 0; b < 4; ++b) pre[b] = make_uint2(0u, 0u);
-    if (bit_mask && row_off >= 0) {
+    if (row_off >= 0) {
 #pragma unroll
       for (int b = 0; b < 4; ++b)
         if (b * 64 < a.bn && t.nf0 + b * 64 < a.ext_cols)
@@ -559,7 +559,7 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
     }
     uint4 mk[MASK ? 8 : 1];
     if constexpr (MASK) {
-     if (bit_mask) {
+     if constexpr (MBITS) {
       const int blk = c0 >> 6;
       expand_mask_bits(blk == 0 ? pre[0] : blk == 1 ? pre[1] : blk == 2 ? pre[2] : pre[3], mk);
      } else {
@@ -599,7 +599,7 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
 // EPI selects the epilogue compiled into the instantiation: 0 = direct stores from registers,
 // 1 = staged TMA store with fp32 arithmetic, 2 = staged TMA store with packed 16-bit arithmetic,
 // 3 = as 2 with the ReLU-gradient mask (GemmArgs::relu_mask), 4 = as 2 writing the sign bits of the
-// result (GemmArgs::bitmask_out).
+// result (GemmArgs::bitmask_out), 5 = as 3 with the mask as one bit per element (GemmArgs::mask_bits).
 // One epilogue per instantiation keeps each kernel's register allocation tight.
 //
 // A CTA runs up to two independent pipelines ("groups") side by side, each with its own TMA
@@ -1087,8 +1087,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       mask_slot.sub_w = sub_w;
       mask_slot.sub_h = sub_h;
       mask_slot.sub_n = sub_n;
-      if (a.mask_bits == nullptr)
-        for (uint32_t i = 0; i < mask_slot.nslots; ++i) request_mask_block(a, ws, mask_slot);
+      for (uint32_t i = 0; i < mask_slot.nslots; ++i) request_mask_block(a, ws, mask_slot);
     }
 #pragma unroll 1
     for (int tile = first_tile; tile < total_tiles; tile += tile_step, walker.advance()) {
@@ -1101,7 +1100,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
       const uint32_t tmem_acc = grp_tmem + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
       const bool zero = !(t.ks_end > t.ks_begin);
       if constexpr (EPI >= 2) {
-        if (!epilogue_tile_tma_fast<OutT, EPI == 3, EPI == 4>(a, t, tmem_acc, lane, zero, ws, store_count, bias_s, q * 32, mask_slot,
+        if (!epilogue_tile_tma_fast<OutT, EPI == 3 || EPI == 5, EPI == 4, EPI == 5>(a, t, tmem_acc, lane, zero, ws, store_count, bias_s, q * 32, mask_slot,
                                                     abort_flag))
           break;
       } else if constexpr (EPI == 1) {
@@ -1712,12 +1711,14 @@ GemmKernel select_kernel(bool split, int epi, int out_dtype) {
   }
   switch (out_dtype) {
     case PDNN_F16:
-      return epi == 4 ? umma_gemm_kernel<false, 4, __half>
+      return epi == 5 ? umma_gemm_kernel<false, 5, __half>
+             : epi == 4 ? umma_gemm_kernel<false, 4, __half>
              : epi == 3 ? umma_gemm_kernel<false, 3, __half>
              : epi == 2 ? umma_gemm_kernel<false, 2, __half>
                       : epi == 1 ? umma_gemm_kernel<false, 1, __half> : umma_gemm_kernel<false, 0, __half>;
     case PDNN_BF16:
-      return epi == 4 ? umma_gemm_kernel<false, 4, __nv_bfloat16>
+      return epi == 5 ? umma_gemm_kernel<false, 5, __nv_bfloat16>
+             : epi == 4 ? umma_gemm_kernel<false, 4, __nv_bfloat16>
              : epi == 3 ? umma_gemm_kernel<false, 3, __nv_bfloat16>
              : epi == 2 ? umma_gemm_kernel<false, 2, __nv_bfloat16>
                       : epi == 1 ? umma_gemm_kernel<false, 1, __nv_bfloat16> : umma_gemm_kernel<false, 0, __nv_bfloat16>;
@@ -1811,7 +1812,7 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
     std::lock_guard<std::mutex> lock(mu);
     if (!opted_in[dev]) {
       for (int sp = 0; sp < 2; ++sp)
-        for (int epi = 0; epi < 5; ++epi)
+        for (int epi = 0; epi < 6; ++epi)
           for (int dt = 0; dt < 3; ++dt) {
             GemmKernel k = select_kernel(sp != 0, epi, dt);
             if (k != nullptr && cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) != cudaSuccess) {
@@ -1822,7 +1823,8 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
       opted_in[dev] = true;
     }
   }
-  const int epi = g.epi_fast ? (g.relu_mask != nullptr ? 3 : g.bitmask_out != nullptr ? 4 : 2) : (g.tma_store ? 1 : 0);
+  const int epi = g.epi_fast ? (g.mask_bits != nullptr ? 5 : g.relu_mask != nullptr ? 3 : g.bitmask_out != nullptr ? 4 : 2)
+                             : (g.tma_store ? 1 : 0);
   GemmKernel kernel = select_kernel(split, epi, g.out_dtype);
   if (kernel == nullptr) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: no kernel for this output type");
   const int sms = device_sm_count();
