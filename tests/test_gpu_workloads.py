@@ -164,3 +164,94 @@ def test_resnet50_train_step_gradients(orc):
     assert checked_dw == 53 and checked_dx == 49 and not expect, (checked_dw, checked_dx, list(expect))
     # the stem pool's gradient routing is exact: one contribution, copied values
     assert net.grads[0] is not None
+
+
+def test_resnet50_train_step_at_the_benchmark_batch(orc):
+    """The training step at the benchmark's batch of 256: the activation gradients of two sampled images (the
+    input backprop is independent per image) through every layer, and the filter gradients - sums over the
+    whole batch - of five layers that take different kernels (the few-channel stem, a 3x3 with two taps per
+    tile, a strided 3x3, a strided projection without ReLU, a 7x7-pixel 1x1 expansion), against the oracle
+    applied to the GPU's own incoming gradient of that layer."""
+    batch, images = 256, (0, 255)
+    full_dw = {"stem", "s1b1_3x3", "s2b1_3x3", "s3b1_proj", "s4b3_1x1b"}
+    net = workloads.ConvStackRunner(workloads.resnet50_v15(batch), torch.device("cuda", 0), seed=29, training=True)
+    net.forward()
+    net.backward()
+    torch.cuda.synchronize()
+    assert_no_device_error()
+    layers, last = net.layers, net.conv_ids[-1]
+
+    def image_of(t, img):
+        per = t.numel() // batch
+        return host(t[img * per:(img + 1) * per])
+
+    def one_image(p):
+        q = type(p)(*[getattr(p, f) for f, _ in p._fields_])
+        q.batch = 1
+        return q
+
+    def incoming(i, take):
+        """(gradient arriving at layer i, whether the producing call already applied the ReLU mask) or None."""
+        if i == last:
+            return take(net.dy_last), False
+        if net.grads[i] is not None:
+            return take(net.grads[i]), i in net._masked
+        return None
+
+    checked_dx = 0
+    for img in images:
+        take = lambda t: image_of(t, img)
+        block_grad, expect = {}, {}
+        for i in reversed(range(len(layers))):
+            l, p, j = layers[i], layers[i].params, net.src_idx[i]
+            arriving = incoming(i, take)
+            if arriving is None and l.name.endswith("_proj"):
+                arriving = (block_grad[l.name[:-5]], False)
+            if arriving is None:
+                continue
+            dy, masked = arriving
+            if isinstance(l, workloads.ConvLayer):
+                g = dy if (masked or l.activation == pd.ACT_NONE) else orc.pointwise_grad(0, take(net.acts[i]), dy)
+                if l.name.endswith("_1x1b"):
+                    block_grad[l.name[:-5]] = g
+                if j >= 0:
+                    dx = orc.conv2d(orc.INPUT_BACKPROP, g, host(net.weights[i]), oparams(orc, one_image(p)))
+                    if net.fuse_mask[j]:
+                        dx = orc.pointwise_grad(0, take(net.acts[j]), dx)
+                    expect[j] = expect.get(j, 0) + dx
+            elif l.op == pd.POOL_MAX and j >= 0:
+                dx = orc.pool_max_grad(l.op, take(net.acts[j]), take(net.acts[i]), dy, opool(orc, one_image(p)))
+                if j in net._masked:
+                    dx = orc.pointwise_grad(0, take(net.acts[j]), dx)
+                expect[j] = expect.get(j, 0) + dx
+            for t in [t for t in expect if all(net.src_idx[r] != t or r >= i for r in range(len(layers)))]:
+                e = rel_err(take(net.grads[t]), expect.pop(t))
+                assert e <= 2e-2, ("dx into", layers[t].name, "image", img, e)
+                checked_dx += 1
+        assert not expect
+    assert checked_dx == 49 * len(images), checked_dx
+
+    checked_dw = 0
+    block_grad_full = {}
+    for i in reversed(range(len(layers))):
+        l, p, j = layers[i], layers[i].params, net.src_idx[i]
+        if not isinstance(l, workloads.ConvLayer):
+            continue
+        wanted = l.name in full_dw or (l.name.endswith("_1x1b") and l.name[:-5] + "_proj" in full_dw)
+        if not wanted:
+            continue
+        arriving = incoming(i, host)
+        if arriving is None and l.name.endswith("_proj"):
+            arriving = (block_grad_full[l.name[:-5]], False)
+        dy, masked = arriving
+        g = dy if (masked or l.activation == pd.ACT_NONE) else orc.pointwise_grad(0, host(net.acts[i]), dy)
+        if l.name.endswith("_1x1b"):
+            block_grad_full[l.name[:-5]] = g
+        if l.name not in full_dw:
+            continue
+        x = host(net.input if j < 0 else net.acts[j])
+        dw_ref = orc.conv2d(orc.FILTER_BACKPROP, x, g, oparams(orc, p))
+        e = rel_err(host(net.bucket.view(net.conv_ids.index(i))), dw_ref)
+        assert e <= 2e-2, ("dW", l.name, e)
+        checked_dw += 1
+    assert checked_dw == len(full_dw), checked_dw
