@@ -111,6 +111,36 @@ def test_mobilenet_v2_depthwise_layers(orc):
         assert e <= 2e-2, (p.in_rows, p.channels, p.stride_rows, e)
 
 
+def test_mobilenet_v2_depthwise_layers_at_the_benchmark_batch(orc):
+    """The 17 depthwise layers at the benchmark's batch of 128 (the launch heuristics - rows per thread,
+    row segments, wave sizes - depend on the tensor sizes): forward of every layer, input and filter
+    backprop of the four layers larger than L2 and of three small ones."""
+    rng = np.random.default_rng(19)
+    seen = set()
+    for idx, p in enumerate(workloads.mobilenet_v2_depthwise(128)):
+        key = (p.in_rows, p.channels, p.stride_rows)
+        if key in seen:
+            continue
+        seen.add(key)
+        po = orc.DepthwiseParams(*[getattr(p, f) for f, _ in p._fields_])
+        x = half_round(rng.standard_normal(p.batch * p.in_rows * p.in_cols * p.channels, dtype=np.float32))
+        f = half_round(rng.standard_normal(9 * p.channels, dtype=np.float32) * 0.3)
+        xd, fd = torch.from_numpy(x).cuda().half(), torch.from_numpy(f).cuda().half()
+        e = rel_err(host(pd.depthwise_conv2d(pd.FORWARD, xd, fd, p)), orc.depthwise_conv2d(orc.FORWARD, x, f, po))
+        assert e <= 2e-2, ("forward", key, e)
+        if idx < 4 or key in ((28, 192, 2), (14, 576, 1), (7, 960, 1)):
+            dy = half_round(rng.standard_normal(p.batch * p.out_rows * p.out_cols * p.channels, dtype=np.float32))
+            dyd = torch.from_numpy(dy).cuda().half()
+            e = rel_err(host(pd.depthwise_conv2d(pd.INPUT_BACKPROP, dyd, fd, p)),
+                        orc.depthwise_conv2d(orc.INPUT_BACKPROP, dy, f, po))
+            assert e <= 2e-2, ("input backprop", key, e)
+            # sums of up to 1.6 million products per filter element, rounded once to fp16
+            e = rel_err(host(pd.depthwise_conv2d(pd.FILTER_BACKPROP, xd, dyd, p)),
+                        orc.depthwise_conv2d(orc.FILTER_BACKPROP, x, dy, po))
+            assert e <= 2e-2, ("filter backprop", key, e)
+    assert_no_device_error()
+
+
 def test_resnet50_train_step_gradients(orc):
     """One training step at batch 2: every filter gradient in the bucket and every activation
     gradient the runner keeps, against oracle ReLU-gradient / filter-backprop / input-backprop /
