@@ -24,6 +24,7 @@
 #include <algorithm>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 namespace pdnn {
 
@@ -620,10 +621,11 @@ __device__ __forceinline__ bool epilogue_tile_tma_fast(const GemmArgs& a, const 
 //   warp 6g + 1      MMA issuer of group g (warp 1 also owns the TMEM allocation)
 //   warps 6g + 2..5  epilogue of group g (warp % 4 selects the TMEM lane quarter)
 //   SPLIT: warps 6..9 are the hi/lo split warps of the only group
+// The body of the kernel for CTA `cta` of `n_ctas` that work on the GEMM `a` (the whole grid, or the share
+// of it that umma_gemm_multi_kernel gives to one of its GEMMs).
 template <bool SPLIT, int EPI, typename OutT>
-__global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const __grid_constant__ GemmArgs args) {
+__device__ __forceinline__ void umma_gemm_body(const GemmArgs& a, const int cta, const int n_ctas) {
   extern __shared__ uint8_t smem_raw[];
-  const GemmArgs& a = args;
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
   uint8_t* smem = smem_raw + (base - raw_addr);
@@ -673,7 +675,7 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * (2 * kBarsPerGroup + 1) + 4);
   // with bias_tile_only the copy starts at the CTA's column tile; the address is biased so that
   // indexing by absolute column still works
-  const int bias_col0 = a.bias_tile_only ? ((int)blockIdx.x % a.n_tiles) * a.bn : 0;
+  const int bias_col0 = a.bias_tile_only ? (cta % a.n_tiles) * a.bn : 0;
   const uint32_t bias_s =
       (EPI >= 2 && a.bias != nullptr) ? bar_base + kBarBlockBytes - (uint32_t)bias_col0 * 2u : 0u;
 
@@ -730,8 +732,8 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
   const int total_tiles = a.a_mn ? a.n_tiles * a.tiles_w * ((a.num_taps + a.tap_pack - 1) / a.tap_pack) * a.splits
                                  : a.n_tiles * a.tiles_w * a.tiles_h * a.tiles_n;
   // pair mode: both groups walk the same tiles (each takes one row tile of the pair)
-  const int first_tile = (int)blockIdx.x + (pair ? 0 : grp * (int)gridDim.x);
-  const int tile_step = (pair ? 1 : groups) * (int)gridDim.x;
+  const int first_tile = cta + (pair ? 0 : grp * n_ctas);
+  const int tile_step = (pair ? 1 : groups) * n_ctas;
   const bool active = grp < groups;
   // offset of this group's row tile inside the pair
   const int sub_w = pair && a.pair_dim == 1 ? grp * a.tw : 0, sub_h = pair && a.pair_dim == 2 ? grp * a.th : 0,
@@ -779,10 +781,10 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
         }
       };
       auto load_b = [&](uint32_t sb, uint32_t fb, int kc, int nf0, int btap) { load_b_from(bmap, sb, fb, kc, nf0, btap); };
-      if (b_res && grp == 0 && (int)blockIdx.x < total_tiles) {
+      if (b_res && grp == 0 && cta < total_tiles) {
         warp_arrive_expect_tx(bres_bar, res_bytes);
         uint32_t dst = base;
-        const int nt_begin = a.b_res == 2 ? (int)blockIdx.x % a.n_tiles : 0;
+        const int nt_begin = a.b_res == 2 ? cta % a.n_tiles : 0;
         const int nt_end = a.b_res == 2 ? nt_begin + 1 : a.n_tiles;
 #pragma unroll 1
         for (int nt = nt_begin; nt < nt_end; ++nt)
@@ -1176,6 +1178,38 @@ __global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const _
     __syncthreads();
   }
   if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)a.tmem_cols);
+}
+
+template <bool SPLIT, int EPI, typename OutT>
+__global__ void __launch_bounds__(SPLIT ? 320 : 384, 1) umma_gemm_kernel(const __grid_constant__ GemmArgs args) {
+  umma_gemm_body<SPLIT, EPI, OutT>(args, (int)blockIdx.x, (int)gridDim.x);
+}
+
+// Several independent GEMMs in one launch, each on its own share of the grid: the parity classes of
+// a strided input backprop (up to four GEMMs over disjoint pixels of dx).  As separate launches each
+// class pays its own ramp and tail on a quarter of the work; side by side they finish together.
+// CTAs first_cta[i] .. first_cta[i + 1] - 1 work on GEMM i.
+constexpr int kMaxMulti = 4;
+struct alignas(64) GemmArgsMulti {
+  GemmArgs gemm[kMaxMulti];
+  int count;
+  int first_cta[kMaxMulti + 1];
+};
+
+template <int EPI, typename OutT>
+__global__ void __launch_bounds__(384, 1) umma_gemm_multi_kernel(const __grid_constant__ GemmArgsMulti args) {
+  int which = 0;
+  while (which + 1 < args.count && (int)blockIdx.x >= args.first_cta[which + 1]) ++which;
+  const int cta = (int)blockIdx.x - args.first_cta[which], n_ctas = args.first_cta[which + 1] - args.first_cta[which];
+  // One copy of the body per GEMM: with a run-time index the fields of the arguments stop being
+  // constant-bank operands and become loads, which the single-thread roles and the short epilogues
+  // of the body cannot afford (measured: twice the time on the 56x56 layer).
+  switch (which) {
+    case 0: umma_gemm_body<false, EPI, OutT>(args.gemm[0], cta, n_ctas); break;
+    case 1: umma_gemm_body<false, EPI, OutT>(args.gemm[1], cta, n_ctas); break;
+    case 2: umma_gemm_body<false, EPI, OutT>(args.gemm[2], cta, n_ctas); break;
+    default: umma_gemm_body<false, EPI, OutT>(args.gemm[3], cta, n_ctas); break;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1701,6 +1735,7 @@ bool setup_store(GemmArgs& g, int compute_dtype, const uint64_t out_dims[4], con
 }
 
 using GemmKernel = void (*)(const GemmArgs);
+using GemmKernelMulti = void (*)(const GemmArgsMulti);
 
 // Kernel instantiation for (split, epilogue kind, output dtype); nullptr for combinations that
 // are never launched (the split kernel only produces fp32; packed arithmetic is 16-bit only).
@@ -1856,6 +1891,138 @@ int launch_gemm(const GemmArgs& g, int dtype, cudaStream_t s) {
   }
   if (g.bitmask_out != nullptr) bitmask_written_flag() = true;
   return check_launch("tensor-core gemm");
+}
+
+// The packed-epilogue kernels that exist as multi-GEMM instantiations: plain, tensor mask, bit mask.
+GemmKernelMulti select_multi_kernel(int epi, int out_dtype) {
+  if (out_dtype == PDNN_F16)
+    return epi == 2 ? umma_gemm_multi_kernel<2, __half>
+           : epi == 3 ? umma_gemm_multi_kernel<3, __half> : epi == 5 ? umma_gemm_multi_kernel<5, __half> : nullptr;
+  if (out_dtype == PDNN_BF16)
+    return epi == 2 ? umma_gemm_multi_kernel<2, __nv_bfloat16>
+           : epi == 3 ? umma_gemm_multi_kernel<3, __nv_bfloat16> : epi == 5 ? umma_gemm_multi_kernel<5, __nv_bfloat16> : nullptr;
+  return nullptr;
+}
+
+int gemm_epilogue_kind(const GemmArgs& g) {
+  return g.epi_fast ? (g.mask_bits != nullptr ? 5 : g.relu_mask != nullptr ? 3 : g.bitmask_out != nullptr ? 4 : 2)
+                    : (g.tma_store ? 1 : 0);
+}
+
+size_t gemm_smem_bytes(const GemmArgs& g, bool split) {
+  const unsigned stage = g.pair   ? 2u * kABytes + (unsigned)g.bn * 128u
+                         : g.halo ? g.halo_stage_bytes
+                                  : g.b_res ? (unsigned)kABytes : (kABytes + (unsigned)g.bn * 128u) * (split ? 2u : 1u);
+  const int rings = g.pair ? 1 : g.groups;
+  const size_t smem = 1024 + (size_t)g.b_res_bytes + (size_t)rings * g.stages * stage +
+                      (g.tma_store ? (size_t)g.groups * (g.nsw + g.mask_slots) * 4 * 4096 : 0) + kBarBlockBytes +
+                      (size_t)g.bias_smem_bytes + (size_t)g.mask_smem_bytes;
+  // At least 120 KB, so that two CTAs never share an SM: the second one would wait for TMEM
+  // columns the first one holds.
+  return std::max<size_t>(smem, 120 * 1024);
+}
+
+long long gemm_total_tiles(const GemmArgs& g) {
+  const int tap_pack = std::max(g.tap_pack, 1);
+  return g.a_mn ? (long long)g.n_tiles * g.tiles_w * ((g.num_taps + tap_pack - 1) / tap_pack) * g.splits
+                : (long long)g.n_tiles * g.tiles_w * g.tiles_h * g.tiles_n;
+}
+
+// True if these GEMMs can share one launch: 16-bit packed epilogue of one kind, one pipeline layout
+// (no CTA pairs, no fp32 split), every GEMM with work, and enough SMs to give each its column tiles.
+bool multi_launchable(const GemmArgs* list, int count, int sms) {
+  if (count < 2 || count > kMaxMulti) return false;
+  const int epi = gemm_epilogue_kind(list[0]);
+  if (select_multi_kernel(epi, list[0].out_dtype) == nullptr) return false;
+  int min_ctas = 0;
+  for (int i = 0; i < count; ++i) {
+    const GemmArgs& g = list[i];
+    if (gemm_epilogue_kind(g) != epi || g.out_dtype != list[0].out_dtype || g.cta_pair || g.a_mn) return false;
+    // a GEMM without reduction steps only writes zeros: side by side it would take SMs from the ones that
+    // compute and finish no sooner (measured on a strided 1x1 layer: 0.31 against 0.21 ms)
+    if (g.num_taps < 1) return false;
+    const long long total = gemm_total_tiles(g);
+    if (total <= 0 || total > 0x7FFFFFFFll) return false;
+    if (gemm_smem_bytes(g, false) > (size_t)kSmemBudget) return false;
+    min_ctas += (g.b_res == 2 || g.bias_tile_only) ? g.n_tiles : 1;
+  }
+  return min_ctas <= sms;
+}
+
+int launch_gemm_multi(const GemmArgs* list, int count, cudaStream_t s) {
+  const int sms = device_sm_count();
+  const int epi = gemm_epilogue_kind(list[0]);
+  GemmKernelMulti kernel = select_multi_kernel(epi, list[0].out_dtype);
+  {
+    static std::mutex mu;
+    static bool opted_in[kMaxDevices] = {};
+    const int dev = current_device();
+    if (dev < 0 || dev >= kMaxDevices) return fail(PDNN_ALLOCATION_PROBLEM, "tensor-core gemm: no usable current device");
+    std::lock_guard<std::mutex> lock(mu);
+    if (!opted_in[dev]) {
+      for (int e : {2, 3, 5})
+        for (int dt : {PDNN_F16, PDNN_BF16})
+          if (cudaFuncSetAttribute(select_multi_kernel(e, dt), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(PDNN_ALLOCATION_PROBLEM, "cannot opt in to %d bytes of shared memory", kSmemBudget);
+          }
+      opted_in[dev] = true;
+    }
+  }
+  // Shares of the SMs in proportion to the time each GEMM needs (tiles x cost of a tile),
+  // every GEMM at least one CTA (or one per column tile where its CTAs stay on one column tile).
+  static thread_local GemmArgsMulti m;  // (8 KB: kept off the stack)
+  m.count = count;
+  size_t smem = 0;
+  double work[kMaxMulti], all_work = 0;
+  int floor_ctas[kMaxMulti], share[kMaxMulti], given = 0;
+  for (int i = 0; i < count; ++i) {
+    m.gemm[i] = list[i];
+    m.gemm[i].tap_pack = std::max(list[i].tap_pack, 1);
+    m.gemm[i].wait_limit_ns = kWaitLimitNs;
+    smem = std::max(smem, gemm_smem_bytes(list[i], false));
+    // a tile costs its reduction steps, but never less than its epilogue and its bytes: about four steps' worth
+    work[i] = (double)gemm_total_tiles(list[i]) * std::max(4, list[i].num_taps * list[i].cblocks);
+    all_work += work[i];
+    floor_ctas[i] = (list[i].b_res == 2 || list[i].bias_tile_only) ? list[i].n_tiles : 1;
+  }
+  for (int i = 0; i < count; ++i) {
+    const long long total = gemm_total_tiles(list[i]);
+    int want = (int)std::min<long long>(total, std::max<long long>(floor_ctas[i], (long long)(sms * work[i] / all_work)));
+    want = std::max(want, floor_ctas[i]);
+    if (floor_ctas[i] > 1) want -= want % floor_ctas[i];
+    share[i] = want;
+    given += want;
+  }
+  // rounding may leave SMs over or ask for too many: take from / give to the largest share
+  while (given > sms) {
+    int big = 0;
+    for (int i = 1; i < count; ++i)
+      if (share[i] - floor_ctas[i] > share[big] - floor_ctas[big]) big = i;
+    const int step = floor_ctas[big] > 1 ? floor_ctas[big] : 1;
+    if (share[big] - step < floor_ctas[big]) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: cannot share the grid");
+    share[big] -= step;
+    given -= step;
+  }
+  m.first_cta[0] = 0;
+  for (int i = 0; i < count; ++i) m.first_cta[i + 1] = m.first_cta[i] + share[i];
+  for (int i = count + 1; i <= kMaxMulti; ++i) m.first_cta[i] = m.first_cta[count];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)m.first_cta[count]);
+  cfg.blockDim = dim3(384);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, m);
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return fail(PDNN_ALLOCATION_PROBLEM, "tensor-core gemm: launch failed: %s", cudaGetErrorString(le));
+  }
+  return check_launch("tensor-core gemm (several GEMMs)");
 }
 
 void set_epilogue(GemmArgs& g, const PdnnConvEpilogue* epi) {
@@ -2363,6 +2530,7 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
   // dx is produced one output parity class at a time: positions h = sr*i + qh, w = sc*j + qw only
   // receive taps with r = (qh + pad) mod sr, s = (qw + pad) mod sc, and within a class the
   // relation between i and the dy row is a plain shift.
+  std::vector<GemmArgs> planned_classes;
   for (int qh = 0; qh < p.stride_rows; ++qh)
     for (int qw = 0; qw < p.stride_cols; ++qw) {
       const int Hq = ceil_div(p.in_rows - qh, p.stride_rows), Wq = ceil_div(p.in_cols - qw, p.stride_cols);
@@ -2525,9 +2693,19 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
         // An earlier class may already have masked its pixels; masking them again changes nothing.
         mask_pending = true;
       }
+      planned_classes.push_back(g);
+    }
+  // The classes of a strided layer write disjoint pixels of dx: side by side in one launch where
+  // their kernels agree, else one launch each.
+  if (multi_launchable(planned_classes.data(), (int)planned_classes.size(), sms)) {
+    const int st_ = launch_gemm_multi(planned_classes.data(), (int)planned_classes.size(), s);
+    if (st_ != PDNN_OK) return st_;
+  } else {
+    for (const GemmArgs& g : planned_classes) {
       const int st_ = launch_gemm(g, dtype, s);
       if (st_ != PDNN_OK) return st_;
     }
+  }
   if (mask_pending && mask_bits != nullptr)
     return launch_relu_grad_bits(dtype, mask_bits, dx, (size_t)p.batch * p.in_rows * p.in_cols * p.channels, s);
   if (mask_pending)
