@@ -2000,7 +2000,7 @@ int launch_gemm_multi(const GemmArgs* list, int count, cudaStream_t s) {
     for (int i = 1; i < count; ++i)
       if (share[i] - floor_ctas[i] > share[big] - floor_ctas[big]) big = i;
     const int step = floor_ctas[big] > 1 ? floor_ctas[big] : 1;
-    if (share[big] - step < floor_ctas[big]) return fail(PDNN_INVALID_PARAMETER, "tensor-core gemm: cannot share the grid");
+    if (share[big] - step < floor_ctas[big]) return kPlanAgain;  // (the caller launches the GEMMs one by one)
     share[big] -= step;
     given -= step;
   }
@@ -2697,14 +2697,16 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
     }
   // The classes of a strided layer write disjoint pixels of dx: side by side in one launch where
   // their kernels agree, else one launch each.
-  if (multi_launchable(planned_classes.data(), (int)planned_classes.size(), sms)) {
-    const int st_ = launch_gemm_multi(planned_classes.data(), (int)planned_classes.size(), s);
-    if (st_ != PDNN_OK) return st_;
-  } else {
+  int together = kPlanAgain;
+  if (multi_launchable(planned_classes.data(), (int)planned_classes.size(), sms))
+    together = launch_gemm_multi(planned_classes.data(), (int)planned_classes.size(), s);
+  if (together == kPlanAgain) {
     for (const GemmArgs& g : planned_classes) {
       const int st_ = launch_gemm(g, dtype, s);
       if (st_ != PDNN_OK) return st_;
     }
+  } else if (together != PDNN_OK) {
+    return together;
   }
   if (mask_pending && mask_bits != nullptr)
     return launch_relu_grad_bits(dtype, mask_bits, dx, (size_t)p.batch * p.in_rows * p.in_cols * p.channels, s);
