@@ -916,7 +916,7 @@ constexpr int kFbpRowsWarps = 8, kFbpRowsBlocks = 3;  // 80 registers per thread
 template <typename T, int ST>
 __global__ void __launch_bounds__(kFbpRowsWarps * 32, kFbpRowsBlocks)
     depthwise_filter_backprop_rows_kernel(const T* __restrict__ x, const T* __restrict__ dy, float* __restrict__ partial,
-                                          PdnnDepthwiseConv2DParams p, int segs, int seg_cols) {
+                                          PdnnDepthwiseConv2DParams p, int segs, int seg_cols, int per_full, int per_tail) {
   constexpr int E = WordOf<T>::E;
   // U output columns per trip: their ST * U new input columns and U dy words are requested together
   // (a warp has to keep a dozen lines in flight to cover the latency), the CARRY columns the next
@@ -925,7 +925,19 @@ __global__ void __launch_bounds__(kFbpRowsWarps * 32, kFbpRowsBlocks)
   __shared__ float red[kFbpRowsWarps][9 * E][32];
   const int F = p.channels, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const unsigned wstride = (unsigned)(F / E);  // 32-bit words per pixel
-  const unsigned lw = min((unsigned)(blockIdx.y * 32 + lane), wstride - 1u);  // idle lanes repeat the last word
+  // The last block of words may be narrow (72 words per pixel leave 8): up to 16 words wide it takes
+  // several rows side by side, rows_here of them, lane = row * words_here + word; otherwise idle lanes
+  // repeat the last word.
+  // The grid is one row of blocks: per_full blocks for each full block of 32 words, per_tail for the last
+  // block of words (which has less to do when it packs rows); block bx of nbx works on word block by and
+  // writes slice bx of the partial sums.
+  const int groups = ((int)wstride + 31) / 32;
+  const int by = min((int)blockIdx.x / per_full, groups - 1), bx = (int)blockIdx.x - by * per_full;
+  const int nbx = by == groups - 1 ? per_tail : per_full;
+  const int first_word = by * 32, words_here = min(32, (int)wstride - first_word);
+  const int rows_here = words_here <= 16 ? 32 / words_here : 1;
+  const int sub = rows_here > 1 ? lane / words_here : 0;
+  const unsigned lw = (unsigned)(first_word + (rows_here > 1 ? lane % words_here : min(lane, words_here - 1)));
   // 32-bit word indices from the tensors' bases (the host only takes this path below 2^32 words)
   const unsigned* __restrict__ xw = reinterpret_cast<const unsigned*>(x);
   const unsigned* __restrict__ dw = reinterpret_cast<const unsigned*>(dy);
@@ -936,14 +948,18 @@ __global__ void __launch_bounds__(kFbpRowsWarps * 32, kFbpRowsBlocks)
     for (int e = 0; e < E; ++e) acc[t][e] = 0.f;
   // A unit of work is one segment (seg_cols columns, a multiple of U) of one output row: whole rows
   // are too coarse to spread evenly over a wave of warps (6.05 rows per warp cost as much as 7).
-  const unsigned units = (unsigned)(p.batch * p.out_rows * segs);
-  for (unsigned u = blockIdx.x * (unsigned)kFbpRowsWarps + (unsigned)warp; u < units; u += gridDim.x * (unsigned)kFbpRowsWarps) {
+  const unsigned all_rows = (unsigned)(p.batch * p.out_rows);
+  const unsigned units = ((all_rows + (unsigned)rows_here - 1u) / (unsigned)rows_here) * (unsigned)segs;
+  for (unsigned u = (unsigned)bx * (unsigned)kFbpRowsWarps + (unsigned)warp; u < units; u += (unsigned)nbx * (unsigned)kFbpRowsWarps) {
     const int seg = (int)(u % (unsigned)segs);
-    const unsigned row = u / (unsigned)segs;
+    const unsigned want_row = (u / (unsigned)segs) * (unsigned)rows_here + (unsigned)sub;
+    // a lane without a row (beyond the last one, or beyond the rows a warp packs) walks the last row and adds zeros
+    const bool dead = sub >= rows_here || want_row >= all_rows;
+    const unsigned row = min(want_row, all_rows - 1u);
     const int oh = (int)(row % (unsigned)p.out_rows), n = (int)(row / (unsigned)p.out_rows);
     const int ow_begin = seg * seg_cols, ow_end = min(ow_begin + seg_cols, p.out_cols);
     const int ih0 = oh * ST - p.pad_rows;
-    const bool rows_inside = ih0 >= 0 && ih0 + 2 < p.in_rows;
+    const bool rows_inside = !dead && ih0 >= 0 && ih0 + 2 < p.in_rows;
     unsigned xrow[3];  // word index of column 0 of the three input rows (clamped into the image)
     bool rok[3];
 #pragma unroll
@@ -1012,7 +1028,7 @@ __global__ void __launch_bounds__(kFbpRowsWarps * 32, kFbpRowsBlocks)
         for (int j = 0; j < NEW; ++j) zero_outside(iw_new + j, win[CARRY + j]);
 #pragma unroll
         for (int uu = 0; uu < U; ++uu)
-          if (ow + uu >= p.out_cols) dv[uu] = 0u;
+          if (dead || ow + uu >= p.out_cols) dv[uu] = 0u;
       }
       if (ow + U < ow_end) fetch(ow + U);
 #pragma unroll
@@ -1032,15 +1048,16 @@ __global__ void __launch_bounds__(kFbpRowsWarps * 32, kFbpRowsBlocks)
 #pragma unroll
     for (int e = 0; e < E; ++e) red[warp][t * E + e][lane] = acc[t][e];
   __syncthreads();
-  for (int i = threadIdx.x; i < 9 * E * 32; i += kFbpRowsWarps * 32) {
-    const int l = i & 31, te = i >> 5, t = te / E, e = te % E;
-    const int ch = (blockIdx.y * 32 + l) * E + e;
-    if (ch < F) {
-      float sum = 0.f;
+  for (int i = threadIdx.x; i < 9 * E * words_here; i += kFbpRowsWarps * 32) {
+    const int wd = i % words_here, te = i / words_here, t = te / E, e = te % E;
+    const int ch = (first_word + wd) * E + e;
+    float sum = 0.f;
+    for (int r = 0; r < rows_here; ++r)
 #pragma unroll
-      for (int w = 0; w < kFbpRowsWarps; ++w) sum += red[w][te][l];
-      partial[((size_t)blockIdx.x * 9 + t) * F + ch] = sum;
-    }
+      for (int w = 0; w < kFbpRowsWarps; ++w) sum += red[w][te][r * words_here + wd];
+    partial[((size_t)bx * 9 + t) * F + ch] = sum;
+    // the slices that only the full word blocks fill hold zeros for these channels
+    for (int slice = bx + nbx; slice < per_full; slice += nbx) partial[((size_t)slice * 9 + t) * F + ch] = 0.f;
   }
 }
 
@@ -1911,17 +1928,20 @@ int launch_fbp_partials(bool vec, const T* in, const T* dy, float* partial, cons
       cudaGetLastError();
       per_sm = 2;
     }
-    const long long wave = std::max(1, per_sm * sms / groups);
+    // the last block of words packs several rows per warp when it is narrow, and gets that much less of the wave
+    const int tail_words = F / E - 32 * (groups - 1), tail_rows = tail_words <= 16 ? 32 / tail_words : 1;
+    const long long wave = std::max<long long>(1, (long long)(per_sm * sms / (groups - 1 + 1.0 / tail_rows)));
     const unsigned gx = (unsigned)std::min<long long>(std::min<long long>(slices, wave), (units + kFbpRowsWarps - 1) / kFbpRowsWarps);
-    dim3 grid(gx, groups);
+    const unsigned g_tail = std::max(1u, (gx + (unsigned)tail_rows - 1u) / (unsigned)tail_rows);
+    dim3 grid(gx * (unsigned)(groups - 1) + g_tail);
     // rows are cut into up to four segments until a warp has a dozen units to walk
     const int trip = p.stride_rows == 1 ? 4 : 2;  // the kernel's U
     int segs = 1;
     while (segs < 4 && units * segs < (long long)gx * kFbpRowsWarps * 12 && (p.out_cols + 2 * segs - 1) / (2 * segs) >= 2 * trip) segs *= 2;
     const int seg_cols = ((p.out_cols + segs - 1) / segs + trip - 1) / trip * trip;
     segs = (p.out_cols + seg_cols - 1) / seg_cols;
-    if (p.stride_rows == 1) depthwise_filter_backprop_rows_kernel<T, 1><<<grid, kFbpRowsWarps * 32, 0, s>>>(in, dy, partial, p, segs, seg_cols);
-    else depthwise_filter_backprop_rows_kernel<T, 2><<<grid, kFbpRowsWarps * 32, 0, s>>>(in, dy, partial, p, segs, seg_cols);
+    if (p.stride_rows == 1) depthwise_filter_backprop_rows_kernel<T, 1><<<grid, kFbpRowsWarps * 32, 0, s>>>(in, dy, partial, p, segs, seg_cols, (int)gx, (int)g_tail);
+    else depthwise_filter_backprop_rows_kernel<T, 2><<<grid, kFbpRowsWarps * 32, 0, s>>>(in, dy, partial, p, segs, seg_cols, (int)gx, (int)g_tail);
     return (int)gx;
   }
   if (fbp_all_taps(p, V)) {
