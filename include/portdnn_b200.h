@@ -123,6 +123,11 @@ typedef struct PdnnConvEpilogue {
                          output element, bit (i % 8) of byte (i / 8) for element i, set where the result is
                          positive - the ReLU mask a later input backprop needs, at a sixteenth of the bytes
                          (PdnnBackpropFusion::relu_bitmask) */
+  int constant_filter; /* non-zero: the caller states that filter and bias were not written by the kernel that
+                          precedes this call in the stream (the weights of a trained network).  The
+                          convolution kernel is launched so that its set-up overlaps the end of that kernel
+                          (programmatic dependent launch) and then waits for it before it touches a tensor;
+                          with this flag it fetches the filter and the bias before that wait.  0 is always safe. */
 } PdnnConvEpilogue;
 
 /* Replaces conv2d::launch -> sublaunch -> launch_{direct,tiled,im2col,winograd,matmul}
@@ -171,6 +176,7 @@ typedef struct PdnnBackpropFusion {
   int output_f32;
   int accumulate;
   const void* relu_bitmask;
+  int constant_filter; /* InputBackprop: as PdnnConvEpilogue::constant_filter, for the filter */
 } PdnnBackpropFusion;
 
 /* As pdnn_conv2d for PDNN_INPUT_BACKPROP / PDNN_FILTER_BACKPROP, with the fused forms described at

@@ -72,12 +72,12 @@ class BatchNormParams(ctypes.Structure):
 
 class _BackpropFusion(ctypes.Structure):
     _fields_ = [("relu_forward_output", ctypes.c_void_p), ("output_f32", ctypes.c_int), ("accumulate", ctypes.c_int),
-                ("relu_bitmask", ctypes.c_void_p)]
+                ("relu_bitmask", ctypes.c_void_p), ("constant_filter", ctypes.c_int)]
 
 
 class _Epilogue(ctypes.Structure):
     _fields_ = [("bias", ctypes.c_void_p), ("activation", ctypes.c_int), ("alpha", ctypes.c_float),
-                ("beta", ctypes.c_float), ("relu_bitmask", ctypes.c_void_p)]
+                ("beta", ctypes.c_float), ("relu_bitmask", ctypes.c_void_p), ("constant_filter", ctypes.c_int)]
 
 
 def library_path():
@@ -189,14 +189,17 @@ def conv2d_workspace_size(pass_, dtype, params, algorithm):
 
 
 def conv2d(pass_, inp, fil, params, algorithm=ALGO_IM2COL, out=None, workspace=None, bias=None, activation=ACT_NONE,
-           alpha=1.0, beta=0.0, relu_forward_output=None, output_f32=False, accumulate=False, relu_bitmask=None):
+           alpha=1.0, beta=0.0, relu_forward_output=None, output_f32=False, accumulate=False, relu_bitmask=None,
+           constant_filter=False):
     """conv2d::launch<T, ConvType>(input, filter, output, params, selector, backend, workspace, size)
     (include/portdnn/conv2d/launch.h:59-72) with the selector's answer passed as ``algorithm``.
     Slots: Forward (x, w) -> y; InputBackprop (dy, w) -> dx; FilterBackprop (x, dy) -> dW.
     bias / activation / alpha / beta select the fused forward epilogue; relu_forward_output and accumulate
     (InputBackprop: dx += ..., then the mask; FilterBackprop: dW += ...) and output_f32 (FilterBackprop) the fused backprop forms of
     PdnnBackpropFusion.  relu_bitmask: a uint8 tensor of one bit per element (numel / 8 bytes) - written by
-    the forward pass beside its output, read by the input backprop in place of relu_forward_output."""
+    the forward pass beside its output, read by the input backprop in place of relu_forward_output.
+    constant_filter (Forward, InputBackprop): filter and bias were not written by the kernel that precedes this
+    call in the stream, so the kernel may fetch them while that kernel is still finishing."""
     torch = _torch()
     _require_cuda(inp, fil, out, workspace, bias)
     n_in, n_fil, n_out = conv_sizes(pass_, params)
@@ -209,7 +212,8 @@ def conv2d(pass_, inp, fil, params, algorithm=ALGO_IM2COL, out=None, workspace=N
         n_bits = n_out  # forward: the output's mask; input backprop: the mask of dx
         if relu_bitmask.dtype != torch.uint8 or relu_bitmask.numel() * 8 != n_bits:
             raise ValueError("relu_bitmask must be a uint8 tensor of one bit per element")
-    backprop_fused = relu_forward_output is not None or output_f32 or accumulate or (relu_bitmask is not None and pass_ != FORWARD)
+    backprop_fused = (relu_forward_output is not None or output_f32 or accumulate or
+                      (relu_bitmask is not None and pass_ != FORWARD) or (constant_filter and pass_ == INPUT_BACKPROP))
     if backprop_fused and (pass_ == FORWARD or (relu_forward_output is not None and pass_ != INPUT_BACKPROP) or
                            (output_f32 and pass_ != FILTER_BACKPROP)):
         raise ValueError("relu_forward_output belongs to the input backprop, output_f32 to the filter backprop")
@@ -226,17 +230,18 @@ def conv2d(pass_, inp, fil, params, algorithm=ALGO_IM2COL, out=None, workspace=N
             raise ValueError("relu_forward_output must have the shape of the input gradient")
         fus = _BackpropFusion(relu_forward_output.data_ptr() if relu_forward_output is not None else None, int(output_f32),
                               int(accumulate),  # accumulate: False / True, or 2 (dx already carries the mask)
-                              relu_bitmask.data_ptr() if relu_bitmask is not None else None)
+                              relu_bitmask.data_ptr() if relu_bitmask is not None else None, int(bool(constant_filter)))
         _check(lib().pdnn_conv2d_backprop_fused(pass_, _dtype_code(inp), _ptr(inp), _ptr(fil), _ptr(out),
                                                 ctypes.byref(params), algorithm, ctypes.byref(fus), _ptr(workspace),
                                                 ctypes.c_size_t(ws_elems), _stream()))
         return out
-    fused = bias is not None or activation != ACT_NONE or alpha != 1.0 or beta != 0.0 or relu_bitmask is not None
+    fused = (bias is not None or activation != ACT_NONE or alpha != 1.0 or beta != 0.0 or relu_bitmask is not None or
+             (constant_filter and pass_ == FORWARD))
     if fused:
         if pass_ != FORWARD:
             raise ValueError("the fused epilogue exists for the forward pass only")
         epi = _Epilogue(bias.data_ptr() if bias is not None else None, activation, alpha, beta,
-                        relu_bitmask.data_ptr() if relu_bitmask is not None else None)
+                        relu_bitmask.data_ptr() if relu_bitmask is not None else None, int(bool(constant_filter)))
         st = lib().pdnn_conv2d_fused(_dtype_code(inp), _ptr(inp), _ptr(fil), _ptr(out), ctypes.byref(params), algorithm,
                                      ctypes.byref(epi), _ptr(workspace), ctypes.c_size_t(ws_elems), _stream())
     else:

@@ -127,6 +127,9 @@ struct alignas(64) GemmArgs {
   void* bitmask_out;
   const void* mask_bits;
   int mask_slots;        // 4 KB mask slots per epilogue warp: 2 where shared memory allows, else 1
+  // 1: the filter (the resident B copy) and the bias are known not to be written by the kernel that
+  // precedes this one in the stream: they are fetched before the wait for that kernel
+  int early_b;
   int accumulate;  // packed 16-bit epilogues, no bias: the block already in the output is added (before the mask)
   int reduce_add;  // staged fp32 epilogue of the filter backprop: every pixel split adds its tile to the output
   int mask_smem_bytes;  // the barriers of the epilogue warps' mask slots (the slots themselves follow the staging slices)
@@ -709,18 +712,67 @@ __device__ __forceinline__ void umma_gemm_body(const GemmArgs& a, const int cta,
   // kernel touches tensors that kernel may have written (or may still be reading), so it waits
   // for it.  The next kernel may be scheduled as soon as SMs free up: this grid is a single wave,
   // so nothing of it is still waiting for an SM.
+  const int total_tiles = a.a_mn ? a.n_tiles * a.tiles_w * ((a.num_taps + a.tap_pack - 1) / a.tap_pack) * a.splits
+                                 : a.n_tiles * a.tiles_w * a.tiles_h * a.tiles_n;
+  // one B tile of a forward-style GEMM (a_mn == 0): reduction block kc of tap btap, columns from nf0
+  auto load_b_from = [&](const CUtensorMap* bmap, uint32_t sb, uint32_t fb, int kc, int nf0, int btap) {
+    const int epr = a.epr;
+    switch (a.b_mode) {
+      case B_MN_3X: warp_tma_load_4d(sb, bmap, fb, 0, kc, nf0 / epr, btap); break;
+      case B_MN_3:
+#pragma unroll 1
+        for (int j = 0; j < a.b_boxes; ++j)
+          warp_tma_load_4d(sb + (uint32_t)j * a.b_box_bytes, bmap, fb, nf0 + j * epr, kc, btap, 0);
+        break;
+      case B_K_3: warp_tma_load_4d(sb, bmap, fb, kc, nf0, btap, 0); break;
+      case B_K_FHWC: warp_tma_load_4d(sb, bmap, fb, kc, btap, nf0, 0); break;
+      default:  // B_MN_FHWC
+#pragma unroll 1
+        for (int j = 0; j < a.b_boxes; ++j)
+          warp_tma_load_4d(sb + (uint32_t)j * a.b_box_bytes, bmap, fb, nf0 + j * epr, btap, kc, 0);
+        break;
+    }
+  };
+  // the whole B operand of the CTA's column tiles into the resident area (called by one warp)
+  auto load_resident_b = [&] {
+    warp_arrive_expect_tx(bres_bar, res_bytes);
+    uint32_t dst = base;
+    const int nt_begin = a.b_res == 2 ? cta % a.n_tiles : 0;
+    const int nt_end = a.b_res == 2 ? nt_begin + 1 : a.n_tiles;
+#pragma unroll 1
+    for (int nt = nt_begin; nt < nt_end; ++nt)
+#pragma unroll 1
+      for (int tap = 0; tap < a.num_taps; ++tap) {
+        const TapEntry e = a.taps[tap];
+        const int cnt = halo ? e.cnt : 1;
+#pragma unroll 1
+        for (int g = 0; g < cnt; ++g)
+#pragma unroll 1
+          for (int cb = 0, kc = 0; cb < a.cblocks; ++cb, kc += a.epr, dst += b_bytes)
+            load_b_from(&a.b_map, dst, bres_bar, kc, nt * a.bn, e.b_tap + g * e.b_step);
+      }
+  };
+  auto copy_bias = [&] {
+    if (EPI >= 2 && a.bias != nullptr) {
+      // the CTA's copy of the bias vector, zero beyond the last column
+      const OutT* bias = static_cast<const OutT*>(a.bias);
+      uint4* dst = reinterpret_cast<uint4*>(bar_mem + kBarBlockBytes);
+      const int chunks = a.bias_smem_bytes >> 4;
+      for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
+        const int col = bias_col0 + i * 8;
+        dst[i] = (col + 8 <= a.ext_cols) ? __ldg(reinterpret_cast<const uint4*>(bias + col)) : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+  const bool early_b = !SPLIT && a.early_b != 0;
+  if (early_b) {
+    __syncthreads();  // the barrier of the resident copy is initialised
+    if (warp == 0 && b_res && cta < total_tiles) load_resident_b();
+    copy_bias();
+  }
   grid_dependency_wait();
   grid_launch_dependents();
-  if (EPI >= 2 && a.bias != nullptr) {
-    // the CTA's copy of the bias vector, zero beyond the last column
-    const OutT* bias = static_cast<const OutT*>(a.bias);
-    uint4* dst = reinterpret_cast<uint4*>(bar_mem + kBarBlockBytes);
-    const int chunks = a.bias_smem_bytes >> 4;
-    for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
-      const int col = bias_col0 + i * 8;
-      dst[i] = (col + 8 <= a.ext_cols) ? __ldg(reinterpret_cast<const uint4*>(bias + col)) : make_uint4(0u, 0u, 0u, 0u);
-    }
-  }
+  if (!early_b) copy_bias();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -729,8 +781,6 @@ __device__ __forceinline__ void umma_gemm_body(const GemmArgs& a, const int cta,
   const uint32_t acc_bufs = (uint32_t)a.acc_bufs, acc_stride = (uint32_t)a.acc_stride;
   const uint32_t grp_tmem = tmem_base + (uint32_t)grp * acc_bufs * acc_stride;
 
-  const int total_tiles = a.a_mn ? a.n_tiles * a.tiles_w * ((a.num_taps + a.tap_pack - 1) / a.tap_pack) * a.splits
-                                 : a.n_tiles * a.tiles_w * a.tiles_h * a.tiles_n;
   // pair mode: both groups walk the same tiles (each takes one row tile of the pair)
   const int first_tile = cta + (pair ? 0 : grp * n_ctas);
   const int tile_step = (pair ? 1 : groups) * n_ctas;
@@ -762,43 +812,8 @@ __device__ __forceinline__ void umma_gemm_body(const GemmArgs& a, const int cta,
       const int pair_dw = a.pair_dim == 1 ? a.tw : 0, pair_dh = a.pair_dim == 2 ? a.th : 0,
                 pair_dn = a.pair_dim == 3 ? a.tn : 0;
       const CUtensorMap* bmap = &a.b_map;
-      // one B tile of a forward-style GEMM (a_mn == 0): reduction block kc of tap btap, columns from nf0
-      auto load_b_from = [&](const CUtensorMap* bmap, uint32_t sb, uint32_t fb, int kc, int nf0, int btap) {
-        switch (b_mode) {
-          case B_MN_3X: warp_tma_load_4d(sb, bmap, fb, 0, kc, nf0 / epr, btap); break;
-          case B_MN_3:
-#pragma unroll 1
-            for (int j = 0; j < b_boxes; ++j)
-              warp_tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, nf0 + j * epr, kc, btap, 0);
-            break;
-          case B_K_3: warp_tma_load_4d(sb, bmap, fb, kc, nf0, btap, 0); break;
-          case B_K_FHWC: warp_tma_load_4d(sb, bmap, fb, kc, btap, nf0, 0); break;
-          default:  // B_MN_FHWC
-#pragma unroll 1
-            for (int j = 0; j < b_boxes; ++j)
-              warp_tma_load_4d(sb + (uint32_t)j * b_box_bytes, bmap, fb, nf0 + j * epr, btap, kc, 0);
-            break;
-        }
-      };
       auto load_b = [&](uint32_t sb, uint32_t fb, int kc, int nf0, int btap) { load_b_from(bmap, sb, fb, kc, nf0, btap); };
-      if (b_res && grp == 0 && cta < total_tiles) {
-        warp_arrive_expect_tx(bres_bar, res_bytes);
-        uint32_t dst = base;
-        const int nt_begin = a.b_res == 2 ? cta % a.n_tiles : 0;
-        const int nt_end = a.b_res == 2 ? nt_begin + 1 : a.n_tiles;
-#pragma unroll 1
-        for (int nt = nt_begin; nt < nt_end; ++nt)
-#pragma unroll 1
-          for (int tap = 0; tap < a.num_taps; ++tap) {
-            const TapEntry e = a.taps[tap];
-            const int cnt = halo ? e.cnt : 1;
-#pragma unroll 1
-            for (int g = 0; g < cnt; ++g)
-#pragma unroll 1
-              for (int cb = 0, kc = 0; cb < cblocks; ++cb, kc += epr, dst += b_bytes)
-                load_b(dst, bres_bar, kc, nt * a.bn, e.b_tap + g * e.b_step);
-          }
-      }
+      if (b_res && !early_b && grp == 0 && cta < total_tiles) load_resident_b();
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -2413,6 +2428,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     g.idesc = make_idesc(dtype == PDNN_BF16 ? 1 : 0, 0, 1, 256, 256);
   const uint32_t abox[4] = {(uint32_t)epr, (uint32_t)g.tw, (uint32_t)(halo ? g.th + p.window_rows - 1 : g.th),
                             (uint32_t)g.tn};
+  g.early_b = (epi != nullptr && epi->constant_filter != 0 && dtype != PDNN_F32) ? 1 : 0;
   if (!make_parity_maps(g, dtype, false, x, p, abox, x_ld)) return PDNN_INVALID_PARAMETER;
   // taps
   int nt = 0;
@@ -2501,7 +2517,7 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
 // carries the same mask, so that positions this convolution does not reach (parity classes without a
 // tap) are left as they are.
 int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, const PdnnConv2DParams& p,
-                        const void* relu_mask, const void* mask_bits, int accumulate, cudaStream_t s,
+                        const void* relu_mask, const void* mask_bits, int accumulate, bool constant_filter, cudaStream_t s,
                         bool try_halo = true) {
   bool mask_pending = false;  // some parity class could not apply the mask in its epilogue
   const size_t es = dtype_size(dtype);
@@ -2538,6 +2554,7 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
       GemmArgs g;
       std::memset(&g, 0, sizeof(g));
       g.a_mn = 0;
+      g.early_b = (constant_filter && dtype != PDNN_F32) ? 1 : 0;
       // Stride 1: the taps of one window column read overlapping rows of dy, as in the forward
       // pass (halo mode), if the whole filter can stay in shared memory.
       int hw = 0, hh = 0;
@@ -2685,7 +2702,7 @@ int conv_input_backprop(int dtype, const void* dy, const void* w, void* dx, cons
           planned = setup_store(g, dtype, od, os);
         }
         if (!planned) {
-          if (g.halo || g.pair) return conv_input_backprop(dtype, dy, w, dx, p, relu_mask, mask_bits, accumulate, s, false);  // plan again without the halo / pairing
+          if (g.halo || g.pair) return conv_input_backprop(dtype, dy, w, dx, p, relu_mask, mask_bits, accumulate, constant_filter, s, false);  // plan again without the halo / pairing
           return PDNN_INVALID_PARAMETER;
         }
       }
@@ -3173,7 +3190,7 @@ int tc_conv2d(int pass, int dtype, const void* in, const void* fil, void* out, c
       return conv_forward(dtype, in, fil, out, p, epi, s);
     case PDNN_INPUT_BACKPROP:
       return conv_input_backprop(dtype, in, fil, out, p, relu_mask, fusion != nullptr ? fusion->relu_bitmask : nullptr,
-                                 accumulate, s);
+                                 accumulate, fusion != nullptr && fusion->constant_filter != 0, s);
     case PDNN_FILTER_BACKPROP:
       if (small_c_applicable(dtype, p)) {
         const int st = conv_filter_backprop_small_c(dtype, in, fil, out, p, out_f32, accumulate != 0, ws, ws_elems, s);

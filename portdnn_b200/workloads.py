@@ -244,7 +244,8 @@ class ConvStackRunner:
         if isinstance(l, ConvLayer):
             api.conv2d(api.FORWARD, self._in(i), self.weights[i], p, algorithm=api.ALGO_IM2COL, out=self._out(i),
                        bias=self.biases[i], activation=l.activation, workspace=self.workspaces.get(i),
-                       relu_bitmask=self.bits.get(i) if self.training else None)
+                       relu_bitmask=self.bits.get(i) if self.training else None,
+                       constant_filter=True)  # the weights are not written inside a step
         else:
             api.pooling(l.op, 0, self._in(i), p, out=self._out(i))
 
@@ -374,7 +375,7 @@ class ConvStackRunner:
                         api.conv2d(api.INPUT_BACKPROP, g, self.weights[i], p, algorithm=api.ALGO_IM2COL, out=dst,
                                    relu_forward_output=mask if (masked and bits is None) else None,
                                    relu_bitmask=bits if masked else None,
-                                   accumulate=(2 if mask is not None else 1) if accumulate else 0)
+                                   accumulate=(2 if mask is not None else 1) if accumulate else 0, constant_filter=True)
 
                     self._add_grad(j, ibp)
                     if mask is not None:

@@ -87,6 +87,26 @@ def test_forward_fused_epilogue(orc, dtype):
     assert rel_err(to_host(out), ref) <= TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+@pytest.mark.parametrize("shape", [(2, 28, 28, 512, 128, 1, 1), (3, 14, 14, 256, 256, 3, 1), (2, 56, 56, 128, 128, 3, 2),
+                                   (2, 56, 56, 64, 256, 1, 1)])
+def test_constant_filter_changes_nothing_but_the_schedule(orc, dtype, shape):
+    """constant_filter only moves the fetch of filter and bias ahead of the wait for the preceding kernel
+    (resident-filter plans of the forward pass and the input backprop): the results are bit for bit the same."""
+    n, h, w, c, k, win, st = shape
+    p, po, x, wt, dy = _conv_case(orc, dtype, n, h, w, c, k, win, st)
+    bias = to_dev(rounded(np.random.default_rng(2).standard_normal(k).astype(np.float32), dtype), dtype)
+    xd, wd, dyd = to_dev(x, dtype), to_dev(wt, dtype), to_dev(dy, dtype)
+    plain = pd.conv2d(pd.FORWARD, xd, wd, p, bias=bias, activation=pd.ACT_RELU)
+    early = pd.conv2d(pd.FORWARD, xd, wd, p, bias=bias, activation=pd.ACT_RELU, constant_filter=True)
+    assert torch.equal(plain, early)
+    plain = pd.conv2d(pd.INPUT_BACKPROP, dyd, wd, p)
+    early = pd.conv2d(pd.INPUT_BACKPROP, dyd, wd, p, constant_filter=True)
+    assert torch.equal(plain, early)
+    assert_no_device_error()
+    assert rel_err(to_host(early), orc.conv2d(orc.INPUT_BACKPROP, dy, wt, po)) <= TOL[dtype]
+
+
 GROUPED_SHAPES = [
     # n, h, w, c, k, window, stride, groups
     (2, 14, 14, 64, 128, 3, 1, 2),
