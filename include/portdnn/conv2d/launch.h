@@ -42,6 +42,8 @@ struct FusedEpilogue {
   int activation = PDNN_ACT_NONE;
   float alpha = 1.f;
   float beta = 0.f;
+  void* relu_bitmask = nullptr;  // PdnnConvEpilogue::relu_bitmask
+  bool constant_filter = false;  // PdnnConvEpilogue::constant_filter
 };
 
 template <typename T, typename ConvType, typename Backend>
@@ -69,7 +71,8 @@ template <typename T, typename Backend>
 SNNStatus launch_fused(T const* input, T const* filter, T* output, Conv2DParams const& params, Selector& selector,
                        Backend& backend, FusedEpilogue const& epilogue, T* workspace = nullptr, size_t workspace_size = 0) {
   const Algorithm algo = selector.select<conv_type::Forward>(params);
-  const PdnnConvEpilogue e{epilogue.bias, epilogue.activation, epilogue.alpha, epilogue.beta};
+  const PdnnConvEpilogue e{epilogue.bias,         epilogue.activation, epilogue.alpha, epilogue.beta,
+                           epilogue.relu_bitmask, epilogue.constant_filter ? 1 : 0};
   const int st = pdnn_conv2d_fused(backend::dtype_of<T>::value, input, filter, output,
                                    reinterpret_cast<const PdnnConv2DParams*>(&params), int(algo), &e, workspace,
                                    workspace_size, backend.get_queue());
