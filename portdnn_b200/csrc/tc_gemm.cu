@@ -2094,8 +2094,9 @@ bool make_parity_maps(GemmArgs& g, int dtype, bool mn_major, const void* x, cons
 }
 
 // Output side of a forward convolution: y is [N, Ho, Wo, K].
+// plan_out (may be null): the finished plan is stored there instead of being launched.
 int finish_forward(GemmArgs& g, int dtype, void* y, const PdnnConv2DParams& p, const PdnnConvEpilogue* epi,
-                   cudaStream_t s, int y_ld = 0) {
+                   cudaStream_t s, int y_ld = 0, GemmArgs* plan_out = nullptr) {
   const size_t es = dtype_size(dtype);
   const long long ld = y_ld > 0 ? y_ld : p.features;
   set_epilogue(g, epi);
@@ -2112,6 +2113,10 @@ int finish_forward(GemmArgs& g, int dtype, void* y, const PdnnConv2DParams& p, c
   const uint64_t od[4] = {(uint64_t)p.features, (uint64_t)p.out_cols, (uint64_t)p.out_rows, (uint64_t)p.batch};
   const uint64_t os[3] = {(uint64_t)ld * es, (uint64_t)p.out_cols * ld * es, (uint64_t)p.out_rows * p.out_cols * ld * es};
   if (!setup_store(g, dtype, od, os)) return (g.halo || g.pair) ? kPlanAgain : PDNN_INVALID_PARAMETER;
+  if (plan_out != nullptr) {
+    *plan_out = g;
+    return PDNN_OK;
+  }
   return launch_gemm(g, dtype, s);
 }
 
@@ -2345,7 +2350,8 @@ __global__ void __launch_bounds__(256) split_lo_kernel(const float* __restrict__
 
 int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnConv2DParams& p,
                  const PdnnConvEpilogue* epi, cudaStream_t s, bool try_halo = true, bool try_cta_pair = true,
-                 const ConvLd* ld = nullptr) {
+                 const ConvLd* ld = nullptr, GemmArgs* plan_out = nullptr) {
+  if (plan_out != nullptr && dtype == PDNN_F32) return PDNN_INVALID_PARAMETER;  // (the fp32 plan owns scratch)
   const int x_ld = ld != nullptr ? ld->x : 0, y_ld = ld != nullptr ? ld->y : 0;
   const uint64_t w_ld = ld != nullptr && ld->w > 0 ? (uint64_t)ld->w : (uint64_t)p.features;
   GemmArgs g;
@@ -2502,11 +2508,11 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     if (w_split != nullptr) cudaFreeAsync(w_split, s);
     return PDNN_INVALID_PARAMETER;
   }
-  const int status = finish_forward(g, dtype, y, p, epi, s, y_ld);
+  const int status = finish_forward(g, dtype, y, p, epi, s, y_ld, plan_out);
   if (w_split != nullptr) cudaFreeAsync(w_split, s);
   if (status == kPlanAgain)  // first without the CTA pairs, then without halo / pair mode
-    return g.cta_pair ? conv_forward(dtype, x, w, y, p, epi, s, try_halo, false, ld)
-                      : conv_forward(dtype, x, w, y, p, epi, s, false, false, ld);
+    return g.cta_pair ? conv_forward(dtype, x, w, y, p, epi, s, try_halo, false, ld, plan_out)
+                      : conv_forward(dtype, x, w, y, p, epi, s, false, false, ld, plan_out);
   return status;
 }
 
@@ -3141,6 +3147,21 @@ int tc_grouped_conv_forward(int dtype, const void* in, const void* fil, void* ou
   const bool hwcf = p.filter_format == 0;
   const ConvLd ld{p.channels, hwcf ? p.features : 0, p.features};
   const size_t fhwc_group = (size_t)q.features * p.window_rows * p.window_cols * q.channels;
+  // 16-bit: the groups are planned first and launched four at a time, side by side (umma_gemm_multi_kernel):
+  // a group is a small GEMM that rarely fills the device on its own.
+  const int sms = device_sm_count();
+  GemmArgs plans[kMaxMulti];
+  int planned = 0;
+  auto flush = [&]() -> int {
+    int st = kPlanAgain;
+    if (multi_launchable(plans, planned, sms)) st = launch_gemm_multi(plans, planned, s);
+    if (st == kPlanAgain) {
+      st = PDNN_OK;
+      for (int i = 0; i < planned && st == PDNN_OK; ++i) st = launch_gemm(plans[i], dtype, s);
+    }
+    planned = 0;
+    return st;
+  };
   for (int g = 0; g < p.groups; ++g) {
     PdnnConvEpilogue e;
     if (epi != nullptr) {
@@ -3150,10 +3171,16 @@ int tc_grouped_conv_forward(int dtype, const void* in, const void* fil, void* ou
     const char* xg = static_cast<const char*>(in) + (size_t)g * q.channels * es;
     const char* wg = static_cast<const char*>(fil) + (hwcf ? (size_t)g * q.features : (size_t)g * fhwc_group) * es;
     char* yg = static_cast<char*>(out) + (size_t)g * q.features * es;
-    const int st = conv_forward(dtype, xg, wg, yg, q, epi != nullptr ? &e : nullptr, s, true, true, &ld);
+    const bool plan_only = dtype != PDNN_F32;
+    const int st = conv_forward(dtype, xg, wg, yg, q, epi != nullptr ? &e : nullptr, s, true, true, &ld,
+                                plan_only ? &plans[planned] : nullptr);
     if (st != PDNN_OK) return st;
+    if (plan_only && ++planned == kMaxMulti) {
+      const int fs = flush();
+      if (fs != PDNN_OK) return fs;
+    }
   }
-  return PDNN_OK;
+  return planned > 0 ? flush() : PDNN_OK;
 }
 
 size_t tc_conv_workspace_elems(int pass, int dtype, const PdnnConv2DParams& p) {
