@@ -1493,6 +1493,11 @@ __global__ void __launch_bounds__(kStripBlock, 3)
   constexpr int SLOTS = PF + 1;
   constexpr uint32_t kPacketPitch = kStripBlock * 16;  // bytes between two packets of one thread
   extern __shared__ uint4 dw_async_smem[];
+  // Launched with programmatic stream serialization: the blocks are placed while the preceding kernel of the
+  // stream is finishing and wait here for its results; the next kernel may be placed as soon as the last of
+  // these blocks has started.  (Both are no-ops under an ordinary launch.)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const size_t idx = (size_t)blockIdx.x * kStripBlock + threadIdx.x;
   if (idx >= n_threads) return;
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dw_async_smem) + threadIdx.x * 16u;
@@ -1621,7 +1626,20 @@ bool launch_depthwise3_async(const T* x, const T* w, T* y, const StripGeometry& 
     }
     attr_set[dev] = true;
   }
-  kernel<<<blocks, kStripBlock, kSmem, s>>>(x, w, y, g, n_threads);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(kStripBlock);
+  cfg.dynamicSmemBytes = kSmem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, x, w, y, g, n_threads) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
   return true;
 }
 
