@@ -401,6 +401,12 @@ def run_layer_mode(args):
     for e0, e1 in evs:
         ms = e0.elapsed_time(e1)
         print("ms %.4f  TFLOP/s %.1f" % (ms, flops / ms / 1e9))
+    # a single launch bracketed by events includes the launch latency of an idle device (tens of microseconds
+    # for the short layers); 20 launches replayed as a CUDA graph give the time of the kernel itself
+    graph = capture_graph(torch, lambda: [run() for _ in range(20)])
+    graph.replay()
+    ms = timed(torch, graph.replay, 3) / 20
+    print("graph replay of 20 launches: ms %.4f  TFLOP/s %.1f" % (ms, flops / ms / 1e9))
     print("device error record", pd.device_error_record())
 
 

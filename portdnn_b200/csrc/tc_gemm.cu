@@ -2427,6 +2427,12 @@ int conv_forward(int dtype, const void* x, const void* w, void* y, const PdnnCon
     if (dtype != PDNN_F32 && !halo && p.window_rows * p.window_cols == 1 &&
         ksteps_all >= 16 && p.features == 256 && row_tiles >= 2 * sms)
       g.bn = 256;
+    // One or two reduction steps over pixels narrower than 64 bytes (MobileNet-v2's 24 -> 144 expansions):
+    // with two column tiles the input tile is fetched twice, and fetching such short rows is what the layer
+    // spends its time on; one wide tile reads it once (measured 0.053 -> 0.035 ms on 56x56x24 -> 144; layers
+    // with 32 and more channels do not care, 64 -> 256 is 2% better with two tiles).
+    if (dtype != PDNN_F32 && !halo && ksteps_all <= 2 && p.features > 128 && p.features <= 256 && p.channels * es < 64)
+      g.bn = ceil_div(p.features, 64) * 64;
   }
   g.n_tiles = ceil_div(p.features, g.bn);
   set_operand_layout(g, dtype, hwcf ? 1 : 0);
