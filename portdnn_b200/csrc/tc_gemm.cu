@@ -2019,6 +2019,19 @@ int launch_gemm_multi(const GemmArgs* list, int count, cudaStream_t s) {
     share[big] -= step;
     given -= step;
   }
+  // ... and SMs that the rounding left over go to the GEMM with the most work per CTA
+  while (given < sms) {
+    int best = -1;
+    for (int i = 0; i < count; ++i) {
+      const int step = floor_ctas[i] > 1 ? floor_ctas[i] : 1;
+      if (given + step > sms || share[i] + step > gemm_total_tiles(list[i])) continue;
+      if (best < 0 || work[i] / share[i] > work[best] / share[best]) best = i;
+    }
+    if (best < 0) break;
+    const int step = floor_ctas[best] > 1 ? floor_ctas[best] : 1;
+    share[best] += step;
+    given += step;
+  }
   m.first_cta[0] = 0;
   for (int i = 0; i < count; ++i) m.first_cta[i + 1] = m.first_cta[i] + share[i];
   for (int i = count + 1; i <= kMaxMulti; ++i) m.first_cta[i] = m.first_cta[count];
